@@ -1,0 +1,151 @@
+/*
+ * sbk.h -- C ABI of libsbk.so: the B200 (sm_100a) kernels behind the hybrid
+ * decode-time cache path of SpikingBrain-7B (sliding-window paged KV + GLA
+ * recurrent state).
+ *
+ * Conventions
+ *  - Every pointer is a DEVICE pointer unless the name ends in `_host`.
+ *  - The library allocates nothing, keeps no pointer after a call returns and
+ *    never synchronises; every launch is ordered on `stream` (a cudaStream_t
+ *    passed as void*; NULL = the legacy default stream).
+ *  - Return value: 0 on success, a negative SBK_E_* code when the host can see
+ *    that the arguments are wrong (nothing is launched); sbk_last_error()
+ *    then returns a thread-local description.
+ *  - Device-side violations (a slot or block id outside the pool) never trap:
+ *    the offending work item is skipped and a bit is OR-ed into `*status`
+ *    (a device int32 the caller zeroes and reads when it wishes; may be NULL).
+ *  - Element types are given as SBK_BF16 / SBK_F32 codes.
+ *
+ * Citations name the file of BICLab/SpikingBrain-7B whose call the entry point
+ * stands in for.
+ */
+#ifndef SBK_H_
+#define SBK_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define SBK_ABI_VERSION 1
+
+/* element type codes */
+#define SBK_BF16 0
+#define SBK_F32 1
+
+/* host-side error codes (return values) */
+#define SBK_OK 0
+#define SBK_E_ARG (-1)      /* bad shape / null pointer / unsupported combination */
+#define SBK_E_ALIGN (-2)    /* a pointer or stride breaks the 16-byte rule */
+#define SBK_E_WORKSPACE (-3) /* workspace too small */
+#define SBK_E_LAUNCH (-4)   /* cudaGetLastError() after the launch was not cudaSuccess */
+
+/* device-side status bits (OR-ed into *status) */
+#define SBK_ST_BAD_SLOT 1      /* slot id >= num_blocks*block_size: token not written */
+#define SBK_ST_BAD_BLOCK 2     /* block-table entry outside [0,num_blocks) inside the window */
+#define SBK_ST_WAIT_TIMEOUT 4  /* a bounded in-kernel wait ran out; result of that CTA invalid */
+#define SBK_ST_RETIRE_OVERFLOW 8 /* more blocks left the window than retired_out has columns */
+
+int sbk_abi_version(void);
+const char* sbk_last_error(void);
+
+/*
+ * Paged-KV append with sliding-window block retirement.
+ * Stands in for torch.ops._C_cache_ops.reshape_and_cache_flash as called at
+ * vllm_hymeta/attention/meta_attention.py:790-799 (kv_cache_dtype "auto": a
+ * plain copy), and for the block retirement the reference leaves to vLLM's
+ * block manager behind the window-truncated block table of
+ * meta_attention.py:479-485.
+ *
+ *  key,value     [T, kvh, D] rows of `elem_bytes`-wide elements; token stride
+ *                `kv_token_stride_bytes` (>= kvh*D*elem_bytes)
+ *  k_cache,v_cache  [num_blocks, block_size, kvh, D]; `cache_block_stride_bytes`
+ *                between blocks, rows of one block contiguous
+ *  slot_mapping  [T] int64 flat slot = block*block_size + offset; negative = skip
+ *                (PAD_SLOT_ID, meta_attention.py:558)
+ * Retirement (skipped when block_tables == NULL):
+ *  block_tables  [B, max_blocks] int32, MUTATED: entries of logical blocks that
+ *                lie wholly before the window are replaced by -1
+ *  seq_lens      [B] int32 length of each sequence INCLUDING the appended tokens
+ *  query_start_loc [B+1] int32 or NULL (NULL: one new token per sequence)
+ *  window_left   keys visible to the left of a query (-1: unbounded, nothing retires).
+ *                The first token still needed is max(0, seq_len - n_new - window_left).
+ *  retired_out   [B, max_retired] int32: ids that left the window this call, in
+ *                logical order, padded with -1 (may be NULL: only the table is edited)
+ */
+int sbk_kv_append(const void* key, const void* value, void* k_cache, void* v_cache,
+                  const int64_t* slot_mapping, int T, int kvh, int D, int elem_bytes,
+                  int64_t kv_token_stride_bytes, int64_t num_blocks, int block_size,
+                  int64_t cache_block_stride_bytes,
+                  int32_t* block_tables, int max_blocks, const int32_t* seq_lens,
+                  const int32_t* query_start_loc, int B, int window_left,
+                  int32_t* retired_out, int max_retired,
+                  int32_t* status, void* stream);
+
+/*
+ * Gather the in-window tokens of every sequence through the block table into
+ * dense head-first tensors [B, kvh, n_out, D] -- the tensors the reference's
+ * Cache.update returns as `attn_state` (hf_7B_model/cache.py:94-108).
+ * Row i of sequence b is token t0+i, t0 = max(0, seq_len-1-window_left);
+ * rows past the visible length are zero-filled.
+ */
+int sbk_kv_gather(const void* k_cache, const void* v_cache, const int32_t* block_tables,
+                  int max_blocks, const int32_t* seq_lens, int B, int kvh, int D,
+                  int elem_bytes, int64_t num_blocks, int block_size,
+                  int64_t cache_block_stride_bytes, int window_left,
+                  void* k_out, void* v_out, int n_out,
+                  int32_t* status, void* stream);
+
+/*
+ * Sliding-window paged-attention decode (one query token per sequence).
+ * Stands in for flash_attn_cuda.fwd_kvcache as reached from
+ * meta_attention.py:955-981 through fa_kernel_metatoken.py:84-105
+ * (causal, window (window_left, -1), no alibi, no softcap, key2 == None).
+ *
+ *  q            [B, H, D] bf16, `q_seq_stride` elements between sequences
+ *  k_cache,v_cache [num_blocks, block_size, kvh, D] bf16 (rows of a block contiguous)
+ *  block_tables [B, max_blocks] int32; seq_lens [B] int32 (query is token seq_len-1)
+ *  window_left  keys visible left of the query (-1 = all)
+ *  out          [B, H, D] of `out_dtype` (SBK_BF16 or SBK_F32), `out_seq_stride` elements
+ *  lse_out      [B, H] float natural-log-sum-exp of the scaled scores, or NULL
+ *  workspace    split-K partials; at least sbk_swa_workspace_bytes(B,H,D,max_pieces) bytes
+ *  split_chunks target number of 16-token chunks per split (<=0: library default)
+ *  max_pieces   upper bound on splits per sequence (grid.x); >= 1
+ * Supported: D == 128, H % kvh == 0, H/kvh <= 8, kvh in {1,2,4}, block_size % 16 == 0.
+ */
+size_t sbk_swa_workspace_bytes(int B, int H, int D, int max_pieces);
+int sbk_swa_decode(const void* q, int64_t q_seq_stride, const void* k_cache, const void* v_cache,
+                   const int32_t* block_tables, int max_blocks, const int32_t* seq_lens,
+                   int B, int H, int kvh, int D, int64_t num_blocks, int block_size,
+                   int64_t cache_block_stride_bytes, int window_left, float scale,
+                   void* out, int out_dtype, int64_t out_seq_stride, float* lse_out,
+                   void* workspace, size_t workspace_bytes, int split_chunks, int max_pieces,
+                   int32_t* status, void* stream);
+
+/*
+ * Fused GLA recurrent-state step, in place in the slot cache:
+ *    S[slot] <- diag(exp(g)) . S[slot] + k^T v ;   o = (q*scale) . S[slot]
+ * Stands in for my_fused_recurrent_gla
+ * (vllm_hymeta/model_for_7B/my_fused_recurrent.py:138-153, kernel :9-80) and,
+ * with slot_idx == NULL, for fused_recurrent_gla as called at
+ * hf_7B_model/gla_attention.py:153 on a [B,H,D,D] state.
+ *
+ *  q            [B, H, D]; k,v,g [B, Hkv, D] with Hkv == H (heads already repeated,
+ *               as the reference passes them) or Hkv a divisor of H (head h reads
+ *               kv head h / (H/Hkv), the repeat_interleave order of repeat_kv)
+ *  in_dtype     type of q,k,v,g: SBK_BF16 or SBK_F32; out_dtype likewise for out [B, H, D]
+ *  state        [num_slots, H, D, D] float32 (k index before v index)
+ *  slot_idx     [B] int64 (NULL: slot b for sequence b); -1: row untouched, out row not written
+ *  D in {64, 128}
+ */
+int sbk_gla_step(const void* q, const void* k, const void* v, const void* g, int in_dtype,
+                 float* state, int64_t num_slots, const int64_t* slot_idx,
+                 int B, int H, int Hkv, int D, float scale,
+                 void* out, int out_dtype, int32_t* status, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* SBK_H_ */

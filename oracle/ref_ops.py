@@ -1,0 +1,215 @@
+"""Plain-PyTorch CPU restatements of the reference algorithms (test infrastructure only).
+
+Each function names the reference file:line it follows (paths inside
+BICLab/SpikingBrain-7B).
+"""
+from typing import Dict, List, Optional, Tuple
+
+import torch
+
+
+# --------------------------------------------------------------------------- HF cache
+class RefWindowCache:
+    """Restates Cache.update / get_seq_length of hf_7B_model/cache.py:40-118.
+
+    states[i] is a dict(recurrent_state, attn_state, conv_state). The seen-token
+    counter moves only for layer 0 (:70-71). First insert of a layer trims to the
+    last `window_size` tokens (:81-83); afterwards a layer whose cached length
+    EQUALS the window rolls left and overwrites its tail (:94-104), any other
+    length concatenates (:105-107).
+    """
+
+    def __init__(self, seen_tokens: int = 0):
+        self.states: List[Dict] = []
+        self._seen_tokens = seen_tokens
+
+    def __len__(self):
+        return len(self.states)
+
+    def __getitem__(self, i):
+        if i < len(self.states):
+            return self.states[i]
+        raise KeyError(f"Cache only has {len(self)} layers, attempted to access layer with index {i}")
+
+    def get_seq_length(self, layer_idx: int = 0) -> int:
+        return 0 if len(self.states) <= layer_idx else self._seen_tokens
+
+    def update(self, recurrent_state=None, attn_state=None, conv_state=None, layer_idx: int = 0,
+               offset: int = 1, cache_kwargs: Optional[dict] = None) -> Dict:
+        if layer_idx == 0:
+            self._seen_tokens += offset
+        window = None
+        n_new = 0
+        if attn_state is not None:
+            n_new = attn_state[0].shape[-2]
+            window = cache_kwargs.get("window_size", None)
+            if not isinstance(attn_state, tuple) or len(attn_state) != 2:
+                raise ValueError("`attn_state` must be a tuple of two tensors for key/value states")
+        if len(self.states) <= layer_idx:
+            if attn_state is not None and window is not None and n_new > window:
+                attn_state = tuple(t[..., -window:, :].contiguous() for t in attn_state)
+            state = dict(recurrent_state=recurrent_state, attn_state=attn_state, conv_state=conv_state)
+            self.states.append(state)
+            return state
+        state = self.states[layer_idx]
+        if recurrent_state is not None:
+            state["recurrent_state"] = recurrent_state
+        if attn_state is not None:
+            k_old, v_old = state["attn_state"]
+            if window is not None and k_old.shape[-2] == window:
+                k_new = k_old.roll(-n_new, -2)
+                v_new = v_old.roll(-n_new, -2)
+                k_new[..., -n_new:, :] = attn_state[0]
+                v_new[..., -n_new:, :] = attn_state[1]
+            else:
+                k_new = torch.cat([k_old, attn_state[0]], -2)
+                v_new = torch.cat([v_old, attn_state[1]], -2)
+            state["attn_state"] = (k_new, v_new)
+        if conv_state is not None:
+            state["conv_state"] = conv_state
+        return state
+
+
+# ------------------------------------------------------------------------ paged cache
+def paged_append(key: torch.Tensor, value: torch.Tensor, k_cache: torch.Tensor,
+                 v_cache: torch.Tensor, slot_mapping: torch.Tensor) -> None:
+    """reshape_and_cache_flash as called at vllm_hymeta/attention/meta_attention.py:790-799
+    with kv_cache_dtype "auto": token i goes to cache[slot // block, slot % block];
+    negative slots (PAD_SLOT_ID, :558) are skipped. In place."""
+    bs = k_cache.shape[1]
+    for i, s in enumerate(slot_mapping.tolist()):
+        if s < 0:
+            continue
+        k_cache[s // bs, s % bs] = key[i]
+        v_cache[s // bs, s % bs] = value[i]
+
+
+def first_visible(seq_len: int, n_new: int, window_left: int) -> int:
+    """First token the oldest query of this step still sees: the flash-attn rule the
+    reference relies on (keys in [i - window_left, i]) for the step's first query
+    at position seq_len - n_new."""
+    if window_left < 0:
+        return 0
+    return max(0, seq_len - n_new - window_left)
+
+
+def retire_blocks(block_tables: torch.Tensor, seq_lens: List[int], n_new: List[int],
+                  window_left: int, block_size: int) -> List[List[int]]:
+    """Sliding-window block retirement: logical blocks that end before the first visible
+    token are dropped from the table (entry -> -1) and their ids returned per sequence in
+    logical order. This is the policy behind the window-truncated block table of
+    meta_attention.py:479-485 (the reference delegates it to vLLM's block manager)."""
+    out = []
+    for b, (L, n) in enumerate(zip(seq_lens, n_new)):
+        first_live = min(first_visible(L, n, window_left) // block_size, block_tables.shape[1])
+        ids = []
+        for j in range(first_live):
+            if block_tables[b, j] >= 0:
+                ids.append(int(block_tables[b, j]))
+                block_tables[b, j] = -1
+        out.append(ids)
+    return out
+
+
+def window_gather(k_cache: torch.Tensor, v_cache: torch.Tensor, table: torch.Tensor, seq_len: int,
+                  window_left: int) -> Tuple[torch.Tensor, torch.Tensor]:
+    """Tokens [t0, seq_len) of one sequence through its block table, head-first
+    [kvh, n_vis, D] -- the layout of attn_state in hf_7B_model/cache.py:94-108."""
+    bs = k_cache.shape[1]
+    t0 = first_visible(seq_len, 1, window_left)
+    toks = torch.arange(t0, seq_len)
+    blk = table[toks // bs].long()
+    k = k_cache[blk, toks % bs]  # [n, kvh, D]
+    v = v_cache[blk, toks % bs]
+    return k.transpose(0, 1).contiguous(), v.transpose(0, 1).contiguous()
+
+
+# -------------------------------------------------------------------------- attention
+def repeat_kv(x: torch.Tensor, n_rep: int) -> torch.Tensor:
+    """[.., kvh, L, D] -> [.., kvh*n_rep, L, D], repeat_interleave order
+    (hf_7B_model/window_attention_sdpa.py repeat_kv; same in gla_attention.py:24-34)."""
+    if n_rep == 1:
+        return x
+    *lead, kvh, L, D = x.shape
+    return x.unsqueeze(-3).expand(*lead, kvh, n_rep, L, D).reshape(*lead, kvh * n_rep, L, D)
+
+
+def swa_decode_ref(q: torch.Tensor, k_win: torch.Tensor, v_win: torch.Tensor, scale: float,
+                   window: Optional[int] = None, return_lse: bool = False):
+    """One query per sequence against its cached window, in fp32, following
+    hf_7B_model/window_attention_sdpa.py:140-214: keys repeated per query group, mask
+    `k_pos <= q_abs and k_pos > q_abs - window` (:144-148) with the query at the last
+    key position, softmax(q k^T * scale) v.
+      q [H, D]; k_win, v_win [kvh, n, D] (the n most recent tokens, query token last)."""
+    H, D = q.shape
+    kvh, n, _ = k_win.shape
+    k = repeat_kv(k_win.float(), H // kvh)
+    v = repeat_kv(v_win.float(), H // kvh)
+    s = torch.einsum("hd,hnd->hn", q.float(), k) * scale
+    if window is not None:
+        k_pos = torch.arange(n)
+        q_abs = n - 1
+        allowed = (k_pos <= q_abs) & (k_pos > q_abs - window)
+        s = s.masked_fill(~allowed[None, :], float("-inf"))
+    p = torch.softmax(s, dim=-1)
+    o = torch.einsum("hn,hnd->hd", p, v)
+    if return_lse:
+        return o, torch.logsumexp(s, dim=-1)
+    return o
+
+
+def swa_paged_decode_ref(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor,
+                         block_tables: torch.Tensor, seq_lens: List[int], window_left: int,
+                         scale: float, return_lse: bool = False):
+    """The decode call of meta_attention.py:955-981 (flash_attn fwd_kvcache with causal=True,
+    window (window_left, -1), fa_kernel_metatoken.py:84-105): per sequence gather the visible
+    tokens through the block table, then swa_decode_ref. q [B, H, D] -> [B, H, D] fp32."""
+    outs, lses = [], []
+    for b, L in enumerate(seq_lens):
+        if L <= 0:
+            outs.append(torch.zeros(q.shape[1:], dtype=torch.float32))
+            lses.append(torch.full((q.shape[1],), float("-inf")))
+            continue
+        k, v = window_gather(k_cache, v_cache, block_tables[b], L, window_left)
+        o, lse = swa_decode_ref(q[b], k, v, scale, return_lse=True)
+        outs.append(o)
+        lses.append(lse)
+    o = torch.stack(outs)
+    return (o, torch.stack(lses)) if return_lse else o
+
+
+# -------------------------------------------------------------------------------- GLA
+def gla_step_ref(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, g: torch.Tensor,
+                 state: torch.Tensor, slot_idx: Optional[torch.Tensor] = None,
+                 scale: Optional[float] = None) -> torch.Tensor:
+    """Single-token GLA step in fp32, in place on `state` [slots, H, D, D], in the order of
+    vllm_hymeta/model_for_7B/my_fused_recurrent.py:60-80: decay the old state by exp(g)
+    along the key index, add the outer product k v^T, read the output out of the NEW
+    state with q * scale. q [B, H, D]; k, v, g [B, Hkv, D] (Hkv divides H; head h uses
+    kv head h // (H // Hkv), the repeat_kv order of gla_attention.py:265-267).
+    slot -1 leaves the state row untouched and the output row zero (:34-36)."""
+    B, H, D = q.shape
+    Hkv = k.shape[1]
+    rep = H // Hkv
+    if scale is None:
+        scale = D ** -0.5
+    out = torch.zeros(B, H, D, dtype=torch.float32)
+    kf = k.float().repeat_interleave(rep, dim=1)
+    vf = v.float().repeat_interleave(rep, dim=1)
+    gf = g.float().repeat_interleave(rep, dim=1)
+    qf = q.float() * scale
+    for b in range(B):
+        s = b if slot_idx is None else int(slot_idx[b])
+        if s < 0:
+            continue
+        new = torch.exp(gf[b])[:, :, None] * state[s] + kf[b][:, :, None] * vf[b][:, None, :]
+        state[s] = new
+        out[b] = torch.einsum("hk,hkv->hv", qf[b], new)
+    return out
+
+
+def gla_prepare_inputs(q_proj: torch.Tensor, k_proj: torch.Tensor, gk_proj: torch.Tensor,
+                       normalizer: float = 16.0):
+    """Input preparation of hf_7B_model/gla_attention.py:134-145: ReLU feature map on q and k,
+    log-decay g = logsigmoid(gk) / gate_logit_normalizer."""
+    return torch.relu(q_proj), torch.relu(k_proj), torch.nn.functional.logsigmoid(gk_proj) / normalizer

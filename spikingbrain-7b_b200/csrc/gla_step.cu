@@ -1,0 +1,153 @@
+// Fused GLA recurrent-state step: one pass over the fp32 state tile of a
+// (sequence, head) pair updates it in place and reads the output out of the
+// NEW state, in the order of vllm_hymeta/model_for_7B/my_fused_recurrent.py:60-80:
+//   S[k,v] <- exp(g[k]) * S[k,v] + k[k] * v[v];   o[v] = sum_k (q[k]*scale) * S[k,v]
+// Every v column is independent, so a thread owns four v columns (one float4)
+// and strides over k rows; the tile is read and written exactly once with
+// 128-bit streaming accesses. HBM-bound: 2*D*D*4 bytes per (sequence, head).
+#include <math.h>
+
+#include "sbk_common.cuh"
+
+namespace sbk {
+
+template <typename T>
+__device__ __forceinline__ float to_f32(T x);
+template <>
+__device__ __forceinline__ float to_f32<float>(float x) { return x; }
+template <>
+__device__ __forceinline__ float to_f32<__nv_bfloat16>(__nv_bfloat16 x) { return __bfloat162float(x); }
+
+template <typename T>
+__device__ __forceinline__ T from_f32(float x);
+template <>
+__device__ __forceinline__ float from_f32<float>(float x) { return x; }
+template <>
+__device__ __forceinline__ __nv_bfloat16 from_f32<__nv_bfloat16>(float x) { return __float2bfloat16_rn(x); }
+
+// D = 128: 32 threads span a row (float4 each), 8 row groups, 16 rows per thread.
+// D = 64 : 16 threads span a row, 16 row groups, 4 rows per thread.
+template <typename T, typename TO, int D>
+__global__ void __launch_bounds__(256)
+gla_step_kernel(const T* __restrict__ q, const T* __restrict__ k, const T* __restrict__ v,
+                const T* __restrict__ g, float* __restrict__ state, int64_t num_slots,
+                const int64_t* __restrict__ slot_idx, int H, int Hkv, float scale,
+                TO* __restrict__ out, int32_t* status) {
+  constexpr int TPR = D / 4;          // threads per state row
+  constexpr int GROUPS = 256 / TPR;   // row groups
+  constexpr int RPT = D / GROUPS;     // rows per thread
+  const int h = blockIdx.x;
+  const int b = blockIdx.y;
+  const int64_t slot = slot_idx ? slot_idx[b] : (int64_t)b;
+  if (slot < 0) return;  // padded sequence: state row untouched, output row not written
+  if (slot >= num_slots) {
+    if (threadIdx.x == 0) raise_status(status, SBK_ST_BAD_SLOT);
+    return;
+  }
+  const int hk = h / (H / Hkv);
+
+  __shared__ float s_q[D], s_k[D], s_decay[D];
+  __shared__ float4 s_o[GROUPS][TPR];
+
+  const int tid = threadIdx.x;
+  if (tid < D) {
+    s_q[tid] = to_f32(q[((int64_t)b * H + h) * D + tid]) * scale;
+    const int64_t kv_off = ((int64_t)b * Hkv + hk) * D + tid;
+    s_k[tid] = to_f32(k[kv_off]);
+    s_decay[tid] = expf(to_f32(g[kv_off]));
+  }
+  const int c4 = tid % TPR;
+  const int r0 = tid / TPR;
+  float4 vv;
+  {
+    const T* vp = v + ((int64_t)b * Hkv + hk) * D + c4 * 4;
+    vv = make_float4(to_f32(vp[0]), to_f32(vp[1]), to_f32(vp[2]), to_f32(vp[3]));
+  }
+  float4* tile = reinterpret_cast<float4*>(state + ((slot * H + h) * (int64_t)D) * D);
+
+  float4 s[RPT];
+#pragma unroll
+  for (int i = 0; i < RPT; ++i) s[i] = ld_stream_f4(tile + (int64_t)(r0 + i * GROUPS) * TPR + c4);
+  __syncthreads();
+
+  float4 o = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+  for (int i = 0; i < RPT; ++i) {
+    const int r = r0 + i * GROUPS;
+    const float d = s_decay[r], kk = s_k[r], qq = s_q[r];
+    float4 n;
+    n.x = fmaf(d, s[i].x, kk * vv.x);
+    n.y = fmaf(d, s[i].y, kk * vv.y);
+    n.z = fmaf(d, s[i].z, kk * vv.z);
+    n.w = fmaf(d, s[i].w, kk * vv.w);
+    st_stream_f4(tile + (int64_t)r * TPR + c4, n);
+    o.x = fmaf(qq, n.x, o.x);
+    o.y = fmaf(qq, n.y, o.y);
+    o.z = fmaf(qq, n.z, o.z);
+    o.w = fmaf(qq, n.w, o.w);
+  }
+  s_o[r0][c4] = o;
+  __syncthreads();
+  if (tid < D) {
+    const float* so = reinterpret_cast<const float*>(&s_o[0][0]);
+    float acc = 0.f;
+#pragma unroll
+    for (int gi = 0; gi < GROUPS; ++gi) acc += so[gi * D + tid];
+    out[((int64_t)b * H + h) * D + tid] = from_f32<TO>(acc);
+  }
+}
+
+}  // namespace sbk
+
+extern "C" int sbk_gla_step(const void* q, const void* k, const void* v, const void* g,
+                            int in_dtype, float* state, int64_t num_slots,
+                            const int64_t* slot_idx, int B, int H, int Hkv, int D, float scale,
+                            void* out, int out_dtype, int32_t* status, void* stream) {
+  using namespace sbk;
+  if (B < 0 || H <= 0 || Hkv <= 0 || H % Hkv != 0 || num_slots < 0) {
+    set_error("sbk_gla_step: bad head counts H=%d Hkv=%d or negative size", H, Hkv);
+    return SBK_E_ARG;
+  }
+  if (D != 64 && D != 128) {
+    set_error("sbk_gla_step: D=%d unsupported (64 or 128)", D);
+    return SBK_E_ARG;
+  }
+  if ((in_dtype != SBK_BF16 && in_dtype != SBK_F32) || (out_dtype != SBK_BF16 && out_dtype != SBK_F32)) {
+    set_error("sbk_gla_step: in_dtype=%d / out_dtype=%d unsupported", in_dtype, out_dtype);
+    return SBK_E_ARG;
+  }
+  if (B == 0) return SBK_OK;
+  if (!q || !k || !v || !g || !state || !out) {
+    set_error("sbk_gla_step: null pointer");
+    return SBK_E_ARG;
+  }
+  if (!aligned16(state)) {
+    set_error("sbk_gla_step: state must be 16-byte aligned");
+    return SBK_E_ALIGN;
+  }
+  if (B > 65535) {
+    set_error("sbk_gla_step: B=%d exceeds 65535", B);
+    return SBK_E_ARG;
+  }
+  dim3 grid(H, B);
+  cudaStream_t st = (cudaStream_t)stream;
+#define SBK_GLA_LAUNCH(T, TO, DD)                                                               \
+  gla_step_kernel<T, TO, DD><<<grid, 256, 0, st>>>((const T*)q, (const T*)k, (const T*)v,       \
+                                                   (const T*)g, state, num_slots, slot_idx, H,  \
+                                                   Hkv, scale, (TO*)out, status)
+#define SBK_GLA_DISPATCH_D(T, TO)         \
+  do {                                    \
+    if (D == 128) SBK_GLA_LAUNCH(T, TO, 128); \
+    else SBK_GLA_LAUNCH(T, TO, 64);       \
+  } while (0)
+  if (in_dtype == SBK_BF16) {
+    if (out_dtype == SBK_BF16) SBK_GLA_DISPATCH_D(__nv_bfloat16, __nv_bfloat16);
+    else SBK_GLA_DISPATCH_D(__nv_bfloat16, float);
+  } else {
+    if (out_dtype == SBK_BF16) SBK_GLA_DISPATCH_D(float, __nv_bfloat16);
+    else SBK_GLA_DISPATCH_D(float, float);
+  }
+#undef SBK_GLA_DISPATCH_D
+#undef SBK_GLA_LAUNCH
+  return check_launch("sbk_gla_step");
+}

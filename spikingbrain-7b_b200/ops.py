@@ -1,0 +1,202 @@
+"""Tensor-level wrappers of the libsbk kernels.
+
+Each wrapper checks device, dtype and layout on the host, passes raw device
+pointers and the current CUDA stream through the C ABI, and raises on a
+non-zero return code. Nothing here computes on the CPU and nothing falls back
+to PyTorch ops: without a CUDA device and libsbk.so these functions raise.
+"""
+from typing import Optional, Tuple
+
+import torch
+
+from . import _abi
+from ._abi import SBK_BF16, SBK_F32
+
+_DTYPE_CODE = {torch.bfloat16: SBK_BF16, torch.float32: SBK_F32}
+DEFAULT_SPLIT_CHUNKS = 32  # 16-token chunks per split of a sequence (512 tokens)
+
+
+def _ptr(t: Optional[torch.Tensor]) -> Optional[int]:
+    return None if t is None else t.data_ptr()
+
+
+def _stream() -> int:
+    return torch.cuda.current_stream().cuda_stream
+
+
+def _need_cuda(*tensors: Optional[torch.Tensor]) -> None:
+    for t in tensors:
+        if t is not None and not t.is_cuda:
+            raise RuntimeError("libsbk ops take CUDA tensors only (there is no CPU path)")
+
+
+def _cache_geometry(k_cache: torch.Tensor, v_cache: torch.Tensor) -> Tuple[int, int, int, int, int]:
+    """k_cache / v_cache: [num_blocks, block_size, kvh, D], rows of a block contiguous."""
+    if k_cache.dim() != 4 or k_cache.shape != v_cache.shape or k_cache.dtype != v_cache.dtype:
+        raise ValueError("k_cache and v_cache must be equal-shaped [num_blocks, block, kvh, D] tensors")
+    nb, bs, kvh, d = k_cache.shape
+    for c in (k_cache, v_cache):
+        if nb and c.stride()[1:] != (kvh * d, d, 1):
+            raise ValueError("the rows of a cache block must be contiguous")
+    if k_cache.stride(0) != v_cache.stride(0):
+        raise ValueError("k_cache and v_cache must share one block stride")
+    return nb, bs, kvh, d, k_cache.stride(0) * k_cache.element_size()
+
+
+def kv_append(key: torch.Tensor, value: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor,
+              slot_mapping: torch.Tensor, *, block_tables: Optional[torch.Tensor] = None,
+              seq_lens: Optional[torch.Tensor] = None,
+              query_start_loc: Optional[torch.Tensor] = None, window_left: int = -1,
+              retired_out: Optional[torch.Tensor] = None,
+              status: Optional[torch.Tensor] = None) -> None:
+    """Write key/value [T, kvh, D] into the paged cache at ``slot_mapping`` and, when
+    ``block_tables`` is given, replace table entries of blocks that left the window by -1
+    (their ids are listed in ``retired_out`` [B, max_retired])."""
+    _need_cuda(key, value, k_cache, v_cache, slot_mapping, block_tables, seq_lens, retired_out, status)
+    nb, bs, kvh, d, bstride = _cache_geometry(k_cache, v_cache)
+    T = key.shape[0]
+    if key.shape != (T, kvh, d) or value.shape != key.shape:
+        raise ValueError(f"key/value must be [T, {kvh}, {d}], got {tuple(key.shape)} / {tuple(value.shape)}")
+    if key.dtype != k_cache.dtype or value.dtype != k_cache.dtype:
+        raise ValueError("key/value dtype differs from the cache dtype")
+    if T and (key.stride()[1:] != (d, 1) or value.stride() != key.stride()):
+        raise ValueError("key/value rows must be contiguous and share one token stride")
+    if slot_mapping.dtype != torch.int64 or slot_mapping.numel() != T or not slot_mapping.is_contiguous():
+        raise ValueError("slot_mapping must be a contiguous int64 tensor with one entry per token")
+    B = max_blocks = max_ret = 0
+    if block_tables is not None:
+        if seq_lens is None:
+            raise ValueError("retirement needs seq_lens")
+        B, max_blocks = block_tables.shape
+        for t, n in ((block_tables, None), (seq_lens, B), (query_start_loc, B + 1)):
+            if t is None:
+                continue
+            if t.dtype != torch.int32 or not t.is_contiguous() or (n is not None and t.numel() != n):
+                raise ValueError("block_tables / seq_lens / query_start_loc must be contiguous int32 of matching size")
+        if retired_out is not None:
+            if retired_out.dtype != torch.int32 or not retired_out.is_contiguous() or retired_out.shape[0] != B:
+                raise ValueError("retired_out must be contiguous int32 [B, max_retired]")
+            max_ret = retired_out.shape[1]
+    es = k_cache.element_size()
+    tok_stride = (key.stride(0) if T else kvh * d) * es
+    rc = _abi.lib.sbk_kv_append(
+        _ptr(key), _ptr(value), _ptr(k_cache), _ptr(v_cache), _ptr(slot_mapping), T, kvh, d, es,
+        tok_stride, nb, bs, bstride, _ptr(block_tables), max_blocks, _ptr(seq_lens),
+        _ptr(query_start_loc), B, window_left, _ptr(retired_out), max_ret, _ptr(status), _stream())
+    _abi.check("sbk_kv_append", rc)
+
+
+def kv_gather(k_cache: torch.Tensor, v_cache: torch.Tensor, block_tables: torch.Tensor,
+              seq_lens: torch.Tensor, n_out: int, *, window_left: int = -1,
+              status: Optional[torch.Tensor] = None) -> Tuple[torch.Tensor, torch.Tensor]:
+    """Dense head-first copies [B, kvh, n_out, D] of every sequence's visible window."""
+    _need_cuda(k_cache, v_cache, block_tables, seq_lens, status)
+    nb, bs, kvh, d, bstride = _cache_geometry(k_cache, v_cache)
+    B, max_blocks = block_tables.shape
+    if block_tables.dtype != torch.int32 or seq_lens.dtype != torch.int32 or seq_lens.numel() != B:
+        raise ValueError("block_tables / seq_lens must be int32 with one row / entry per sequence")
+    if not (block_tables.is_contiguous() and seq_lens.is_contiguous()):
+        raise ValueError("block_tables / seq_lens must be contiguous")
+    k_out = torch.empty((B, kvh, n_out, d), dtype=k_cache.dtype, device=k_cache.device)
+    v_out = torch.empty_like(k_out)
+    rc = _abi.lib.sbk_kv_gather(
+        _ptr(k_cache), _ptr(v_cache), _ptr(block_tables), max_blocks, _ptr(seq_lens), B, kvh, d,
+        k_cache.element_size(), nb, bs, bstride, window_left, _ptr(k_out), _ptr(v_out), n_out,
+        _ptr(status), _stream())
+    _abi.check("sbk_kv_gather", rc)
+    return k_out, v_out
+
+
+def swa_max_pieces(max_visible_tokens: int, split_chunks: int = DEFAULT_SPLIT_CHUNKS) -> int:
+    """Upper bound on the splits of one sequence whose window holds ``max_visible_tokens``."""
+    chunks = (max(int(max_visible_tokens), 1) + 15) // 16 + 1  # +1: a window rarely starts on a chunk edge
+    return max(1, -(-chunks // split_chunks))
+
+
+def swa_workspace(B: int, H: int, D: int, max_pieces: int, device) -> Optional[torch.Tensor]:
+    n = _abi.lib.sbk_swa_workspace_bytes(B, H, D, max_pieces)
+    return torch.empty(n, dtype=torch.uint8, device=device) if n else None
+
+
+def swa_decode(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor,
+               block_tables: torch.Tensor, seq_lens: torch.Tensor, *, window_left: int,
+               scale: Optional[float] = None, out: Optional[torch.Tensor] = None,
+               out_dtype: Optional[torch.dtype] = None, lse: Optional[torch.Tensor] = None,
+               workspace: Optional[torch.Tensor] = None, max_pieces: Optional[int] = None,
+               split_chunks: int = DEFAULT_SPLIT_CHUNKS,
+               status: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """Single-query sliding-window attention over the paged cache; q [B, H, D] bf16."""
+    _need_cuda(q, k_cache, v_cache, block_tables, seq_lens, out, lse, workspace, status)
+    nb, bs, kvh, d, bstride = _cache_geometry(k_cache, v_cache)
+    if q.dim() != 3 or q.shape[2] != d or q.dtype != torch.bfloat16 or k_cache.dtype != torch.bfloat16:
+        raise ValueError("q must be bf16 [B, H, D] and the cache bf16")
+    B, H, _ = q.shape
+    if B and q.stride()[1:] != (d, 1):
+        raise ValueError("the heads of q must be contiguous")
+    if block_tables.shape[0] != B or seq_lens.numel() != B:
+        raise ValueError("block_tables / seq_lens need one row / entry per query")
+    if block_tables.dtype != torch.int32 or seq_lens.dtype != torch.int32:
+        raise ValueError("block_tables / seq_lens must be int32")
+    if not (block_tables.is_contiguous() and seq_lens.is_contiguous()):
+        raise ValueError("block_tables / seq_lens must be contiguous")
+    if out is None:
+        out = torch.empty((B, H, d), dtype=out_dtype or torch.bfloat16, device=q.device)
+    elif out.shape != (B, H, d) or (B and out.stride()[1:] != (d, 1)):
+        raise ValueError("out must be [B, H, D] with contiguous heads")
+    if out.dtype not in _DTYPE_CODE:
+        raise ValueError("out must be bf16 or fp32")
+    if lse is not None and (lse.dtype != torch.float32 or lse.shape != (B, H) or not lse.is_contiguous()):
+        raise ValueError("lse must be contiguous fp32 [B, H]")
+    max_blocks = block_tables.shape[1]
+    if max_pieces is None:
+        vis = max_blocks * bs if window_left < 0 else min(max_blocks * bs, window_left + 1)
+        max_pieces = swa_max_pieces(vis, split_chunks)
+    if max_pieces > 1 and workspace is None:
+        workspace = swa_workspace(B, H, d, max_pieces, q.device)
+    if scale is None:
+        scale = d ** -0.5
+    rc = _abi.lib.sbk_swa_decode(
+        _ptr(q), q.stride(0) if B else H * d, _ptr(k_cache), _ptr(v_cache), _ptr(block_tables),
+        max_blocks, _ptr(seq_lens), B, H, kvh, d, nb, bs, bstride, window_left, float(scale),
+        _ptr(out), _DTYPE_CODE[out.dtype], out.stride(0) if B else H * d, _ptr(lse),
+        _ptr(workspace), workspace.numel() if workspace is not None else 0, split_chunks,
+        max_pieces, _ptr(status), _stream())
+    _abi.check("sbk_swa_decode", rc)
+    return out
+
+
+def gla_step(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, g: torch.Tensor,
+             state: torch.Tensor, slot_idx: Optional[torch.Tensor] = None, *,
+             scale: Optional[float] = None, out: Optional[torch.Tensor] = None,
+             out_dtype: Optional[torch.dtype] = None,
+             status: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """In-place GLA state step on ``state`` [slots, H, D, D] fp32; q [B, H, D], k/v/g [B, Hkv, D]."""
+    _need_cuda(q, k, v, g, state, slot_idx, out, status)
+    if q.dim() != 3 or k.dim() != 3:
+        raise ValueError("q must be [B, H, D] and k, v, g [B, Hkv, D]")
+    B, H, D = q.shape
+    Hkv = k.shape[1]
+    if k.shape != (B, Hkv, D) or v.shape != k.shape or g.shape != k.shape:
+        raise ValueError("k, v, g must share the shape [B, Hkv, D]")
+    if q.dtype not in _DTYPE_CODE or any(t.dtype != q.dtype for t in (k, v, g)):
+        raise ValueError("q, k, v, g must share one dtype (bf16 or fp32)")
+    if not all(t.is_contiguous() for t in (q, k, v, g)):
+        raise ValueError("q, k, v, g must be contiguous")
+    if state.dtype != torch.float32 or state.dim() != 4 or state.shape[1:] != (H, D, D) or not state.is_contiguous():
+        raise ValueError(f"state must be contiguous fp32 [slots, {H}, {D}, {D}]")
+    if slot_idx is not None and (slot_idx.dtype != torch.int64 or slot_idx.numel() != B or not slot_idx.is_contiguous()):
+        raise ValueError("slot_idx must be contiguous int64 [B]")
+    if slot_idx is None and state.shape[0] < B:
+        raise ValueError("state has fewer slots than sequences")
+    if out is None:
+        out = torch.empty((B, H, D), dtype=out_dtype or q.dtype, device=q.device)
+    elif out.shape != (B, H, D) or not out.is_contiguous() or out.dtype not in _DTYPE_CODE:
+        raise ValueError("out must be contiguous [B, H, D] bf16 or fp32")
+    if scale is None:
+        scale = D ** -0.5
+    rc = _abi.lib.sbk_gla_step(
+        _ptr(q), _ptr(k), _ptr(v), _ptr(g), _DTYPE_CODE[q.dtype], _ptr(state), state.shape[0],
+        _ptr(slot_idx), B, H, Hkv, D, float(scale), _ptr(out), _DTYPE_CODE[out.dtype],
+        _ptr(status), _stream())
+    _abi.check("sbk_gla_step", rc)
+    return out

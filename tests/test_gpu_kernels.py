@@ -1,0 +1,323 @@
+"""GPU parity tests: the CUDA kernels, called through the C ABI, against the CPU oracle."""
+import math
+
+import pytest
+import torch
+
+from oracle import ref_ops
+from tests.helpers import make_paged_kv, mean_rel, rel_err
+
+pytestmark = pytest.mark.gpu
+
+DEV = "cuda:0"
+# bf16 attention: max-abs 2e-2 and mean-rel 1e-3 against the fp32 oracle rounded to the
+# output dtype; fp32 GLA state and output: rel 1e-4 of the largest magnitude.
+ATTN_MAX_ABS, ATTN_MEAN_REL = 2e-2, 1e-3
+GLA_REL = 1e-4
+
+
+@pytest.fixture(scope="module")
+def ops(sb):
+    from spikingbrain_7b_b200 import ops as _ops
+    assert torch.cuda.is_available()
+    return _ops
+
+
+def _status():
+    return torch.zeros(1, dtype=torch.int32, device=DEV)
+
+
+# ------------------------------------------------------------------ append / retire / gather
+@pytest.mark.parametrize("dtype,kvh,D,bs", [(torch.bfloat16, 4, 128, 16), (torch.float32, 2, 64, 16),
+                                           (torch.bfloat16, 1, 128, 64)])
+def test_kv_append_bit_exact(ops, dtype, kvh, D, bs):
+    g = torch.Generator().manual_seed(1)
+    nb, T = 37, 53
+    kc = torch.randn(nb, bs, kvh, D, generator=g).to(dtype)
+    vc = torch.randn(nb, bs, kvh, D, generator=g).to(dtype)
+    key = torch.randn(T, kvh, D, generator=g).to(dtype)
+    val = torch.randn(T, kvh, D, generator=g).to(dtype)
+    slots = torch.randperm(nb * bs, generator=g)[:T].to(torch.int64)
+    slots[::7] = -1  # padding tokens are skipped
+    kc_ref, vc_ref = kc.clone(), vc.clone()
+    ref_ops.paged_append(key, val, kc_ref, vc_ref, slots)
+    kc_d, vc_d = kc.to(DEV), vc.to(DEV)
+    st = _status()
+    ops.kv_append(key.to(DEV), val.to(DEV), kc_d, vc_d, slots.to(DEV), status=st)
+    assert st.item() == 0
+    assert torch.equal(kc_d.cpu().view(torch.uint8), kc_ref.view(torch.uint8))
+    assert torch.equal(vc_d.cpu().view(torch.uint8), vc_ref.view(torch.uint8))
+
+
+def test_kv_append_strided_views_and_bad_slot(ops):
+    """key/value as column slices of a fused qkv row (the layout the attention layer hands
+    over), caches as the two halves of one [2, NB, bs, kvh, D] tensor; an out-of-pool slot
+    raises the status bit and writes nothing."""
+    g = torch.Generator().manual_seed(2)
+    kvh, D, bs, nb, T, H = 4, 128, 16, 9, 5, 28
+    qkv = torch.randn(T, (H + 2 * kvh) * D, generator=g).bfloat16().to(DEV)
+    key = qkv[:, H * D:(H + kvh) * D].view(T, kvh, D)
+    val = qkv[:, (H + kvh) * D:].view(T, kvh, D)
+    kv = torch.zeros(2, nb, bs, kvh, D, dtype=torch.bfloat16, device=DEV)
+    slots = torch.tensor([3, 17, nb * bs, 40, 41], dtype=torch.int64)
+    st = _status()
+    ops.kv_append(key, val, kv[0], kv[1], slots.to(DEV), status=st)
+    assert st.item() == 1  # SBK_ST_BAD_SLOT
+    kc_ref = torch.zeros(nb, bs, kvh, D, dtype=torch.bfloat16)
+    vc_ref = torch.zeros_like(kc_ref)
+    good = slots.clone(); good[2] = -1
+    ref_ops.paged_append(key.cpu(), val.cpu(), kc_ref, vc_ref, good)
+    assert torch.equal(kv[0].cpu(), kc_ref) and torch.equal(kv[1].cpu(), vc_ref)
+
+
+@pytest.mark.parametrize("bs", [16, 32])
+def test_retire_matches_oracle_over_steps(ops, bs):
+    """Decode steps that move the window across block edges: the device table edits and the
+    retired ids equal the oracle's, step by step."""
+    B, wl, steps = 5, 40, 70
+    lens = [1, 15, 41, 64, 100]
+    max_blocks = (max(lens) + steps + bs - 1) // bs
+    table = torch.arange(B * max_blocks, dtype=torch.int32).view(B, max_blocks).contiguous()
+    table_d = table.to(DEV)
+    kvh, D = 1, 128
+    kv = torch.zeros(2, B * max_blocks, bs, kvh, D, dtype=torch.bfloat16, device=DEV)
+    st = _status()
+    for step in range(steps):
+        lens = [L + 1 for L in lens]
+        slots = torch.tensor([int(table[b, (L - 1) // bs]) * bs + (L - 1) % bs if table[b, (L - 1) // bs] >= 0 else -1
+                              for b, L in enumerate(lens)], dtype=torch.int64)
+        exp = ref_ops.retire_blocks(table, lens, [1] * B, wl, bs)
+        retired = torch.full((B, 4), -7, dtype=torch.int32, device=DEV)
+        kx = torch.zeros(B, kvh, D, dtype=torch.bfloat16, device=DEV)
+        ops.kv_append(kx, kx, kv[0], kv[1], slots.to(DEV), block_tables=table_d,
+                      seq_lens=torch.tensor(lens, dtype=torch.int32, device=DEV), window_left=wl,
+                      retired_out=retired, status=st)
+        assert torch.equal(table_d.cpu(), table), f"step {step}"
+        got = [[x for x in row if x >= 0] for row in retired.cpu().tolist()]
+        assert got == exp, f"step {step}"
+    assert st.item() == 0
+
+
+def test_retire_multi_token_and_overflow(ops):
+    """A chunk of new tokens per sequence (query_start_loc given): the window edge is taken
+    from the chunk's first query; too few retired_out columns raise the overflow bit but
+    the table is still edited."""
+    bs, wl = 16, 32
+    lens = [200, 90]
+    n_new = [64, 8]
+    max_blocks = 16
+    table = torch.arange(2 * max_blocks, dtype=torch.int32).view(2, max_blocks).contiguous()
+    exp_table = table.clone()
+    exp = ref_ops.retire_blocks(exp_table, lens, n_new, wl, bs)
+    assert len(exp[0]) > 2
+    table_d = table.to(DEV)
+    retired = torch.full((2, 2), -7, dtype=torch.int32, device=DEV)
+    st = _status()
+    kv = torch.zeros(2, 2, bs, 1, 128, dtype=torch.bfloat16, device=DEV)
+    empty = torch.zeros(0, 1, 128, dtype=torch.bfloat16, device=DEV)
+    ops.kv_append(empty, empty, kv[0], kv[1], torch.zeros(0, dtype=torch.int64, device=DEV),
+                  block_tables=table_d, seq_lens=torch.tensor(lens, dtype=torch.int32, device=DEV),
+                  query_start_loc=torch.tensor([0, 64, 72], dtype=torch.int32, device=DEV),
+                  window_left=wl, retired_out=retired, status=st)
+    assert torch.equal(table_d.cpu(), exp_table)
+    assert st.item() == 8  # SBK_ST_RETIRE_OVERFLOW
+    assert retired.cpu().tolist()[0] == exp[0][:2]
+
+
+@pytest.mark.parametrize("dtype,kvh,D", [(torch.bfloat16, 4, 128), (torch.float32, 2, 64)])
+def test_kv_gather_bit_exact(ops, dtype, kvh, D):
+    bs, wl = 16, 63
+    lens = [1, 16, 17, 64, 65, 200, 333]
+    kv, table, nb = make_paged_kv(lens, wl, kvh, D, bs, dtype=dtype, seed=3)
+    n_out = max(min(L, wl + 1) for L in lens)
+    st = _status()
+    k_out, v_out = ops.kv_gather(kv[0].to(DEV), kv[1].to(DEV), table.to(DEV),
+                                 torch.tensor(lens, dtype=torch.int32, device=DEV), n_out,
+                                 window_left=wl, status=st)
+    assert st.item() == 0
+    for b, L in enumerate(lens):
+        k_ref, v_ref = ref_ops.window_gather(kv[0], kv[1], table[b], L, wl)
+        n = k_ref.shape[1]
+        assert torch.equal(k_out[b, :, :n].cpu(), k_ref) and torch.equal(v_out[b, :, :n].cpu(), v_ref)
+        assert not k_out[b, :, n:].any() and not v_out[b, :, n:].any()
+
+
+# ------------------------------------------------------------------------------ attention
+def _run_attn(ops, lens, wl, H, kvh, bs, seed, out_dtype=torch.bfloat16, split_chunks=32, max_pieces=None,
+              full_retention=False):
+    D = 128
+    kv, table, nb = make_paged_kv(lens, wl, kvh, D, bs, seed=seed, full_retention=full_retention)
+    g = torch.Generator().manual_seed(seed + 100)
+    q = (torch.randn(len(lens), H, D, generator=g) / math.sqrt(D)).bfloat16()
+    scale = D ** -0.5
+    ref, lse_ref = ref_ops.swa_paged_decode_ref(q, kv[0], kv[1], table, lens, wl, scale, return_lse=True)
+    st = _status()
+    lse = torch.empty(len(lens), H, dtype=torch.float32, device=DEV)
+    kv_d = kv.to(DEV)
+    out = ops.swa_decode(q.to(DEV), kv_d[0], kv_d[1], table.to(DEV),
+                         torch.tensor(lens, dtype=torch.int32, device=DEV), window_left=wl,
+                         scale=scale, out_dtype=out_dtype, lse=lse, split_chunks=split_chunks,
+                         max_pieces=max_pieces, status=st)
+    torch.cuda.synchronize()
+    assert st.item() == 0
+    return out.cpu(), ref, lse.cpu(), lse_ref
+
+
+def _check_attn(out, ref, lse, lse_ref):
+    assert torch.isfinite(out.float()).all()
+    tgt = ref.to(out.dtype).float()
+    assert float((out.float() - tgt).abs().max()) <= ATTN_MAX_ABS
+    assert mean_rel(out.float(), tgt) <= ATTN_MEAN_REL
+    fin = torch.isfinite(lse_ref)
+    assert torch.equal(torch.isfinite(lse), fin)
+    assert float((lse[fin] - lse_ref[fin]).abs().max()) <= 1e-3
+
+
+@pytest.mark.parametrize("lens", [[1], [16], [17], [15, 31, 33], [64, 65, 66, 127, 128, 129]])
+def test_swa_decode_small_edges(ops, lens):
+    out, ref, lse, lse_ref = _run_attn(ops, lens, wl=63, H=28, kvh=4, bs=16, seed=5)
+    _check_attn(out, ref, lse, lse_ref)
+
+
+@pytest.mark.parametrize("wl", [0, 1, 15, 16, 17, 4095, 4096, -1])
+def test_swa_decode_window_edges(ops, wl):
+    lens = [5000, 4097, 4096, 4095, 33, 1]
+    out, ref, lse, lse_ref = _run_attn(ops, lens, wl=wl, H=28, kvh=4, bs=16, seed=6)
+    _check_attn(out, ref, lse, lse_ref)
+
+
+@pytest.mark.parametrize("H,kvh", [(7, 1), (14, 2), (28, 4), (32, 4), (4, 4), (16, 2), (1, 1)])
+def test_swa_decode_head_layouts(ops, H, kvh):
+    lens = [700, 129, 4100]
+    out, ref, lse, lse_ref = _run_attn(ops, lens, wl=2047, H=H, kvh=kvh, bs=16, seed=7)
+    _check_attn(out, ref, lse, lse_ref)
+
+
+@pytest.mark.parametrize("bs", [16, 32, 64, 128])
+def test_swa_decode_block_sizes_full_retention(ops, bs):
+    lens = [3000, 777, 64, 2049]
+    out, ref, lse, lse_ref = _run_attn(ops, lens, wl=1024, H=28, kvh=4, bs=bs, seed=8, full_retention=True)
+    _check_attn(out, ref, lse, lse_ref)
+
+
+@pytest.mark.parametrize("split_chunks,max_pieces", [(1, 300), (3, 7), (32, 1), (1000, 4)])
+def test_swa_decode_split_settings(ops, split_chunks, max_pieces):
+    lens = [4100, 513, 40, 2000]
+    out, ref, lse, lse_ref = _run_attn(ops, lens, wl=4096, H=28, kvh=4, bs=16, seed=9,
+                                      split_chunks=split_chunks, max_pieces=max_pieces)
+    _check_attn(out, ref, lse, lse_ref)
+
+
+def test_swa_decode_fp32_out_tight(ops):
+    """With fp32 output the only bf16 rounding left is that of the probabilities."""
+    lens = [4100, 900, 77]
+    out, ref, lse, lse_ref = _run_attn(ops, lens, wl=4096, H=28, kvh=4, bs=16, seed=10, out_dtype=torch.float32)
+    assert rel_err(out, ref) <= 2e-3
+    assert mean_rel(out, ref) <= ATTN_MEAN_REL
+
+
+def test_swa_decode_empty_and_bad_block(ops):
+    """seq_len 0 yields a zero row; a table entry outside the pool inside the window raises
+    the status bit, and every output stays finite."""
+    D, H, kvh, bs, wl = 128, 28, 4, 16, 63
+    lens = [0, 100, 50]
+    kv, table, nb = make_paged_kv([1, 100, 50], wl, kvh, D, bs, seed=11)
+    table[2, 50 // bs] = nb + 5
+    q = torch.randn(3, H, D).bfloat16()
+    st = _status()
+    kv_d = kv.to(DEV)
+    out = ops.swa_decode(q.to(DEV), kv_d[0], kv_d[1], table.to(DEV),
+                         torch.tensor(lens, dtype=torch.int32, device=DEV), window_left=wl, status=st)
+    torch.cuda.synchronize()
+    assert st.item() == 2  # SBK_ST_BAD_BLOCK
+    assert not out[0].any() and torch.isfinite(out.float()).all()
+    ref = ref_ops.swa_paged_decode_ref(q[1:2], kv[0], kv[1], table[1:2], [100], wl, D ** -0.5)
+    assert float((out[1].float().cpu() - ref[0]).abs().max()) <= ATTN_MAX_ABS
+
+
+def test_swa_decode_config2_shapes(ops):
+    """The single-step op test: 28/4 heads, D 128, window 4096, batch 64, context lengths
+    uniform in [1k, 32k], block 16, permuted block table, q/k/v ~ N(0,1)/sqrt(128)."""
+    g = torch.Generator().manual_seed(0)
+    lens = torch.randint(1024, 32769, (64,), generator=g).tolist()
+    out, ref, lse, lse_ref = _run_attn(ops, lens, wl=4096, H=28, kvh=4, bs=16, seed=12)
+    _check_attn(out, ref, lse, lse_ref)
+
+
+# ------------------------------------------------------------------------------------ GLA
+def _gla_inputs(B, H, Hkv, D, dtype, seed):
+    g = torch.Generator().manual_seed(seed)
+    q = torch.relu(torch.randn(B, H, D, generator=g) / math.sqrt(D)).to(dtype)
+    k = torch.relu(torch.randn(B, Hkv, D, generator=g) / math.sqrt(D)).to(dtype)
+    v = (torch.randn(B, Hkv, D, generator=g) / math.sqrt(D)).to(dtype)
+    gk = (torch.nn.functional.logsigmoid(torch.randn(B, Hkv, D, generator=g)) / 16).to(dtype)
+    return q, k, v, gk, g
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float32])
+@pytest.mark.parametrize("B,H,Hkv,D", [(3, 28, 4, 128), (2, 28, 28, 128), (2, 8, 2, 64), (5, 7, 1, 128)])
+def test_gla_step_matches_oracle(ops, dtype, B, H, Hkv, D):
+    q, k, v, gk, g = _gla_inputs(B, H, Hkv, D, dtype, seed=20)
+    slots = B + 3
+    state = torch.randn(slots, H, D, D, generator=g)
+    slot_idx = torch.randperm(slots, generator=g)[:B].to(torch.int64)
+    slot_idx[0] = -1
+    ref_state = state.clone()
+    ref_out = ref_ops.gla_step_ref(q, k, v, gk, ref_state, slot_idx)
+    state_d = state.to(DEV)
+    out = torch.full((B, H, D), 123.0, dtype=torch.float32, device=DEV)
+    st = _status()
+    ops.gla_step(q.to(DEV), k.to(DEV), v.to(DEV), gk.to(DEV), state_d, slot_idx.to(DEV), out=out, status=st)
+    assert st.item() == 0
+    assert rel_err(state_d.cpu(), ref_state) <= GLA_REL
+    assert rel_err(out[1:].cpu(), ref_out[1:]) <= GLA_REL
+    assert (out[0] == 123.0).all()  # slot -1: output row not written
+    untouched = [s for s in range(slots) if s not in slot_idx.tolist()]
+    assert torch.equal(state_d[untouched].cpu(), state[untouched])  # bit-exact: never touched
+
+
+def test_gla_step_carry_and_bf16_out(ops):
+    """32 chained steps carry the state; bf16 output equals the oracle output to one bf16 ulp."""
+    B, H, Hkv, D = 4, 28, 4, 128
+    g = torch.Generator().manual_seed(21)
+    state = torch.zeros(B, H, D, D)
+    state_d = state.to(DEV)
+    for step in range(32):
+        q, k, v, gk, _ = _gla_inputs(B, H, Hkv, D, torch.bfloat16, seed=100 + step)
+        ref_out = ref_ops.gla_step_ref(q, k, v, gk, state)
+        out = ops.gla_step(q.to(DEV), k.to(DEV), v.to(DEV), gk.to(DEV), state_d)
+        assert out.dtype == torch.bfloat16
+        diff = (out.float().cpu() - ref_out.bfloat16().float()).abs()
+        assert float((diff / ref_out.abs().clamp_min(1e-6)).max()) <= 2 ** -7
+    assert rel_err(state_d.cpu(), state) <= GLA_REL
+
+
+def test_gla_step_config2_shapes(ops):
+    """Batch 64, 28 heads, fp32 state [64, 28, 128, 128] ~ N(0,1), g = logsigmoid(N(0,1))/16."""
+    B, H, Hkv, D = 64, 28, 4, 128
+    q, k, v, gk, g = _gla_inputs(B, H, Hkv, D, torch.bfloat16, seed=0)
+    state = torch.randn(B, H, D, D, generator=g)
+    ref_state = state.clone()
+    ref_out = ref_ops.gla_step_ref(q, k, v, gk, ref_state)
+    state_d = state.to(DEV)
+    out = ops.gla_step(q.to(DEV), k.to(DEV), v.to(DEV), gk.to(DEV), state_d, out_dtype=torch.float32)
+    assert rel_err(state_d.cpu(), ref_state) <= GLA_REL
+    assert rel_err(out.cpu(), ref_out) <= GLA_REL
+
+
+# ---------------------------------------------------------------------- argument errors
+def test_argument_errors_are_reported(ops):
+    from spikingbrain_7b_b200._abi import SbkError
+    kv = torch.zeros(2, 4, 16, 4, 128, dtype=torch.bfloat16, device=DEV)
+    q = torch.zeros(1, 28, 128, dtype=torch.bfloat16, device=DEV)
+    table = torch.zeros(1, 4, dtype=torch.int32, device=DEV)
+    lens = torch.ones(1, dtype=torch.int32, device=DEV)
+    with pytest.raises(SbkError) as e:
+        ops.swa_decode(q, kv[0], kv[1], table, lens, window_left=63, max_pieces=3,
+                       workspace=torch.empty(16, dtype=torch.uint8, device=DEV))
+    assert e.value.code == -3
+    with pytest.raises(SbkError):
+        ops.swa_decode(torch.zeros(1, 36, 128, dtype=torch.bfloat16, device=DEV), kv[0], kv[1], table, lens,
+                       window_left=63)  # 9 query heads per kv head
+    with pytest.raises(RuntimeError):
+        ops.gla_step(q.cpu(), q.cpu(), q.cpu(), q.cpu(), torch.zeros(1, 28, 128, 128))
