@@ -1,0 +1,448 @@
+"""Decode-step benchmark of the hybrid cache path (SpikingBrain-7B shapes) on B200.
+
+One step = one decode token for every sequence of the batch through the cache path of all
+28 layers of the 7B model: 14 sliding-window layers (paged-KV append + block retirement,
+then sliding-window paged attention, through MetaAttentionImpl.forward) and 14 GLA layers
+(in-place recurrent-state step + read-out, through my_fused_recurrent_gla). The dense
+projections / MLP of the model are the callers of this path and are not part of it.
+
+Workload (per GPU): batch 256, every sequence at 8192 tokens of context, window 4096
+(window_left 4096: the query plus 4096 keys, the vLLM-side convention of the reference),
+28 query / 4 kv heads, head_dim 128, bf16 K/V in 16-token blocks behind a randomly
+permuted block table, fp32 GLA state [256, 28, 128, 128] per layer. Synthetic data.
+N GPUs: every rank owns its own 256 sequences (sequence sharding, no collective) -> weak scaling.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl reference] [--batch B] [--ctx L]
+
+Prints ONE JSON line (rank 0). `--impl reference` times the CPU oracle (the PyTorch
+restatement of the reference path) on the host cores instead.
+"""
+import argparse
+import json
+import math
+import os
+import statistics
+import subprocess
+import sys
+import tempfile
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+H, KVH, D, WINDOW_LEFT, BLOCK = 28, 4, 128, 4096, 16
+N_SWA, N_GLA = 14, 14
+NOMINAL_HBM_GBS = 8000.0
+FALLBACK_HBM_GBS = 6650.0
+
+
+def parse_args():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=50)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
+    ap.add_argument("--batch", type=int, default=256, help="sequences per GPU")
+    ap.add_argument("--ctx", type=int, default=8192, help="context length of every sequence")
+    ap.add_argument("--swa-layers", type=int, default=N_SWA)
+    ap.add_argument("--gla-layers", type=int, default=N_GLA)
+    ap.add_argument("--no-e2e", action="store_true")
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    return ap.parse_args()
+
+
+# ------------------------------------------------------------------------- bytes model
+def cache_bytes_per_step(batch, ctx_after, n_swa, n_gla):
+    """Algorithmic cache bytes of one decode step (K/V read + appended, GLA state read+written)."""
+    vis = min(ctx_after, WINDOW_LEFT + 1)
+    swa = batch * (vis * 2 * KVH * D * 2 + 2 * KVH * D * 2)
+    gla = batch * 2 * H * D * D * 4
+    return n_swa * swa + n_gla * gla, swa, gla
+
+
+# ------------------------------------------------------------------- CPU oracle timing
+def cpu_reference_step_seconds(n_seqs, ctx, repeats):
+    """Seconds the CPU restatement of the reference path needs for ONE sliding-window layer
+    plus ONE GLA layer on `n_seqs` sequences at context `ctx` (median of `repeats`):
+    Cache.update window roll + repeat_kv + masked softmax attention (the HF path), and the
+    fp32 recurrence on a fresh state tensor."""
+    import torch
+    from oracle import ref_ops
+    torch.manual_seed(0)
+    W = WINDOW_LEFT  # the HF cache keeps `window` tokens
+    n_cached = min(ctx, W)
+    cache = ref_ops.RefWindowCache()
+    k0 = (torch.randn(n_seqs, KVH, n_cached, D) / math.sqrt(D)).bfloat16()
+    v0 = (torch.randn(n_seqs, KVH, n_cached, D) / math.sqrt(D)).bfloat16()
+    cache.update(attn_state=(k0, v0), layer_idx=0, offset=n_cached, cache_kwargs={"window_size": W})
+    q = (torch.randn(n_seqs, H, D) / math.sqrt(D)).bfloat16()
+    kn = (torch.randn(n_seqs, KVH, 1, D) / math.sqrt(D)).bfloat16()
+    gq, gk, gg = ref_ops.gla_prepare_inputs(torch.randn(n_seqs, H, D), torch.randn(n_seqs, KVH, D),
+                                            torch.randn(n_seqs, KVH, D))
+    gv = torch.randn(n_seqs, KVH, D)
+    state = torch.randn(n_seqs, H, D, D)
+    times = []
+    for it in range(repeats + 1):
+        t0 = time.perf_counter()
+        st = cache.update(attn_state=(kn, kn), layer_idx=0, offset=1, cache_kwargs={"window_size": W})
+        kc, vc = st["attn_state"]
+        for b in range(n_seqs):
+            ref_ops.swa_decode_ref(q[b], kc[b], vc[b], D ** -0.5, window=W)
+        ref_ops.gla_step_ref(gq, gk, gv, gg, state)
+        dt = time.perf_counter() - t0
+        if it > 0:
+            times.append(dt)
+    return statistics.median(times)
+
+
+def cpu_baseline(args, sample_seqs=8, repeats=3):
+    import torch
+    cores = torch.get_num_threads()
+    t = cpu_reference_step_seconds(sample_seqs, args.ctx + 1, repeats)
+    per_seq_layerpair = t / sample_seqs
+    # a full step = batch sequences x (swa_layers + gla_layers); the sample timed one of each
+    pairs = max(args.swa_layers, args.gla_layers)
+    step_s = per_seq_layerpair * args.batch * pairs
+    return {
+        "value": args.batch / step_s, "unit": "tokens/s", "cores": cores, "kind": "port",
+        "sample": f"{sample_seqs} sequences x (1 sliding-window layer + 1 GLA layer) at ctx {args.ctx + 1}, "
+                  f"median of {repeats}, scaled x{args.batch / sample_seqs:g} sequences x{pairs} layer pairs",
+    }
+
+
+# --------------------------------------------------------------------- clocks sampling
+class ClockSampler:
+    Q = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
+         "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+         "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_index):
+        self.gpu_index = gpu_index
+        self.proc = None
+        self.path = None
+
+    def start(self):
+        try:
+            f = tempfile.NamedTemporaryFile("w", suffix=".csv", delete=False)
+            self.path = f.name
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", "-i", str(self.gpu_index), f"--query-gpu={self.Q}",
+                 "--format=csv,noheader,nounits", "-lms", "50"], stdout=f, stderr=subprocess.DEVNULL)
+        except OSError:
+            self.proc = None
+
+    def stop(self):
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+        sm, smax, reasons = [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        with open(self.path) as f:
+            for line in f:
+                p = [x.strip() for x in line.split(",")]
+                if len(p) < 9:
+                    continue
+                try:
+                    sm.append(float(p[1])); smax.append(float(p[2]))
+                except ValueError:
+                    continue
+                for nm, val in zip(names, p[5:9]):
+                    if val.lower().startswith("active"):
+                        reasons.add(nm)
+        os.unlink(self.path)
+        return {"sm_mhz": statistics.median(sm) if sm else None,
+                "sm_max_mhz": max(smax) if smax else None, "reasons": sorted(reasons),
+                "samples": len(sm)}
+
+
+# -------------------------------------------------------------------------- the engine
+class DecodeEngine:
+    """Holds the per-layer caches of one GPU and runs decode steps through the reference-facing
+    surfaces: MetaAttentionImpl.forward for sliding-window layers, my_fused_recurrent_gla for
+    GLA layers, with a SlidingWindowBlockManager standing in for the serving engine's."""
+
+    def __init__(self, args, device):
+        import numpy as np
+        import torch
+        from spikingbrain_7b_b200 import ops
+        from spikingbrain_7b_b200.backend import MetaAttentionImpl, MetaAttentionMetadata
+        from spikingbrain_7b_b200.block_pool import SlidingWindowBlockManager
+        from spikingbrain_7b_b200.gla_slots import GLACacheManager, my_fused_recurrent_gla
+        self.torch, self.np, self.ops = torch, np, ops
+        self.Meta = MetaAttentionMetadata
+        self.gla_fn = my_fused_recurrent_gla
+        self.device = device
+        self.B = B = args.batch
+        self.n_swa, self.n_gla = args.swa_layers, args.gla_layers
+        total_steps = args.steps * 2 + args.warmup * 2 + 8
+        max_len = args.ctx + total_steps + 1
+        self.max_blocks = (max_len + BLOCK - 1) // BLOCK + 1
+        live = (WINDOW_LEFT + 1) // BLOCK + 3
+        n_blocks = B * live + 64
+        self.mgr = SlidingWindowBlockManager(n_blocks, BLOCK, WINDOW_LEFT, B, self.max_blocks)
+        # sequences arrive with `ctx` tokens of context: only the window's blocks are resident
+        g = np.random.default_rng(1234 + (device.index or 0))
+        order = g.permutation(n_blocks)       # the pool hands blocks out in a random order
+        self.mgr.pool._free = [int(x) for x in order[::-1]]
+        first_live = max(0, args.ctx - WINDOW_LEFT) // BLOCK
+        for row in range(B):
+            self.mgr.admit(row)
+            self.mgr.lens[row] = args.ctx
+            self.mgr._first_live[row] = first_live
+            for j in range(first_live, (args.ctx + BLOCK - 1) // BLOCK):
+                self.mgr.table[row, j] = self.mgr.pool.allocate()
+        self.table_d = torch.from_numpy(self.mgr.table).to(device)
+        self.lens_d = torch.from_numpy(self.mgr.lens.copy()).to(device)
+        self.slots_d = torch.zeros(B, dtype=torch.int64, device=device)
+        self.kv = []
+        for _ in range(self.n_swa):
+            t = torch.empty(2, n_blocks, BLOCK, KVH, D, dtype=torch.bfloat16, device=device)
+            t.normal_(0.0, 1.0 / math.sqrt(D))
+            self.kv.append(t)
+        self.gla = GLACacheManager(torch.float32, (max(self.n_gla, 1), B, H, D, D), device=device)
+        self.gla.cache.normal_(0.0, 1.0)
+        _, self.slot_idx = self.gla.current_run_tensors({f"r{i}": [0] for i in range(B)})
+        self.impls = [MetaAttentionImpl(H, D, D ** -0.5, KVH, None, WINDOW_LEFT + 1, "auto")
+                      for _ in range(self.n_swa)]
+        # layer inputs (what the projections of the model would hand over), device resident
+        rn = lambda *s: (torch.randn(*s, device=device) / math.sqrt(D)).bfloat16()
+        self.q = [rn(B, H, D) for _ in range(2)]
+        self.k = [rn(B, KVH, D) for _ in range(2)]
+        self.v = [rn(B, KVH, D) for _ in range(2)]
+        self.gq = torch.relu(rn(B, H, 1, D))
+        self.gk = torch.relu(rn(B, KVH, 1, D))
+        self.gv = rn(B, KVH, 1, D)
+        self.gg = (torch.nn.functional.logsigmoid(torch.randn(B, KVH, 1, D, device=device)) / 16).bfloat16()
+        self.out = torch.empty(B, H, D, dtype=torch.bfloat16, device=device)
+        # pinned host staging for the end-to-end mode
+        pin = lambda t: t.cpu().pin_memory()
+        self.h_q, self.h_k, self.h_v = pin(self.q[0]), pin(self.k[0]), pin(self.v[0])
+        self.h_gq, self.h_gk, self.h_gv, self.h_gg = pin(self.gq), pin(self.gk), pin(self.gv), pin(self.gg)
+        self.h_out = torch.empty(B, H, D, dtype=torch.bfloat16).pin_memory()
+        self.copy_stream = torch.cuda.Stream(device=device)
+        self.h2d_bytes = self.d2h_bytes = 0
+
+    def _advance_metadata(self):
+        """Host side of a step: slots of the new tokens, new lengths, newly allocated blocks."""
+        torch = self.torch
+        plan = self.mgr.advance(self.np.ones(self.B, dtype=self.np.int64))
+        # Pageable sources: the runtime stages them before the call returns, so the host may
+        # overwrite its arrays for the next step while the GPU is still several steps behind.
+        self.slots_d.copy_(torch.from_numpy(plan.slot_mapping), non_blocking=True)
+        self.lens_d.copy_(torch.from_numpy(plan.seq_lens), non_blocking=True)
+        nbytes = plan.slot_mapping.nbytes + plan.seq_lens.nbytes
+        if plan.new_entries.size:
+            e = torch.from_numpy(plan.new_entries).to(self.device, non_blocking=True).long()
+            self.table_d[e[:, 0], e[:, 1]] = e[:, 2].int()
+            nbytes += plan.new_entries.nbytes
+        # blocks that left the window are dropped from the device table by the append kernel of
+        # the first sliding-window layer (same rule as the host mirror)
+        max_len = int(plan.seq_lens.max())
+        meta = self.Meta(num_prefills=0, num_prefill_tokens=0, num_decode_tokens=self.B,
+                         slot_mapping=self.slots_d, seq_lens=None, seq_lens_tensor=self.lens_d,
+                         max_prefill_seq_len=0, max_decode_seq_len=max_len, context_lens_tensor=None,
+                         block_tables=self.table_d, use_cuda_graph=False, max_query_len=1,
+                         max_decode_query_len=1)
+        return meta, nbytes
+
+    def step(self, e2e=False):
+        torch, ops = self.torch, self.ops
+        meta, meta_bytes = self._advance_metadata()
+        cur = torch.cuda.current_stream()
+        if e2e:
+            self.h2d_bytes += meta_bytes
+        first_swa = True
+        n_pairs = max(self.n_swa, self.n_gla)
+        for i in range(n_pairs):
+            if i < self.n_gla:   # even layers of the model are GLA layers
+                if e2e:
+                    for dst, src in ((self.gq, self.h_gq), (self.gk, self.h_gk), (self.gv, self.h_gv), (self.gg, self.h_gg)):
+                        dst.copy_(src, non_blocking=True)
+                        self.h2d_bytes += src.numel() * src.element_size()
+                o = self.gla_fn(self.gq, self.gk, self.gv, self.gg, kv_caches=self.gla.cache[i], slot_idx=self.slot_idx)
+                if e2e:
+                    self.h_out.copy_(o, non_blocking=True)
+                    self.d2h_bytes += o.numel() * o.element_size()
+            if i < self.n_swa:   # odd layers are sliding-window layers
+                j = i & 1
+                if e2e:
+                    for dst, src in ((self.q[j], self.h_q), (self.k[j], self.h_k), (self.v[j], self.h_v)):
+                        dst.copy_(src, non_blocking=True)
+                        self.h2d_bytes += src.numel() * src.element_size()
+                if first_swa:
+                    # retire on the device what the host mirror released this step
+                    ops.kv_append(self.k[j][:0], self.v[j][:0], self.kv[i][0], self.kv[i][1], self.slots_d[:0],
+                                  block_tables=self.table_d, seq_lens=self.lens_d, window_left=WINDOW_LEFT)
+                    first_swa = False
+                self.impls[i].forward(None, self.q[j], self.k[j], self.v[j], None, None, None, self.kv[i],
+                                      meta, output=self.out)
+                if e2e:
+                    self.h_out.copy_(self.out, non_blocking=True)
+                    self.d2h_bytes += self.out.numel() * self.out.element_size()
+        if e2e:
+            cur.synchronize()   # the caller holds the step's result on the host
+
+
+def run_b200(args):
+    import torch
+    import torch.distributed as dist
+    rank = int(os.environ.get("RANK", 0))
+    world = int(os.environ.get("WORLD_SIZE", 1))
+    local = int(os.environ.get("LOCAL_RANK", 0))
+    if world != args.gpus:
+        if world == 1 and args.gpus > 1:
+            raise SystemExit("launch multi-GPU runs with torch.distributed.run (one rank per GPU)")
+    torch.cuda.set_device(local)
+    device = torch.device("cuda", local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=device)
+
+    # builds the library on first use if needed (it normally travels prebuilt)
+    import importlib.util
+    spec = importlib.util.spec_from_file_location("_sb7b_build", os.path.join(ROOT, "spikingbrain-7b_b200", "build.py"))
+    bmod = importlib.util.module_from_spec(spec); spec.loader.exec_module(bmod)
+    if rank == 0:
+        bmod.build_library()
+    if world > 1:
+        dist.barrier()
+
+    from spikingbrain_7b_b200 import ops
+    eng = DecodeEngine(args, device)
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    def timed(n_steps, e2e):
+        barrier()
+        e0 = torch.cuda.Event(enable_timing=True); e1 = torch.cuda.Event(enable_timing=True)
+        t0 = time.perf_counter()
+        e0.record()
+        for _ in range(n_steps):
+            eng.step(e2e=e2e)
+        e1.record()
+        torch.cuda.synchronize()
+        wall = (time.perf_counter() - t0) * 1e3
+        ms = max(e0.elapsed_time(e1), 0.0)
+        if e2e:
+            ms = max(ms, wall)   # the host waits inside an end-to-end step; take the slower clock
+        t = torch.tensor([ms], dtype=torch.float64, device=device)
+        if world > 1:
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        barrier()
+        return float(t.item())
+
+    # ---- device-resident timing ----
+    sampler = ClockSampler(local)
+    if rank == 0:
+        sampler.start()   # sampling starts with the warm-up: the tool needs a moment to come up
+    for _ in range(max(args.warmup, 3)):
+        eng.step()
+    launches0 = ops.LAUNCHES
+    ops.SWA_TIMING = []
+    total_ms = timed(args.steps, e2e=False)
+    swa_pairs = ops.SWA_TIMING
+    ops.SWA_TIMING = None
+    launches = ops.LAUNCHES - launches0
+    clocks = sampler.stop() if rank == 0 else None
+    ms_per_step = total_ms / args.steps
+    swa_ms = [a.elapsed_time(b) for a, b in swa_pairs]
+
+    # ---- end to end: host buffers in, host result out, every step ----
+    e2e_obj = None
+    if not args.no_e2e:
+        for _ in range(3):
+            eng.step(e2e=True)
+        eng.h2d_bytes = eng.d2h_bytes = 0
+        e2e_ms = timed(args.steps, e2e=True) / args.steps
+        e2e_obj = {"value": args.batch * world / (e2e_ms * 1e-3), "unit": "tokens/s",
+                   "h2d_bytes_per_step": eng.h2d_bytes // args.steps,
+                   "d2h_bytes_per_step": eng.d2h_bytes // args.steps, "ms_per_step": e2e_ms}
+
+    status = sum(impl.status() for impl in eng.impls)
+    if rank != 0:
+        if world > 1:
+            dist.destroy_process_group()
+        return
+
+    peaks_path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(peaks_path):
+        peak, peak_src = float(json.load(open(peaks_path))["hbm_gbs"]), "measured (MEASURED_PEAKS.json hbm_gbs)"
+    else:
+        peak, peak_src = FALLBACK_HBM_GBS, "fallback"
+    ctx_after = args.ctx + max(args.warmup, 3) + args.steps // 2
+    step_bytes, swa_layer_bytes, gla_layer_bytes = cache_bytes_per_step(args.batch, ctx_after, args.swa_layers, args.gla_layers)
+    swa_avg_ms = statistics.mean(swa_ms) if swa_ms else None
+    achieved = swa_layer_bytes / (swa_avg_ms * 1e-3) / 1e9 if swa_avg_ms else None
+    line = {
+        "metric": "decode tokens/s and cache HBM GB/s (% of 8 TB/s)",
+        "value": args.batch * world / (ms_per_step * 1e-3), "unit": "tokens/s",
+        "n_gpus": world, "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": ms_per_step,
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16 K/V, f32 GLA state",
+        "data": "synthetic",
+        "config": {"workload": f"7B-shaped decode step, cache path of {args.swa_layers} sliding-window + "
+                               f"{args.gla_layers} GLA layers, batch {args.batch} per GPU, ctx {args.ctx}, "
+                               f"window_left {WINDOW_LEFT}, block {BLOCK}, 28/4 heads, head_dim 128",
+                   "parallelism": f"sequence-sharded x{world}, no collective",
+                   "l2": "working set (KV pools + GLA state, tens of GB) far exceeds the 126 MB L2; no flush needed"},
+        "cache_gbs": step_bytes / (ms_per_step * 1e-3) / 1e9,
+        "cache_frac_of_8tbs": step_bytes / (ms_per_step * 1e-3) / 1e9 / NOMINAL_HBM_GBS,
+        "cache_bytes_per_step": step_bytes,
+        "roofline": {"bound": "hbm", "kernel": "swa_decode_kernel (+ its split reduce)",
+                     "achieved": achieved, "peak": peak, "unit": "GB/s",
+                     "frac": achieved / peak if achieved else None, "peak_source": peak_src,
+                     "frac_of_8tbs": achieved / NOMINAL_HBM_GBS if achieved else None,
+                     "algorithmic_bytes_per_launch": swa_layer_bytes, "avg_launch_ms": swa_avg_ms,
+                     "launches_timed": len(swa_ms), "traffic": None},
+        "e2e": e2e_obj, "gpu_launches": launches, "clocks": clocks, "device_status": status,
+    }
+    if not args.no_cpu_baseline:
+        line["cpu_baseline"] = cpu_baseline(args)
+    print(json.dumps(line))
+    if world > 1:
+        dist.destroy_process_group()
+
+
+def run_reference(args):
+    """The reference's CPU path (oracle port) on the host cores; rank 0 only."""
+    if int(os.environ.get("RANK", 0)) != 0:
+        return
+    import torch
+    sample_seqs = 8
+    cores = torch.get_num_threads()
+    pairs = max(args.swa_layers, args.gla_layers)
+    for _ in range(max(args.warmup, 1)):
+        cpu_reference_step_seconds(sample_seqs, args.ctx + 1, 1)
+    ts = [cpu_reference_step_seconds(sample_seqs, args.ctx + 1, 1) for _ in range(args.steps)]
+    t = statistics.mean(ts)
+    step_s = t / sample_seqs * args.batch * pairs
+    value = args.batch / step_s
+    sample = (f"each step: {sample_seqs} sequences x (1 sliding-window layer + 1 GLA layer) at ctx {args.ctx + 1}, "
+              f"scaled x{args.batch / sample_seqs:g} sequences x{pairs} layer pairs")
+    print(json.dumps({
+        "impl": "reference", "metric": "decode tokens/s and cache HBM GB/s (% of 8 TB/s)", "value": value,
+        "unit": "tokens/s", "n_gpus": args.gpus, "steps": args.steps, "warmup": max(args.warmup, 1),
+        "ms_per_step": step_s * 1e3, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "dtype": "bf16 K/V, f32 GLA state", "data": "synthetic",
+        "config": {"workload": f"7B-shaped decode step, cache path of {args.swa_layers} sliding-window + "
+                               f"{args.gla_layers} GLA layers, batch {args.batch} per GPU, ctx {args.ctx}, "
+                               f"window_left {WINDOW_LEFT}, block {BLOCK}, 28/4 heads, head_dim 128",
+                   "parallelism": "host cores of rank 0"},
+        "cpu_baseline": {"value": value, "unit": "tokens/s", "cores": cores, "kind": "port", "sample": sample},
+        "e2e": {"value": value, "unit": "tokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+    }))
+
+
+if __name__ == "__main__":
+    a = parse_args()
+    if a.impl == "reference":
+        run_reference(a)
+    else:
+        run_b200(a)

@@ -101,7 +101,7 @@ def retire_blocks(block_tables: torch.Tensor, seq_lens: List[int], n_new: List[i
     meta_attention.py:479-485 (the reference delegates it to vLLM's block manager)."""
     out = []
     for b, (L, n) in enumerate(zip(seq_lens, n_new)):
-        first_live = min(first_visible(L, n, window_left) // block_size, block_tables.shape[1])
+        first_live = min(first_visible(L, max(n, 1), window_left) // block_size, block_tables.shape[1])
         ids = []
         for j in range(first_live):
             if block_tables[b, j] >= 0:

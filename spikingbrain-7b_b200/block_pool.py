@@ -1,0 +1,217 @@
+"""Host-side block allocator with sliding-window retirement.
+
+Stands in for the block manager the reference leaves to vLLM: it decides which
+physical block holds which 16-token span of which sequence, hands out the flat
+slot ids the append kernel writes to (the `slot_mapping` of
+vllm_hymeta/attention/meta_attention.py:487-494), and recycles blocks that fall
+wholly before the sliding window (the window-truncated tables of :479-485).
+
+The retirement rule is the one the device applies inside `sbk_kv_append`, so the
+host mirror and the device table stay identical without reading anything back:
+    first token still needed  t0 = max(0, seq_len - n_new - window_left)
+    logical blocks            j < t0 // block_size   are released.
+Pure numpy: no tensor maths happens here.
+"""
+from dataclasses import dataclass
+from typing import List, Sequence
+
+import numpy as np
+
+
+class OutOfBlocks(MemoryError):
+    """The pool has no free block left."""
+
+
+class BlockPool:
+    """LIFO free list over ``num_blocks`` physical blocks: the block retired last is
+    handed out first, so a churning batch fragments the pool the way a serving engine does."""
+
+    def __init__(self, num_blocks: int):
+        if num_blocks <= 0:
+            raise ValueError("num_blocks must be positive")
+        self.num_blocks = num_blocks
+        self._free: List[int] = list(range(num_blocks - 1, -1, -1))
+        self._is_free = np.ones(num_blocks, dtype=bool)
+
+    @property
+    def num_free(self) -> int:
+        return len(self._free)
+
+    def allocate(self) -> int:
+        if not self._free:
+            raise OutOfBlocks(f"all {self.num_blocks} KV blocks are in use")
+        b = self._free.pop()
+        self._is_free[b] = False
+        return b
+
+    def release(self, ids: Sequence[int]) -> None:
+        for b in ids:
+            b = int(b)
+            if not 0 <= b < self.num_blocks:
+                raise ValueError(f"block id {b} outside the pool")
+            if self._is_free[b]:
+                raise ValueError(f"block {b} released twice")
+            self._is_free[b] = True
+            self._free.append(b)
+
+
+def first_visible(seq_len: int, n_new: int, window_left: int) -> int:
+    if window_left < 0:
+        return 0
+    return max(0, seq_len - n_new - window_left)
+
+
+@dataclass
+class StepPlan:
+    """What one call of ``SlidingWindowBlockManager.advance`` decided."""
+    slot_mapping: np.ndarray       # int64 [T]  flat slot per new token, rows in order, -1 = padding
+    seq_lens: np.ndarray           # int32 [rows] lengths AFTER the append (0 = inactive row)
+    query_start_loc: np.ndarray    # int32 [rows+1]
+    new_entries: np.ndarray        # int32 [n, 3] (row, logical block, physical block) allocated now
+    retired: List[List[int]]       # per row, ids released now, in logical order
+
+
+class SlidingWindowBlockManager:
+    """Block tables of up to ``max_seqs`` sequences over one pool.
+
+    Rows are stable: a sequence keeps its row from ``admit`` to ``finish``; an inactive row
+    has length 0 and takes no part in a step. ``table`` is the host mirror of the device
+    block table ([max_seqs, max_blocks] int32, -1 = no block)."""
+
+    def __init__(self, num_blocks: int, block_size: int, window_left: int, max_seqs: int,
+                 max_blocks_per_seq: int):
+        if block_size <= 0 or block_size % 16:
+            raise ValueError(f"Invalid block size {block_size}. Must be a multiple of 16 and at least 16.")
+        self.pool = BlockPool(num_blocks)
+        self.block_size = block_size
+        self.window_left = window_left
+        self.max_seqs = max_seqs
+        self.max_blocks = max_blocks_per_seq
+        self.table = np.full((max_seqs, max_blocks_per_seq), -1, dtype=np.int32)
+        self.lens = np.zeros(max_seqs, dtype=np.int32)
+        self.active = np.zeros(max_seqs, dtype=bool)
+        self._first_live = np.zeros(max_seqs, dtype=np.int64)  # first logical block not yet retired
+
+    # ---------------------------------------------------------------- sequences
+    def admit(self, row: int) -> None:
+        if self.active[row]:
+            raise ValueError(f"row {row} already holds a sequence")
+        self.active[row] = True
+        self.lens[row] = 0
+        self._first_live[row] = 0
+
+    def finish(self, row: int) -> List[int]:
+        """Release every block of the sequence in ``row``; returns the released ids."""
+        if not self.active[row]:
+            raise ValueError(f"row {row} holds no sequence")
+        ids = [int(b) for b in self.table[row] if b >= 0]
+        self.pool.release(ids)
+        self.table[row] = -1
+        self.lens[row] = 0
+        self.active[row] = False
+        self._first_live[row] = 0
+        return ids
+
+    def resident_blocks(self, row: int) -> int:
+        return int((self.table[row] >= 0).sum())
+
+    # --------------------------------------------------------------------- step
+    def advance(self, n_new: Sequence[int], pad_inactive: bool = True) -> StepPlan:
+        """Append ``n_new[row]`` tokens to every active row: allocate the blocks they need,
+        compute their slots, then retire what left the window. With ``pad_inactive`` an
+        inactive row contributes one -1 slot when every active row appends one token
+        (the static decode batch: token i belongs to row i)."""
+        n_new = np.asarray(n_new, dtype=np.int64)
+        if n_new.shape != (self.max_seqs,):
+            raise ValueError("n_new needs one entry per row")
+        if (n_new[~self.active] != 0).any():
+            raise ValueError("inactive rows cannot take tokens")
+        bs = self.block_size
+        if pad_inactive and bool((n_new[self.active] == 1).all()):
+            return self._advance_decode()
+        slots: List[np.ndarray] = []
+        new_entries: List[List[int]] = []
+        qsl = np.zeros(self.max_seqs + 1, dtype=np.int32)
+        for row in range(self.max_seqs):
+            n = int(n_new[row])
+            if n == 0:
+                qsl[row + 1] = qsl[row]
+                continue
+            L0 = int(self.lens[row])
+            pos = np.arange(L0, L0 + n, dtype=np.int64)
+            lb = pos // bs
+            if lb[-1] >= self.max_blocks:
+                raise ValueError(f"row {row}: {L0 + n} tokens exceed max_blocks_per_seq={self.max_blocks}")
+            for j in range(int(lb[0]), int(lb[-1]) + 1):
+                if self.table[row, j] < 0:
+                    if j < self._first_live[row]:
+                        raise RuntimeError("append into a block that was already retired")
+                    pb = self.pool.allocate()
+                    self.table[row, j] = pb
+                    new_entries.append([row, j, pb])
+            slots.append(self.table[row, lb].astype(np.int64) * bs + pos % bs)
+            self.lens[row] = L0 + n
+            qsl[row + 1] = qsl[row] + n
+        retired = self._retire(n_new)
+        return StepPlan(
+            slot_mapping=np.concatenate(slots) if slots else np.zeros(0, dtype=np.int64),
+            seq_lens=self.lens.copy(), query_start_loc=qsl,
+            new_entries=np.asarray(new_entries, dtype=np.int32).reshape(-1, 3), retired=retired)
+
+    def _advance_decode(self) -> StepPlan:
+        """The decode step (one token per active row, token i <-> row i) without a Python
+        loop over rows: only rows that cross a block edge are visited one by one."""
+        bs = self.block_size
+        rows = np.nonzero(self.active)[0]
+        pos = self.lens[rows].astype(np.int64)
+        lb = pos // bs
+        if rows.size and lb.max() >= self.max_blocks:
+            raise ValueError(f"a sequence exceeds max_blocks_per_seq={self.max_blocks}")
+        new_entries: List[List[int]] = []
+        for i in np.nonzero(self.table[rows, lb] < 0)[0]:
+            row, j = int(rows[i]), int(lb[i])
+            if j < self._first_live[row]:
+                raise RuntimeError("append into a block that was already retired")
+            pb = self.pool.allocate()
+            self.table[row, j] = pb
+            new_entries.append([row, j, pb])
+        slot_mapping = np.full(self.max_seqs, -1, dtype=np.int64)
+        slot_mapping[rows] = self.table[rows, lb].astype(np.int64) * bs + pos % bs
+        self.lens[rows] += 1
+        retired: List[List[int]] = [[] for _ in range(self.max_seqs)]
+        if self.window_left >= 0 and rows.size:
+            t0 = np.maximum(self.lens[rows].astype(np.int64) - 1 - self.window_left, 0)
+            first_live = np.minimum(t0 // bs, self.max_blocks)
+            for i in np.nonzero(first_live > self._first_live[rows])[0]:
+                row = int(rows[i])
+                ids = []
+                for j in range(int(self._first_live[row]), int(first_live[i])):
+                    if self.table[row, j] >= 0:
+                        ids.append(int(self.table[row, j]))
+                        self.table[row, j] = -1
+                self._first_live[row] = int(first_live[i])
+                self.pool.release(ids)
+                retired[row] = ids
+        return StepPlan(slot_mapping=slot_mapping, seq_lens=self.lens.copy(),
+                        query_start_loc=np.arange(self.max_seqs + 1, dtype=np.int32),
+                        new_entries=np.asarray(new_entries, dtype=np.int32).reshape(-1, 3),
+                        retired=retired)
+
+    def _retire(self, n_new: np.ndarray) -> List[List[int]]:
+        out: List[List[int]] = [[] for _ in range(self.max_seqs)]
+        if self.window_left < 0:
+            return out
+        for row in np.nonzero(self.active)[0]:
+            n = int(n_new[row]) if n_new[row] > 0 else 1
+            t0 = first_visible(int(self.lens[row]), n, self.window_left)
+            first_live = min(t0 // self.block_size, self.max_blocks)
+            ids = []
+            for j in range(int(self._first_live[row]), first_live):
+                if self.table[row, j] >= 0:
+                    ids.append(int(self.table[row, j]))
+                    self.table[row, j] = -1
+            if first_live > self._first_live[row]:
+                self._first_live[row] = first_live
+            self.pool.release(ids)
+            out[int(row)] = ids
+        return out

@@ -40,7 +40,8 @@ kv_append_kernel(const uint8_t* __restrict__ key, const uint8_t* __restrict__ va
   const int b = (bid - T) * 128 + threadIdx.x;
   if (b >= B) return;
   const int L = seq_lens[b];
-  const int n_new = query_start_loc ? (query_start_loc[b + 1] - query_start_loc[b]) : 1;
+  int n_new = query_start_loc ? (query_start_loc[b + 1] - query_start_loc[b]) : 1;
+  if (n_new < 1) n_new = 1;  // a row without a query this step keeps what its last query saw
   const int t0 = first_visible(L, n_new, window_left);
   int first_live = t0 / block_size;
   if (first_live > max_blocks) first_live = max_blocks;

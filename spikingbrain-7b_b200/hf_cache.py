@@ -1,0 +1,265 @@
+"""The HF ``Cache`` surface of hf_7B_model/cache.py over paged device memory.
+
+Same constructor, ``update`` / ``get_seq_length`` / ``get_max_length`` /
+``to_legacy_cache`` / ``from_legacy_cache`` and container protocol as the reference
+class, same values in everything it returns -- but the sliding-window K/V of a layer
+live in a paged pool that is appended to in place (2 KiB per token and layer at 7B
+shapes) instead of being rolled or re-concatenated on every step
+(hf_7B_model/cache.py:94-107 moves the whole window per token).
+
+What a caller gets back from ``update(...)['attn_state']`` is gathered on demand through
+the block table, so a caller that only wants attention over the window should use the
+fast paths instead and never materialise it:
+    cache.swa_decode(q, layer_idx)           sliding-window attention on the paged K/V
+    cache.gla_step(q, k, v, g, layer_idx)    in-place GLA state step + read-out
+
+Behaviour at the edges of the reference class (hf_7B_model/cache.py:96-107):
+  * an append of n tokens onto a FULL window with n > window raises RuntimeError (the
+    reference fails with a shape mismatch there);
+  * an append that takes a not-yet-full window past the window size raises
+    NotImplementedError: the reference silently stops trimming from then on and grows
+    without bound, which no caller wants from a paged pool.
+Tensors must live on a CUDA device: there is no CPU path.
+"""
+from typing import Any, Dict, List, Optional, Tuple
+
+import numpy as np
+import torch
+import transformers
+
+from . import ops
+from .block_pool import SlidingWindowBlockManager
+
+
+class _PagedWindow:
+    """Paged K/V of one sliding-window layer for a fixed batch of equally long sequences."""
+
+    def __init__(self, B: int, kvh: int, D: int, dtype: torch.dtype, device, window: Optional[int],
+                 block_size: int, capacity_tokens: int):
+        self.B, self.kvh, self.D, self.dtype, self.device = B, kvh, D, dtype, device
+        self.window = window
+        self.bs = block_size
+        self.n_cached = 0  # tokens the reference class would hold now
+        self._alloc(capacity_tokens)
+        for row in range(B):
+            self.mgr.admit(row)
+
+    def _alloc(self, capacity_tokens: int) -> None:
+        self.max_blocks = -(-capacity_tokens // self.bs) + 2
+        nb = self.B * self.max_blocks
+        self.mgr = SlidingWindowBlockManager(nb, self.bs, -1 if self.window is None else self.window - 1,
+                                             self.B, self.max_blocks)
+        self.kv = torch.zeros(2, nb, self.bs, self.kvh, self.D, dtype=self.dtype, device=self.device)
+        self.table_d = torch.full((self.B, self.max_blocks), -1, dtype=torch.int32, device=self.device)
+        self.lens_d = torch.zeros(self.B, dtype=torch.int32, device=self.device)
+        self.status = torch.zeros(1, dtype=torch.int32, device=self.device)
+
+    # The logical block index of a sequence only ever grows; before it would run off the table
+    # the live blocks are moved back to column 0 (positions are relative, nothing else changes).
+    def _make_room(self, n: int) -> None:
+        L = int(self.mgr.lens[0])
+        if (L + n + self.bs - 1) // self.bs <= self.max_blocks:
+            return
+        if self.window is None:  # unbounded layer: double the pool and carry the contents over
+            k_all, v_all = self.gather()
+            self._alloc(2 * (L + n))
+            for row in range(self.B):
+                self.mgr.admit(row)
+            self.n_cached = 0
+            self.append(k_all, v_all)
+            return
+        shift = int(self.mgr._first_live.min())
+        if shift == 0:
+            raise RuntimeError("window layer out of table columns with nothing retired")
+        m = self.mgr
+        m.table[:, :-shift] = m.table[:, shift:]
+        m.table[:, -shift:] = -1
+        m.lens -= shift * self.bs
+        m._first_live -= shift
+        self.table_d.copy_(torch.from_numpy(m.table))
+        self.lens_d.copy_(torch.from_numpy(m.lens))
+        if (int(m.lens[0]) + n + self.bs - 1) // self.bs > self.max_blocks:
+            raise RuntimeError(f"{n} new tokens do not fit the table of a window-{self.window} layer")
+
+    def append(self, k: torch.Tensor, v: torch.Tensor) -> None:
+        """k, v: [B, kvh, n, D] -- the reference layout of `attn_state`."""
+        n = k.shape[-2]
+        W = self.window
+        if self.n_cached == 0:
+            if W is not None and n > W:  # first insert keeps the last `window` tokens (cache.py:81-83)
+                k, v, n = k[..., -W:, :], v[..., -W:, :], W
+            n_cached = n
+        elif W is not None and self.n_cached == W:
+            if n > W:
+                raise RuntimeError(f"cannot roll {n} new tokens into a full window of {W}")
+            n_cached = W
+        else:
+            if W is not None and self.n_cached + n > W:
+                raise NotImplementedError(
+                    f"appending {n} tokens to {self.n_cached} cached ones crosses the window of {W}; "
+                    "the reference class stops trimming in this case and grows without bound")
+            n_cached = self.n_cached + n
+        self._make_room(n)
+        self.n_cached = n_cached
+        plan = self.mgr.advance(np.full(self.B, n, dtype=np.int64), pad_inactive=(n == 1))
+        if plan.new_entries.size:
+            e = torch.from_numpy(plan.new_entries).to(self.device, non_blocking=True).long()
+            self.table_d[e[:, 0], e[:, 1]] = e[:, 2].int()
+        slots = torch.from_numpy(plan.slot_mapping).to(self.device, non_blocking=True)
+        self.lens_d.copy_(torch.from_numpy(plan.seq_lens), non_blocking=True)
+        qsl = torch.from_numpy(plan.query_start_loc).to(self.device, non_blocking=True)
+        kt = k.transpose(1, 2).reshape(self.B * n, self.kvh, self.D)
+        vt = v.transpose(1, 2).reshape(self.B * n, self.kvh, self.D)
+        ops.kv_append(kt, vt, self.kv[0], self.kv[1], slots, block_tables=self.table_d,
+                      seq_lens=self.lens_d, query_start_loc=qsl, window_left=self.mgr.window_left,
+                      status=self.status)
+
+    def gather(self) -> Tuple[torch.Tensor, torch.Tensor]:
+        return ops.kv_gather(self.kv[0], self.kv[1], self.table_d, self.lens_d, self.n_cached,
+                             window_left=self.n_cached - 1, status=self.status)
+
+    def decode(self, q: torch.Tensor, scale: Optional[float], out=None) -> torch.Tensor:
+        return ops.swa_decode(q, self.kv[0], self.kv[1], self.table_d, self.lens_d,
+                              window_left=self.n_cached - 1, scale=scale, out=out, status=self.status)
+
+
+class _LayerState(dict):
+    """The per-layer dict of the reference class; 'attn_state' of a paged layer is gathered
+    through the block table when it is read."""
+
+    def __init__(self, recurrent_state=None, attn_state=None, conv_state=None,
+                 paged: Optional[_PagedWindow] = None):
+        super().__init__(recurrent_state=recurrent_state, attn_state=attn_state, conv_state=conv_state)
+        self.paged = paged
+
+    def __getitem__(self, key):
+        if key == "attn_state" and self.paged is not None:
+            return self.paged.gather()
+        return super().__getitem__(key)
+
+    def get(self, key, default=None):
+        return self[key] if key in self else default
+
+    def materialise(self) -> Dict[str, Any]:
+        return {k: self[k] for k in ("recurrent_state", "attn_state", "conv_state")}
+
+
+class Cache(transformers.cache_utils.Cache):
+    """Drop-in for hf_7B_model/cache.py:11 `Cache` (same public surface and values)."""
+
+    def __init__(self, seen_tokens: int = 0, *, block_size: int = 16, unbounded_capacity: int = 4096):
+        # like the reference, the transformers base initialiser is not chained
+        self.states: List[_LayerState] = []
+        self._seen_tokens = seen_tokens
+        self._block_size = block_size
+        self._unbounded_capacity = unbounded_capacity
+
+    def __getitem__(self, layer_idx: int) -> Dict[str, Any]:
+        if layer_idx < len(self):
+            return self.states[layer_idx]
+        raise KeyError(f"Cache only has {len(self)} layers, attempted to access layer with index {layer_idx}")
+
+    def __iter__(self):
+        for state in self.states:
+            yield state
+
+    def __len__(self):
+        return len(self.states)
+
+    def _new_paged(self, attn_state, window) -> _PagedWindow:
+        k = attn_state[0]
+        if not k.is_cuda:
+            raise RuntimeError("this Cache keeps K/V in paged CUDA memory; CPU tensors are not supported")
+        B, kvh, n, D = k.shape
+        cap = 3 * window + 2 * self._block_size if window is not None else max(self._unbounded_capacity, 2 * n)
+        return _PagedWindow(B, kvh, D, k.dtype, k.device, window, self._block_size, cap)
+
+    def update(self, recurrent_state: torch.Tensor = None,
+               attn_state: Tuple[torch.Tensor, torch.Tensor] = None,
+               conv_state: Tuple[torch.Tensor] = None, layer_idx: int = 0,
+               offset: Optional[int] = 1, cache_kwargs: Optional[Dict[str, Any]] = None) -> Dict[str, Any]:
+        if layer_idx == 0:
+            self._seen_tokens += offset
+        window = None
+        if attn_state is not None:
+            window = (cache_kwargs or {}).get("window_size", None)
+            if not isinstance(attn_state, tuple) or len(attn_state) != 2:
+                raise ValueError("`attn_state` must be a tuple of two tensors for key/value states")
+        if len(self.states) <= layer_idx:
+            paged = None
+            if attn_state is not None:
+                paged = self._new_paged(attn_state, window)
+                paged.append(*attn_state)
+            state = _LayerState(recurrent_state=recurrent_state, conv_state=conv_state, paged=paged)
+            self.states.append(state)
+            return state
+        state = self.states[layer_idx]
+        if recurrent_state is not None:
+            dict.__setitem__(state, "recurrent_state", recurrent_state)
+        if attn_state is not None:
+            if state.paged is None:  # a layer restored from a legacy tuple: page it now
+                dense = dict.__getitem__(state, "attn_state")
+                state.paged = self._new_paged(dense if dense is not None else attn_state, window)
+                if dense is not None:
+                    # restored tensors are what the reference would hold: already trimmed
+                    state.paged.append(*dense)
+                    dict.__setitem__(state, "attn_state", None)
+            if state.paged.window != window:
+                raise ValueError("window_size changed between updates of one layer")
+            state.paged.append(*attn_state)
+        if conv_state is not None:
+            dict.__setitem__(state, "conv_state", conv_state)
+        return state
+
+    def get_seq_length(self, layer_idx: Optional[int] = 0) -> int:
+        if len(self.states) <= layer_idx:
+            return 0
+        return self._seen_tokens
+
+    def get_max_length(self) -> Optional[int]:
+        return None
+
+    def to_legacy_cache(self) -> Tuple[Dict[str, Any], ...]:
+        return tuple(s.materialise() for s in self.states)
+
+    @classmethod
+    def from_legacy_cache(cls, past_key_values: Optional[Tuple[Dict[str, Any], ...]] = None,
+                          seen_tokens: int = 0) -> "Cache":
+        cache = cls(seen_tokens)
+        if past_key_values is not None:
+            for d in past_key_values:
+                cache.states.append(_LayerState(recurrent_state=d.get("recurrent_state"),
+                                                attn_state=d.get("attn_state"),
+                                                conv_state=d.get("conv_state")))
+        return cache
+
+    # ------------------------------------------------------------------ fast paths
+    def swa_decode(self, q: torch.Tensor, layer_idx: int, scale: Optional[float] = None,
+                   out: Optional[torch.Tensor] = None) -> torch.Tensor:
+        """Attention of one query token per sequence over the layer's cached window, the
+        query's own K/V having been appended by `update` first. q: [B, H, D] or [B, H, 1, D]
+        (bf16); returns [B, H, D]. Equals softmax(q K^T * scale) V over exactly the tokens
+        `update(...)['attn_state']` would return."""
+        state = self[layer_idx]
+        if state.paged is None:
+            raise ValueError(f"layer {layer_idx} holds no paged attention state")
+        if q.dim() == 4:
+            q = q.squeeze(2)
+        return state.paged.decode(q.contiguous(), scale, out)
+
+    def gla_step(self, q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, g: torch.Tensor,
+                 layer_idx: int, scale: Optional[float] = None) -> torch.Tensor:
+        """One-token GLA step of layer `layer_idx`, in place on its recurrent state:
+        what `fused_recurrent_gla(q, k, v, g, initial_state=S, output_final_state=True)`
+        followed by `update(recurrent_state=S', layer_idx, offset=1)` does in
+        hf_7B_model/gla_attention.py:153-168, without allocating a new state.
+        q [B, H, 1, D] or [B, H, D]; k, v, g likewise with H or Hkv heads. Returns o [B, H, D]."""
+        sq = lambda t: (t.squeeze(2) if t.dim() == 4 else t).contiguous()
+        q, k, v, g = sq(q), sq(k), sq(v), sq(g)
+        B, H, D = q.shape
+        S = self[layer_idx]["recurrent_state"] if layer_idx < len(self) else None
+        if S is None:
+            S = torch.zeros(B, H, D, D, dtype=torch.float32, device=q.device)
+        o = ops.gla_step(q, k, v, g, S, scale=scale)
+        self.update(recurrent_state=S, layer_idx=layer_idx, offset=1)
+        return o

@@ -15,6 +15,12 @@ from ._abi import SBK_BF16, SBK_F32
 _DTYPE_CODE = {torch.bfloat16: SBK_BF16, torch.float32: SBK_F32}
 DEFAULT_SPLIT_CHUNKS = 32  # 16-token chunks per split of a sequence (512 tokens)
 
+# Instrumentation for benchmarks. LAUNCHES counts the kernels this module has launched.
+# When SWA_TIMING is a list, every swa_decode call appends a (start, end) pair of CUDA
+# events recorded on the launching stream around its kernels.
+LAUNCHES = 0
+SWA_TIMING = None
+
 
 def _ptr(t: Optional[torch.Tensor]) -> Optional[int]:
     return None if t is None else t.data_ptr()
@@ -84,6 +90,8 @@ def kv_append(key: torch.Tensor, value: torch.Tensor, k_cache: torch.Tensor, v_c
         tok_stride, nb, bs, bstride, _ptr(block_tables), max_blocks, _ptr(seq_lens),
         _ptr(query_start_loc), B, window_left, _ptr(retired_out), max_ret, _ptr(status), _stream())
     _abi.check("sbk_kv_append", rc)
+    global LAUNCHES
+    LAUNCHES += 1 if (T or B) else 0
 
 
 def kv_gather(k_cache: torch.Tensor, v_cache: torch.Tensor, block_tables: torch.Tensor,
@@ -104,6 +112,8 @@ def kv_gather(k_cache: torch.Tensor, v_cache: torch.Tensor, block_tables: torch.
         k_cache.element_size(), nb, bs, bstride, window_left, _ptr(k_out), _ptr(v_out), n_out,
         _ptr(status), _stream())
     _abi.check("sbk_kv_gather", rc)
+    global LAUNCHES
+    LAUNCHES += 1 if (B and n_out) else 0
     return k_out, v_out
 
 
@@ -155,6 +165,11 @@ def swa_decode(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor,
         workspace = swa_workspace(B, H, d, max_pieces, q.device)
     if scale is None:
         scale = d ** -0.5
+    timing = SWA_TIMING
+    if timing is not None:
+        ev0 = torch.cuda.Event(enable_timing=True)
+        ev1 = torch.cuda.Event(enable_timing=True)
+        ev0.record()
     rc = _abi.lib.sbk_swa_decode(
         _ptr(q), q.stride(0) if B else H * d, _ptr(k_cache), _ptr(v_cache), _ptr(block_tables),
         max_blocks, _ptr(seq_lens), B, H, kvh, d, nb, bs, bstride, window_left, float(scale),
@@ -162,6 +177,11 @@ def swa_decode(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor,
         _ptr(workspace), workspace.numel() if workspace is not None else 0, split_chunks,
         max_pieces, _ptr(status), _stream())
     _abi.check("sbk_swa_decode", rc)
+    if timing is not None:
+        ev1.record()
+        timing.append((ev0, ev1))
+    global LAUNCHES
+    LAUNCHES += (2 if max_pieces > 1 else 1) if B else 0
     return out
 
 
@@ -199,4 +219,6 @@ def gla_step(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, g: torch.Tensor,
         _ptr(slot_idx), B, H, Hkv, D, float(scale), _ptr(out), _DTYPE_CODE[out.dtype],
         _ptr(status), _stream())
     _abi.check("sbk_gla_step", rc)
+    global LAUNCHES
+    LAUNCHES += 1 if B else 0
     return out

@@ -1,0 +1,210 @@
+"""Generates the golden fixtures in this directory by running the REFERENCE's own code.
+
+Run it only in a container that holds the reference checkout (read-only):
+
+    python tests/golden/make_golden.py [/path/to/SpikingBrain-7B]
+
+It executes, on the CPU,
+  * hf_7B_model/cache.py `Cache.update` on deterministic K/V streams          -> cache_*.npz
+  * hf_7B_model/window_attention_sdpa.py `FlashAttention.forward` with the
+    projections replaced by slicers (q/k/v injected, RoPE neutral at position 0)
+    on top of that Cache                                                      -> swa_sdpa.npz
+  * the Triton kernel of vllm_hymeta/model_for_7B/my_fused_recurrent.py under
+    TRITON_INTERPRET=1 (fp32 inputs: the interpreter has no bf16)             -> gla_triton.npz
+The fixtures are what the oracle (oracle/ref_ops.py) and the CUDA kernels are pinned to;
+the tests never import the reference.
+"""
+import hashlib
+import importlib.util
+import os
+import sys
+
+os.environ["TRITON_INTERPRET"] = "1"  # must be set before triton is imported
+
+import numpy as np
+import torch
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+REF = sys.argv[1] if len(sys.argv) > 1 else "/root/reference"
+
+
+def load_ref(rel_path, name):
+    spec = importlib.util.spec_from_file_location(name, os.path.join(REF, rel_path))
+    mod = importlib.util.module_from_spec(spec)
+    sys.modules[name] = mod
+    spec.loader.exec_module(mod)
+    return mod
+
+
+def digest(t: torch.Tensor) -> str:
+    return hashlib.sha256(t.contiguous().numpy().tobytes()).hexdigest()
+
+
+def stream_kv(B, kvh, n, D, t_start, salt):
+    """Deterministic, all-distinct K/V values: no RNG, so tests rebuild them exactly."""
+    b = torch.arange(B).view(B, 1, 1, 1)
+    h = torch.arange(kvh).view(1, kvh, 1, 1)
+    t = (t_start + torch.arange(n)).view(1, 1, n, 1)
+    d = torch.arange(D).view(1, 1, 1, D)
+    k = ((b * 7919 + h * 613 + t * 131 + d * 17 + salt) % 8191).float() / 8191.0 - 0.5
+    v = ((b * 6151 + h * 389 + t * 97 + d * 29 + salt * 3) % 8179).float() / 8179.0 - 0.5
+    return k, v
+
+
+# ------------------------------------------------------------------ 1. cache streams
+def cache_streams():
+    cache_mod = load_ref("hf_7B_model/cache.py", "ref_cache")
+    cases = {
+        # name: (B, kvh, D, window, prefill, [append sizes...])
+        "prefill_gt_window": (2, 2, 64, 64, 128, [1] * 32),          # configs[0] shapes
+        "prefill_lt_window": (2, 2, 64, 64, 40, [1] * 40),           # grows to exactly W, then rolls
+        "prefill_eq_window": (1, 4, 128, 32, 32, [1] * 5),
+        "chunks_on_full_window": (2, 2, 64, 64, 64, [16, 16, 1, 16, 64]),
+        "single_token_start": (1, 1, 64, 16, 1, [1] * 20),
+    }
+    out = {}
+    for name, (B, kvh, D, W, prefill, appends) in cases.items():
+        cache = cache_mod.Cache()
+        # layer 0 is a GLA layer (recurrent slot), layer 1 the SWA layer, as in configs[0]
+        digests, seen = [], []
+        t = 0
+        for step, n in enumerate([prefill] + appends):
+            rs = torch.full((B, 2, 4, 4), float(step))
+            cache.update(recurrent_state=rs, layer_idx=0, offset=n)
+            assert cache[0]["recurrent_state"] is rs  # a reference swap, not a copy
+            k, v = stream_kv(B, kvh, n, D, t, salt=len(name))
+            st = cache.update(attn_state=(k, v), layer_idx=1, offset=n, cache_kwargs={"window_size": W})
+            kc, vc = st["attn_state"]
+            digests.append(digest(kc) + digest(vc))
+            seen.append((cache.get_seq_length(0), cache.get_seq_length(1), kc.shape[-2]))
+            t += n
+        out[name + "/meta"] = np.array([B, kvh, D, W, prefill] + appends, dtype=np.int64)
+        out[name + "/digests"] = np.array(digests)
+        out[name + "/seen"] = np.array(seen, dtype=np.int64)
+        out[name + "/final_k"] = kc.numpy()
+        out[name + "/final_v"] = vc.numpy()
+    # behaviours at the edges of what the class supports (hf_7B_model/cache.py:96-107)
+    c = cache_mod.Cache()
+    k, v = stream_kv(1, 1, 60, 64, 0, 1)
+    c.update(attn_state=(k, v), layer_idx=0, offset=60, cache_kwargs={"window_size": 64})
+    k, v = stream_kv(1, 1, 8, 64, 60, 1)
+    n68 = c.update(attn_state=(k, v), layer_idx=0, offset=8, cache_kwargs={"window_size": 64})["attn_state"][0].shape[-2]
+    out["overshoot_len"] = np.array([n68])  # 68: the cat branch overshoots the window and never rolls again
+    try:
+        c2 = cache_mod.Cache()
+        k, v = stream_kv(1, 1, 64, 64, 0, 1)
+        c2.update(attn_state=(k, v), layer_idx=0, offset=64, cache_kwargs={"window_size": 64})
+        k, v = stream_kv(1, 1, 128, 64, 64, 1)
+        c2.update(attn_state=(k, v), layer_idx=0, offset=128, cache_kwargs={"window_size": 64})
+        out["oversize_chunk_raises"] = np.array([0])
+    except RuntimeError:
+        out["oversize_chunk_raises"] = np.array([1])
+    try:
+        cache_mod.Cache()[0]
+        out["getitem_raises_keyerror"] = np.array([0])
+    except KeyError:
+        out["getitem_raises_keyerror"] = np.array([1])
+    np.savez_compressed(os.path.join(HERE, "cache_streams.npz"), **out)
+    print("cache_streams.npz", {k: v.shape for k, v in out.items() if k.endswith("seen")})
+
+
+# ---------------------------------------------------------------- 2. SWA decode (SDPA)
+class _Slice(torch.nn.Module):
+    def __init__(self, lo, hi):
+        super().__init__()
+        self.lo, self.hi = lo, hi
+
+    def forward(self, x):
+        return x[..., self.lo:self.hi]
+
+
+def swa_sdpa():
+    # the package __init__ pulls in fla-backed modules; load the two files it needs directly
+    import types
+    pkg = types.ModuleType("hf_7B_model")
+    pkg.__path__ = [os.path.join(REF, "hf_7B_model")]
+    sys.modules["hf_7B_model"] = pkg
+    load_ref("hf_7B_model/cache.py", "hf_7B_model.cache")
+    wa = load_ref("hf_7B_model/window_attention_sdpa.py", "hf_7B_model.window_attention_sdpa")
+    cache_mod = sys.modules["hf_7B_model.cache"]
+    out = {}
+    for name, (B, H, kvh, D, W, prefill, steps) in {
+        "g7": (1, 14, 2, 128, 64, 100, 6),       # 7 query heads per kv head, window crossed
+        "short": (1, 4, 4, 128, 64, 5, 4),      # fewer tokens than the window
+    }.items():
+        torch.manual_seed(1234)
+        attn = wa.FlashAttention(hidden_size=H * D, num_heads=H, num_key_value_heads=kvh,
+                                 sliding_window=W, layer_idx=0)
+        attn.q_proj = _Slice(0, H * D)
+        attn.k_proj = _Slice(H * D, (H + kvh) * D)
+        attn.v_proj = _Slice((H + kvh) * D, (H + 2 * kvh) * D)
+        attn.o_proj = torch.nn.Identity()
+        attn.eval()
+        cache = cache_mod.Cache()
+        total = prefill + steps
+        x = (torch.randn(B, total, (H + 2 * kvh) * D) / D ** 0.5).bfloat16().float()  # bf16-representable
+        outs = []
+        with torch.no_grad():
+            for (lo, hi) in [(0, prefill)] + [(prefill + i, prefill + i + 1) for i in range(steps)]:
+                pos = torch.zeros(B, hi - lo, dtype=torch.long)  # cos=1, sin=0: RoPE is the identity
+                o, _, _ = attn(x[:, lo:hi], position_ids=pos, past_key_values=cache, use_cache=True)
+                # the reference counts tokens on layer 0 only; this one-layer harness IS layer 0
+                outs.append(o)
+        out[name + "/meta"] = np.array([B, H, kvh, D, W, prefill, steps], dtype=np.int64)
+        out[name + "/x_bf16"] = x.bfloat16().view(torch.int16).numpy()
+        out[name + "/prefill_out_tail"] = outs[0][:, -4:].numpy()
+        out[name + "/decode_out"] = torch.cat(outs[1:], dim=1).numpy()
+    np.savez_compressed(os.path.join(HERE, "swa_sdpa.npz"), **out)
+    print("swa_sdpa.npz", {k: v.shape for k, v in out.items()})
+
+
+# ------------------------------------------------------------------- 3. GLA (Triton)
+def golden_state(slots, H, D):
+    """Deterministic fp32 start state (no RNG): values in [-1, 1) with a different pattern
+    per slot, head, row and column."""
+    i = torch.arange(slots * H * D * D, dtype=torch.int64)
+    return (((i * 2654435761) % 1000003).double() / 500001.5 - 1.0).float().view(slots, H, D, D)
+
+
+def gla_triton():
+    mfr = load_ref("vllm_hymeta/model_for_7B/my_fused_recurrent.py", "ref_mfr")
+    out = {}
+    for name, (B, H, D, slots, dtype) in {
+        "f32_d128": (3, 2, 128, 4, torch.float32),
+        "f32_d64": (2, 8, 64, 2, torch.float32),
+        "f32_d128_g7": (1, 7, 128, 2, torch.float32),
+    }.items():
+        g = torch.Generator().manual_seed(77)
+        q = torch.relu(torch.randn(B, H, 1, D, generator=g)).to(dtype)
+        k = torch.relu(torch.randn(B, H, 1, D, generator=g)).to(dtype)
+        v = torch.randn(B, H, 1, D, generator=g).to(dtype)
+        gk = (torch.nn.functional.logsigmoid(torch.randn(B, H, 1, D, generator=g)) / 16).to(dtype)
+        state = golden_state(slots, H, D)
+        slot = torch.randperm(slots, generator=g)[:B].to(torch.int64)
+        if B > 2:
+            slot[1] = -1
+        state0 = state.clone()
+        o = torch.zeros_like(q)
+        steps_out = []
+        for _ in range(2):  # two chained steps on the same inputs: the state carries
+            mfr.my_fused_recurrent_fwd_kernel[(B, H, D // 64)](
+                q, k, v, gk, o, D, state, slot, D ** -0.5, q.stride(0), q.stride(1),
+                state.stride(0), state.stride(1), state.stride(2), state.stride(3), 64)
+            steps_out.append(o.float().clone())
+        out[name + "/meta"] = np.array([B, H, D, slots, int(dtype == torch.bfloat16)], dtype=np.int64)
+        for nm, t in (("q", q), ("k", k), ("v", v), ("g", gk)):
+            out[f"{name}/{nm}"] = t.float().squeeze(2).numpy()
+        out[name + "/slot"] = slot.numpy()
+        out[name + "/state2"] = state.numpy()  # state0 is golden_state(): rebuilt by the tests
+        assert torch.equal(state[[i for i in range(slots) if i not in slot.tolist()]],
+                           state0[[i for i in range(slots) if i not in slot.tolist()]])
+        out[name + "/out1"] = steps_out[0].squeeze(2).numpy()
+        out[name + "/out2"] = steps_out[1].squeeze(2).numpy()
+    np.savez_compressed(os.path.join(HERE, "gla_triton.npz"), **out)
+    print("gla_triton.npz", {k: v.shape for k, v in out.items() if k.endswith("state2")})
+
+
+if __name__ == "__main__":
+    cache_streams()
+    swa_sdpa()
+    gla_triton()

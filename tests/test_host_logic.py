@@ -1,0 +1,296 @@
+"""CPU: host-side logic -- the C ABI exports, the block manager, the backend metadata classes,
+the GLA slot manager and the argument checking of the surfaces. No kernel is launched here."""
+import ctypes
+import os
+import re
+
+import numpy as np
+import pytest
+import torch
+
+from oracle import ref_ops
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+# ------------------------------------------------------------------------------- C ABI
+def test_library_exports_every_declared_symbol(sb):
+    header = open(os.path.join(ROOT, "include", "sbk.h")).read()
+    declared = set(re.findall(r"\b(sbk_[a-z_0-9]+)\s*\(", header))
+    assert {"sbk_kv_append", "sbk_kv_gather", "sbk_swa_decode", "sbk_swa_workspace_bytes",
+            "sbk_gla_step", "sbk_last_error", "sbk_abi_version"} <= declared
+    lib = ctypes.CDLL(os.path.join(ROOT, "spikingbrain-7b_b200", "libsbk.so"))
+    for name in declared:
+        assert hasattr(lib, name), f"{name} declared in include/sbk.h but not exported"
+    from spikingbrain_7b_b200 import _abi
+    assert set(_abi.SIGNATURES) == declared
+    assert _abi.lib.sbk_abi_version() == 1
+
+
+def test_host_side_argument_errors_need_no_gpu(sb):
+    """Argument validation happens before any CUDA call, so it can be exercised on the CPU."""
+    from spikingbrain_7b_b200 import _abi
+    lib = _abi.lib
+    rc = lib.sbk_gla_step(None, None, None, None, 0, None, 4, None, 2, 28, 4, 96, 1.0, None, 0, None, None)
+    assert rc == _abi.SBK_E_ARG and b"D=96" in lib.sbk_last_error()
+    rc = lib.sbk_swa_decode(None, 0, None, None, None, 4, None, 2, 36, 4, 128, 8, 16, 0, 63, 1.0, None, 0, 0,
+                            None, None, 0, 0, 1, None, None)
+    assert rc == _abi.SBK_E_ARG and b"unsupported shape" in lib.sbk_last_error()
+    rc = lib.sbk_swa_decode(None, 0, None, None, None, 4, None, 2, 28, 4, 128, 8, 24, 0, 63, 1.0, None, 0, 0,
+                            None, None, 0, 0, 1, None, None)
+    assert rc == _abi.SBK_E_ARG and b"multiple of 16" in lib.sbk_last_error()
+    assert lib.sbk_kv_append(None, None, None, None, None, 3, 4, 128, 2, 1024, 8, 16, 16384, None, 0, None,
+                             None, 0, -1, None, 0, None, None) == _abi.SBK_E_ARG
+    # empty work is a successful no-op
+    assert lib.sbk_gla_step(None, None, None, None, 0, None, 0, None, 0, 28, 4, 128, 1.0, None, 0, None, None) == 0
+    assert lib.sbk_swa_workspace_bytes(256, 28, 128, 9) >= 256 * 9 * 28 * 130 * 4
+    with pytest.raises(RuntimeError):
+        from spikingbrain_7b_b200 import ops
+        ops.gla_step(torch.zeros(1, 2, 64), torch.zeros(1, 2, 64), torch.zeros(1, 2, 64),
+                     torch.zeros(1, 2, 64), torch.zeros(1, 2, 64, 64))   # CPU tensors: no CPU path
+
+
+# ----------------------------------------------------------------------- block manager
+@pytest.mark.parametrize("bs,wl", [(16, 40), (32, 63), (16, -1), (16, 0)])
+def test_block_manager_matches_oracle_retirement(bs, wl):
+    """Prompt + decode steps: slots, table and retired ids equal the oracle's rule applied to
+    an independently tracked table."""
+    from spikingbrain_7b_b200.block_pool import SlidingWindowBlockManager
+    lens0 = [1, 15, 16, 17, 100, 333]
+    B, steps = len(lens0), 80
+    max_blocks = (max(lens0) + steps + bs) // bs + 1
+    mgr = SlidingWindowBlockManager(B * (max_blocks + 1), bs, wl, B, max_blocks)
+    for r in range(B):
+        mgr.admit(r)
+    shadow = torch.full((B, max_blocks), -1, dtype=torch.int32)
+    lens = [0] * B
+    for step in range(steps + 1):
+        n_new = lens0 if step == 0 else [1] * B
+        plan = mgr.advance(np.array(n_new))
+        for r, j, pb in plan.new_entries.tolist():
+            assert shadow[r, j] == -1
+            shadow[r, j] = pb
+        lens = [L + n for L, n in zip(lens, n_new)]
+        assert plan.seq_lens.tolist() == lens
+        # slots point at the right place of the right block
+        off = 0
+        for r, n in enumerate(n_new):
+            for i in range(n):
+                pos = lens[r] - n + i
+                assert plan.slot_mapping[off + i] == int(shadow[r, pos // bs]) * bs + pos % bs
+            off += n
+        exp = ref_ops.retire_blocks(shadow, lens, n_new, wl, bs)
+        assert plan.retired == exp, f"step {step}"
+        assert np.array_equal(mgr.table, shadow.numpy())
+        if wl >= 0 and step > 0:
+            for r in range(B):   # after a decode step the resident blocks are bounded by the window
+                assert mgr.resident_blocks(r) <= (wl + 1 + bs - 1) // bs + 1
+    used = int((mgr.table >= 0).sum())
+    assert used + mgr.pool.num_free == mgr.pool.num_blocks      # nothing leaked
+
+
+def test_block_manager_churn_reuses_blocks_and_pads_inactive_rows():
+    from spikingbrain_7b_b200.block_pool import OutOfBlocks, SlidingWindowBlockManager
+    bs, wl, B = 16, 63, 8
+    mgr = SlidingWindowBlockManager(64, bs, wl, B, 64)
+    rng = np.random.default_rng(0)
+    allocations = 0
+    for r in range(B - 1):
+        mgr.admit(r)
+    mgr.advance(np.array([int(x) for x in rng.integers(1, 120, B - 1)] + [0]), pad_inactive=False)
+    for step in range(200):
+        plan = mgr.advance(mgr.active.astype(np.int64))
+        assert plan.slot_mapping.shape == (B,) and (plan.slot_mapping[~mgr.active] == -1).all()
+        live = plan.slot_mapping[mgr.active]
+        assert len(set(live.tolist())) == len(live)              # no two sequences share a slot
+        allocations += len(plan.new_entries)
+        if step % 5 == 0:                                        # one sequence finishes, one arrives
+            victim = int(rng.choice(np.nonzero(mgr.active)[0]))
+            mgr.finish(victim)
+            newcomer = int(np.nonzero(~mgr.active)[0][0])
+            mgr.admit(newcomer)
+            mgr.advance(np.where(np.arange(B) == newcomer, int(rng.integers(1, 200)), 0), pad_inactive=False)
+    assert allocations > mgr.pool.num_blocks                     # retired blocks went round again
+    small = SlidingWindowBlockManager(2, bs, -1, 1, 8)
+    small.admit(0)
+    with pytest.raises(OutOfBlocks):
+        small.advance(np.array([100]))
+    with pytest.raises(ValueError):
+        SlidingWindowBlockManager(4, 24, 8, 1, 4)                # block size must be a multiple of 16
+
+
+# ------------------------------------------------------------------------------ backend
+def test_backend_static_surface():
+    from spikingbrain_7b_b200.backend import (MetaAttentionBackend, MetaAttentionImpl, MetaAttentionMetadata,
+                                               MetaAttentionMetadataBuilder)
+    assert MetaAttentionBackend.get_name() == "META_FLASH_ATTN"
+    assert MetaAttentionBackend.accept_output_buffer is True
+    assert MetaAttentionBackend.get_supported_head_sizes() == [32, 64, 96, 128, 160, 192, 224, 256]
+    assert MetaAttentionBackend.get_kv_cache_shape(10, 16, 4, 128) == (2, 10, 16, 4, 128)
+    with pytest.raises(ValueError):
+        MetaAttentionBackend.get_kv_cache_shape(10, 8, 4, 128)
+    assert MetaAttentionBackend.get_impl_cls() is MetaAttentionImpl
+    assert MetaAttentionBackend.get_metadata_cls() is MetaAttentionMetadata
+    assert MetaAttentionBackend.get_builder_cls() is MetaAttentionMetadataBuilder
+    impl = MetaAttentionImpl(28, 128, 128 ** -0.5, 4, None, 4097, "auto")
+    assert impl.sliding_window == (4096, 0) and impl.num_queries_per_kv == 7
+    assert MetaAttentionImpl(28, 128, 1.0, 4, None, None, "auto").sliding_window == (-1, -1)
+    with pytest.raises(NotImplementedError):
+        MetaAttentionImpl(28, 128, 1.0, 4, None, 4097, "auto", kv_sharing_target_layer_name="x")
+    with pytest.raises(ValueError):
+        MetaAttentionImpl(28, 128, 1.0, 4, None, 4097, "auto", blocksparse_params={})
+    with pytest.raises(ValueError):
+        MetaAttentionImpl(28, 100, 1.0, 4, None, 4097, "auto")
+    with pytest.raises(NotImplementedError):
+        MetaAttentionImpl(28, 128, 1.0, 4, None, 4097, "fp8")
+    # block copies are plain tensor moves
+    kv = torch.arange(2 * 6 * 2, dtype=torch.float32).view(2, 6, 2)
+    before = kv.clone()
+    MetaAttentionBackend.copy_blocks([kv], torch.tensor([[0, 3], [1, 5]]))
+    assert torch.equal(kv[:, 3], before[:, 0]) and torch.equal(kv[:, 5], before[:, 1])
+    dst = torch.zeros_like(kv)
+    MetaAttentionBackend.swap_blocks(kv, dst, torch.tensor([[2, 4]]))
+    assert torch.equal(dst[:, 4], kv[:, 2]) and dst[:, :4].sum() == 0
+
+
+class _Obj:
+    def __init__(self, **kw):
+        self.__dict__.update(kw)
+
+
+def _builder(inter, sliding_window, block_size=16, chunked=False):
+    from spikingbrain_7b_b200.backend import MetaAttentionMetadataBuilder
+    runner = _Obj(device="cpu", pin_memory=False, graph_block_tables=np.zeros((8, 6), dtype=np.int32))
+    ib = _Obj(runner=runner, sliding_window=sliding_window, block_size=block_size, inter_data_list=inter,
+              chunked_prefill_enabled=chunked)
+    b = MetaAttentionMetadataBuilder(ib)
+    b.prepare()
+    return b
+
+
+def test_metadata_builder_decode_window_truncates_tables():
+    """Two decoding sequences under a window: trailing blocks only, slots at the last position,
+    views split correctly (meta_attention.py:435-494, 521-608)."""
+    tables = {7: list(range(100, 140)), 9: [5, 6]}
+    inter = [
+        _Obj(is_prompt=False, block_tables=tables, seq_ids=[7], input_tokens=[[1]], orig_seq_lens=[600],
+             seq_lens=[72], query_lens=[1], context_lens=[599], curr_sliding_window_blocks=[5],
+             multi_modal_placeholder_maps=None, prefix_cache_hit=False),
+        _Obj(is_prompt=False, block_tables=tables, seq_ids=[9], input_tokens=[[2]], orig_seq_lens=[20],
+             seq_lens=[20], query_lens=[1], context_lens=[19], curr_sliding_window_blocks=[0],
+             multi_modal_placeholder_maps=None, prefix_cache_hit=False),
+    ]
+    b = _builder(inter, sliding_window=65)
+    md = b.build(seq_lens=[72, 20], query_lens=[1, 1], cuda_graph_pad_size=-1, batch_size=2)
+    assert md.num_prefills == 0 and md.num_decode_tokens == 2 and md.max_decode_seq_len == 72
+    assert md.block_tables.tolist() == [[135, 136, 137, 138, 139], [5, 6, 0, 0, 0]]
+    assert md.slot_mapping.tolist() == [tables[7][599 // 16] * 16 + 599 % 16, 6 * 16 + 3]
+    assert md.seq_lens_tensor.dtype == torch.int32 and md.slot_mapping.dtype == torch.int64
+    assert md.query_start_loc.tolist() == [0, 1, 2] and md.seq_start_loc.tolist() == [0, 72, 92]
+    assert md.prefill_metadata is None
+    dm = md.decode_metadata
+    assert dm is md.decode_metadata and dm.num_decode_tokens == 2 and dm.block_tables.shape == (2, 5)
+
+
+def test_metadata_builder_mixed_batch_and_graph_padding():
+    """A chunked prompt followed by a decode, then the captured-graph padding path."""
+    tables = {1: [3, 4, 8], 2: [9]}
+    inter = [
+        _Obj(is_prompt=True, block_tables=tables, seq_ids=[1], input_tokens=[[0] * 20], orig_seq_lens=[40],
+             seq_lens=[40], query_lens=[20], context_lens=[20], curr_sliding_window_blocks=[0],
+             multi_modal_placeholder_maps=None, prefix_cache_hit=False),
+        _Obj(is_prompt=False, block_tables=tables, seq_ids=[2], input_tokens=[[5]], orig_seq_lens=[4],
+             seq_lens=[4], query_lens=[1], context_lens=[3], curr_sliding_window_blocks=[0],
+             multi_modal_placeholder_maps=None, prefix_cache_hit=False),
+    ]
+    b = _builder(inter, sliding_window=None, chunked=True)
+    md = b.build(seq_lens=[40, 4], query_lens=[20, 1], cuda_graph_pad_size=-1, batch_size=21)
+    assert (md.num_prefills, md.num_prefill_tokens, md.num_decode_tokens) == (1, 20, 1)
+    exp = [tables[1][p // 16] * 16 + p % 16 for p in range(20, 40)] + [9 * 16 + 3]
+    assert md.slot_mapping.tolist() == exp
+    pm, dm = md.prefill_metadata, md.decode_metadata
+    assert pm.slot_mapping.tolist() == exp[:20] and dm.slot_mapping.tolist() == exp[20:]
+    assert pm.block_tables.tolist() == [[3, 4, 8]] and dm.block_tables.tolist() == [[9, 0, 0]]
+    assert pm.context_lens_tensor.tolist() == [20] and dm.query_start_loc.tolist() == [0, 1]
+    # a prompt longer than the window masks the tokens nothing will look at again
+    from spikingbrain_7b_b200.backend import PAD_SLOT_ID, compute_slot_mapping, compute_slot_mapping_start_idx
+    sm = []
+    start = compute_slot_mapping_start_idx(True, 40, 0, 16)
+    compute_slot_mapping(False, sm, 1, 40, 0, start, 16, {1: [3, 4, 8]})
+    assert sm[:24] == [PAD_SLOT_ID] * 24 and sm[24:] == [4 * 16 + 8 + i for i in range(8)] + [8 * 16 + i for i in range(8)]
+    sm = []
+    compute_slot_mapping(True, sm, 1, 40, 0, 0, 16, None)      # profile run: nothing is written
+    assert sm == [PAD_SLOT_ID] * 40
+    # captured graph: batch padded from 1 to 4 sequences
+    inter = [inter[1]]
+    b = _builder(inter, sliding_window=None)
+    md = b.build(seq_lens=[4, 1, 1, 1], query_lens=[1, 1, 1, 1], cuda_graph_pad_size=3, batch_size=4)
+    assert md.use_cuda_graph and md.num_decode_tokens == 4
+    assert md.slot_mapping.tolist() == [9 * 16 + 3, -1, -1, -1]
+    assert md.block_tables.shape == (4, 6) and md.block_tables[0, 0] == 9
+
+
+def test_metadata_advance_step_moves_slots_on_device_tensors():
+    from spikingbrain_7b_b200.backend import MetaAttentionMetadata
+    tables = torch.tensor([[3, 4, 8], [9, 2, 0]], dtype=torch.int32)
+    md = MetaAttentionMetadata(
+        num_prefills=0, num_prefill_tokens=0, num_decode_tokens=2,
+        slot_mapping=torch.tensor([4 * 16 + 15, 9 * 16 + 3]), seq_lens=[32, 4],
+        seq_lens_tensor=torch.tensor([32, 4], dtype=torch.int32), max_prefill_seq_len=0, max_decode_seq_len=32,
+        context_lens_tensor=torch.tensor([31, 3], dtype=torch.int32), block_tables=tables, use_cuda_graph=False,
+        max_query_len=1, max_decode_query_len=1, query_start_loc=torch.tensor([0, 1, 2], dtype=torch.int32),
+        seq_start_loc=torch.tensor([0, 32, 36], dtype=torch.int32))
+    mi = _Obj(input_tokens=torch.zeros(2, dtype=torch.long), input_positions=torch.zeros(2, dtype=torch.long))
+    md.advance_step(mi, torch.tensor([[11], [12]]), block_size=16, num_seqs=2, num_queries=2)
+    assert md.seq_lens == [33, 5] and md.seq_lens_tensor.tolist() == [33, 5] and md.max_decode_seq_len == 33
+    assert md.slot_mapping.tolist() == [8 * 16 + 0, 9 * 16 + 4]     # first sequence moved into its next block
+    assert mi.input_tokens.tolist() == [11, 12] and mi.input_positions.tolist() == [32, 4]
+
+
+# ---------------------------------------------------------------------------- GLA slots
+def test_gla_slot_manager_assigns_releases_and_forks():
+    from spikingbrain_7b_b200.gla_slots import GLACacheManager, GLACacheParams
+    mgr = GLACacheManager(torch.float32, (2, 4, 3, 8, 8), device="cpu")
+    cache, idx = mgr.current_run_tensors({"a": [0], "b": [1]})
+    assert cache.shape == (2, 4, 3, 8, 8) and idx.dtype == torch.int64 and len(set(idx.tolist())) == 2
+    sa = int(idx[0])
+    cache[:, sa] = 7.0
+    _, idx2 = mgr.current_run_tensors({"a": [0, 5], "b": [1]}, pad_to=5)      # "a" forks a second sequence
+    assert idx2.tolist()[0] == sa and idx2.tolist()[3:] == [-1, -1]
+    fork = idx2.tolist()[1]
+    assert torch.equal(cache[:, fork], cache[:, sa])            # the fork starts from its sibling's state
+    _, idx3 = mgr.current_run_tensors({"c": [2]}, finished_requests_ids=["a"])
+    assert int(idx3[0]) in (sa, fork) and cache[:, int(idx3[0])].abs().sum() == 0   # reused slot comes back zeroed
+    p = GLACacheParams(cache, idx3).at_layer_idx(1)
+    assert p.gla_cache.shape == (4, 3, 8, 8) and p.state_indices_tensor is idx3
+    with pytest.raises(ValueError):
+        GLACacheManager(torch.bfloat16, (2, 4, 3, 8, 8), device="cpu")
+    with pytest.raises(RuntimeError):
+        mgr.current_run_tensors({"d": [0], "e": [0], "f": [0], "g": [0]})    # more sequences than slots
+
+
+# ----------------------------------------------------------------------------- HF cache
+def test_hf_cache_surface_without_gpu():
+    import transformers
+    from spikingbrain_7b_b200.hf_cache import Cache
+    c = Cache()
+    assert isinstance(c, transformers.cache_utils.Cache)
+    assert len(c) == 0 and c.get_seq_length() == 0 and c.get_max_length() is None and list(c) == []
+    with pytest.raises(KeyError):
+        c[0]
+    rs = torch.zeros(2, 4, 8, 8)
+    st = c.update(recurrent_state=rs, layer_idx=0, offset=5)
+    assert st["recurrent_state"] is rs and st["attn_state"] is None and c.get_seq_length() == 5
+    assert c.get_seq_length(1) == 0                              # layer 1 has no entry yet
+    rs2 = torch.ones(2, 4, 8, 8)
+    c.update(recurrent_state=rs2, layer_idx=0, offset=1)
+    assert c[0]["recurrent_state"] is rs2 and c.get_seq_length() == 6
+    with pytest.raises(ValueError):
+        c.update(attn_state=[rs, rs], layer_idx=1, cache_kwargs={"window_size": 4})
+    with pytest.raises(RuntimeError):                           # K/V must live on the GPU
+        c.update(attn_state=(torch.zeros(1, 1, 2, 64), torch.zeros(1, 1, 2, 64)), layer_idx=1,
+                 cache_kwargs={"window_size": 4})
+    legacy = c.to_legacy_cache()
+    assert isinstance(legacy, tuple) and legacy[0]["recurrent_state"] is rs2
+    c2 = Cache.from_legacy_cache(legacy, seen_tokens=6)
+    assert len(c2) == 1 and c2.get_seq_length() == 6 and c2[0]["recurrent_state"] is rs2
