@@ -110,7 +110,12 @@ int sbk_kv_gather(const void* k_cache, const void* v_cache, const int32_t* block
  *  window_left  keys visible left of the query (-1 = all)
  *  out          [B, H, D] of `out_dtype` (SBK_BF16 or SBK_F32), `out_seq_stride` elements
  *  lse_out      [B, H] float natural-log-sum-exp of the scaled scores, or NULL
- *  workspace    split-K partials; at least sbk_swa_workspace_bytes(B,H,D,max_pieces) bytes
+ *  workspace    at least sbk_swa_workspace_bytes(B,H,D,max_pieces) bytes, 16-byte aligned. It
+ *               begins with the work-ticket counter and one completion counter per sequence
+ *               (16 + 4*roundup(B,4) bytes): these must be ZERO before the first call with a
+ *               given buffer and B, and every call that ends without SBK_ST_WAIT_TIMEOUT leaves
+ *               them zero. Split-K partials follow. Calls that overlap on the GPU need
+ *               separate workspaces.
  *  split_chunks target number of 16-token chunks per split (<=0: library default)
  *  max_pieces   upper bound on splits per sequence (grid.x); >= 1
  * Supported: D == 128, H % kvh == 0, H/kvh <= 8, kvh in {1,2,4}, block_size % 16 == 0.

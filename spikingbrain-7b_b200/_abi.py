@@ -8,7 +8,8 @@ import os
 from ctypes import c_char_p, c_float, c_int, c_int64, c_size_t, c_void_p
 
 PKG_DIR = os.path.dirname(os.path.abspath(__file__))
-LIB_PATH = os.path.join(PKG_DIR, "libsbk.so")
+# SBK_LIB_PATH points the binding at another build of the same sources (profiling variants)
+LIB_PATH = os.environ.get("SBK_LIB_PATH") or os.path.join(PKG_DIR, "libsbk.so")
 
 SBK_BF16, SBK_F32 = 0, 1
 SBK_OK, SBK_E_ARG, SBK_E_ALIGN, SBK_E_WORKSPACE, SBK_E_LAUNCH = 0, -1, -2, -3, -4

@@ -425,15 +425,16 @@ class MetaAttentionImpl:
             raise NotImplementedError("the sliding-window decode kernel is built for head size 128")
         self.attn_type = attn_type
         self._status: Optional[torch.Tensor] = None
-        self._workspace: Optional[torch.Tensor] = None
+        self._workspace: Dict[Any, Optional[torch.Tensor]] = {}
 
     def _scratch(self, B: int, max_pieces: int, device) -> Optional[torch.Tensor]:
-        need = ops._abi.lib.sbk_swa_workspace_bytes(B, self.num_heads, self.head_size, max_pieces)
-        if need == 0:
-            return None
-        if self._workspace is None or self._workspace.numel() < need or self._workspace.device != device:
-            self._workspace = torch.empty(need, dtype=torch.uint8, device=device)
-        return self._workspace
+        # one zero-initialised buffer per batch geometry: the counters at its head are laid out
+        # by batch size and are handed back zeroed by every call
+        key = (B, max_pieces, str(device))
+        ws = self._workspace.get(key)
+        if ws is None:
+            ws = self._workspace[key] = ops.swa_workspace(B, self.num_heads, self.head_size, max_pieces, device)
+        return ws
 
     def status(self) -> int:
         """Device-side status bits accumulated by this layer's kernels (synchronises)."""

@@ -1,54 +1,57 @@
-// Sliding-window paged-attention decode for sm_100a.
+// Sliding-window paged-attention decode for sm_100a: a persistent, warp-specialised,
+// HBM-streaming kernel.
 //
 // Work decomposition
-//   grid = (max_pieces, B). A CTA owns one split ("piece") of one sequence: a
-//   run of 16-token chunks inside the visible window [t0, seq_len). It streams
-//   those chunks for ALL kv heads, so every token it touches is one contiguous
-//   kvh*D*2-byte row of K and one of V.
+//   A work item is one split ("piece") of one sequence: a run of 16-token chunks of the
+//   visible window [t0, seq_len). The grid is two CTAs per SM; each CTA draws items from a
+//   global ticket counter until none is left, so ragged batches balance themselves and the
+//   copy pipeline never drains between items.
 // Data movement
-//   One producer warp walks the block table and issues one bulk async copy
-//   (TMA engine, untiled form) per token row into a ring of shared-memory
-//   stages; completion is counted in bytes on an mbarrier per stage. Rows are
-//   laid down with a 16-byte skew so that ldmatrix reads of 8 tokens at a
-//   fixed head/dim offset hit 8 different bank groups.
+//   One producer warp per CTA walks the block table and issues one bulk async copy (TMA
+//   engine, untiled form) per token row -- all kv heads of a token are one contiguous
+//   kvh*256-byte row of K and one of V -- into a ring of 32 KiB shared-memory stages.
+//   Completion is counted in bytes on an mbarrier per stage. Rows are laid down with a
+//   16-byte skew so that ldmatrix reads of 8 tokens at one head/dim offset hit 8 different
+//   bank groups. A stage also carries a small descriptor (sequence, piece, token range,
+//   first/last flags), so the consumers learn about items from the stream itself.
 // Math
-//   4 consumer warps; warp w serves kv head w % kvh and every (4/kvh)-th chunk.
-//   Warps that take the same chunks form a group with a private ring of stages
-//   and private barriers, so every waiter sees every phase of its barriers in
-//   order (a parity wait cannot tell phase n from phase n+2).
-//   Scores are formed TRANSPOSED, S^T[token, head] = K[token, :] . Q^T, with
-//   mma.sync m16n8k16 (16 tokens x 8 query heads of the kv group), so the
-//   7-of-8 head padding wastes 1/8 of the tile instead of 9/16; softmax runs
-//   on the accumulator fragment with warp shuffles over the token axis;
-//   P^T is turned into the B fragment with movmatrix; O^T[d, head] += V^T . P^T,
-//   with P split into a bf16 head and a bf16 remainder (two MMAs) so that the
-//   rounding of the probabilities stays below the bf16 rounding of the output.
-//   Warps that share a kv head merge their (m, l, O) through shared memory.
+//   4 consumer warps. A stage holds 64/kvh tokens; warp w serves kv head w % kvh and the
+//   16-token sub-chunk w / kvh of every stage. Scores are formed TRANSPOSED,
+//   S^T[token, head] = K[token, :] . Q^T, with mma.sync m16n8k16 (16 tokens x the 8 query
+//   heads of a kv group), so padding 7 heads to 8 wastes 1/8 of the tile; softmax runs on
+//   the accumulator fragment with warp shuffles over the token axis; P^T becomes the B
+//   fragment through movmatrix; O^T[d, head] += V^T . P^T with P split into a bf16 head and
+//   a bf16 remainder (two MMAs), which keeps the rounding of the probabilities below the
+//   bf16 rounding of the output.
 // Split-K
-//   A sequence with more than one piece writes un-normalised partials to the
-//   workspace; swa_reduce_kernel folds them. One piece writes `out` directly.
-// HBM-bound: min(seq_len, window_left+1) * kvh*D*2*2 bytes read per sequence.
+//   A sequence with several pieces writes un-normalised partials (m, l, O) to the workspace;
+//   the CTA that completes the last piece of a sequence (a counter per sequence) folds them
+//   and writes the output, so there is no second kernel. A single piece writes `out` directly.
+// HBM-bound: min(seq_len, window_left+1) * kvh*128*2*2 bytes read per sequence.
 #include "sbk_common.cuh"
 
 namespace sbk {
 
-constexpr int kChunk = 16;          // tokens per pipeline stage
-constexpr int kD = 128;             // head dim
+constexpr int kChunk = 16;            // tokens per MMA tile
+constexpr int kD = 128;               // head dim
 constexpr int kConsumerWarps = 4;
-constexpr int kStagesPerGroup = 3;
-constexpr int kThreads = (kConsumerWarps + 1) * 32;
-constexpr int kHeadStride = 132;    // floats per head row in the merge buffer (bank skew)
+constexpr int kConsumers = kConsumerWarps * 32;
+constexpr int kThreads = kConsumers + 32;
+constexpr int kMaxSeqs = 1024;        // sequences per launch (prefix and length tables in shared memory)
+constexpr int kHeadStride = 132;      // floats per head row in the merge buffer (bank skew)
+constexpr int kMergeWarpBytes = 8 * kHeadStride * 4 + 64;
 constexpr float kLog2e = 1.4426950408889634f;
 constexpr float kLn2 = 0.6931471805599453f;
 constexpr float kNegBig = -1.0e30f;
+
+enum : int { kFlagFirst = 1, kFlagLast = 2, kFlagBad = 4, kFlagEnd = 8 };
 
 struct Plan {
   int t0, c_first, n_chunks, n_pieces, chunks_per_piece;
 };
 
-// The split of a sequence into pieces; the main and the reduce kernel must agree on it.
-__device__ __forceinline__ Plan make_plan(int L, int window_left, int split_chunks,
-                                          int max_pieces) {
+// The split of a sequence into pieces.
+__device__ __forceinline__ Plan make_plan(int L, int window_left, int split_chunks, int max_pieces) {
   Plan p;
   if (L <= 0) {
     p.t0 = 0; p.c_first = 0; p.n_chunks = 0; p.n_pieces = 1; p.chunks_per_piece = 0;
@@ -64,18 +67,30 @@ __device__ __forceinline__ Plan make_plan(int L, int window_left, int split_chun
   return p;
 }
 
+struct StageInfo {   // written by the producer before it arms the stage's barrier
+  int b, piece, n_pieces, tok_base, lo, hi, flags, pad;
+};
+
 template <int KVH>
 struct Cfg {
+  static constexpr int kSub = kConsumerWarps / KVH;            // 16-token sub-chunks per stage
+  static constexpr int kStageTokens = kSub * kChunk;
   static constexpr int kRowBytes = KVH * kD * 2;
   static constexpr int kRowStride = kRowBytes + 16;
-  static constexpr int kStageBytes = 2 * kChunk * kRowStride;   // K rows then V rows
-  static constexpr int kWarpsPerHead = kConsumerWarps / KVH;   // = number of chunk groups
-  static constexpr int kStages = kWarpsPerHead * kStagesPerGroup;
-  static constexpr int kMergeBytes = kConsumerWarps * (8 * kHeadStride * 4 + 64);
+  static constexpr int kVOffset = kStageTokens * kRowStride;   // K rows, then V rows
+  static constexpr int kStageBytes = 2 * kVOffset;
+  static constexpr int kStages = KVH == 4 ? 3 : 2;
   static constexpr int kRingBytes = kStages * kStageBytes;
-  static constexpr int kSmemBytes = (kRingBytes > kMergeBytes ? kRingBytes : kMergeBytes) +
-                                    2 * kStages * 8 + 16;
+  static constexpr int kMergeBytes = kSub > 1 ? kConsumerWarps * kMergeWarpBytes : 0;
+  static constexpr int kInfoOff = kRingBytes + kMergeBytes;
+  static constexpr int kPreOff = kInfoOff + kStages * (int)sizeof(StageInfo);
+  static constexpr int kLensOff = kPreOff + (kMaxSeqs + 4) * 4;
+  static constexpr int kBarOff = kLensOff + kMaxSeqs * 4;
+  static constexpr int kMiscOff = kBarOff + 2 * kStages * 8;
+  static constexpr int kSmemBytes = kMiscOff + 32;
+  static constexpr int kRowsPerLane = 2 * kStageTokens / 32;
   static_assert(kConsumerWarps % KVH == 0, "warps must split evenly over kv heads");
+  static_assert(kSmemBytes <= 115200, "two CTAs must fit one SM");
 };
 
 template <typename TO>
@@ -87,315 +102,471 @@ __device__ __forceinline__ void store_out<__nv_bfloat16>(__nv_bfloat16* p, float
   *p = __float2bfloat16_rn(x);
 }
 
+__device__ __forceinline__ void consumer_bar() {
+  asm volatile("bar.sync 1, %0;" ::"n"(kConsumers) : "memory");
+}
+
+struct Params {
+  const __nv_bfloat16* q; int64_t q_seq_stride;
+  const uint8_t* k_cache; const uint8_t* v_cache;
+  const int32_t* block_tables; int max_blocks;
+  const int32_t* seq_lens; int B; int H; int64_t num_blocks;
+  int block_size; int64_t block_stride; int window_left; float scale_log2;
+  void* out; int64_t out_seq_stride; float* lse_out;
+  int32_t* ctrl;      // [0] next ticket, [1] CTAs that ran out of tickets
+  int32_t* done;      // [B] pieces finished per sequence
+  float* ws_o; float* ws_ml; int split_chunks; int max_pieces; int32_t* status;
+};
+
 template <int KVH, typename TO>
-__global__ void __launch_bounds__(kThreads, 2)
-swa_decode_kernel(const __nv_bfloat16* __restrict__ q, int64_t q_seq_stride,
-                  const uint8_t* __restrict__ k_cache, const uint8_t* __restrict__ v_cache,
-                  const int32_t* __restrict__ block_tables, int max_blocks,
-                  const int32_t* __restrict__ seq_lens, int H, int64_t num_blocks,
-                  int block_size, int64_t block_stride, int window_left, float scale_log2,
-                  TO* __restrict__ out, int64_t out_seq_stride, float* __restrict__ lse_out,
-                  float* __restrict__ ws_o, float* __restrict__ ws_ml, int split_chunks,
-                  int max_pieces, int32_t* status) {
+__global__ void __launch_bounds__(kThreads, 2) swa_decode_kernel(const Params P) {
   using C = Cfg<KVH>;
   extern __shared__ __align__(128) uint8_t smem[];
-  const int b = blockIdx.y;
-  const int piece = blockIdx.x;
-  const int L = seq_lens[b];
-  const Plan plan = make_plan(L, window_left, split_chunks, max_pieces);
-  if (piece >= plan.n_pieces) return;
-  const int G = H / KVH;
-
-  int cb = plan.c_first + piece * plan.chunks_per_piece;
-  int n = plan.n_chunks - piece * plan.chunks_per_piece;
-  if (n > plan.chunks_per_piece) n = plan.chunks_per_piece;
-  if (n < 0) n = 0;
-  const int t0 = plan.t0;
-  const int32_t* table = block_tables + (int64_t)b * max_blocks;
-
-  // ---- every block id this piece will dereference must lie inside the pool ----
-  {
-    int bad = 0;
-    if (n > 0) {
-      int tb = cb * kChunk; if (tb < t0) tb = t0;
-      int te = (cb + n) * kChunk; if (te > L) te = L;
-      const int lb0 = tb / block_size, lb1 = (te - 1) / block_size;
-      for (int lb = lb0 + threadIdx.x; lb <= lb1; lb += kThreads) {
-        if (lb >= max_blocks) { bad = 1; break; }
-        const int32_t pb = table[lb];
-        if (pb < 0 || pb >= num_blocks) { bad = 1; break; }
-      }
-    }
-    if (__syncthreads_or(bad)) {
-      if (threadIdx.x == 0) raise_status(status, SBK_ST_BAD_BLOCK);
-      n = 0;  // contribute nothing; the output stays finite
-    }
-  }
-
   const uint32_t ring = smem_u32(smem);
-  const uint32_t bar_full = ring + (C::kSmemBytes - 2 * C::kStages * 8 - 16);
+  StageInfo* info = reinterpret_cast<StageInfo*>(smem + C::kInfoOff);
+  int* pre = reinterpret_cast<int*>(smem + C::kPreOff);
+  int* lens_s = reinterpret_cast<int*>(smem + C::kLensOff);
+  const uint32_t bar_full = ring + C::kBarOff;
   const uint32_t bar_empty = bar_full + C::kStages * 8;
-  volatile int* abort_flag = reinterpret_cast<volatile int*>(smem + C::kSmemBytes - 16);
-
+  volatile int* misc = reinterpret_cast<volatile int*>(smem + C::kMiscOff);  // [0] abort, [1] fold flag, [2..6] scan
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
+  const int G = P.H / KVH;
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < C::kStages; ++s) {
       mbar_init(bar_full + 8 * s, 1);
-      mbar_init(bar_empty + 8 * s, KVH);
+      mbar_init(bar_empty + 8 * s, kConsumerWarps);
     }
-    *abort_flag = 0;
+    misc[0] = 0;
+    pre[0] = 0;
     fence_mbar_init();
   }
-  // V rows that a ragged first or last chunk never fills must still hold finite values,
-  // since a zero probability times a NaN would poison the accumulator.
-  for (int s = 0; s < C::kStages; ++s) {
-    uint4* vreg = reinterpret_cast<uint4*>(smem + s * C::kStageBytes + kChunk * C::kRowStride);
-    for (int i = threadIdx.x; i < kChunk * C::kRowStride / 16; i += kThreads)
-      vreg[i] = make_uint4(0, 0, 0, 0);
+  // ---- number of pieces of every sequence, as an exclusive prefix: item w belongs to the
+  //      sequence b with pre[b] <= w < pre[b+1] ----
+  {
+    int running = 0;
+    for (int base = 0; base < P.B; base += kThreads) {
+      const int b = base + threadIdx.x;
+      const int Lb = b < P.B ? P.seq_lens[b] : 0;
+      if (b < P.B) lens_s[b] = Lb;
+      int incl = b < P.B ? make_plan(Lb, P.window_left, P.split_chunks, P.max_pieces).n_pieces : 0;
+#pragma unroll
+      for (int off = 1; off < 32; off <<= 1) {
+        const int t = __shfl_up_sync(0xffffffffu, incl, off);
+        if (lane >= off) incl += t;
+      }
+      __syncthreads();
+      if (lane == 31) misc[2 + warp] = incl;
+      __syncthreads();
+      int warp_off = 0, tile = 0;
+#pragma unroll
+      for (int w2 = 0; w2 < kThreads / 32; ++w2) {
+        const int t = misc[2 + w2];
+        if (w2 < warp) warp_off += t;
+        tile += t;
+      }
+      if (b < P.B) pre[b + 1] = running + warp_off + incl;
+      running += tile;
+    }
+    __syncthreads();
   }
-  fence_proxy_async_smem();
-  __syncthreads();
+  const int total = pre[P.B];
 
   if (warp == kConsumerWarps) {
-    // =============================== producer ===============================
-    const int r = lane & 15;
-    const int is_v = lane >> 4;
-    const uint8_t* base = is_v ? v_cache : k_cache;
-    for (int i = 0; i < n; ++i) {
-      const int grp = i % C::kWarpsPerHead, j = i / C::kWarpsPerHead;
-      const int s = grp * kStagesPerGroup + j % kStagesPerGroup;
-      const int use = j / kStagesPerGroup;
-      if (use > 0) {
-        if (!mbar_wait_bounded(bar_empty + 8 * s, (use - 1) & 1)) {
-          if (lane == 0) { raise_status(status, SBK_ST_WAIT_TIMEOUT); *abort_flag = 1; }
+    // ================================= producer =================================
+    int it = 0;
+    bool aborted = false;
+    int w_next = 0;
+    if (lane == 0) w_next = atomicAdd(&P.ctrl[0], 1);
+    while (!aborted) {
+      const int w = __shfl_sync(0xffffffffu, w_next, 0);
+      if (w >= total) break;
+      if (lane == 0) w_next = atomicAdd(&P.ctrl[0], 1);   // the next ticket is on its way while this item streams
+      int lo_b = 0, hi_b = P.B;   // largest b with pre[b] <= w
+      while (hi_b - lo_b > 1) {
+        const int mid = (lo_b + hi_b) >> 1;
+        if (pre[mid] <= w) lo_b = mid; else hi_b = mid;
+      }
+      const int b = lo_b;
+      const int piece = w - pre[b];
+      const int L = lens_s[b];
+      const Plan plan = make_plan(L, P.window_left, P.split_chunks, P.max_pieces);
+      const int cb = plan.c_first + piece * plan.chunks_per_piece;
+      int n = plan.n_chunks - piece * plan.chunks_per_piece;
+      if (n > plan.chunks_per_piece) n = plan.chunks_per_piece;
+      if (n < 0) n = 0;
+      int nst = (n + C::kSub - 1) / C::kSub;
+      if (nst < 1) nst = 1;   // an empty sequence still gets its (zero) output written
+      const int item_end = (cb + n) * kChunk;
+      const int32_t* table = P.block_tables + (int64_t)b * P.max_blocks;
+      int64_t pb_lane = -1;   // physical block of chunk (batch_c0 + lane): one table read per 32 chunks
+      int batch_c0 = 0;
+      for (int j = 0; j < nst; ++j, ++it) {
+        const int c0 = cb + j * C::kSub;       // first chunk of this stage
+        if (j == 0 || c0 + C::kSub > batch_c0 + 32) {
+          batch_c0 = c0;
+          const int c = c0 + lane;
+          const int lb = (c * kChunk) / P.block_size;
+          pb_lane = (c < cb + n && lb < P.max_blocks) ? (int64_t)table[lb] : -1;
+        }
+        const int s = it % C::kStages;
+        const int use = it / C::kStages;
+        if (use > 0 && !mbar_wait_bounded(bar_empty + 8 * s, (use - 1) & 1)) {
+          if (lane == 0) { raise_status(P.status, SBK_ST_WAIT_TIMEOUT); misc[0] = 1; }
+          aborted = true;
           break;
         }
+        if (misc[0]) { aborted = true; break; }
+        const int tok_base = c0 * kChunk;
+        int lo = tok_base > plan.t0 ? tok_base : plan.t0;
+        int hi = tok_base + C::kStageTokens;
+        if (hi > L) hi = L;
+        if (hi > item_end) hi = item_end;
+        if (hi < lo) hi = lo;
+        const uint8_t* src[C::kRowsPerLane];
+        bool valid[C::kRowsPerLane];
+        bool bad = false;
+#pragma unroll
+        for (int i = 0; i < C::kRowsPerLane; ++i) {
+          const int r = lane + 32 * i;
+          const int ti = r % C::kStageTokens;
+          const int is_v = r / C::kStageTokens;
+          const int tok = tok_base + ti;
+          valid[i] = tok >= lo && tok < hi;
+          const int64_t pb = __shfl_sync(0xffffffffu, pb_lane, (c0 - batch_c0) + ti / kChunk);
+          src[i] = nullptr;
+          if (valid[i]) {
+            if (pb < 0 || pb >= P.num_blocks) bad = true;
+            else src[i] = (is_v ? P.v_cache : P.k_cache) + pb * P.block_stride +
+                          (int64_t)(tok % P.block_size) * C::kRowBytes;
+          }
+        }
+        bad = __any_sync(0xffffffffu, bad);
+        if (lane == 0) {
+          StageInfo si;
+          si.b = b; si.piece = piece; si.n_pieces = plan.n_pieces; si.tok_base = tok_base;
+          si.lo = lo; si.hi = hi; si.pad = 0;
+          si.flags = (j == 0 ? kFlagFirst : 0) | (j == nst - 1 ? kFlagLast : 0) | (bad ? kFlagBad : 0);
+          info[s] = si;
+          if (bad) raise_status(P.status, SBK_ST_BAD_BLOCK);
+#ifdef SBK_SWA_BIGCOPY   // experiment only (needs SBK_SWA_SKIP_MATH, kvh 4, block 16): two 16 KiB copies per stage
+          mbar_arrive_expect_tx(bar_full + 8 * s, bad ? 0u : 2u * 16384u);
+#else
+          mbar_arrive_expect_tx(bar_full + 8 * s, bad ? 0u : 2u * (uint32_t)(hi - lo) * C::kRowBytes);
+#endif
+        }
+        __syncwarp();
+#ifdef SBK_SWA_BIGCOPY
+        const int64_t pb0 = __shfl_sync(0xffffffffu, pb_lane, c0 - batch_c0);
+        if (!bad && lane < 2) {
+          bulk_g2s(ring + s * C::kStageBytes + lane * C::kVOffset,
+                   (lane ? P.v_cache : P.k_cache) + pb0 * P.block_stride, 16384u, bar_full + 8 * s);
+        }
+        if (false) {
+#else
+        if (!bad) {
+#endif
+#pragma unroll
+          for (int i = 0; i < C::kRowsPerLane; ++i) {
+            if (valid[i]) {
+              const int r = lane + 32 * i;
+              bulk_g2s(ring + s * C::kStageBytes + r * C::kRowStride, src[i], C::kRowBytes, bar_full + 8 * s);
+            }
+          }
+        }
       }
-      if (*abort_flag) break;
-      const int tok_base = (cb + i) * kChunk;
-      int lo = tok_base > t0 ? tok_base : t0;
-      int hi = tok_base + kChunk < L ? tok_base + kChunk : L;
-      int nvalid = hi - lo; if (nvalid < 0) nvalid = 0;
-      if (lane == 0) mbar_arrive_expect_tx(bar_full + 8 * s, 2u * nvalid * C::kRowBytes);
-      __syncwarp();
-      const int tok = tok_base + r;
-      if (tok >= t0 && tok < L) {
-        const int lb = tok / block_size;
-        const int64_t pb = table[lb];
-        const uint8_t* src = base + pb * block_stride + (int64_t)(tok - lb * block_size) * C::kRowBytes;
-        const uint32_t dst = ring + s * C::kStageBytes + is_v * (kChunk * C::kRowStride) + r * C::kRowStride;
-        bulk_g2s(dst, src, C::kRowBytes, bar_full + 8 * s);
+    }
+    if (!aborted) {
+      // the end marker travels through the ring like any stage
+      const int s = it % C::kStages;
+      const int use = it / C::kStages;
+      if (use == 0 || mbar_wait_bounded(bar_empty + 8 * s, (use - 1) & 1)) {
+        if (lane == 0) {
+          StageInfo si = {};
+          si.flags = kFlagEnd;
+          info[s] = si;
+          mbar_arrive_expect_tx(bar_full + 8 * s, 0u);
+        }
+      } else if (lane == 0) {
+        raise_status(P.status, SBK_ST_WAIT_TIMEOUT);
+        misc[0] = 1;
+      }
+      // the CTA that draws the last losing ticket rewinds the counters for the next launch
+      if (lane == 0) {
+        const int f = atomicAdd(&P.ctrl[1], 1);
+        if (f == (int)gridDim.x - 1) { P.ctrl[0] = 0; P.ctrl[1] = 0; __threadfence(); }
       }
     }
     return;
   }
 
-  // ================================ consumers ================================
-  const int hk = warp % KVH;
-  const int phase = warp / KVH;
-  const int gq = lane >> 2;   // B-fragment column: query head inside the kv group
+  // ================================== consumers ==================================
+  const int hk = warp % KVH;     // kv head
+  const int sub = warp / KVH;    // 16-token sub-chunk of a stage
+  const int gq = lane >> 2;      // fragment row: token (scores) / head (B operand) / dim (output)
   const int tq = lane & 3;
+  TO* const out = reinterpret_cast<TO*>(P.out);
 
-  // Q^T as the B operand of S^T = K . Q^T : b0 = dims 2tq,2tq+1 of step kk, b1 = +8
   uint32_t qf[kD / 16][2];
-  {
-    const __nv_bfloat16* qp = q + (int64_t)b * q_seq_stride + (int64_t)(hk * G + gq) * kD + tq * 2;
-#pragma unroll
-    for (int kk = 0; kk < kD / 16; ++kk) {
-      if (gq < G) {
-        qf[kk][0] = *reinterpret_cast<const uint32_t*>(qp + kk * 16);
-        qf[kk][1] = *reinterpret_cast<const uint32_t*>(qp + kk * 16 + 8);
-      } else {
-        qf[kk][0] = 0u; qf[kk][1] = 0u;
-      }
-    }
-  }
   float acc[kD / 16][4];
-#pragma unroll
-  for (int mt = 0; mt < kD / 16; ++mt) { acc[mt][0] = acc[mt][1] = acc[mt][2] = acc[mt][3] = 0.f; }
   float m0 = -INFINITY, m1 = -INFINITY, l0 = 0.f, l1 = 0.f;
 
-  // per-lane ldmatrix row addresses inside a stage
   const int lj = lane >> 3, lr = lane & 7;
-  const uint32_t k_lane_off = (lr + ((lj & 1) ? 8 : 0)) * C::kRowStride + hk * (kD * 2) + ((lj >> 1) ? 16 : 0);
-  const uint32_t v_lane_off = kChunk * C::kRowStride + (lr + ((lj >> 1) ? 8 : 0)) * C::kRowStride +
+  const uint32_t k_lane_off = (sub * kChunk + lr + ((lj & 1) ? 8 : 0)) * C::kRowStride + hk * (kD * 2) +
+                              ((lj >> 1) ? 16 : 0);
+  const uint32_t v_lane_off = C::kVOffset + (sub * kChunk + lr + ((lj >> 1) ? 8 : 0)) * C::kRowStride +
                               hk * (kD * 2) + ((lj & 1) ? 16 : 0);
 
-  for (int i = phase, j = 0; i < n; i += C::kWarpsPerHead, ++j) {
-    const int s = phase * kStagesPerGroup + j % kStagesPerGroup;
-    if (!mbar_wait_bounded(bar_full + 8 * s, (j / kStagesPerGroup) & 1)) {
-      if (lane == 0) { raise_status(status, SBK_ST_WAIT_TIMEOUT); *abort_flag = 1; }
+  for (int it = 0;; ++it) {
+    const int s = it % C::kStages;
+    if (!mbar_wait_bounded(bar_full + 8 * s, (it / C::kStages) & 1)) {
+      if (lane == 0) { raise_status(P.status, SBK_ST_WAIT_TIMEOUT); misc[0] = 1; }
       break;
     }
+    const StageInfo si = info[s];
+    if (si.flags & kFlagEnd) break;
     const uint32_t stage = ring + s * C::kStageBytes;
 
-    // ---- S^T[16 tokens, 8 heads] ----
-    float sa[4] = {0.f, 0.f, 0.f, 0.f}, sb[4] = {0.f, 0.f, 0.f, 0.f};
+    if (si.flags & kFlagFirst) {
+      // Q^T as the B operand of S^T = K . Q^T : b0 = dims 2tq,2tq+1 of k-step kk, b1 = +8
+      const __nv_bfloat16* qp = P.q + (int64_t)si.b * P.q_seq_stride + (int64_t)(hk * G + gq) * kD + tq * 2;
 #pragma unroll
-    for (int kk = 0; kk < kD / 16; kk += 2) {
-      uint32_t a[4];
-      ldmatrix_x4(a, stage + k_lane_off + kk * 32);
-      mma_bf16_16816(sa, a, qf[kk][0], qf[kk][1]);
-      ldmatrix_x4(a, stage + k_lane_off + (kk + 1) * 32);
-      mma_bf16_16816(sb, a, qf[kk + 1][0], qf[kk + 1][1]);
-    }
-    float sc[4];
+      for (int kk = 0; kk < kD / 16; ++kk) {
+        if (gq < G) {
+          qf[kk][0] = *reinterpret_cast<const uint32_t*>(qp + kk * 16);
+          qf[kk][1] = *reinterpret_cast<const uint32_t*>(qp + kk * 16 + 8);
+        } else {
+          qf[kk][0] = 0u; qf[kk][1] = 0u;
+        }
+      }
 #pragma unroll
-    for (int e = 0; e < 4; ++e) sc[e] = (sa[e] + sb[e]) * scale_log2;
-
-    const int tok_base = (cb + i) * kChunk;
-    if (tok_base < t0 || tok_base + kChunk > L) {
-      const int ta = tok_base + gq, tb2 = ta + 8;
-      if (ta < t0 || ta >= L) { sc[0] = -INFINITY; sc[1] = -INFINITY; }
-      if (tb2 < t0 || tb2 >= L) { sc[2] = -INFINITY; sc[3] = -INFINITY; }
+      for (int mt = 0; mt < kD / 16; ++mt) { acc[mt][0] = acc[mt][1] = acc[mt][2] = acc[mt][3] = 0.f; }
+      m0 = m1 = -INFINITY; l0 = l1 = 0.f;
     }
 
-    // ---- online softmax over the token axis (lanes with equal tq share heads) ----
-    float mx0 = fmaxf(sc[0], sc[2]), mx1 = fmaxf(sc[1], sc[3]);
+    const int tb = si.tok_base + sub * kChunk;            // my 16 tokens: [tb, tb+16)
+    const int vlo = si.lo > tb ? si.lo : tb;
+    const int vhi = si.hi < tb + kChunk ? si.hi : tb + kChunk;
+    const bool ragged = vlo > tb || vhi < tb + kChunk;
+#ifdef SBK_SWA_SKIP_MATH
+    if (false) {
+#else
+    if (!(si.flags & kFlagBad) && vhi > vlo) {
+#endif
+      if (ragged) {
+        // V rows no copy filled must hold finite values: a zero probability times a NaN would
+        // poison the accumulator. Each warp clears its own head's 256 bytes of those rows.
 #pragma unroll
-    for (int off = 4; off < 32; off <<= 1) {
-      mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, off));
-      mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, off));
-    }
-    const float mn0 = fmaxf(m0, mx0), mn1 = fmaxf(m1, mx1);
-    const float ms0 = fmaxf(mn0, kNegBig), ms1 = fmaxf(mn1, kNegBig);
-    const float al0 = fast_exp2(m0 - ms0), al1 = fast_exp2(m1 - ms1);
-    m0 = mn0; m1 = mn1;
-    float p[4];
-    p[0] = fast_exp2(sc[0] - ms0);
-    p[1] = fast_exp2(sc[1] - ms1);
-    p[2] = fast_exp2(sc[2] - ms0);
-    p[3] = fast_exp2(sc[3] - ms1);
-    l0 = l0 * al0 + p[0] + p[2];
-    l1 = l1 * al1 + p[1] + p[3];
+        for (int r0 = 0; r0 < kChunk; r0 += 2) {
+          const int r = r0 + (lane >> 4);
+          const int tok = tb + r;
+          if (tok < vlo || tok >= vhi) {
+            *reinterpret_cast<uint4*>(smem + s * C::kStageBytes + C::kVOffset + (sub * kChunk + r) * C::kRowStride +
+                                      hk * (kD * 2) + (lane & 15) * 16) = make_uint4(0, 0, 0, 0);
+          }
+        }
+        __syncwarp();
+      }
+      // ---- S^T[16 tokens, 8 heads] ----
+      float sa[4] = {0.f, 0.f, 0.f, 0.f}, sb[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
-    for (int mt = 0; mt < kD / 16; ++mt) {
-      acc[mt][0] *= al0; acc[mt][1] *= al1; acc[mt][2] *= al0; acc[mt][3] *= al1;
-    }
-    // P^T as the B operand of O^T = V^T . P^T; p = head + remainder, both bf16
-    float ph[4], pl[4];
+      for (int kk = 0; kk < kD / 16; kk += 2) {
+        uint32_t a[4];
+        ldmatrix_x4(a, stage + k_lane_off + kk * 32);
+        mma_bf16_16816(sa, a, qf[kk][0], qf[kk][1]);
+        ldmatrix_x4(a, stage + k_lane_off + (kk + 1) * 32);
+        mma_bf16_16816(sb, a, qf[kk + 1][0], qf[kk + 1][1]);
+      }
+      float sc[4];
 #pragma unroll
-    for (int e = 0; e < 4; ++e) {
-      ph[e] = __bfloat162float(__float2bfloat16_rn(p[e]));
-      pl[e] = p[e] - ph[e];
-    }
-    const uint32_t pb0 = movmatrix_trans(pack_bf16x2(ph[0], ph[1]));
-    const uint32_t pb1 = movmatrix_trans(pack_bf16x2(ph[2], ph[3]));
-    const uint32_t pc0 = movmatrix_trans(pack_bf16x2(pl[0], pl[1]));
-    const uint32_t pc1 = movmatrix_trans(pack_bf16x2(pl[2], pl[3]));
+      for (int e = 0; e < 4; ++e) sc[e] = (sa[e] + sb[e]) * P.scale_log2;
+      if (ragged) {
+        const int ta = tb + gq, tb2 = ta + 8;
+        if (ta < vlo || ta >= vhi) { sc[0] = -INFINITY; sc[1] = -INFINITY; }
+        if (tb2 < vlo || tb2 >= vhi) { sc[2] = -INFINITY; sc[3] = -INFINITY; }
+      }
+      // ---- online softmax over the token axis (lanes with equal tq share heads) ----
+      float mx0 = fmaxf(sc[0], sc[2]), mx1 = fmaxf(sc[1], sc[3]);
 #pragma unroll
-    for (int mt = 0; mt < kD / 16; ++mt) {
-      uint32_t a[4];
-      ldmatrix_x4_trans(a, stage + v_lane_off + mt * 32);
-      mma_bf16_16816(acc[mt], a, pb0, pb1);
-      mma_bf16_16816(acc[mt], a, pc0, pc1);
+      for (int off = 4; off < 32; off <<= 1) {
+        mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, off));
+        mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, off));
+      }
+      const float mn0 = fmaxf(m0, mx0), mn1 = fmaxf(m1, mx1);
+      const float ms0 = fmaxf(mn0, kNegBig), ms1 = fmaxf(mn1, kNegBig);
+      const float al0 = fast_exp2(m0 - ms0), al1 = fast_exp2(m1 - ms1);
+      m0 = mn0; m1 = mn1;
+      float p[4];
+      p[0] = fast_exp2(sc[0] - ms0);
+      p[1] = fast_exp2(sc[1] - ms1);
+      p[2] = fast_exp2(sc[2] - ms0);
+      p[3] = fast_exp2(sc[3] - ms1);
+      l0 = l0 * al0 + p[0] + p[2];
+      l1 = l1 * al1 + p[1] + p[3];
+#pragma unroll
+      for (int mt = 0; mt < kD / 16; ++mt) {
+        acc[mt][0] *= al0; acc[mt][1] *= al1; acc[mt][2] *= al0; acc[mt][3] *= al1;
+      }
+      // P^T as the B operand of O^T = V^T . P^T; p = head + remainder, both bf16
+      float ph[4], pl[4];
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        ph[e] = __bfloat162float(__float2bfloat16_rn(p[e]));
+        pl[e] = p[e] - ph[e];
+      }
+      const uint32_t pb0 = movmatrix_trans(pack_bf16x2(ph[0], ph[1]));
+      const uint32_t pb1 = movmatrix_trans(pack_bf16x2(ph[2], ph[3]));
+      const uint32_t pc0 = movmatrix_trans(pack_bf16x2(pl[0], pl[1]));
+      const uint32_t pc1 = movmatrix_trans(pack_bf16x2(pl[2], pl[3]));
+#pragma unroll
+      for (int mt = 0; mt < kD / 16; ++mt) {
+        uint32_t a[4];
+        ldmatrix_x4_trans(a, stage + v_lane_off + mt * 32);
+        mma_bf16_16816(acc[mt], a, pb0, pb1);
+        mma_bf16_16816(acc[mt], a, pc0, pc1);
+      }
+      if (ragged) fence_proxy_async_smem();   // my zero fill precedes the next bulk copy into these rows
     }
     __syncwarp();
     if (lane == 0) mbar_arrive(bar_empty + 8 * s);
-  }
+    if (!(si.flags & kFlagLast)) continue;
 
-  // l: sum over the 8 token lanes that share this thread's heads
+    // ================= end of an item: write its partial or the output =================
+    float ls0 = l0, ls1 = l1;   // l: sum over the 8 token lanes that share this thread's heads
 #pragma unroll
-  for (int off = 4; off < 32; off <<= 1) {
-    l0 += __shfl_xor_sync(0xffffffffu, l0, off);
-    l1 += __shfl_xor_sync(0xffffffffu, l1, off);
-  }
-
-  // A wait that ran out may have left copies in flight: give them time to land before the
-  // ring is reused or the CTA retires (bounded; the result is already flagged invalid).
-  if (*abort_flag) {
-    for (int i = 0; i < 1000; ++i) __nanosleep(1000);
-  }
-  // ---- merge the warps of a kv head through shared memory (the ring is idle now) ----
-  asm volatile("bar.sync 1, %0;" ::"n"(kConsumerWarps * 32) : "memory");
-  {
-    float* wo = reinterpret_cast<float*>(smem + warp * (8 * kHeadStride * 4 + 64));
-    float* wml = wo + 8 * kHeadStride;
+    for (int off = 4; off < 32; off <<= 1) {
+      ls0 += __shfl_xor_sync(0xffffffffu, ls0, off);
+      ls1 += __shfl_xor_sync(0xffffffffu, ls1, off);
+    }
+    const bool direct = si.n_pieces == 1;
+    const int64_t pbase = ((int64_t)si.b * P.max_pieces + si.piece) * P.H;
+    if constexpr (C::kSub == 1) {
+      // one warp owns a kv head outright: straight from the accumulator fragments
 #pragma unroll
-    for (int mt = 0; mt < kD / 16; ++mt) {
-      const int d = mt * 16 + gq;
-      wo[(2 * tq) * kHeadStride + d] = acc[mt][0];
-      wo[(2 * tq + 1) * kHeadStride + d] = acc[mt][1];
-      wo[(2 * tq) * kHeadStride + d + 8] = acc[mt][2];
-      wo[(2 * tq + 1) * kHeadStride + d + 8] = acc[mt][3];
-    }
-    if (gq == 0) {
-      wml[2 * tq] = m0; wml[2 * tq + 1] = m1;
-      wml[8 + 2 * tq] = l0; wml[8 + 2 * tq + 1] = l1;
-    }
-  }
-  asm volatile("bar.sync 1, %0;" ::"n"(kConsumerWarps * 32) : "memory");
-
-  const int d = threadIdx.x & (kD - 1);
-  const bool direct = plan.n_pieces == 1;
-  for (int h = threadIdx.x >> 7; h < H; h += (kConsumerWarps * 32) / kD) {
-    const int kvhd = h / G, nq = h - kvhd * G;
-    float M = -INFINITY;
+      for (int e = 0; e < 2; ++e) {
+        const int nq = 2 * tq + e;
+        if (nq < G) {
+          const int h = hk * G + nq;
+          const float M = e ? m1 : m0, Ls = e ? ls1 : ls0;
+          if (direct) {
+            const float inv = Ls > 0.f ? 1.f / Ls : 0.f;
+            TO* op = out + (int64_t)si.b * P.out_seq_stride + (int64_t)h * kD;
 #pragma unroll
-    for (int ph = 0; ph < C::kWarpsPerHead; ++ph) {
-      const float* wml = reinterpret_cast<const float*>(smem + (kvhd + KVH * ph) * (8 * kHeadStride * 4 + 64)) + 8 * kHeadStride;
-      M = fmaxf(M, wml[nq]);
-    }
-    const float Ms = fmaxf(M, kNegBig);
-    float Lsum = 0.f, O = 0.f;
+            for (int mt = 0; mt < kD / 16; ++mt) {
+              store_out<TO>(op + mt * 16 + gq, acc[mt][e] * inv);
+              store_out<TO>(op + mt * 16 + gq + 8, acc[mt][2 + e] * inv);
+            }
+            if (P.lse_out && gq == 0)
+              P.lse_out[(int64_t)si.b * P.H + h] = Ls > 0.f ? (M + log2f(Ls)) * kLn2 : -INFINITY;
+          } else {
+            float* wp = P.ws_o + (pbase + h) * kD;
 #pragma unroll
-    for (int ph = 0; ph < C::kWarpsPerHead; ++ph) {
-      const float* wo = reinterpret_cast<const float*>(smem + (kvhd + KVH * ph) * (8 * kHeadStride * 4 + 64));
-      const float* wml = wo + 8 * kHeadStride;
-      const float w = fast_exp2(wml[nq] - Ms);
-      Lsum += wml[8 + nq] * w;
-      O += wo[nq * kHeadStride + d] * w;
-    }
-    if (direct) {
-      const float inv = Lsum > 0.f ? 1.f / Lsum : 0.f;
-      store_out<TO>(out + (int64_t)b * out_seq_stride + (int64_t)h * kD + d, O * inv);
-      if (lse_out && d == 0)
-        lse_out[(int64_t)b * H + h] = Lsum > 0.f ? (M + log2f(Lsum)) * kLn2 : -INFINITY;
+            for (int mt = 0; mt < kD / 16; ++mt) {
+              wp[mt * 16 + gq] = acc[mt][e];
+              wp[mt * 16 + gq + 8] = acc[mt][2 + e];
+            }
+            if (gq == 0) { P.ws_ml[(pbase + h) * 2] = M; P.ws_ml[(pbase + h) * 2 + 1] = Ls; }
+          }
+        }
+      }
     } else {
-      const int64_t pi = ((int64_t)b * max_pieces + piece) * H + h;
-      ws_o[pi * kD + d] = O;
-      if (d == 0) { ws_ml[pi * 2] = M; ws_ml[pi * 2 + 1] = Lsum; }
+      // several warps share a kv head (each took other tokens): merge through shared memory
+      uint8_t* mbuf = smem + C::kRingBytes;
+      float* wo = reinterpret_cast<float*>(mbuf + warp * kMergeWarpBytes);
+      float* wml = wo + 8 * kHeadStride;
+#pragma unroll
+      for (int mt = 0; mt < kD / 16; ++mt) {
+        const int d = mt * 16 + gq;
+        wo[(2 * tq) * kHeadStride + d] = acc[mt][0];
+        wo[(2 * tq + 1) * kHeadStride + d] = acc[mt][1];
+        wo[(2 * tq) * kHeadStride + d + 8] = acc[mt][2];
+        wo[(2 * tq + 1) * kHeadStride + d + 8] = acc[mt][3];
+      }
+      if (gq == 0) {
+        wml[2 * tq] = m0; wml[2 * tq + 1] = m1;
+        wml[8 + 2 * tq] = ls0; wml[8 + 2 * tq + 1] = ls1;
+      }
+      consumer_bar();
+      const int d = threadIdx.x;   // 128 consumer threads <-> 128 dims
+      for (int h = 0; h < P.H; ++h) {
+        const int kvhd = h / G, nq = h - kvhd * G;
+        float M = -INFINITY;
+#pragma unroll
+        for (int sw = 0; sw < C::kSub; ++sw)
+          M = fmaxf(M, reinterpret_cast<const float*>(mbuf + (kvhd + KVH * sw) * kMergeWarpBytes)[8 * kHeadStride + nq]);
+        const float Ms = fmaxf(M, kNegBig);
+        float Ls = 0.f, O = 0.f;
+#pragma unroll
+        for (int sw = 0; sw < C::kSub; ++sw) {
+          const float* po = reinterpret_cast<const float*>(mbuf + (kvhd + KVH * sw) * kMergeWarpBytes);
+          const float wgt = fast_exp2(po[8 * kHeadStride + nq] - Ms);
+          Ls += po[8 * kHeadStride + 8 + nq] * wgt;
+          O += po[nq * kHeadStride + d] * wgt;
+        }
+        if (direct) {
+          const float inv = Ls > 0.f ? 1.f / Ls : 0.f;
+          store_out<TO>(out + (int64_t)si.b * P.out_seq_stride + (int64_t)h * kD + d, O * inv);
+          if (P.lse_out && d == 0)
+            P.lse_out[(int64_t)si.b * P.H + h] = Ls > 0.f ? (M + log2f(Ls)) * kLn2 : -INFINITY;
+        } else {
+          P.ws_o[(pbase + h) * kD + d] = O;
+          if (d == 0) { P.ws_ml[(pbase + h) * 2] = M; P.ws_ml[(pbase + h) * 2 + 1] = Ls; }
+        }
+      }
+      if (direct) consumer_bar();   // the merge buffer is free again only after every reader is done
+    }
+    if (direct) continue;
+
+    // ---- split sequence: whoever completes the last piece folds all of them ----
+    __threadfence();
+    consumer_bar();
+    if (threadIdx.x == 0) {
+      const int prev = atomicAdd(&P.done[si.b], 1);
+      const int last = prev == si.n_pieces - 1;
+      if (last) P.done[si.b] = 0;   // ready for the next launch
+      misc[1] = last;
+    }
+    consumer_bar();
+    const int fold = misc[1];
+    consumer_bar();   // misc[1] may be rewritten by the next item only after everyone has read it
+    if (!fold) continue;
+    __threadfence();
+    {
+      // 128 threads, a float4 of dims each, heads strided by 4
+      const int d4 = threadIdx.x & 31;
+      for (int h = threadIdx.x >> 5; h < P.H; h += kConsumerWarps) {
+        const int64_t hb = (int64_t)si.b * P.max_pieces * P.H + h;
+        float M = -INFINITY;
+        for (int pc = 0; pc < si.n_pieces; ++pc) M = fmaxf(M, __ldcg(P.ws_ml + (hb + (int64_t)pc * P.H) * 2));
+        const float Ms = fmaxf(M, kNegBig);
+        float Ls = 0.f;
+        float4 O = make_float4(0.f, 0.f, 0.f, 0.f);
+        for (int pc = 0; pc < si.n_pieces; ++pc) {
+          const int64_t pi = hb + (int64_t)pc * P.H;
+          const float wgt = fast_exp2(__ldcg(P.ws_ml + pi * 2) - Ms);
+          Ls += __ldcg(P.ws_ml + pi * 2 + 1) * wgt;
+          const float4 o = __ldcg(reinterpret_cast<const float4*>(P.ws_o + pi * kD) + d4);
+          O.x += o.x * wgt; O.y += o.y * wgt; O.z += o.z * wgt; O.w += o.w * wgt;
+        }
+        const float inv = Ls > 0.f ? 1.f / Ls : 0.f;
+        TO* op = out + (int64_t)si.b * P.out_seq_stride + (int64_t)h * kD + d4 * 4;
+        store_out<TO>(op, O.x * inv); store_out<TO>(op + 1, O.y * inv);
+        store_out<TO>(op + 2, O.z * inv); store_out<TO>(op + 3, O.w * inv);
+        if (P.lse_out && d4 == 0)
+          P.lse_out[(int64_t)si.b * P.H + h] = Ls > 0.f ? (M + log2f(Ls)) * kLn2 : -INFINITY;
+      }
     }
   }
-}
-
-// Folds the partials of sequences that were split; one CTA per sequence.
-template <typename TO>
-__global__ void __launch_bounds__(256)
-swa_reduce_kernel(const int32_t* __restrict__ seq_lens, int H, int window_left, int split_chunks,
-                  int max_pieces, const float* __restrict__ ws_o, const float* __restrict__ ws_ml,
-                  TO* __restrict__ out, int64_t out_seq_stride, float* __restrict__ lse_out) {
-  const int b = blockIdx.x;
-  const Plan plan = make_plan(seq_lens[b], window_left, split_chunks, max_pieces);
-  if (plan.n_pieces <= 1) return;
-  const int d = threadIdx.x & (kD - 1);
-  for (int h = threadIdx.x >> 7; h < H; h += 256 / kD) {
-    float M = -INFINITY;
-    for (int p = 0; p < plan.n_pieces; ++p)
-      M = fmaxf(M, ws_ml[(((int64_t)b * max_pieces + p) * H + h) * 2]);
-    const float Ms = fmaxf(M, kNegBig);
-    float Lsum = 0.f, O = 0.f;
-    for (int p = 0; p < plan.n_pieces; ++p) {
-      const int64_t pi = ((int64_t)b * max_pieces + p) * H + h;
-      const float w = fast_exp2(ws_ml[pi * 2] - Ms);
-      Lsum += ws_ml[pi * 2 + 1] * w;
-      O += ws_o[pi * kD + d] * w;
-    }
-    const float inv = Lsum > 0.f ? 1.f / Lsum : 0.f;
-    store_out<TO>(out + (int64_t)b * out_seq_stride + (int64_t)h * kD + d, O * inv);
-    if (lse_out && d == 0)
-      lse_out[(int64_t)b * H + h] = Lsum > 0.f ? (M + log2f(Lsum)) * kLn2 : -INFINITY;
+  // A wait that ran out may have left copies in flight: give them time to land before the
+  // CTA retires (bounded; the result is already flagged invalid).
+  if (misc[0]) {
+    for (int i = 0; i < 1000; ++i) __nanosleep(1000);
   }
 }
 
 template <int KVH, typename TO>
-int launch_swa(const void* q, int64_t q_seq_stride, const void* k_cache, const void* v_cache,
-               const int32_t* block_tables, int max_blocks, const int32_t* seq_lens, int B, int H,
-               int64_t num_blocks, int block_size, int64_t block_stride, int window_left,
-               float scale, void* out, int64_t out_seq_stride, float* lse_out, float* ws_o,
-               float* ws_ml, int split_chunks, int max_pieces, int32_t* status, cudaStream_t st) {
+int launch_swa(const Params& P0, int B_total, int n_ctas, cudaStream_t st) {
   using C = Cfg<KVH>;
   auto kern = swa_decode_kernel<KVH, TO>;
   // The opt-in to large dynamic shared memory is per device; remember which devices have it.
@@ -411,24 +582,39 @@ int launch_swa(const void* q, int64_t q_seq_stride, const void* k_cache, const v
     }
     if (dev >= 0 && dev < 64) configured[dev] = true;
   }
-  dim3 grid(max_pieces, B);
-  kern<<<grid, kThreads, C::kSmemBytes, st>>>(
-      (const __nv_bfloat16*)q, q_seq_stride, (const uint8_t*)k_cache, (const uint8_t*)v_cache,
-      block_tables, max_blocks, seq_lens, H, num_blocks, block_size, block_stride, window_left,
-      scale * kLog2e, (TO*)out, out_seq_stride, lse_out, ws_o, ws_ml, split_chunks, max_pieces,
-      status);
-  int rc = check_launch("sbk_swa_decode");
-  if (rc != SBK_OK || max_pieces == 1) return rc;
-  swa_reduce_kernel<TO><<<B, 256, 0, st>>>(seq_lens, H, window_left, split_chunks, max_pieces, ws_o,
-                                           ws_ml, (TO*)out, out_seq_stride, lse_out);
-  return check_launch("sbk_swa_decode(reduce)");
+  // at most kMaxSeqs sequences per launch; consecutive launches reuse the ticket counters,
+  // which every launch leaves at zero
+  for (int b0 = 0; b0 < B_total; b0 += kMaxSeqs) {
+    Params P = P0;
+    P.B = B_total - b0 < kMaxSeqs ? B_total - b0 : kMaxSeqs;
+    P.q = P0.q + (int64_t)b0 * P0.q_seq_stride;
+    P.block_tables = P0.block_tables + (int64_t)b0 * P0.max_blocks;
+    P.seq_lens = P0.seq_lens + b0;
+    P.out = (uint8_t*)P0.out + (int64_t)b0 * P0.out_seq_stride * sizeof(TO);
+    if (P0.lse_out) P.lse_out = P0.lse_out + (int64_t)b0 * P0.H;
+    P.done = P0.done + b0;
+    if (P0.ws_o) {
+      P.ws_o = P0.ws_o + (int64_t)b0 * P0.max_pieces * P0.H * kD;
+      P.ws_ml = P0.ws_ml + (int64_t)b0 * P0.max_pieces * P0.H * 2;
+    }
+    int64_t items = (int64_t)P.B * P0.max_pieces;
+    const int grid = (int)(items < n_ctas ? items : n_ctas);
+    kern<<<grid, kThreads, C::kSmemBytes, st>>>(P);
+    int rc = check_launch("sbk_swa_decode");
+    if (rc != SBK_OK) return rc;
+  }
+  return SBK_OK;
 }
+
+static size_t ctrl_bytes(int B) { return 16 + (size_t)((B + 3) / 4 * 4) * 4; }
 
 }  // namespace sbk
 
 extern "C" size_t sbk_swa_workspace_bytes(int B, int H, int D, int max_pieces) {
-  if (B <= 0 || H <= 0 || D <= 0 || max_pieces <= 1) return 0;
-  return (size_t)B * max_pieces * H * ((size_t)D + 2) * sizeof(float);
+  if (B <= 0 || H <= 0 || D <= 0 || max_pieces < 1) return 0;
+  size_t n = sbk::ctrl_bytes(B);
+  if (max_pieces > 1) n += (size_t)B * max_pieces * H * ((size_t)D + 2) * sizeof(float);
+  return n;
 }
 
 extern "C" int sbk_swa_decode(const void* q, int64_t q_seq_stride, const void* k_cache,
@@ -457,8 +643,8 @@ extern "C" int sbk_swa_decode(const void* q, int64_t q_seq_stride, const void* k
     set_error("sbk_swa_decode: out_dtype=%d unsupported", out_dtype);
     return SBK_E_ARG;
   }
-  if (max_pieces < 1 || max_pieces > 65535 || B > 65535) {
-    set_error("sbk_swa_decode: max_pieces=%d / B=%d outside [1,65535]", max_pieces, B);
+  if (max_pieces < 1 || max_pieces > 65535) {
+    set_error("sbk_swa_decode: max_pieces=%d outside [1,65535]", max_pieces);
     return SBK_E_ARG;
   }
   if (B == 0) return SBK_OK;
@@ -477,34 +663,47 @@ extern "C" int sbk_swa_decode(const void* q, int64_t q_seq_stride, const void* k
     return SBK_E_ARG;
   }
   if (split_chunks <= 0) split_chunks = 32;
-  float* ws_o = nullptr;
-  float* ws_ml = nullptr;
-  if (max_pieces > 1) {
-    const size_t need = sbk_swa_workspace_bytes(B, H, D, max_pieces);
-    if (!workspace || workspace_bytes < need) {
-      set_error("sbk_swa_decode: workspace of %zu bytes given, %zu needed", workspace_bytes, need);
-      return SBK_E_WORKSPACE;
-    }
-    if (!aligned16(workspace)) {
-      set_error("sbk_swa_decode: workspace must be 16-byte aligned");
-      return SBK_E_ALIGN;
-    }
-    ws_o = (float*)workspace;
-    ws_ml = ws_o + (size_t)B * max_pieces * H * D;
+  const size_t need = sbk_swa_workspace_bytes(B, H, D, max_pieces);
+  if (!workspace || workspace_bytes < need) {
+    set_error("sbk_swa_decode: workspace of %zu bytes given, %zu needed", workspace_bytes, need);
+    return SBK_E_WORKSPACE;
   }
+  if (!aligned16(workspace)) {
+    set_error("sbk_swa_decode: workspace must be 16-byte aligned");
+    return SBK_E_ALIGN;
+  }
+  Params P;
+  P.q = (const __nv_bfloat16*)q; P.q_seq_stride = q_seq_stride;
+  P.k_cache = (const uint8_t*)k_cache; P.v_cache = (const uint8_t*)v_cache;
+  P.block_tables = block_tables; P.max_blocks = max_blocks; P.seq_lens = seq_lens;
+  P.B = B; P.H = H; P.num_blocks = num_blocks; P.block_size = block_size;
+  P.block_stride = cache_block_stride_bytes; P.window_left = window_left;
+  P.scale_log2 = scale * kLog2e; P.out = out; P.out_seq_stride = out_seq_stride; P.lse_out = lse_out;
+  P.ctrl = (int32_t*)workspace; P.done = P.ctrl + 4;
+  P.ws_o = nullptr; P.ws_ml = nullptr;
+  if (max_pieces > 1) {
+    P.ws_o = (float*)((uint8_t*)workspace + ctrl_bytes(B));
+    P.ws_ml = P.ws_o + (size_t)B * max_pieces * H * D;
+  }
+  P.split_chunks = split_chunks; P.max_pieces = max_pieces; P.status = status;
+
+  static int sm_count[64] = {};
+  int dev = 0;
+  cudaGetDevice(&dev);
+  int sms = (dev >= 0 && dev < 64) ? sm_count[dev] : 0;
+  if (sms == 0) {
+    cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+    if (sms <= 0) sms = 148;
+    if (dev >= 0 && dev < 64) sm_count[dev] = sms;
+  }
+  const int n_ctas = 2 * sms;
   cudaStream_t st = (cudaStream_t)stream;
-#define SBK_SWA_CALL(KVH, TO)                                                                     \
-  return launch_swa<KVH, TO>(q, q_seq_stride, k_cache, v_cache, block_tables, max_blocks, seq_lens, \
-                             B, H, num_blocks, block_size, cache_block_stride_bytes, window_left,  \
-                             scale, out, out_seq_stride, lse_out, ws_o, ws_ml, split_chunks,       \
-                             max_pieces, status, st)
-#define SBK_SWA_KVH(TO)                 \
-  switch (kvh) {                        \
-    case 1: SBK_SWA_CALL(1, TO);        \
-    case 2: SBK_SWA_CALL(2, TO);        \
-    default: SBK_SWA_CALL(4, TO);       \
+#define SBK_SWA_KVH(TO)                                              \
+  switch (kvh) {                                                     \
+    case 1: return launch_swa<1, TO>(P, B, n_ctas, st);              \
+    case 2: return launch_swa<2, TO>(P, B, n_ctas, st);              \
+    default: return launch_swa<4, TO>(P, B, n_ctas, st);             \
   }
   if (out_dtype == SBK_BF16) { SBK_SWA_KVH(__nv_bfloat16) } else { SBK_SWA_KVH(float) }
 #undef SBK_SWA_KVH
-#undef SBK_SWA_CALL
 }

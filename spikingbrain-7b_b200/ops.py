@@ -65,8 +65,11 @@ def kv_append(key: torch.Tensor, value: torch.Tensor, k_cache: torch.Tensor, v_c
         raise ValueError(f"key/value must be [T, {kvh}, {d}], got {tuple(key.shape)} / {tuple(value.shape)}")
     if key.dtype != k_cache.dtype or value.dtype != k_cache.dtype:
         raise ValueError("key/value dtype differs from the cache dtype")
-    if T and (key.stride()[1:] != (d, 1) or value.stride() != key.stride()):
-        raise ValueError("key/value rows must be contiguous and share one token stride")
+    for t in (key, value):  # strides of size-1 dimensions carry no meaning
+        if T and ((d > 1 and t.stride(2) != 1) or (kvh > 1 and t.stride(1) != d)):
+            raise ValueError("key/value rows must be contiguous")
+    if T > 1 and value.stride(0) != key.stride(0):
+        raise ValueError("key and value must share one token stride")
     if slot_mapping.dtype != torch.int64 or slot_mapping.numel() != T or not slot_mapping.is_contiguous():
         raise ValueError("slot_mapping must be a contiguous int64 tensor with one entry per token")
     B = max_blocks = max_ret = 0
@@ -124,8 +127,11 @@ def swa_max_pieces(max_visible_tokens: int, split_chunks: int = DEFAULT_SPLIT_CH
 
 
 def swa_workspace(B: int, H: int, D: int, max_pieces: int, device) -> Optional[torch.Tensor]:
+    """Scratch for swa_decode with exactly these B and max_pieces. It starts with the ticket
+    and per-sequence completion counters, which must be zero before the first call and which
+    every call leaves at zero; hence zero-filled, and not to be shared between batch sizes."""
     n = _abi.lib.sbk_swa_workspace_bytes(B, H, D, max_pieces)
-    return torch.empty(n, dtype=torch.uint8, device=device) if n else None
+    return torch.zeros(n, dtype=torch.uint8, device=device) if n else None
 
 
 def swa_decode(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor,
@@ -161,7 +167,7 @@ def swa_decode(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor,
     if max_pieces is None:
         vis = max_blocks * bs if window_left < 0 else min(max_blocks * bs, window_left + 1)
         max_pieces = swa_max_pieces(vis, split_chunks)
-    if max_pieces > 1 and workspace is None:
+    if workspace is None:
         workspace = swa_workspace(B, H, d, max_pieces, q.device)
     if scale is None:
         scale = d ** -0.5
@@ -181,7 +187,7 @@ def swa_decode(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor,
         ev1.record()
         timing.append((ev0, ev1))
     global LAUNCHES
-    LAUNCHES += (2 if max_pieces > 1 else 1) if B else 0
+    LAUNCHES += -(-B // 2048)
     return out
 
 

@@ -1,0 +1,291 @@
+"""GPU: the reference-facing surfaces (HF Cache, attention backend, GLA slot op) against the
+golden fixtures recorded from the reference's own code and against the oracle."""
+import hashlib
+import math
+import os
+
+import numpy as np
+import pytest
+import torch
+
+from oracle import ref_ops
+from tests.helpers import mean_rel, rel_err
+from tests.test_oracle_golden import CACHE_CASES, GOLD, golden_state, stream_kv
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda:0"
+
+
+def digest(t):
+    return hashlib.sha256(t.contiguous().cpu().numpy().tobytes()).hexdigest()
+
+
+@pytest.fixture(scope="module")
+def pkg(sb):
+    assert torch.cuda.is_available()
+    return sb
+
+
+# ---------------------------------------------------------------------------- HF Cache
+@pytest.mark.parametrize("name", CACHE_CASES)
+def test_hf_cache_stream_bit_exact_vs_reference(pkg, name):
+    """The same K/V streams the reference class was run on: what update() returns (gathered
+    through the block table from the paged pool) has the reference's bytes at every step."""
+    from spikingbrain_7b_b200.hf_cache import Cache
+    gold = np.load(os.path.join(GOLD, "cache_streams.npz"))
+    meta = gold[name + "/meta"].tolist()
+    B, kvh, D, W, prefill = meta[:5]
+    cache = Cache()
+    t = 0
+    for step, n in enumerate([prefill] + meta[5:]):
+        rs = torch.full((B, 2, 4, 4), float(step), device=DEV)
+        cache.update(recurrent_state=rs, layer_idx=0, offset=n)
+        assert cache[0]["recurrent_state"] is rs
+        k, v = stream_kv(B, kvh, n, D, t, salt=len(name))
+        st = cache.update(attn_state=(k.to(DEV), v.to(DEV)), layer_idx=1, offset=n, cache_kwargs={"window_size": W})
+        kc, vc = st["attn_state"]
+        assert digest(kc) + digest(vc) == str(gold[name + "/digests"][step]), f"step {step}"
+        assert [cache.get_seq_length(0), cache.get_seq_length(1), kc.shape[-2]] == gold[name + "/seen"][step].tolist()
+        t += n
+    assert torch.equal(kc.cpu(), torch.from_numpy(gold[name + "/final_k"]))
+    assert cache[1].paged.status.item() == 0
+    legacy = cache.to_legacy_cache()
+    assert torch.equal(legacy[1]["attn_state"][1].cpu(), torch.from_numpy(gold[name + "/final_v"]))
+    # round trip through the legacy tuple, then keep appending
+    c2 = Cache.from_legacy_cache(legacy, seen_tokens=cache.get_seq_length())
+    ref = ref_ops.RefWindowCache()
+    ref.update(attn_state=(kc.cpu(), vc.cpu()), layer_idx=0, offset=0, cache_kwargs={"window_size": W})
+    k, v = stream_kv(B, kvh, 1, D, t, salt=3)
+    c2.update(recurrent_state=None, layer_idx=0, offset=1)
+    got = c2.update(attn_state=(k.to(DEV), v.to(DEV)), layer_idx=1, offset=1, cache_kwargs={"window_size": W})["attn_state"]
+    exp = ref.update(attn_state=(k, v), layer_idx=0, offset=1, cache_kwargs={"window_size": W})["attn_state"]
+    assert torch.equal(got[0].cpu(), exp[0]) and torch.equal(got[1].cpu(), exp[1])
+
+
+def test_hf_cache_long_decode_rebases_table_and_unbounded_layer_grows(pkg):
+    """Many more decode steps than the block table has columns (the live blocks are moved back),
+    and a layer without a window that outgrows its pool: contents stay those of the reference."""
+    from spikingbrain_7b_b200.hf_cache import Cache
+    B, kvh, D, W = 2, 2, 64, 32
+    cache, ref = Cache(unbounded_capacity=64), ref_ops.RefWindowCache()
+    t = 0
+    for step in range(400):
+        n = 40 if step == 0 else 1
+        k, v = stream_kv(B, kvh, n, D, t, salt=5)
+        for layer, win in ((0, W), (1, None)):
+            got = cache.update(attn_state=(k.to(DEV), v.to(DEV)), layer_idx=layer, offset=n,
+                               cache_kwargs={"window_size": win})
+            exp = ref.update(attn_state=(k, v), layer_idx=layer, offset=n, cache_kwargs={"window_size": win})
+            if step % 37 == 0 or step == 399:
+                g, e = got["attn_state"], exp["attn_state"]
+                assert torch.equal(g[0].cpu(), e[0]) and torch.equal(g[1].cpu(), e[1]), f"step {step} layer {layer}"
+        t += n
+    assert cache.get_seq_length() == ref.get_seq_length() == 439
+
+
+def test_hf_cache_edges_raise(pkg):
+    from spikingbrain_7b_b200.hf_cache import Cache
+    mk = lambda n: tuple(torch.zeros(1, 1, n, 64, device=DEV) for _ in range(2))
+    c = Cache()
+    c.update(attn_state=mk(60), layer_idx=0, offset=60, cache_kwargs={"window_size": 64})
+    with pytest.raises(NotImplementedError):      # the reference would stop trimming here and grow for ever
+        c.update(attn_state=mk(8), layer_idx=0, offset=8, cache_kwargs={"window_size": 64})
+    c = Cache()
+    c.update(attn_state=mk(64), layer_idx=0, offset=64, cache_kwargs={"window_size": 64})
+    with pytest.raises(RuntimeError):             # the reference fails with a shape mismatch
+        c.update(attn_state=mk(128), layer_idx=0, offset=128, cache_kwargs={"window_size": 64})
+
+
+def test_hf_cache_fast_paths_match_reference_attention_layer(pkg):
+    """cache.swa_decode on the paged window == the reference's SDPA attention layer run on the
+    same injected q/k/v (fixture swa_sdpa.npz), within the bf16 attention bar."""
+    from spikingbrain_7b_b200.hf_cache import Cache
+    gold = np.load(os.path.join(GOLD, "swa_sdpa.npz"))
+    for name in ("g7", "short"):
+        B, H, kvh, D, W, prefill, steps = gold[name + "/meta"].tolist()
+        x = torch.from_numpy(gold[name + "/x_bf16"]).view(torch.bfloat16).to(DEV)
+        q = x[..., :H * D].view(B, -1, H, D)
+        k = x[..., H * D:(H + kvh) * D].view(B, -1, kvh, D).transpose(1, 2)   # [B, kvh, T, D]
+        v = x[..., (H + kvh) * D:].view(B, -1, kvh, D).transpose(1, 2)
+        ref_out = torch.from_numpy(gold[name + "/decode_out"]).view(B, steps, H, D)
+        cache = Cache()
+        cache.update(attn_state=(k[:, :, :prefill], v[:, :, :prefill]), layer_idx=0, offset=prefill,
+                     cache_kwargs={"window_size": W})
+        for s in range(steps):
+            pos = prefill + s
+            cache.update(attn_state=(k[:, :, pos:pos + 1], v[:, :, pos:pos + 1]), layer_idx=0, offset=1,
+                         cache_kwargs={"window_size": W})
+            o = cache.swa_decode(q[:, pos].contiguous(), 0).float().cpu()
+            tgt = ref_out[:, s].bfloat16().float()
+            assert float((o - tgt).abs().max()) <= 2e-2 and mean_rel(o, tgt) <= 1e-3, f"{name} step {s}"
+
+
+def test_hf_cache_gla_step_carries_state_like_the_reference_kernel(pkg):
+    """cache.gla_step twice == the reference Triton kernel's two chained steps (fixture)."""
+    from spikingbrain_7b_b200.hf_cache import Cache
+    gold = np.load(os.path.join(GOLD, "gla_triton.npz"))
+    name = "f32_d64"
+    B, H, D, slots, _ = gold[name + "/meta"].tolist()
+    q, k, v, g = (torch.from_numpy(gold[f"{name}/{n}"]).to(DEV) for n in "qkvg")
+    slot = gold[name + "/slot"].tolist()
+    state = golden_state(slots, H, D)[slot].contiguous().to(DEV)       # the cache holds one state per sequence
+    cache = Cache()
+    cache.update(recurrent_state=state, layer_idx=0, offset=5)
+    o1 = cache.gla_step(q.unsqueeze(2), k.unsqueeze(2), v.unsqueeze(2), g.unsqueeze(2), 0)
+    o2 = cache.gla_step(q, k, v, g, 0)
+    assert cache.get_seq_length() == 7 and cache[0]["recurrent_state"] is state
+    assert rel_err(o1.cpu(), torch.from_numpy(gold[name + "/out1"])) <= 1e-4
+    assert rel_err(o2.cpu(), torch.from_numpy(gold[name + "/out2"])) <= 1e-4
+    assert rel_err(state.cpu(), torch.from_numpy(gold[name + "/state2"])[slot]) <= 1e-4
+
+
+# --------------------------------------------------------------------------- GLA slot op
+@pytest.mark.parametrize("name", ["f32_d128", "f32_d64", "f32_d128_g7"])
+def test_my_fused_recurrent_gla_matches_reference_kernel(pkg, name):
+    """The drop-in of my_fused_recurrent_gla on the reference kernel's own inputs and outputs."""
+    from spikingbrain_7b_b200.gla_slots import my_fused_recurrent_gla
+    gold = np.load(os.path.join(GOLD, "gla_triton.npz"))
+    B, H, D, slots, _ = gold[name + "/meta"].tolist()
+    q, k, v, g = (torch.from_numpy(gold[f"{name}/{n}"]).unsqueeze(2).to(DEV) for n in "qkvg")
+    slot = torch.from_numpy(gold[name + "/slot"]).to(DEV)
+    state0 = golden_state(slots, H, D)
+    state = state0.to(DEV)
+    o1 = my_fused_recurrent_gla(q, k, v, g, kv_caches=state, slot_idx=slot).cpu()
+    o2 = my_fused_recurrent_gla(q, k, v, g, kv_caches=state, slot_idx=slot).cpu()
+    live = (slot >= 0).cpu()
+    assert o1.shape == (B, H, D)
+    assert rel_err(o1[live], torch.from_numpy(gold[name + "/out1"])[live]) <= 1e-4
+    assert rel_err(o2[live], torch.from_numpy(gold[name + "/out2"])[live]) <= 1e-4
+    assert rel_err(state.cpu(), torch.from_numpy(gold[name + "/state2"])) <= 1e-4
+    untouched = [s for s in range(slots) if s not in slot.tolist()]
+    assert torch.equal(state[untouched].cpu(), state0[untouched])
+
+
+# ------------------------------------------------------------------------------- backend
+def _decode_meta(Meta, slots, lens, table):
+    return Meta(num_prefills=0, num_prefill_tokens=0, num_decode_tokens=len(lens), slot_mapping=slots,
+                seq_lens=None, seq_lens_tensor=lens, max_prefill_seq_len=0, max_decode_seq_len=int(lens.max()),
+                context_lens_tensor=None, block_tables=table, use_cuda_graph=False, max_query_len=1,
+                max_decode_query_len=1)
+
+
+def test_backend_forward_decode_steps_vs_oracle(pkg):
+    """Impl.forward over several decode steps with the V0-style window-truncated tables the
+    builder hands over: cache contents bit-exact, outputs within the attention bar."""
+    from spikingbrain_7b_b200.backend import MetaAttentionBackend, MetaAttentionImpl, MetaAttentionMetadata
+    H, kvh, D, bs, sw = 28, 4, 128, 16, 65            # sliding_window 65 -> window_left 64
+    lens = [10, 64, 65, 66, 200]
+    B, steps = len(lens), 20
+    nb = B * ((max(lens) + steps) // bs + 2)
+    g = torch.Generator().manual_seed(5)
+    kv = torch.zeros(MetaAttentionBackend.get_kv_cache_shape(nb, bs, kvh, D), dtype=torch.bfloat16)
+    tables = [torch.randperm(nb, generator=g)[b * (nb // B):(b + 1) * (nb // B)].tolist() for b in range(B)]
+    for b, L in enumerate(lens):
+        for t in range(L):
+            kv[:, tables[b][t // bs], t % bs] = (torch.randn(2, kvh, D, generator=g) / math.sqrt(D)).bfloat16()
+    kv_d = kv.to(DEV)
+    impl = MetaAttentionImpl(H, D, D ** -0.5, kvh, None, sw, "auto")
+    wl = impl.sliding_window[0]
+    for step in range(steps):
+        q = (torch.randn(B, H * D, generator=g) / math.sqrt(D)).bfloat16()
+        k = (torch.randn(B, kvh * D, generator=g) / math.sqrt(D)).bfloat16()
+        v = (torch.randn(B, kvh * D, generator=g) / math.sqrt(D)).bfloat16()
+        slots = torch.tensor([tables[b][L // bs] * bs + L % bs for b, L in enumerate(lens)])
+        lens = [L + 1 for L in lens]
+        ref_ops.paged_append(k.view(B, kvh, D), v.view(B, kvh, D), kv[0], kv[1], slots)
+        # what the V0 model runner passes under a sliding window: trailing blocks, clipped length
+        sw_blocks = (sw + bs - 1) // bs
+        trunc_tables, trunc_lens = [], []
+        for b, L in enumerate(lens):
+            n_blocks = (L + bs - 1) // bs
+            suff = L % bs
+            cur = sw_blocks + (1 if suff else 0)
+            trunc_lens.append(min(L, sw_blocks * bs + suff) if suff else min(L, sw_blocks * bs))
+            trunc_tables.append(tables[b][:n_blocks][-cur:])
+        width = max(len(t) for t in trunc_tables)
+        tt = torch.tensor([t + [0] * (width - len(t)) for t in trunc_tables], dtype=torch.int32)
+        full_t = torch.tensor([t[:(max(lens) + bs - 1) // bs] for t in tables], dtype=torch.int32)
+        ref = ref_ops.swa_paged_decode_ref(q.view(B, H, D), kv[0], kv[1], full_t, lens, wl, D ** -0.5)
+        md = _decode_meta(MetaAttentionMetadata, slots.to(DEV), torch.tensor(trunc_lens, dtype=torch.int32, device=DEV),
+                          tt.to(DEV))
+        out = torch.empty(B, H * D, dtype=torch.bfloat16, device=DEV)
+        ret = impl.forward(None, q.to(DEV), k.to(DEV), v.to(DEV), None, None, None, kv_d, md, output=out)
+        assert ret is out
+        o = out.view(B, H, D).float().cpu()
+        tgt = ref.bfloat16().float()
+        assert float((o - tgt).abs().max()) <= 2e-2 and mean_rel(o, tgt) <= 1e-3, f"step {step}"
+    assert torch.equal(kv_d.cpu(), kv) and impl.status() == 0
+
+
+def test_backend_forward_chunked_prefill_plus_decode(pkg):
+    """A mixed batch: two prompt chunks (one continuing a cached context) followed by two decodes.
+    Every prompt token attends causally inside the window through its sequence's block table."""
+    from spikingbrain_7b_b200.backend import MetaAttentionImpl, MetaAttentionMetadata
+    H, kvh, D, bs, sw = 14, 2, 128, 16, 33
+    g = torch.Generator().manual_seed(6)
+    ctx = [0, 40, 90, 7]            # cached tokens before this step
+    new = [50, 30, 1, 1]            # tokens of this step (2 prefill chunks, 2 decodes)
+    B = 4
+    nb = 40
+    perm = torch.randperm(nb, generator=g).tolist()
+    tables = [perm[b * 10:(b + 1) * 10] for b in range(B)]
+    kv = torch.zeros(2, nb, bs, kvh, D, dtype=torch.bfloat16)
+    for b in range(B):
+        for t in range(ctx[b]):
+            kv[:, tables[b][t // bs], t % bs] = (torch.randn(2, kvh, D, generator=g) / math.sqrt(D)).bfloat16()
+    T = sum(new)
+    q = (torch.randn(T, H, D, generator=g) / math.sqrt(D)).bfloat16()
+    k = (torch.randn(T, kvh, D, generator=g) / math.sqrt(D)).bfloat16()
+    v = (torch.randn(T, kvh, D, generator=g) / math.sqrt(D)).bfloat16()
+    slots, owner = [], []
+    for b in range(B):
+        for p in range(ctx[b], ctx[b] + new[b]):
+            slots.append(tables[b][p // bs] * bs + p % bs)
+            owner.append((b, p))
+    slots = torch.tensor(slots)
+    kv_d = kv.to(DEV)
+    ref_ops.paged_append(k, v, kv[0], kv[1], slots)
+    impl = MetaAttentionImpl(H, D, D ** -0.5, kvh, None, sw, "auto")
+    wl = impl.sliding_window[0]
+    tab = torch.tensor(tables, dtype=torch.int32)
+    ref = torch.stack([ref_ops.swa_paged_decode_ref(q[i:i + 1], kv[0], kv[1], tab[b:b + 1], [p + 1], wl, D ** -0.5)[0]
+                       for i, (b, p) in enumerate(owner)])
+    seq_lens = [c + n for c, n in zip(ctx, new)]
+    qsl = [0, 50, 80, 81, 82]
+    md = MetaAttentionMetadata(
+        num_prefills=2, num_prefill_tokens=80, num_decode_tokens=2, slot_mapping=slots.to(DEV), seq_lens=seq_lens,
+        seq_lens_tensor=torch.tensor(seq_lens, dtype=torch.int32, device=DEV), max_prefill_seq_len=70,
+        max_decode_seq_len=91, context_lens_tensor=torch.tensor(ctx, dtype=torch.int32, device=DEV),
+        block_tables=tab.to(DEV), use_cuda_graph=False, max_query_len=50, max_decode_query_len=1,
+        query_start_loc=torch.tensor(qsl, dtype=torch.int32, device=DEV),
+        seq_start_loc=torch.tensor([0, 50, 120, 211, 219], dtype=torch.int32, device=DEV))
+    out = torch.empty(T, H, D, dtype=torch.bfloat16, device=DEV)
+    impl.forward(None, q.to(DEV), k.to(DEV), v.to(DEV), None, None, None, kv_d, md, output=out)
+    assert torch.equal(kv_d.cpu(), kv) and impl.status() == 0
+    o, tgt = out.float().cpu(), ref.bfloat16().float()
+    assert float((o - tgt).abs().max()) <= 2e-2 and mean_rel(o, tgt) <= 1e-3
+
+
+def test_backend_forward_unsupported_paths_raise(pkg):
+    from spikingbrain_7b_b200.backend import MetaAttentionImpl, MetaAttentionMetadata
+    impl = MetaAttentionImpl(28, 128, 1.0, 4, None, 65, "auto")
+    q = torch.zeros(2, 28, 128, dtype=torch.bfloat16, device=DEV)
+    kx = torch.zeros(2, 4, 128, dtype=torch.bfloat16, device=DEV)
+    kv = torch.zeros(2, 4, 16, 4, 128, dtype=torch.bfloat16, device=DEV)
+    md = _decode_meta(MetaAttentionMetadata, torch.tensor([0, 16], device=DEV),
+                      torch.tensor([1, 1], dtype=torch.int32, device=DEV),
+                      torch.tensor([[0], [1]], dtype=torch.int32, device=DEV))
+    with pytest.raises(AssertionError):
+        impl.forward(None, q, kx, kx, None, None, None, kv, md, output=None)
+    with pytest.raises(NotImplementedError):       # sink tokens are a later row of the scope table
+        impl.forward(None, q, kx, kx, None, kx, kx, kv, md, output=torch.empty_like(q))
+    pm = MetaAttentionMetadata(num_prefills=1, num_prefill_tokens=2, num_decode_tokens=0,
+                               slot_mapping=torch.tensor([-1, -1], device=DEV), seq_lens=[2],
+                               seq_lens_tensor=torch.tensor([2], dtype=torch.int32, device=DEV),
+                               max_prefill_seq_len=2, max_decode_seq_len=0,
+                               context_lens_tensor=torch.tensor([0], dtype=torch.int32, device=DEV),
+                               block_tables=torch.zeros(1, 0, dtype=torch.int32, device=DEV), use_cuda_graph=False,
+                               max_query_len=2, query_start_loc=torch.tensor([0, 2], dtype=torch.int32, device=DEV),
+                               seq_start_loc=torch.tensor([0, 2], dtype=torch.int32, device=DEV))
+    with pytest.raises(NotImplementedError):       # a prompt whose K/V cannot be reached through tables
+        impl.forward(None, q, kx, kx, None, None, None, kv, pm, output=torch.empty_like(q))
