@@ -108,8 +108,9 @@ class _PagedWindow:
         slots = torch.from_numpy(plan.slot_mapping).to(self.device, non_blocking=True)
         self.lens_d.copy_(torch.from_numpy(plan.seq_lens), non_blocking=True)
         qsl = torch.from_numpy(plan.query_start_loc).to(self.device, non_blocking=True)
-        kt = k.transpose(1, 2).reshape(self.B * n, self.kvh, self.D)
-        vt = v.transpose(1, 2).reshape(self.B * n, self.kvh, self.D)
+        # token-major rows [T, kvh, D]; a view for one new token, a copy for a prompt chunk
+        kt = k.transpose(1, 2).reshape(self.B * n, self.kvh, self.D).contiguous()
+        vt = v.transpose(1, 2).reshape(self.B * n, self.kvh, self.D).contiguous()
         ops.kv_append(kt, vt, self.kv[0], self.kv[1], slots, block_tables=self.table_d,
                       seq_lens=self.lens_d, query_start_loc=qsl, window_left=self.mgr.window_left,
                       status=self.status)
