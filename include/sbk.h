@@ -121,6 +121,10 @@ int sbk_kv_gather(const void* k_cache, const void* v_cache, const int32_t* block
  * Supported: D == 128, H % kvh == 0, H/kvh <= 8, kvh in {1,2,4}, block_size % 16 == 0.
  */
 size_t sbk_swa_workspace_bytes(int B, int H, int D, int max_pieces);
+/* How sbk_swa_decode moves a 16-token tile into shared memory on this driver: 1 = one tensor
+ * copy per tile (kvh*4 KiB), 0 = one per 128-byte row (2 KiB), -1 = no call made yet.
+ * Diagnostic only; no counterpart in the reference. */
+int sbk_swa_copy_mode(void);
 int sbk_swa_decode(const void* q, int64_t q_seq_stride, const void* k_cache, const void* v_cache,
                    const int32_t* block_tables, int max_blocks, const int32_t* seq_lens,
                    int B, int H, int kvh, int D, int64_t num_blocks, int block_size,

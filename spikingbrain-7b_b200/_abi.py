@@ -28,6 +28,7 @@ SIGNATURES = {
         c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int, c_int64, c_int,
         c_int64, c_int, c_void_p, c_void_p, c_int, c_void_p, c_void_p]),
     "sbk_swa_workspace_bytes": (c_size_t, [c_int, c_int, c_int, c_int]),
+    "sbk_swa_copy_mode": (c_int, []),
     "sbk_swa_decode": (c_int, [
         c_void_p, c_int64, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_int,
         c_int, c_int64, c_int, c_int64, c_int, c_float, c_void_p, c_int, c_int64, c_void_p,

@@ -506,7 +506,8 @@ class MetaAttentionImpl:
         bs = kv_cache.shape[2]
         width = block_tables.shape[1] * bs
         vis = width if window_left < 0 else min(width, window_left + 1)
-        max_pieces = ops.swa_max_pieces(vis)
+        split = ops.swa_auto_split(B, vis, q.device)
+        max_pieces = ops.swa_max_pieces(vis, split)
         D = self.head_size
         if q.stride()[1:] != (D, 1):
             q = q.contiguous()
@@ -514,6 +515,6 @@ class MetaAttentionImpl:
         ops.swa_decode(q, kv_cache[0], kv_cache[1], block_tables.contiguous(), seq_lens.contiguous(),
                        window_left=window_left, scale=self.scale, out=tmp,
                        workspace=self._scratch(B, max_pieces, q.device), max_pieces=max_pieces,
-                       status=self._status)
+                       split_chunks=split, status=self._status)
         if tmp is not out:
             out.copy_(tmp)

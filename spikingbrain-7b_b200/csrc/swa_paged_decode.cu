@@ -7,13 +7,16 @@
 //   global ticket counter until none is left, so ragged batches balance themselves and the
 //   copy pipeline never drains between items.
 // Data movement
-//   One producer warp per CTA walks the block table and issues one bulk async copy (TMA
-//   engine, untiled form) per token row -- all kv heads of a token are one contiguous
-//   kvh*256-byte row of K and one of V -- into a ring of 32 KiB shared-memory stages.
-//   Completion is counted in bytes on an mbarrier per stage. Rows are laid down with a
-//   16-byte skew so that ldmatrix reads of 8 tokens at one head/dim offset hit 8 different
-//   bank groups. A stage also carries a small descriptor (sequence, piece, token range,
-//   first/last flags), so the consumers learn about items from the stream itself.
+//   One producer warp per CTA walks the block table and issues TMA tensor copies
+//   (cp.async.bulk.tensor, no multicast) of 16-token tiles -- all kv heads of a token are one
+//   contiguous kvh*256-byte row of K and one of V -- into a ring of 32 KiB shared-memory
+//   stages; completion is counted in bytes on an mbarrier per stage. The tensor map views a
+//   cache as [block][128-byte row of a token][token in block][64 elements] and lands a tile as
+//   [128-byte row][token][128 B] with the 128-byte swizzle, so ldmatrix reads of 8 tokens at one
+//   head/dim offset hit 8 different bank groups. Where the driver accepts the permuted strides
+//   a whole tile is ONE copy of kvh*4 KiB; otherwise one copy per 128-byte row (2 KiB each).
+//   A stage also carries a small descriptor (sequence, piece, token range, first/last flags),
+//   so the consumers learn about items from the stream itself.
 // Math
 //   4 consumer warps. A stage holds 64/kvh tokens; warp w serves kv head w % kvh and the
 //   16-token sub-chunk w / kvh of every stage. Scores are formed TRANSPOSED,
@@ -28,6 +31,10 @@
 //   the CTA that completes the last piece of a sequence (a counter per sequence) folds them
 //   and writes the output, so there is no second kernel. A single piece writes `out` directly.
 // HBM-bound: min(seq_len, window_left+1) * kvh*128*2*2 bytes read per sequence.
+#include <cuda.h>
+
+#include <mutex>
+
 #include "sbk_common.cuh"
 
 namespace sbk {
@@ -75,10 +82,10 @@ template <int KVH>
 struct Cfg {
   static constexpr int kSub = kConsumerWarps / KVH;            // 16-token sub-chunks per stage
   static constexpr int kStageTokens = kSub * kChunk;
-  static constexpr int kRowBytes = KVH * kD * 2;
-  static constexpr int kRowStride = kRowBytes + 16;
-  static constexpr int kVOffset = kStageTokens * kRowStride;   // K rows, then V rows
-  static constexpr int kStageBytes = 2 * kVOffset;
+  static constexpr int kRows128 = 2 * KVH;                     // 128-byte rows per token (K or V)
+  static constexpr int kTileBytes = kChunk * kRows128 * 128;   // one sub-chunk of K or of V
+  static constexpr int kVOffset = kSub * kTileBytes;           // = 16 KiB: K tiles, then V tiles
+  static constexpr int kStageBytes = 2 * kVOffset;             // = 32 KiB
   static constexpr int kStages = KVH == 4 ? 3 : 2;
   static constexpr int kRingBytes = kStages * kStageBytes;
   static constexpr int kMergeBytes = kSub > 1 ? kConsumerWarps * kMergeWarpBytes : 0;
@@ -87,11 +94,21 @@ struct Cfg {
   static constexpr int kLensOff = kPreOff + (kMaxSeqs + 4) * 4;
   static constexpr int kBarOff = kLensOff + kMaxSeqs * 4;
   static constexpr int kMiscOff = kBarOff + 2 * kStages * 8;
-  static constexpr int kSmemBytes = kMiscOff + 32;
-  static constexpr int kRowsPerLane = 2 * kStageTokens / 32;
+  static constexpr int kSmemBytes = kMiscOff + 32 + 1024;      // + slack to align the ring to 1 KiB
   static_assert(kConsumerWarps % KVH == 0, "warps must split evenly over kv heads");
+  static_assert(kVOffset == 16384, "a stage holds 16 KiB of K and 16 KiB of V");
   static_assert(kSmemBytes <= 115200, "two CTAs must fit one SM");
 };
+
+// 4-D tensor copy global -> shared (TMA), completion in bytes on an mbarrier
+__device__ __forceinline__ void tma_load_4d(uint32_t dst, const CUtensorMap* map, int c0, int c1, int c2, int c3,
+                                            uint32_t bar) {
+  asm volatile(
+      "cp.async.bulk.tensor.4d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4, %5}], [%6];" ::
+          "r"(dst),
+      "l"(reinterpret_cast<uint64_t>(map)), "r"(c0), "r"(c1), "r"(c2), "r"(c3), "r"(bar)
+      : "memory");
+}
 
 template <typename TO>
 __device__ __forceinline__ void store_out(TO* p, float x);
@@ -116,12 +133,17 @@ struct Params {
   int32_t* ctrl;      // [0] next ticket, [1] CTAs that ran out of tickets
   int32_t* done;      // [B] pieces finished per sequence
   float* ws_o; float* ws_ml; int split_chunks; int max_pieces; int32_t* status;
+  int tile_copy;      // 1: one copy per tile (permuted-stride map), 0: one copy per 128-byte row
 };
 
 template <int KVH, typename TO>
-__global__ void __launch_bounds__(kThreads, 2) swa_decode_kernel(const Params P) {
+__global__ void __launch_bounds__(kThreads, 2)
+swa_decode_kernel(const Params P, const __grid_constant__ CUtensorMap map_k,
+                  const __grid_constant__ CUtensorMap map_v) {
   using C = Cfg<KVH>;
-  extern __shared__ __align__(128) uint8_t smem[];
+  extern __shared__ uint8_t smem_raw[];
+  // the swizzle pattern is a function of the shared-memory address: tiles sit on 1 KiB boundaries
+  uint8_t* const smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
   const uint32_t ring = smem_u32(smem);
   StageInfo* info = reinterpret_cast<StageInfo*>(smem + C::kInfoOff);
   int* pre = reinterpret_cast<int*>(smem + C::kPreOff);
@@ -224,25 +246,27 @@ __global__ void __launch_bounds__(kThreads, 2) swa_decode_kernel(const Params P)
         if (hi > L) hi = L;
         if (hi > item_end) hi = item_end;
         if (hi < lo) hi = lo;
-        const uint8_t* src[C::kRowsPerLane];
-        bool valid[C::kRowsPerLane];
-        bool bad = false;
-#pragma unroll
-        for (int i = 0; i < C::kRowsPerLane; ++i) {
-          const int r = lane + 32 * i;
-          const int ti = r % C::kStageTokens;
-          const int is_v = r / C::kStageTokens;
-          const int tok = tok_base + ti;
-          valid[i] = tok >= lo && tok < hi;
-          const int64_t pb = __shfl_sync(0xffffffffu, pb_lane, (c0 - batch_c0) + ti / kChunk);
-          src[i] = nullptr;
-          if (valid[i]) {
-            if (pb < 0 || pb >= P.num_blocks) bad = true;
-            else src[i] = (is_v ? P.v_cache : P.k_cache) + pb * P.block_stride +
-                          (int64_t)(tok % P.block_size) * C::kRowBytes;
-          }
-        }
+        // lane -> one copy of this stage: K or V, sub-chunk, and (row-wise mode) 128-byte row
+        const int n_copies = P.tile_copy ? 2 * C::kSub : 2 * C::kSub * C::kRows128;
+        const int is_v = lane & 1;
+        const int r2 = lane >> 1;
+        const int sc = P.tile_copy ? r2 : r2 / C::kRows128;
+        const int row = P.tile_copy ? 0 : r2 % C::kRows128;
+        const bool active = lane < n_copies;
+        const int my_c = c0 + (active ? sc : 0);
+        int src_lane = my_c - batch_c0;
+        src_lane = src_lane < 0 ? 0 : (src_lane > 31 ? 31 : src_lane);
+        const int64_t pb = __shfl_sync(0xffffffffu, pb_lane, src_lane);
+        const int tbl = my_c * kChunk;
+        const bool has_tok = (tbl > lo ? tbl : lo) < (tbl + kChunk < hi ? tbl + kChunk : hi);
+        bool bad = active && has_tok && (pb < 0 || pb >= P.num_blocks);
         bad = __any_sync(0xffffffffu, bad);
+        int n_sub = 0;   // sub-chunks of this stage that carry tokens
+#pragma unroll
+        for (int q2 = 0; q2 < C::kSub; ++q2) {
+          const int t2 = tok_base + q2 * kChunk;
+          n_sub += ((t2 > lo ? t2 : lo) < (t2 + kChunk < hi ? t2 + kChunk : hi)) ? 1 : 0;
+        }
         if (lane == 0) {
           StageInfo si;
           si.b = b; si.piece = piece; si.n_pieces = plan.n_pieces; si.tok_base = tok_base;
@@ -250,30 +274,14 @@ __global__ void __launch_bounds__(kThreads, 2) swa_decode_kernel(const Params P)
           si.flags = (j == 0 ? kFlagFirst : 0) | (j == nst - 1 ? kFlagLast : 0) | (bad ? kFlagBad : 0);
           info[s] = si;
           if (bad) raise_status(P.status, SBK_ST_BAD_BLOCK);
-#ifdef SBK_SWA_BIGCOPY   // experiment only (needs SBK_SWA_SKIP_MATH, kvh 4, block 16): two 16 KiB copies per stage
-          mbar_arrive_expect_tx(bar_full + 8 * s, bad ? 0u : 2u * 16384u);
-#else
-          mbar_arrive_expect_tx(bar_full + 8 * s, bad ? 0u : 2u * (uint32_t)(hi - lo) * C::kRowBytes);
-#endif
+          mbar_arrive_expect_tx(bar_full + 8 * s, bad ? 0u : (uint32_t)n_sub * 2u * C::kTileBytes);
         }
         __syncwarp();
-#ifdef SBK_SWA_BIGCOPY
-        const int64_t pb0 = __shfl_sync(0xffffffffu, pb_lane, c0 - batch_c0);
-        if (!bad && lane < 2) {
-          bulk_g2s(ring + s * C::kStageBytes + lane * C::kVOffset,
-                   (lane ? P.v_cache : P.k_cache) + pb0 * P.block_stride, 16384u, bar_full + 8 * s);
-        }
-        if (false) {
-#else
-        if (!bad) {
-#endif
-#pragma unroll
-          for (int i = 0; i < C::kRowsPerLane; ++i) {
-            if (valid[i]) {
-              const int r = lane + 32 * i;
-              bulk_g2s(ring + s * C::kStageBytes + r * C::kRowStride, src[i], C::kRowBytes, bar_full + 8 * s);
-            }
-          }
+        if (!bad && active && has_tok) {
+          const uint32_t dst = ring + s * C::kStageBytes + is_v * C::kVOffset + sc * C::kTileBytes + row * 2048;
+          const int tin = tbl % P.block_size;
+          if (P.tile_copy) tma_load_4d(dst, is_v ? &map_v : &map_k, 0, tin, 0, (int)pb, bar_full + 8 * s);
+          else tma_load_4d(dst, is_v ? &map_v : &map_k, 0, row, tin, (int)pb, bar_full + 8 * s);
         }
       }
     }
@@ -312,11 +320,17 @@ __global__ void __launch_bounds__(kThreads, 2) swa_decode_kernel(const Params P)
   float acc[kD / 16][4];
   float m0 = -INFINITY, m1 = -INFINITY, l0 = 0.f, l1 = 0.f;
 
+  // ldmatrix row addresses inside a stage. A tile is [128-byte row = head*2 + half][token][128 B] with
+  // the 16-byte chunk index XOR-ed by (token & 7) (the 128-byte swizzle of the tensor copy).
   const int lj = lane >> 3, lr = lane & 7;
-  const uint32_t k_lane_off = (sub * kChunk + lr + ((lj & 1) ? 8 : 0)) * C::kRowStride + hk * (kD * 2) +
-                              ((lj >> 1) ? 16 : 0);
-  const uint32_t v_lane_off = C::kVOffset + (sub * kChunk + lr + ((lj >> 1) ? 8 : 0)) * C::kRowStride +
-                              hk * (kD * 2) + ((lj & 1) ? 16 : 0);
+  const int tok_k = lr + ((lj & 1) ? 8 : 0), cj_k = lj >> 1;
+  const int tok_v = lr + ((lj >> 1) ? 8 : 0), cj_v = lj & 1;
+  const uint32_t k_lane_off = sub * C::kTileBytes + (hk * 32 + tok_k) * 128;
+  const uint32_t v_lane_off = C::kVOffset + sub * C::kTileBytes + (hk * 32 + tok_v) * 128;
+  const int xk = tok_k & 7, xv = tok_v & 7;
+  // dims [16*i, 16*i+16) of a head: half = i/4 (2 KiB apart), chunks 2*(i%4) and 2*(i%4)+1
+#define SBK_K_ADDR(i) (stage + k_lane_off + ((i) >> 2) * 2048 + ((((((i) & 3) << 1) + cj_k) ^ xk) << 4))
+#define SBK_V_ADDR(i) (stage + v_lane_off + ((i) >> 2) * 2048 + ((((((i) & 3) << 1) + cj_v) ^ xv) << 4))
 
   for (int it = 0;; ++it) {
     const int s = it % C::kStages;
@@ -355,15 +369,17 @@ __global__ void __launch_bounds__(kThreads, 2) swa_decode_kernel(const Params P)
     if (!(si.flags & kFlagBad) && vhi > vlo) {
 #endif
       if (ragged) {
-        // V rows no copy filled must hold finite values: a zero probability times a NaN would
-        // poison the accumulator. Each warp clears its own head's 256 bytes of those rows.
+        // A tile always brings 16 token rows; those outside the visible range may hold anything.
+        // Their V must be finite (a zero probability times a NaN would poison the accumulator):
+        // each warp clears its own head's 256 bytes of those rows.
 #pragma unroll
         for (int r0 = 0; r0 < kChunk; r0 += 2) {
           const int r = r0 + (lane >> 4);
           const int tok = tb + r;
-          if (tok < vlo || tok >= vhi) {
-            *reinterpret_cast<uint4*>(smem + s * C::kStageBytes + C::kVOffset + (sub * kChunk + r) * C::kRowStride +
-                                      hk * (kD * 2) + (lane & 15) * 16) = make_uint4(0, 0, 0, 0);
+          if (tok < vlo || tok >= vhi) {   // both 128-byte rows of my head for this token
+            *reinterpret_cast<uint4*>(smem + s * C::kStageBytes + C::kVOffset + sub * C::kTileBytes +
+                                      ((hk * 2 + ((lane >> 3) & 1)) * 16 + r) * 128 + (lane & 7) * 16) =
+                make_uint4(0, 0, 0, 0);
           }
         }
         __syncwarp();
@@ -373,9 +389,9 @@ __global__ void __launch_bounds__(kThreads, 2) swa_decode_kernel(const Params P)
 #pragma unroll
       for (int kk = 0; kk < kD / 16; kk += 2) {
         uint32_t a[4];
-        ldmatrix_x4(a, stage + k_lane_off + kk * 32);
+        ldmatrix_x4(a, SBK_K_ADDR(kk));
         mma_bf16_16816(sa, a, qf[kk][0], qf[kk][1]);
-        ldmatrix_x4(a, stage + k_lane_off + (kk + 1) * 32);
+        ldmatrix_x4(a, SBK_K_ADDR(kk + 1));
         mma_bf16_16816(sb, a, qf[kk + 1][0], qf[kk + 1][1]);
       }
       float sc[4];
@@ -422,11 +438,11 @@ __global__ void __launch_bounds__(kThreads, 2) swa_decode_kernel(const Params P)
 #pragma unroll
       for (int mt = 0; mt < kD / 16; ++mt) {
         uint32_t a[4];
-        ldmatrix_x4_trans(a, stage + v_lane_off + mt * 32);
+        ldmatrix_x4_trans(a, SBK_V_ADDR(mt));
         mma_bf16_16816(acc[mt], a, pb0, pb1);
         mma_bf16_16816(acc[mt], a, pc0, pc1);
       }
-      if (ragged) fence_proxy_async_smem();   // my zero fill precedes the next bulk copy into these rows
+      if (ragged) fence_proxy_async_smem();   // my zero fill precedes the next tensor copy into these rows
     }
     __syncwarp();
     if (lane == 0) mbar_arrive(bar_empty + 8 * s);
@@ -565,8 +581,89 @@ __global__ void __launch_bounds__(kThreads, 2) swa_decode_kernel(const Params P)
   }
 }
 
+// ---- tensor maps ------------------------------------------------------------------------
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*,
+                                  CUtensorMapInterleave, CUtensorMapSwizzle, CUtensorMapL2promotion,
+                                  CUtensorMapFloatOOBfill);
+
+static EncodeTiledFn encode_fn() {
+  static EncodeTiledFn fn = nullptr;
+  if (!fn) {
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
+        q == cudaDriverEntryPointSuccess)
+      fn = reinterpret_cast<EncodeTiledFn>(p);
+  }
+  return fn;
+}
+
+// A cache [num_blocks][block][kvh][128] bf16 seen as 64-element (128-byte) rows.
+//   tile_copy: dims (64, token in block, 128-byte row of a token, block) -- the token stride (kvh*256)
+//              comes BEFORE the row stride (128), so a box of (64,16,2kvh,1) lands as [row][token];
+//   row-wise : dims (64, 128-byte row, token in block, block), box (64,1,16,1).
+static bool encode_map(CUtensorMap* m, const void* base, int kvh, int64_t num_blocks, int block_size,
+                       int64_t block_stride, bool tile_copy) {
+  EncodeTiledFn fn = encode_fn();
+  if (!fn) return false;
+  const cuuint64_t row_bytes = (cuuint64_t)kvh * 256;
+  cuuint64_t dim[4], stride[3];
+  cuuint32_t box[4], estr[4] = {1, 1, 1, 1};
+  dim[0] = 64; dim[3] = (cuuint64_t)num_blocks;
+  stride[2] = (cuuint64_t)block_stride;
+  if (tile_copy) {
+    dim[1] = (cuuint64_t)block_size; dim[2] = 2 * kvh;
+    stride[0] = row_bytes; stride[1] = 128;
+    box[0] = 64; box[1] = 16; box[2] = 2 * kvh; box[3] = 1;
+  } else {
+    dim[1] = 2 * kvh; dim[2] = (cuuint64_t)block_size;
+    stride[0] = 128; stride[1] = row_bytes;
+    box[0] = 64; box[1] = 1; box[2] = 16; box[3] = 1;
+  }
+  return fn(m, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 4, const_cast<void*>(base), dim, stride, box, estr,
+            CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+            CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+struct MapKey {
+  const void* base; int kvh; int64_t num_blocks; int block_size; int64_t block_stride;
+  bool operator==(const MapKey& o) const {
+    return base == o.base && kvh == o.kvh && num_blocks == o.num_blocks && block_size == o.block_size &&
+           block_stride == o.block_stride;
+  }
+};
+
+// Small process-wide cache of encoded maps (one per cache tensor and geometry). A map holds
+// nothing but the address and the dimensions, so it stays valid as long as the geometry does.
+// Returns the copy mode in *tile_copy: the permuted-stride form is tried once per process.
+static int g_copy_mode = -1;   // -1 unknown, 1 tile copies, 0 row copies
+static bool get_map(CUtensorMap* out, const MapKey& key, int* tile_copy) {
+  static std::mutex mu;
+  int& mode = g_copy_mode;
+  constexpr int kSlots = 128;
+  static MapKey keys[kSlots];
+  static CUtensorMap maps[kSlots];
+  static int used = 0, next = 0;
+  std::lock_guard<std::mutex> lock(mu);
+  if (mode < 0) {
+    CUtensorMap probe;
+    mode = encode_map(&probe, key.base, key.kvh, key.num_blocks, key.block_size, key.block_stride, true) ? 1 : 0;
+  }
+  *tile_copy = mode;
+  for (int i = 0; i < used; ++i)
+    if (keys[i] == key) { *out = maps[i]; return true; }
+  CUtensorMap m;
+  if (!encode_map(&m, key.base, key.kvh, key.num_blocks, key.block_size, key.block_stride, mode == 1)) return false;
+  const int slot = used < kSlots ? used++ : (next++ % kSlots);
+  keys[slot] = key; maps[slot] = m;
+  *out = m;
+  return true;
+}
+
 template <int KVH, typename TO>
-int launch_swa(const Params& P0, int B_total, int n_ctas, cudaStream_t st) {
+int launch_swa(const Params& P0, int B_total, int n_ctas, const CUtensorMap& map_k, const CUtensorMap& map_v,
+               cudaStream_t st) {
   using C = Cfg<KVH>;
   auto kern = swa_decode_kernel<KVH, TO>;
   // The opt-in to large dynamic shared memory is per device; remember which devices have it.
@@ -599,7 +696,7 @@ int launch_swa(const Params& P0, int B_total, int n_ctas, cudaStream_t st) {
     }
     int64_t items = (int64_t)P.B * P0.max_pieces;
     const int grid = (int)(items < n_ctas ? items : n_ctas);
-    kern<<<grid, kThreads, C::kSmemBytes, st>>>(P);
+    kern<<<grid, kThreads, C::kSmemBytes, st>>>(P, map_k, map_v);
     int rc = check_launch("sbk_swa_decode");
     if (rc != SBK_OK) return rc;
   }
@@ -609,6 +706,8 @@ int launch_swa(const Params& P0, int B_total, int n_ctas, cudaStream_t st) {
 static size_t ctrl_bytes(int B) { return 16 + (size_t)((B + 3) / 4 * 4) * 4; }
 
 }  // namespace sbk
+
+extern "C" int sbk_swa_copy_mode(void) { return sbk::g_copy_mode; }
 
 extern "C" size_t sbk_swa_workspace_bytes(int B, int H, int D, int max_pieces) {
   if (B <= 0 || H <= 0 || D <= 0 || max_pieces < 1) return 0;
@@ -697,12 +796,21 @@ extern "C" int sbk_swa_decode(const void* q, int64_t q_seq_stride, const void* k
     if (dev >= 0 && dev < 64) sm_count[dev] = sms;
   }
   const int n_ctas = 2 * sms;
+  CUtensorMap map_k, map_v;
+  int tile_copy = 0;
+  if (!get_map(&map_k, MapKey{k_cache, kvh, num_blocks, block_size, cache_block_stride_bytes}, &tile_copy) ||
+      !get_map(&map_v, MapKey{v_cache, kvh, num_blocks, block_size, cache_block_stride_bytes}, &tile_copy)) {
+    set_error("sbk_swa_decode: cuTensorMapEncodeTiled rejected the cache geometry (blocks=%lld block=%d kvh=%d)",
+              (long long)num_blocks, block_size, kvh);
+    return SBK_E_ARG;
+  }
+  P.tile_copy = tile_copy;
   cudaStream_t st = (cudaStream_t)stream;
-#define SBK_SWA_KVH(TO)                                              \
-  switch (kvh) {                                                     \
-    case 1: return launch_swa<1, TO>(P, B, n_ctas, st);              \
-    case 2: return launch_swa<2, TO>(P, B, n_ctas, st);              \
-    default: return launch_swa<4, TO>(P, B, n_ctas, st);             \
+#define SBK_SWA_KVH(TO)                                                            \
+  switch (kvh) {                                                                   \
+    case 1: return launch_swa<1, TO>(P, B, n_ctas, map_k, map_v, st);              \
+    case 2: return launch_swa<2, TO>(P, B, n_ctas, map_k, map_v, st);              \
+    default: return launch_swa<4, TO>(P, B, n_ctas, map_k, map_v, st);             \
   }
   if (out_dtype == SBK_BF16) { SBK_SWA_KVH(__nv_bfloat16) } else { SBK_SWA_KVH(float) }
 #undef SBK_SWA_KVH

@@ -120,6 +120,21 @@ def kv_gather(k_cache: torch.Tensor, v_cache: torch.Tensor, block_tables: torch.
     return k_out, v_out
 
 
+_SM_COUNT = {}
+
+
+def swa_auto_split(B: int, max_visible_tokens: int, device) -> int:
+    """Chunks (of 16 tokens) per split such that a batch of B sequences yields about one work
+    item per resident CTA (two CTAs per SM): large batches are not split at all, small ones are
+    cut just fine enough to occupy the machine. Never below 4 chunks."""
+    idx = torch.device(device).index or 0
+    if idx not in _SM_COUNT:
+        _SM_COUNT[idx] = torch.cuda.get_device_properties(idx).multi_processor_count
+    chunks = (max(int(max_visible_tokens), 1) + 15) // 16 + 1
+    pieces = max(1, round(2 * _SM_COUNT[idx] / max(B, 1)))
+    return max(4, -(-chunks // pieces))
+
+
 def swa_max_pieces(max_visible_tokens: int, split_chunks: int = DEFAULT_SPLIT_CHUNKS) -> int:
     """Upper bound on the splits of one sequence whose window holds ``max_visible_tokens``."""
     chunks = (max(int(max_visible_tokens), 1) + 15) // 16 + 1  # +1: a window rarely starts on a chunk edge
@@ -139,9 +154,10 @@ def swa_decode(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor,
                scale: Optional[float] = None, out: Optional[torch.Tensor] = None,
                out_dtype: Optional[torch.dtype] = None, lse: Optional[torch.Tensor] = None,
                workspace: Optional[torch.Tensor] = None, max_pieces: Optional[int] = None,
-               split_chunks: int = DEFAULT_SPLIT_CHUNKS,
+               split_chunks: Optional[int] = None,
                status: Optional[torch.Tensor] = None) -> torch.Tensor:
-    """Single-query sliding-window attention over the paged cache; q [B, H, D] bf16."""
+    """Single-query sliding-window attention over the paged cache; q [B, H, D] bf16.
+    ``split_chunks`` (16-token chunks per split of a sequence) defaults to swa_auto_split."""
     _need_cuda(q, k_cache, v_cache, block_tables, seq_lens, out, lse, workspace, status)
     nb, bs, kvh, d, bstride = _cache_geometry(k_cache, v_cache)
     if q.dim() != 3 or q.shape[2] != d or q.dtype != torch.bfloat16 or k_cache.dtype != torch.bfloat16:
@@ -164,8 +180,10 @@ def swa_decode(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor,
     if lse is not None and (lse.dtype != torch.float32 or lse.shape != (B, H) or not lse.is_contiguous()):
         raise ValueError("lse must be contiguous fp32 [B, H]")
     max_blocks = block_tables.shape[1]
+    vis = max_blocks * bs if window_left < 0 else min(max_blocks * bs, window_left + 1)
+    if split_chunks is None:
+        split_chunks = swa_auto_split(B, vis, q.device) if B else DEFAULT_SPLIT_CHUNKS
     if max_pieces is None:
-        vis = max_blocks * bs if window_left < 0 else min(max_blocks * bs, window_left + 1)
         max_pieces = swa_max_pieces(vis, split_chunks)
     if workspace is None:
         workspace = swa_workspace(B, H, d, max_pieces, q.device)
