@@ -134,6 +134,30 @@ int sbk_swa_decode(const void* q, int64_t q_seq_stride, const void* k_cache, con
                    int32_t* status, void* stream);
 
 /*
+ * sbk_swa_decode for callers that cannot allocate device memory -- a server that gave all free
+ * HBM to its KV pool at start-up, a loop that forbids allocator calls once running, a binding
+ * with no tensor library behind it. No counterpart in the reference. Same arguments as
+ * sbk_swa_decode without `workspace`: the scratch is a fixed array of
+ * sbk_swa_static_scratch_bytes() (16 MiB) inside the library, resident on every GPU that loads
+ * the library until the process ends.
+ *  - sbk_swa_workspace_bytes(B, H, D, max_pieces) must not exceed that size, else
+ *    SBK_E_WORKSPACE is returned and nothing is launched (with one piece per sequence any B up
+ *    to about four million fits; with 9 pieces and 28 heads B up to 128).
+ *  - The first call on a device looks the array's device address up; make that call before
+ *    starting a stream capture. The call itself performs no allocation of any kind.
+ *  - All calls share the one array: two calls whose kernels can overlap on the GPU (different
+ *    streams, no dependency) race on it. Calls on one stream are safe; the counters are
+ *    cleared on `stream` at the start of every call.
+ */
+size_t sbk_swa_static_scratch_bytes(void);
+int sbk_swa_decode_static(const void* q, int64_t q_seq_stride, const void* k_cache, const void* v_cache,
+                          const int32_t* block_tables, int max_blocks, const int32_t* seq_lens,
+                          int B, int H, int kvh, int D, int64_t num_blocks, int block_size,
+                          int64_t cache_block_stride_bytes, int window_left, float scale,
+                          void* out, int out_dtype, int64_t out_seq_stride, float* lse_out,
+                          int split_chunks, int max_pieces, int32_t* status, void* stream);
+
+/*
  * Fused GLA recurrent-state step, in place in the slot cache:
  *    S[slot] <- diag(exp(g)) . S[slot] + k^T v ;   o = (q*scale) . S[slot]
  * Stands in for my_fused_recurrent_gla

@@ -815,3 +815,71 @@ extern "C" int sbk_swa_decode(const void* q, int64_t q_seq_stride, const void* k
   if (out_dtype == SBK_BF16) { SBK_SWA_KVH(__nv_bfloat16) } else { SBK_SWA_KVH(float) }
 #undef SBK_SWA_KVH
 }
+
+// ---------------------------------------------------------------------------------------------
+// sbk_swa_decode_static: the same decode, for callers that must not allocate device memory.
+//
+// A serving process often hands every spare byte of HBM to its KV-cache pool when it starts, a
+// real-time loop may forbid allocator calls once it is running, and a binding written in a
+// language without a tensor library has no allocator to ask at all. For them the scratch of
+// the decode kernel (work tickets, per-sequence completion counters, split partials) lives in
+// a fixed array inside the library's own device image instead of a caller-supplied buffer.
+// The price: kStaticScratchBytes of HBM on every GPU that loads the library, held until the
+// process exits, and an upper limit on B * max_pieces.
+namespace sbk {
+constexpr size_t kStaticScratchBytes = 16u << 20;   // 16 MiB
+static __device__ __align__(256) unsigned char g_swa_static_scratch[kStaticScratchBytes];
+}  // namespace sbk
+
+extern "C" size_t sbk_swa_static_scratch_bytes(void) { return sbk::kStaticScratchBytes; }
+
+extern "C" int sbk_swa_decode_static(const void* q, int64_t q_seq_stride, const void* k_cache,
+                                     const void* v_cache, const int32_t* block_tables, int max_blocks,
+                                     const int32_t* seq_lens, int B, int H, int kvh, int D,
+                                     int64_t num_blocks, int block_size,
+                                     int64_t cache_block_stride_bytes, int window_left, float scale,
+                                     void* out, int out_dtype, int64_t out_seq_stride, float* lse_out,
+                                     int split_chunks, int max_pieces, int32_t* status, void* stream) {
+  using namespace sbk;
+  if (B < 0 || H <= 0 || D <= 0 || max_pieces < 1) {
+    set_error("sbk_swa_decode_static: bad sizes B=%d H=%d D=%d max_pieces=%d", B, H, D, max_pieces);
+    return SBK_E_ARG;
+  }
+  if (B == 0) return SBK_OK;
+  const size_t need = sbk_swa_workspace_bytes(B, H, D, max_pieces);
+  if (need > kStaticScratchBytes) {
+    set_error("sbk_swa_decode_static: B=%d x max_pieces=%d needs %zu bytes of scratch, the built-in array "
+              "holds %zu; lower max_pieces or use sbk_swa_decode with a workspace of your own",
+              B, max_pieces, need, kStaticScratchBytes);
+    return SBK_E_WORKSPACE;
+  }
+  // Inside host code the array's name is only a handle: the address a kernel can use has to be
+  // asked for, once per device, while that device is current.
+  static void* scratch_of_device[64] = {};
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) {
+    set_error("sbk_swa_decode_static: no current CUDA device (or index above 63)");
+    return SBK_E_ARG;
+  }
+  void* scratch = scratch_of_device[dev];
+  if (scratch == nullptr) {
+    cudaError_t e = cudaGetSymbolAddress(&scratch, g_swa_static_scratch);
+    if (e != cudaSuccess || scratch == nullptr) {
+      set_error("sbk_swa_decode_static: cudaGetSymbolAddress failed on device %d: %s", dev,
+                cudaGetErrorString(e));
+      return SBK_E_LAUNCH;
+    }
+    scratch_of_device[dev] = scratch;
+  }
+  // The array keeps whatever the previous call left in it. The partials are rewritten before
+  // they are read; the counters at its head have to start from zero.
+  cudaError_t e = cudaMemsetAsync(scratch, 0, ctrl_bytes(B), (cudaStream_t)stream);
+  if (e != cudaSuccess) {
+    set_error("sbk_swa_decode_static: clearing the counters failed: %s", cudaGetErrorString(e));
+    return SBK_E_LAUNCH;
+  }
+  return sbk_swa_decode(q, q_seq_stride, k_cache, v_cache, block_tables, max_blocks, seq_lens, B, H, kvh, D,
+                        num_blocks, block_size, cache_block_stride_bytes, window_left, scale, out, out_dtype,
+                        out_seq_stride, lse_out, scratch, kStaticScratchBytes, split_chunks, max_pieces, status,
+                        stream);
+}
