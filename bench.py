@@ -224,8 +224,6 @@ class DecodeEngine:
         pin = lambda t: t.cpu().pin_memory()
         self.h_q, self.h_k, self.h_v = pin(self.q[0]), pin(self.k[0]), pin(self.v[0])
         self.h_gq, self.h_gk, self.h_gv, self.h_gg = pin(self.gq), pin(self.gk), pin(self.gv), pin(self.gg)
-        self.h_out = torch.empty(B, H, D, dtype=torch.bfloat16).pin_memory()
-        self.copy_stream = torch.cuda.Stream(device=device)
         self.h2d_bytes = self.d2h_bytes = 0
 
     def _advance_metadata(self):
@@ -252,29 +250,16 @@ class DecodeEngine:
         return meta, nbytes
 
     def step(self, e2e=False):
-        torch, ops = self.torch, self.ops
-        meta, meta_bytes = self._advance_metadata()
-        cur = torch.cuda.current_stream()
         if e2e:
-            self.h2d_bytes += meta_bytes
+            return self._step_e2e()
+        ops = self.ops
+        meta, _ = self._advance_metadata()
         first_swa = True
-        n_pairs = max(self.n_swa, self.n_gla)
-        for i in range(n_pairs):
+        for i in range(max(self.n_swa, self.n_gla)):
             if i < self.n_gla:   # even layers of the model are GLA layers
-                if e2e:
-                    for dst, src in ((self.gq, self.h_gq), (self.gk, self.h_gk), (self.gv, self.h_gv), (self.gg, self.h_gg)):
-                        dst.copy_(src, non_blocking=True)
-                        self.h2d_bytes += src.numel() * src.element_size()
-                o = self.gla_fn(self.gq, self.gk, self.gv, self.gg, kv_caches=self.gla.cache[i], slot_idx=self.slot_idx)
-                if e2e:
-                    self.h_out.copy_(o, non_blocking=True)
-                    self.d2h_bytes += o.numel() * o.element_size()
+                self.gla_fn(self.gq, self.gk, self.gv, self.gg, kv_caches=self.gla.cache[i], slot_idx=self.slot_idx)
             if i < self.n_swa:   # odd layers are sliding-window layers
                 j = i & 1
-                if e2e:
-                    for dst, src in ((self.q[j], self.h_q), (self.k[j], self.h_k), (self.v[j], self.h_v)):
-                        dst.copy_(src, non_blocking=True)
-                        self.h2d_bytes += src.numel() * src.element_size()
                 if first_swa:
                     # retire on the device what the host mirror released this step
                     ops.kv_append(self.k[j][:0], self.v[j][:0], self.kv[i][0], self.kv[i][1], self.slots_d[:0],
@@ -282,26 +267,125 @@ class DecodeEngine:
                     first_swa = False
                 self.impls[i].forward(None, self.q[j], self.k[j], self.v[j], None, None, None, self.kv[i],
                                       meta, output=self.out)
-                if e2e:
-                    self.h_out.copy_(self.out, non_blocking=True)
-                    self.d2h_bytes += self.out.numel() * self.out.element_size()
-        if e2e:
-            cur.synchronize()   # the caller holds the step's result on the host
+
+    def _e2e_setup(self):
+        """Double-buffered device inputs/outputs, one stream per copy direction, and the events
+        that order them against the compute stream."""
+        torch = self.torch
+        if hasattr(self, "_e2e"):
+            return self._e2e
+        dev = self.device
+        ev = lambda: torch.cuda.Event()
+        st = type("E2E", (), {})()
+        st.h2d, st.d2h = torch.cuda.Stream(device=dev), torch.cuda.Stream(device=dev)
+        st.g_in = [[torch.empty_like(t) for t in (self.gq, self.gk, self.gv, self.gg)] for _ in range(2)]
+        st.s_in = [[self.q[j], self.k[j], self.v[j]] for j in range(2)]
+        st.out = [torch.empty_like(self.out) for _ in range(2)]
+        st.h_out = [torch.empty(self.out.shape, dtype=self.out.dtype).pin_memory() for _ in range(2)]
+        st.in_ready = {k: [ev(), ev()] for k in "gs"}     # recorded on h2d: inputs of slot landed
+        st.in_free = {k: [ev(), ev()] for k in "gs"}      # recorded on compute: slot consumed
+        st.out_ready, st.out_free = [ev(), ev()], [ev(), ev()]
+        cur = torch.cuda.current_stream()
+        for k in "gs":
+            for e in st.in_free[k]:
+                e.record(cur)
+        for e in st.out_free:
+            e.record(cur)
+        st.n = 0
+        self._e2e = st
+        return st
+
+    def _step_e2e(self):
+        """One step as a caller with HOST buffers sees it: every layer's inputs travel from pinned
+        host memory (H2D stream, one layer ahead of the math), every layer's output travels
+        back (D2H stream), and the step ends when the last output is on the host."""
+        torch, ops = self.torch, self.ops
+        st = self._e2e_setup()
+        cur = torch.cuda.current_stream()
+        meta, meta_bytes = self._advance_metadata()
+        self.h2d_bytes += meta_bytes
+        first_swa = True
+
+        def upload(kind, slot, pairs):
+            st.h2d.wait_event(st.in_free[kind][slot])
+            with torch.cuda.stream(st.h2d):
+                for dst, src in pairs:
+                    dst.copy_(src, non_blocking=True)
+                    self.h2d_bytes += src.numel() * src.element_size()
+            st.in_ready[kind][slot].record(st.h2d)
+            cur.wait_event(st.in_ready[kind][slot])
+
+        def download(o, oslot):
+            st.out_ready[oslot].record(cur)
+            st.d2h.wait_event(st.out_ready[oslot])
+            with torch.cuda.stream(st.d2h):
+                st.h_out[oslot].copy_(o, non_blocking=True)
+            o.record_stream(st.d2h)
+            st.out_free[oslot].record(st.d2h)
+            self.d2h_bytes += o.numel() * o.element_size()
+
+        for i in range(max(self.n_swa, self.n_gla)):
+            slot = i & 1
+            if i < self.n_gla:
+                gi = st.g_in[slot]
+                upload("g", slot, zip(gi, (self.h_gq, self.h_gk, self.h_gv, self.h_gg)))
+                o = self.gla_fn(gi[0], gi[1], gi[2], gi[3], kv_caches=self.gla.cache[i], slot_idx=self.slot_idx)
+                st.in_free["g"][slot].record(cur)
+                oslot = st.n & 1; st.n += 1
+                download(o, oslot)
+            if i < self.n_swa:
+                q, k, v = st.s_in[slot]
+                upload("s", slot, zip((q, k, v), (self.h_q, self.h_k, self.h_v)))
+                if first_swa:
+                    ops.kv_append(k[:0], v[:0], self.kv[i][0], self.kv[i][1], self.slots_d[:0],
+                                  block_tables=self.table_d, seq_lens=self.lens_d, window_left=WINDOW_LEFT)
+                    first_swa = False
+                oslot = st.n & 1; st.n += 1
+                cur.wait_event(st.out_free[oslot])      # its previous content is on the host
+                self.impls[i].forward(None, q, k, v, None, None, None, self.kv[i], meta, output=st.out[oslot])
+                st.in_free["s"][slot].record(cur)
+                download(st.out[oslot], oslot)
+        st.d2h.synchronize()   # the caller now holds every layer output of the step
+
+
+# ------------------------------------------------------------------- multi-rank plumbing
+def dist_setup(backend, device=None):
+    """(rank, world); joins the process group when launched with more than one rank."""
+    import torch.distributed as dist
+    rank = int(os.environ.get("RANK", 0))
+    world = int(os.environ.get("WORLD_SIZE", 1))
+    if world > 1 and not dist.is_initialized():
+        if backend == "nccl":
+            dist.init_process_group("nccl", device_id=device)
+        else:
+            dist.init_process_group(backend)
+    return rank, world
+
+
+def max_over_ranks(value, device):
+    """The slowest rank's time: every rank works on its own sequences, the job ends with the last."""
+    import torch
+    import torch.distributed as dist
+    t = torch.tensor([value], dtype=torch.float64, device=device)
+    if dist.is_available() and dist.is_initialized() and dist.get_world_size() > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    return float(t.item())
+
+
+def job_tokens_per_s(batch_per_rank, world, ms_per_step):
+    """Whole-job throughput: every rank decodes one token for each of its sequences per step."""
+    return batch_per_rank * world / (ms_per_step * 1e-3)
 
 
 def run_b200(args):
     import torch
     import torch.distributed as dist
-    rank = int(os.environ.get("RANK", 0))
-    world = int(os.environ.get("WORLD_SIZE", 1))
     local = int(os.environ.get("LOCAL_RANK", 0))
-    if world != args.gpus:
-        if world == 1 and args.gpus > 1:
-            raise SystemExit("launch multi-GPU runs with torch.distributed.run (one rank per GPU)")
+    if int(os.environ.get("WORLD_SIZE", 1)) == 1 and args.gpus > 1:
+        raise SystemExit("launch multi-GPU runs with torch.distributed.run (one rank per GPU)")
     torch.cuda.set_device(local)
     device = torch.device("cuda", local)
-    if world > 1:
-        dist.init_process_group("nccl", device_id=device)
+    rank, world = dist_setup("nccl", device)
 
     # builds the library on first use if needed (it normally travels prebuilt)
     import importlib.util
@@ -333,11 +417,9 @@ def run_b200(args):
         ms = max(e0.elapsed_time(e1), 0.0)
         if e2e:
             ms = max(ms, wall)   # the host waits inside an end-to-end step; take the slower clock
-        t = torch.tensor([ms], dtype=torch.float64, device=device)
-        if world > 1:
-            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms = max_over_ranks(ms, device)
         barrier()
-        return float(t.item())
+        return ms
 
     # ---- device-resident timing ----
     sampler = ClockSampler(local)
@@ -362,7 +444,7 @@ def run_b200(args):
             eng.step(e2e=True)
         eng.h2d_bytes = eng.d2h_bytes = 0
         e2e_ms = timed(args.steps, e2e=True) / args.steps
-        e2e_obj = {"value": args.batch * world / (e2e_ms * 1e-3), "unit": "tokens/s",
+        e2e_obj = {"value": job_tokens_per_s(args.batch, world, e2e_ms), "unit": "tokens/s",
                    "h2d_bytes_per_step": eng.h2d_bytes // args.steps,
                    "d2h_bytes_per_step": eng.d2h_bytes // args.steps, "ms_per_step": e2e_ms}
 
@@ -383,7 +465,7 @@ def run_b200(args):
     achieved = swa_layer_bytes / (swa_avg_ms * 1e-3) / 1e9 if swa_avg_ms else None
     line = {
         "metric": "decode tokens/s and cache HBM GB/s (% of 8 TB/s)",
-        "value": args.batch * world / (ms_per_step * 1e-3), "unit": "tokens/s",
+        "value": job_tokens_per_s(args.batch, world, ms_per_step), "unit": "tokens/s",
         "n_gpus": world, "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": ms_per_step,
         "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16 K/V, f32 GLA state",
         "data": "synthetic",
@@ -392,9 +474,10 @@ def run_b200(args):
                                f"window_left {WINDOW_LEFT}, block {BLOCK}, 28/4 heads, head_dim 128",
                    "parallelism": f"sequence-sharded x{world}, no collective",
                    "l2": "working set (KV pools + GLA state, tens of GB) far exceeds the 126 MB L2; no flush needed"},
-        "cache_gbs": step_bytes / (ms_per_step * 1e-3) / 1e9,
+        "cache_gbs": world * step_bytes / (ms_per_step * 1e-3) / 1e9,
+        "cache_gbs_per_gpu": step_bytes / (ms_per_step * 1e-3) / 1e9,
         "cache_frac_of_8tbs": step_bytes / (ms_per_step * 1e-3) / 1e9 / NOMINAL_HBM_GBS,
-        "cache_bytes_per_step": step_bytes,
+        "cache_bytes_per_step_per_gpu": step_bytes,
         "roofline": {"bound": "hbm", "kernel": "swa_decode_kernel (+ its split reduce)",
                      "achieved": achieved, "peak": peak, "unit": "GB/s",
                      "frac": achieved / peak if achieved else None, "peak_source": peak_src,

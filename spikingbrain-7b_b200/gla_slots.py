@@ -60,7 +60,7 @@ class GLACacheManager:
             for slot in self.cache_indices_mapping.pop(rid, {}).values():
                 self.free_cache_indices.append(slot)
 
-    def _assign(self, rid: str, seq_id: int) -> int:
+    def _assign(self, rid: str, seq_id: int, to_clear: List[int]) -> int:
         seqs = self.cache_indices_mapping.setdefault(rid, {})
         if seq_id in seqs:
             return seqs[seq_id]
@@ -70,7 +70,7 @@ class GLACacheManager:
         if seqs:  # a fork of a running request starts from its sibling's state
             self._copy_cache(next(iter(seqs.values())), slot)
         else:
-            self.clear_slots([slot])
+            to_clear.append(slot)
         seqs[seq_id] = slot
         return slot
 
@@ -80,7 +80,9 @@ class GLACacheManager:
         """(state tensor, state_indices_tensor[int64]) for this step's sequences, in the order
         of ``request_ids_to_seq_ids``; ``pad_to`` appends -1 entries (captured-graph batches)."""
         self._release_finished(finished_requests_ids or [])
-        slots = [self._assign(rid, sid) for rid, sids in request_ids_to_seq_ids.items() for sid in sids]
+        to_clear: List[int] = []
+        slots = [self._assign(rid, sid, to_clear) for rid, sids in request_ids_to_seq_ids.items() for sid in sids]
+        self.clear_slots(to_clear)   # slots handed to new sequences start from a zero state, in one launch
         if pad_to is not None:
             slots += [-1] * (pad_to - len(slots))
         if len(set(s for s in slots if s >= 0)) != sum(1 for s in slots if s >= 0):

@@ -1,0 +1,89 @@
+"""CPU, two ranks over gloo: the multi-rank plumbing of bench.py (join, slowest-rank timing,
+whole-job throughput) and the independence of the per-rank block managers. Sequences are
+sharded across ranks without any data-path collective, so this is all the N>1 logic there is."""
+import os
+import socket
+import subprocess
+import sys
+import textwrap
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+WORKER = textwrap.dedent("""
+    import os, sys, json
+    sys.path.insert(0, {root!r})
+    import numpy as np
+    import torch
+    import torch.distributed as dist
+    import bench
+    from spikingbrain_7b_b200.block_pool import SlidingWindowBlockManager
+
+    rank, world = bench.dist_setup("gloo")
+    assert (rank, world) == (int(os.environ["RANK"]), 2) and dist.get_backend() == "gloo"
+    # every rank owns its own sequences, pool and tables: same shapes, different contents
+    B, bs, wl = 6, 16, 63
+    mgr = SlidingWindowBlockManager(B * 12, bs, wl, B, 40)
+    rng = np.random.default_rng(100 + rank)
+    mgr.pool._free = [int(x) for x in rng.permutation(B * 12)]
+    for r in range(B):
+        mgr.admit(r)
+    mgr.advance(rng.integers(1, 150, B))
+    slots = [mgr.advance(np.ones(B, dtype=np.int64)).slot_mapping for _ in range(40)]
+    digest = torch.tensor([int(np.concatenate(slots).sum()), int(mgr.lens.sum()), mgr.pool.num_free])
+    gathered = [torch.zeros_like(digest) for _ in range(world)]
+    dist.all_gather(gathered, digest)           # test-side only: the data path itself never communicates
+    assert gathered[0][0] != gathered[1][0], "ranks must not mirror each other's block assignment"
+    for r in range(B):
+        assert mgr.resident_blocks(r) <= (wl + 1 + bs - 1) // bs + 1
+    # the job's step time is the slowest rank's; throughput adds up over ranks
+    ms = bench.max_over_ranks(5.0 + 2.0 * rank, "cpu")
+    assert ms == 7.0
+    assert bench.job_tokens_per_s(256, world, ms) == 2 * 256 / 7.0e-3
+    dist.barrier()
+    if rank == 0:
+        print(json.dumps({{"ok": True, "ms": ms}}))
+    dist.destroy_process_group()
+""")
+
+
+def _free_port():
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        return s.getsockname()[1]
+
+
+def test_two_gloo_ranks_time_and_shard_independently(sb, tmp_path):
+    script = tmp_path / "worker.py"
+    script.write_text(WORKER.format(root=ROOT))
+    port = _free_port()
+    procs = []
+    for rank in range(2):
+        env = dict(os.environ, RANK=str(rank), LOCAL_RANK=str(rank), WORLD_SIZE="2", MASTER_ADDR="127.0.0.1",
+                   MASTER_PORT=str(port))
+        procs.append(subprocess.Popen([sys.executable, str(script)], env=env, stdout=subprocess.PIPE,
+                                      stderr=subprocess.PIPE, text=True))
+    outs = [p.communicate(timeout=240) for p in procs]
+    for p, (out, err) in zip(procs, outs):
+        assert p.returncode == 0, err[-2000:]
+    assert '"ok": true' in outs[0][0] and outs[1][0].strip() == ""
+
+
+def test_reference_arm_runs_on_rank_zero_only(monkeypatch, capsys):
+    """Under a multi-rank launch the CPU reference arm is rank 0's job; the others leave quietly."""
+    sys.path.insert(0, ROOT)
+    import bench
+    monkeypatch.setenv("RANK", "1")
+    monkeypatch.setenv("WORLD_SIZE", "2")
+    monkeypatch.setattr(sys, "argv", ["bench.py", "--impl", "reference", "--gpus", "2", "--steps", "1"])
+    assert bench.run_reference(bench.parse_args()) is None
+    assert capsys.readouterr().out == ""
+
+
+def test_cache_byte_model_matches_the_shapes():
+    sys.path.insert(0, ROOT)
+    import bench
+    total, swa, gla = bench.cache_bytes_per_step(256, 8193, 14, 14)
+    assert swa == 256 * (4097 * 2048 + 2048)            # window of K/V read + one token appended
+    assert gla == 256 * 2 * 28 * 128 * 128 * 4          # state read + written
+    assert total == 14 * (swa + gla) == 43232788480
+    assert bench.cache_bytes_per_step(2, 100, 1, 0)[0] == 2 * (100 * 2048 + 2048)
