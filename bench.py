@@ -36,6 +36,10 @@ H, KVH, D, WINDOW_LEFT, BLOCK = 28, 4, 128, 4096, 16
 N_SWA, N_GLA = 14, 14
 NOMINAL_HBM_GBS = 8000.0
 FALLBACK_HBM_GBS = 6650.0
+# DRAM bytes moved per algorithmic byte by the sliding-window decode kernel, from the ncu capture
+# summarised in profiles/swa_decode_kernel_b256_ctx8192.md (2.1584 GB read + 4.9 MB written for
+# 2.1481 GB of visible K/V: no re-reads). Traffic grows in proportion to the tokens read.
+SWA_TRAFFIC_PER_ALGORITHMIC_BYTE = (2.158386e9 + 4.914944e6) / (256 * 4097 * 2048)
 
 
 def parse_args():
@@ -97,9 +101,18 @@ def cpu_reference_step_seconds(n_seqs, ctx, repeats):
     return statistics.median(times)
 
 
-def cpu_baseline(args, sample_seqs=8, repeats=3):
+def use_all_host_threads():
+    """Launchers such as torch.distributed.run pin OMP_NUM_THREADS to 1; the CPU arm is meant to
+    use every core the box has."""
     import torch
-    cores = torch.get_num_threads()
+    n = os.cpu_count() or 1
+    if torch.get_num_threads() < n:
+        torch.set_num_threads(n)
+    return torch.get_num_threads()
+
+
+def cpu_baseline(args, sample_seqs=8, repeats=3):
+    cores = use_all_host_threads()
     t = cpu_reference_step_seconds(sample_seqs, args.ctx + 1, repeats)
     per_seq_layerpair = t / sample_seqs
     # a full step = batch sequences x (swa_layers + gla_layers); the sample timed one of each
@@ -483,7 +496,10 @@ def run_b200(args):
                      "frac": achieved / peak if achieved else None, "peak_source": peak_src,
                      "frac_of_8tbs": achieved / NOMINAL_HBM_GBS if achieved else None,
                      "algorithmic_bytes_per_launch": swa_layer_bytes, "avg_launch_ms": swa_avg_ms,
-                     "launches_timed": len(swa_ms), "traffic": None},
+                     "launches_timed": len(swa_ms),
+                     "traffic": int(swa_layer_bytes * SWA_TRAFFIC_PER_ALGORITHMIC_BYTE),
+                     "traffic_source": "ncu dram__bytes_read.sum + dram__bytes_write.sum of one launch of the same "
+                                       "batch and context (profiles/swa_decode_kernel_b256_ctx8192.md), scaled by tokens"},
         "e2e": e2e_obj, "gpu_launches": launches, "clocks": clocks, "device_status": status,
     }
     if not args.no_cpu_baseline:
@@ -497,9 +513,8 @@ def run_reference(args):
     """The reference's CPU path (oracle port) on the host cores; rank 0 only."""
     if int(os.environ.get("RANK", 0)) != 0:
         return
-    import torch
     sample_seqs = 8
-    cores = torch.get_num_threads()
+    cores = use_all_host_threads()
     pairs = max(args.swa_layers, args.gla_layers)
     for _ in range(max(args.warmup, 1)):
         cpu_reference_step_seconds(sample_seqs, args.ctx + 1, 1)

@@ -117,8 +117,8 @@ class SlidingWindowBlockManager:
 
     # --------------------------------------------------------------------- step
     def advance(self, n_new: Sequence[int], pad_inactive: bool = True) -> StepPlan:
-        """Append ``n_new[row]`` tokens to every active row: allocate the blocks they need,
-        compute their slots, then retire what left the window. With ``pad_inactive`` an
+        """Append ``n_new[row]`` tokens to every active row: release the blocks this step's queries
+        can no longer see, allocate the blocks the new tokens need, compute their slots. With ``pad_inactive`` an
         inactive row contributes one -1 slot when every active row appends one token
         (the static decode batch: token i belongs to row i)."""
         n_new = np.asarray(n_new, dtype=np.int64)
@@ -129,30 +129,33 @@ class SlidingWindowBlockManager:
         bs = self.block_size
         if pad_inactive and bool((n_new[self.active] == 1).all()):
             return self._advance_decode()
+        if ((self.lens.astype(np.int64) + n_new + bs - 1) // bs > self.max_blocks).any():
+            raise ValueError(f"a sequence exceeds max_blocks_per_seq={self.max_blocks}")
+        old_lens = self.lens.copy()
+        self.lens = (self.lens.astype(np.int64) + n_new).astype(np.int32)
+        # Blocks that this step's queries can no longer see go back to the pool BEFORE the new
+        # tokens take theirs: nothing reads them in this step, so they may be reused at once.
+        retired = self._retire(n_new)
         slots: List[np.ndarray] = []
         new_entries: List[List[int]] = []
         qsl = np.zeros(self.max_seqs + 1, dtype=np.int32)
         for row in range(self.max_seqs):
             n = int(n_new[row])
+            qsl[row + 1] = qsl[row] + n
             if n == 0:
-                qsl[row + 1] = qsl[row]
                 continue
-            L0 = int(self.lens[row])
+            L0 = int(old_lens[row])
             pos = np.arange(L0, L0 + n, dtype=np.int64)
             lb = pos // bs
-            if lb[-1] >= self.max_blocks:
-                raise ValueError(f"row {row}: {L0 + n} tokens exceed max_blocks_per_seq={self.max_blocks}")
             for j in range(int(lb[0]), int(lb[-1]) + 1):
                 if self.table[row, j] < 0:
                     if j < self._first_live[row]:
-                        raise RuntimeError("append into a block that was already retired")
+                        continue   # a prompt longer than the window: its oldest tokens are never stored
                     pb = self.pool.allocate()
                     self.table[row, j] = pb
                     new_entries.append([row, j, pb])
-            slots.append(self.table[row, lb].astype(np.int64) * bs + pos % bs)
-            self.lens[row] = L0 + n
-            qsl[row + 1] = qsl[row] + n
-        retired = self._retire(n_new)
+            blk = self.table[row, lb].astype(np.int64)
+            slots.append(np.where(blk >= 0, blk * bs + pos % bs, -1))
         return StepPlan(
             slot_mapping=np.concatenate(slots) if slots else np.zeros(0, dtype=np.int64),
             seq_lens=self.lens.copy(), query_start_loc=qsl,
@@ -167,19 +170,9 @@ class SlidingWindowBlockManager:
         lb = pos // bs
         if rows.size and lb.max() >= self.max_blocks:
             raise ValueError(f"a sequence exceeds max_blocks_per_seq={self.max_blocks}")
-        new_entries: List[List[int]] = []
-        for i in np.nonzero(self.table[rows, lb] < 0)[0]:
-            row, j = int(rows[i]), int(lb[i])
-            if j < self._first_live[row]:
-                raise RuntimeError("append into a block that was already retired")
-            pb = self.pool.allocate()
-            self.table[row, j] = pb
-            new_entries.append([row, j, pb])
-        slot_mapping = np.full(self.max_seqs, -1, dtype=np.int64)
-        slot_mapping[rows] = self.table[rows, lb].astype(np.int64) * bs + pos % bs
         self.lens[rows] += 1
         retired: List[List[int]] = [[] for _ in range(self.max_seqs)]
-        if self.window_left >= 0 and rows.size:
+        if self.window_left >= 0 and rows.size:   # retire first: the freed blocks can be reused at once
             t0 = np.maximum(self.lens[rows].astype(np.int64) - 1 - self.window_left, 0)
             first_live = np.minimum(t0 // bs, self.max_blocks)
             for i in np.nonzero(first_live > self._first_live[rows])[0]:
@@ -192,6 +185,16 @@ class SlidingWindowBlockManager:
                 self._first_live[row] = int(first_live[i])
                 self.pool.release(ids)
                 retired[row] = ids
+        new_entries: List[List[int]] = []
+        for i in np.nonzero(self.table[rows, lb] < 0)[0]:
+            row, j = int(rows[i]), int(lb[i])
+            if j < self._first_live[row]:
+                raise RuntimeError("append into a block that was already retired")
+            pb = self.pool.allocate()
+            self.table[row, j] = pb
+            new_entries.append([row, j, pb])
+        slot_mapping = np.full(self.max_seqs, -1, dtype=np.int64)
+        slot_mapping[rows] = self.table[rows, lb].astype(np.int64) * bs + pos % bs
         return StepPlan(slot_mapping=slot_mapping, seq_lens=self.lens.copy(),
                         query_start_loc=np.arange(self.max_seqs + 1, dtype=np.int32),
                         new_entries=np.asarray(new_entries, dtype=np.int32).reshape(-1, 3),
