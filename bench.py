@@ -53,6 +53,7 @@ def parse_args():
     ap.add_argument("--swa-layers", type=int, default=N_SWA)
     ap.add_argument("--gla-layers", type=int, default=N_GLA)
     ap.add_argument("--no-e2e", action="store_true")
+    ap.add_argument("--no-graph", action="store_true", help="launch every kernel from the host instead of replaying a CUDA graph")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     return ap.parse_args()
 
@@ -233,11 +234,16 @@ class DecodeEngine:
         self.gv = rn(B, KVH, 1, D)
         self.gg = (torch.nn.functional.logsigmoid(torch.randn(B, KVH, 1, D, device=device)) / 16).bfloat16()
         self.out = torch.empty(B, H, D, dtype=torch.bfloat16, device=device)
+        self.gla_out = torch.empty(B, H, D, dtype=torch.bfloat16, device=device)
+        self.graph = self.graph_e2e = self._e2e = None
+        self.swa_events = []
+        self.launches_per_step = 0
         # pinned host staging for the end-to-end mode
         pin = lambda t: t.cpu().pin_memory()
         self.h_q, self.h_k, self.h_v = pin(self.q[0]), pin(self.k[0]), pin(self.v[0])
         self.h_gq, self.h_gk, self.h_gv, self.h_gg = pin(self.gq), pin(self.gk), pin(self.gv), pin(self.gg)
         self.h2d_bytes = self.d2h_bytes = 0
+        self.e2e_in_bytes = self.e2e_out_bytes = 0
 
     def _advance_metadata(self):
         """Host side of a step: slots of the new tokens, new lengths, newly allocated blocks."""
@@ -262,15 +268,17 @@ class DecodeEngine:
                          max_decode_query_len=1)
         return meta, nbytes
 
-    def step(self, e2e=False):
-        if e2e:
-            return self._step_e2e()
-        ops = self.ops
-        meta, _ = self._advance_metadata()
+    # ---------------------------------------------------------------- device-resident step
+    def enqueue_layers(self, meta, timing=None):
+        """All kernels of one decode step on the current stream, through the reference-facing
+        calls. `timing`: list that receives an (start, end) event pair around every sliding-window
+        decode call (events created with external=True so that a captured graph records them)."""
+        torch, ops = self.torch, self.ops
         first_swa = True
         for i in range(max(self.n_swa, self.n_gla)):
             if i < self.n_gla:   # even layers of the model are GLA layers
-                self.gla_fn(self.gq, self.gk, self.gv, self.gg, kv_caches=self.gla.cache[i], slot_idx=self.slot_idx)
+                self.gla_fn(self.gq, self.gk, self.gv, self.gg, kv_caches=self.gla.cache[i], slot_idx=self.slot_idx,
+                            out=self.gla_out)
             if i < self.n_swa:   # odd layers are sliding-window layers
                 j = i & 1
                 if first_swa:
@@ -278,14 +286,69 @@ class DecodeEngine:
                     ops.kv_append(self.k[j][:0], self.v[j][:0], self.kv[i][0], self.kv[i][1], self.slots_d[:0],
                                   block_tables=self.table_d, seq_lens=self.lens_d, window_left=WINDOW_LEFT)
                     first_swa = False
+                ops.SWA_TIMING = timing
                 self.impls[i].forward(None, self.q[j], self.k[j], self.v[j], None, None, None, self.kv[i],
                                       meta, output=self.out)
+                ops.SWA_TIMING = None
 
+    def step(self, e2e=False):
+        """One decode step: the host decides slots / lengths / new blocks and uploads them, then
+        the step's kernels run -- replayed from a captured CUDA graph once `capture()` was called,
+        launched one by one before that."""
+        meta, meta_bytes = self._advance_metadata()
+        if e2e:
+            self.h2d_bytes += meta_bytes
+            if self.graph_e2e is not None:
+                self.graph_e2e.replay()
+                self.h2d_bytes += self.e2e_in_bytes
+                self.d2h_bytes += self.e2e_out_bytes
+                self.torch.cuda.current_stream().synchronize()
+            else:
+                self._enqueue_e2e(meta)
+                self._e2e.done.synchronize()
+            # either way the caller now holds every layer output of the step on the host
+        elif self.graph is not None:
+            self.graph.replay()
+        else:
+            self.enqueue_layers(meta)
+
+    def capture(self, e2e=False):
+        """Capture the kernels (and, end to end, the host<->device copies) of one step into a CUDA
+        graph. The metadata tensors the graph reads (slots, lengths, block table) live at fixed
+        addresses and are refreshed by the host before every replay."""
+        torch, ops = self.torch, self.ops
+        meta, _ = self._advance_metadata()      # the capture reads the metadata tensors in place
+        side = torch.cuda.Stream(device=self.device)
+        side.wait_stream(torch.cuda.current_stream())
+        g = torch.cuda.CUDAGraph()
+        launches0 = ops.LAUNCHES
+        with torch.cuda.stream(side):
+            if e2e:
+                self._e2e_setup()
+                self._enqueue_e2e(meta)             # warm-up of the multi-stream pattern on the side stream
+                side.wait_event(self._e2e.done)
+                self.h2d_bytes = self.d2h_bytes = 0
+                with torch.cuda.graph(g, stream=side):
+                    self._enqueue_e2e(meta)
+                self.e2e_in_bytes, self.e2e_out_bytes = self.h2d_bytes, self.d2h_bytes
+                self.graph_e2e = g
+            else:
+                self.enqueue_layers(meta)
+                launches0 = ops.LAUNCHES
+                self.swa_events = []
+                with torch.cuda.graph(g, stream=side):
+                    self.enqueue_layers(meta, timing=self.swa_events)
+                self.launches_per_step = ops.LAUNCHES - launches0
+                self.graph = g
+        torch.cuda.current_stream().wait_stream(side)
+        torch.cuda.synchronize()
+
+    # ------------------------------------------------------------------- end-to-end step
     def _e2e_setup(self):
         """Double-buffered device inputs/outputs, one stream per copy direction, and the events
         that order them against the compute stream."""
         torch = self.torch
-        if hasattr(self, "_e2e"):
+        if self._e2e is not None:
             return self._e2e
         dev = self.device
         ev = lambda: torch.cuda.Event()
@@ -298,26 +361,24 @@ class DecodeEngine:
         st.in_ready = {k: [ev(), ev()] for k in "gs"}     # recorded on h2d: inputs of slot landed
         st.in_free = {k: [ev(), ev()] for k in "gs"}      # recorded on compute: slot consumed
         st.out_ready, st.out_free = [ev(), ev()], [ev(), ev()]
+        st.done = ev()
+        self._e2e = st
+        return st
+
+    def _enqueue_e2e(self, meta):
+        """One step as a caller with HOST buffers sees it: every layer's inputs travel from pinned
+        host memory (H2D stream, a layer ahead of the math), every layer's output travels back
+        (D2H stream); `done` fires when the last output is on the host."""
+        torch, ops = self.torch, self.ops
+        st = self._e2e_setup()
         cur = torch.cuda.current_stream()
-        for k in "gs":
+        first_swa = True
+        for k in "gs":                      # every buffer starts the step free
             for e in st.in_free[k]:
                 e.record(cur)
         for e in st.out_free:
             e.record(cur)
-        st.n = 0
-        self._e2e = st
-        return st
-
-    def _step_e2e(self):
-        """One step as a caller with HOST buffers sees it: every layer's inputs travel from pinned
-        host memory (H2D stream, one layer ahead of the math), every layer's output travels
-        back (D2H stream), and the step ends when the last output is on the host."""
-        torch, ops = self.torch, self.ops
-        st = self._e2e_setup()
-        cur = torch.cuda.current_stream()
-        meta, meta_bytes = self._advance_metadata()
-        self.h2d_bytes += meta_bytes
-        first_swa = True
+        n_out = 0
 
         def upload(kind, slot, pairs):
             st.h2d.wait_event(st.in_free[kind][slot])
@@ -333,7 +394,6 @@ class DecodeEngine:
             st.d2h.wait_event(st.out_ready[oslot])
             with torch.cuda.stream(st.d2h):
                 st.h_out[oslot].copy_(o, non_blocking=True)
-            o.record_stream(st.d2h)
             st.out_free[oslot].record(st.d2h)
             self.d2h_bytes += o.numel() * o.element_size()
 
@@ -342,10 +402,12 @@ class DecodeEngine:
             if i < self.n_gla:
                 gi = st.g_in[slot]
                 upload("g", slot, zip(gi, (self.h_gq, self.h_gk, self.h_gv, self.h_gg)))
-                o = self.gla_fn(gi[0], gi[1], gi[2], gi[3], kv_caches=self.gla.cache[i], slot_idx=self.slot_idx)
+                oslot = n_out & 1; n_out += 1
+                cur.wait_event(st.out_free[oslot])      # its previous content is on the host
+                self.gla_fn(gi[0], gi[1], gi[2], gi[3], kv_caches=self.gla.cache[i], slot_idx=self.slot_idx,
+                            out=st.out[oslot])
                 st.in_free["g"][slot].record(cur)
-                oslot = st.n & 1; st.n += 1
-                download(o, oslot)
+                download(st.out[oslot], oslot)
             if i < self.n_swa:
                 q, k, v = st.s_in[slot]
                 upload("s", slot, zip((q, k, v), (self.h_q, self.h_k, self.h_v)))
@@ -353,12 +415,14 @@ class DecodeEngine:
                     ops.kv_append(k[:0], v[:0], self.kv[i][0], self.kv[i][1], self.slots_d[:0],
                                   block_tables=self.table_d, seq_lens=self.lens_d, window_left=WINDOW_LEFT)
                     first_swa = False
-                oslot = st.n & 1; st.n += 1
-                cur.wait_event(st.out_free[oslot])      # its previous content is on the host
+                oslot = n_out & 1; n_out += 1
+                cur.wait_event(st.out_free[oslot])
                 self.impls[i].forward(None, q, k, v, None, None, None, self.kv[i], meta, output=st.out[oslot])
                 st.in_free["s"][slot].record(cur)
                 download(st.out[oslot], oslot)
-        st.d2h.synchronize()   # the caller now holds every layer output of the step
+        cur.wait_stream(st.h2d)             # join both copy streams (needed when this is captured)
+        cur.wait_stream(st.d2h)
+        st.done.record(cur)
 
 
 # ------------------------------------------------------------------- multi-rank plumbing
@@ -417,13 +481,22 @@ def run_b200(args):
             dist.barrier()
         torch.cuda.synchronize()
 
-    def timed(n_steps, e2e):
+    swa_ms = []
+
+    def harvest():
+        """Durations of the sliding-window decode launches of the step that just ran."""
+        torch.cuda.synchronize()
+        swa_ms.extend(a.elapsed_time(b) for a, b in eng.swa_events)
+
+    def timed(n_steps, e2e, sample_every=0):
         barrier()
         e0 = torch.cuda.Event(enable_timing=True); e1 = torch.cuda.Event(enable_timing=True)
         t0 = time.perf_counter()
         e0.record()
-        for _ in range(n_steps):
+        for i in range(n_steps):
             eng.step(e2e=e2e)
+            if sample_every and (i + 1) % sample_every == 0:
+                harvest()
         e1.record()
         torch.cuda.synchronize()
         wall = (time.perf_counter() - t0) * 1e3
@@ -440,20 +513,32 @@ def run_b200(args):
         sampler.start()   # sampling starts with the warm-up: the tool needs a moment to come up
     for _ in range(max(args.warmup, 3)):
         eng.step()
-    launches0 = ops.LAUNCHES
-    ops.SWA_TIMING = []
-    total_ms = timed(args.steps, e2e=False)
-    swa_pairs = ops.SWA_TIMING
-    ops.SWA_TIMING = None
-    launches = ops.LAUNCHES - launches0
+    if args.no_graph:
+        launches0 = ops.LAUNCHES
+        timing = []
+        _orig = eng.enqueue_layers
+        eng.enqueue_layers = lambda meta, timing=timing: _orig(meta, timing=timing)
+        total_ms = timed(args.steps, e2e=False)
+        torch.cuda.synchronize()
+        swa_ms.extend(a.elapsed_time(b) for a, b in timing)
+        launches = ops.LAUNCHES - launches0
+        eng.enqueue_layers = _orig
+    else:
+        eng.capture()
+        eng.step()
+        # every 10th step the launch timings of that replay are read back (one host sync each)
+        total_ms = timed(args.steps, e2e=False, sample_every=10)
+        launches = eng.launches_per_step * args.steps
     clocks = sampler.stop() if rank == 0 else None
     ms_per_step = total_ms / args.steps
-    swa_ms = [a.elapsed_time(b) for a, b in swa_pairs]
 
     # ---- end to end: host buffers in, host result out, every step ----
     e2e_obj = None
     if not args.no_e2e:
         for _ in range(3):
+            eng.step(e2e=True)
+        if not args.no_graph:
+            eng.capture(e2e=True)
             eng.step(e2e=True)
         eng.h2d_bytes = eng.d2h_bytes = 0
         e2e_ms = timed(args.steps, e2e=True) / args.steps
@@ -486,6 +571,7 @@ def run_b200(args):
                                f"{args.gla_layers} GLA layers, batch {args.batch} per GPU, ctx {args.ctx}, "
                                f"window_left {WINDOW_LEFT}, block {BLOCK}, 28/4 heads, head_dim 128",
                    "parallelism": f"sequence-sharded x{world}, no collective",
+                   "launch": "host launches" if args.no_graph else "CUDA graph replay of the step's kernels; metadata refreshed by the host",
                    "l2": "working set (KV pools + GLA state, tens of GB) far exceeds the 126 MB L2; no flush needed"},
         "cache_gbs": world * step_bytes / (ms_per_step * 1e-3) / 1e9,
         "cache_gbs_per_gpu": step_bytes / (ms_per_step * 1e-3) / 1e9,

@@ -95,10 +95,12 @@ def my_fused_recurrent_gla(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, g:
                            kv_caches: torch.Tensor = None, slot_idx: torch.Tensor = None,
                            scale: Optional[float] = None, initial_state: torch.Tensor = None,
                            output_final_state: bool = False, reverse: bool = False,
-                           status: Optional[torch.Tensor] = None) -> torch.Tensor:
+                           status: Optional[torch.Tensor] = None,
+                           out: Optional[torch.Tensor] = None) -> torch.Tensor:
     """Single-token GLA decode, in place on ``kv_caches`` [slots, H, D, D] (float32).
     q [B, H, 1, D]; k, v, g [B, H, 1, D] or, un-repeated, [B, Hkv, 1, D]; returns o [B, H, D]
-    in q's dtype. Rows whose slot is -1 are left alone and their output row is unspecified."""
+    in q's dtype (written into ``out`` [B, H, D] when given, e.g. a static buffer of a captured
+    graph). Rows whose slot is -1 are left alone and their output row is unspecified."""
     if q.dim() != 4 or q.shape[2] != 1:
         raise ValueError("q must be [B, H, 1, D] (one token per sequence)")
     if initial_state is not None or output_final_state or reverse:
@@ -109,4 +111,4 @@ def my_fused_recurrent_gla(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, g:
     sq = lambda t: t.reshape(B, t.shape[1], D).contiguous()
     if slot_idx is not None and slot_idx.dtype != torch.int64:
         slot_idx = slot_idx.to(torch.int64)
-    return ops.gla_step(sq(q), sq(k), sq(v), sq(g), kv_caches, slot_idx, scale=scale, status=status)
+    return ops.gla_step(sq(q), sq(k), sq(v), sq(g), kv_caches, slot_idx, scale=scale, out=out, status=status)

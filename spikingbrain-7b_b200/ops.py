@@ -191,8 +191,10 @@ def swa_decode(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor,
         scale = d ** -0.5
     timing = SWA_TIMING
     if timing is not None:
-        ev0 = torch.cuda.Event(enable_timing=True)
-        ev1 = torch.cuda.Event(enable_timing=True)
+        # external: inside a stream capture these become event-record nodes of the graph, so
+        # the pair times the launch of the latest replay
+        ev0 = torch.cuda.Event(enable_timing=True, external=True)
+        ev1 = torch.cuda.Event(enable_timing=True, external=True)
         ev0.record()
     rc = _abi.lib.sbk_swa_decode(
         _ptr(q), q.stride(0) if B else H * d, _ptr(k_cache), _ptr(v_cache), _ptr(block_tables),
