@@ -11,6 +11,8 @@ It executes, on the CPU,
     on top of that Cache                                                      -> swa_sdpa.npz
   * the Triton kernel of vllm_hymeta/model_for_7B/my_fused_recurrent.py under
     TRITON_INTERPRET=1 (fp32 inputs: the interpreter has no bf16)             -> gla_triton.npz
+  * hf_7B_model GLAswaForCausalLM, two layers, prompt + 32 greedy steps (three third-party
+    GPU-only ops swapped for PyTorch, see config1_hf_model)                   -> config1_hf.npz
 The fixtures are what the oracle (oracle/ref_ops.py) and the CUDA kernels are pinned to;
 the tests never import the reference.
 """
@@ -204,7 +206,110 @@ def gla_triton():
     print("gla_triton.npz", {k: v.shape for k, v in out.items() if k.endswith("state2")})
 
 
+# ------------------------------------------------------- 4. the two-layer HF model (configs[0])
+def config1_hf_model():
+    """The reference GLAswaForCausalLM (2 layers: GLA then sliding window, hidden 512, 8/2 heads,
+    head_dim 64, window 64, fp32) run on the CPU: batch 2, a 128-token prompt of uniform random ids
+    over a 32k vocabulary, 32 greedy steps. Three GPU-only third-party pieces are swapped for PyTorch
+    equivalents (nothing of the reference itself is changed):
+      fla RMSNorm                  -> rms_norm_ref, the reference's own definition (hf_7B_model/layernorm.py:39-52)
+      fla fused_recurrent/chunk GLA -> the recurrence in a loop (fp32, head-first layout, scale D^-1/2)
+      flash_attn varlen + pad_input -> softmax attention with the same bottom-right causal window (W, 0)
+    Weights are overwritten parameter by parameter with tests.helpers.det_param so that the GPU-side
+    harness can rebuild them."""
+    sys.path.insert(0, os.path.dirname(os.path.dirname(HERE)))
+    from tests.helpers import det_param
+    for k in [k for k in sys.modules if k.startswith("hf_7B_model")]:
+        del sys.modules[k]
+    sys.path.insert(0, REF)
+    import hf_7B_model.modeling_gla_swa as M
+    import hf_7B_model.gla_attention as GA
+    import hf_7B_model.window_attention as WA
+    from hf_7B_model.layernorm import rms_norm_ref
+    from hf_7B_model.configuration_gla_swa import GLAswaConfig
+
+    class TorchRMSNorm(torch.nn.Module):
+        def __init__(self, hidden_size, elementwise_affine=True, eps=1e-5):
+            super().__init__()
+            self.weight = torch.nn.Parameter(torch.ones(hidden_size))
+            self.eps = eps
+
+        def forward(self, x, residual=None, prenorm=False, residual_in_fp32=False):
+            return rms_norm_ref(x, self.weight, None, residual=residual, eps=self.eps, prenorm=prenorm)
+
+    def torch_gla(q, k, v, gk, initial_state=None, output_final_state=False, scale=None, **kw):
+        B, H, T, D = q.shape
+        S = torch.zeros(B, H, D, v.shape[-1]) if initial_state is None else initial_state.float().clone()
+        scale = D ** -0.5 if scale is None else scale
+        out = []
+        for t in range(T):
+            S = torch.exp(gk[:, :, t].float())[..., None] * S + k[:, :, t].float()[..., None] * v[:, :, t].float()[..., None, :]
+            out.append(torch.einsum("bhk,bhkv->bhv", q[:, :, t].float() * scale, S))
+        return torch.stack(out, 2).to(q.dtype), (S if output_final_state else None)
+
+    def varlen_attn(q, k, v, cu_seqlens_q, cu_seqlens_k, max_seqlen_q, max_seqlen_k, dropout_p=0.0,
+                    softmax_scale=None, causal=True, window_size=(-1, -1)):
+        outs = []
+        for b in range(len(cu_seqlens_q) - 1):
+            qb = q[cu_seqlens_q[b]:cu_seqlens_q[b + 1]].transpose(0, 1)
+            kb = k[cu_seqlens_k[b]:cu_seqlens_k[b + 1]].transpose(0, 1)
+            vb = v[cu_seqlens_k[b]:cu_seqlens_k[b + 1]].transpose(0, 1)
+            sq, sk = qb.shape[1], kb.shape[1]
+            qi = torch.arange(sq)[:, None] + (sk - sq)
+            kj = torch.arange(sk)[None, :]
+            mask = (kj <= qi + window_size[1]) & (kj >= qi - window_size[0])
+            s = (qb @ kb.transpose(1, 2)) * softmax_scale
+            outs.append((torch.softmax(s.masked_fill(~mask, float("-inf")), -1) @ vb).transpose(0, 1))
+        return torch.cat(outs, 0)
+
+    def pad_input(x, indices, batch, seqlen):
+        out = torch.zeros(batch * seqlen, *x.shape[1:], dtype=x.dtype)
+        out[indices] = x
+        return out.view(batch, seqlen, *x.shape[1:])
+
+    M.RMSNorm = GA.RMSNorm = TorchRMSNorm
+    GA.fused_recurrent_gla = GA.chunk_gla = GA.fused_chunk_gla = torch_gla
+    WA.flash_attn_varlen_func, WA.pad_input, WA.unpad_input = varlen_attn, pad_input, None
+
+    torch.manual_seed(0)
+    cfg = GLAswaConfig(vocab_size=32000, hidden_size=512, num_hidden_layers=2, num_attention_heads=8,
+                       num_key_value_heads=2, sliding_window=64, intermediate_size=1024, fuse_cross_entropy=False)
+    model = M.GLAswaForCausalLM(cfg).eval()
+    names_shapes = []
+    with torch.no_grad():
+        for name, p in model.named_parameters():
+            p.copy_(det_param(name, p.shape))
+            names_shapes.append((name, tuple(p.shape)))
+    ids = torch.randint(0, 32000, (2, 128))
+    probe = torch.arange(0, 32000, 500)          # 64 vocabulary entries whose logits are recorded
+    logits_probe, tokens, seen = [], [], []
+    cache = None
+    cur = ids
+    with torch.no_grad():
+        for step in range(33):
+            out = model(input_ids=cur, past_key_values=cache, use_cache=True)
+            cache = out.past_key_values
+            last = out.logits[:, -1]
+            logits_probe.append(last[:, probe])
+            nxt = last.argmax(-1)
+            tokens.append(nxt)
+            seen.append([cache.get_seq_length(0), cache.get_seq_length(1), cache[1]["attn_state"][0].shape[-2]])
+            cur = nxt[:, None]
+    assert type(cache).__module__ == "hf_7B_model.cache"
+    res = {
+        "input_ids": ids.numpy(), "probe": probe.numpy(), "logits_probe": torch.stack(logits_probe).numpy(),
+        "tokens": torch.stack(tokens, 1).numpy(), "seen": np.array(seen, dtype=np.int64),
+        "final_k": cache[1]["attn_state"][0].numpy(), "final_v": cache[1]["attn_state"][1].numpy(),
+        "final_state": cache[0]["recurrent_state"].numpy(),
+        "param_names": np.array([n for n, _ in names_shapes]),
+        "param_shapes": np.array([",".join(map(str, s)) for _, s in names_shapes]),
+    }
+    np.savez_compressed(os.path.join(HERE, "config1_hf.npz"), **res)
+    print("config1_hf.npz tokens", res["tokens"][:, :8].tolist(), "seen", seen[0], seen[-1])
+
+
 if __name__ == "__main__":
+    config1_hf_model()
     cache_streams()
     swa_sdpa()
     gla_triton()

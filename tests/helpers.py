@@ -49,3 +49,16 @@ def rel_err(a: torch.Tensor, b: torch.Tensor) -> float:
 def mean_rel(a: torch.Tensor, b: torch.Tensor) -> float:
     """sum |a-b| / sum |b|."""
     return float((a.double() - b.double()).abs().sum() / b.double().abs().sum().clamp_min(1e-30))
+
+
+# --------------------------------------------------------------- deterministic weights
+def det_param(name: str, shape) -> torch.Tensor:
+    """Weights of the two-layer plumbing model, rebuilt identically wherever they are needed:
+    one seeded CPU generator per parameter name. Norm weights sit around 1, everything else is
+    N(0, 0.05) (biases included, so that they matter)."""
+    import zlib
+    g = torch.Generator().manual_seed(zlib.crc32(name.encode()) & 0x7FFFFFFF)
+    t = torch.randn(tuple(shape), generator=g)
+    if name.endswith("norm.weight"):
+        return 1.0 + 0.1 * t
+    return 0.05 * t
