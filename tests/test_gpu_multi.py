@@ -1,0 +1,86 @@
+"""GPU, two ranks over NCCL: the head-sharded decode step. Each rank holds half of the kv heads
+(its slice of the paged K/V pool) and half of the query heads (its slice of the GLA state), runs the
+same kernels on its slice, and the head outputs are all-gathered. Skipped on a box with one GPU."""
+import os
+import socket
+import subprocess
+import sys
+import textwrap
+
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+WORKER = textwrap.dedent("""
+    import os, sys, math, json
+    sys.path.insert(0, {root!r})
+    import torch
+    import torch.distributed as dist
+    from oracle import ref_ops
+    from tests.helpers import make_paged_kv, mean_rel, rel_err
+    from spikingbrain_7b_b200 import ops
+    from spikingbrain_7b_b200.head_shard import all_gather_heads, shard_heads
+
+    rank, world = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"])
+    torch.cuda.set_device(rank)
+    dev = torch.device("cuda", rank)
+    dist.init_process_group("nccl", device_id=dev)
+    H, KVH, D, bs, wl = 28, 4, 128, 16, 1023
+    lens = [1500, 17, 1024, 1025, 300, 64]
+    B = len(lens)
+    # the same global problem on every rank (seeded), of which a rank keeps its head slice
+    kv, table, nb = make_paged_kv(lens, wl, KVH, D, bs, seed=50)
+    g = torch.Generator().manual_seed(51)
+    q = (torch.randn(B, H, D, generator=g) / math.sqrt(D)).bfloat16()
+    gq = torch.relu(torch.randn(B, H, D, generator=g) / math.sqrt(D)).bfloat16()
+    gk = torch.relu(torch.randn(B, KVH, D, generator=g) / math.sqrt(D)).bfloat16()
+    gv = (torch.randn(B, KVH, D, generator=g) / math.sqrt(D)).bfloat16()
+    gg = (torch.nn.functional.logsigmoid(torch.randn(B, KVH, D, generator=g)) / 16).bfloat16()
+    state = torch.randn(B, H, D, D, generator=g)
+    qh, kh = shard_heads(H, KVH, world, rank)
+    kv_l = kv[:, :, :, kh.start:kh.stop].contiguous().to(dev)        # [2, NB, bs, kvh/tp, D]
+    lens_d = torch.tensor(lens, dtype=torch.int32, device=dev)
+    o_l = ops.swa_decode(q[:, qh.start:qh.stop].contiguous().to(dev), kv_l[0], kv_l[1], table.to(dev), lens_d,
+                         window_left=wl)
+    o = all_gather_heads(o_l)
+    state_l = state[:, qh.start:qh.stop].contiguous().to(dev)
+    go_l = ops.gla_step(gq[:, qh.start:qh.stop].contiguous().to(dev), gk[:, kh.start:kh.stop].contiguous().to(dev),
+                        gv[:, kh.start:kh.stop].contiguous().to(dev), gg[:, kh.start:kh.stop].contiguous().to(dev),
+                        state_l, out_dtype=torch.float32)
+    go = all_gather_heads(go_l)
+    torch.cuda.synchronize()
+    ref = ref_ops.swa_paged_decode_ref(q, kv[0], kv[1], table, lens, wl, D ** -0.5).bfloat16().float()
+    ref_state = state.clone()
+    gref = ref_ops.gla_step_ref(gq, gk, gv, gg, ref_state)
+    a = o.float().cpu()
+    assert a.shape == (B, H, D)
+    assert float((a - ref).abs().max()) <= 2e-2 and mean_rel(a, ref) <= 1e-3      # every rank holds all heads
+    assert rel_err(go.cpu(), gref) <= 1e-4
+    assert rel_err(state_l.cpu(), ref_state[:, qh.start:qh.stop]) <= 1e-4
+    dist.barrier()
+    if rank == 0:
+        print(json.dumps({{"ok": True}}))
+    dist.destroy_process_group()
+""")
+
+
+def test_head_sharded_decode_two_ranks_nccl(sb, tmp_path):
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs two GPUs")
+    script = tmp_path / "worker.py"
+    script.write_text(WORKER.format(root=ROOT))
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        port = s.getsockname()[1]
+    procs = []
+    for rank in range(2):
+        env = dict(os.environ, RANK=str(rank), LOCAL_RANK=str(rank), WORLD_SIZE="2", MASTER_ADDR="127.0.0.1",
+                   MASTER_PORT=str(port))
+        procs.append(subprocess.Popen([sys.executable, str(script)], env=env, stdout=subprocess.PIPE,
+                                      stderr=subprocess.PIPE, text=True))
+    outs = [p.communicate(timeout=600) for p in procs]
+    for p, (out, err) in zip(procs, outs):
+        assert p.returncode == 0, err[-3000:]
+    assert '"ok": true' in outs[0][0]

@@ -39,6 +39,13 @@ WORKER = textwrap.dedent("""
     ms = bench.max_over_ranks(5.0 + 2.0 * rank, "cpu")
     assert ms == 7.0
     assert bench.job_tokens_per_s(256, world, ms) == 2 * 256 / 7.0e-3
+    # head-sharded gather: rank r contributes heads [r*Hl, (r+1)*Hl) of every token
+    from spikingbrain_7b_b200.head_shard import all_gather_heads, shard_heads
+    full = torch.arange(5 * 8 * 4, dtype=torch.float32).view(5, 8, 4)
+    qh, kvh = shard_heads(8, 2, world, rank)
+    assert (list(qh), list(kvh)) == ([4 * rank + i for i in range(4)], [rank])
+    got = all_gather_heads(full[:, qh.start:qh.stop].contiguous())
+    assert torch.equal(got, full)
     dist.barrier()
     if rank == 0:
         print(json.dumps({{"ok": True, "ms": ms}}))
@@ -87,3 +94,16 @@ def test_cache_byte_model_matches_the_shapes():
     assert gla == 256 * 2 * 28 * 128 * 128 * 4          # state read + written
     assert total == 14 * (swa + gla) == 43232788480
     assert bench.cache_bytes_per_step(2, 100, 1, 0)[0] == 2 * (100 * 2048 + 2048)
+
+
+def test_head_shard_rules_follow_the_reference():
+    import pytest
+    from spikingbrain_7b_b200.head_shard import shard_heads
+    assert [list(shard_heads(28, 4, 4, r)[0])[0] for r in range(4)] == [0, 7, 14, 21]
+    assert [list(shard_heads(28, 4, 4, r)[1]) for r in range(4)] == [[0], [1], [2], [3]]
+    assert list(shard_heads(28, 4, 2, 1)[1]) == [2, 3] and len(shard_heads(28, 4, 2, 1)[0]) == 14
+    assert [list(shard_heads(28, 4, 28, r)[1]) for r in (0, 6, 7, 27)] == [[0], [0], [1], [3]]   # kv heads replicated
+    with pytest.raises(ValueError):
+        shard_heads(28, 4, 8, 0)          # 28 query heads do not split eight ways: the reference rejects it too
+    with pytest.raises(ValueError):
+        shard_heads(24, 4, 6, 0)
