@@ -178,6 +178,27 @@ int sbk_gla_step(const void* q, const void* k, const void* v, const void* g, int
                  int B, int H, int Hkv, int D, float scale,
                  void* out, int out_dtype, int32_t* status, void* stream);
 
+/*
+ * GLA scan over a run of tokens per sequence with state carry (prefill and chunked prefill):
+ * for each sequence the state is read once, advanced token by token exactly as sbk_gla_step
+ * would, and written back once. Stands in for the per-sequence loop of
+ * GatedLinearAttention._prefill_and_mix_infer (vllm_hymeta/model_for_7B/gla_attention.py:179-211:
+ * fused_chunk_gla with initial_state from the slot, then the copy back into the slot) and for
+ * chunk_gla / fused_chunk_gla as called at hf_7B_model/gla_attention.py:155-157.
+ *
+ *  q            [T, H, D] token-major; k,v,g [T, Hkv, D]; tokens of sequence s are rows
+ *               query_start_loc[s] .. query_start_loc[s+1]-1   (query_start_loc: [n_seqs+1] int32)
+ *  state        [num_slots, H, D, D] float32; slot_idx [n_seqs] int64 (NULL: slot s; -1: skip)
+ *  reset        [n_seqs] uint8 or NULL: non-zero = start this sequence from a zero state (a new
+ *               prompt; the reference clears such slots in GLAswaModel._clear_prefill_cache,
+ *               modeling_gla_swa.py:391-414) instead of reading the slot
+ *  out          [T, H, D] of out_dtype
+ */
+int sbk_gla_scan(const void* q, const void* k, const void* v, const void* g, int in_dtype,
+                 const int32_t* query_start_loc, int n_seqs, float* state, int64_t num_slots,
+                 const int64_t* slot_idx, const uint8_t* reset, int H, int Hkv, int D, float scale,
+                 void* out, int out_dtype, int32_t* status, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

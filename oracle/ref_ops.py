@@ -208,6 +208,26 @@ def gla_step_ref(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, g: torch.Ten
     return out
 
 
+def gla_scan_ref(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, g: torch.Tensor, state: torch.Tensor,
+                 query_start_loc: List[int], slot_idx: Optional[List[int]] = None,
+                 reset: Optional[List[bool]] = None, scale: Optional[float] = None) -> torch.Tensor:
+    """Runs of tokens through the recurrence with state carry: the per-sequence prefill loop of
+    vllm_hymeta/model_for_7B/gla_attention.py:179-211 (fused_chunk_gla with initial_state from the
+    slot, final state copied back), restated as gla_step_ref applied token after token.
+    q [T, H, D], k/v/g [T, Hkv, D] token-major -> [T, H, D] fp32; `state` advanced in place."""
+    out = torch.zeros(q.shape, dtype=torch.float32)
+    for s in range(len(query_start_loc) - 1):
+        slot = s if slot_idx is None else int(slot_idx[s])
+        if slot < 0:
+            continue
+        if reset is not None and reset[s]:
+            state[slot] = 0
+        for t in range(query_start_loc[s], query_start_loc[s + 1]):
+            out[t] = gla_step_ref(q[t:t + 1], k[t:t + 1], v[t:t + 1], g[t:t + 1], state,
+                                  torch.tensor([slot]), scale=scale)[0]
+    return out
+
+
 def gla_prepare_inputs(q_proj: torch.Tensor, k_proj: torch.Tensor, gk_proj: torch.Tensor,
                        normalizer: float = 16.0):
     """Input preparation of hf_7B_model/gla_attention.py:134-145: ReLU feature map on q and k,

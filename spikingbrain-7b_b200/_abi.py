@@ -33,6 +33,9 @@ SIGNATURES = {
         c_void_p, c_int64, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_int,
         c_int, c_int64, c_int, c_int64, c_int, c_float, c_void_p, c_int, c_int64, c_void_p,
         c_void_p, c_size_t, c_int, c_int, c_void_p, c_void_p]),
+    "sbk_gla_scan": (c_int, [
+        c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int, c_void_p, c_int64, c_void_p,
+        c_void_p, c_int, c_int, c_int, c_float, c_void_p, c_int, c_void_p, c_void_p]),
     "sbk_swa_static_scratch_bytes": (c_size_t, []),
     "sbk_swa_decode_static": (c_int, [
         c_void_p, c_int64, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_int,

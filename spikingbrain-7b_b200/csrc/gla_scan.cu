@@ -1,0 +1,172 @@
+// GLA scan over a run of tokens per sequence (prefill / chunked prefill), carrying the fp32
+// state: the multi-token form of gla_step.cu. For every sequence s with tokens [t0, t1):
+//     S <- state[slot[s]]  (or zero when reset[s])
+//     for t in t0..t1-1:   S <- diag(exp(g_t)) . S + k_t^T v_t ;   o_t = (q_t * scale) . S
+//     state[slot[s]] <- S
+// One CTA of 256 threads per (sequence, head). The 64 KiB state tile lives in REGISTERS for the
+// whole run (thread = float4 of v columns x 16 k rows), so it crosses HBM twice per chunk instead
+// of twice per token; per token only the four 128-vectors q, k, g, v are read and o written.
+// Tokens are staged four at a time through shared memory; the read-out's sum over k rows is
+// finished across the 8 row groups once per four tokens.
+#include <math.h>
+
+#include "sbk_common.cuh"
+
+namespace sbk {
+
+template <typename T>
+__device__ __forceinline__ float scan_to_f32(T x);
+template <>
+__device__ __forceinline__ float scan_to_f32<float>(float x) { return x; }
+template <>
+__device__ __forceinline__ float scan_to_f32<__nv_bfloat16>(__nv_bfloat16 x) { return __bfloat162float(x); }
+template <typename T>
+__device__ __forceinline__ T scan_from_f32(float x);
+template <>
+__device__ __forceinline__ float scan_from_f32<float>(float x) { return x; }
+template <>
+__device__ __forceinline__ __nv_bfloat16 scan_from_f32<__nv_bfloat16>(float x) { return __float2bfloat16_rn(x); }
+
+constexpr int kScanTokens = 4;   // tokens staged per round
+
+template <typename T, typename TO, int D>
+__global__ void __launch_bounds__(256)
+gla_scan_kernel(const T* __restrict__ q, const T* __restrict__ k, const T* __restrict__ v,
+                const T* __restrict__ g, const int32_t* __restrict__ query_start_loc,
+                float* __restrict__ state, int64_t num_slots, const int64_t* __restrict__ slot_idx,
+                const uint8_t* __restrict__ reset, int H, int Hkv, float scale, TO* __restrict__ out,
+                int32_t* status) {
+  constexpr int TPR = D / 4;          // threads per state row
+  constexpr int GROUPS = 256 / TPR;   // row groups
+  constexpr int RPT = D / GROUPS;     // rows per thread
+  const int h = blockIdx.x;
+  const int s = blockIdx.y;
+  const int t0 = query_start_loc[s], t1 = query_start_loc[s + 1];
+  const int64_t slot = slot_idx ? slot_idx[s] : (int64_t)s;
+  if (slot < 0 || t1 <= t0) return;
+  if (slot >= num_slots) {
+    if (threadIdx.x == 0) raise_status(status, SBK_ST_BAD_SLOT);
+    return;
+  }
+  const int hk = h / (H / Hkv);
+  const int tid = threadIdx.x;
+  const int c4 = tid % TPR, r0 = tid / TPR;
+
+  __shared__ float s_q[kScanTokens][D], s_k[kScanTokens][D], s_d[kScanTokens][D];
+  __shared__ float4 s_v[kScanTokens][TPR];
+  __shared__ float4 s_o[kScanTokens][GROUPS][TPR];
+
+  float4* tile = reinterpret_cast<float4*>(state + ((slot * H + h) * (int64_t)D) * D);
+  float4 S[RPT];
+  if (reset && reset[s]) {
+#pragma unroll
+    for (int i = 0; i < RPT; ++i) S[i] = make_float4(0.f, 0.f, 0.f, 0.f);
+  } else {
+#pragma unroll
+    for (int i = 0; i < RPT; ++i) S[i] = ld_stream_f4(tile + (int64_t)(r0 + i * GROUPS) * TPR + c4);
+  }
+
+  for (int tb = t0; tb < t1; tb += kScanTokens) {
+    const int nt = t1 - tb < kScanTokens ? t1 - tb : kScanTokens;
+    // ---- stage q*scale, k, exp(g), v of up to four tokens ----
+    for (int idx = tid; idx < nt * D; idx += 256) {
+      const int tt = idx / D, d = idx - tt * D;
+      const int64_t tok = tb + tt;
+      s_q[tt][d] = scan_to_f32(q[(tok * H + h) * D + d]) * scale;
+      const int64_t kv_off = (tok * Hkv + hk) * D + d;
+      s_k[tt][d] = scan_to_f32(k[kv_off]);
+      s_d[tt][d] = expf(scan_to_f32(g[kv_off]));
+      reinterpret_cast<float*>(&s_v[tt][0])[d] = scan_to_f32(v[kv_off]);
+    }
+    __syncthreads();
+    for (int tt = 0; tt < nt; ++tt) {
+      const float4 vv = s_v[tt][c4];
+      float4 o = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+      for (int i = 0; i < RPT; ++i) {
+        const int r = r0 + i * GROUPS;
+        const float d = s_d[tt][r], kk = s_k[tt][r], qq = s_q[tt][r];
+        S[i].x = fmaf(d, S[i].x, kk * vv.x);
+        S[i].y = fmaf(d, S[i].y, kk * vv.y);
+        S[i].z = fmaf(d, S[i].z, kk * vv.z);
+        S[i].w = fmaf(d, S[i].w, kk * vv.w);
+        o.x = fmaf(qq, S[i].x, o.x);
+        o.y = fmaf(qq, S[i].y, o.y);
+        o.z = fmaf(qq, S[i].z, o.z);
+        o.w = fmaf(qq, S[i].w, o.w);
+      }
+      s_o[tt][r0][c4] = o;
+    }
+    __syncthreads();
+    // ---- finish the read-out: sum the row groups, one output element per thread and trip ----
+    for (int idx = tid; idx < nt * D; idx += 256) {
+      const int tt = idx / D, d = idx - tt * D;
+      const float* so = reinterpret_cast<const float*>(&s_o[tt][0][0]);
+      float acc = 0.f;
+#pragma unroll
+      for (int gi = 0; gi < GROUPS; ++gi) acc += so[gi * D + d];
+      out[((int64_t)(tb + tt) * H + h) * D + d] = scan_from_f32<TO>(acc);
+    }
+    // the next round's staging only touches s_q/s_k/s_d/s_v, and its first barrier orders the
+    // reads of s_o above before the next writes to s_o
+  }
+#pragma unroll
+  for (int i = 0; i < RPT; ++i) st_stream_f4(tile + (int64_t)(r0 + i * GROUPS) * TPR + c4, S[i]);
+}
+
+}  // namespace sbk
+
+extern "C" int sbk_gla_scan(const void* q, const void* k, const void* v, const void* g, int in_dtype,
+                            const int32_t* query_start_loc, int n_seqs, float* state,
+                            int64_t num_slots, const int64_t* slot_idx, const uint8_t* reset, int H,
+                            int Hkv, int D, float scale, void* out, int out_dtype, int32_t* status,
+                            void* stream) {
+  using namespace sbk;
+  if (n_seqs < 0 || H <= 0 || Hkv <= 0 || H % Hkv != 0 || num_slots < 0) {
+    set_error("sbk_gla_scan: bad head counts H=%d Hkv=%d or negative size", H, Hkv);
+    return SBK_E_ARG;
+  }
+  if (D != 64 && D != 128) {
+    set_error("sbk_gla_scan: D=%d unsupported (64 or 128)", D);
+    return SBK_E_ARG;
+  }
+  if ((in_dtype != SBK_BF16 && in_dtype != SBK_F32) || (out_dtype != SBK_BF16 && out_dtype != SBK_F32)) {
+    set_error("sbk_gla_scan: in_dtype=%d / out_dtype=%d unsupported", in_dtype, out_dtype);
+    return SBK_E_ARG;
+  }
+  if (n_seqs == 0) return SBK_OK;
+  if (!q || !k || !v || !g || !state || !out || !query_start_loc) {
+    set_error("sbk_gla_scan: null pointer");
+    return SBK_E_ARG;
+  }
+  if (!aligned16(state)) {
+    set_error("sbk_gla_scan: state must be 16-byte aligned");
+    return SBK_E_ALIGN;
+  }
+  if (n_seqs > 65535) {
+    set_error("sbk_gla_scan: n_seqs=%d exceeds 65535", n_seqs);
+    return SBK_E_ARG;
+  }
+  dim3 grid(H, n_seqs);
+  cudaStream_t st = (cudaStream_t)stream;
+#define SBK_SCAN_LAUNCH(T, TO, DD)                                                              \
+  gla_scan_kernel<T, TO, DD><<<grid, 256, 0, st>>>((const T*)q, (const T*)k, (const T*)v,       \
+                                                   (const T*)g, query_start_loc, state,         \
+                                                   num_slots, slot_idx, reset, H, Hkv, scale,   \
+                                                   (TO*)out, status)
+#define SBK_SCAN_D(T, TO)                     \
+  do {                                        \
+    if (D == 128) SBK_SCAN_LAUNCH(T, TO, 128); \
+    else SBK_SCAN_LAUNCH(T, TO, 64);          \
+  } while (0)
+  if (in_dtype == SBK_BF16) {
+    if (out_dtype == SBK_BF16) SBK_SCAN_D(__nv_bfloat16, __nv_bfloat16);
+    else SBK_SCAN_D(__nv_bfloat16, float);
+  } else {
+    if (out_dtype == SBK_BF16) SBK_SCAN_D(float, __nv_bfloat16);
+    else SBK_SCAN_D(float, float);
+  }
+#undef SBK_SCAN_D
+#undef SBK_SCAN_LAUNCH
+  return check_launch("sbk_gla_scan");
+}

@@ -112,3 +112,23 @@ def my_fused_recurrent_gla(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, g:
     if slot_idx is not None and slot_idx.dtype != torch.int64:
         slot_idx = slot_idx.to(torch.int64)
     return ops.gla_step(sq(q), sq(k), sq(v), sq(g), kv_caches, slot_idx, scale=scale, out=out, status=status)
+
+
+def gla_prefill_scan(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, g: torch.Tensor,
+                     kv_caches: torch.Tensor, slot_idx: torch.Tensor, query_start_loc: torch.Tensor,
+                     context_lens: Optional[torch.Tensor] = None, scale: Optional[float] = None,
+                     status: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """The prefill half of GatedLinearAttention._prefill_and_mix_infer
+    (vllm_hymeta/model_for_7B/gla_attention.py:179-211) in one launch for all prompt sequences:
+    q [T, H, D], k/v/g [T, H or Hkv, D] are the prompt tokens of `len(slot_idx)` sequences laid
+    end to end (`query_start_loc`); each sequence's state slot is advanced over its tokens and the
+    outputs [T, H, D] returned. A sequence whose `context_lens` entry is 0 is a new prompt and
+    starts from a zero state whatever its slot holds (the reference zeroes such slots beforehand,
+    modeling_gla_swa.py:391-414, and treats NaN-filled slots as empty, gla_attention.py:196-198)."""
+    reset = None
+    if context_lens is not None:
+        reset = (context_lens == 0).to(torch.uint8)
+    if slot_idx.dtype != torch.int64:
+        slot_idx = slot_idx.to(torch.int64)
+    return ops.gla_scan(q.contiguous(), k.contiguous(), v.contiguous(), g.contiguous(), kv_caches,
+                        query_start_loc.to(torch.int32), slot_idx, reset, scale=scale, status=status)

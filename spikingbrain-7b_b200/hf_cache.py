@@ -264,3 +264,20 @@ class Cache(transformers.cache_utils.Cache):
         o = ops.gla_step(q, k, v, g, S, scale=scale)
         self.update(recurrent_state=S, layer_idx=layer_idx, offset=1)
         return o
+
+    def gla_chunk(self, q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, g: torch.Tensor,
+                  layer_idx: int, scale: Optional[float] = None) -> torch.Tensor:
+        """A run of T tokens through the GLA layer `layer_idx` with state carry: what
+        `chunk_gla(q, k, v, g, initial_state=S, output_final_state=True)` followed by
+        `update(recurrent_state=S', layer_idx, offset=T)` does in hf_7B_model/gla_attention.py:155-168.
+        q [B, H, T, D] (the reference's head-first layout), k/v/g [B, H or Hkv, T, D];
+        returns o [B, H, T, D]. The state tensor of the layer is advanced in place."""
+        B, H, T, D = q.shape
+        tm = lambda t: t.transpose(1, 2).reshape(B * T, t.shape[1], D).contiguous()   # token-major rows
+        S = self[layer_idx]["recurrent_state"] if layer_idx < len(self) else None
+        if S is None:
+            S = torch.zeros(B, H, D, D, dtype=torch.float32, device=q.device)
+        qsl = torch.arange(B + 1, dtype=torch.int32, device=q.device) * T
+        o = ops.gla_scan(tm(q), tm(k), tm(v), tm(g), S, qsl, scale=scale)
+        self.update(recurrent_state=S, layer_idx=layer_idx, offset=T)
+        return o.view(B, T, H, D).transpose(1, 2)

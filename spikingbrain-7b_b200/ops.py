@@ -248,3 +248,52 @@ def gla_step(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, g: torch.Tensor,
     global LAUNCHES
     LAUNCHES += 1 if B else 0
     return out
+
+
+def gla_scan(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, g: torch.Tensor, state: torch.Tensor,
+             query_start_loc: torch.Tensor, slot_idx: Optional[torch.Tensor] = None,
+             reset: Optional[torch.Tensor] = None, *, scale: Optional[float] = None,
+             out: Optional[torch.Tensor] = None, out_dtype: Optional[torch.dtype] = None,
+             status: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """GLA over runs of tokens with state carry. q [T, H, D], k/v/g [T, Hkv, D] token-major;
+    sequence s owns rows query_start_loc[s]:query_start_loc[s+1]; ``state`` [slots, H, D, D] fp32 is
+    advanced in place; ``reset`` [n_seqs] uint8/bool marks sequences that start from zero."""
+    _need_cuda(q, k, v, g, state, query_start_loc, slot_idx, reset, out, status)
+    if q.dim() != 3 or k.dim() != 3:
+        raise ValueError("q must be [T, H, D] and k, v, g [T, Hkv, D]")
+    T, H, D = q.shape
+    Hkv = k.shape[1]
+    if k.shape != (T, Hkv, D) or v.shape != k.shape or g.shape != k.shape:
+        raise ValueError("k, v, g must share the shape [T, Hkv, D]")
+    if q.dtype not in _DTYPE_CODE or any(t.dtype != q.dtype for t in (k, v, g)):
+        raise ValueError("q, k, v, g must share one dtype (bf16 or fp32)")
+    if not all(t.is_contiguous() for t in (q, k, v, g)):
+        raise ValueError("q, k, v, g must be contiguous")
+    if state.dtype != torch.float32 or state.dim() != 4 or state.shape[1:] != (H, D, D) or not state.is_contiguous():
+        raise ValueError(f"state must be contiguous fp32 [slots, {H}, {D}, {D}]")
+    if query_start_loc.dtype != torch.int32 or query_start_loc.dim() != 1 or not query_start_loc.is_contiguous():
+        raise ValueError("query_start_loc must be contiguous int32 [n_seqs + 1]")
+    n_seqs = query_start_loc.numel() - 1
+    if slot_idx is not None and (slot_idx.dtype != torch.int64 or slot_idx.numel() != n_seqs or not slot_idx.is_contiguous()):
+        raise ValueError("slot_idx must be contiguous int64 [n_seqs]")
+    if slot_idx is None and state.shape[0] < n_seqs:
+        raise ValueError("state has fewer slots than sequences")
+    if reset is not None:
+        if reset.dtype == torch.bool:
+            reset = reset.to(torch.uint8)
+        if reset.dtype != torch.uint8 or reset.numel() != n_seqs or not reset.is_contiguous():
+            raise ValueError("reset must be contiguous uint8/bool [n_seqs]")
+    if out is None:
+        out = torch.empty((T, H, D), dtype=out_dtype or q.dtype, device=q.device)
+    elif out.shape != (T, H, D) or not out.is_contiguous() or out.dtype not in _DTYPE_CODE:
+        raise ValueError("out must be contiguous [T, H, D] bf16 or fp32")
+    if scale is None:
+        scale = D ** -0.5
+    rc = _abi.lib.sbk_gla_scan(
+        _ptr(q), _ptr(k), _ptr(v), _ptr(g), _DTYPE_CODE[q.dtype], _ptr(query_start_loc), n_seqs,
+        _ptr(state), state.shape[0], _ptr(slot_idx), _ptr(reset), H, Hkv, D, float(scale), _ptr(out),
+        _DTYPE_CODE[out.dtype], _ptr(status), _stream())
+    _abi.check("sbk_gla_scan", rc)
+    global LAUNCHES
+    LAUNCHES += 1 if n_seqs else 0
+    return out

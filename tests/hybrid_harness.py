@@ -51,9 +51,13 @@ class HybridHarness:
                 v = self.lin(h, pre + "attn.v_proj").view(B, T, KVH, D)
                 gk = self.lin(self.lin(h, pre + "attn.gk_proj.0"), pre + "attn.gk_proj.1").view(B, T, KVH, D)
                 g = F.logsigmoid(gk) / 16
-                outs = [cache.gla_step(q[:, t].contiguous(), k[:, t].contiguous(), v[:, t].contiguous(),
-                                       g[:, t].contiguous(), i) for t in range(T)]
-                o = torch.stack(outs, 1)                       # [B, T, H, D]
+                if T > 1 and hasattr(cache, "gla_chunk"):      # a prompt: one scan with state carry
+                    o = cache.gla_chunk(q.transpose(1, 2), k.transpose(1, 2), v.transpose(1, 2), g.transpose(1, 2),
+                                        i).transpose(1, 2)
+                else:
+                    outs = [cache.gla_step(q[:, t].contiguous(), k[:, t].contiguous(), v[:, t].contiguous(),
+                                           g[:, t].contiguous(), i) for t in range(T)]
+                    o = torch.stack(outs, 1)                   # [B, T, H, D]
                 o = rms(o, self.p[pre + "attn.g_norm.weight"], self.gla_eps).reshape(B, T, H * D)
             else:                                              # sliding-window attention
                 q = self.rope(self.lin(h, pre + "attn.q_proj").view(B, T, H, D).transpose(1, 2), pos)

@@ -305,6 +305,69 @@ def test_gla_step_config2_shapes(ops):
     assert rel_err(out.cpu(), ref_out) <= GLA_REL
 
 
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float32])
+@pytest.mark.parametrize("H,Hkv,D", [(28, 4, 128), (8, 2, 64), (7, 7, 128)])
+def test_gla_scan_matches_oracle_on_ragged_runs(ops, dtype, H, Hkv, D):
+    """Several sequences of different lengths (one empty, one with slot -1, one restarted from
+    zero) scanned in one launch: outputs and final states equal the token-by-token oracle."""
+    runs = [5, 0, 37, 1, 64, 9]
+    qsl = [0]
+    for n in runs:
+        qsl.append(qsl[-1] + n)
+    T, n_seqs = qsl[-1], len(runs)
+    g = torch.Generator().manual_seed(30)
+    q = torch.relu(torch.randn(T, H, D, generator=g) / math.sqrt(D)).to(dtype)
+    k = torch.relu(torch.randn(T, Hkv, D, generator=g) / math.sqrt(D)).to(dtype)
+    v = (torch.randn(T, Hkv, D, generator=g) / math.sqrt(D)).to(dtype)
+    gk = (torch.nn.functional.logsigmoid(torch.randn(T, Hkv, D, generator=g)) / 16).to(dtype)
+    slots = n_seqs + 2
+    state = torch.randn(slots, H, D, D, generator=g)
+    slot_idx = torch.randperm(slots, generator=g)[:n_seqs].to(torch.int64)
+    slot_idx[3] = -1
+    reset = [False, False, True, False, False, True]
+    ref_state = state.clone()
+    ref = ref_ops.gla_scan_ref(q, k, v, gk, ref_state, qsl, slot_idx.tolist(), reset)
+    state_d = state.to(DEV)
+    st = _status()
+    out = ops.gla_scan(q.to(DEV), k.to(DEV), v.to(DEV), gk.to(DEV), state_d,
+                       torch.tensor(qsl, dtype=torch.int32, device=DEV), slot_idx.to(DEV),
+                       torch.tensor(reset, device=DEV), out_dtype=torch.float32, status=st)
+    assert st.item() == 0
+    live = torch.ones(T, dtype=torch.bool)
+    live[qsl[3]:qsl[4]] = False
+    assert rel_err(out.cpu()[live], ref[live]) <= GLA_REL
+    assert rel_err(state_d.cpu(), ref_state) <= GLA_REL
+    untouched = [s for s in range(slots) if s not in slot_idx.tolist()] + [int(slot_idx[1])]
+    assert torch.equal(state_d[untouched].cpu(), state[untouched])
+
+
+def test_gla_scan_equals_chained_steps_and_chunking_is_invisible(ops):
+    """One scan over 48 tokens == three scans over 16 == 48 single-token steps of sbk_gla_step."""
+    B, T, H, Hkv, D = 2, 48, 28, 4, 128
+    g = torch.Generator().manual_seed(31)
+    mk = lambda h, relu=False: ((torch.relu if relu else (lambda x: x))(torch.randn(B, T, h, D, generator=g) / math.sqrt(D))).bfloat16().to(DEV)
+    q, k, v = mk(H, True), mk(Hkv, True), mk(Hkv)
+    gk = (torch.nn.functional.logsigmoid(torch.randn(B, T, Hkv, D, generator=g)) / 16).bfloat16().to(DEV)
+    flat = lambda t: t.reshape(B * T, t.shape[2], D)
+    s_all = torch.zeros(B, H, D, D, device=DEV)
+    o_all = ops.gla_scan(flat(q), flat(k), flat(v), flat(gk), s_all,
+                         torch.tensor([0, T, 2 * T], dtype=torch.int32, device=DEV), out_dtype=torch.float32)
+    s_chunks = torch.zeros_like(s_all)
+    s_steps = torch.zeros_like(s_all)
+    o_chunks, o_steps = [], []
+    for c in range(0, T, 16):
+        sl = lambda t: t[:, c:c + 16].reshape(B * 16, t.shape[2], D).contiguous()
+        o_chunks.append(ops.gla_scan(sl(q), sl(k), sl(v), sl(gk), s_chunks,
+                                     torch.tensor([0, 16, 32], dtype=torch.int32, device=DEV),
+                                     out_dtype=torch.float32).view(B, 16, H, D))
+    for t in range(T):
+        o_steps.append(ops.gla_step(q[:, t].contiguous(), k[:, t].contiguous(), v[:, t].contiguous(),
+                                    gk[:, t].contiguous(), s_steps, out_dtype=torch.float32))
+    o_all = o_all.view(B, T, H, D)
+    assert torch.equal(torch.cat(o_chunks, 1), o_all) and torch.equal(s_chunks, s_all)      # same arithmetic, same bits
+    assert rel_err(torch.stack(o_steps, 1), o_all) <= 1e-6 and rel_err(s_steps, s_all) <= 1e-6
+
+
 # ---------------------------------------------------------------------- argument errors
 def test_argument_errors_are_reported(ops):
     from spikingbrain_7b_b200._abi import SbkError

@@ -114,12 +114,20 @@ def test_gla_state_carried_across_chunks_equals_single_scan(sb):
     gk = (torch.nn.functional.logsigmoid(torch.randn(B, T, KVH, D, generator=g)) / 16).bfloat16()
     ref_state = torch.zeros(B, H, D, D)
     ref_out = [ref_ops.gla_step_ref(q[:, t], k[:, t], v[:, t], gk[:, t], ref_state) for t in range(T)]
+    from spikingbrain_7b_b200.gla_slots import gla_prefill_scan
     outs = []
     for c0 in range(0, T, chunk):
         cache, idx = mgr.current_run_tensors({f"req{b}": [0] for b in range(B)})   # same slots every chunk
-        for t in range(c0, c0 + chunk):
-            dv = lambda x: x[:, t].unsqueeze(2).to(DEV)
-            outs.append(my_fused_recurrent_gla(dv(q), dv(k), dv(v), dv(gk), kv_caches=cache[0], slot_idx=idx).float().cpu())
+        if c0 == 0:        # first chunk token by token (the decode op), later chunks as scans
+            for t in range(c0, c0 + chunk):
+                dv = lambda x: x[:, t].unsqueeze(2).to(DEV)
+                outs.append(my_fused_recurrent_gla(dv(q), dv(k), dv(v), dv(gk), kv_caches=cache[0], slot_idx=idx).float().cpu())
+        else:
+            fl = lambda x: x[:, c0:c0 + chunk].reshape(B * chunk, x.shape[2], D).contiguous().to(DEV)
+            qsl = torch.arange(B + 1, dtype=torch.int32, device=DEV) * chunk
+            o = gla_prefill_scan(fl(q), fl(k), fl(v), fl(gk), cache[0], idx, qsl,
+                                 context_lens=torch.full((B,), c0, dtype=torch.int32, device=DEV))
+            outs.extend(o.view(B, chunk, H, D).float().cpu().unbind(1))
     state = mgr.cache[0][idx.cpu()].cpu()
     assert float((state - ref_state).abs().max() / ref_state.abs().max()) <= 1e-4
     for t in (0, 31, 32, 95):

@@ -161,6 +161,35 @@ def test_my_fused_recurrent_gla_matches_reference_kernel(pkg, name):
     assert torch.equal(state[untouched].cpu(), state0[untouched])
 
 
+def test_gla_prefill_scan_matches_reference_kernel_chain(pkg):
+    """The reference kernel applied twice to the same token == one scan over that token laid down
+    twice; a sequence with context_len 0 starts from zero whatever its slot holds."""
+    from spikingbrain_7b_b200.gla_slots import gla_prefill_scan
+    gold = np.load(os.path.join(GOLD, "gla_triton.npz"))
+    name = "f32_d128"
+    B, H, D, slots, _ = gold[name + "/meta"].tolist()
+    q, k, v, g = (torch.from_numpy(gold[f"{name}/{n}"]) for n in "qkvg")          # [B, H, D]
+    slot = torch.from_numpy(gold[name + "/slot"])
+    live = [b for b in range(B) if slot[b] >= 0]
+    twice = lambda t: torch.stack([t[live], t[live]], 1).reshape(2 * len(live), H, D).to(DEV)   # sequence-major
+    state = golden_state(slots, H, D).to(DEV)
+    qsl = torch.arange(len(live) + 1, dtype=torch.int32, device=DEV) * 2
+    o = gla_prefill_scan(twice(q), twice(k), twice(v), twice(g), state, slot[live].to(DEV), qsl,
+                         context_lens=torch.ones(len(live), dtype=torch.int32, device=DEV)).view(len(live), 2, H, D).cpu()
+    assert rel_err(o[:, 0], torch.from_numpy(gold[name + "/out1"])[live]) <= 1e-4
+    assert rel_err(o[:, 1], torch.from_numpy(gold[name + "/out2"])[live]) <= 1e-4
+    assert rel_err(state.cpu(), torch.from_numpy(gold[name + "/state2"])) <= 1e-4
+    # a new prompt (context_len 0) on a dirty slot
+    state2 = torch.full((1, H, D, D), float("nan"), device=DEV)
+    o2 = gla_prefill_scan(twice(q)[:2], twice(k)[:2], twice(v)[:2], twice(g)[:2], state2,
+                          torch.zeros(1, dtype=torch.int64, device=DEV), qsl[:2],
+                          context_lens=torch.zeros(1, dtype=torch.int32, device=DEV))
+    ref_state = torch.zeros(1, H, D, D)
+    ref = ref_ops.gla_scan_ref(twice(q)[:2].cpu(), twice(k)[:2].cpu(), twice(v)[:2].cpu(), twice(g)[:2].cpu(),
+                               ref_state, [0, 2])
+    assert torch.isfinite(state2).all() and rel_err(o2.cpu(), ref) <= 1e-4 and rel_err(state2.cpu(), ref_state) <= 1e-4
+
+
 # ------------------------------------------------------------------------------- backend
 def _decode_meta(Meta, slots, lens, table):
     return Meta(num_prefills=0, num_prefill_tokens=0, num_decode_tokens=len(lens), slot_mapping=slots,
