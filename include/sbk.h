@@ -179,6 +179,29 @@ int sbk_gla_step(const void* q, const void* k, const void* v, const void* g, int
                  void* out, int out_dtype, int32_t* status, void* stream);
 
 /*
+ * Sliding-window attention for runs of query tokens over the paged cache (prefill with block
+ * tables, chunked prefill). Stands in for metatoken_flash_attn_varlen_func(..., causal=True,
+ * window_size=(window_left, 0), block_tables=prefill_meta.block_tables) as called at
+ * vllm_hymeta/attention/meta_attention.py:900-919 (-> flash-attn _flash_attn_varlen_forward,
+ * fa_kernel_metatoken.py:235-253) with key2 == None. The K/V of the new tokens must already be in
+ * the cache. Query i of sequence s sits at position context_lens[s] + i and sees keys
+ * [position - window_left, position] (window_left -1: all keys up to itself).
+ *
+ *  q            [T, H, D] bf16 token-major, `q_tok_stride` elements between tokens; sequence s owns
+ *               rows query_start_loc[s] .. query_start_loc[s+1]-1 (int32 [n_seqs+1])
+ *  context_lens [n_seqs] int32 tokens of the sequence that were in the cache before this call
+ *  max_query_len  longest run of this call (host value; sizes the grid)
+ *  out          [T, H, D] bf16, `out_tok_stride` elements between tokens
+ * Supported: D == 128, H % kvh == 0, H/kvh <= 8, block_size % 16 == 0.
+ */
+int sbk_swa_prefill(const void* q, int64_t q_tok_stride, const void* k_cache, const void* v_cache,
+                    const int32_t* block_tables, int max_blocks, const int32_t* query_start_loc,
+                    const int32_t* context_lens, int n_seqs, int max_query_len, int H, int kvh, int D,
+                    int64_t num_blocks, int block_size, int64_t cache_block_stride_bytes,
+                    int window_left, float scale, void* out, int64_t out_tok_stride,
+                    int32_t* status, void* stream);
+
+/*
  * GLA scan over a run of tokens per sequence with state carry (prefill and chunked prefill):
  * for each sequence the state is read once, advanced token by token exactly as sbk_gla_step
  * would, and written back once. Stands in for the per-sequence loop of

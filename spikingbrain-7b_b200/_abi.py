@@ -33,6 +33,10 @@ SIGNATURES = {
         c_void_p, c_int64, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_int,
         c_int, c_int64, c_int, c_int64, c_int, c_float, c_void_p, c_int, c_int64, c_void_p,
         c_void_p, c_size_t, c_int, c_int, c_void_p, c_void_p]),
+    "sbk_swa_prefill": (c_int, [
+        c_void_p, c_int64, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_int, c_int,
+        c_int, c_int, c_int, c_int64, c_int, c_int64, c_int, c_float, c_void_p, c_int64, c_void_p,
+        c_void_p]),
     "sbk_gla_scan": (c_int, [
         c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int, c_void_p, c_int64, c_void_p,
         c_void_p, c_int, c_int, c_int, c_float, c_void_p, c_int, c_void_p, c_void_p]),

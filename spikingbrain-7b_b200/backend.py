@@ -9,9 +9,8 @@ helpers) are restated here from their documented behaviour.
 What runs where
   cache write         -> sbk_kv_append   (reference: reshape_and_cache_flash, :790-799)
   one-token decode    -> sbk_swa_decode  (reference: flash-attn fwd_kvcache, :955-981)
-  prefill with tables -> the same decode kernel, one query per prompt token (each token
-                         sees [pos - window_left, pos] through its sequence's table);
-                         correct for chunked prefill, not yet a dedicated kernel
+  prefill with tables -> sbk_swa_prefill (reference: flash-attn varlen forward with block
+                         tables, :900-919): 16 query tokens x one kv group per CTA
   prefill without block tables (the profile run / un-paged prompt), multi-token
   "varlen" decode, meta tokens (key2/value2), fp8 KV, ALiBi, soft-cap, encoder and
   cross attention                        -> NotImplementedError, never a fallback.
@@ -482,15 +481,18 @@ class MetaAttentionImpl:
                     "prefill over K/V that is not reachable through block tables (profile run or "
                     "un-chunked first prompt) has no kernel on this path; schedule prompts with "
                     "chunked prefill so that their block tables are passed")
-            # every prompt token is a decode query at its own position over its sequence's table
-            n = prefill_meta.num_prefills
-            qsl = prefill_meta.query_start_loc.long()
-            seq_of_tok = torch.repeat_interleave(torch.arange(n, device=query.device),
-                                                 qsl[1:] - qsl[:-1], output_size=num_prefill_tokens)
-            tok = torch.arange(num_prefill_tokens, device=query.device)
-            lens = (prefill_meta.context_lens_tensor.long()[seq_of_tok] + (tok - qsl[seq_of_tok]) + 1).int()
-            tables = prefill_meta.block_tables[seq_of_tok].contiguous()
-            self._decode(prefill_query, kv_cache, tables, lens, window_left, out3[:num_prefill_tokens])
+            # windowed attention of the prompt tokens over the paged cache (their own K/V included:
+            # the append above has run), 16 queries and one kv group per CTA
+            pq = prefill_query if prefill_query.stride()[1:] == (D, 1) else prefill_query.contiguous()
+            po = out3[:num_prefill_tokens]
+            tmp = po if po.stride()[1:] == (D, 1) else torch.empty_like(po, memory_format=torch.contiguous_format)
+            ops.swa_prefill(pq, kv_cache[0], kv_cache[1], prefill_meta.block_tables.contiguous(),
+                            prefill_meta.query_start_loc.to(torch.int32).contiguous(),
+                            prefill_meta.context_lens_tensor.to(torch.int32).contiguous(),
+                            prefill_meta.max_query_len, window_left=window_left, scale=self.scale, out=tmp,
+                            status=self._status)
+            if tmp is not po:
+                po.copy_(tmp)
 
         if decode_meta := attn_metadata.decode_metadata:
             if decode_meta.max_decode_query_len is not None and decode_meta.max_decode_query_len > 1:

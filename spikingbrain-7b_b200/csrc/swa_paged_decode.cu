@@ -31,11 +31,8 @@
 //   the CTA that completes the last piece of a sequence (a counter per sequence) folds them
 //   and writes the output, so there is no second kernel. A single piece writes `out` directly.
 // HBM-bound: min(seq_len, window_left+1) * kvh*128*2*2 bytes read per sequence.
-#include <cuda.h>
-
-#include <mutex>
-
 #include "sbk_common.cuh"
+#include "sbk_tma.cuh"
 
 namespace sbk {
 
@@ -99,16 +96,6 @@ struct Cfg {
   static_assert(kVOffset == 16384, "a stage holds 16 KiB of K and 16 KiB of V");
   static_assert(kSmemBytes <= 115200, "two CTAs must fit one SM");
 };
-
-// 4-D tensor copy global -> shared (TMA), completion in bytes on an mbarrier
-__device__ __forceinline__ void tma_load_4d(uint32_t dst, const CUtensorMap* map, int c0, int c1, int c2, int c3,
-                                            uint32_t bar) {
-  asm volatile(
-      "cp.async.bulk.tensor.4d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4, %5}], [%6];" ::
-          "r"(dst),
-      "l"(reinterpret_cast<uint64_t>(map)), "r"(c0), "r"(c1), "r"(c2), "r"(c3), "r"(bar)
-      : "memory");
-}
 
 template <typename TO>
 __device__ __forceinline__ void store_out(TO* p, float x);
@@ -581,86 +568,6 @@ swa_decode_kernel(const Params P, const __grid_constant__ CUtensorMap map_k,
   }
 }
 
-// ---- tensor maps ------------------------------------------------------------------------
-typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
-                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*,
-                                  CUtensorMapInterleave, CUtensorMapSwizzle, CUtensorMapL2promotion,
-                                  CUtensorMapFloatOOBfill);
-
-static EncodeTiledFn encode_fn() {
-  static EncodeTiledFn fn = nullptr;
-  if (!fn) {
-    void* p = nullptr;
-    cudaDriverEntryPointQueryResult q;
-    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
-        q == cudaDriverEntryPointSuccess)
-      fn = reinterpret_cast<EncodeTiledFn>(p);
-  }
-  return fn;
-}
-
-// A cache [num_blocks][block][kvh][128] bf16 seen as 64-element (128-byte) rows.
-//   tile_copy: dims (64, token in block, 128-byte row of a token, block) -- the token stride (kvh*256)
-//              comes BEFORE the row stride (128), so a box of (64,16,2kvh,1) lands as [row][token];
-//   row-wise : dims (64, 128-byte row, token in block, block), box (64,1,16,1).
-static bool encode_map(CUtensorMap* m, const void* base, int kvh, int64_t num_blocks, int block_size,
-                       int64_t block_stride, bool tile_copy) {
-  EncodeTiledFn fn = encode_fn();
-  if (!fn) return false;
-  const cuuint64_t row_bytes = (cuuint64_t)kvh * 256;
-  cuuint64_t dim[4], stride[3];
-  cuuint32_t box[4], estr[4] = {1, 1, 1, 1};
-  dim[0] = 64; dim[3] = (cuuint64_t)num_blocks;
-  stride[2] = (cuuint64_t)block_stride;
-  if (tile_copy) {
-    dim[1] = (cuuint64_t)block_size; dim[2] = 2 * kvh;
-    stride[0] = row_bytes; stride[1] = 128;
-    box[0] = 64; box[1] = 16; box[2] = 2 * kvh; box[3] = 1;
-  } else {
-    dim[1] = 2 * kvh; dim[2] = (cuuint64_t)block_size;
-    stride[0] = 128; stride[1] = row_bytes;
-    box[0] = 64; box[1] = 1; box[2] = 16; box[3] = 1;
-  }
-  return fn(m, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 4, const_cast<void*>(base), dim, stride, box, estr,
-            CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
-            CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
-}
-
-struct MapKey {
-  const void* base; int kvh; int64_t num_blocks; int block_size; int64_t block_stride;
-  bool operator==(const MapKey& o) const {
-    return base == o.base && kvh == o.kvh && num_blocks == o.num_blocks && block_size == o.block_size &&
-           block_stride == o.block_stride;
-  }
-};
-
-// Small process-wide cache of encoded maps (one per cache tensor and geometry). A map holds
-// nothing but the address and the dimensions, so it stays valid as long as the geometry does.
-// Returns the copy mode in *tile_copy: the permuted-stride form is tried once per process.
-static int g_copy_mode = -1;   // -1 unknown, 1 tile copies, 0 row copies
-static bool get_map(CUtensorMap* out, const MapKey& key, int* tile_copy) {
-  static std::mutex mu;
-  int& mode = g_copy_mode;
-  constexpr int kSlots = 128;
-  static MapKey keys[kSlots];
-  static CUtensorMap maps[kSlots];
-  static int used = 0, next = 0;
-  std::lock_guard<std::mutex> lock(mu);
-  if (mode < 0) {
-    CUtensorMap probe;
-    mode = encode_map(&probe, key.base, key.kvh, key.num_blocks, key.block_size, key.block_stride, true) ? 1 : 0;
-  }
-  *tile_copy = mode;
-  for (int i = 0; i < used; ++i)
-    if (keys[i] == key) { *out = maps[i]; return true; }
-  CUtensorMap m;
-  if (!encode_map(&m, key.base, key.kvh, key.num_blocks, key.block_size, key.block_stride, mode == 1)) return false;
-  const int slot = used < kSlots ? used++ : (next++ % kSlots);
-  keys[slot] = key; maps[slot] = m;
-  *out = m;
-  return true;
-}
-
 template <int KVH, typename TO>
 int launch_swa(const Params& P0, int B_total, int n_ctas, const CUtensorMap& map_k, const CUtensorMap& map_v,
                cudaStream_t st) {
@@ -707,7 +614,7 @@ static size_t ctrl_bytes(int B) { return 16 + (size_t)((B + 3) / 4 * 4) * 4; }
 
 }  // namespace sbk
 
-extern "C" int sbk_swa_copy_mode(void) { return sbk::g_copy_mode; }
+extern "C" int sbk_swa_copy_mode(void) { return sbk::copy_mode(); }
 
 extern "C" size_t sbk_swa_workspace_bytes(int B, int H, int D, int max_pieces) {
   if (B <= 0 || H <= 0 || D <= 0 || max_pieces < 1) return 0;
@@ -798,8 +705,8 @@ extern "C" int sbk_swa_decode(const void* q, int64_t q_seq_stride, const void* k
   const int n_ctas = 2 * sms;
   CUtensorMap map_k, map_v;
   int tile_copy = 0;
-  if (!get_map(&map_k, MapKey{k_cache, kvh, num_blocks, block_size, cache_block_stride_bytes}, &tile_copy) ||
-      !get_map(&map_v, MapKey{v_cache, kvh, num_blocks, block_size, cache_block_stride_bytes}, &tile_copy)) {
+  if (!get_map(&map_k, MapKey{k_cache, kvh, num_blocks, block_size, cache_block_stride_bytes, 2 * kvh}, &tile_copy) ||
+      !get_map(&map_v, MapKey{v_cache, kvh, num_blocks, block_size, cache_block_stride_bytes, 2 * kvh}, &tile_copy)) {
     set_error("sbk_swa_decode: cuTensorMapEncodeTiled rejected the cache geometry (blocks=%lld block=%d kvh=%d)",
               (long long)num_blocks, block_size, kvh);
     return SBK_E_ARG;

@@ -297,3 +297,38 @@ def gla_scan(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, g: torch.Tensor,
     global LAUNCHES
     LAUNCHES += 1 if n_seqs else 0
     return out
+
+
+def swa_prefill(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, block_tables: torch.Tensor,
+                query_start_loc: torch.Tensor, context_lens: torch.Tensor, max_query_len: int, *,
+                window_left: int, scale: Optional[float] = None, out: Optional[torch.Tensor] = None,
+                status: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """Sliding-window attention of runs of query tokens (q [T, H, D] bf16, token-major) over the
+    paged cache, the runs' own K/V already appended. Sequence s owns rows
+    query_start_loc[s]:query_start_loc[s+1] and had context_lens[s] tokens cached before."""
+    _need_cuda(q, k_cache, v_cache, block_tables, query_start_loc, context_lens, out, status)
+    nb, bs, kvh, d, bstride = _cache_geometry(k_cache, v_cache)
+    if q.dim() != 3 or q.shape[2] != d or q.dtype != torch.bfloat16 or k_cache.dtype != torch.bfloat16:
+        raise ValueError("q must be bf16 [T, H, D] and the cache bf16")
+    T, H, _ = q.shape
+    if T and q.stride()[1:] != (d, 1):
+        raise ValueError("the heads of q must be contiguous")
+    n_seqs = block_tables.shape[0]
+    for t, n in ((block_tables, None), (query_start_loc, n_seqs + 1), (context_lens, n_seqs)):
+        if t.dtype != torch.int32 or not t.is_contiguous() or (n is not None and t.numel() != n):
+            raise ValueError("block_tables / query_start_loc / context_lens must be contiguous int32 of matching size")
+    if out is None:
+        out = torch.empty((T, H, d), dtype=torch.bfloat16, device=q.device)
+    elif out.shape != (T, H, d) or out.dtype != torch.bfloat16 or (T and out.stride()[1:] != (d, 1)):
+        raise ValueError("out must be bf16 [T, H, D] with contiguous heads")
+    if scale is None:
+        scale = d ** -0.5
+    rc = _abi.lib.sbk_swa_prefill(
+        _ptr(q), q.stride(0) if T else H * d, _ptr(k_cache), _ptr(v_cache), _ptr(block_tables),
+        block_tables.shape[1], _ptr(query_start_loc), _ptr(context_lens), n_seqs, int(max_query_len), H,
+        kvh, d, nb, bs, bstride, window_left, float(scale), _ptr(out), out.stride(0) if T else H * d,
+        _ptr(status), _stream())
+    _abi.check("sbk_swa_prefill", rc)
+    global LAUNCHES
+    LAUNCHES += 1 if (n_seqs and max_query_len) else 0
+    return out

@@ -244,6 +244,61 @@ def test_swa_decode_config2_shapes(ops):
     _check_attn(out, ref, lse, lse_ref)
 
 
+# --------------------------------------------------------------------- prefill attention
+def _prefill_case(ops, ctx, new, wl, H, kvh, bs, seed):
+    """Sequences with `ctx[s]` cached tokens get `new[s]` more: append, then windowed attention of
+    the new tokens; the oracle treats every new token as a one-token decode at its position."""
+    D = 128
+    B = len(ctx)
+    total = [c + n for c, n in zip(ctx, new)]
+    kv, table, nb = make_paged_kv(total, -1, kvh, D, bs, seed=seed)       # every token resident
+    g = torch.Generator().manual_seed(seed + 1)
+    T = sum(new)
+    q = (torch.randn(T, H, D, generator=g) / math.sqrt(D)).bfloat16()
+    qsl = [0]
+    for n in new:
+        qsl.append(qsl[-1] + n)
+    st = _status()
+    kv_d = kv.to(DEV)
+    out = ops.swa_prefill(q.to(DEV), kv_d[0], kv_d[1], table.to(DEV), torch.tensor(qsl, dtype=torch.int32, device=DEV),
+                          torch.tensor(ctx, dtype=torch.int32, device=DEV), max(new), window_left=wl, status=st)
+    torch.cuda.synchronize()
+    assert st.item() == 0
+    o = out.float().cpu()
+    assert torch.isfinite(o).all()
+    worst, num, den = 0.0, 0.0, 0.0
+    rng = torch.Generator().manual_seed(seed + 2)
+    for s in range(B):
+        picks = sorted(set([0, 1, 15, 16, 17, new[s] - 1] + torch.randint(0, new[s], (12,), generator=rng).tolist()))
+        for i in [p for p in picks if 0 <= p < new[s]]:
+            pos = ctx[s] + i
+            ref = ref_ops.swa_paged_decode_ref(q[qsl[s] + i][None], kv[0], kv[1], table[s:s + 1], [pos + 1], wl,
+                                               D ** -0.5)[0].bfloat16().float()
+            d = (o[qsl[s] + i] - ref).abs()
+            worst = max(worst, float(d.max())); num += float(d.sum()); den += float(ref.abs().sum())
+    assert worst <= ATTN_MAX_ABS and num / den <= ATTN_MEAN_REL, (worst, num / den)
+
+
+@pytest.mark.parametrize("ctx,new", [([0], [1]), ([0], [16]), ([0], [17]), ([5], [40]), ([0, 100, 33], [70, 3, 129])])
+def test_swa_prefill_small_edges(ops, ctx, new):
+    _prefill_case(ops, ctx, new, wl=63, H=28, kvh=4, bs=16, seed=60)
+
+
+@pytest.mark.parametrize("wl", [0, 15, 16, 255, 4096, -1])
+def test_swa_prefill_window_edges(ops, wl):
+    _prefill_case(ops, [300, 0, 1000], [200, 513, 64], wl=wl, H=28, kvh=4, bs=16, seed=61)
+
+
+@pytest.mark.parametrize("H,kvh,bs", [(7, 1, 16), (14, 2, 32), (32, 4, 64), (4, 4, 16), (16, 2, 128)])
+def test_swa_prefill_head_layouts_and_block_sizes(ops, H, kvh, bs):
+    _prefill_case(ops, [700, 0], [300, 260], wl=511, H=H, kvh=kvh, bs=bs, seed=62)
+
+
+def test_swa_prefill_long_chunk_at_model_shapes(ops):
+    """One 2048-token chunk on top of 6000 cached tokens, window 4096, 28/4 heads."""
+    _prefill_case(ops, [6000], [2048], wl=4096, H=28, kvh=4, bs=16, seed=63)
+
+
 # ------------------------------------------------------------------------------------ GLA
 def _gla_inputs(B, H, Hkv, D, dtype, seed):
     g = torch.Generator().manual_seed(seed)

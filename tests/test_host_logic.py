@@ -18,7 +18,7 @@ def test_library_exports_every_declared_symbol(sb):
     header = open(os.path.join(ROOT, "include", "sbk.h")).read()
     declared = set(re.findall(r"\b(sbk_[a-z_0-9]+)\s*\(", header))
     assert {"sbk_kv_append", "sbk_kv_gather", "sbk_swa_decode", "sbk_swa_workspace_bytes",
-            "sbk_gla_step", "sbk_gla_scan", "sbk_last_error", "sbk_abi_version", "sbk_swa_copy_mode"} <= declared
+            "sbk_gla_step", "sbk_gla_scan", "sbk_swa_prefill", "sbk_last_error", "sbk_abi_version", "sbk_swa_copy_mode"} <= declared
     lib = ctypes.CDLL(os.path.join(ROOT, "spikingbrain-7b_b200", "libsbk.so"))
     for name in declared:
         assert hasattr(lib, name), f"{name} declared in include/sbk.h but not exported"
