@@ -29,7 +29,7 @@
 extern "C" {
 #endif
 
-#define SBK_ABI_VERSION 1
+#define SBK_ABI_VERSION 2
 
 /* element type codes */
 #define SBK_BF16 0
@@ -116,6 +116,10 @@ int sbk_kv_gather(const void* k_cache, const void* v_cache, const int32_t* block
  *               given buffer and B, and every call that ends without SBK_ST_WAIT_TIMEOUT leaves
  *               them zero. Split-K partials follow. Calls that overlap on the GPU need
  *               separate workspaces.
+ *  key2,value2  [num_meta, kvh, D] bf16 contiguous "meta" (sink) tokens that every query sees on top of
+ *               its window -- the second attention pass over k2/v2 and the log-sum-exp merge of
+ *               fa_kernel_metatoken.py:124-194, done here as extra leading tiles of the same
+ *               softmax; num_meta a multiple of 16, 0 (with NULLs) for none
  *  split_chunks target number of 16-token chunks per split (<=0: library default)
  *  max_pieces   upper bound on splits per sequence (grid.x); >= 1
  * Supported: D == 128, H % kvh == 0, H/kvh <= 8, kvh in {1,2,4}, block_size % 16 == 0.
@@ -131,6 +135,7 @@ int sbk_swa_decode(const void* q, int64_t q_seq_stride, const void* k_cache, con
                    int64_t cache_block_stride_bytes, int window_left, float scale,
                    void* out, int out_dtype, int64_t out_seq_stride, float* lse_out,
                    void* workspace, size_t workspace_bytes, int split_chunks, int max_pieces,
+                   const void* key2, const void* value2, int num_meta,
                    int32_t* status, void* stream);
 
 /*
@@ -192,6 +197,8 @@ int sbk_gla_step(const void* q, const void* k, const void* v, const void* g, int
  *  context_lens [n_seqs] int32 tokens of the sequence that were in the cache before this call
  *  max_query_len  longest run of this call (host value; sizes the grid)
  *  out          [T, H, D] bf16, `out_tok_stride` elements between tokens
+ *  key2,value2,num_meta  sink tokens as in sbk_swa_decode (the k2/v2 pass of
+ *               fa_kernel_metatoken.py:198-280), or NULL, NULL, 0
  * Supported: D == 128, H % kvh == 0, H/kvh <= 8, block_size % 16 == 0.
  */
 int sbk_swa_prefill(const void* q, int64_t q_tok_stride, const void* k_cache, const void* v_cache,
@@ -199,6 +206,7 @@ int sbk_swa_prefill(const void* q, int64_t q_tok_stride, const void* k_cache, co
                     const int32_t* context_lens, int n_seqs, int max_query_len, int H, int kvh, int D,
                     int64_t num_blocks, int block_size, int64_t cache_block_stride_bytes,
                     int window_left, float scale, void* out, int64_t out_tok_stride,
+                    const void* key2, const void* value2, int num_meta,
                     int32_t* status, void* stream);
 
 /*

@@ -160,10 +160,12 @@ def swa_decode_ref(q: torch.Tensor, k_win: torch.Tensor, v_win: torch.Tensor, sc
 
 def swa_paged_decode_ref(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor,
                          block_tables: torch.Tensor, seq_lens: List[int], window_left: int,
-                         scale: float, return_lse: bool = False):
+                         scale: float, return_lse: bool = False, key2: Optional[torch.Tensor] = None,
+                         value2: Optional[torch.Tensor] = None):
     """The decode call of meta_attention.py:955-981 (flash_attn fwd_kvcache with causal=True,
     window (window_left, -1), fa_kernel_metatoken.py:84-105): per sequence gather the visible
-    tokens through the block table, then swa_decode_ref. q [B, H, D] -> [B, H, D] fp32."""
+    tokens through the block table, then swa_decode_ref. q [B, H, D] -> [B, H, D] fp32.
+    key2 / value2 [n_meta, kvh, D]: meta tokens of the 76B-style backend use (None for the 7B path)."""
     outs, lses = [], []
     for b, L in enumerate(seq_lens):
         if L <= 0:
@@ -171,6 +173,13 @@ def swa_paged_decode_ref(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.
             lses.append(torch.full((q.shape[1],), float("-inf")))
             continue
         k, v = window_gather(k_cache, v_cache, block_tables[b], L, window_left)
+        if key2 is not None:
+            # meta (sink) tokens: always visible, in front of the window -- the mask of
+            # vllm_hymeta/attention/fa_kernel_metatoken.py:390-391 and the key order of :397-398;
+            # the reference reaches the same softmax by a second pass over k2/v2 and a
+            # log-sum-exp merge (:157-192)
+            k = torch.cat([key2.transpose(0, 1), k], 1)
+            v = torch.cat([value2.transpose(0, 1), v], 1)
         o, lse = swa_decode_ref(q[b], k, v, scale, return_lse=True)
         outs.append(o)
         lses.append(lse)

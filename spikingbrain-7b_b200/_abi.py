@@ -14,7 +14,7 @@ LIB_PATH = os.environ.get("SBK_LIB_PATH") or os.path.join(PKG_DIR, "libsbk.so")
 SBK_BF16, SBK_F32 = 0, 1
 SBK_OK, SBK_E_ARG, SBK_E_ALIGN, SBK_E_WORKSPACE, SBK_E_LAUNCH = 0, -1, -2, -3, -4
 ST_BAD_SLOT, ST_BAD_BLOCK, ST_WAIT_TIMEOUT, ST_RETIRE_OVERFLOW = 1, 2, 4, 8
-ABI_VERSION = 1
+ABI_VERSION = 2
 
 # name -> (restype, argtypes); must list every function include/sbk.h declares
 SIGNATURES = {
@@ -32,11 +32,11 @@ SIGNATURES = {
     "sbk_swa_decode": (c_int, [
         c_void_p, c_int64, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_int,
         c_int, c_int64, c_int, c_int64, c_int, c_float, c_void_p, c_int, c_int64, c_void_p,
-        c_void_p, c_size_t, c_int, c_int, c_void_p, c_void_p]),
+        c_void_p, c_size_t, c_int, c_int, c_void_p, c_void_p, c_int, c_void_p, c_void_p]),
     "sbk_swa_prefill": (c_int, [
         c_void_p, c_int64, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_int, c_int,
         c_int, c_int, c_int, c_int64, c_int, c_int64, c_int, c_float, c_void_p, c_int64, c_void_p,
-        c_void_p]),
+        c_void_p, c_int, c_void_p, c_void_p]),
     "sbk_gla_scan": (c_int, [
         c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int, c_void_p, c_int64, c_void_p,
         c_void_p, c_int, c_int, c_int, c_float, c_void_p, c_int, c_void_p, c_void_p]),

@@ -11,9 +11,12 @@ What runs where
   one-token decode    -> sbk_swa_decode  (reference: flash-attn fwd_kvcache, :955-981)
   prefill with tables -> sbk_swa_prefill (reference: flash-attn varlen forward with block
                          tables, :900-919): 16 query tokens x one kv group per CTA
+  meta tokens         -> key2/value2 are streamed as extra always-visible leading tiles of the same
+                         softmax (reference: second flash-attn pass + LSE merge,
+                         fa_kernel_metatoken.py:124-194); query2 is not supported
   prefill without block tables (the profile run / un-paged prompt), multi-token
-  "varlen" decode, meta tokens (key2/value2), fp8 KV, ALiBi, soft-cap, encoder and
-  cross attention                        -> NotImplementedError, never a fallback.
+  "varlen" decode, query2, fp8 KV, ALiBi, soft-cap, encoder and cross attention
+                                         -> NotImplementedError, never a fallback.
 """
 from collections import defaultdict
 from dataclasses import dataclass
@@ -453,8 +456,16 @@ class MetaAttentionImpl:
             assert (getattr(layer, "_k_scale_float", 1.0) == 1.0
                     and getattr(layer, "_v_scale_float", 1.0) == 1.0), (
                 "key/v_scale is only supported with an fp8 cache, which this path does not have")
-        if query2 is not None or key2 is not None or value2 is not None:
-            raise NotImplementedError("meta (sink) tokens are not implemented on this path yet")
+        if query2 is not None:
+            raise NotImplementedError(
+                "queries of the meta tokens themselves (the step that first computes them) have no kernel "
+                "on this path; pass their cached key2/value2 with query2=None")
+        if (key2 is None) != (value2 is None):
+            raise ValueError("key2 and value2 come together")
+        if key2 is not None:
+            assert self.num_meta_tokens == key2.shape[0], "num_meta_tokens differs from key2"
+            key2 = key2.view(-1, self.num_kv_heads, self.head_size).contiguous()
+            value2 = value2.view(-1, self.num_kv_heads, self.head_size).contiguous()
         H, D = self.num_heads, self.head_size
         query = query.view(-1, H, D)
         out3 = output.view(-1, H, D)
@@ -490,7 +501,7 @@ class MetaAttentionImpl:
                             prefill_meta.query_start_loc.to(torch.int32).contiguous(),
                             prefill_meta.context_lens_tensor.to(torch.int32).contiguous(),
                             prefill_meta.max_query_len, window_left=window_left, scale=self.scale, out=tmp,
-                            status=self._status)
+                            key2=key2, value2=value2, status=self._status)
             if tmp is not po:
                 po.copy_(tmp)
 
@@ -498,10 +509,10 @@ class MetaAttentionImpl:
             if decode_meta.max_decode_query_len is not None and decode_meta.max_decode_query_len > 1:
                 raise NotImplementedError("multi-token (varlen) decode has no kernel on this path")
             self._decode(decode_query, kv_cache, decode_meta.block_tables, decode_meta.seq_lens_tensor,
-                         window_left, out3[num_prefill_tokens:])
+                         window_left, out3[num_prefill_tokens:], key2, value2)
         return output
 
-    def _decode(self, q, kv_cache, block_tables, seq_lens, window_left, out) -> None:
+    def _decode(self, q, kv_cache, block_tables, seq_lens, window_left, out, key2=None, value2=None) -> None:
         B = q.shape[0]
         if B == 0:
             return
@@ -517,6 +528,6 @@ class MetaAttentionImpl:
         ops.swa_decode(q, kv_cache[0], kv_cache[1], block_tables.contiguous(), seq_lens.contiguous(),
                        window_left=window_left, scale=self.scale, out=tmp,
                        workspace=self._scratch(B, max_pieces, q.device), max_pieces=max_pieces,
-                       split_chunks=split, status=self._status)
+                       split_chunks=split, key2=key2, value2=value2, status=self._status)
         if tmp is not out:
             out.copy_(tmp)

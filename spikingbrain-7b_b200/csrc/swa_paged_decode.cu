@@ -121,12 +121,14 @@ struct Params {
   int32_t* done;      // [B] pieces finished per sequence
   float* ws_o; float* ws_ml; int split_chunks; int max_pieces; int32_t* status;
   int tile_copy;      // 1: one copy per tile (permuted-stride map), 0: one copy per 128-byte row
+  int n_meta_chunks;  // 16-token chunks of always-visible sink keys (key2/value2), 0 = none
 };
 
 template <int KVH, typename TO>
 __global__ void __launch_bounds__(kThreads, 2)
 swa_decode_kernel(const Params P, const __grid_constant__ CUtensorMap map_k,
-                  const __grid_constant__ CUtensorMap map_v) {
+                  const __grid_constant__ CUtensorMap map_v, const __grid_constant__ CUtensorMap map_k2,
+                  const __grid_constant__ CUtensorMap map_v2) {
   using C = Cfg<KVH>;
   extern __shared__ uint8_t smem_raw[];
   // the swizzle pattern is a function of the shared-memory address: tiles sit on 1 KiB boundaries
@@ -211,9 +213,14 @@ swa_decode_kernel(const Params P, const __grid_constant__ CUtensorMap map_k,
       const int32_t* table = P.block_tables + (int64_t)b * P.max_blocks;
       int64_t pb_lane = -1;   // physical block of chunk (batch_c0 + lane): one table read per 32 chunks
       int batch_c0 = 0;
-      for (int j = 0; j < nst; ++j, ++it) {
-        const int c0 = cb + j * C::kSub;       // first chunk of this stage
-        if (j == 0 || c0 + C::kSub > batch_c0 + 32) {
+      // Sink ("meta") keys are visible to every query: the first piece of a sequence streams them
+      // ahead of its window, as stages of their own from the [n_meta, kvh, D] tensors.
+      const int n_ms = (piece == 0 && L > 0) ? (P.n_meta_chunks + C::kSub - 1) / C::kSub : 0;
+      for (int jj = -n_ms; jj < nst; ++jj, ++it) {
+        const bool meta = jj < 0;
+        const int j = meta ? jj + n_ms : jj;
+        const int c0 = meta ? j * C::kSub : cb + j * C::kSub;       // first chunk of this stage
+        if (!meta && (j == 0 || c0 + C::kSub > batch_c0 + 32)) {
           batch_c0 = c0;
           const int c = c0 + lane;
           const int lb = (c * kChunk) / P.block_size;
@@ -228,11 +235,18 @@ swa_decode_kernel(const Params P, const __grid_constant__ CUtensorMap map_k,
         }
         if (misc[0]) { aborted = true; break; }
         const int tok_base = c0 * kChunk;
-        int lo = tok_base > plan.t0 ? tok_base : plan.t0;
-        int hi = tok_base + C::kStageTokens;
-        if (hi > L) hi = L;
-        if (hi > item_end) hi = item_end;
-        if (hi < lo) hi = lo;
+        int lo, hi;
+        if (meta) {
+          lo = tok_base;
+          hi = tok_base + C::kStageTokens;
+          if (hi > P.n_meta_chunks * kChunk) hi = P.n_meta_chunks * kChunk;
+        } else {
+          lo = tok_base > plan.t0 ? tok_base : plan.t0;
+          hi = tok_base + C::kStageTokens;
+          if (hi > L) hi = L;
+          if (hi > item_end) hi = item_end;
+          if (hi < lo) hi = lo;
+        }
         // lane -> one copy of this stage: K or V, sub-chunk, and (row-wise mode) 128-byte row
         const int n_copies = P.tile_copy ? 2 * C::kSub : 2 * C::kSub * C::kRows128;
         const int is_v = lane & 1;
@@ -243,10 +257,11 @@ swa_decode_kernel(const Params P, const __grid_constant__ CUtensorMap map_k,
         const int my_c = c0 + (active ? sc : 0);
         int src_lane = my_c - batch_c0;
         src_lane = src_lane < 0 ? 0 : (src_lane > 31 ? 31 : src_lane);
-        const int64_t pb = __shfl_sync(0xffffffffu, pb_lane, src_lane);
+        const int64_t pb_tab = __shfl_sync(0xffffffffu, pb_lane, src_lane);
+        const int64_t pb = meta ? (int64_t)my_c : pb_tab;      // the sink tensors are their own block table
         const int tbl = my_c * kChunk;
         const bool has_tok = (tbl > lo ? tbl : lo) < (tbl + kChunk < hi ? tbl + kChunk : hi);
-        bool bad = active && has_tok && (pb < 0 || pb >= P.num_blocks);
+        bool bad = !meta && active && has_tok && (pb < 0 || pb >= P.num_blocks);
         bad = __any_sync(0xffffffffu, bad);
         int n_sub = 0;   // sub-chunks of this stage that carry tokens
 #pragma unroll
@@ -258,7 +273,7 @@ swa_decode_kernel(const Params P, const __grid_constant__ CUtensorMap map_k,
           StageInfo si;
           si.b = b; si.piece = piece; si.n_pieces = plan.n_pieces; si.tok_base = tok_base;
           si.lo = lo; si.hi = hi; si.pad = 0;
-          si.flags = (j == 0 ? kFlagFirst : 0) | (j == nst - 1 ? kFlagLast : 0) | (bad ? kFlagBad : 0);
+          si.flags = (jj == -n_ms ? kFlagFirst : 0) | (jj == nst - 1 ? kFlagLast : 0) | (bad ? kFlagBad : 0);
           info[s] = si;
           if (bad) raise_status(P.status, SBK_ST_BAD_BLOCK);
           mbar_arrive_expect_tx(bar_full + 8 * s, bad ? 0u : (uint32_t)n_sub * 2u * C::kTileBytes);
@@ -266,9 +281,10 @@ swa_decode_kernel(const Params P, const __grid_constant__ CUtensorMap map_k,
         __syncwarp();
         if (!bad && active && has_tok) {
           const uint32_t dst = ring + s * C::kStageBytes + is_v * C::kVOffset + sc * C::kTileBytes + row * 2048;
-          const int tin = tbl % P.block_size;
-          if (P.tile_copy) tma_load_4d(dst, is_v ? &map_v : &map_k, 0, tin, 0, (int)pb, bar_full + 8 * s);
-          else tma_load_4d(dst, is_v ? &map_v : &map_k, 0, row, tin, (int)pb, bar_full + 8 * s);
+          const int tin = meta ? 0 : tbl % P.block_size;
+          const CUtensorMap* map = meta ? (is_v ? &map_v2 : &map_k2) : (is_v ? &map_v : &map_k);
+          if (P.tile_copy) tma_load_4d(dst, map, 0, tin, 0, (int)pb, bar_full + 8 * s);
+          else tma_load_4d(dst, map, 0, row, tin, (int)pb, bar_full + 8 * s);
         }
       }
     }
@@ -570,7 +586,7 @@ swa_decode_kernel(const Params P, const __grid_constant__ CUtensorMap map_k,
 
 template <int KVH, typename TO>
 int launch_swa(const Params& P0, int B_total, int n_ctas, const CUtensorMap& map_k, const CUtensorMap& map_v,
-               cudaStream_t st) {
+               const CUtensorMap& map_k2, const CUtensorMap& map_v2, cudaStream_t st) {
   using C = Cfg<KVH>;
   auto kern = swa_decode_kernel<KVH, TO>;
   // The opt-in to large dynamic shared memory is per device; remember which devices have it.
@@ -603,7 +619,7 @@ int launch_swa(const Params& P0, int B_total, int n_ctas, const CUtensorMap& map
     }
     int64_t items = (int64_t)P.B * P0.max_pieces;
     const int grid = (int)(items < n_ctas ? items : n_ctas);
-    kern<<<grid, kThreads, C::kSmemBytes, st>>>(P, map_k, map_v);
+    kern<<<grid, kThreads, C::kSmemBytes, st>>>(P, map_k, map_v, map_k2, map_v2);
     int rc = check_launch("sbk_swa_decode");
     if (rc != SBK_OK) return rc;
   }
@@ -630,8 +646,14 @@ extern "C" int sbk_swa_decode(const void* q, int64_t q_seq_stride, const void* k
                               int window_left, float scale, void* out, int out_dtype,
                               int64_t out_seq_stride, float* lse_out, void* workspace,
                               size_t workspace_bytes, int split_chunks, int max_pieces,
+                              const void* key2, const void* value2, int num_meta,
                               int32_t* status, void* stream) {
   using namespace sbk;
+  if (num_meta < 0 || num_meta % 16 != 0 || (num_meta > 0 && (!key2 || !value2 || !aligned16(key2) || !aligned16(value2)))) {
+    set_error("sbk_swa_decode: sink tokens need 16-byte aligned key2/value2 and a count that is a multiple of 16 (got %d)",
+              num_meta);
+    return SBK_E_ARG;
+  }
   if (B < 0 || H <= 0 || kvh <= 0 || H % kvh != 0 || max_blocks <= 0 || num_blocks < 0) {
     set_error("sbk_swa_decode: bad sizes B=%d H=%d kvh=%d max_blocks=%d", B, H, kvh, max_blocks);
     return SBK_E_ARG;
@@ -712,12 +734,24 @@ extern "C" int sbk_swa_decode(const void* q, int64_t q_seq_stride, const void* k
     return SBK_E_ARG;
   }
   P.tile_copy = tile_copy;
+  CUtensorMap map_k2 = map_k, map_v2 = map_v;
+  P.n_meta_chunks = 0;
+  if (num_meta > 0) {
+    // the sink tensors [num_meta, kvh, D] read as a cache of num_meta/16 blocks of 16 tokens
+    const int64_t mstride = (int64_t)16 * kvh * D * 2;
+    if (!get_map(&map_k2, MapKey{key2, kvh, num_meta / 16, 16, mstride, 2 * kvh}, &tile_copy) ||
+        !get_map(&map_v2, MapKey{value2, kvh, num_meta / 16, 16, mstride, 2 * kvh}, &tile_copy)) {
+      set_error("sbk_swa_decode: cuTensorMapEncodeTiled rejected the sink-token tensors");
+      return SBK_E_ARG;
+    }
+    P.n_meta_chunks = num_meta / 16;
+  }
   cudaStream_t st = (cudaStream_t)stream;
 #define SBK_SWA_KVH(TO)                                                            \
   switch (kvh) {                                                                   \
-    case 1: return launch_swa<1, TO>(P, B, n_ctas, map_k, map_v, st);              \
-    case 2: return launch_swa<2, TO>(P, B, n_ctas, map_k, map_v, st);              \
-    default: return launch_swa<4, TO>(P, B, n_ctas, map_k, map_v, st);             \
+    case 1: return launch_swa<1, TO>(P, B, n_ctas, map_k, map_v, map_k2, map_v2, st);  \
+    case 2: return launch_swa<2, TO>(P, B, n_ctas, map_k, map_v, map_k2, map_v2, st);  \
+    default: return launch_swa<4, TO>(P, B, n_ctas, map_k, map_v, map_k2, map_v2, st); \
   }
   if (out_dtype == SBK_BF16) { SBK_SWA_KVH(__nv_bfloat16) } else { SBK_SWA_KVH(float) }
 #undef SBK_SWA_KVH
@@ -787,6 +821,6 @@ extern "C" int sbk_swa_decode_static(const void* q, int64_t q_seq_stride, const 
   }
   return sbk_swa_decode(q, q_seq_stride, k_cache, v_cache, block_tables, max_blocks, seq_lens, B, H, kvh, D,
                         num_blocks, block_size, cache_block_stride_bytes, window_left, scale, out, out_dtype,
-                        out_seq_stride, lse_out, scratch, kStaticScratchBytes, split_chunks, max_pieces, status,
-                        stream);
+                        out_seq_stride, lse_out, scratch, kStaticScratchBytes, split_chunks, max_pieces, nullptr,
+                        nullptr, 0, status, stream);
 }

@@ -39,11 +39,13 @@ struct Params {
   int window_left; float scale_log2;
   __nv_bfloat16* out; int64_t out_tok_stride;
   int32_t* status; int tile_copy;
+  int n_meta_chunks;   // 16-token chunks of always-visible sink keys, streamed ahead of the window
 };
 
 __global__ void __launch_bounds__(288, 1)
 swa_prefill_kernel(const Params P, const __grid_constant__ CUtensorMap map_k,
-                   const __grid_constant__ CUtensorMap map_v) {
+                   const __grid_constant__ CUtensorMap map_v, const __grid_constant__ CUtensorMap map_k2,
+                   const __grid_constant__ CUtensorMap map_v2) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* const smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
   const uint32_t ring = smem_u32(smem);
@@ -62,7 +64,8 @@ swa_prefill_kernel(const Params P, const __grid_constant__ CUtensorMap map_k,
   const int key_hi = p0 + nq_tile;                            // exclusive
   const int c_lo = key_lo / kChunk, c_hi = (key_hi - 1) / kChunk;
   const int n_chunks = c_hi - c_lo + 1;
-  const int n_stages = (n_chunks + kStageChunks - 1) / kStageChunks;
+  const int n_ms = (P.n_meta_chunks + kStageChunks - 1) / kStageChunks;    // sink-token stages come first
+  const int n_stages = n_ms + (n_chunks + kStageChunks - 1) / kStageChunks;
   const int G = P.G;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
 
@@ -82,8 +85,10 @@ swa_prefill_kernel(const Params P, const __grid_constant__ CUtensorMap map_k,
     int64_t pb_lane = -1;
     int batch_c0 = 0;
     for (int st = 0; st < n_stages; ++st) {
-      const int c0 = c_lo + st * kStageChunks;
-      if (st == 0 || c0 + kStageChunks > batch_c0 + 32) {      // one table read per 32 chunks
+      const bool meta = st < n_ms;
+      const int c0 = meta ? st * kStageChunks : c_lo + (st - n_ms) * kStageChunks;
+      const int c_end = meta ? P.n_meta_chunks - 1 : c_hi;     // last chunk of this kind
+      if (!meta && (st == n_ms || c0 + kStageChunks > batch_c0 + 32)) {      // one table read per 32 chunks
         batch_c0 = c0;
         const int c = c0 + lane;
         const int lb = (c * kChunk) / P.block_size;
@@ -101,13 +106,14 @@ swa_prefill_kernel(const Params P, const __grid_constant__ CUtensorMap map_k,
       const int is_v = P.tile_copy ? lane & 1 : (lane >> 1) & 1;
       const int half = P.tile_copy ? 0 : lane & 1;
       const int c = c0 + (lane < n_copies ? i : 0);
-      const bool active = lane < n_copies && c <= c_hi;
+      const bool active = lane < n_copies && c <= c_end;
       int src_lane = c - batch_c0;
       src_lane = src_lane < 0 ? 0 : (src_lane > 31 ? 31 : src_lane);
-      const int64_t pb = __shfl_sync(0xffffffffu, pb_lane, src_lane);
-      bool bad = active && (pb < 0 || pb >= P.num_blocks);
+      const int64_t pb_tab = __shfl_sync(0xffffffffu, pb_lane, src_lane);
+      const int64_t pb = meta ? (int64_t)c : pb_tab;           // the sink tensors are their own block table
+      bool bad = !meta && active && (pb < 0 || pb >= P.num_blocks);
       bad = __any_sync(0xffffffffu, bad);
-      const int nvalid = c_hi - c0 + 1 < kStageChunks ? c_hi - c0 + 1 : kStageChunks;
+      const int nvalid = c_end - c0 + 1 < kStageChunks ? c_end - c0 + 1 : kStageChunks;
       if (lane == 0) {
         flags[slot] = bad ? 1 : 0;
         if (bad) raise_status(P.status, SBK_ST_BAD_BLOCK);
@@ -116,9 +122,10 @@ swa_prefill_kernel(const Params P, const __grid_constant__ CUtensorMap map_k,
       __syncwarp();
       if (!bad && active) {
         const uint32_t dst = ring + slot * kStageBytes + is_v * kVOffset + i * kTileBytes + half * 2048;
-        const int tin = (c * kChunk) % P.block_size;
-        if (P.tile_copy) tma_load_4d(dst, is_v ? &map_v : &map_k, 0, tin, hk * 2, (int)pb, bar_full + 8 * slot);
-        else tma_load_4d(dst, is_v ? &map_v : &map_k, 0, hk * 2 + half, tin, (int)pb, bar_full + 8 * slot);
+        const int tin = meta ? 0 : (c * kChunk) % P.block_size;
+        const CUtensorMap* map = meta ? (is_v ? &map_v2 : &map_k2) : (is_v ? &map_v : &map_k);
+        if (P.tile_copy) tma_load_4d(dst, map, 0, tin, hk * 2, (int)pb, bar_full + 8 * slot);
+        else tma_load_4d(dst, map, 0, hk * 2 + half, tin, (int)pb, bar_full + 8 * slot);
       }
     }
     return;
@@ -163,14 +170,16 @@ swa_prefill_kernel(const Params P, const __grid_constant__ CUtensorMap map_k,
       break;
     }
     const bool bad = flags[slot] != 0;
-    const int c0 = c_lo + st * kStageChunks;
-    const int nch = c_hi - c0 + 1 < kStageChunks ? c_hi - c0 + 1 : kStageChunks;
+    const bool meta = st < n_ms;
+    const int c0 = meta ? st * kStageChunks : c_lo + (st - n_ms) * kStageChunks;
+    const int c_end = meta ? P.n_meta_chunks - 1 : c_hi;
+    const int nch = c_end - c0 + 1 < kStageChunks ? c_end - c0 + 1 : kStageChunks;
     bool wrote = false;
     for (int i = 0; i < nch && !bad; ++i) {
       const int kbase = (c0 + i) * kChunk;                    // position of the tile's first key
       const uint32_t ktile = ring + slot * kStageBytes + i * kTileBytes;
       const uint32_t vtile = ktile + kVOffset;
-      if (kbase + kChunk > key_hi) {
+      if (!meta && kbase + kChunk > key_hi) {
         // keys past the last query of the tile may be memory no token has reached: their V must
         // be finite before it meets a zero probability (every warp writes the same zeros)
         for (int r = lane >> 4; r < kChunk; r += 2) {
@@ -192,8 +201,8 @@ swa_prefill_kernel(const Params P, const __grid_constant__ CUtensorMap map_k,
       }
 #pragma unroll
       for (int e = 0; e < 4; ++e) { s0[e] *= P.scale_log2; s1[e] *= P.scale_log2; }
-      const bool interior = kbase + kChunk - 1 <= p0 &&
-                            (P.window_left < 0 || kbase >= p0 + nq_tile - 1 - P.window_left) && nq_tile == kBQ;
+      const bool interior = meta || (kbase + kChunk - 1 <= p0 &&
+                            (P.window_left < 0 || kbase >= p0 + nq_tile - 1 - P.window_left) && nq_tile == kBQ);
       if (!interior) {
 #pragma unroll
         for (int e = 0; e < 4; ++e) {
@@ -288,9 +297,15 @@ extern "C" int sbk_swa_prefill(const void* q, int64_t q_tok_stride, const void* 
                                const int32_t* context_lens, int n_seqs, int max_query_len, int H, int kvh,
                                int D, int64_t num_blocks, int block_size, int64_t cache_block_stride_bytes,
                                int window_left, float scale, void* out, int64_t out_tok_stride,
+                               const void* key2, const void* value2, int num_meta,
                                int32_t* status, void* stream) {
   using namespace sbk;
   using namespace sbk::prefill;
+  if (num_meta < 0 || num_meta % 16 != 0 || (num_meta > 0 && (!key2 || !value2 || !aligned16(key2) || !aligned16(value2)))) {
+    set_error("sbk_swa_prefill: sink tokens need 16-byte aligned key2/value2 and a count that is a multiple of 16 (got %d)",
+              num_meta);
+    return SBK_E_ARG;
+  }
   if (n_seqs < 0 || max_query_len < 0 || H <= 0 || kvh <= 0 || H % kvh != 0 || max_blocks <= 0 || num_blocks < 0) {
     set_error("sbk_swa_prefill: bad sizes n_seqs=%d H=%d kvh=%d max_blocks=%d", n_seqs, H, kvh, max_blocks);
     return SBK_E_ARG;
@@ -344,8 +359,20 @@ extern "C" int sbk_swa_prefill(const void* q, int64_t q_tok_stride, const void* 
   P.query_start_loc = query_start_loc; P.context_lens = context_lens;
   P.n_seqs = n_seqs; P.tiles_per_seq = tiles; P.H = H; P.G = H / kvh; P.num_blocks = num_blocks;
   P.block_size = block_size; P.window_left = window_left; P.scale_log2 = scale * kLog2e;
-  P.out = (__nv_bfloat16*)out; P.out_tok_stride = out_tok_stride; P.status = status; P.tile_copy = tile_copy;
+  P.out = (__nv_bfloat16*)out; P.out_tok_stride = out_tok_stride; P.status = status;
+  CUtensorMap map_k2 = map_k, map_v2 = map_v;
+  P.n_meta_chunks = 0;
+  if (num_meta > 0) {
+    const int64_t mstride = (int64_t)16 * kvh * D * 2;
+    if (!get_map(&map_k2, MapKey{key2, kvh, num_meta / 16, 16, mstride, 2}, &tile_copy) ||
+        !get_map(&map_v2, MapKey{value2, kvh, num_meta / 16, 16, mstride, 2}, &tile_copy)) {
+      set_error("sbk_swa_prefill: cuTensorMapEncodeTiled rejected the sink-token tensors");
+      return SBK_E_ARG;
+    }
+    P.n_meta_chunks = num_meta / 16;
+  }
+  P.tile_copy = tile_copy;
   dim3 grid(n_seqs * tiles, kvh);
-  swa_prefill_kernel<<<grid, (P.G + 1) * 32, kSmemBytes, (cudaStream_t)stream>>>(P, map_k, map_v);
+  swa_prefill_kernel<<<grid, (P.G + 1) * 32, kSmemBytes, (cudaStream_t)stream>>>(P, map_k, map_v, map_k2, map_v2);
   return check_launch("sbk_swa_prefill");
 }

@@ -123,6 +123,21 @@ def kv_gather(k_cache: torch.Tensor, v_cache: torch.Tensor, block_tables: torch.
 _SM_COUNT = {}
 
 
+def _check_meta(key2, value2, kvh: int, d: int) -> int:
+    """Sink-token tensors [n_meta, kvh, D] bf16, contiguous, n_meta a multiple of 16; returns n_meta."""
+    if key2 is None and value2 is None:
+        return 0
+    if key2 is None or value2 is None:
+        raise ValueError("key2 and value2 come together")
+    _need_cuda(key2, value2)
+    for t in (key2, value2):
+        if t.dtype != torch.bfloat16 or t.dim() != 3 or t.shape[1:] != (kvh, d) or not t.is_contiguous():
+            raise ValueError(f"key2 / value2 must be contiguous bf16 [n_meta, {kvh}, {d}]")
+    if key2.shape != value2.shape or key2.shape[0] % 16:
+        raise ValueError("key2 / value2 must share a token count that is a multiple of 16")
+    return key2.shape[0]
+
+
 def swa_auto_split(B: int, max_visible_tokens: int, device) -> int:
     """Chunks (of 16 tokens) per split such that a batch of B sequences yields about one work
     item per resident CTA (two CTAs per SM): large batches are not split at all, small ones are
@@ -154,10 +169,12 @@ def swa_decode(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor,
                scale: Optional[float] = None, out: Optional[torch.Tensor] = None,
                out_dtype: Optional[torch.dtype] = None, lse: Optional[torch.Tensor] = None,
                workspace: Optional[torch.Tensor] = None, max_pieces: Optional[int] = None,
-               split_chunks: Optional[int] = None,
+               split_chunks: Optional[int] = None, key2: Optional[torch.Tensor] = None,
+               value2: Optional[torch.Tensor] = None,
                status: Optional[torch.Tensor] = None) -> torch.Tensor:
     """Single-query sliding-window attention over the paged cache; q [B, H, D] bf16.
-    ``split_chunks`` (16-token chunks per split of a sequence) defaults to swa_auto_split."""
+    ``split_chunks`` (16-token chunks per split of a sequence) defaults to swa_auto_split.
+    ``key2`` / ``value2`` [n_meta, kvh, D]: sink tokens every query sees besides its window."""
     _need_cuda(q, k_cache, v_cache, block_tables, seq_lens, out, lse, workspace, status)
     nb, bs, kvh, d, bstride = _cache_geometry(k_cache, v_cache)
     if q.dim() != 3 or q.shape[2] != d or q.dtype != torch.bfloat16 or k_cache.dtype != torch.bfloat16:
@@ -189,6 +206,7 @@ def swa_decode(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor,
         workspace = swa_workspace(B, H, d, max_pieces, q.device)
     if scale is None:
         scale = d ** -0.5
+    n_meta = _check_meta(key2, value2, kvh, d)
     timing = SWA_TIMING
     if timing is not None:
         # external: inside a stream capture these become event-record nodes of the graph, so
@@ -201,7 +219,7 @@ def swa_decode(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor,
         max_blocks, _ptr(seq_lens), B, H, kvh, d, nb, bs, bstride, window_left, float(scale),
         _ptr(out), _DTYPE_CODE[out.dtype], out.stride(0) if B else H * d, _ptr(lse),
         _ptr(workspace), workspace.numel() if workspace is not None else 0, split_chunks,
-        max_pieces, _ptr(status), _stream())
+        max_pieces, _ptr(key2), _ptr(value2), n_meta, _ptr(status), _stream())
     _abi.check("sbk_swa_decode", rc)
     if timing is not None:
         ev1.record()
@@ -302,6 +320,7 @@ def gla_scan(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, g: torch.Tensor,
 def swa_prefill(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, block_tables: torch.Tensor,
                 query_start_loc: torch.Tensor, context_lens: torch.Tensor, max_query_len: int, *,
                 window_left: int, scale: Optional[float] = None, out: Optional[torch.Tensor] = None,
+                key2: Optional[torch.Tensor] = None, value2: Optional[torch.Tensor] = None,
                 status: Optional[torch.Tensor] = None) -> torch.Tensor:
     """Sliding-window attention of runs of query tokens (q [T, H, D] bf16, token-major) over the
     paged cache, the runs' own K/V already appended. Sequence s owns rows
@@ -327,7 +346,7 @@ def swa_prefill(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, b
         _ptr(q), q.stride(0) if T else H * d, _ptr(k_cache), _ptr(v_cache), _ptr(block_tables),
         block_tables.shape[1], _ptr(query_start_loc), _ptr(context_lens), n_seqs, int(max_query_len), H,
         kvh, d, nb, bs, bstride, window_left, float(scale), _ptr(out), out.stride(0) if T else H * d,
-        _ptr(status), _stream())
+        _ptr(key2), _ptr(value2), _check_meta(key2, value2, kvh, d), _ptr(status), _stream())
     _abi.check("sbk_swa_prefill", rc)
     global LAUNCHES
     LAUNCHES += 1 if (n_seqs and max_query_len) else 0

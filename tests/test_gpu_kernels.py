@@ -244,6 +244,53 @@ def test_swa_decode_config2_shapes(ops):
     _check_attn(out, ref, lse, lse_ref)
 
 
+@pytest.mark.parametrize("H,kvh,n_meta", [(28, 4, 128), (7, 1, 16), (14, 2, 48)])
+def test_swa_decode_with_sink_tokens(ops, H, kvh, n_meta):
+    """Meta (sink) tokens every query sees besides its window: one softmax over both."""
+    D, bs, wl = 128, 16, 511
+    lens = [1, 40, 512, 513, 2000, 0]
+    kv, table, nb = make_paged_kv([max(L, 1) for L in lens], wl, kvh, D, bs, seed=70)
+    g = torch.Generator().manual_seed(71)
+    q = (torch.randn(len(lens), H, D, generator=g) / math.sqrt(D)).bfloat16()
+    k2 = (torch.randn(n_meta, kvh, D, generator=g) / math.sqrt(D)).bfloat16()
+    v2 = (torch.randn(n_meta, kvh, D, generator=g) / math.sqrt(D)).bfloat16()
+    ref, lse_ref = ref_ops.swa_paged_decode_ref(q, kv[0], kv[1], table, lens, wl, D ** -0.5, return_lse=True,
+                                                key2=k2, value2=v2)
+    st = _status()
+    kv_d = kv.to(DEV)
+    lse = torch.empty(len(lens), H, dtype=torch.float32, device=DEV)
+    for split in (None, 4):
+        out = ops.swa_decode(q.to(DEV), kv_d[0], kv_d[1], table.to(DEV), torch.tensor(lens, dtype=torch.int32, device=DEV),
+                             window_left=wl, lse=lse, split_chunks=split, key2=k2.to(DEV), value2=v2.to(DEV), status=st)
+        torch.cuda.synchronize()
+        assert st.item() == 0
+        _check_attn(out.cpu(), ref, lse.cpu(), lse_ref)
+
+
+def test_swa_prefill_with_sink_tokens(ops):
+    D, H, kvh, bs, wl, n_meta = 128, 28, 4, 16, 63, 128
+    ctx, new = [0, 90], [50, 33]
+    total = [c + n for c, n in zip(ctx, new)]
+    kv, table, nb = make_paged_kv(total, -1, kvh, D, bs, seed=72)
+    g = torch.Generator().manual_seed(73)
+    q = (torch.randn(sum(new), H, D, generator=g) / math.sqrt(D)).bfloat16()
+    k2 = (torch.randn(n_meta, kvh, D, generator=g) / math.sqrt(D)).bfloat16()
+    v2 = (torch.randn(n_meta, kvh, D, generator=g) / math.sqrt(D)).bfloat16()
+    kv_d = kv.to(DEV)
+    st = _status()
+    out = ops.swa_prefill(q.to(DEV), kv_d[0], kv_d[1], table.to(DEV), torch.tensor([0, 50, 83], dtype=torch.int32, device=DEV),
+                          torch.tensor(ctx, dtype=torch.int32, device=DEV), 50, window_left=wl, key2=k2.to(DEV),
+                          value2=v2.to(DEV), status=st).float().cpu()
+    assert st.item() == 0
+    row = 0
+    for s in range(2):
+        for i in range(new[s]):
+            ref = ref_ops.swa_paged_decode_ref(q[row][None], kv[0], kv[1], table[s:s + 1], [ctx[s] + i + 1], wl, D ** -0.5,
+                                               key2=k2, value2=v2)[0].bfloat16().float()
+            assert float((out[row] - ref).abs().max()) <= ATTN_MAX_ABS and mean_rel(out[row], ref) <= 2 * ATTN_MEAN_REL
+            row += 1
+
+
 # --------------------------------------------------------------------- prefill attention
 def _prefill_case(ops, ctx, new, wl, H, kvh, bs, seed):
     """Sequences with `ctx[s]` cached tokens get `new[s]` more: append, then windowed attention of

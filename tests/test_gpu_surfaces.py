@@ -295,6 +295,30 @@ def test_backend_forward_chunked_prefill_plus_decode(pkg):
     assert float((o - tgt).abs().max()) <= 2e-2 and mean_rel(o, tgt) <= 1e-3
 
 
+def test_backend_forward_with_meta_tokens(pkg):
+    """The 76B-style use of the backend: key2/value2 (128 sink tokens) with query2=None, a decode
+    batch. Equals one softmax over sink keys + window keys."""
+    from spikingbrain_7b_b200.backend import MetaAttentionImpl, MetaAttentionMetadata
+    from tests.helpers import make_paged_kv
+    H, kvh, D, bs, sw = 28, 4, 128, 16, 129
+    lens = [300, 5, 128]
+    kv, table, nb = make_paged_kv(lens, -1, kvh, D, bs, seed=80)
+    g = torch.Generator().manual_seed(81)
+    q = (torch.randn(3, H, D, generator=g) / math.sqrt(D)).bfloat16()
+    k2 = (torch.randn(128, kvh, D, generator=g) / math.sqrt(D)).bfloat16()
+    v2 = (torch.randn(128, kvh, D, generator=g) / math.sqrt(D)).bfloat16()
+    impl = MetaAttentionImpl(H, D, D ** -0.5, kvh, None, sw, "auto", num_meta_tokens=128)
+    md = _decode_meta(MetaAttentionMetadata, torch.full((3,), -1, dtype=torch.int64, device=DEV),
+                      torch.tensor(lens, dtype=torch.int32, device=DEV), table.to(DEV))
+    out = torch.empty(3, H, D, dtype=torch.bfloat16, device=DEV)
+    knew = torch.zeros(3, kvh, D, dtype=torch.bfloat16, device=DEV)      # slots are -1: nothing is appended
+    impl.forward(None, q.to(DEV), knew, knew, None, k2.to(DEV), v2.to(DEV), kv.to(DEV), md, output=out)
+    ref = ref_ops.swa_paged_decode_ref(q, kv[0], kv[1], table, lens, sw - 1, D ** -0.5, key2=k2, value2=v2)
+    o, tgt = out.float().cpu(), ref.bfloat16().float()
+    assert impl.status() == 0
+    assert float((o - tgt).abs().max()) <= 2e-2 and mean_rel(o, tgt) <= 1e-3
+
+
 def test_backend_forward_unsupported_paths_raise(pkg):
     from spikingbrain_7b_b200.backend import MetaAttentionImpl, MetaAttentionMetadata
     impl = MetaAttentionImpl(28, 128, 1.0, 4, None, 65, "auto")
@@ -306,7 +330,9 @@ def test_backend_forward_unsupported_paths_raise(pkg):
                       torch.tensor([[0], [1]], dtype=torch.int32, device=DEV))
     with pytest.raises(AssertionError):
         impl.forward(None, q, kx, kx, None, None, None, kv, md, output=None)
-    with pytest.raises(NotImplementedError):       # sink tokens are a later row of the scope table
+    with pytest.raises(NotImplementedError):       # the meta tokens' own queries have no kernel here
+        impl.forward(None, q, kx, kx, q, None, None, kv, md, output=torch.empty_like(q))
+    with pytest.raises(AssertionError):            # num_meta_tokens (128) must match key2
         impl.forward(None, q, kx, kx, None, kx, kx, kv, md, output=torch.empty_like(q))
     pm = MetaAttentionMetadata(num_prefills=1, num_prefill_tokens=2, num_decode_tokens=0,
                                slot_mapping=torch.tensor([-1, -1], device=DEV), seq_lens=[2],

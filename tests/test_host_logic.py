@@ -24,7 +24,7 @@ def test_library_exports_every_declared_symbol(sb):
         assert hasattr(lib, name), f"{name} declared in include/sbk.h but not exported"
     from spikingbrain_7b_b200 import _abi
     assert set(_abi.SIGNATURES) == declared
-    assert _abi.lib.sbk_abi_version() == 1
+    assert _abi.lib.sbk_abi_version() == _abi.ABI_VERSION == 2
 
 
 def test_host_side_argument_errors_need_no_gpu(sb):
@@ -34,10 +34,13 @@ def test_host_side_argument_errors_need_no_gpu(sb):
     rc = lib.sbk_gla_step(None, None, None, None, 0, None, 4, None, 2, 28, 4, 96, 1.0, None, 0, None, None)
     assert rc == _abi.SBK_E_ARG and b"D=96" in lib.sbk_last_error()
     rc = lib.sbk_swa_decode(None, 0, None, None, None, 4, None, 2, 36, 4, 128, 8, 16, 0, 63, 1.0, None, 0, 0,
-                            None, None, 0, 0, 1, None, None)
+                            None, None, 0, 0, 1, None, None, 0, None, None)
     assert rc == _abi.SBK_E_ARG and b"unsupported shape" in lib.sbk_last_error()
     rc = lib.sbk_swa_decode(None, 0, None, None, None, 4, None, 2, 28, 4, 128, 8, 24, 0, 63, 1.0, None, 0, 0,
-                            None, None, 0, 0, 1, None, None)
+                            None, None, 0, 0, 1, None, None, 0, None, None)
+    rc2 = lib.sbk_swa_decode(None, 0, None, None, None, 4, None, 2, 28, 4, 128, 8, 16, 0, 63, 1.0, None, 0, 0,
+                             None, None, 0, 0, 1, None, None, 100, None, None)
+    assert rc2 == _abi.SBK_E_ARG            # 100 sink tokens: not a multiple of 16, and no tensors
     assert rc == _abi.SBK_E_ARG and b"multiple of 16" in lib.sbk_last_error()
     assert lib.sbk_kv_append(None, None, None, None, None, 3, 4, 128, 2, 1024, 8, 16, 16384, None, 0, None,
                              None, 0, -1, None, 0, None, None) == _abi.SBK_E_ARG

@@ -39,7 +39,7 @@ def _call(lib, static, q, kv, table, lens, out, lse, H, kvh, D, bs, wl, split, m
     tail = (split, max_pieces, status.data_ptr(), stream)
     if static:
         return lib.sbk_swa_decode_static(*head, *tail)
-    return lib.sbk_swa_decode(*head, ws.data_ptr(), ws.numel(), *tail)
+    return lib.sbk_swa_decode(*head, ws.data_ptr(), ws.numel(), split, max_pieces, None, None, 0, status.data_ptr(), stream)
 
 
 def test_static_scratch_entry_point_matches_workspace_entry_point_twice(sb):
