@@ -29,7 +29,7 @@
 extern "C" {
 #endif
 
-#define SBK_ABI_VERSION 2
+#define SBK_ABI_VERSION 3
 
 /* element type codes */
 #define SBK_BF16 0
@@ -47,6 +47,7 @@ extern "C" {
 #define SBK_ST_BAD_BLOCK 2     /* block-table entry outside [0,num_blocks) inside the window */
 #define SBK_ST_WAIT_TIMEOUT 4  /* a bounded in-kernel wait ran out; result of that CTA invalid */
 #define SBK_ST_RETIRE_OVERFLOW 8 /* more blocks left the window than retired_out has columns */
+#define SBK_ST_BAD_POSITION 16   /* a position outside the cos/sin table (token left untouched) */
 
 int sbk_abi_version(void);
 const char* sbk_last_error(void);
@@ -163,6 +164,41 @@ int sbk_swa_decode_static(const void* q, int64_t q_seq_stride, const void* k_cac
                           int split_chunks, int max_pieces, int32_t* status, void* stream);
 
 /*
+ * Rotary position embedding fused into the append: rotates the new tokens' query rows in place,
+ * rotates their key rows on the way into the cache, copies the value rows and retires blocks,
+ * all in one launch. Stands in for GLAswaRotaryEmbedding.forward
+ * (vllm_hymeta/model_for_7B/modeling_gla_swa.py:79-93, called at :215) followed by the cache
+ * write of MetaAttentionImpl.forward (vllm_hymeta/attention/meta_attention.py:790-799), and for
+ * apply_rotary_pos_emb + Cache.update on the HF side (hf_7B_model/window_attention.py:161-175).
+ * NeoX (rotate-half) form over the first rot_dim elements of every head; each product and the
+ * sum are rounded to the element type separately, as the reference's tensor expression
+ * (x * cos) + (rotate_half(x) * sin) rounds them.
+ *
+ *  query        [T, H, D], `q_token_stride_bytes` between tokens, rotated IN PLACE; NULL: skipped
+ *  key          [T, kvh, D]; the rotated rows go to k_cache; with key_in_place != 0 they are also
+ *               written back to `key` (the reference's prompt pass attends over that tensor)
+ *  value        [T, kvh, D], copied to v_cache; key and value share kv_token_stride_bytes
+ *  positions    [T] int64 position of every token; outside [0, max_position) raises
+ *               SBK_ST_BAD_POSITION and the token is skipped
+ *  cos_sin_cache [max_position, rot_dim] of `dtype`: cos of the rot_dim/2 frequencies, then sin
+ *               (the layout of GLAswaRotaryEmbedding._compute_cos_sin_cache, :71-79)
+ *  dtype        SBK_BF16 or SBK_F32: element type of query, key, value, the caches and the table
+ *  slot_mapping entry -1: nothing is written to the cache for that token; its query (and key, with
+ *               key_in_place) is still rotated
+ *  remaining arguments: as in sbk_kv_append
+ * rot_dim a multiple of 16 (bf16) or 8 (fp32) elements, rot_dim <= D.
+ */
+int sbk_rope_kv_append(void* query, int H, int64_t q_token_stride_bytes, void* key, const void* value,
+                       int key_in_place, void* k_cache, void* v_cache, const int64_t* slot_mapping,
+                       const int64_t* positions, const void* cos_sin_cache, int rot_dim,
+                       int64_t max_position, int T, int kvh, int D, int dtype,
+                       int64_t kv_token_stride_bytes, int64_t num_blocks, int block_size,
+                       int64_t cache_block_stride_bytes, int32_t* block_tables, int max_blocks,
+                       const int32_t* seq_lens, const int32_t* query_start_loc, int B,
+                       int window_left, int32_t* retired_out, int max_retired, int32_t* status,
+                       void* stream);
+
+/*
  * Fused GLA recurrent-state step, in place in the slot cache:
  *    S[slot] <- diag(exp(g)) . S[slot] + k^T v ;   o = (q*scale) . S[slot]
  * Stands in for my_fused_recurrent_gla
@@ -177,11 +213,25 @@ int sbk_swa_decode_static(const void* q, int64_t q_seq_stride, const void* k_cac
  *  state        [num_slots, H, D, D] float32 (k index before v index)
  *  slot_idx     [B] int64 (NULL: slot b for sequence b); -1: row untouched, out row not written
  *  D in {64, 128}
+ *
+ * The element-wise neighbours of the call in the reference layer can be folded in
+ * (vllm_hymeta/model_for_7B/gla_attention.py:250-262 and :233; hf_7B_model/gla_attention.py:
+ * 134-145, 170), so that q, k and the gate logits arrive straight from the projections:
+ *  fuse_flags   SBK_GLA_RELU_QK: q <- relu(q), k <- relu(k) (the layer's feature map);
+ *               SBK_GLA_GATE_LOGITS: g holds gate logits and the log-decay is
+ *               logsigmoid(g) / gate_normalizer, each of the two steps rounded to in_dtype as
+ *               the reference's tensor expression rounds them; 0: none
+ *  norm_weight  [D] in in_dtype, or NULL: o <- o * rsqrt(mean_d(o^2) + norm_eps) * norm_weight per
+ *               head (the layer's g_norm), computed on the fp32 read-out before the one rounding
+ *               to out_dtype
  */
+#define SBK_GLA_RELU_QK 1
+#define SBK_GLA_GATE_LOGITS 2
 int sbk_gla_step(const void* q, const void* k, const void* v, const void* g, int in_dtype,
                  float* state, int64_t num_slots, const int64_t* slot_idx,
                  int B, int H, int Hkv, int D, float scale,
-                 void* out, int out_dtype, int32_t* status, void* stream);
+                 void* out, int out_dtype, int fuse_flags, float gate_normalizer,
+                 const void* norm_weight, float norm_eps, int32_t* status, void* stream);
 
 /*
  * Sliding-window attention for runs of query tokens over the paged cache (prefill with block
@@ -224,11 +274,13 @@ int sbk_swa_prefill(const void* q, int64_t q_tok_stride, const void* k_cache, co
  *               prompt; the reference clears such slots in GLAswaModel._clear_prefill_cache,
  *               modeling_gla_swa.py:391-414) instead of reading the slot
  *  out          [T, H, D] of out_dtype
+ *  fuse_flags, gate_normalizer, norm_weight, norm_eps   as in sbk_gla_step
  */
 int sbk_gla_scan(const void* q, const void* k, const void* v, const void* g, int in_dtype,
                  const int32_t* query_start_loc, int n_seqs, float* state, int64_t num_slots,
                  const int64_t* slot_idx, const uint8_t* reset, int H, int Hkv, int D, float scale,
-                 void* out, int out_dtype, int32_t* status, void* stream);
+                 void* out, int out_dtype, int fuse_flags, float gate_normalizer,
+                 const void* norm_weight, float norm_eps, int32_t* status, void* stream);
 
 #ifdef __cplusplus
 }

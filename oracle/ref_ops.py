@@ -242,3 +242,46 @@ def gla_prepare_inputs(q_proj: torch.Tensor, k_proj: torch.Tensor, gk_proj: torc
     """Input preparation of hf_7B_model/gla_attention.py:134-145: ReLU feature map on q and k,
     log-decay g = logsigmoid(gk) / gate_logit_normalizer."""
     return torch.relu(q_proj), torch.relu(k_proj), torch.nn.functional.logsigmoid(gk_proj) / normalizer
+
+
+def gla_norm_ref(o: torch.Tensor, weight: torch.Tensor, eps: float = 1e-5) -> torch.Tensor:
+    """The GLA layer's g_norm on the read-out [.., H, D]: RMS norm over each head's D values
+    (hf_7B_model/gla_attention.py:89,170; vllm_hymeta/model_for_7B/gla_attention.py:177,233), in the
+    arithmetic of the reference's rms_norm_ref (hf_7B_model/layernorm.py:39-52), kept in fp32."""
+    of = o.float()
+    rstd = 1.0 / torch.sqrt(of.square().mean(dim=-1, keepdim=True) + eps)
+    return of * rstd * weight.float()
+
+
+def gla_layer_step_ref(q_proj: torch.Tensor, k_proj: torch.Tensor, v: torch.Tensor, gk_logits: torch.Tensor,
+                       state: torch.Tensor, slot_idx: Optional[torch.Tensor] = None,
+                       normalizer: float = 16.0, norm_weight: Optional[torch.Tensor] = None,
+                       eps: float = 1e-5, scale: Optional[float] = None) -> torch.Tensor:
+    """Decode branch of the GLA layer between its projections and its output gate
+    (vllm_hymeta/model_for_7B/gla_attention.py:250-267 then :225-233): feature map, gate,
+    the recurrent step, g_norm. Rows with slot -1 stay zero. Returns fp32 [B, H, D]."""
+    q, k, g = gla_prepare_inputs(q_proj, k_proj, gk_logits, normalizer)
+    o = gla_step_ref(q, k, v, g, state, slot_idx, scale=scale)
+    if norm_weight is None:
+        return o
+    normed = gla_norm_ref(o, norm_weight, eps)
+    if slot_idx is not None:
+        normed[torch.as_tensor(slot_idx) < 0] = 0
+    return normed
+
+
+def rope_cos_sin_ref(positions: torch.Tensor, rot_dim: int, base: float, dtype: torch.dtype):
+    """cos, sin [T, rot_dim] of RotaryEmbedding.forward (hf_7B_model/window_attention.py:23-47):
+    fp32 angles position * base^(-2i/rot_dim), the half-table repeated twice, cast to `dtype`."""
+    inv_freq = 1.0 / (base ** (torch.arange(0, rot_dim, 2, dtype=torch.int64).float() / rot_dim))
+    freqs = positions.float()[:, None] * inv_freq[None, :]
+    emb = torch.cat((freqs, freqs), dim=-1)
+    return emb.cos().to(dtype), emb.sin().to(dtype)
+
+
+def rope_ref(x: torch.Tensor, cos: torch.Tensor, sin: torch.Tensor) -> torch.Tensor:
+    """apply_rotary_pos_emb (hf_7B_model/window_attention.py:49-80) on token-major x [T, heads, D]
+    with cos, sin [T, D]: (x * cos) + (rotate_half(x) * sin), every tensor op in x's dtype."""
+    half = x.shape[-1] // 2
+    rot = torch.cat((-x[..., half:], x[..., :half]), dim=-1)
+    return (x * cos[:, None, :]) + (rot * sin[:, None, :])

@@ -13,8 +13,8 @@ LIB_PATH = os.environ.get("SBK_LIB_PATH") or os.path.join(PKG_DIR, "libsbk.so")
 
 SBK_BF16, SBK_F32 = 0, 1
 SBK_OK, SBK_E_ARG, SBK_E_ALIGN, SBK_E_WORKSPACE, SBK_E_LAUNCH = 0, -1, -2, -3, -4
-ST_BAD_SLOT, ST_BAD_BLOCK, ST_WAIT_TIMEOUT, ST_RETIRE_OVERFLOW = 1, 2, 4, 8
-ABI_VERSION = 2
+ST_BAD_SLOT, ST_BAD_BLOCK, ST_WAIT_TIMEOUT, ST_RETIRE_OVERFLOW, ST_BAD_POSITION = 1, 2, 4, 8, 16
+ABI_VERSION = 3
 
 # name -> (restype, argtypes); must list every function include/sbk.h declares
 SIGNATURES = {
@@ -39,15 +39,21 @@ SIGNATURES = {
         c_void_p, c_int, c_void_p, c_void_p]),
     "sbk_gla_scan": (c_int, [
         c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int, c_void_p, c_int64, c_void_p,
-        c_void_p, c_int, c_int, c_int, c_float, c_void_p, c_int, c_void_p, c_void_p]),
+        c_void_p, c_int, c_int, c_int, c_float, c_void_p, c_int, c_int, c_float, c_void_p, c_float,
+        c_void_p, c_void_p]),
     "sbk_swa_static_scratch_bytes": (c_size_t, []),
     "sbk_swa_decode_static": (c_int, [
         c_void_p, c_int64, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_int,
         c_int, c_int64, c_int, c_int64, c_int, c_float, c_void_p, c_int, c_int64, c_void_p,
         c_int, c_int, c_void_p, c_void_p]),
+    "sbk_rope_kv_append": (c_int, [
+        c_void_p, c_int, c_int64, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p,
+        c_void_p, c_int, c_int64, c_int, c_int, c_int, c_int, c_int64, c_int64, c_int, c_int64,
+        c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_void_p, c_int, c_void_p, c_void_p]),
     "sbk_gla_step": (c_int, [
         c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int64, c_void_p, c_int, c_int,
-        c_int, c_int, c_float, c_void_p, c_int, c_void_p, c_void_p]),
+        c_int, c_int, c_float, c_void_p, c_int, c_int, c_float, c_void_p, c_float, c_void_p,
+        c_void_p]),
 }
 
 

@@ -446,9 +446,15 @@ class MetaAttentionImpl:
                 query2: Optional[torch.Tensor], key2: Optional[torch.Tensor],
                 value2: Optional[torch.Tensor], kv_cache: torch.Tensor,
                 attn_metadata: MetaAttentionMetadata, output: Optional[torch.Tensor] = None,
-                output_scale: Optional[torch.Tensor] = None) -> torch.Tensor:
+                output_scale: Optional[torch.Tensor] = None, positions: Optional[torch.Tensor] = None,
+                cos_sin_cache: Optional[torch.Tensor] = None) -> torch.Tensor:
         """query [T, H, D]; key, value [T, KVH, D]; kv_cache [2, NB, BS, KVH, D] (numel 0 on the
-        memory-profiling run); writes into `output` ([T, H, D] or [T, H*D]) and returns it."""
+        memory-profiling run); writes into `output` ([T, H, D] or [T, H*D]) and returns it.
+
+        With ``positions`` [T] int64 and ``cos_sin_cache`` (ops.build_cos_sin_cache) the rotary
+        embedding the reference applies just before this call
+        (vllm_hymeta/model_for_7B/modeling_gla_swa.py:215) is folded into the cache write: pass
+        the UN-rotated query and key; both are rotated in place by the same launch that appends."""
         assert output is not None, "Output tensor must be provided."
         if output_scale is not None:
             raise NotImplementedError("fused output quantization is not supported in MetaAttention.")
@@ -472,10 +478,21 @@ class MetaAttentionImpl:
         if self._status is None or self._status.device != query.device:
             self._status = torch.zeros(1, dtype=torch.int32, device=query.device)
 
+        if (positions is None) != (cos_sin_cache is None):
+            raise ValueError("positions and cos_sin_cache come together")
         if kv_cache.numel() > 0 and key is not None and value is not None:
-            ops.kv_append(key.view(-1, self.num_kv_heads, D), value.view(-1, self.num_kv_heads, D),
-                          kv_cache[0], kv_cache[1], attn_metadata.slot_mapping.flatten(),
-                          status=self._status)
+            if positions is not None:
+                ops.rope_kv_append(query, key.view(-1, self.num_kv_heads, D),
+                                   value.view(-1, self.num_kv_heads, D), kv_cache[0], kv_cache[1],
+                                   attn_metadata.slot_mapping.flatten(), positions.flatten(),
+                                   cos_sin_cache, key_in_place=True, status=self._status)
+            else:
+                ops.kv_append(key.view(-1, self.num_kv_heads, D), value.view(-1, self.num_kv_heads, D),
+                              kv_cache[0], kv_cache[1], attn_metadata.slot_mapping.flatten(),
+                              status=self._status)
+        elif positions is not None:
+            raise NotImplementedError("the fused rotary embedding rides on the cache write; without a "
+                                      "cache (profile run) rotate query and key beforehand")
 
         num_prefill_tokens = attn_metadata.num_prefill_tokens
         num_decode_tokens = attn_metadata.num_decode_tokens

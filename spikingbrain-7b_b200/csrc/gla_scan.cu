@@ -7,7 +7,8 @@
 // whole run (thread = float4 of v columns x 16 k rows), so it crosses HBM twice per chunk instead
 // of twice per token; per token only the four 128-vectors q, k, g, v are read and o written.
 // Tokens are staged four at a time through shared memory; the read-out's sum over k rows is
-// finished across the 8 row groups once per four tokens.
+// finished across the 8 row groups once per four tokens. The same optional fused neighbours as
+// the single-token step (GlaFusion): ReLU on q/k, gate logits -> log-decay, per-head RMS norm.
 #include <math.h>
 
 #include "sbk_common.cuh"
@@ -35,7 +36,7 @@ gla_scan_kernel(const T* __restrict__ q, const T* __restrict__ k, const T* __res
                 const T* __restrict__ g, const int32_t* __restrict__ query_start_loc,
                 float* __restrict__ state, int64_t num_slots, const int64_t* __restrict__ slot_idx,
                 const uint8_t* __restrict__ reset, int H, int Hkv, float scale, TO* __restrict__ out,
-                int32_t* status) {
+                int32_t* status, const GlaFusion fu) {
   constexpr int TPR = D / 4;          // threads per state row
   constexpr int GROUPS = 256 / TPR;   // row groups
   constexpr int RPT = D / GROUPS;     // rows per thread
@@ -55,6 +56,7 @@ gla_scan_kernel(const T* __restrict__ q, const T* __restrict__ k, const T* __res
   __shared__ float s_q[kScanTokens][D], s_k[kScanTokens][D], s_d[kScanTokens][D];
   __shared__ float4 s_v[kScanTokens][TPR];
   __shared__ float4 s_o[kScanTokens][GROUPS][TPR];
+  __shared__ float s_sq[2][8];
 
   float4* tile = reinterpret_cast<float4*>(state + ((slot * H + h) * (int64_t)D) * D);
   float4 S[RPT];
@@ -72,10 +74,13 @@ gla_scan_kernel(const T* __restrict__ q, const T* __restrict__ k, const T* __res
     for (int idx = tid; idx < nt * D; idx += 256) {
       const int tt = idx / D, d = idx - tt * D;
       const int64_t tok = tb + tt;
-      s_q[tt][d] = scan_to_f32(q[(tok * H + h) * D + d]) * scale;
+      float qv = scan_to_f32(q[(tok * H + h) * D + d]);
       const int64_t kv_off = (tok * Hkv + hk) * D + d;
-      s_k[tt][d] = scan_to_f32(k[kv_off]);
-      s_d[tt][d] = expf(scan_to_f32(g[kv_off]));
+      float kv = scan_to_f32(k[kv_off]);
+      if (fu.relu_qk) { qv = fmaxf(qv, 0.f); kv = fmaxf(kv, 0.f); }
+      s_q[tt][d] = qv * scale;
+      s_k[tt][d] = kv;
+      s_d[tt][d] = expf(gla_gate<T>(scan_to_f32(g[kv_off]), fu));
       reinterpret_cast<float*>(&s_v[tt][0])[d] = scan_to_f32(v[kv_off]);
     }
     __syncthreads();
@@ -99,13 +104,33 @@ gla_scan_kernel(const T* __restrict__ q, const T* __restrict__ k, const T* __res
     }
     __syncthreads();
     // ---- finish the read-out: sum the row groups, one output element per thread and trip ----
-    for (int idx = tid; idx < nt * D; idx += 256) {
-      const int tt = idx / D, d = idx - tt * D;
-      const float* so = reinterpret_cast<const float*>(&s_o[tt][0][0]);
+    // (nt * D is a multiple of 32, so a warp is valid or idle as a whole; a token's D outputs
+    // sit in D/32 consecutive warps of one trip)
+    for (int base = 0, trip = 0; base < nt * D; base += 256, ++trip) {
+      const int idx = base + tid;
+      const bool valid = idx < nt * D;
+      const int tt = valid ? idx / D : 0, d = valid ? idx - tt * D : 0;
       float acc = 0.f;
+      if (valid) {
+        const float* so = reinterpret_cast<const float*>(&s_o[tt][0][0]);
 #pragma unroll
-      for (int gi = 0; gi < GROUPS; ++gi) acc += so[gi * D + d];
-      out[((int64_t)(tb + tt) * H + h) * D + d] = scan_from_f32<TO>(acc);
+        for (int gi = 0; gi < GROUPS; ++gi) acc += so[gi * D + d];
+      }
+      if (fu.norm_weight != nullptr) {
+        float sq = acc * acc;
+#pragma unroll
+        for (int off = 16; off > 0; off >>= 1) sq += __shfl_xor_sync(0xffffffffu, sq, off);
+        if ((tid & 31) == 0) s_sq[trip & 1][tid >> 5] = sq;
+        __syncthreads();
+        constexpr int WPT = D / 32;
+        const int w0 = ((tid >> 5) / WPT) * WPT;
+        float tot = 0.f;
+#pragma unroll
+        for (int w = 0; w < WPT; ++w) tot += s_sq[trip & 1][w0 + w];
+        acc = acc * rsqrtf(tot / D + fu.norm_eps) *
+              scan_to_f32(reinterpret_cast<const T*>(fu.norm_weight)[d]);
+      }
+      if (valid) out[((int64_t)(tb + tt) * H + h) * D + d] = scan_from_f32<TO>(acc);
     }
     // the next round's staging only touches s_q/s_k/s_d/s_v, and its first barrier orders the
     // reads of s_o above before the next writes to s_o
@@ -119,9 +144,12 @@ gla_scan_kernel(const T* __restrict__ q, const T* __restrict__ k, const T* __res
 extern "C" int sbk_gla_scan(const void* q, const void* k, const void* v, const void* g, int in_dtype,
                             const int32_t* query_start_loc, int n_seqs, float* state,
                             int64_t num_slots, const int64_t* slot_idx, const uint8_t* reset, int H,
-                            int Hkv, int D, float scale, void* out, int out_dtype, int32_t* status,
-                            void* stream) {
+                            int Hkv, int D, float scale, void* out, int out_dtype, int fuse_flags,
+                            float gate_normalizer, const void* norm_weight, float norm_eps,
+                            int32_t* status, void* stream) {
   using namespace sbk;
+  GlaFusion fu;
+  if (!make_gla_fusion(&fu, "sbk_gla_scan", fuse_flags, gate_normalizer, norm_weight, norm_eps)) return SBK_E_ARG;
   if (n_seqs < 0 || H <= 0 || Hkv <= 0 || H % Hkv != 0 || num_slots < 0) {
     set_error("sbk_gla_scan: bad head counts H=%d Hkv=%d or negative size", H, Hkv);
     return SBK_E_ARG;
@@ -153,7 +181,7 @@ extern "C" int sbk_gla_scan(const void* q, const void* k, const void* v, const v
   gla_scan_kernel<T, TO, DD><<<grid, 256, 0, st>>>((const T*)q, (const T*)k, (const T*)v,       \
                                                    (const T*)g, query_start_loc, state,         \
                                                    num_slots, slot_idx, reset, H, Hkv, scale,   \
-                                                   (TO*)out, status)
+                                                   (TO*)out, status, fu)
 #define SBK_SCAN_D(T, TO)                     \
   do {                                        \
     if (D == 128) SBK_SCAN_LAUNCH(T, TO, 128); \

@@ -25,6 +25,10 @@ __device__ __forceinline__ float from_f32<float>(float x) { return x; }
 template <>
 __device__ __forceinline__ __nv_bfloat16 from_f32<__nv_bfloat16>(float x) { return __float2bfloat16_rn(x); }
 
+// The element-wise neighbours of the step in the reference model can ride along (GlaFusion,
+// sbk_common.cuh): ReLU on q and k, g = logsigmoid(gate logits) / normalizer, and the per-head
+// RMS norm of the output (vllm_hymeta/model_for_7B/gla_attention.py:250-262 and :233).
+//
 // D = 128: 32 threads span a row (float4 each), 8 row groups, 16 rows per thread.
 // D = 64 : 16 threads span a row, 16 row groups, 4 rows per thread.
 template <typename T, typename TO, int D>
@@ -32,7 +36,7 @@ __global__ void __launch_bounds__(256)
 gla_step_kernel(const T* __restrict__ q, const T* __restrict__ k, const T* __restrict__ v,
                 const T* __restrict__ g, float* __restrict__ state, int64_t num_slots,
                 const int64_t* __restrict__ slot_idx, int H, int Hkv, float scale,
-                TO* __restrict__ out, int32_t* status) {
+                TO* __restrict__ out, int32_t* status, const GlaFusion fu) {
   constexpr int TPR = D / 4;          // threads per state row
   constexpr int GROUPS = 256 / TPR;   // row groups
   constexpr int RPT = D / GROUPS;     // rows per thread
@@ -51,10 +55,13 @@ gla_step_kernel(const T* __restrict__ q, const T* __restrict__ k, const T* __res
 
   const int tid = threadIdx.x;
   if (tid < D) {
-    s_q[tid] = to_f32(q[((int64_t)b * H + h) * D + tid]) * scale;
+    float qv = to_f32(q[((int64_t)b * H + h) * D + tid]);
     const int64_t kv_off = ((int64_t)b * Hkv + hk) * D + tid;
-    s_k[tid] = to_f32(k[kv_off]);
-    s_decay[tid] = expf(to_f32(g[kv_off]));
+    float kv = to_f32(k[kv_off]);
+    if (fu.relu_qk) { qv = fmaxf(qv, 0.f); kv = fmaxf(kv, 0.f); }
+    s_q[tid] = qv * scale;
+    s_k[tid] = kv;
+    s_decay[tid] = expf(gla_gate<T>(to_f32(g[kv_off]), fu));
   }
   const int c4 = tid % TPR;
   const int r0 = tid / TPR;
@@ -88,13 +95,26 @@ gla_step_kernel(const T* __restrict__ q, const T* __restrict__ k, const T* __res
   }
   s_o[r0][c4] = o;
   __syncthreads();
+  float acc = 0.f;
   if (tid < D) {
     const float* so = reinterpret_cast<const float*>(&s_o[0][0]);
-    float acc = 0.f;
 #pragma unroll
     for (int gi = 0; gi < GROUPS; ++gi) acc += so[gi * D + tid];
-    out[((int64_t)b * H + h) * D + tid] = from_f32<TO>(acc);
   }
+  if (fu.norm_weight != nullptr) {
+    // per-head RMS norm of the D outputs (they sit in threads 0..D-1)
+    float sq = tid < D ? acc * acc : 0.f;
+#pragma unroll
+    for (int off = 16; off > 0; off >>= 1) sq += __shfl_xor_sync(0xffffffffu, sq, off);
+    __syncthreads();               // everyone is done reading s_q
+    if ((tid & 31) == 0) s_q[tid >> 5] = sq;
+    __syncthreads();
+    float tot = 0.f;
+#pragma unroll
+    for (int w = 0; w < D / 32; ++w) tot += s_q[w];
+    if (tid < D) acc = acc * rsqrtf(tot / D + fu.norm_eps) * to_f32(reinterpret_cast<const T*>(fu.norm_weight)[tid]);
+  }
+  if (tid < D) out[((int64_t)b * H + h) * D + tid] = from_f32<TO>(acc);
 }
 
 }  // namespace sbk
@@ -102,8 +122,11 @@ gla_step_kernel(const T* __restrict__ q, const T* __restrict__ k, const T* __res
 extern "C" int sbk_gla_step(const void* q, const void* k, const void* v, const void* g,
                             int in_dtype, float* state, int64_t num_slots,
                             const int64_t* slot_idx, int B, int H, int Hkv, int D, float scale,
-                            void* out, int out_dtype, int32_t* status, void* stream) {
+                            void* out, int out_dtype, int fuse_flags, float gate_normalizer,
+                            const void* norm_weight, float norm_eps, int32_t* status, void* stream) {
   using namespace sbk;
+  GlaFusion fu;
+  if (!make_gla_fusion(&fu, "sbk_gla_step", fuse_flags, gate_normalizer, norm_weight, norm_eps)) return SBK_E_ARG;
   if (B < 0 || H <= 0 || Hkv <= 0 || H % Hkv != 0 || num_slots < 0) {
     set_error("sbk_gla_step: bad head counts H=%d Hkv=%d or negative size", H, Hkv);
     return SBK_E_ARG;
@@ -134,7 +157,7 @@ extern "C" int sbk_gla_step(const void* q, const void* k, const void* v, const v
 #define SBK_GLA_LAUNCH(T, TO, DD)                                                               \
   gla_step_kernel<T, TO, DD><<<grid, 256, 0, st>>>((const T*)q, (const T*)k, (const T*)v,       \
                                                    (const T*)g, state, num_slots, slot_idx, H,  \
-                                                   Hkv, scale, (TO*)out, status)
+                                                   Hkv, scale, (TO*)out, status, fu)
 #define SBK_GLA_DISPATCH_D(T, TO)         \
   do {                                    \
     if (D == 128) SBK_GLA_LAUNCH(T, TO, 128); \

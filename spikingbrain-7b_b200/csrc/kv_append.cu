@@ -36,33 +36,8 @@ kv_append_kernel(const uint8_t* __restrict__ key, const uint8_t* __restrict__ va
     return;
   }
   // ---- retirement: blocks wholly before the first token still visible ----
-  if (block_tables == nullptr) return;
-  const int b = (bid - T) * 128 + threadIdx.x;
-  if (b >= B) return;
-  const int L = seq_lens[b];
-  int n_new = query_start_loc ? (query_start_loc[b + 1] - query_start_loc[b]) : 1;
-  if (n_new < 1) n_new = 1;  // a row without a query this step keeps what its last query saw
-  const int t0 = first_visible(L, n_new, window_left);
-  int first_live = t0 / block_size;
-  if (first_live > max_blocks) first_live = max_blocks;
-  int32_t* row = block_tables + (int64_t)b * max_blocks;
-  int32_t* rout = retired_out ? retired_out + (int64_t)b * max_retired : nullptr;
-  int cnt = 0;
-  // Blocks retired by earlier calls are already -1, so walk back from the window edge until
-  // the first entry that is already retired.
-  int j = first_live - 1;
-  while (j >= 0 && row[j] >= 0) --j;
-  for (int i = j + 1; i < first_live; ++i) {
-    const int32_t id = row[i];
-    row[i] = -1;
-    if (rout) {
-      if (cnt < max_retired) rout[cnt] = id;
-      else raise_status(status, SBK_ST_RETIRE_OVERFLOW);
-    }
-    ++cnt;
-  }
-  if (rout)
-    for (int i = cnt; i < max_retired; ++i) rout[i] = -1;
+  retire_rows((bid - T) * 128 + threadIdx.x, block_tables, max_blocks, seq_lens, query_start_loc, B,
+              window_left, block_size, retired_out, max_retired, status);
 }
 
 // Dense gather of the visible window: out[b, h, i, :] = cache[token t0+i, head h].

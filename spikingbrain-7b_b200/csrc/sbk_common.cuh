@@ -141,11 +141,71 @@ __device__ __forceinline__ void st_stream_f4(float4* p, const float4& v) {
                : "memory");
 }
 
+// ---- optional element-wise work fused into the GLA kernels ---------------------------------
+struct GlaFusion {
+  int relu_qk;              // q <- relu(q), k <- relu(k)            (feature map of the model)
+  int gate_logits;          // g <- logsigmoid(g) / gate_normalizer  (g arrives as gate logits)
+  float gate_normalizer;
+  const void* norm_weight;  // [D] in the input dtype: o <- rms_norm(o) * weight per head, or NULL
+  float norm_eps;
+};
+bool make_gla_fusion(GlaFusion* fu, const char* who, int flags, float gate_normalizer,
+                     const void* norm_weight, float norm_eps);
+
+// The log-decay of a key row. With gate logits, logsigmoid is evaluated in fp32 and rounded to
+// the input type before the division, which is what the reference's `F.logsigmoid(gk) / 16` on a
+// bf16 tensor produces.
+template <typename T>
+__device__ __forceinline__ float gla_gate(float x, const GlaFusion& fu) {
+  if (!fu.gate_logits) return x;
+  float ls = fminf(x, 0.f) - log1pf(expf(-fabsf(x)));
+  if (sizeof(T) == 2) ls = __bfloat162float(__float2bfloat16_rn(ls));
+  float gq = ls / fu.gate_normalizer;
+  if (sizeof(T) == 2) gq = __bfloat162float(__float2bfloat16_rn(gq));
+  return gq;
+}
+
 // first token a decode query at position seq_len-1 can still see
 __device__ __host__ __forceinline__ int first_visible(int seq_len, int n_new, int window_left) {
   if (window_left < 0) return 0;
   int t0 = seq_len - n_new - window_left;
   return t0 > 0 ? t0 : 0;
+}
+
+// Window retirement of one sequence's block-table row (thread b of the retirement CTAs of the
+// append kernels): entries of blocks wholly before the first visible token become -1 and their
+// ids are listed in retired_out[b, :].
+__device__ __forceinline__ void retire_rows(int b, int32_t* __restrict__ block_tables, int max_blocks,
+                                            const int32_t* __restrict__ seq_lens,
+                                            const int32_t* __restrict__ query_start_loc, int B,
+                                            int window_left, int block_size,
+                                            int32_t* __restrict__ retired_out, int max_retired,
+                                            int32_t* status) {
+  if (block_tables == nullptr || b >= B) return;
+  const int L = seq_lens[b];
+  int n_new = query_start_loc ? (query_start_loc[b + 1] - query_start_loc[b]) : 1;
+  if (n_new < 1) n_new = 1;  // a row without a query this step keeps what its last query saw
+  const int t0 = first_visible(L, n_new, window_left);
+  int first_live = t0 / block_size;
+  if (first_live > max_blocks) first_live = max_blocks;
+  int32_t* row = block_tables + (int64_t)b * max_blocks;
+  int32_t* rout = retired_out ? retired_out + (int64_t)b * max_retired : nullptr;
+  int cnt = 0;
+  // Blocks retired by earlier calls are already -1, so walk back from the window edge until
+  // the first entry that is already retired.
+  int j = first_live - 1;
+  while (j >= 0 && row[j] >= 0) --j;
+  for (int i = j + 1; i < first_live; ++i) {
+    const int32_t id = row[i];
+    row[i] = -1;
+    if (rout) {
+      if (cnt < max_retired) rout[cnt] = id;
+      else raise_status(status, SBK_ST_RETIRE_OVERFLOW);
+    }
+    ++cnt;
+  }
+  if (rout)
+    for (int i = cnt; i < max_retired; ++i) rout[i] = -1;
 }
 
 }  // namespace sbk

@@ -96,11 +96,13 @@ def my_fused_recurrent_gla(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, g:
                            scale: Optional[float] = None, initial_state: torch.Tensor = None,
                            output_final_state: bool = False, reverse: bool = False,
                            status: Optional[torch.Tensor] = None,
-                           out: Optional[torch.Tensor] = None) -> torch.Tensor:
+                           out: Optional[torch.Tensor] = None, **fused) -> torch.Tensor:
     """Single-token GLA decode, in place on ``kv_caches`` [slots, H, D, D] (float32).
     q [B, H, 1, D]; k, v, g [B, H, 1, D] or, un-repeated, [B, Hkv, 1, D]; returns o [B, H, D]
     in q's dtype (written into ``out`` [B, H, D] when given, e.g. a static buffer of a captured
-    graph). Rows whose slot is -1 are left alone and their output row is unspecified."""
+    graph). Rows whose slot is -1 are left alone and their output row is unspecified.
+    ``fused``: the keyword arguments of ops.gla_step that fold the layer's neighbours in
+    (relu_qk, gate_logit_normalizer, norm_weight, norm_eps); see gla_decode_layer."""
     if q.dim() != 4 or q.shape[2] != 1:
         raise ValueError("q must be [B, H, 1, D] (one token per sequence)")
     if initial_state is not None or output_final_state or reverse:
@@ -111,24 +113,46 @@ def my_fused_recurrent_gla(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, g:
     sq = lambda t: t.reshape(B, t.shape[1], D).contiguous()
     if slot_idx is not None and slot_idx.dtype != torch.int64:
         slot_idx = slot_idx.to(torch.int64)
-    return ops.gla_step(sq(q), sq(k), sq(v), sq(g), kv_caches, slot_idx, scale=scale, out=out, status=status)
+    return ops.gla_step(sq(q), sq(k), sq(v), sq(g), kv_caches, slot_idx, scale=scale, out=out,
+                        status=status, **fused)
+
+
+def gla_decode_layer(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, gk: torch.Tensor,
+                     kv_caches: torch.Tensor, slot_idx: torch.Tensor, g_norm_weight: torch.Tensor, *,
+                     gate_logit_normalizer: float = 16.0, norm_eps: float = 1e-5,
+                     scale: Optional[float] = None, out: Optional[torch.Tensor] = None,
+                     status: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """Decode branch of GatedLinearAttention.forward between the projections and the output gate
+    (vllm_hymeta/model_for_7B/gla_attention.py:250-267 and _decode_infer :213-235) in ONE launch:
+    q [B, H, D] and k, v, gk [B, Hkv, D] are the projection outputs as they come (no feature map,
+    gate logits, kv heads not repeated); the kernel applies relu to q and k, turns gk into
+    logsigmoid(gk) / gate_logit_normalizer, steps the slots' states, and applies g_norm
+    (``g_norm_weight`` [D]) to the read-out. Returns o [B, H, D] in q's dtype."""
+    if slot_idx is not None and slot_idx.dtype != torch.int64:
+        slot_idx = slot_idx.to(torch.int64)
+    return ops.gla_step(q.contiguous(), k.contiguous(), v.contiguous(), gk.contiguous(), kv_caches,
+                        slot_idx, scale=scale, out=out, status=status, relu_qk=True,
+                        gate_logit_normalizer=gate_logit_normalizer, norm_weight=g_norm_weight,
+                        norm_eps=norm_eps)
 
 
 def gla_prefill_scan(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, g: torch.Tensor,
                      kv_caches: torch.Tensor, slot_idx: torch.Tensor, query_start_loc: torch.Tensor,
                      context_lens: Optional[torch.Tensor] = None, scale: Optional[float] = None,
-                     status: Optional[torch.Tensor] = None) -> torch.Tensor:
+                     status: Optional[torch.Tensor] = None, **fused) -> torch.Tensor:
     """The prefill half of GatedLinearAttention._prefill_and_mix_infer
     (vllm_hymeta/model_for_7B/gla_attention.py:179-211) in one launch for all prompt sequences:
     q [T, H, D], k/v/g [T, H or Hkv, D] are the prompt tokens of `len(slot_idx)` sequences laid
     end to end (`query_start_loc`); each sequence's state slot is advanced over its tokens and the
     outputs [T, H, D] returned. A sequence whose `context_lens` entry is 0 is a new prompt and
     starts from a zero state whatever its slot holds (the reference zeroes such slots beforehand,
-    modeling_gla_swa.py:391-414, and treats NaN-filled slots as empty, gla_attention.py:196-198)."""
+    modeling_gla_swa.py:391-414, and treats NaN-filled slots as empty, gla_attention.py:196-198).
+    ``fused``: relu_qk, gate_logit_normalizer, norm_weight, norm_eps of ops.gla_scan."""
     reset = None
     if context_lens is not None:
         reset = (context_lens == 0).to(torch.uint8)
     if slot_idx.dtype != torch.int64:
         slot_idx = slot_idx.to(torch.int64)
     return ops.gla_scan(q.contiguous(), k.contiguous(), v.contiguous(), g.contiguous(), kv_caches,
-                        query_start_loc.to(torch.int32), slot_idx, reset, scale=scale, status=status)
+                        query_start_loc.to(torch.int32), slot_idx, reset, scale=scale, status=status,
+                        **fused)

@@ -81,13 +81,17 @@ class _PagedWindow:
         if (int(m.lens[0]) + n + self.bs - 1) // self.bs > self.max_blocks:
             raise RuntimeError(f"{n} new tokens do not fit the table of a window-{self.window} layer")
 
-    def append(self, k: torch.Tensor, v: torch.Tensor) -> None:
-        """k, v: [B, kvh, n, D] -- the reference layout of `attn_state`."""
-        n = k.shape[-2]
+    def append(self, k: torch.Tensor, v: torch.Tensor, rope=None) -> Optional[torch.Tensor]:
+        """k, v: [B, kvh, n, D] -- the reference layout of `attn_state`. ``rope`` = (q [B, H, n, D]
+        or None, position_ids [B, n], cos_sin_cache): k arrives un-rotated and is rotated on its way
+        into the cache by the same launch, which also rotates q; the rotated q is returned."""
+        n = n_in = k.shape[-2]
         W = self.window
         if self.n_cached == 0:
             if W is not None and n > W:  # first insert keeps the last `window` tokens (cache.py:81-83)
-                k, v, n = k[..., -W:, :], v[..., -W:, :], W
+                n = W
+                if rope is None:
+                    k, v = k[..., -W:, :], v[..., -W:, :]
             n_cached = n
         elif W is not None and self.n_cached == W:
             if n > W:
@@ -109,11 +113,24 @@ class _PagedWindow:
         self.lens_d.copy_(torch.from_numpy(plan.seq_lens), non_blocking=True)
         qsl = torch.from_numpy(plan.query_start_loc).to(self.device, non_blocking=True)
         # token-major rows [T, kvh, D]; a view for one new token, a copy for a prompt chunk
-        kt = k.transpose(1, 2).reshape(self.B * n, self.kvh, self.D).contiguous()
-        vt = v.transpose(1, 2).reshape(self.B * n, self.kvh, self.D).contiguous()
-        ops.kv_append(kt, vt, self.kv[0], self.kv[1], slots, block_tables=self.table_d,
-                      seq_lens=self.lens_d, query_start_loc=qsl, window_left=self.mgr.window_left,
-                      status=self.status)
+        tm = lambda t: t.transpose(1, 2).reshape(self.B * t.shape[-2], t.shape[1], self.D).contiguous()
+        kt, vt = tm(k), tm(v)
+        if rope is None:
+            ops.kv_append(kt, vt, self.kv[0], self.kv[1], slots, block_tables=self.table_d,
+                          seq_lens=self.lens_d, query_start_loc=qsl, window_left=self.mgr.window_left,
+                          status=self.status)
+            return None
+        q, position_ids, table = rope
+        if n_in != n:  # prompt longer than the window: every token is rotated, the last W are cached
+            full = torch.full((self.B, n_in), -1, dtype=torch.int64, device=self.device)
+            full[:, n_in - n:] = slots.view(self.B, n)
+            slots = full.view(-1)
+        qt = tm(q) if q is not None else None
+        ops.rope_kv_append(qt, kt, vt, self.kv[0], self.kv[1], slots,
+                           position_ids.to(torch.int64).expand(self.B, n_in).reshape(-1).contiguous(), table,
+                           block_tables=self.table_d, seq_lens=self.lens_d, query_start_loc=qsl,
+                           window_left=self.mgr.window_left, status=self.status)
+        return None if qt is None else qt.view(self.B, n_in, q.shape[1], self.D).transpose(1, 2)
 
     def gather(self) -> Tuple[torch.Tensor, torch.Tensor]:
         return ops.kv_gather(self.kv[0], self.kv[1], self.table_d, self.lens_d, self.n_cached,
@@ -181,16 +198,17 @@ class Cache(transformers.cache_utils.Cache):
                offset: Optional[int] = 1, cache_kwargs: Optional[Dict[str, Any]] = None) -> Dict[str, Any]:
         if layer_idx == 0:
             self._seen_tokens += offset
-        window = None
+        window = rope = None
         if attn_state is not None:
             window = (cache_kwargs or {}).get("window_size", None)
+            rope = (cache_kwargs or {}).get("rotary", None)
             if not isinstance(attn_state, tuple) or len(attn_state) != 2:
                 raise ValueError("`attn_state` must be a tuple of two tensors for key/value states")
         if len(self.states) <= layer_idx:
             paged = None
             if attn_state is not None:
                 paged = self._new_paged(attn_state, window)
-                paged.append(*attn_state)
+                self._rotated_q = paged.append(*attn_state, rope=rope)
             state = _LayerState(recurrent_state=recurrent_state, conv_state=conv_state, paged=paged)
             self.states.append(state)
             return state
@@ -207,7 +225,7 @@ class Cache(transformers.cache_utils.Cache):
                     dict.__setitem__(state, "attn_state", None)
             if state.paged.window != window:
                 raise ValueError("window_size changed between updates of one layer")
-            state.paged.append(*attn_state)
+            self._rotated_q = state.paged.append(*attn_state, rope=rope)
         if conv_state is not None:
             dict.__setitem__(state, "conv_state", conv_state)
         return state
@@ -235,6 +253,20 @@ class Cache(transformers.cache_utils.Cache):
         return cache
 
     # ------------------------------------------------------------------ fast paths
+    def update_rotary(self, q: Optional[torch.Tensor], k: torch.Tensor, v: torch.Tensor,
+                      position_ids: torch.Tensor, cos_sin_cache: torch.Tensor, layer_idx: int,
+                      window_size: Optional[int] = None) -> Optional[torch.Tensor]:
+        """`apply_rotary_pos_emb(q, k, cos, sin)` followed by `update(attn_state=(k, v), layer_idx,
+        offset=n, cache_kwargs={"window_size": W})` (hf_7B_model/window_attention.py:161-175) as one
+        launch: q [B, H, n, D], k and v [B, kvh, n, D] come un-rotated, `position_ids` [B, n] (or
+        [1, n]) index ``cos_sin_cache`` (ops.build_cos_sin_cache). Returns the rotated q
+        [B, H, n, D] (for n == 1 contiguous input it is q itself, rotated in place)."""
+        self._rotated_q = None
+        self.update(attn_state=(k, v), layer_idx=layer_idx, offset=k.shape[-2],
+                    cache_kwargs={"window_size": window_size, "rotary": (q, position_ids, cos_sin_cache)})
+        q_rot, self._rotated_q = self._rotated_q, None
+        return q_rot
+
     def swa_decode(self, q: torch.Tensor, layer_idx: int, scale: Optional[float] = None,
                    out: Optional[torch.Tensor] = None) -> torch.Tensor:
         """Attention of one query token per sequence over the layer's cached window, the
@@ -249,35 +281,38 @@ class Cache(transformers.cache_utils.Cache):
         return state.paged.decode(q.contiguous(), scale, out)
 
     def gla_step(self, q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, g: torch.Tensor,
-                 layer_idx: int, scale: Optional[float] = None) -> torch.Tensor:
+                 layer_idx: int, scale: Optional[float] = None, **fused) -> torch.Tensor:
         """One-token GLA step of layer `layer_idx`, in place on its recurrent state:
         what `fused_recurrent_gla(q, k, v, g, initial_state=S, output_final_state=True)`
         followed by `update(recurrent_state=S', layer_idx, offset=1)` does in
         hf_7B_model/gla_attention.py:153-168, without allocating a new state.
-        q [B, H, 1, D] or [B, H, D]; k, v, g likewise with H or Hkv heads. Returns o [B, H, D]."""
+        q [B, H, 1, D] or [B, H, D]; k, v, g likewise with H or Hkv heads. Returns o [B, H, D].
+        ``fused`` (relu_qk, gate_logit_normalizer, norm_weight, norm_eps of ops.gla_step) folds in
+        the layer's feature map, gate and g_norm (:134-145, :170)."""
         sq = lambda t: (t.squeeze(2) if t.dim() == 4 else t).contiguous()
         q, k, v, g = sq(q), sq(k), sq(v), sq(g)
         B, H, D = q.shape
         S = self[layer_idx]["recurrent_state"] if layer_idx < len(self) else None
         if S is None:
             S = torch.zeros(B, H, D, D, dtype=torch.float32, device=q.device)
-        o = ops.gla_step(q, k, v, g, S, scale=scale)
+        o = ops.gla_step(q, k, v, g, S, scale=scale, **fused)
         self.update(recurrent_state=S, layer_idx=layer_idx, offset=1)
         return o
 
     def gla_chunk(self, q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, g: torch.Tensor,
-                  layer_idx: int, scale: Optional[float] = None) -> torch.Tensor:
+                  layer_idx: int, scale: Optional[float] = None, **fused) -> torch.Tensor:
         """A run of T tokens through the GLA layer `layer_idx` with state carry: what
         `chunk_gla(q, k, v, g, initial_state=S, output_final_state=True)` followed by
         `update(recurrent_state=S', layer_idx, offset=T)` does in hf_7B_model/gla_attention.py:155-168.
         q [B, H, T, D] (the reference's head-first layout), k/v/g [B, H or Hkv, T, D];
-        returns o [B, H, T, D]. The state tensor of the layer is advanced in place."""
+        returns o [B, H, T, D]. The state tensor of the layer is advanced in place. ``fused`` as
+        in gla_step."""
         B, H, T, D = q.shape
         tm = lambda t: t.transpose(1, 2).reshape(B * T, t.shape[1], D).contiguous()   # token-major rows
         S = self[layer_idx]["recurrent_state"] if layer_idx < len(self) else None
         if S is None:
             S = torch.zeros(B, H, D, D, dtype=torch.float32, device=q.device)
         qsl = torch.arange(B + 1, dtype=torch.int32, device=q.device) * T
-        o = ops.gla_scan(tm(q), tm(k), tm(v), tm(g), S, qsl, scale=scale)
+        o = ops.gla_scan(tm(q), tm(k), tm(v), tm(g), S, qsl, scale=scale, **fused)
         self.update(recurrent_state=S, layer_idx=layer_idx, offset=T)
         return o.view(B, T, H, D).transpose(1, 2)

@@ -49,16 +49,11 @@ def _cache_geometry(k_cache: torch.Tensor, v_cache: torch.Tensor) -> Tuple[int, 
     return nb, bs, kvh, d, k_cache.stride(0) * k_cache.element_size()
 
 
-def kv_append(key: torch.Tensor, value: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor,
-              slot_mapping: torch.Tensor, *, block_tables: Optional[torch.Tensor] = None,
-              seq_lens: Optional[torch.Tensor] = None,
-              query_start_loc: Optional[torch.Tensor] = None, window_left: int = -1,
-              retired_out: Optional[torch.Tensor] = None,
-              status: Optional[torch.Tensor] = None) -> None:
-    """Write key/value [T, kvh, D] into the paged cache at ``slot_mapping`` and, when
-    ``block_tables`` is given, replace table entries of blocks that left the window by -1
-    (their ids are listed in ``retired_out`` [B, max_retired])."""
-    _need_cuda(key, value, k_cache, v_cache, slot_mapping, block_tables, seq_lens, retired_out, status)
+def _append_args(key, value, k_cache, v_cache, slot_mapping, block_tables, seq_lens, query_start_loc,
+                 retired_out):
+    """Shared validation of the two append entry points -> (nb, bs, kvh, d, bstride, T, B,
+    max_blocks, max_ret, es, tok_stride)."""
+    _need_cuda(key, value, k_cache, v_cache, slot_mapping, block_tables, seq_lens, query_start_loc, retired_out)
     nb, bs, kvh, d, bstride = _cache_geometry(k_cache, v_cache)
     T = key.shape[0]
     if key.shape != (T, kvh, d) or value.shape != key.shape:
@@ -88,11 +83,79 @@ def kv_append(key: torch.Tensor, value: torch.Tensor, k_cache: torch.Tensor, v_c
             max_ret = retired_out.shape[1]
     es = k_cache.element_size()
     tok_stride = (key.stride(0) if T else kvh * d) * es
+    return nb, bs, kvh, d, bstride, T, B, max_blocks, max_ret, es, tok_stride
+
+
+def kv_append(key: torch.Tensor, value: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor,
+              slot_mapping: torch.Tensor, *, block_tables: Optional[torch.Tensor] = None,
+              seq_lens: Optional[torch.Tensor] = None,
+              query_start_loc: Optional[torch.Tensor] = None, window_left: int = -1,
+              retired_out: Optional[torch.Tensor] = None,
+              status: Optional[torch.Tensor] = None) -> None:
+    """Write key/value [T, kvh, D] into the paged cache at ``slot_mapping`` and, when
+    ``block_tables`` is given, replace table entries of blocks that left the window by -1
+    (their ids are listed in ``retired_out`` [B, max_retired])."""
+    _need_cuda(status)
+    nb, bs, kvh, d, bstride, T, B, max_blocks, max_ret, es, tok_stride = _append_args(
+        key, value, k_cache, v_cache, slot_mapping, block_tables, seq_lens, query_start_loc, retired_out)
     rc = _abi.lib.sbk_kv_append(
         _ptr(key), _ptr(value), _ptr(k_cache), _ptr(v_cache), _ptr(slot_mapping), T, kvh, d, es,
         tok_stride, nb, bs, bstride, _ptr(block_tables), max_blocks, _ptr(seq_lens),
         _ptr(query_start_loc), B, window_left, _ptr(retired_out), max_ret, _ptr(status), _stream())
     _abi.check("sbk_kv_append", rc)
+    global LAUNCHES
+    LAUNCHES += 1 if (T or B) else 0
+
+
+def build_cos_sin_cache(rot_dim: int, max_position: int, base: float = 10000.0,
+                        dtype: torch.dtype = torch.bfloat16, device="cuda") -> torch.Tensor:
+    """The [max_position, rot_dim] cos|sin table sbk_rope_kv_append reads, computed as
+    GLAswaRotaryEmbedding._compute_cos_sin_cache does (vllm_hymeta/model_for_7B/
+    modeling_gla_swa.py:66-79): fp32 angles position x base^(-2i/rot_dim), cos and sin taken in
+    fp32, then one cast to ``dtype``. The HF RotaryEmbedding (hf_7B_model/window_attention.py:
+    23-47) produces the same cos/sin values per call."""
+    inv_freq = 1.0 / (base ** (torch.arange(0, rot_dim, 2, dtype=torch.float, device=device) / rot_dim))
+    t = torch.arange(max_position, dtype=torch.float, device=device)
+    freqs = torch.einsum("i,j -> ij", t, inv_freq)
+    return torch.cat((freqs.cos(), freqs.sin()), dim=-1).to(dtype).contiguous()
+
+
+def rope_kv_append(query: Optional[torch.Tensor], key: torch.Tensor, value: torch.Tensor,
+                   k_cache: torch.Tensor, v_cache: torch.Tensor, slot_mapping: torch.Tensor,
+                   positions: torch.Tensor, cos_sin_cache: torch.Tensor, *, key_in_place: bool = False,
+                   block_tables: Optional[torch.Tensor] = None, seq_lens: Optional[torch.Tensor] = None,
+                   query_start_loc: Optional[torch.Tensor] = None, window_left: int = -1,
+                   retired_out: Optional[torch.Tensor] = None,
+                   status: Optional[torch.Tensor] = None) -> None:
+    """kv_append with the NeoX rotary embedding folded in: ``query`` [T, H, D] (optional) is rotated
+    in place, ``key`` [T, kvh, D] is rotated on its way into the cache (and in place too with
+    ``key_in_place``), ``value`` is copied. ``positions`` [T] int64 index ``cos_sin_cache``
+    [max_position, rot_dim] (build_cos_sin_cache)."""
+    _need_cuda(query, positions, cos_sin_cache, status)
+    nb, bs, kvh, d, bstride, T, B, max_blocks, max_ret, es, tok_stride = _append_args(
+        key, value, k_cache, v_cache, slot_mapping, block_tables, seq_lens, query_start_loc, retired_out)
+    if k_cache.dtype not in _DTYPE_CODE:
+        raise ValueError("the fused rotary append takes bf16 or fp32 tensors")
+    if cos_sin_cache.dim() != 2 or cos_sin_cache.dtype != k_cache.dtype or not cos_sin_cache.is_contiguous():
+        raise ValueError("cos_sin_cache must be contiguous [max_position, rot_dim] in the cache dtype")
+    max_pos, rot_dim = cos_sin_cache.shape
+    if positions.dtype != torch.int64 or positions.numel() != T or not positions.is_contiguous():
+        raise ValueError("positions must be a contiguous int64 tensor with one entry per token")
+    H = q_stride = 0
+    if query is not None:
+        if query.dim() != 3 or query.shape[0] != T or query.shape[2] != d or query.dtype != k_cache.dtype:
+            raise ValueError(f"query must be [T, H, {d}] in the cache dtype")
+        H = query.shape[1]
+        if T and ((d > 1 and query.stride(2) != 1) or (H > 1 and query.stride(1) != d)):
+            raise ValueError("query rows must be contiguous")
+        q_stride = (query.stride(0) if T else H * d) * es
+    rc = _abi.lib.sbk_rope_kv_append(
+        _ptr(query), H, q_stride, _ptr(key), _ptr(value), int(key_in_place), _ptr(k_cache), _ptr(v_cache),
+        _ptr(slot_mapping), _ptr(positions), _ptr(cos_sin_cache), rot_dim, max_pos, T, kvh, d,
+        _DTYPE_CODE[k_cache.dtype], tok_stride, nb, bs, bstride, _ptr(block_tables), max_blocks,
+        _ptr(seq_lens), _ptr(query_start_loc), B, window_left, _ptr(retired_out), max_ret, _ptr(status),
+        _stream())
+    _abi.check("sbk_rope_kv_append", rc)
     global LAUNCHES
     LAUNCHES += 1 if (T or B) else 0
 
@@ -229,13 +292,40 @@ def swa_decode(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor,
     return out
 
 
+GLA_RELU_QK = 1
+GLA_GATE_LOGITS = 2
+
+
+def _gla_fusion_args(q, D, relu_qk, gate_logit_normalizer, norm_weight):
+    flags = GLA_RELU_QK if relu_qk else 0
+    gnorm = 0.0
+    if gate_logit_normalizer is not None:
+        if not gate_logit_normalizer > 0:
+            raise ValueError("gate_logit_normalizer must be positive")
+        flags |= GLA_GATE_LOGITS
+        gnorm = float(gate_logit_normalizer)
+    if norm_weight is not None and (norm_weight.shape != (D,) or norm_weight.dtype != q.dtype
+                                    or not norm_weight.is_contiguous()):
+        raise ValueError("norm_weight must be contiguous [D] in the dtype of q")
+    return flags, gnorm
+
+
 def gla_step(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, g: torch.Tensor,
              state: torch.Tensor, slot_idx: Optional[torch.Tensor] = None, *,
              scale: Optional[float] = None, out: Optional[torch.Tensor] = None,
-             out_dtype: Optional[torch.dtype] = None,
+             out_dtype: Optional[torch.dtype] = None, relu_qk: bool = False,
+             gate_logit_normalizer: Optional[float] = None,
+             norm_weight: Optional[torch.Tensor] = None, norm_eps: float = 1e-5,
              status: Optional[torch.Tensor] = None) -> torch.Tensor:
-    """In-place GLA state step on ``state`` [slots, H, D, D] fp32; q [B, H, D], k/v/g [B, Hkv, D]."""
-    _need_cuda(q, k, v, g, state, slot_idx, out, status)
+    """In-place GLA state step on ``state`` [slots, H, D, D] fp32; q [B, H, D], k/v/g [B, Hkv, D].
+
+    Fused neighbours of the reference layer (all off by default): ``relu_qk`` applies the feature
+    map to q and k; ``gate_logit_normalizer`` makes ``g`` gate logits, turned into
+    ``logsigmoid(g) / normalizer`` in the kernel; ``norm_weight`` [D] applies the per-head RMS norm
+    (g_norm) to the read-out."""
+    _need_cuda(q, k, v, g, state, slot_idx, out, status, norm_weight)
+    flags, gnorm = _gla_fusion_args(q, D=q.shape[-1], relu_qk=relu_qk,
+                                    gate_logit_normalizer=gate_logit_normalizer, norm_weight=norm_weight)
     if q.dim() != 3 or k.dim() != 3:
         raise ValueError("q must be [B, H, D] and k, v, g [B, Hkv, D]")
     B, H, D = q.shape
@@ -261,7 +351,7 @@ def gla_step(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, g: torch.Tensor,
     rc = _abi.lib.sbk_gla_step(
         _ptr(q), _ptr(k), _ptr(v), _ptr(g), _DTYPE_CODE[q.dtype], _ptr(state), state.shape[0],
         _ptr(slot_idx), B, H, Hkv, D, float(scale), _ptr(out), _DTYPE_CODE[out.dtype],
-        _ptr(status), _stream())
+        flags, gnorm, _ptr(norm_weight), float(norm_eps), _ptr(status), _stream())
     _abi.check("sbk_gla_step", rc)
     global LAUNCHES
     LAUNCHES += 1 if B else 0
@@ -272,11 +362,16 @@ def gla_scan(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, g: torch.Tensor,
              query_start_loc: torch.Tensor, slot_idx: Optional[torch.Tensor] = None,
              reset: Optional[torch.Tensor] = None, *, scale: Optional[float] = None,
              out: Optional[torch.Tensor] = None, out_dtype: Optional[torch.dtype] = None,
+             relu_qk: bool = False, gate_logit_normalizer: Optional[float] = None,
+             norm_weight: Optional[torch.Tensor] = None, norm_eps: float = 1e-5,
              status: Optional[torch.Tensor] = None) -> torch.Tensor:
     """GLA over runs of tokens with state carry. q [T, H, D], k/v/g [T, Hkv, D] token-major;
     sequence s owns rows query_start_loc[s]:query_start_loc[s+1]; ``state`` [slots, H, D, D] fp32 is
-    advanced in place; ``reset`` [n_seqs] uint8/bool marks sequences that start from zero."""
-    _need_cuda(q, k, v, g, state, query_start_loc, slot_idx, reset, out, status)
+    advanced in place; ``reset`` [n_seqs] uint8/bool marks sequences that start from zero. The
+    fused neighbours (``relu_qk``, ``gate_logit_normalizer``, ``norm_weight``) are those of gla_step."""
+    _need_cuda(q, k, v, g, state, query_start_loc, slot_idx, reset, out, status, norm_weight)
+    flags, gnorm = _gla_fusion_args(q, D=q.shape[-1], relu_qk=relu_qk,
+                                    gate_logit_normalizer=gate_logit_normalizer, norm_weight=norm_weight)
     if q.dim() != 3 or k.dim() != 3:
         raise ValueError("q must be [T, H, D] and k, v, g [T, Hkv, D]")
     T, H, D = q.shape
@@ -310,7 +405,8 @@ def gla_scan(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, g: torch.Tensor,
     rc = _abi.lib.sbk_gla_scan(
         _ptr(q), _ptr(k), _ptr(v), _ptr(g), _DTYPE_CODE[q.dtype], _ptr(query_start_loc), n_seqs,
         _ptr(state), state.shape[0], _ptr(slot_idx), _ptr(reset), H, Hkv, D, float(scale), _ptr(out),
-        _DTYPE_CODE[out.dtype], _ptr(status), _stream())
+        _DTYPE_CODE[out.dtype], flags, gnorm, _ptr(norm_weight), float(norm_eps), _ptr(status),
+        _stream())
     _abi.check("sbk_gla_scan", rc)
     global LAUNCHES
     LAUNCHES += 1 if n_seqs else 0

@@ -11,6 +11,10 @@ It executes, on the CPU,
     on top of that Cache                                                      -> swa_sdpa.npz
   * the Triton kernel of vllm_hymeta/model_for_7B/my_fused_recurrent.py under
     TRITON_INTERPRET=1 (fp32 inputs: the interpreter has no bf16)             -> gla_triton.npz
+  * the element-wise neighbours of that kernel in the GLA layer (feature map, gate, repeat_kv,
+    rms_norm_ref as g_norm) around the same Triton kernel                     -> gla_fused.npz
+  * RotaryEmbedding + apply_rotary_pos_emb of hf_7B_model/window_attention_sdpa.py (the same
+    two definitions as in window_attention.py) on bf16 and fp32 tensors       -> rope.npz
   * hf_7B_model GLAswaForCausalLM, two layers, prompt + 32 greedy steps (three third-party
     GPU-only ops swapped for PyTorch, see config1_hf_model)                   -> config1_hf.npz
 The fixtures are what the oracle (oracle/ref_ops.py) and the CUDA kernels are pinned to;
@@ -206,6 +210,98 @@ def gla_triton():
     print("gla_triton.npz", {k: v.shape for k, v in out.items() if k.endswith("state2")})
 
 
+def det_unit(shape, salt):
+    """Deterministic values in [-1, 1) (no RNG); tests rebuild them with tests.helpers.det_unit."""
+    n = 1
+    for d in shape:
+        n *= d
+    i = torch.arange(n, dtype=torch.int64) + salt * 1000003
+    return (((i * 2246822519) % 999983).double() / 499991.5 - 1.0).float().view(*shape)
+
+
+def gla_fused():
+    """The decode branch of the GLA layer around its kernel, in the reference's order
+    (vllm_hymeta/model_for_7B/gla_attention.py:250-267, :232-233): relu(q), relu(k),
+    logsigmoid(gk)/16, repeat_kv of k, v, gk, the Triton step kernel, then g_norm, for which the
+    reference's own rms_norm_ref (hf_7B_model/layernorm.py:39-52) stands in for the vLLM layer.
+    fp32 end to end (the interpreter has no bf16); the bf16 gate expression is recorded separately."""
+    mfr = load_ref("vllm_hymeta/model_for_7B/my_fused_recurrent.py", "ref_mfr")
+    sys.path.insert(0, REF)
+    for k in [k for k in sys.modules if k.startswith("hf_7B_model")]:
+        del sys.modules[k]
+    lnmod = load_ref("hf_7B_model/layernorm.py", "ref_layernorm")
+    out = {}
+    for ci, (name, (B, H, Hkv, D, slots)) in enumerate({
+        "d128_h2_kv1": (3, 2, 1, 128, 3),
+        "d64_h8_kv8": (2, 8, 8, 64, 3),
+    }.items()):
+        qp = det_unit((B, H, D), 11 + ci) * 2.0
+        kp = det_unit((B, Hkv, D), 12 + ci) * 2.0
+        v = det_unit((B, Hkv, D), 13 + ci)
+        gl = det_unit((B, Hkv, D), 14 + ci) * 4.0
+        w = 1.0 + 0.5 * det_unit((D,), 15 + ci)
+        rep = H // Hkv
+        q = torch.relu(qp)
+        k = torch.relu(kp)
+        gk = torch.nn.functional.logsigmoid(gl) / 16
+        rk = lambda t: t.repeat_interleave(rep, dim=1).unsqueeze(2).contiguous()
+        q4, k4, v4, g4 = q.unsqueeze(2).contiguous(), rk(k), rk(v), rk(gk)
+        state = golden_state(slots, H, D)
+        slot = torch.arange(B, dtype=torch.int64)
+        if B > 2:
+            slot[1] = -1
+        o = torch.zeros_like(q4)
+        for step in range(2):
+            mfr.my_fused_recurrent_fwd_kernel[(B, H, D // 64)](
+                q4, k4, v4, g4, o, D, state, slot, D ** -0.5, q4.stride(0), q4.stride(1),
+                state.stride(0), state.stride(1), state.stride(2), state.stride(3), 64)
+            out[f"{name}/out{step + 1}"] = lnmod.rms_norm_ref(o.squeeze(2), w, None, eps=1e-5).numpy()
+        out[name + "/meta"] = np.array([B, H, Hkv, D, slots, 11 + ci], dtype=np.int64)
+        out[name + "/slot"] = slot.numpy()
+        out[name + "/state2"] = state.numpy()
+    # the gate expression on a bf16 tensor, as the layer evaluates it when the model runs in bf16
+    gl16 = (det_unit((4096,), 21) * 12.0).to(torch.bfloat16)
+    out["gate_bf16/g"] = (torch.nn.functional.logsigmoid(gl16) / 16).float().numpy()
+    np.savez_compressed(os.path.join(HERE, "gla_fused.npz"), **out)
+    print("gla_fused.npz", sorted(out))
+
+
+ROPE_POSITIONS = [0, 1, 2, 17, 255, 4095, 4096, 8191, 65535, 131071]
+
+
+def rope():
+    """cos/sin and rotated q, k as the reference's HF attention computes them
+    (hf_7B_model/window_attention.py:23-80 == window_attention_sdpa.py:23-80, used at :161-162)."""
+    import types
+    pkg = types.ModuleType("hf_7B_model")
+    pkg.__path__ = [os.path.join(REF, "hf_7B_model")]
+    sys.modules["hf_7B_model"] = pkg
+    load_ref("hf_7B_model/cache.py", "hf_7B_model.cache")
+    wa = load_ref("hf_7B_model/window_attention_sdpa.py", "hf_7B_model.window_attention_sdpa")
+    out = {}
+    for ci, (name, (H, kvh, D, base, dtype)) in enumerate({
+        "bf16_d128_theta1e6": (4, 2, 128, 1000000.0, torch.bfloat16),
+        "bf16_d128_theta1e4": (3, 1, 128, 10000.0, torch.bfloat16),
+        "f32_d64_theta1e4": (4, 2, 64, 10000.0, torch.float32),
+    }.items()):
+        T = len(ROPE_POSITIONS)
+        q = (det_unit((1, H, T, D), 31 + ci) * 3.0).to(dtype)
+        k = (det_unit((1, kvh, T, D), 41 + ci) * 3.0).to(dtype)
+        pos = torch.tensor([ROPE_POSITIONS], dtype=torch.long)
+        emb = wa.RotaryEmbedding(D, max_position_embeddings=131072, base=base)
+        cos, sin = emb(q, pos)
+        qe, ke = wa.apply_rotary_pos_emb(q, k, cos, sin)
+        assert qe.dtype == dtype and cos.dtype == dtype
+        store = (lambda t: t.view(torch.int16).numpy()) if dtype == torch.bfloat16 else (lambda t: t.numpy())
+        out[name + "/meta"] = np.array([H, kvh, D, int(base), int(dtype == torch.bfloat16), 31 + ci], dtype=np.int64)
+        out[name + "/cos"] = store(cos[0].contiguous())          # [T, D] (the two halves are equal)
+        out[name + "/sin"] = store(sin[0].contiguous())
+        out[name + "/q"] = store(qe[0].transpose(0, 1).contiguous())   # token-major [T, H, D]
+        out[name + "/k"] = store(ke[0].transpose(0, 1).contiguous())
+    np.savez_compressed(os.path.join(HERE, "rope.npz"), **out)
+    print("rope.npz", {k: v.shape for k, v in out.items()})
+
+
 # ------------------------------------------------------- 4. the two-layer HF model (configs[0])
 def config1_hf_model():
     """The reference GLAswaForCausalLM (2 layers: GLA then sliding window, hidden 512, 8/2 heads,
@@ -313,3 +409,5 @@ if __name__ == "__main__":
     cache_streams()
     swa_sdpa()
     gla_triton()
+    gla_fused()
+    rope()

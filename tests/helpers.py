@@ -62,3 +62,13 @@ def det_param(name: str, shape) -> torch.Tensor:
     if name.endswith("norm.weight"):
         return 1.0 + 0.1 * t
     return 0.05 * t
+
+
+def det_unit(shape, salt):
+    """Deterministic values in [-1, 1) without an RNG: the inputs of tests/golden/gla_fused.npz
+    (the generator script holds the same formula)."""
+    n = 1
+    for d in shape:
+        n *= d
+    i = torch.arange(n, dtype=torch.int64) + salt * 1000003
+    return (((i * 2246822519) % 999983).double() / 499991.5 - 1.0).float().view(*shape)

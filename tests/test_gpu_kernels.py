@@ -470,6 +470,177 @@ def test_gla_scan_equals_chained_steps_and_chunking_is_invisible(ops):
     assert rel_err(torch.stack(o_steps, 1), o_all) <= 1e-6 and rel_err(s_steps, s_all) <= 1e-6
 
 
+# ------------------------------------------------------------- rotary embedding in the append
+@pytest.mark.parametrize("name", ["bf16_d128_theta1e6", "bf16_d128_theta1e4", "f32_d64_theta1e4"])
+def test_rope_append_is_bit_exact_with_reference_fixture(ops, name):
+    """Query rotated in place, key rotated into the cache (and in place), value copied: all equal,
+    bit for bit, to the reference's RotaryEmbedding + apply_rotary_pos_emb outputs (rope.npz)."""
+    import os
+    import numpy as np
+    from tests.test_oracle_golden import GOLD, ROPE_POSITIONS, rope_case
+    gold = np.load(os.path.join(GOLD, "rope.npz"))
+    (H, kvh, D, base, dtype), q, k, want = rope_case(gold, name)
+    T, bs, nb = len(ROPE_POSITIONS), 16, 4
+    table = ops.build_cos_sin_cache(D, 131072, base, dtype, device=DEV)
+    g = torch.Generator().manual_seed(50)
+    v = torch.randn(T, kvh, D, generator=g).to(dtype)
+    kc = torch.zeros(nb, bs, kvh, D, dtype=dtype, device=DEV)
+    vc = torch.zeros_like(kc)
+    slots = torch.randperm(nb * bs, generator=g)[:T].to(torch.int64)
+    slots[3] = -1                                     # padding token: rotated, not cached
+    qd, kd = q.to(DEV), k.to(DEV)
+    st = _status()
+    ops.rope_kv_append(qd, kd, v.to(DEV), kc, vc, slots.to(DEV),
+                       torch.tensor(ROPE_POSITIONS, dtype=torch.int64, device=DEV), table,
+                       key_in_place=True, status=st)
+    assert st.item() == 0
+    assert torch.equal(qd.cpu(), want["q"]) and torch.equal(kd.cpu(), want["k"])
+    flat_k, flat_v = kc.view(nb * bs, kvh, D).cpu(), vc.view(nb * bs, kvh, D).cpu()
+    live = slots >= 0
+    assert torch.equal(flat_k[slots[live]], want["k"][live]) and torch.equal(flat_v[slots[live]], v[live])
+    untouched = torch.ones(nb * bs, dtype=torch.bool)
+    untouched[slots[live]] = False
+    assert not flat_k[untouched].any() and not flat_v[untouched].any()
+
+
+@pytest.mark.parametrize("rot_dim", [128, 64, 32])
+def test_rope_append_matches_oracle_with_retirement_and_partial_rotation(ops, rot_dim):
+    """Model shapes (28/4 heads, D 128), strided q/k/v views of one projection output, key left
+    as it was, partial rotary widths, and the block retirement of the plain append."""
+    T = B = 6
+    H, kvh, D, bs, wl = 28, 4, 128, 16, 31
+    g = torch.Generator().manual_seed(51)
+    qkv = torch.randn(T, (H + 2 * kvh) * D, generator=g).bfloat16().to(DEV)
+    q = qkv[:, :H * D].view(T, H, D)
+    k = qkv[:, H * D:(H + kvh) * D].view(T, kvh, D)
+    v = qkv[:, (H + kvh) * D:].view(T, kvh, D)
+    q0, k0 = q.clone().cpu(), k.clone().cpu()
+    seq_lens = torch.tensor([70, 33, 48, 80, 1, 97], dtype=torch.int32)
+    positions = (seq_lens - 1).to(torch.int64)
+    max_blocks = 16
+    tables = torch.arange(B * max_blocks, dtype=torch.int32).view(B, max_blocks)
+    ref_tables = tables.clone()
+    slots = torch.tensor([int(tables[b, (int(seq_lens[b]) - 1) // bs]) * bs + (int(seq_lens[b]) - 1) % bs
+                          for b in range(B)], dtype=torch.int64)
+    nb = B * max_blocks
+    kc = torch.zeros(nb, bs, kvh, D, dtype=torch.bfloat16, device=DEV)
+    vc = torch.zeros_like(kc)
+    table = ops.build_cos_sin_cache(rot_dim, 256, 10000.0, torch.bfloat16, device=DEV)
+    tables_d = tables.to(DEV)
+    retired = torch.full((B, 4), -7, dtype=torch.int32, device=DEV)
+    st = _status()
+    ops.rope_kv_append(q, k, v, kc, vc, slots.to(DEV), positions.to(DEV), table, block_tables=tables_d,
+                       seq_lens=seq_lens.to(DEV), window_left=wl, retired_out=retired, status=st)
+    assert st.item() == 0
+    cos, sin = ref_ops.rope_cos_sin_ref(positions, rot_dim, 10000.0, torch.bfloat16)
+    rot = lambda x: torch.cat((ref_ops.rope_ref(x[..., :rot_dim], cos, sin), x[..., rot_dim:]), dim=-1)
+    assert torch.equal(q.cpu(), rot(q0))
+    assert torch.equal(k.cpu(), k0)                                   # key_in_place off
+    assert torch.equal(kc.view(nb * bs, kvh, D)[slots.to(DEV)].cpu(), rot(k0))
+    assert torch.equal(vc.view(nb * bs, kvh, D)[slots.to(DEV)].cpu(), v.cpu())
+    want_ret = ref_ops.retire_blocks(ref_tables, seq_lens.tolist(), [1] * B, wl, bs)
+    assert torch.equal(tables_d.cpu(), ref_tables)
+    for b in range(B):
+        assert retired[b].tolist()[:len(want_ret[b])] == want_ret[b]
+
+
+def test_rope_append_flags_positions_outside_the_table(ops):
+    kc = torch.zeros(2, 16, 1, 64, dtype=torch.bfloat16, device=DEV)
+    vc = torch.zeros_like(kc)
+    k = torch.ones(2, 1, 64, dtype=torch.bfloat16, device=DEV)
+    table = ops.build_cos_sin_cache(64, 8, 10000.0, torch.bfloat16, device=DEV)
+    st = _status()
+    ops.rope_kv_append(None, k, k.clone(), kc, vc, torch.tensor([0, 1], device=DEV),
+                       torch.tensor([3, 8], device=DEV), table, status=st)
+    assert st.item() == 16                       # SBK_ST_BAD_POSITION; token 1 skipped
+    assert kc[0, 0].any() and not kc[0, 1].any()
+
+
+# ------------------------------------------------------------- GLA with fused neighbours
+@pytest.mark.parametrize("name", ["d128_h2_kv1", "d64_h8_kv8"])
+def test_gla_fused_step_matches_reference_layer_fixture(ops, name):
+    """relu / gate / step / g_norm in one launch == the reference layer's pieces chained around
+    its Triton kernel (tests/golden/gla_fused.npz), fp32, two steps, a slot of -1."""
+    import numpy as np
+    from tests.test_oracle_golden import GOLD, fused_case, golden_state
+    import os
+    gold = np.load(os.path.join(GOLD, "gla_fused.npz"))
+    (B, H, Hkv, D, slots), (qp, kp, v, gl, w), slot = fused_case(gold, name)
+    state_d = golden_state(slots, H, D).to(DEV)
+    live = slot >= 0
+    for step in (1, 2):
+        o = ops.gla_step(qp.to(DEV), kp.to(DEV), v.to(DEV), gl.to(DEV), state_d, slot.to(DEV),
+                         relu_qk=True, gate_logit_normalizer=16.0, norm_weight=w.to(DEV), norm_eps=1e-5)
+        assert rel_err(o.cpu()[live], torch.from_numpy(gold[f"{name}/out{step}"])[live]) <= GLA_REL
+    assert rel_err(state_d.cpu(), torch.from_numpy(gold[name + "/state2"])) <= GLA_REL
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float32])
+@pytest.mark.parametrize("B,H,Hkv,D", [(5, 28, 4, 128), (3, 8, 2, 64)])
+def test_gla_fused_step_equals_separate_ops(ops, dtype, B, H, Hkv, D):
+    """The fused call == torch relu / logsigmoid-gate in the input dtype, the plain kernel, and
+    the oracle's g_norm on its fp32 read-out. The state must agree bit for bit: the prologue
+    reproduces the roundings of the reference's tensor expressions."""
+    g = torch.Generator().manual_seed(40)
+    qp = torch.randn(B, H, D, generator=g).to(dtype).to(DEV)
+    kp = torch.randn(B, Hkv, D, generator=g).to(dtype).to(DEV)
+    v = torch.randn(B, Hkv, D, generator=g).to(dtype).to(DEV)
+    gl = (3 * torch.randn(B, Hkv, D, generator=g)).to(dtype).to(DEV)
+    w = (1 + 0.3 * torch.randn(D, generator=g)).to(dtype).to(DEV)
+    state = torch.randn(B, H, D, D, generator=g).to(DEV)
+    s_fused, s_plain = state.clone(), state.clone()
+    o_fused = ops.gla_step(qp, kp, v, gl, s_fused, relu_qk=True, gate_logit_normalizer=16.0,
+                           norm_weight=w, norm_eps=1e-5, out_dtype=torch.float32)
+    gk = torch.nn.functional.logsigmoid(gl) / 16
+    assert gk.dtype == dtype
+    o_plain = ops.gla_step(torch.relu(qp), torch.relu(kp), v, gk, s_plain, out_dtype=torch.float32)
+    if dtype == torch.bfloat16:
+        assert torch.equal(s_fused, s_plain)
+    else:
+        assert rel_err(s_fused, s_plain) <= 1e-6
+    want = ref_ops.gla_norm_ref(o_plain.cpu(), w.cpu(), 1e-5)
+    assert rel_err(o_fused.cpu(), want) <= GLA_REL
+
+
+@pytest.mark.parametrize("D,H,Hkv", [(128, 28, 4), (64, 8, 8)])
+def test_gla_fused_scan_equals_fused_steps(ops, D, H, Hkv):
+    """Ragged runs through the fused scan == the fused single-token kernel token after token."""
+    runs = [3, 9, 1, 6]
+    qsl = [0]
+    for n in runs:
+        qsl.append(qsl[-1] + n)
+    T = qsl[-1]
+    g = torch.Generator().manual_seed(41)
+    mk = lambda h, s=1.0: (s * torch.randn(T, h, D, generator=g)).bfloat16().to(DEV)
+    qp, kp, v, gl = mk(H), mk(Hkv), mk(Hkv), mk(Hkv, 3.0)
+    w = (1 + 0.3 * torch.randn(D, generator=g)).bfloat16().to(DEV)
+    fused = dict(relu_qk=True, gate_logit_normalizer=16.0, norm_weight=w, norm_eps=1e-5)
+    s_scan = torch.randn(len(runs), H, D, D, generator=g).to(DEV)
+    s_step = s_scan.clone()
+    o_scan = ops.gla_scan(qp, kp, v, gl, s_scan, torch.tensor(qsl, dtype=torch.int32, device=DEV),
+                          out_dtype=torch.float32, **fused)
+    o_step = torch.zeros_like(o_scan)
+    for s, n in enumerate(runs):
+        slot = torch.tensor([s], dtype=torch.int64, device=DEV)
+        for t in range(qsl[s], qsl[s + 1]):
+            o_step[t] = ops.gla_step(qp[t:t + 1], kp[t:t + 1], v[t:t + 1], gl[t:t + 1], s_step, slot,
+                                     out_dtype=torch.float32, **fused)[0]
+    assert rel_err(o_scan, o_step) <= 1e-5 and rel_err(s_scan, s_step) <= 1e-6
+
+
+def test_gla_fusion_argument_errors(ops):
+    from spikingbrain_7b_b200._abi import SbkError, lib
+    q = torch.zeros(1, 4, 128, dtype=torch.bfloat16, device=DEV)
+    S = torch.zeros(1, 4, 128, 128, device=DEV)
+    with pytest.raises(ValueError):
+        ops.gla_step(q, q, q, q, S, gate_logit_normalizer=0.0)
+    with pytest.raises(ValueError):
+        ops.gla_step(q, q, q, q, S, norm_weight=torch.ones(64, dtype=torch.bfloat16, device=DEV))
+    rc = lib.sbk_gla_step(q.data_ptr(), q.data_ptr(), q.data_ptr(), q.data_ptr(), 0, S.data_ptr(), 1, None,
+                          1, 4, 4, 128, 1.0, q.data_ptr(), 0, 64, 0.0, None, 0.0, None, None)
+    assert rc == -1 and b"fuse_flags" in lib.sbk_last_error()
+
+
 # ---------------------------------------------------------------------- argument errors
 def test_argument_errors_are_reported(ops):
     from spikingbrain_7b_b200._abi import SbkError

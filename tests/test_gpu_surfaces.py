@@ -344,3 +344,92 @@ def test_backend_forward_unsupported_paths_raise(pkg):
                                seq_start_loc=torch.tensor([0, 2], dtype=torch.int32, device=DEV))
     with pytest.raises(NotImplementedError):       # a prompt whose K/V cannot be reached through tables
         impl.forward(None, q, kx, kx, None, None, None, kv, pm, output=torch.empty_like(q))
+
+
+# ------------------------------------------------------- fused neighbours through the surfaces
+def test_hf_cache_update_rotary_equals_rotate_then_update(pkg):
+    """update_rotary (one launch) == the oracle's apply_rotary_pos_emb on q, k followed by update():
+    a prompt longer than the window (every token rotated, the last W cached), then decode steps."""
+    from spikingbrain_7b_b200 import ops
+    from spikingbrain_7b_b200.hf_cache import Cache
+    B, H, kvh, D, W, prompt = 2, 4, 2, 128, 32, 45
+    table = ops.build_cos_sin_cache(D, 512, 10000.0, torch.bfloat16, device=DEV)
+    g = torch.Generator().manual_seed(70)
+    fused, plain = Cache(), Cache()
+    t = 0
+    for n in [prompt] + [1] * 6:
+        q = torch.randn(B, H, n, D, generator=g).bfloat16()
+        k = torch.randn(B, kvh, n, D, generator=g).bfloat16()
+        v = torch.randn(B, kvh, n, D, generator=g).bfloat16()
+        pos = torch.arange(t, t + n)[None, :]
+        cos, sin = ref_ops.rope_cos_sin_ref(pos[0], D, 10000.0, torch.bfloat16)
+        rot = lambda x: ref_ops.rope_ref(x.transpose(1, 2).reshape(B * n, -1, D), cos.repeat(B, 1),
+                                         sin.repeat(B, 1)).view(B, n, -1, D).transpose(1, 2)
+        q_rot = fused.update_rotary(q.to(DEV), k.to(DEV), v.to(DEV), pos.to(DEV), table, layer_idx=0,
+                                    window_size=W)
+        want = plain.update(attn_state=(rot(k).to(DEV), v.to(DEV)), layer_idx=0, offset=n,
+                            cache_kwargs={"window_size": W})["attn_state"]
+        got = fused[0]["attn_state"]
+        assert torch.equal(q_rot.cpu(), rot(q))
+        assert torch.equal(got[0], want[0]) and torch.equal(got[1], want[1])
+        assert fused.get_seq_length() == plain.get_seq_length() == t + n
+        t += n
+    assert fused[0].paged.status.item() == 0
+
+
+def test_backend_forward_with_fused_rotary_equals_rotate_then_forward(pkg):
+    """MetaAttentionImpl.forward(positions=, cos_sin_cache=) on un-rotated q, k == forward on
+    q, k rotated beforehand by the oracle: same cache bytes, same attention output."""
+    from spikingbrain_7b_b200 import ops
+    from spikingbrain_7b_b200.backend import MetaAttentionImpl, MetaAttentionMetadata
+    B, H, kvh, D, bs, W = 3, 28, 4, 128, 16, 64
+    g = torch.Generator().manual_seed(71)
+    seq_lens = torch.tensor([90, 17, 64], dtype=torch.int32)
+    max_blocks = 8
+    nb = B * max_blocks
+    tables = torch.arange(nb, dtype=torch.int32).view(B, max_blocks)
+    cache0 = torch.randn(2, nb, bs, kvh, D, generator=g).bfloat16()
+    slots = torch.tensor([int(tables[b, (int(seq_lens[b]) - 1) // bs]) * bs + (int(seq_lens[b]) - 1) % bs
+                          for b in range(B)], dtype=torch.int64)
+    q = torch.randn(B, H, D, generator=g).bfloat16()
+    k = torch.randn(B, kvh, D, generator=g).bfloat16()
+    v = torch.randn(B, kvh, D, generator=g).bfloat16()
+    positions = (seq_lens - 1).to(torch.int64)
+    table = ops.build_cos_sin_cache(D, 128, 1000000.0, torch.bfloat16, device=DEV)
+    cos, sin = ref_ops.rope_cos_sin_ref(positions, D, 1000000.0, torch.bfloat16)
+
+    def run(qi, ki, **kw):
+        impl = MetaAttentionImpl(H, D, D ** -0.5, kvh, None, W + 1, "auto")
+        meta = _decode_meta(MetaAttentionMetadata, slots.to(DEV), seq_lens.to(DEV), tables.to(DEV))
+        kv = cache0.clone().to(DEV)
+        out = torch.empty(B, H * D, dtype=torch.bfloat16, device=DEV)
+        impl.forward(None, qi.to(DEV), ki.to(DEV), v.to(DEV), None, None, None, kv, meta, output=out, **kw)
+        assert impl.status() == 0
+        return out, kv
+
+    o_fused, kv_fused = run(q.clone(), k.clone(), positions=positions.to(DEV), cos_sin_cache=table)
+    o_plain, kv_plain = run(ref_ops.rope_ref(q, cos, sin), ref_ops.rope_ref(k, cos, sin))
+    assert torch.equal(kv_fused, kv_plain) and torch.equal(o_fused, o_plain)
+
+
+def test_gla_decode_layer_surface_matches_layer_oracle(pkg):
+    """gla_decode_layer (projection outputs in, normed read-out out, one launch) == the oracle of
+    the layer's decode branch; bf16 in and out."""
+    from spikingbrain_7b_b200.gla_slots import gla_decode_layer
+    B, H, Hkv, D, slots = 6, 28, 4, 128, 9
+    g = torch.Generator().manual_seed(72)
+    qp = torch.randn(B, H, D, generator=g).bfloat16()
+    kp = torch.randn(B, Hkv, D, generator=g).bfloat16()
+    v = torch.randn(B, Hkv, D, generator=g).bfloat16()
+    gl = (3 * torch.randn(B, Hkv, D, generator=g)).bfloat16()
+    w = (1 + 0.3 * torch.randn(D, generator=g)).bfloat16()
+    state = torch.randn(slots, H, D, D, generator=g)
+    slot = torch.randperm(slots, generator=g)[:B].to(torch.int64)
+    ref_state = state.clone()
+    want = ref_ops.gla_layer_step_ref(qp, kp, v, gl, ref_state, slot, 16.0, w, 1e-5)
+    state_d = state.to(DEV)
+    got = gla_decode_layer(qp.to(DEV), kp.to(DEV), v.to(DEV), gl.to(DEV), state_d, slot.to(DEV), w.to(DEV))
+    assert got.dtype == torch.bfloat16
+    assert rel_err(state_d.cpu(), ref_state) <= 1e-4
+    diff = (got.float().cpu() - want).abs()
+    assert float((diff / want.abs().clamp_min(1e-2)).max()) <= 2 ** -7   # one bf16 rounding of the output

@@ -24,14 +24,14 @@ def test_library_exports_every_declared_symbol(sb):
         assert hasattr(lib, name), f"{name} declared in include/sbk.h but not exported"
     from spikingbrain_7b_b200 import _abi
     assert set(_abi.SIGNATURES) == declared
-    assert _abi.lib.sbk_abi_version() == _abi.ABI_VERSION == 2
+    assert _abi.lib.sbk_abi_version() == _abi.ABI_VERSION == 3
 
 
 def test_host_side_argument_errors_need_no_gpu(sb):
     """Argument validation happens before any CUDA call, so it can be exercised on the CPU."""
     from spikingbrain_7b_b200 import _abi
     lib = _abi.lib
-    rc = lib.sbk_gla_step(None, None, None, None, 0, None, 4, None, 2, 28, 4, 96, 1.0, None, 0, None, None)
+    rc = lib.sbk_gla_step(None, None, None, None, 0, None, 4, None, 2, 28, 4, 96, 1.0, None, 0, 0, 0.0, None, 0.0, None, None)
     assert rc == _abi.SBK_E_ARG and b"D=96" in lib.sbk_last_error()
     rc = lib.sbk_swa_decode(None, 0, None, None, None, 4, None, 2, 36, 4, 128, 8, 16, 0, 63, 1.0, None, 0, 0,
                             None, None, 0, 0, 1, None, None, 0, None, None)
@@ -45,7 +45,7 @@ def test_host_side_argument_errors_need_no_gpu(sb):
     assert lib.sbk_kv_append(None, None, None, None, None, 3, 4, 128, 2, 1024, 8, 16, 16384, None, 0, None,
                              None, 0, -1, None, 0, None, None) == _abi.SBK_E_ARG
     # empty work is a successful no-op
-    assert lib.sbk_gla_step(None, None, None, None, 0, None, 0, None, 0, 28, 4, 128, 1.0, None, 0, None, None) == 0
+    assert lib.sbk_gla_step(None, None, None, None, 0, None, 0, None, 0, 28, 4, 128, 1.0, None, 0, 0, 0.0, None, 0.0, None, None) == 0
     assert lib.sbk_swa_workspace_bytes(256, 28, 128, 9) >= 256 * 9 * 28 * 130 * 4
     with pytest.raises(RuntimeError):
         from spikingbrain_7b_b200 import ops
@@ -297,3 +297,19 @@ def test_hf_cache_surface_without_gpu():
     assert isinstance(legacy, tuple) and legacy[0]["recurrent_state"] is rs2
     c2 = Cache.from_legacy_cache(legacy, seen_tokens=6)
     assert len(c2) == 1 and c2.get_seq_length() == 6 and c2[0]["recurrent_state"] is rs2
+
+
+@pytest.mark.parametrize("name", ["bf16_d128_theta1e6", "bf16_d128_theta1e4", "f32_d64_theta1e4"])
+def test_cos_sin_table_rows_equal_reference_rotary_embedding(sb, name):
+    """ops.build_cos_sin_cache (the vLLM-side table layout: cos half | sin half) holds, row by row,
+    the cos / sin the reference's HF RotaryEmbedding returns for that position (rope.npz)."""
+    import numpy as np
+    from spikingbrain_7b_b200 import ops
+    from tests.test_oracle_golden import GOLD, ROPE_POSITIONS, rope_case
+    gold = np.load(os.path.join(GOLD, "rope.npz"))
+    (H, kvh, D, base, dtype), _, _, want = rope_case(gold, name)
+    table = ops.build_cos_sin_cache(D, 131072, base, dtype, device="cpu")
+    assert table.shape == (131072, D) and table.dtype == dtype
+    rows = table[torch.tensor(ROPE_POSITIONS)]
+    assert torch.equal(rows[:, :D // 2], want["cos"][:, :D // 2])
+    assert torch.equal(rows[:, D // 2:], want["sin"][:, :D // 2])

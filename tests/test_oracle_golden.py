@@ -142,6 +142,73 @@ def test_gla_oracle_matches_reference_triton_kernel(name):
     assert torch.equal(state[untouched], golden_state(slots, H, D)[untouched])
 
 
+def fused_case(gold, name):
+    """Rebuilds the inputs of one gla_fused.npz case (formulas of the generator script)."""
+    from tests.helpers import det_unit
+    B, H, Hkv, D, slots, salt = gold[name + "/meta"].tolist()
+    qp = det_unit((B, H, D), salt) * 2.0
+    kp = det_unit((B, Hkv, D), salt + 1) * 2.0
+    v = det_unit((B, Hkv, D), salt + 2)
+    gl = det_unit((B, Hkv, D), salt + 3) * 4.0
+    w = 1.0 + 0.5 * det_unit((D,), salt + 4)
+    return (B, H, Hkv, D, slots), (qp, kp, v, gl, w), torch.from_numpy(gold[name + "/slot"])
+
+
+@pytest.mark.parametrize("name", ["d128_h2_kv1", "d64_h8_kv8"])
+def test_gla_layer_oracle_matches_reference_layer_pieces(name):
+    """gla_layer_step_ref == relu / logsigmoid-gate / repeat_kv / Triton step kernel / rms_norm_ref
+    chained by the generator script in the reference layer's order, two steps, a slot of -1."""
+    gold = np.load(os.path.join(GOLD, "gla_fused.npz"))
+    (B, H, Hkv, D, slots), (qp, kp, v, gl, w), slot = fused_case(gold, name)
+    state = golden_state(slots, H, D)
+    live = slot >= 0
+    for step in (1, 2):
+        o = ref_ops.gla_layer_step_ref(qp, kp, v, gl, state, slot, 16.0, w, 1e-5)
+        want = torch.from_numpy(gold[f"{name}/out{step}"])
+        assert torch.allclose(o[live], want[live], rtol=2e-5, atol=2e-5)
+    assert torch.allclose(state, torch.from_numpy(gold[name + "/state2"]), rtol=1e-5, atol=1e-5)
+
+
+def test_gate_expression_in_bf16_matches_fixture():
+    """logsigmoid(gk) / 16 on a bf16 tensor, bit for bit (gla_prepare_inputs is that expression)."""
+    from tests.helpers import det_unit
+    gold = np.load(os.path.join(GOLD, "gla_fused.npz"))
+    gl16 = (det_unit((4096,), 21) * 12.0).to(torch.bfloat16)
+    _, _, g = ref_ops.gla_prepare_inputs(gl16, gl16, gl16, 16.0)
+    assert g.dtype == torch.bfloat16
+    assert torch.equal(g.float(), torch.from_numpy(gold["gate_bf16/g"]))
+
+
+ROPE_POSITIONS = [0, 1, 2, 17, 255, 4095, 4096, 8191, 65535, 131071]
+ROPE_CASES = ["bf16_d128_theta1e6", "bf16_d128_theta1e4", "f32_d64_theta1e4"]
+
+
+def rope_case(gold, name):
+    """Inputs (rebuilt from the generator's formulas) and reference outputs of one rope.npz case."""
+    from tests.helpers import det_unit
+    H, kvh, D, base, is_bf16, salt = gold[name + "/meta"].tolist()
+    dtype = torch.bfloat16 if is_bf16 else torch.float32
+    T = len(ROPE_POSITIONS)
+    tm = lambda t: t[0].transpose(0, 1).contiguous()
+    q = tm((det_unit((1, H, T, D), salt) * 3.0).to(dtype))
+    k = tm((det_unit((1, kvh, T, D), salt + 10) * 3.0).to(dtype))
+    load = lambda key: (torch.from_numpy(gold[f"{name}/{key}"]).view(torch.bfloat16) if is_bf16
+                        else torch.from_numpy(gold[f"{name}/{key}"]))
+    return (H, kvh, D, float(base), dtype), q, k, {n: load(n) for n in ("cos", "sin", "q", "k")}
+
+
+@pytest.mark.parametrize("name", ROPE_CASES)
+def test_rope_oracle_is_bit_exact_with_reference(name):
+    """rope_cos_sin_ref / rope_ref == RotaryEmbedding + apply_rotary_pos_emb of the reference, bit
+    for bit in bf16 and fp32, positions up to 131071."""
+    gold = np.load(os.path.join(GOLD, "rope.npz"))
+    (H, kvh, D, base, dtype), q, k, want = rope_case(gold, name)
+    cos, sin = ref_ops.rope_cos_sin_ref(torch.tensor(ROPE_POSITIONS), D, base, dtype)
+    assert torch.equal(cos, want["cos"]) and torch.equal(sin, want["sin"])
+    assert torch.equal(ref_ops.rope_ref(q, cos, sin), want["q"])
+    assert torch.equal(ref_ops.rope_ref(k, cos, sin), want["k"])
+
+
 def test_gla_oracle_kv_head_sharing_equals_repeated_heads():
     """k, v, g given per kv head == the reference's repeat_kv'ed per-query-head inputs."""
     g = torch.Generator().manual_seed(9)
