@@ -31,7 +31,7 @@ __device__ __forceinline__ __nv_bfloat16 from_f32<__nv_bfloat16>(float x) { retu
 //
 // D = 128: 32 threads span a row (float4 each), 8 row groups, 16 rows per thread.
 // D = 64 : 16 threads span a row, 16 row groups, 4 rows per thread.
-template <typename T, typename TO, int D>
+template <typename T, typename TO, int D, bool FUSED>
 __global__ void __launch_bounds__(256)
 gla_step_kernel(const T* __restrict__ q, const T* __restrict__ k, const T* __restrict__ v,
                 const T* __restrict__ g, float* __restrict__ state, int64_t num_slots,
@@ -58,10 +58,10 @@ gla_step_kernel(const T* __restrict__ q, const T* __restrict__ k, const T* __res
     float qv = to_f32(q[((int64_t)b * H + h) * D + tid]);
     const int64_t kv_off = ((int64_t)b * Hkv + hk) * D + tid;
     float kv = to_f32(k[kv_off]);
-    if (fu.relu_qk) { qv = fmaxf(qv, 0.f); kv = fmaxf(kv, 0.f); }
+    if (FUSED && fu.relu_qk) { qv = fmaxf(qv, 0.f); kv = fmaxf(kv, 0.f); }
     s_q[tid] = qv * scale;
     s_k[tid] = kv;
-    s_decay[tid] = expf(gla_gate<T>(to_f32(g[kv_off]), fu));
+    s_decay[tid] = expf(FUSED ? gla_gate<T>(to_f32(g[kv_off]), fu) : to_f32(g[kv_off]));
   }
   const int c4 = tid % TPR;
   const int r0 = tid / TPR;
@@ -101,7 +101,7 @@ gla_step_kernel(const T* __restrict__ q, const T* __restrict__ k, const T* __res
 #pragma unroll
     for (int gi = 0; gi < GROUPS; ++gi) acc += so[gi * D + tid];
   }
-  if (fu.norm_weight != nullptr) {
+  if (FUSED && fu.norm_weight != nullptr) {
     // per-head RMS norm of the D outputs (they sit in threads 0..D-1)
     float sq = tid < D ? acc * acc : 0.f;
 #pragma unroll
@@ -154,10 +154,17 @@ extern "C" int sbk_gla_step(const void* q, const void* k, const void* v, const v
   }
   dim3 grid(H, B);
   cudaStream_t st = (cudaStream_t)stream;
-#define SBK_GLA_LAUNCH(T, TO, DD)                                                               \
-  gla_step_kernel<T, TO, DD><<<grid, 256, 0, st>>>((const T*)q, (const T*)k, (const T*)v,       \
-                                                   (const T*)g, state, num_slots, slot_idx, H,  \
-                                                   Hkv, scale, (TO*)out, status, fu)
+  // the plain step keeps its own instantiation: nothing of the fused neighbours is compiled in
+  const bool fused = fuse_flags != 0 || norm_weight != nullptr;
+#define SBK_GLA_LAUNCH_F(T, TO, DD, F)                                                          \
+  gla_step_kernel<T, TO, DD, F><<<grid, 256, 0, st>>>((const T*)q, (const T*)k, (const T*)v,    \
+                                                      (const T*)g, state, num_slots, slot_idx,  \
+                                                      H, Hkv, scale, (TO*)out, status, fu)
+#define SBK_GLA_LAUNCH(T, TO, DD)            \
+  do {                                       \
+    if (fused) SBK_GLA_LAUNCH_F(T, TO, DD, true); \
+    else SBK_GLA_LAUNCH_F(T, TO, DD, false); \
+  } while (0)
 #define SBK_GLA_DISPATCH_D(T, TO)         \
   do {                                    \
     if (D == 128) SBK_GLA_LAUNCH(T, TO, 128); \
@@ -172,5 +179,6 @@ extern "C" int sbk_gla_step(const void* q, const void* k, const void* v, const v
   }
 #undef SBK_GLA_DISPATCH_D
 #undef SBK_GLA_LAUNCH
+#undef SBK_GLA_LAUNCH_F
   return check_launch("sbk_gla_step");
 }

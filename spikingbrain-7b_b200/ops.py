@@ -113,11 +113,13 @@ def build_cos_sin_cache(rot_dim: int, max_position: int, base: float = 10000.0,
     GLAswaRotaryEmbedding._compute_cos_sin_cache does (vllm_hymeta/model_for_7B/
     modeling_gla_swa.py:66-79): fp32 angles position x base^(-2i/rot_dim), cos and sin taken in
     fp32, then one cast to ``dtype``. The HF RotaryEmbedding (hf_7B_model/window_attention.py:
-    23-47) produces the same cos/sin values per call."""
-    inv_freq = 1.0 / (base ** (torch.arange(0, rot_dim, 2, dtype=torch.float, device=device) / rot_dim))
-    t = torch.arange(max_position, dtype=torch.float, device=device)
+    23-47) produces the same cos/sin values per call. The table is always computed by the host's
+    libm and then moved to ``device``: device cos/sin differ from it in the last fp32 bit often
+    enough to flip roundings to bf16, and the fixtures recorded from the reference are host values."""
+    inv_freq = 1.0 / (base ** (torch.arange(0, rot_dim, 2, dtype=torch.float) / rot_dim))
+    t = torch.arange(max_position, dtype=torch.float)
     freqs = torch.einsum("i,j -> ij", t, inv_freq)
-    return torch.cat((freqs.cos(), freqs.sin()), dim=-1).to(dtype).contiguous()
+    return torch.cat((freqs.cos(), freqs.sin()), dim=-1).to(dtype).contiguous().to(device)
 
 
 def rope_kv_append(query: Optional[torch.Tensor], key: torch.Tensor, value: torch.Tensor,
