@@ -179,14 +179,16 @@ class ClockSampler:
 class DecodeEngine:
     """Holds the per-layer caches of one GPU and runs decode steps through the reference-facing
     surfaces: MetaAttentionImpl.forward for sliding-window layers, my_fused_recurrent_gla for
-    GLA layers, with a SlidingWindowBlockManager standing in for the serving engine's."""
+    GLA layers. Lengths, block tables, the free-block ring and the step's slot mapping live on the
+    GPU (DeviceStepPlanner): one sbk_plan_step launch per step stands in for the serving engine's
+    block manager and metadata builder, so a step needs no host-side metadata work."""
 
     def __init__(self, args, device):
         import numpy as np
         import torch
         from spikingbrain_7b_b200 import ops
         from spikingbrain_7b_b200.backend import MetaAttentionImpl, MetaAttentionMetadata
-        from spikingbrain_7b_b200.block_pool import SlidingWindowBlockManager
+        from spikingbrain_7b_b200.block_pool import DeviceStepPlanner
         from spikingbrain_7b_b200.gla_slots import GLACacheManager, my_fused_recurrent_gla
         self.torch, self.np, self.ops = torch, np, ops
         self.Meta = MetaAttentionMetadata
@@ -199,21 +201,19 @@ class DecodeEngine:
         self.max_blocks = (max_len + BLOCK - 1) // BLOCK + 1
         live = (WINDOW_LEFT + 1) // BLOCK + 3
         n_blocks = B * live + 64
-        self.mgr = SlidingWindowBlockManager(n_blocks, BLOCK, WINDOW_LEFT, B, self.max_blocks)
-        # sequences arrive with `ctx` tokens of context: only the window's blocks are resident
+        self.plan = DeviceStepPlanner(n_blocks, BLOCK, WINDOW_LEFT, B, self.max_blocks, device)
+        # sequences arrive with `ctx` tokens of context: only the window's blocks are resident,
+        # handed out in a random order; the rest of the pool is the free ring
         g = np.random.default_rng(1234 + (device.index or 0))
-        order = g.permutation(n_blocks)       # the pool hands blocks out in a random order
-        self.mgr.pool._free = [int(x) for x in order[::-1]]
+        order = g.permutation(n_blocks).astype(np.int32)
         first_live = max(0, args.ctx - WINDOW_LEFT) // BLOCK
-        for row in range(B):
-            self.mgr.admit(row)
-            self.mgr.lens[row] = args.ctx
-            self.mgr._first_live[row] = first_live
-            for j in range(first_live, (args.ctx + BLOCK - 1) // BLOCK):
-                self.mgr.table[row, j] = self.mgr.pool.allocate()
-        self.table_d = torch.from_numpy(self.mgr.table).to(device)
-        self.lens_d = torch.from_numpy(self.mgr.lens.copy()).to(device)
-        self.slots_d = torch.zeros(B, dtype=torch.int64, device=device)
+        last = (args.ctx + BLOCK - 1) // BLOCK
+        table = np.full((B, self.max_blocks), -1, dtype=np.int32)
+        used = B * (last - first_live)
+        table[:, first_live:last] = order[:used].reshape(B, last - first_live)
+        self.plan.load_state(np.full(B, args.ctx, dtype=np.int32), table, order[used:])
+        self.ctx0, self.steps_done = args.ctx, 0
+        self.table_d, self.lens_d, self.slots_d = self.plan.block_tables, self.plan.seq_lens, self.plan.slot_mapping
         self.kv = []
         for _ in range(self.n_swa):
             t = torch.empty(2, n_blocks, BLOCK, KVH, D, dtype=torch.bfloat16, device=device)
@@ -245,28 +245,13 @@ class DecodeEngine:
         self.h2d_bytes = self.d2h_bytes = 0
         self.e2e_in_bytes = self.e2e_out_bytes = 0
 
-    def _advance_metadata(self):
-        """Host side of a step: slots of the new tokens, new lengths, newly allocated blocks."""
-        torch = self.torch
-        plan = self.mgr.advance(self.np.ones(self.B, dtype=self.np.int64))
-        # Pageable sources: the runtime stages them before the call returns, so the host may
-        # overwrite its arrays for the next step while the GPU is still several steps behind.
-        self.slots_d.copy_(torch.from_numpy(plan.slot_mapping), non_blocking=True)
-        self.lens_d.copy_(torch.from_numpy(plan.seq_lens), non_blocking=True)
-        nbytes = plan.slot_mapping.nbytes + plan.seq_lens.nbytes
-        if plan.new_entries.size:
-            e = torch.from_numpy(plan.new_entries).to(self.device, non_blocking=True).long()
-            self.table_d[e[:, 0], e[:, 1]] = e[:, 2].int()
-            nbytes += plan.new_entries.nbytes
-        # blocks that left the window are dropped from the device table by the append kernel of
-        # the first sliding-window layer (same rule as the host mirror)
-        max_len = int(plan.seq_lens.max())
-        meta = self.Meta(num_prefills=0, num_prefill_tokens=0, num_decode_tokens=self.B,
+    def _metadata(self):
+        """The step's metadata object: views of the planner's device tensors (fixed addresses)."""
+        return self.Meta(num_prefills=0, num_prefill_tokens=0, num_decode_tokens=self.B,
                          slot_mapping=self.slots_d, seq_lens=None, seq_lens_tensor=self.lens_d,
-                         max_prefill_seq_len=0, max_decode_seq_len=max_len, context_lens_tensor=None,
-                         block_tables=self.table_d, use_cuda_graph=False, max_query_len=1,
-                         max_decode_query_len=1)
-        return meta, nbytes
+                         max_prefill_seq_len=0, max_decode_seq_len=self.ctx0 + self.steps_done + 1,
+                         context_lens_tensor=None, block_tables=self.table_d, use_cuda_graph=False,
+                         max_query_len=1, max_decode_query_len=1)
 
     # ---------------------------------------------------------------- device-resident step
     def enqueue_layers(self, meta, timing=None):
@@ -274,18 +259,13 @@ class DecodeEngine:
         calls. `timing`: list that receives an (start, end) event pair around every sliding-window
         decode call (events created with external=True so that a captured graph records them)."""
         torch, ops = self.torch, self.ops
-        first_swa = True
+        self.plan.plan()   # retire, allocate, slots, lengths: on the device
         for i in range(max(self.n_swa, self.n_gla)):
             if i < self.n_gla:   # even layers of the model are GLA layers
                 self.gla_fn(self.gq, self.gk, self.gv, self.gg, kv_caches=self.gla.cache[i], slot_idx=self.slot_idx,
                             out=self.gla_out)
             if i < self.n_swa:   # odd layers are sliding-window layers
                 j = i & 1
-                if first_swa:
-                    # retire on the device what the host mirror released this step
-                    ops.kv_append(self.k[j][:0], self.v[j][:0], self.kv[i][0], self.kv[i][1], self.slots_d[:0],
-                                  block_tables=self.table_d, seq_lens=self.lens_d, window_left=WINDOW_LEFT)
-                    first_swa = False
                 # three of the sliding-window launches carry timing events (first, middle, last layer):
                 # an event node between two kernels costs the overlap of their tail and head
                 ops.SWA_TIMING = timing if i in (0, self.n_swa // 2, self.n_swa - 1) else None
@@ -294,12 +274,11 @@ class DecodeEngine:
                 ops.SWA_TIMING = None
 
     def step(self, e2e=False):
-        """One decode step: the host decides slots / lengths / new blocks and uploads them, then
-        the step's kernels run -- replayed from a captured CUDA graph once `capture()` was called,
-        launched one by one before that."""
-        meta, meta_bytes = self._advance_metadata()
+        """One decode step: the planner launch and the layers' kernels -- replayed from a captured
+        CUDA graph once `capture()` was called, launched one by one before that."""
+        meta = self._metadata()
+        self.steps_done += 1
         if e2e:
-            self.h2d_bytes += meta_bytes
             if self.graph_e2e is not None:
                 self.graph_e2e.replay()
                 self.h2d_bytes += self.e2e_in_bytes
@@ -317,9 +296,9 @@ class DecodeEngine:
     def capture(self, e2e=False):
         """Capture the kernels (and, end to end, the host<->device copies) of one step into a CUDA
         graph. The metadata tensors the graph reads (slots, lengths, block table) live at fixed
-        addresses and are refreshed by the host before every replay."""
+        addresses and are advanced by the graph's own first node."""
         torch, ops = self.torch, self.ops
-        meta, _ = self._advance_metadata()      # the capture reads the metadata tensors in place
+        meta = self._metadata()
         side = torch.cuda.Stream(device=self.device)
         side.wait_stream(torch.cuda.current_stream())
         g = torch.cuda.CUDAGraph()
@@ -374,7 +353,7 @@ class DecodeEngine:
         torch, ops = self.torch, self.ops
         st = self._e2e_setup()
         cur = torch.cuda.current_stream()
-        first_swa = True
+        self.plan.plan()
         for k in "gs":                      # every buffer starts the step free
             for e in st.in_free[k]:
                 e.record(cur)
@@ -413,10 +392,6 @@ class DecodeEngine:
             if i < self.n_swa:
                 q, k, v = st.s_in[slot]
                 upload("s", slot, zip((q, k, v), (self.h_q, self.h_k, self.h_v)))
-                if first_swa:
-                    ops.kv_append(k[:0], v[:0], self.kv[i][0], self.kv[i][1], self.slots_d[:0],
-                                  block_tables=self.table_d, seq_lens=self.lens_d, window_left=WINDOW_LEFT)
-                    first_swa = False
                 oslot = n_out & 1; n_out += 1
                 cur.wait_event(st.out_free[oslot])
                 self.impls[i].forward(None, q, k, v, None, None, None, self.kv[i], meta, output=st.out[oslot])
@@ -573,7 +548,7 @@ def run_b200(args):
                                f"{args.gla_layers} GLA layers, batch {args.batch} per GPU, ctx {args.ctx}, "
                                f"window_left {WINDOW_LEFT}, block {BLOCK}, 28/4 heads, head_dim 128",
                    "parallelism": f"sequence-sharded x{world}, no collective",
-                   "launch": "host launches" if args.no_graph else "CUDA graph replay of the step's kernels; metadata refreshed by the host",
+                   "launch": "host launches" if args.no_graph else "CUDA graph replay of the step (planner launch + layer kernels); no host metadata work",
                    "l2": "working set (KV pools + GLA state, tens of GB) far exceeds the 126 MB L2; no flush needed"},
         "cache_gbs": world * step_bytes / (ms_per_step * 1e-3) / 1e9,
         "cache_gbs_per_gpu": step_bytes / (ms_per_step * 1e-3) / 1e9,

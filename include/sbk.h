@@ -48,6 +48,8 @@ extern "C" {
 #define SBK_ST_WAIT_TIMEOUT 4  /* a bounded in-kernel wait ran out; result of that CTA invalid */
 #define SBK_ST_RETIRE_OVERFLOW 8 /* more blocks left the window than retired_out has columns */
 #define SBK_ST_BAD_POSITION 16   /* a position outside the cos/sin table (token left untouched) */
+#define SBK_ST_OUT_OF_BLOCKS 32  /* sbk_plan_step: the ring of free blocks cannot serve the step */
+#define SBK_ST_TABLE_FULL 64     /* sbk_plan_step: a table row or slot_mapping is too short for the step */
 
 int sbk_abi_version(void);
 const char* sbk_last_error(void);
@@ -197,6 +199,45 @@ int sbk_rope_kv_append(void* query, int H, int64_t q_token_stride_bytes, void* k
                        const int32_t* seq_lens, const int32_t* query_start_loc, int B,
                        int window_left, int32_t* retired_out, int max_retired, int32_t* status,
                        void* stream);
+
+/*
+ * Device-resident step planning and block allocation. State that stays on the GPU between steps:
+ *    seq_lens [B] int32, block_tables [B, max_blocks] int32 (-1 = no block),
+ *    ring [num_blocks] int32 (free block ids, FIFO), ctrl [4] uint64 (head, tail, lowest free
+ *    count seen, steps planned).
+ * sbk_plan_step does, in one launch, what the reference does on the host every step - the
+ * per-sequence loop of MetaAttentionMetadataBuilder (vllm_hymeta/attention/meta_attention.py:
+ * 435-494: context length, window-truncated block table, slot mapping) with the engine's block
+ * manager behind it - and what MetaAttentionMetadata.advance_step (:338-409) does on the device
+ * for multi-step decode. For every row b with n_new[b] > 0 (n_new NULL: one token per row):
+ *   - blocks wholly before max(0, seq_lens[b] - window_left) are retired: pushed on the ring,
+ *     their table entries set to -1 (retire != 0; window_left -1 retires nothing);
+ *   - missing table entries of the logical blocks the new tokens fall in are filled from the ring
+ *     (retirement first, so blocks freed by this step can be reused by it);
+ *   - slot_mapping [T] int64 and positions [T] int64 (or NULL) get one entry per new token,
+ *     tokens of row b at query_start_loc[b] ...; entries past the last token: slot -1;
+ *   - context_lens [B] (or NULL) = length before the step; query_start_loc [B+1] is written (it may
+ *     be NULL only when n_new is NULL); seq_lens[b] += n_new[b].
+ * ring == NULL (with ctrl NULL): no allocator; the tables are filled by someone else (the engine's
+ * scheduler) and a missing entry raises SBK_ST_OUT_OF_BLOCKS: this is advance_step.
+ * A step that cannot be served - ring too empty (SBK_ST_OUT_OF_BLOCKS), a row longer than its table
+ * or more new tokens than T (SBK_ST_TABLE_FULL) - changes no state and fills slot_mapping with -1.
+ * Pushes and pops are placed in row order, so the allocator is deterministic. One CTA; meant for
+ * B up to a few thousand rows. T must equal the host's count of new tokens or exceed it (padding).
+ *
+ * sbk_pool_init: ring <- 0..num_blocks-1, counters reset; seq_lens <- 0 and block_tables <- -1
+ * when given. sbk_release_rows: rows [n_rows] int32 name finished sequences; their live blocks go
+ * back on the ring, their entries become -1 and their lengths 0.
+ */
+int sbk_pool_init(int32_t* ring, uint64_t* ctrl, int num_blocks, int32_t* seq_lens,
+                  int32_t* block_tables, int max_blocks, int B, void* stream);
+int sbk_plan_step(const int32_t* n_new, int32_t* seq_lens, int32_t* block_tables, int max_blocks,
+                  int B, int block_size, int window_left, int retire, int32_t* ring, uint64_t* ctrl,
+                  int num_blocks, int64_t* slot_mapping, int64_t* positions, int32_t* context_lens,
+                  int32_t* query_start_loc, int T, int32_t* status, void* stream);
+int sbk_release_rows(const int32_t* rows, int n_rows, int32_t* seq_lens, int32_t* block_tables,
+                     int max_blocks, int B, int block_size, int32_t* ring, uint64_t* ctrl,
+                     int num_blocks, int32_t* status, void* stream);
 
 /*
  * Fused GLA recurrent-state step, in place in the slot cache:

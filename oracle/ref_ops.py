@@ -285,3 +285,81 @@ def rope_ref(x: torch.Tensor, cos: torch.Tensor, sin: torch.Tensor) -> torch.Ten
     half = x.shape[-1] // 2
     rot = torch.cat((-x[..., half:], x[..., :half]), dim=-1)
     return (x * cos[:, None, :]) + (rot * sin[:, None, :])
+
+
+class StepPlannerRef:
+    """CPU model of the device-resident step planner (libsbk's sbk_pool_init / sbk_plan_step /
+    sbk_release_rows): per-row lengths and block tables, a FIFO ring of free block ids. It carries
+    out, with the same visibility rule as retire_blocks / first_visible above, the per-sequence
+    work of MetaAttentionMetadataBuilder._add_seq_group (vllm_hymeta/attention/meta_attention.py:
+    435-494) and of MetaAttentionMetadata.advance_step (:338-409), plus the block hand-out the
+    reference leaves to the engine's block manager. Policy: rows in index order; within a step
+    every row's out-of-window blocks are pushed (oldest first) before any block is popped; a step
+    that cannot be served changes nothing and returns None."""
+
+    def __init__(self, num_blocks: int, block_size: int, B: int, max_blocks: int,
+                 window_left: int = -1, allocate: bool = True):
+        self.bs, self.B, self.max_blocks, self.wl = block_size, B, max_blocks, window_left
+        self.num_blocks = num_blocks
+        self.ring = list(range(num_blocks)) if allocate else None
+        self.lens = [0] * B
+        self.table = [[-1] * max_blocks for _ in range(B)]
+        self.min_free = num_blocks
+
+    def plan(self, n_new: Optional[List[int]] = None, T: Optional[int] = None, retire: bool = True):
+        n_new = [1] * self.B if n_new is None else [max(0, int(n)) for n in n_new]
+        total = sum(n_new)
+        T = total if T is None else T
+        pushes, need = [], 0
+        for b, n in enumerate(n_new):
+            if n == 0:
+                continue
+            L = self.lens[b]
+            lb0, lb1 = L // self.bs, (L + n - 1) // self.bs
+            if lb1 >= self.max_blocks or total > T:
+                return None
+            need += sum(1 for lb in range(lb0, lb1 + 1) if self.table[b][lb] < 0)
+            if retire:
+                first_live = first_visible(L + n, n, self.wl) // self.bs
+                j = first_live - 1
+                while j >= 0 and self.table[b][j] >= 0:
+                    j -= 1
+                pushes.append((b, j + 1, first_live))
+        n_push = sum(hi - lo for _, lo, hi in pushes)
+        if need > ((len(self.ring) + n_push) if self.ring is not None else 0):
+            return None
+        for b, lo, hi in pushes:
+            for j in range(lo, hi):
+                if self.ring is not None:
+                    self.ring.append(self.table[b][j])
+                self.table[b][j] = -1
+        slots, positions, ctx, qsl = [], [], [], [0]
+        for b, n in enumerate(n_new):
+            L = self.lens[b]
+            ctx.append(L)
+            qsl.append(qsl[-1] + n)
+            for lb in range(L // self.bs, (L + n - 1) // self.bs + 1 if n else 0):
+                if self.table[b][lb] < 0:
+                    self.table[b][lb] = self.ring.pop(0)
+            for t in range(L, L + n):
+                slots.append(self.table[b][t // self.bs] * self.bs + t % self.bs)
+                positions.append(t)
+            self.lens[b] = L + n
+        if self.ring is not None:
+            self.min_free = min(self.min_free, len(self.ring))
+        slots += [-1] * (T - total)
+        positions += [0] * (T - total)
+        return dict(slot_mapping=slots, positions=positions, context_lens=ctx, query_start_loc=qsl)
+
+    def release(self, rows: List[int]) -> None:
+        for b in rows:
+            L = self.lens[b]
+            last = min((L - 1) // self.bs if L > 0 else -1, self.max_blocks - 1)
+            j = last
+            while j >= 0 and self.table[b][j] >= 0:
+                j -= 1
+            for i in range(j + 1, last + 1):
+                if self.ring is not None:
+                    self.ring.append(self.table[b][i])
+                self.table[b][i] = -1
+            self.lens[b] = 0

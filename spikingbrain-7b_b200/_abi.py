@@ -14,6 +14,7 @@ LIB_PATH = os.environ.get("SBK_LIB_PATH") or os.path.join(PKG_DIR, "libsbk.so")
 SBK_BF16, SBK_F32 = 0, 1
 SBK_OK, SBK_E_ARG, SBK_E_ALIGN, SBK_E_WORKSPACE, SBK_E_LAUNCH = 0, -1, -2, -3, -4
 ST_BAD_SLOT, ST_BAD_BLOCK, ST_WAIT_TIMEOUT, ST_RETIRE_OVERFLOW, ST_BAD_POSITION = 1, 2, 4, 8, 16
+ST_OUT_OF_BLOCKS, ST_TABLE_FULL = 32, 64
 ABI_VERSION = 3
 
 # name -> (restype, argtypes); must list every function include/sbk.h declares
@@ -50,6 +51,13 @@ SIGNATURES = {
         c_void_p, c_int, c_int64, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p,
         c_void_p, c_int, c_int64, c_int, c_int, c_int, c_int, c_int64, c_int64, c_int, c_int64,
         c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_void_p, c_int, c_void_p, c_void_p]),
+    "sbk_pool_init": (c_int, [c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_void_p]),
+    "sbk_plan_step": (c_int, [
+        c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_int,
+        c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p]),
+    "sbk_release_rows": (c_int, [
+        c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p, c_void_p, c_int, c_void_p,
+        c_void_p]),
     "sbk_gla_step": (c_int, [
         c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int64, c_void_p, c_int, c_int,
         c_int, c_int, c_float, c_void_p, c_int, c_int, c_float, c_void_p, c_float, c_void_p,

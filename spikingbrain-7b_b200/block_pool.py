@@ -13,7 +13,7 @@ host mirror and the device table stay identical without reading anything back:
 Pure numpy: no tensor maths happens here.
 """
 from dataclasses import dataclass
-from typing import List, Sequence
+from typing import List, Sequence, Optional
 
 import numpy as np
 
@@ -218,3 +218,78 @@ class SlidingWindowBlockManager:
             self.pool.release(ids)
             out[int(row)] = ids
         return out
+
+
+class DeviceStepPlanner:
+    """The sliding-window block manager with its state on the GPU: lengths, block tables, the
+    ring of free block ids and the per-step metadata (slot mapping, positions, context lengths,
+    query starts) are device tensors that one `sbk_plan_step` launch advances, so a decode loop
+    needs no host work and no host-to-device copy per step, and the launch can sit in a CUDA
+    graph. It stands in for the per-step work of MetaAttentionMetadataBuilder
+    (vllm_hymeta/attention/meta_attention.py:435-494, 532-583), MetaAttentionMetadata.advance_step
+    (:338-409) and the engine's block manager. The host keeps no copy of the lengths;
+    `snapshot()` reads the state back when it is wanted (tests, debugging)."""
+
+    def __init__(self, num_blocks: int, block_size: int, window_left: int, max_seqs: int,
+                 max_blocks_per_seq: int, device, max_tokens: Optional[int] = None):
+        import torch
+        from . import ops
+        self._ops = ops
+        self.num_blocks, self.block_size, self.window_left = num_blocks, block_size, window_left
+        self.max_seqs, self.max_blocks = max_seqs, max_blocks_per_seq
+        T = max_tokens or max_seqs
+        i32 = dict(dtype=torch.int32, device=device)
+        self.ring = torch.empty(num_blocks, **i32)
+        self.ctrl = torch.zeros(4, dtype=torch.int64, device=device)
+        self.seq_lens = torch.empty(max_seqs, **i32)
+        self.block_tables = torch.empty(max_seqs, max_blocks_per_seq, **i32)
+        self.slot_mapping = torch.full((T,), -1, dtype=torch.int64, device=device)
+        self.positions = torch.zeros(T, dtype=torch.int64, device=device)
+        self.context_lens = torch.zeros(max_seqs, **i32)
+        self.query_start_loc = torch.zeros(max_seqs + 1, **i32)
+        self.status = torch.zeros(1, **i32)
+        ops.pool_init(self.ring, self.ctrl, self.seq_lens, self.block_tables)
+
+    def load_state(self, lens, table, free_ids) -> None:
+        """Adopt an existing state (host arrays): per-row lengths, the block table, and the ids of
+        the free blocks in the order they are to be handed out."""
+        import numpy as np
+        import torch
+        lens = np.ascontiguousarray(lens, dtype=np.int32)
+        table = np.ascontiguousarray(table, dtype=np.int32)
+        free_ids = np.ascontiguousarray(free_ids, dtype=np.int32)
+        if lens.shape != (self.max_seqs,) or table.shape != (self.max_seqs, self.max_blocks):
+            raise ValueError("lens / table do not match the planner's shape")
+        live = table[table >= 0]
+        if len(live) + len(free_ids) > self.num_blocks or len(np.unique(np.concatenate([live, free_ids]))) != len(live) + len(free_ids):
+            raise ValueError("a block id is owned twice (or the pool is over-subscribed)")
+        self.seq_lens.copy_(torch.from_numpy(lens))
+        self.block_tables.copy_(torch.from_numpy(table))
+        ring = np.zeros(self.num_blocks, dtype=np.int32)
+        ring[:len(free_ids)] = free_ids
+        self.ring.copy_(torch.from_numpy(ring))
+        self.ctrl.copy_(torch.tensor([0, len(free_ids), len(free_ids), 0], dtype=torch.int64))
+
+    def plan(self, n_new=None, retire: bool = True) -> None:
+        """Advance every row by n_new[b] tokens (device int32 [max_seqs]; None: one token each).
+        Results are in slot_mapping / positions / context_lens / query_start_loc / seq_lens /
+        block_tables; nothing is returned and nothing is synchronised."""
+        self._ops.plan_step(self.seq_lens, self.block_tables, self.slot_mapping,
+                            block_size=self.block_size, num_blocks=self.num_blocks,
+                            window_left=self.window_left, retire=retire, n_new=n_new, ring=self.ring,
+                            ctrl=self.ctrl, positions=self.positions, context_lens=self.context_lens,
+                            query_start_loc=self.query_start_loc, status=self.status)
+
+    def release(self, rows) -> None:
+        """rows: device int32 tensor of finished table rows; their blocks return to the ring."""
+        self._ops.release_rows(rows, self.seq_lens, self.block_tables, block_size=self.block_size,
+                               num_blocks=self.num_blocks, ring=self.ring, ctrl=self.ctrl,
+                               status=self.status)
+
+    def snapshot(self) -> dict:
+        """Host copy of the state (synchronises): lens, table, free ids in ring order, counters."""
+        head, tail, min_free, steps = (int(x) for x in self.ctrl.tolist())
+        ring = self.ring.tolist()
+        free = [ring[i % self.num_blocks] for i in range(head, tail)]
+        return dict(lens=self.seq_lens.tolist(), table=self.block_tables.tolist(), free=free,
+                    min_free=min_free, steps=steps, status=int(self.status.item()))

@@ -23,16 +23,17 @@ Tensors must live on a CUDA device: there is no CPU path.
 """
 from typing import Any, Dict, List, Optional, Tuple
 
-import numpy as np
 import torch
 import transformers
 
 from . import ops
-from .block_pool import SlidingWindowBlockManager
+from .block_pool import DeviceStepPlanner
 
 
 class _PagedWindow:
-    """Paged K/V of one sliding-window layer for a fixed batch of equally long sequences."""
+    """Paged K/V of one sliding-window layer for a fixed batch of equally long sequences. Lengths,
+    block table, free ring and slot mapping live on the device (DeviceStepPlanner): an append is
+    one planner launch and one append launch, with nothing copied from the host."""
 
     def __init__(self, B: int, kvh: int, D: int, dtype: torch.dtype, device, window: Optional[int],
                  block_size: int, capacity_tokens: int):
@@ -40,45 +41,47 @@ class _PagedWindow:
         self.window = window
         self.bs = block_size
         self.n_cached = 0  # tokens the reference class would hold now
+        self.L = 0         # length the planner holds for every row (relative to the table's column 0)
         self._alloc(capacity_tokens)
-        for row in range(B):
-            self.mgr.admit(row)
 
     def _alloc(self, capacity_tokens: int) -> None:
         self.max_blocks = -(-capacity_tokens // self.bs) + 2
-        nb = self.B * self.max_blocks
-        self.mgr = SlidingWindowBlockManager(nb, self.bs, -1 if self.window is None else self.window - 1,
-                                             self.B, self.max_blocks)
+        if self.window is None:
+            per_row = self.max_blocks
+        else:  # the window, the partial blocks at both ends, and a chunk of up to `window` new tokens
+            per_row = min(self.max_blocks, 2 * (-(-self.window // self.bs)) + 3)
+        nb = self.B * per_row
+        self.plan = DeviceStepPlanner(nb, self.bs, -1 if self.window is None else self.window - 1,
+                                      self.B, self.max_blocks, self.device, max_tokens=self.B)
         self.kv = torch.zeros(2, nb, self.bs, self.kvh, self.D, dtype=self.dtype, device=self.device)
-        self.table_d = torch.full((self.B, self.max_blocks), -1, dtype=torch.int32, device=self.device)
-        self.lens_d = torch.zeros(self.B, dtype=torch.int32, device=self.device)
-        self.status = torch.zeros(1, dtype=torch.int32, device=self.device)
+        self.table_d, self.lens_d, self.status = self.plan.block_tables, self.plan.seq_lens, self.plan.status
+        self._n_new = torch.zeros(self.B, dtype=torch.int32, device=self.device)
+        self.L = 0
+        self._first_live = 0   # table columns the planner has retired so far (the same for every row)
 
     # The logical block index of a sequence only ever grows; before it would run off the table
     # the live blocks are moved back to column 0 (positions are relative, nothing else changes).
     def _make_room(self, n: int) -> None:
-        L = int(self.mgr.lens[0])
-        if (L + n + self.bs - 1) // self.bs <= self.max_blocks:
+        if (self.L + n + self.bs - 1) // self.bs <= self.max_blocks:
             return
         if self.window is None:  # unbounded layer: double the pool and carry the contents over
             k_all, v_all = self.gather()
-            self._alloc(2 * (L + n))
-            for row in range(self.B):
-                self.mgr.admit(row)
+            self._alloc(2 * (self.L + n))
             self.n_cached = 0
             self.append(k_all, v_all)
             return
-        shift = int(self.mgr._first_live.min())
+        # every row has the same length, so the same leading blocks have been retired
+        shift = self._first_live
         if shift == 0:
             raise RuntimeError("window layer out of table columns with nothing retired")
-        m = self.mgr
-        m.table[:, :-shift] = m.table[:, shift:]
-        m.table[:, -shift:] = -1
-        m.lens -= shift * self.bs
-        m._first_live -= shift
-        self.table_d.copy_(torch.from_numpy(m.table))
-        self.lens_d.copy_(torch.from_numpy(m.lens))
-        if (int(m.lens[0]) + n + self.bs - 1) // self.bs > self.max_blocks:
+        t = self.table_d
+        moved = t[:, shift:].clone()
+        t.fill_(-1)
+        t[:, :self.max_blocks - shift] = moved
+        self.lens_d.sub_(shift * self.bs)
+        self.L -= shift * self.bs
+        self._first_live = 0
+        if (self.L + n + self.bs - 1) // self.bs > self.max_blocks:
             raise RuntimeError(f"{n} new tokens do not fit the table of a window-{self.window} layer")
 
     def append(self, k: torch.Tensor, v: torch.Tensor, rope=None) -> Optional[torch.Tensor]:
@@ -105,20 +108,24 @@ class _PagedWindow:
             n_cached = self.n_cached + n
         self._make_room(n)
         self.n_cached = n_cached
-        plan = self.mgr.advance(np.full(self.B, n, dtype=np.int64), pad_inactive=(n == 1))
-        if plan.new_entries.size:
-            e = torch.from_numpy(plan.new_entries).to(self.device, non_blocking=True).long()
-            self.table_d[e[:, 0], e[:, 1]] = e[:, 2].int()
-        slots = torch.from_numpy(plan.slot_mapping).to(self.device, non_blocking=True)
-        self.lens_d.copy_(torch.from_numpy(plan.seq_lens), non_blocking=True)
-        qsl = torch.from_numpy(plan.query_start_loc).to(self.device, non_blocking=True)
+        if W is not None:   # what this step's planner launch retires (rule of sbk_plan_step)
+            self._first_live = max(self._first_live, max(0, self.L - (W - 1)) // self.bs)
+        self.L += n
+        plan = self.plan
+        if plan.slot_mapping.numel() < self.B * n:
+            plan.slot_mapping = torch.full((self.B * n,), -1, dtype=torch.int64, device=self.device)
+            plan.positions = torch.zeros(self.B * n, dtype=torch.int64, device=self.device)
+        if n == 1:
+            plan.plan()
+        else:
+            self._n_new.fill_(n)
+            plan.plan(self._n_new)
+        slots = plan.slot_mapping[:self.B * n]
         # token-major rows [T, kvh, D]; a view for one new token, a copy for a prompt chunk
         tm = lambda t: t.transpose(1, 2).reshape(self.B * t.shape[-2], t.shape[1], self.D).contiguous()
         kt, vt = tm(k), tm(v)
         if rope is None:
-            ops.kv_append(kt, vt, self.kv[0], self.kv[1], slots, block_tables=self.table_d,
-                          seq_lens=self.lens_d, query_start_loc=qsl, window_left=self.mgr.window_left,
-                          status=self.status)
+            ops.kv_append(kt, vt, self.kv[0], self.kv[1], slots, status=self.status)
             return None
         q, position_ids, table = rope
         if n_in != n:  # prompt longer than the window: every token is rotated, the last W are cached
@@ -128,8 +135,7 @@ class _PagedWindow:
         qt = tm(q) if q is not None else None
         ops.rope_kv_append(qt, kt, vt, self.kv[0], self.kv[1], slots,
                            position_ids.to(torch.int64).expand(self.B, n_in).reshape(-1).contiguous(), table,
-                           block_tables=self.table_d, seq_lens=self.lens_d, query_start_loc=qsl,
-                           window_left=self.mgr.window_left, status=self.status)
+                           status=self.status)
         return None if qt is None else qt.view(self.B, n_in, q.shape[1], self.D).transpose(1, 2)
 
     def gather(self) -> Tuple[torch.Tensor, torch.Tensor]:

@@ -449,3 +449,85 @@ def swa_prefill(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, b
     global LAUNCHES
     LAUNCHES += 1 if (n_seqs and max_query_len) else 0
     return out
+
+
+# ----------------------------------------------------------------- device-resident planning
+def _i32(t, name, n=None):
+    if t is None:
+        return
+    if t.dtype != torch.int32 or not t.is_contiguous() or (n is not None and t.numel() != n):
+        raise ValueError(f"{name} must be contiguous int32" + (f" with {n} entries" if n is not None else ""))
+
+
+def pool_init(ring: torch.Tensor, ctrl: torch.Tensor, seq_lens: Optional[torch.Tensor] = None,
+              block_tables: Optional[torch.Tensor] = None) -> None:
+    """ring [num_blocks] int32 <- 0..num_blocks-1, ctrl [4] int64 counters reset; lengths and
+    tables cleared when given."""
+    _need_cuda(ring, ctrl, seq_lens, block_tables)
+    _i32(ring, "ring")
+    if ctrl.dtype != torch.int64 or ctrl.numel() != 4 or not ctrl.is_contiguous():
+        raise ValueError("ctrl must be contiguous int64 [4]")
+    B = max_blocks = 0
+    if block_tables is not None:
+        _i32(block_tables, "block_tables")
+        B, max_blocks = block_tables.shape
+    if seq_lens is not None:
+        _i32(seq_lens, "seq_lens", B if block_tables is not None else None)
+        B = seq_lens.numel()
+    rc = _abi.lib.sbk_pool_init(_ptr(ring), _ptr(ctrl), ring.numel(), _ptr(seq_lens), _ptr(block_tables),
+                                max_blocks, B, _stream())
+    _abi.check("sbk_pool_init", rc)
+
+
+def plan_step(seq_lens: torch.Tensor, block_tables: torch.Tensor, slot_mapping: torch.Tensor, *,
+              block_size: int, num_blocks: int, window_left: int = -1, retire: bool = True,
+              n_new: Optional[torch.Tensor] = None, ring: Optional[torch.Tensor] = None,
+              ctrl: Optional[torch.Tensor] = None, positions: Optional[torch.Tensor] = None,
+              context_lens: Optional[torch.Tensor] = None, query_start_loc: Optional[torch.Tensor] = None,
+              status: Optional[torch.Tensor] = None) -> None:
+    """One launch that retires out-of-window blocks, allocates the blocks of the new tokens from
+    the ring, writes slot_mapping / positions / context_lens / query_start_loc and advances
+    seq_lens, all on device-resident state (see sbk_plan_step in include/sbk.h)."""
+    _need_cuda(seq_lens, block_tables, slot_mapping, n_new, ring, ctrl, positions, context_lens,
+               query_start_loc, status)
+    B, max_blocks = block_tables.shape
+    _i32(block_tables, "block_tables")
+    _i32(seq_lens, "seq_lens", B)
+    _i32(n_new, "n_new", B)
+    _i32(ring, "ring", num_blocks if ring is not None else None)
+    _i32(context_lens, "context_lens", B)
+    _i32(query_start_loc, "query_start_loc", B + 1)
+    T = slot_mapping.numel()
+    for t, nm in ((slot_mapping, "slot_mapping"), (positions, "positions")):
+        if t is not None and (t.dtype != torch.int64 or not t.is_contiguous() or t.numel() != T):
+            raise ValueError(f"{nm} must be contiguous int64 [T]")
+    if (ring is None) != (ctrl is None):
+        raise ValueError("ring and ctrl come together")
+    if ctrl is not None and (ctrl.dtype != torch.int64 or ctrl.numel() != 4 or not ctrl.is_contiguous()):
+        raise ValueError("ctrl must be contiguous int64 [4]")
+    if n_new is not None and query_start_loc is None:
+        raise ValueError("n_new needs a query_start_loc buffer")
+    rc = _abi.lib.sbk_plan_step(_ptr(n_new), _ptr(seq_lens), _ptr(block_tables), max_blocks, B, block_size,
+                                window_left, int(retire), _ptr(ring), _ptr(ctrl), num_blocks,
+                                _ptr(slot_mapping), _ptr(positions), _ptr(context_lens),
+                                _ptr(query_start_loc), T, _ptr(status), _stream())
+    _abi.check("sbk_plan_step", rc)
+    global LAUNCHES
+    LAUNCHES += 1
+
+
+def release_rows(rows: torch.Tensor, seq_lens: torch.Tensor, block_tables: torch.Tensor, *,
+                 block_size: int, num_blocks: int, ring: Optional[torch.Tensor] = None,
+                 ctrl: Optional[torch.Tensor] = None, status: Optional[torch.Tensor] = None) -> None:
+    """Give the blocks of the finished sequences ``rows`` [n] int32 back to the ring."""
+    _need_cuda(rows, seq_lens, block_tables, ring, ctrl, status)
+    B, max_blocks = block_tables.shape
+    _i32(rows, "rows")
+    _i32(block_tables, "block_tables")
+    _i32(seq_lens, "seq_lens", B)
+    _i32(ring, "ring", num_blocks if ring is not None else None)
+    rc = _abi.lib.sbk_release_rows(_ptr(rows), rows.numel(), _ptr(seq_lens), _ptr(block_tables), max_blocks,
+                                   B, block_size, _ptr(ring), _ptr(ctrl), num_blocks, _ptr(status), _stream())
+    _abi.check("sbk_release_rows", rc)
+    global LAUNCHES
+    LAUNCHES += 1 if rows.numel() else 0

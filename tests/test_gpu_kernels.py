@@ -657,3 +657,112 @@ def test_argument_errors_are_reported(ops):
                        window_left=63)  # 9 query heads per kv head
     with pytest.raises(RuntimeError):
         ops.gla_step(q.cpu(), q.cpu(), q.cpu(), q.cpu(), torch.zeros(1, 28, 128, 128))
+
+
+# ---------------------------------------------------------------- device-resident planner
+def _planner_pair(num_blocks, bs, B, max_blocks, wl, T=None):
+    from spikingbrain_7b_b200.block_pool import DeviceStepPlanner
+    dev = DeviceStepPlanner(num_blocks, bs, wl, B, max_blocks, DEV, max_tokens=T)
+    ref = ref_ops.StepPlannerRef(num_blocks, bs, B, max_blocks, wl)
+    return dev, ref
+
+
+def _same_state(dev, ref):
+    snap = dev.snapshot()
+    assert snap["lens"] == ref.lens and snap["table"] == ref.table
+    assert snap["free"] == ref.ring and snap["min_free"] == ref.min_free
+    return snap
+
+
+def test_plan_step_decode_stream_is_bit_exact_with_cpu_model(ops):
+    """Prompts of ragged lengths, then 100 one-token steps: every slot, position, table entry and
+    the order of the free ring equal the CPU model; resident blocks stay within the window."""
+    B, bs, wl, max_blocks = 7, 16, 40, 64
+    dev, ref = _planner_pair(B * 5 + 3, bs, B, max_blocks, wl, T=256)
+    n0 = [33, 1, 64, 17, 0, 48, 90]
+    want = ref.plan(n0, T=256)
+    dev.plan(torch.tensor(n0, dtype=torch.int32, device=DEV))
+    assert dev.slot_mapping.tolist() == want["slot_mapping"]
+    assert dev.positions.tolist()[:sum(n0)] == want["positions"][:sum(n0)]
+    assert dev.query_start_loc.tolist() == want["query_start_loc"]
+    assert dev.context_lens.tolist() == want["context_lens"]
+    _same_state(dev, ref)
+    for step in range(100):
+        want = ref.plan(None, T=256)
+        dev.plan()
+        assert dev.slot_mapping.tolist() == want["slot_mapping"], f"step {step}"
+        assert dev.positions.tolist()[:B] == want["positions"][:B]
+    snap = _same_state(dev, ref)
+    assert snap["status"] == 0
+    for row in snap["table"]:
+        assert sum(1 for x in row if x >= 0) <= (wl + 1 + bs - 1) // bs + 1
+    live = [x for row in snap["table"] for x in row if x >= 0]
+    assert len(set(live)) == len(live) and not set(live) & set(snap["free"])
+    assert len(live) + len(snap["free"]) == dev.num_blocks            # no block lost, none owned twice
+
+
+def test_plan_step_churn_with_releases_and_chunked_prompts(ops):
+    """Rows finish and are re-admitted with new prompts (some in chunks) while others decode."""
+    import random
+    rng = random.Random(5)
+    B, bs, wl, max_blocks = 24, 16, 63, 40
+    dev, ref = _planner_pair(B * 6, bs, B, max_blocks, wl, T=B * 96)
+    T = B * 96
+    active = [False] * B
+    for step in range(60):
+        done = [b for b in range(B) if active[b] and (rng.random() < 0.08 or ref.lens[b] > 500)]
+        if done:
+            ref.release(done)
+            dev.release(torch.tensor(done, dtype=torch.int32, device=DEV))
+            for b in done:
+                active[b] = False
+        n_new = []
+        for b in range(B):
+            if active[b]:
+                n_new.append(1)
+            elif rng.random() < 0.5:
+                n_new.append(rng.choice([1, 15, 16, 17, 50, 96]))
+                active[b] = True
+            else:
+                n_new.append(0)
+        want = ref.plan(n_new, T=T)
+        assert want is not None
+        dev.plan(torch.tensor(n_new, dtype=torch.int32, device=DEV))
+        assert dev.slot_mapping.tolist() == want["slot_mapping"], f"step {step}"
+        assert dev.query_start_loc.tolist() == want["query_start_loc"]
+        assert dev.context_lens.tolist() == want["context_lens"]
+    snap = _same_state(dev, ref)
+    assert snap["status"] == 0 and snap["steps"] == 60
+
+
+def test_plan_step_refuses_cleanly_when_the_ring_is_empty_or_a_row_is_full(ops):
+    dev, ref = _planner_pair(4, 16, 2, 8, -1, T=2)      # no window: nothing is ever retired
+    for _ in range(32):                                  # 2 rows x 2 blocks = the whole pool
+        dev.plan(); ref.plan(None, T=2)
+    before = _same_state(dev, ref)
+    dev.plan()                                           # both rows need a third block
+    assert ref.plan(None, T=2) is None
+    after = dev.snapshot()
+    assert after["status"] == 32 and dev.slot_mapping.tolist() == [-1, -1]
+    assert {k: after[k] for k in ("lens", "table", "free")} == {k: before[k] for k in ("lens", "table", "free")}
+    dev2, _ = _planner_pair(64, 16, 1, 2, -1, T=1)       # a table row of two columns
+    for _ in range(32):
+        dev2.plan()
+    assert dev2.snapshot()["status"] == 0
+    dev2.plan()
+    assert dev2.snapshot()["status"] == 64 and dev2.seq_lens.item() == 32
+
+
+def test_plan_step_without_ring_is_advance_step(ops):
+    """Tables filled by the engine: lengths and slots advance, a missing block is reported."""
+    B, bs = 3, 16
+    tables = torch.tensor([[5, 9, -1], [2, -1, -1], [7, 1, 3]], dtype=torch.int32, device=DEV)
+    lens = torch.tensor([20, 15, 40], dtype=torch.int32, device=DEV)
+    slots = torch.empty(4, dtype=torch.int64, device=DEV)
+    pos = torch.empty(4, dtype=torch.int64, device=DEV)
+    st = _status()
+    ops.plan_step(lens, tables, slots, block_size=bs, num_blocks=10, retire=False, positions=pos, status=st)
+    assert slots.tolist() == [9 * 16 + 4, 2 * 16 + 15, 3 * 16 + 8, -1] and pos.tolist()[:3] == [20, 15, 40]
+    assert lens.tolist() == [21, 16, 41] and st.item() == 0
+    ops.plan_step(lens, tables, slots, block_size=bs, num_blocks=10, retire=False, status=st)   # row 1 needs a block
+    assert st.item() == 32 and lens.tolist() == [21, 16, 41] and slots.tolist() == [-1] * 4

@@ -313,3 +313,48 @@ def test_cos_sin_table_rows_equal_reference_rotary_embedding(sb, name):
     rows = table[torch.tensor(ROPE_POSITIONS)]
     assert torch.equal(rows[:, :D // 2], want["cos"][:, :D // 2])
     assert torch.equal(rows[:, D // 2:], want["sin"][:, :D // 2])
+
+
+# ------------------------------------------------------- CPU model of the device planner
+def test_step_planner_model_agrees_with_host_manager_and_window_rule():
+    """The planner model (FIFO ring) and the host block manager (LIFO pool) hand out different
+    ids but must agree on everything the window rule fixes: lengths, which logical blocks are
+    live, one slot per token inside the right logical block; and no id is ever owned twice."""
+    from spikingbrain_7b_b200.block_pool import SlidingWindowBlockManager
+    B, bs, wl, max_blocks, nb = 5, 16, 40, 64, 40
+    ref = ref_ops.StepPlannerRef(nb, bs, B, max_blocks, wl)
+    mgr = SlidingWindowBlockManager(nb, bs, wl, B, max_blocks)
+    for r in range(B):
+        mgr.admit(r)
+    steps = [[33, 1, 64, 17, 48]] + [[1] * B] * 70 + [[16, 1, 1, 5, 1]] + [[1] * B] * 10
+    for n_new in steps:
+        want = ref.plan(n_new)
+        plan = mgr.advance(np.array(n_new, dtype=np.int64), pad_inactive=False)
+        assert ref.lens == mgr.lens.tolist() == plan.seq_lens.tolist()
+        assert want["query_start_loc"] == plan.query_start_loc.tolist()
+        live_ref = [[j for j, x in enumerate(row) if x >= 0] for row in ref.table]
+        live_mgr = [[j for j, x in enumerate(row) if x >= 0] for row in mgr.table.tolist()]
+        assert live_ref == live_mgr
+        for t, (slot, pos) in enumerate(zip(want["slot_mapping"], want["positions"])):
+            b = max(i for i in range(B) if want["query_start_loc"][i] <= t and n_new[i] > 0
+                    and want["query_start_loc"][i] + n_new[i] > t)
+            assert slot // bs == ref.table[b][pos // bs] and slot % bs == pos % bs
+        owned = [x for row in ref.table for x in row if x >= 0]
+        assert len(set(owned)) == len(owned) and not set(owned) & set(ref.ring)
+        assert len(owned) + len(ref.ring) == nb
+        for b in range(B):   # nothing visible was retired, nothing invisible is kept beyond one block
+            t0 = ref_ops.first_visible(ref.lens[b], 1, wl)
+            assert all(ref.table[b][j] >= 0 for j in range(t0 // bs, (ref.lens[b] - 1) // bs + 1))
+
+
+def test_step_planner_model_refuses_without_side_effects():
+    ref = ref_ops.StepPlannerRef(4, 16, 2, 8, -1)
+    for _ in range(32):
+        assert ref.plan() is not None
+    state = (list(ref.lens), [list(r) for r in ref.table], list(ref.ring))
+    assert ref.plan() is None
+    assert state == (ref.lens, ref.table, ref.ring)
+    held = [x for x in ref.table[1] if x >= 0]
+    ref.release([1])
+    assert ref.ring == held and ref.lens[1] == 0 and all(x < 0 for x in ref.table[1])
+    assert ref.plan([1, 0]) is not None and ref.lens == [33, 0]
