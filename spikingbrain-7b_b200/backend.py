@@ -537,7 +537,7 @@ class MetaAttentionImpl:
         width = block_tables.shape[1] * bs
         vis = width if window_left < 0 else min(width, window_left + 1)
         split = ops.swa_auto_split(B, vis, q.device)
-        max_pieces = ops.swa_max_pieces(vis, split)
+        max_pieces = ops.swa_max_pieces(vis, split, B, q.device)
         D = self.head_size
         if q.stride()[1:] != (D, 1):
             q = q.contiguous()

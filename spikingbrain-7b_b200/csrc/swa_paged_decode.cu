@@ -6,6 +6,10 @@
 //   visible window [t0, seq_len). The grid is two CTAs per SM; each CTA draws items from a
 //   global ticket counter until none is left, so ragged batches balance themselves and the
 //   copy pipeline never drains between items.
+//   Balanced mode (split_chunks < 0) drops the tickets: the chunks of all sequences, laid end to
+//   end, are cut into one equal run per CTA (a run may cross sequence boundaries; each
+//   sequence it touches is one item), so every CTA streams the same number of bytes whatever
+//   the batch size or the spread of lengths, in a single wave.
 // Data movement
 //   One producer warp per CTA walks the block table and issues TMA tensor copies
 //   (cp.async.bulk.tensor, no multicast) of 16-token tiles -- all kv heads of a token are one
@@ -122,6 +126,7 @@ struct Params {
   float* ws_o; float* ws_ml; int split_chunks; int max_pieces; int32_t* status;
   int tile_copy;      // 1: one copy per tile (permuted-stride map), 0: one copy per 128-byte row
   int n_meta_chunks;  // 16-token chunks of always-visible sink keys (key2/value2), 0 = none
+  int balanced;       // 1: equal runs of chunks per CTA; split_chunks is then the shortest run allowed
 };
 
 template <int KVH, typename TO>
@@ -150,9 +155,11 @@ swa_decode_kernel(const Params P, const __grid_constant__ CUtensorMap map_k,
       mbar_init(bar_empty + 8 * s, kConsumerWarps);
     }
     misc[0] = 0;
+    misc[7] = 0;
     pre[0] = 0;
     fence_mbar_init();
   }
+  __syncthreads();
   // ---- number of pieces of every sequence, as an exclusive prefix: item w belongs to the
   //      sequence b with pre[b] <= w < pre[b+1] ----
   {
@@ -161,7 +168,19 @@ swa_decode_kernel(const Params P, const __grid_constant__ CUtensorMap map_k,
       const int b = base + threadIdx.x;
       const int Lb = b < P.B ? P.seq_lens[b] : 0;
       if (b < P.B) lens_s[b] = Lb;
-      int incl = b < P.B ? make_plan(Lb, P.window_left, P.split_chunks, P.max_pieces).n_pieces : 0;
+      int incl = 0;
+      if (b < P.B) {
+        const Plan pl = make_plan(Lb, P.window_left, P.split_chunks, P.max_pieces);
+        // balanced mode counts chunks (sink chunks included; an empty sequence keeps one, so that
+        // somebody writes its zero output), ticket mode counts pieces
+        incl = P.balanced ? (Lb > 0 ? P.n_meta_chunks + pl.n_chunks : 1) : pl.n_pieces;
+      }
+      if (P.balanced) {
+        int mx = incl;
+#pragma unroll
+        for (int off = 16; off > 0; off >>= 1) mx = max(mx, __shfl_xor_sync(0xffffffffu, mx, off));
+        if (lane == 0) atomicMax(const_cast<int*>(&misc[7]), mx);
+      }
 #pragma unroll
       for (int off = 1; off < 32; off <<= 1) {
         const int t = __shfl_up_sync(0xffffffffu, incl, off);
@@ -188,38 +207,24 @@ swa_decode_kernel(const Params P, const __grid_constant__ CUtensorMap map_k,
     // ================================= producer =================================
     int it = 0;
     bool aborted = false;
-    int w_next = 0;
-    if (lane == 0) w_next = atomicAdd(&P.ctrl[0], 1);
-    while (!aborted) {
-      const int w = __shfl_sync(0xffffffffu, w_next, 0);
-      if (w >= total) break;
-      if (lane == 0) w_next = atomicAdd(&P.ctrl[0], 1);   // the next ticket is on its way while this item streams
-      int lo_b = 0, hi_b = P.B;   // largest b with pre[b] <= w
-      while (hi_b - lo_b > 1) {
-        const int mid = (lo_b + hi_b) >> 1;
-        if (pre[mid] <= w) lo_b = mid; else hi_b = mid;
-      }
-      const int b = lo_b;
-      const int piece = w - pre[b];
+
+    // Streams one item: sink chunks [meta_a, meta_b) of the [n_meta, kvh, D] tensors, as stages of
+    // their own, then window chunks [cb, cb + n) of sequence b (n == 0 with no sink chunk still
+    // sends one empty stage, so that an empty sequence gets its zero output written).
+    auto stream_item = [&](int b, int piece, int n_pieces, int meta_a, int meta_b, int cb, int n) {
       const int L = lens_s[b];
-      const Plan plan = make_plan(L, P.window_left, P.split_chunks, P.max_pieces);
-      const int cb = plan.c_first + piece * plan.chunks_per_piece;
-      int n = plan.n_chunks - piece * plan.chunks_per_piece;
-      if (n > plan.chunks_per_piece) n = plan.chunks_per_piece;
-      if (n < 0) n = 0;
+      const int t0 = first_visible(L, 1, P.window_left);
+      const int n_ms = (meta_b - meta_a + C::kSub - 1) / C::kSub;
       int nst = (n + C::kSub - 1) / C::kSub;
-      if (nst < 1) nst = 1;   // an empty sequence still gets its (zero) output written
+      if (nst < 1 && n_ms < 1) nst = 1;
       const int item_end = (cb + n) * kChunk;
       const int32_t* table = P.block_tables + (int64_t)b * P.max_blocks;
       int64_t pb_lane = -1;   // physical block of chunk (batch_c0 + lane): one table read per 32 chunks
       int batch_c0 = 0;
-      // Sink ("meta") keys are visible to every query: the first piece of a sequence streams them
-      // ahead of its window, as stages of their own from the [n_meta, kvh, D] tensors.
-      const int n_ms = (piece == 0 && L > 0) ? (P.n_meta_chunks + C::kSub - 1) / C::kSub : 0;
       for (int jj = -n_ms; jj < nst; ++jj, ++it) {
         const bool meta = jj < 0;
         const int j = meta ? jj + n_ms : jj;
-        const int c0 = meta ? j * C::kSub : cb + j * C::kSub;       // first chunk of this stage
+        const int c0 = meta ? meta_a + j * C::kSub : cb + j * C::kSub;       // first chunk of this stage
         if (!meta && (j == 0 || c0 + C::kSub > batch_c0 + 32)) {
           batch_c0 = c0;
           const int c = c0 + lane;
@@ -231,17 +236,17 @@ swa_decode_kernel(const Params P, const __grid_constant__ CUtensorMap map_k,
         if (use > 0 && !mbar_wait_bounded(bar_empty + 8 * s, (use - 1) & 1)) {
           if (lane == 0) { raise_status(P.status, SBK_ST_WAIT_TIMEOUT); misc[0] = 1; }
           aborted = true;
-          break;
+          return;
         }
-        if (misc[0]) { aborted = true; break; }
+        if (misc[0]) { aborted = true; return; }
         const int tok_base = c0 * kChunk;
         int lo, hi;
         if (meta) {
           lo = tok_base;
           hi = tok_base + C::kStageTokens;
-          if (hi > P.n_meta_chunks * kChunk) hi = P.n_meta_chunks * kChunk;
+          if (hi > meta_b * kChunk) hi = meta_b * kChunk;
         } else {
-          lo = tok_base > plan.t0 ? tok_base : plan.t0;
+          lo = tok_base > t0 ? tok_base : t0;
           hi = tok_base + C::kStageTokens;
           if (hi > L) hi = L;
           if (hi > item_end) hi = item_end;
@@ -271,7 +276,7 @@ swa_decode_kernel(const Params P, const __grid_constant__ CUtensorMap map_k,
         }
         if (lane == 0) {
           StageInfo si;
-          si.b = b; si.piece = piece; si.n_pieces = plan.n_pieces; si.tok_base = tok_base;
+          si.b = b; si.piece = piece; si.n_pieces = n_pieces; si.tok_base = tok_base;
           si.lo = lo; si.hi = hi; si.pad = 0;
           si.flags = (jj == -n_ms ? kFlagFirst : 0) | (jj == nst - 1 ? kFlagLast : 0) | (bad ? kFlagBad : 0);
           info[s] = si;
@@ -286,6 +291,77 @@ swa_decode_kernel(const Params P, const __grid_constant__ CUtensorMap map_k,
           if (P.tile_copy) tma_load_4d(dst, map, 0, tin, 0, (int)pb, bar_full + 8 * s);
           else tma_load_4d(dst, map, 0, row, tin, (int)pb, bar_full + 8 * s);
         }
+      }
+    };
+
+    if (P.balanced) {
+      // ---- equal runs of chunks: CTA g streams global chunks [g * per, (g + 1) * per) ----
+      const int n_cta = (int)gridDim.x;
+      int per = (total + n_cta - 1) / n_cta;
+      if (per < P.split_chunks) per = P.split_chunks;
+      // a sequence of C chunks meets at most ceil(C / per) + 1 runs: keep that within max_pieces
+      if (P.max_pieces > 1) {
+        const int need = (misc[7] + P.max_pieces - 2) / (P.max_pieces - 1);
+        if (per < need) per = need;
+      } else if (per < misc[7]) {
+        per = misc[7];
+      }
+      if (per < 1) per = 1;
+      const int64_t g0 = (int64_t)blockIdx.x * per;
+      const int64_t g1 = g0 + per < total ? g0 + per : total;
+      // A batch of near-equal sequences that already fills at least half of the CTAs streams
+      // fastest as whole sequences (no partials to write and fold): sequence b goes to CTA
+      // b mod n_cta. The kernel is bound by HBM, not by the busiest CTA, as long as enough CTAs
+      // keep copies in flight.
+      const bool whole = 2 * P.B >= n_cta && (int64_t)misc[7] * P.B <= (int64_t)total + total / 8;
+      if (whole) {
+        for (int b = (int)blockIdx.x; b < P.B && !aborted; b += n_cta) {
+          const int L = lens_s[b];
+          const Plan plan = make_plan(L, P.window_left, P.split_chunks, P.max_pieces);
+          stream_item(b, 0, 1, 0, L > 0 ? P.n_meta_chunks : 0, plan.c_first, plan.n_chunks);
+        }
+      } else if (g0 < total) {
+        int lo_b = 0, hi_b = P.B;   // largest b with pre[b] <= g0
+        while (hi_b - lo_b > 1) {
+          const int mid = (lo_b + hi_b) >> 1;
+          if (pre[mid] <= g0) lo_b = mid; else hi_b = mid;
+        }
+        for (int b = lo_b; b < P.B && pre[b] < g1 && !aborted; ++b) {
+          const int L = lens_s[b];
+          const Plan plan = make_plan(L, P.window_left, P.split_chunks, P.max_pieces);
+          const int nm = L > 0 ? P.n_meta_chunks : 0;
+          const int va = (int)(g0 > pre[b] ? g0 - pre[b] : 0);
+          const int vb = (int)((g1 < pre[b + 1] ? g1 : pre[b + 1]) - pre[b]);
+          const int first_run = pre[b] / per;
+          const int n_pieces = (pre[b + 1] - 1) / per - first_run + 1;
+          const int ma = va < nm ? va : nm, mb = vb < nm ? vb : nm;
+          const int wa = (va > nm ? va : nm) - nm, wb = (vb > nm ? vb : nm) - nm;
+          stream_item(b, (int)blockIdx.x - first_run, n_pieces, ma, mb, plan.c_first + wa,
+                      L > 0 ? wb - wa : 0);
+        }
+      }
+    } else {
+      int w_next = 0;
+      if (lane == 0) w_next = atomicAdd(&P.ctrl[0], 1);
+      while (!aborted) {
+        const int w = __shfl_sync(0xffffffffu, w_next, 0);
+        if (w >= total) break;
+        if (lane == 0) w_next = atomicAdd(&P.ctrl[0], 1);   // the next ticket is on its way while this item streams
+        int lo_b = 0, hi_b = P.B;   // largest b with pre[b] <= w
+        while (hi_b - lo_b > 1) {
+          const int mid = (lo_b + hi_b) >> 1;
+          if (pre[mid] <= w) lo_b = mid; else hi_b = mid;
+        }
+        const int b = lo_b;
+        const int piece = w - pre[b];
+        const int L = lens_s[b];
+        const Plan plan = make_plan(L, P.window_left, P.split_chunks, P.max_pieces);
+        const int cb = plan.c_first + piece * plan.chunks_per_piece;
+        int n = plan.n_chunks - piece * plan.chunks_per_piece;
+        if (n > plan.chunks_per_piece) n = plan.chunks_per_piece;
+        if (n < 0) n = 0;
+        // sink keys are visible to every query: the first piece of a sequence streams them
+        stream_item(b, piece, plan.n_pieces, 0, (piece == 0 && L > 0) ? P.n_meta_chunks : 0, cb, n);
       }
     }
     if (!aborted) {
@@ -304,7 +380,7 @@ swa_decode_kernel(const Params P, const __grid_constant__ CUtensorMap map_k,
         misc[0] = 1;
       }
       // the CTA that draws the last losing ticket rewinds the counters for the next launch
-      if (lane == 0) {
+      if (lane == 0 && !P.balanced) {
         const int f = atomicAdd(&P.ctrl[1], 1);
         if (f == (int)gridDim.x - 1) { P.ctrl[0] = 0; P.ctrl[1] = 0; __threadfence(); }
       }
@@ -556,17 +632,34 @@ swa_decode_kernel(const Params P, const __grid_constant__ CUtensorMap map_k,
       const int d4 = threadIdx.x & 31;
       for (int h = threadIdx.x >> 5; h < P.H; h += kConsumerWarps) {
         const int64_t hb = (int64_t)si.b * P.max_pieces * P.H + h;
-        float M = -INFINITY;
-        for (int pc = 0; pc < si.n_pieces; ++pc) M = fmaxf(M, __ldcg(P.ws_ml + (hb + (int64_t)pc * P.H) * 2));
-        const float Ms = fmaxf(M, kNegBig);
-        float Ls = 0.f;
+        // one pass with a running maximum; four pieces' loads (8 requests) are in flight at a time,
+        // so the fold costs a few L2 round trips per head instead of one per piece
+        float M = -INFINITY, Ls = 0.f;
         float4 O = make_float4(0.f, 0.f, 0.f, 0.f);
-        for (int pc = 0; pc < si.n_pieces; ++pc) {
-          const int64_t pi = hb + (int64_t)pc * P.H;
-          const float wgt = fast_exp2(__ldcg(P.ws_ml + pi * 2) - Ms);
-          Ls += __ldcg(P.ws_ml + pi * 2 + 1) * wgt;
-          const float4 o = __ldcg(reinterpret_cast<const float4*>(P.ws_o + pi * kD) + d4);
-          O.x += o.x * wgt; O.y += o.y * wgt; O.z += o.z * wgt; O.w += o.w * wgt;
+        for (int pc0 = 0; pc0 < si.n_pieces; pc0 += 4) {
+          float2 ml[4];
+          float4 o[4];
+#pragma unroll
+          for (int i = 0; i < 4; ++i) {
+            const bool ok = pc0 + i < si.n_pieces;
+            const int64_t pi = hb + (int64_t)(ok ? pc0 + i : pc0) * P.H;
+            ml[i] = __ldcg(reinterpret_cast<const float2*>(P.ws_ml + pi * 2));
+            o[i] = __ldcg(reinterpret_cast<const float4*>(P.ws_o + pi * kD) + d4);
+            if (!ok) { ml[i].x = -INFINITY; ml[i].y = 0.f; }
+          }
+          float Mn = M;
+#pragma unroll
+          for (int i = 0; i < 4; ++i) Mn = fmaxf(Mn, ml[i].x);
+          const float Ms = fmaxf(Mn, kNegBig);
+          const float resc = fast_exp2(M - Ms);
+          Ls *= resc; O.x *= resc; O.y *= resc; O.z *= resc; O.w *= resc;
+#pragma unroll
+          for (int i = 0; i < 4; ++i) {
+            const float wgt = fast_exp2(ml[i].x - Ms);
+            Ls += ml[i].y * wgt;
+            O.x += o[i].x * wgt; O.y += o[i].y * wgt; O.z += o[i].z * wgt; O.w += o[i].w * wgt;
+          }
+          M = Mn;
         }
         const float inv = Ls > 0.f ? 1.f / Ls : 0.f;
         TO* op = out + (int64_t)si.b * P.out_seq_stride + (int64_t)h * kD + d4 * 4;
@@ -618,7 +711,12 @@ int launch_swa(const Params& P0, int B_total, int n_ctas, const CUtensorMap& map
       P.ws_ml = P0.ws_ml + (int64_t)b0 * P0.max_pieces * P0.H * 2;
     }
     int64_t items = (int64_t)P.B * P0.max_pieces;
-    const int grid = (int)(items < n_ctas ? items : n_ctas);
+    int grid = (int)(items < n_ctas ? items : n_ctas);
+    // Balanced mode with a batch between one and two CTAs per SM: one CTA per sequence. Every
+    // CTA then has work in either of the kernel's two partitions (whole sequences or equal
+    // runs); idle CTAs would otherwise be left to the block scheduler's placement, and an SM
+    // whose two CTAs are both idle streams nothing.
+    if (P0.balanced && 2 * P.B >= n_ctas && P.B < n_ctas) grid = P.B;
     kern<<<grid, kThreads, C::kSmemBytes, st>>>(P, map_k, map_v, map_k2, map_v2);
     int rc = check_launch("sbk_swa_decode");
     if (rc != SBK_OK) return rc;
@@ -690,7 +788,10 @@ extern "C" int sbk_swa_decode(const void* q, int64_t q_seq_stride, const void* k
     set_error("sbk_swa_decode: cache block stride smaller than a block");
     return SBK_E_ARG;
   }
-  if (split_chunks <= 0) split_chunks = 32;
+  // balanced runs cross sequence boundaries, so a sequence may always end up in two pieces
+  const int balanced = split_chunks < 0 && max_pieces > 1;
+  if (split_chunks < 0) split_chunks = -split_chunks;
+  if (split_chunks == 0) split_chunks = 32;
   const size_t need = sbk_swa_workspace_bytes(B, H, D, max_pieces);
   if (!workspace || workspace_bytes < need) {
     set_error("sbk_swa_decode: workspace of %zu bytes given, %zu needed", workspace_bytes, need);
@@ -714,6 +815,7 @@ extern "C" int sbk_swa_decode(const void* q, int64_t q_seq_stride, const void* k
     P.ws_ml = P.ws_o + (size_t)B * max_pieces * H * D;
   }
   P.split_chunks = split_chunks; P.max_pieces = max_pieces; P.status = status;
+  P.balanced = balanced;
 
   static int sm_count[64] = {};
   int dev = 0;

@@ -7,6 +7,8 @@ to PyTorch ops: without a CUDA device and libsbk.so these functions raise.
 """
 from typing import Optional, Tuple
 
+import os
+
 import torch
 
 from . import _abi
@@ -204,21 +206,36 @@ def _check_meta(key2, value2, kvh: int, d: int) -> int:
 
 
 def swa_auto_split(B: int, max_visible_tokens: int, device) -> int:
-    """Chunks (of 16 tokens) per split such that a batch of B sequences yields about one work
-    item per resident CTA (two CTAs per SM): large batches are not split at all, small ones are
-    cut just fine enough to occupy the machine. Never below 4 chunks."""
+    """The default ``split_chunks`` of swa_decode: negative = balanced mode, in which the kernel
+    cuts the batch's chunks (of 16 tokens) into one equal run per CTA (two CTAs per SM) whatever
+    the spread of lengths; the magnitude is the shortest run it may cut (8 chunks = 128 tokens =
+    256 KiB of K and V at 4 kv heads, below which the per-item cost outweighs the balance).
+    The environment variable SBK_SWA_SPLIT_CHUNKS overrides it (tuning, A/B measurements)."""
+    env = os.environ.get("SBK_SWA_SPLIT_CHUNKS")
+    return int(env) if env else -8
+
+
+def _n_ctas(device) -> int:
     idx = torch.device(device).index or 0
     if idx not in _SM_COUNT:
         _SM_COUNT[idx] = torch.cuda.get_device_properties(idx).multi_processor_count
-    chunks = (max(int(max_visible_tokens), 1) + 15) // 16 + 1
-    pieces = max(1, round(2 * _SM_COUNT[idx] / max(B, 1)))
-    return max(4, -(-chunks // pieces))
+    return 2 * _SM_COUNT[idx]
 
 
-def swa_max_pieces(max_visible_tokens: int, split_chunks: int = DEFAULT_SPLIT_CHUNKS) -> int:
-    """Upper bound on the splits of one sequence whose window holds ``max_visible_tokens``."""
+def swa_max_pieces(max_visible_tokens: int, split_chunks: int = DEFAULT_SPLIT_CHUNKS, B: int = 0,
+                   device=None) -> int:
+    """Upper bound on the splits of one sequence whose window holds ``max_visible_tokens``; sizes
+    the workspace. Fixed pieces (split_chunks > 0): ceil(chunks / split_chunks). Balanced mode
+    (split_chunks < 0): the kernel keeps every sequence within the bound it is given, so the bound
+    only has to allow the balance: about CTAs / B runs per sequence, plus the two it may share
+    with its neighbours, and never more than the shortest run permits."""
     chunks = (max(int(max_visible_tokens), 1) + 15) // 16 + 1  # +1: a window rarely starts on a chunk edge
-    return max(1, -(-chunks // split_chunks))
+    if split_chunks > 0:
+        return max(1, -(-chunks // split_chunks))
+    n_ctas = _n_ctas(device) if device is not None else 296
+    by_balance = -(-n_ctas // max(B, 1)) + 2
+    by_run = -(-chunks // max(-split_chunks, 1)) + 1
+    return max(2, min(by_balance, by_run, 33))
 
 
 def swa_workspace(B: int, H: int, D: int, max_pieces: int, device) -> Optional[torch.Tensor]:
@@ -238,7 +255,9 @@ def swa_decode(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor,
                value2: Optional[torch.Tensor] = None,
                status: Optional[torch.Tensor] = None) -> torch.Tensor:
     """Single-query sliding-window attention over the paged cache; q [B, H, D] bf16.
-    ``split_chunks`` (16-token chunks per split of a sequence) defaults to swa_auto_split.
+    ``split_chunks`` > 0: fixed pieces of that many 16-token chunks, drawn by the CTAs from a ticket
+    counter; < 0: balanced mode (equal runs of chunks per CTA, runs no shorter than -split_chunks);
+    default swa_auto_split.
     ``key2`` / ``value2`` [n_meta, kvh, D]: sink tokens every query sees besides its window."""
     _need_cuda(q, k_cache, v_cache, block_tables, seq_lens, out, lse, workspace, status)
     nb, bs, kvh, d, bstride = _cache_geometry(k_cache, v_cache)
@@ -266,7 +285,7 @@ def swa_decode(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor,
     if split_chunks is None:
         split_chunks = swa_auto_split(B, vis, q.device) if B else DEFAULT_SPLIT_CHUNKS
     if max_pieces is None:
-        max_pieces = swa_max_pieces(vis, split_chunks)
+        max_pieces = swa_max_pieces(vis, split_chunks, B, q.device)
     if workspace is None:
         workspace = swa_workspace(B, H, d, max_pieces, q.device)
     if scale is None:

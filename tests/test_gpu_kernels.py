@@ -208,6 +208,34 @@ def test_swa_decode_split_settings(ops, split_chunks, max_pieces):
     _check_attn(out, ref, lse, lse_ref)
 
 
+@pytest.mark.parametrize("split_chunks,max_pieces", [(-1, 2), (-1, 300), (-4, 3), (-8, None), (-1000, 2), (-3, 1)])
+def test_swa_decode_balanced_runs(ops, split_chunks, max_pieces):
+    """Balanced mode: equal runs of chunks per CTA that cross sequence boundaries; the bound on
+    pieces per sequence is honoured whatever it is (max_pieces 1 falls back to whole sequences)."""
+    lens = [4100, 513, 40, 2000, 0, 1, 16, 8193, 333]
+    out, ref, lse, lse_ref = _run_attn(ops, lens, wl=4096, H=28, kvh=4, bs=16, seed=13,
+                                      split_chunks=split_chunks, max_pieces=max_pieces)
+    _check_attn(out, ref, lse, lse_ref)
+
+
+@pytest.mark.parametrize("H,kvh", [(7, 1), (14, 2), (28, 4)])
+def test_swa_decode_balanced_head_layouts_and_many_sequences(ops, H, kvh):
+    """More sequences than CTAs, lengths from 0 to a few windows, every kv-head layout (stages of
+    1, 2 and 4 sub-chunks): runs start and end in the middle of stages."""
+    g = torch.Generator().manual_seed(14)
+    lens = torch.randint(0, 700, (400,), generator=g).tolist()
+    out, ref, lse, lse_ref = _run_attn(ops, lens, wl=255, H=H, kvh=kvh, bs=16, seed=15, split_chunks=-2)
+    _check_attn(out, ref, lse, lse_ref)
+
+
+def test_swa_decode_balanced_uniform_batch_takes_whole_sequences(ops):
+    """Near-equal lengths filling half the CTAs or more: the kernel streams whole sequences
+    (no partials); same numbers either way."""
+    lens = [600 + (i % 5) for i in range(300)]
+    out, ref, lse, lse_ref = _run_attn(ops, lens, wl=511, H=28, kvh=4, bs=16, seed=16, split_chunks=-8)
+    _check_attn(out, ref, lse, lse_ref)
+
+
 def test_swa_decode_fp32_out_tight(ops):
     """With fp32 output the only bf16 rounding left is that of the probabilities."""
     lens = [4100, 900, 77]
@@ -259,7 +287,7 @@ def test_swa_decode_with_sink_tokens(ops, H, kvh, n_meta):
     st = _status()
     kv_d = kv.to(DEV)
     lse = torch.empty(len(lens), H, dtype=torch.float32, device=DEV)
-    for split in (None, 4):
+    for split in (None, 4, -1):
         out = ops.swa_decode(q.to(DEV), kv_d[0], kv_d[1], table.to(DEV), torch.tensor(lens, dtype=torch.int32, device=DEV),
                              window_left=wl, lse=lse, split_chunks=split, key2=k2.to(DEV), value2=v2.to(DEV), status=st)
         torch.cuda.synchronize()
