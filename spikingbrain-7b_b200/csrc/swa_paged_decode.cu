@@ -129,6 +129,72 @@ struct Params {
   int balanced;       // 1: equal runs of chunks per CTA; split_chunks is then the shortest run allowed
 };
 
+// Folds the partials (m, l, O) of a split sequence into its output row; called by the 128
+// consumer threads of the CTA that completed the sequence's last piece. Thread = a float4 of dims
+// of the heads warp, warp + 4, ...; the loads of four heads x four pieces are issued together, so
+// a fold of up to four pieces costs two trips to L2 per thread instead of one per head and piece
+// (this sits at the very end of the kernel in balanced mode, where every CTA ends at once).
+// Inlined on purpose: as a separate function the call alone cost tens of microseconds.
+template <typename TO>
+__device__ __forceinline__ void fold_pieces(const float* __restrict__ ws_o, const float* __restrict__ ws_ml,
+                                         float* lse_out, int H, int max_pieces, int64_t out_seq_stride,
+                                         int b, int n_pieces, TO* out) {
+  const int d4 = threadIdx.x & 31;
+  const int w = threadIdx.x >> 5;
+  for (int h0 = w; h0 < H; h0 += 4 * kConsumerWarps) {
+    float M[4], Ls[4];
+    float4 O[4];
+#pragma unroll
+    for (int j = 0; j < 4; ++j) { M[j] = -INFINITY; Ls[j] = 0.f; O[j] = make_float4(0.f, 0.f, 0.f, 0.f); }
+    for (int pc0 = 0; pc0 < n_pieces; pc0 += 4) {
+      float2 ml[4][4];
+      float4 o[4][4];
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const int h = h0 + j * kConsumerWarps < H ? h0 + j * kConsumerWarps : h0;
+        const int64_t hb = (int64_t)b * max_pieces * H + h;
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          const int64_t pi = hb + (int64_t)(pc0 + i < n_pieces ? pc0 + i : pc0) * H;
+          ml[j][i] = __ldcg(reinterpret_cast<const float2*>(ws_ml + pi * 2));
+          o[j][i] = __ldcg(reinterpret_cast<const float4*>(ws_o + pi * kD) + d4);
+        }
+      }
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        float Mn = M[j];
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          if (pc0 + i >= n_pieces) { ml[j][i].x = -INFINITY; ml[j][i].y = 0.f; }
+          Mn = fmaxf(Mn, ml[j][i].x);
+        }
+        const float Ms = fmaxf(Mn, kNegBig);
+        const float resc = fast_exp2(M[j] - Ms);
+        Ls[j] *= resc; O[j].x *= resc; O[j].y *= resc; O[j].z *= resc; O[j].w *= resc;
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          const float wgt = fast_exp2(ml[j][i].x - Ms);
+          Ls[j] += ml[j][i].y * wgt;
+          O[j].x += o[j][i].x * wgt; O[j].y += o[j][i].y * wgt;
+          O[j].z += o[j][i].z * wgt; O[j].w += o[j][i].w * wgt;
+        }
+        M[j] = Mn;
+      }
+    }
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const int h = h0 + j * kConsumerWarps;
+      if (h >= H) break;
+      const float inv = Ls[j] > 0.f ? 1.f / Ls[j] : 0.f;
+      TO* op = out + (int64_t)b * out_seq_stride + (int64_t)h * kD + d4 * 4;
+      store_out<TO>(op, O[j].x * inv); store_out<TO>(op + 1, O[j].y * inv);
+      store_out<TO>(op + 2, O[j].z * inv); store_out<TO>(op + 3, O[j].w * inv);
+      if (lse_out && d4 == 0)
+        lse_out[(int64_t)b * H + h] = Ls[j] > 0.f ? (M[j] + log2f(Ls[j])) * kLn2 : -INFINITY;
+    }
+  }
+}
+
 template <int KVH, typename TO>
 __global__ void __launch_bounds__(kThreads, 2)
 swa_decode_kernel(const Params P, const __grid_constant__ CUtensorMap map_k,
@@ -627,48 +693,7 @@ swa_decode_kernel(const Params P, const __grid_constant__ CUtensorMap map_k,
     consumer_bar();   // misc[1] may be rewritten by the next item only after everyone has read it
     if (!fold) continue;
     __threadfence();
-    {
-      // 128 threads, a float4 of dims each, heads strided by 4
-      const int d4 = threadIdx.x & 31;
-      for (int h = threadIdx.x >> 5; h < P.H; h += kConsumerWarps) {
-        const int64_t hb = (int64_t)si.b * P.max_pieces * P.H + h;
-        // one pass with a running maximum; four pieces' loads (8 requests) are in flight at a time,
-        // so the fold costs a few L2 round trips per head instead of one per piece
-        float M = -INFINITY, Ls = 0.f;
-        float4 O = make_float4(0.f, 0.f, 0.f, 0.f);
-        for (int pc0 = 0; pc0 < si.n_pieces; pc0 += 4) {
-          float2 ml[4];
-          float4 o[4];
-#pragma unroll
-          for (int i = 0; i < 4; ++i) {
-            const bool ok = pc0 + i < si.n_pieces;
-            const int64_t pi = hb + (int64_t)(ok ? pc0 + i : pc0) * P.H;
-            ml[i] = __ldcg(reinterpret_cast<const float2*>(P.ws_ml + pi * 2));
-            o[i] = __ldcg(reinterpret_cast<const float4*>(P.ws_o + pi * kD) + d4);
-            if (!ok) { ml[i].x = -INFINITY; ml[i].y = 0.f; }
-          }
-          float Mn = M;
-#pragma unroll
-          for (int i = 0; i < 4; ++i) Mn = fmaxf(Mn, ml[i].x);
-          const float Ms = fmaxf(Mn, kNegBig);
-          const float resc = fast_exp2(M - Ms);
-          Ls *= resc; O.x *= resc; O.y *= resc; O.z *= resc; O.w *= resc;
-#pragma unroll
-          for (int i = 0; i < 4; ++i) {
-            const float wgt = fast_exp2(ml[i].x - Ms);
-            Ls += ml[i].y * wgt;
-            O.x += o[i].x * wgt; O.y += o[i].y * wgt; O.z += o[i].z * wgt; O.w += o[i].w * wgt;
-          }
-          M = Mn;
-        }
-        const float inv = Ls > 0.f ? 1.f / Ls : 0.f;
-        TO* op = out + (int64_t)si.b * P.out_seq_stride + (int64_t)h * kD + d4 * 4;
-        store_out<TO>(op, O.x * inv); store_out<TO>(op + 1, O.y * inv);
-        store_out<TO>(op + 2, O.z * inv); store_out<TO>(op + 3, O.w * inv);
-        if (P.lse_out && d4 == 0)
-          P.lse_out[(int64_t)si.b * P.H + h] = Ls > 0.f ? (M + log2f(Ls)) * kLn2 : -INFINITY;
-      }
-    }
+    fold_pieces<TO>(P.ws_o, P.ws_ml, P.lse_out, P.H, P.max_pieces, P.out_seq_stride, si.b, si.n_pieces, out);
   }
   // A wait that ran out may have left copies in flight: give them time to land before the
   // CTA retires (bounded; the result is already flagged invalid).
