@@ -11,7 +11,11 @@
 // rows, O += P V with P as bf16 head + bf16 remainder (32 mma.sync), fp32 accumulation.
 // The new tokens' K/V must already be in the cache (the append runs first).
 #include "sbk_common.cuh"
+#include <stdlib.h>
+#include <string.h>
+
 #include "sbk_tma.cuh"
+#include "swa_prefill_tc.cuh"
 
 namespace sbk {
 namespace prefill {
@@ -334,6 +338,42 @@ extern "C" int sbk_swa_prefill(const void* q, int64_t q_tok_stride, const void* 
   if ((int64_t)n_seqs * tiles > 2147483647LL || kvh > 65535) {
     set_error("sbk_swa_prefill: grid too large");
     return SBK_E_ARG;
+  }
+  // Two kernels serve this entry point: tcgen05 (tensor memory, 128-key tiles) and mma.sync.
+  // SBK_PREFILL_KERNEL = "tc" | "mma" picks one; the tcgen05 kernel moves q and out as 16-byte vectors.
+  const char* pick = getenv("SBK_PREFILL_KERNEL");
+  const bool vec_ok = aligned16(q) && aligned16(out) && q_tok_stride % 8 == 0 && out_tok_stride % 8 == 0;
+  const bool use_tc = vec_ok && pick != nullptr && strcmp(pick, "tc") == 0;
+  if (use_tc) {
+    CUtensorMap mk, mv, mk2, mv2;
+    int tc_mode = 0;
+    if (!get_map(&mk, MapKey{k_cache, kvh, num_blocks, block_size, cache_block_stride_bytes, 1}, &tc_mode) ||
+        !get_map(&mv, MapKey{v_cache, kvh, num_blocks, block_size, cache_block_stride_bytes, 1}, &tc_mode)) {
+      set_error("sbk_swa_prefill: cuTensorMapEncodeTiled rejected the cache geometry");
+      return SBK_E_ARG;
+    }
+    mk2 = mk; mv2 = mv;
+    prefill_tc::Params T;
+    T.q = (const __nv_bfloat16*)q; T.q_tok_stride = q_tok_stride;
+    T.block_tables = block_tables; T.max_blocks = max_blocks;
+    T.query_start_loc = query_start_loc; T.context_lens = context_lens;
+    T.n_seqs = n_seqs; T.tiles_per_seq = tiles; T.H = H; T.G = H / kvh; T.num_blocks = num_blocks;
+    T.block_size = block_size; T.window_left = window_left; T.scale_log2 = scale * kLog2e;
+    T.out = (__nv_bfloat16*)out; T.out_tok_stride = out_tok_stride; T.status = status;
+    T.n_meta_chunks = 0;
+    T.dbg = nullptr;
+    if (const char* d = getenv("SBK_PREFILL_DEBUG_PTR")) T.dbg = (float*)strtoull(d, nullptr, 0);
+    if (num_meta > 0) {
+      const int64_t mstride = (int64_t)16 * kvh * D * 2;
+      if (!get_map(&mk2, MapKey{key2, kvh, num_meta / 16, 16, mstride, 1}, &tc_mode) ||
+          !get_map(&mv2, MapKey{value2, kvh, num_meta / 16, 16, mstride, 1}, &tc_mode)) {
+        set_error("sbk_swa_prefill: cuTensorMapEncodeTiled rejected the sink-token tensors");
+        return SBK_E_ARG;
+      }
+      T.n_meta_chunks = num_meta / 16;
+    }
+    T.tile_copy = tc_mode;
+    return prefill_tc::launch(T, kvh, mk, mv, mk2, mv2, (cudaStream_t)stream);
   }
   CUtensorMap map_k, map_v;
   int tile_copy = 0;

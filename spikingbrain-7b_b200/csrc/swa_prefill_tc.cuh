@@ -1,0 +1,27 @@
+// Interface between the prefill entry point and its tcgen05 kernel.
+#pragma once
+
+#include "sbk_common.cuh"
+#include "sbk_tma.cuh"
+
+namespace sbk {
+namespace prefill_tc {
+
+struct Params {
+  const __nv_bfloat16* q; int64_t q_tok_stride;
+  const int32_t* block_tables; int max_blocks;
+  const int32_t* query_start_loc; const int32_t* context_lens;
+  int n_seqs; int tiles_per_seq; int H; int G; int64_t num_blocks; int block_size;
+  int window_left; float scale_log2;
+  __nv_bfloat16* out; int64_t out_tok_stride;
+  int32_t* status; int tile_copy;
+  int n_meta_chunks;   // 16-token chunks of always-visible sink keys, streamed ahead of the window
+  float* dbg;          // development aid: S, O_t of the first tile of CTA (0,0) are copied here when set
+};
+
+// Tensor maps with ONE 128-byte row (64 dims of one kv head) per copy: box_rows == 1.
+int launch(const Params& P, int kvh, const CUtensorMap& map_k, const CUtensorMap& map_v,
+           const CUtensorMap& map_k2, const CUtensorMap& map_v2, cudaStream_t stream);
+
+}  // namespace prefill_tc
+}  // namespace sbk
