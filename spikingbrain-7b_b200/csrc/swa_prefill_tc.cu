@@ -7,15 +7,23 @@
 // (row = head slot * 16 + query; head slots past the group size are zero rows), so one K/V tile in
 // shared memory serves all of them. Keys are taken 128 at a time:
 //     S[128 rows, 128 keys]  = Q . K^T      8 x tcgen05.mma (M128 N128 K16), accumulator in TMEM
-//     softmax on S: 128 threads, one row each, straight from TMEM (no shuffles), P -> bf16 -> smem
-//     O_t[128 rows, 128 dims] = P . V       16 x tcgen05.mma (P as bf16 head + bf16 remainder), fresh accumulator in TMEM
+//     softmax on S straight from TMEM; P -> bf16 head + bf16 remainder -> shared memory
+//     O_t[128 rows, 128 dims] = P . V       16 x tcgen05.mma, fresh accumulator in TMEM
 //     O += O_t (registers; rescaled by exp2(m_old - m_new) beforehand)
-// Roles: warps 0-3 softmax / accumulate / epilogue (thread = row), warp 4 TMA producer (walks the
-// block table; a 128-key tile of K or V is 16 copies of 2 KiB, one per 16-token block piece and
-// 64-dim half, landing as two [128 keys][128 B] panels with the 128-byte swizzle -- the canonical
-// K-major layout for K in S = Q.K^T and at once the canonical MN-major layout for V in O = P.V),
-// warp 5 allocates TMEM and issues the MMAs (one thread). Hand-offs are mbarriers; the tensor
-// core signals them through tcgen05.commit. Every wait is bounded.
+// Roles (320 threads):
+//   warps 0-7  softmax / accumulate / epilogue. A TMEM lane (= row) can only be read by warps with
+//              the same index mod 4, so warps w and w + 4 share the rows 32 (w mod 4) ... + 31: the
+//              first takes keys 0-63 of a tile and dims 0-63 of the output, the second the other
+//              halves; they exchange their partial row maxima through shared memory once a tile.
+//   warp 8     TMA producer: walks the block table; a 128-key tile of K or V is 16 copies of 2 KiB
+//              (one per 16-token block piece and 64-dim half), landing as two [128 keys][128 B]
+//              panels with the 128-byte swizzle -- the canonical K-major layout for K in S = Q.K^T
+//              and at once the canonical MN-major layout for V in O = P.V. K and V have rings of
+//              their own (two slots each): a K slot is free as soon as its S is computed.
+//   warp 9     allocates TMEM and issues the MMAs (one thread). S is double-buffered in TMEM, so
+//              Q.K^T of tile t+1 runs while the softmax threads work on tile t, and P.V of tile t
+//              runs while they compute the exponentials of tile t+1.
+// Hand-offs are mbarriers; the tensor core signals them through tcgen05.commit. Every wait is bounded.
 // The query at position p sees keys [p - window_left, p]; only tiles at the two ends of that range
 // are masked. Sink (meta) keys, if any, come first as always-visible tiles.
 #include "sbk_common.cuh"
@@ -32,16 +40,19 @@ constexpr int kTileKeys = 128;                // keys per MMA tile
 constexpr int kTileChunks = kTileKeys / kChunk;
 constexpr int kPanelBytes = 128 * 128;        // [128 rows][128 B]: 64 bf16 of every row
 constexpr int kOperandBytes = 2 * kPanelBytes;   // a [128 x 128] bf16 operand: two panels
-constexpr int kStages = 2;
+constexpr int kStages = 2;                    // slots of the K ring and of the V ring
 constexpr int kQOff = 0;
 constexpr int kPOff = kOperandBytes;             // P rounded to bf16
 constexpr int kPLoOff = 2 * kOperandBytes;        // what the rounding dropped, again as bf16
-constexpr int kStageOff = 3 * kOperandBytes;
-constexpr int kStageBytes = 2 * kOperandBytes;   // K tile, then V tile
-constexpr int kBarOff = kStageOff + kStages * kStageBytes;   // 229376
-constexpr int kSmemBytes = kBarOff + 128 + 1024;             // barriers, TMEM slot, flags; + alignment slack
-constexpr int kThreads = 192;
-constexpr int kTmemCols = 256;                // S: columns [0,128), O_t: [128,256)
+constexpr int kKOff = 3 * kOperandBytes;                     // K ring
+constexpr int kVOff = kKOff + kStages * kOperandBytes;       // V ring
+constexpr int kBarOff = kVOff + kStages * kOperandBytes;     // 229376
+constexpr int kXchOff = kBarOff + 128;                       // 2 x 128 floats: partial row maxima / sums
+constexpr int kSmemBytes = kXchOff + 1024 + 64 + 1024;       // + TMEM slot and flags; + alignment slack
+constexpr int kSoftmaxThreads = 256;
+constexpr int kThreads = kSoftmaxThreads + 64;
+constexpr int kTmemCols = 512;                // S0: columns [0,128), S1: [128,256), O_t: [256,384)
+constexpr int kOCol = 256;
 constexpr float kNegBig = -1.0e30f;
 
 // ---- tcgen05 wrappers ---------------------------------------------------------------------
@@ -74,9 +85,9 @@ __device__ __forceinline__ void umma_bf16(uint32_t d_tmem, uint64_t a_desc, uint
 __device__ __forceinline__ void umma_commit(uint32_t bar) {
   asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
 }
-// 32 consecutive fp32 columns of this thread's TMEM lane (warp w reads lanes 32w..32w+31)
-__device__ __forceinline__ void tmem_ld32(uint32_t taddr, float (&v)[32]) {
-  uint32_t r[32];
+// 32 consecutive fp32 columns of this thread's TMEM lane (warp w reads lanes 32 (w mod 4) ... + 31).
+// The load is asynchronous: the registers may be used only after tmem_ld_fence().
+__device__ __forceinline__ void tmem_ld32_issue(uint32_t taddr, uint32_t (&r)[32]) {
   asm volatile(
       "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
       "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
@@ -87,9 +98,15 @@ __device__ __forceinline__ void tmem_ld32(uint32_t taddr, float (&v)[32]) {
         "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
       : "r"(taddr)
       : "memory");
+}
+// Waits for the loads issued so far and ties the registers to the wait, so that the compiler
+// cannot schedule a use of them ahead of it (the empty statements cost nothing at run time).
+__device__ __forceinline__ void tmem_ld_fence(uint32_t (&r)[32]) {
   tc_wait_ld();
 #pragma unroll
-  for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]);
+  for (int i = 0; i < 32; i += 8)
+    asm volatile("" : "+r"(r[i]), "+r"(r[i + 1]), "+r"(r[i + 2]), "+r"(r[i + 3]), "+r"(r[i + 4]), "+r"(r[i + 5]),
+                      "+r"(r[i + 6]), "+r"(r[i + 7]));
 }
 
 // Shared-memory matrix descriptor of a 128-byte-swizzled operand whose 8-row groups are 1 KiB
@@ -113,6 +130,10 @@ __host__ __device__ constexpr uint32_t instr_desc(int b_mn) {
 // byte offset of the 16-byte chunk `c` (0..7) of row `r` inside a [128 rows][128 B] swizzled panel
 __device__ __forceinline__ uint32_t swz(int r, int c) { return (uint32_t)(r * 128 + ((c ^ (r & 7)) << 4)); }
 
+__device__ __forceinline__ void softmax_bar() {
+  asm volatile("bar.sync 1, %0;" ::"n"(kSoftmaxThreads) : "memory");
+}
+
 __global__ void __launch_bounds__(kThreads, 1)
 swa_prefill_tc_kernel(const Params P, const __grid_constant__ CUtensorMap map_k,
                       const __grid_constant__ CUtensorMap map_v, const __grid_constant__ CUtensorMap map_k2,
@@ -120,10 +141,13 @@ swa_prefill_tc_kernel(const Params P, const __grid_constant__ CUtensorMap map_k,
   extern __shared__ uint8_t smem_raw[];
   uint8_t* const smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
   const uint32_t sbase = smem_u32(smem);
-  const uint32_t bar_full = sbase + kBarOff, bar_empty = bar_full + 8 * kStages;
-  const uint32_t bar_s = bar_empty + 8 * kStages, bar_p = bar_s + 8, bar_done = bar_p + 8;
-  volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(smem + kBarOff + 64);
-  volatile int* flags = reinterpret_cast<volatile int*>(smem + kBarOff + 80);   // [0..1] stage bad, [2] abort
+  // barriers: K ring full/empty, V ring full/empty, S0/S1 ready, P ready, O_t ready
+  const uint32_t bar_kf = sbase + kBarOff, bar_ke = bar_kf + 8 * kStages;
+  const uint32_t bar_vf = bar_ke + 8 * kStages, bar_ve = bar_vf + 8 * kStages;
+  const uint32_t bar_s = bar_ve + 8 * kStages, bar_p = bar_s + 16, bar_o = bar_p + 8;
+  float* xch = reinterpret_cast<float*>(smem + kXchOff);                       // [2][128]
+  volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(smem + kXchOff + 1024);
+  volatile int* flags = reinterpret_cast<volatile int*>(smem + kXchOff + 1024 + 16);   // [0..3] tile t & 3 bad, [4] abort
 
   const int s = blockIdx.x / P.tiles_per_seq;
   const int j = blockIdx.x - s * P.tiles_per_seq;
@@ -144,22 +168,22 @@ swa_prefill_tc_kernel(const Params P, const __grid_constant__ CUtensorMap map_k,
 
   if (threadIdx.x == 0) {
     for (int i = 0; i < kStages; ++i) {
-      mbar_init(bar_full + 8 * i, 1);
-      mbar_init(bar_empty + 8 * i, 1);
+      mbar_init(bar_kf + 8 * i, 1);
+      mbar_init(bar_ke + 8 * i, 1);
+      mbar_init(bar_vf + 8 * i, 1);
+      mbar_init(bar_ve + 8 * i, 1);
+      mbar_init(bar_s + 8 * i, 1);
     }
-    mbar_init(bar_s, 1);
-    mbar_init(bar_p, 128);
-    mbar_init(bar_done, 1);
-    flags[0] = flags[1] = flags[2] = 0;
+    mbar_init(bar_p, kSoftmaxThreads);
+    mbar_init(bar_o, 1);
+    for (int i = 0; i < 5; ++i) flags[i] = 0;
     fence_mbar_init();
   }
   // V panels start finite: a tile may be filled only in part (its other keys are masked, and a
   // zero probability must not meet a NaN), and what a slot holds later is older, finite data
-  for (int i = threadIdx.x; i < kStages * kOperandBytes / 16; i += kThreads) {
-    const int st = i / (kOperandBytes / 16), o = i - st * (kOperandBytes / 16);
-    *reinterpret_cast<uint4*>(smem + kStageOff + st * kStageBytes + kOperandBytes + o * 16) = make_uint4(0, 0, 0, 0);
-  }
-  if (warp == 5) {
+  for (int i = threadIdx.x; i < kStages * kOperandBytes / 16; i += kThreads)
+    *reinterpret_cast<uint4*>(smem + kVOff + i * 16) = make_uint4(0, 0, 0, 0);
+  if (warp == 9) {
     tmem_alloc(smem_u32(const_cast<uint32_t*>(tmem_slot)), kTmemCols);
     tmem_relinquish();
   }
@@ -169,12 +193,13 @@ swa_prefill_tc_kernel(const Params P, const __grid_constant__ CUtensorMap map_k,
   tc_fence_after();
   const uint32_t tmem = *tmem_slot;
 
-  if (warp == 4) {
+  if (warp == 8) {
     // ================================= TMA producer =================================
     const int32_t* table = P.block_tables + (int64_t)s * P.max_blocks;
     int64_t pb_lane = -1;
     int batch_c0 = 0;
-    for (int t = 0; t < n_tiles; ++t) {
+    bool ok = true;
+    for (int t = 0; ok && t < n_tiles; ++t) {
       const bool meta = t < n_mt;
       const int c0 = meta ? t * kTileChunks : c_lo + (t - n_mt) * kTileChunks;
       const int c_end = meta ? P.n_meta_chunks - 1 : c_hi;     // last chunk of this kind
@@ -185,11 +210,6 @@ swa_prefill_tc_kernel(const Params P, const __grid_constant__ CUtensorMap map_k,
         pb_lane = (c <= c_hi && lb < P.max_blocks) ? (int64_t)table[lb] : -1;
       }
       const int slot = t % kStages, use = t / kStages;
-      if (use > 0 && !mbar_wait_bounded(bar_empty + 8 * slot, (use - 1) & 1)) {
-        if (lane == 0) { raise_status(P.status, SBK_ST_WAIT_TIMEOUT); flags[2] = 1; }
-        break;
-      }
-      if (flags[2]) break;
       // lane -> one copy of 2 KiB: chunk (lane >> 2), 64-dim half ((lane >> 1) & 1), K or V (lane & 1)
       const int i = lane >> 2, half = (lane >> 1) & 1, is_v = lane & 1;
       const int c = c0 + i;
@@ -201,214 +221,224 @@ swa_prefill_tc_kernel(const Params P, const __grid_constant__ CUtensorMap map_k,
       bool bad = !meta && active && (pb < 0 || pb >= P.num_blocks);
       bad = __any_sync(0xffffffffu, bad);
       const int nvalid = c_end - c0 + 1 < kTileChunks ? c_end - c0 + 1 : kTileChunks;
-      if (lane == 0) {
-        flags[slot] = bad ? 1 : 0;
-        if (bad) raise_status(P.status, SBK_ST_BAD_BLOCK);
-        mbar_arrive_expect_tx(bar_full + 8 * slot, bad ? 0u : (uint32_t)nvalid * 4u * 2048u);
-      }
-      __syncwarp();
-      if (!bad && active) {
-        const uint32_t dst = sbase + kStageOff + slot * kStageBytes + is_v * kOperandBytes + half * kPanelBytes + i * 2048;
-        const int tin = meta ? 0 : (c * kChunk) % P.block_size;
-        const CUtensorMap* map = meta ? (is_v ? &map_v2 : &map_k2) : (is_v ? &map_v : &map_k);
-        if (P.tile_copy) tma_load_4d(dst, map, 0, tin, hk * 2 + half, (int)pb, bar_full + 8 * slot);
-        else tma_load_4d(dst, map, 0, hk * 2 + half, tin, (int)pb, bar_full + 8 * slot);
+      const int tin = meta ? 0 : (c * kChunk) % P.block_size;
+      const uint32_t dst = sbase + (is_v ? kVOff : kKOff) + slot * kOperandBytes + half * kPanelBytes + i * 2048;
+      const CUtensorMap* map = meta ? (is_v ? &map_v2 : &map_k2) : (is_v ? &map_v : &map_k);
+      for (int kind = 0; kind < 2 && ok; ++kind) {   // K first: the first GEMM of the tile needs only K
+        const uint32_t bar_e = (kind ? bar_ve : bar_ke) + 8 * slot, bar_f = (kind ? bar_vf : bar_kf) + 8 * slot;
+        if (use > 0 && !mbar_wait_bounded(bar_e, (use - 1) & 1)) ok = false;
+        if (flags[4]) ok = false;
+        if (!ok) break;
+        if (lane == 0) {
+          if (kind == 0) {
+            flags[t & 3] = bad ? 1 : 0;
+            if (bad) raise_status(P.status, SBK_ST_BAD_BLOCK);
+          }
+          mbar_arrive_expect_tx(bar_f, bad ? 0u : (uint32_t)nvalid * 2u * 2048u);
+        }
+        __syncwarp();
+        if (!bad && active && is_v == kind) {
+          if (P.tile_copy) tma_load_4d(dst, map, 0, tin, hk * 2 + half, (int)pb, bar_f);
+          else tma_load_4d(dst, map, 0, hk * 2 + half, tin, (int)pb, bar_f);
+        }
       }
     }
-  } else if (warp == 5) {
+    if (!ok && lane == 0 && !flags[4]) { raise_status(P.status, SBK_ST_WAIT_TIMEOUT); flags[4] = 1; }
+  } else if (warp == 9) {
     // ================================= MMA issuer =================================
     const uint32_t idesc_qk = instr_desc(0), idesc_pv = instr_desc(1);
     const uint32_t q_addr = sbase + kQOff, p_addr = sbase + kPOff, plo_addr = sbase + kPLoOff;
-    // Q is written by the softmax threads; their first arrival on bar_p (phase 0) announces it
-    bool ok = mbar_wait_bounded(bar_p, 0);
-    for (int t = 0; ok && t < n_tiles; ++t) {
+    // S(t) = Q . K(t)^T into S buffer t & 1; frees the K slot
+    auto issue_qk = [&](int t) -> bool {
       const int slot = t % kStages;
-      const uint32_t k_addr = sbase + kStageOff + slot * kStageBytes, v_addr = k_addr + kOperandBytes;
-      ok = mbar_wait_bounded(bar_full + 8 * slot, (t / kStages) & 1);
-      if (!ok || flags[2]) break;
+      if (!mbar_wait_bounded(bar_kf + 8 * slot, (t / kStages) & 1) || flags[4]) return false;
       tc_fence_after();
       if (lane == 0) {
-        // S = Q . K^T : 8 steps of 16 dims; steps 0-3 in the first 64-dim panel, 4-7 in the second
+        const uint32_t k_addr = sbase + kKOff + slot * kOperandBytes;
 #pragma unroll
-        for (int k = 0; k < 8; ++k) {
+        for (int k = 0; k < 8; ++k) {   // 8 steps of 16 dims: 0-3 in the first 64-dim panel, 4-7 in the second
           const uint32_t off = (k >> 2) * kPanelBytes + (k & 3) * 32;
-          umma_bf16(tmem, smem_desc(q_addr + off, 16), smem_desc(k_addr + off, 16), idesc_qk, k > 0);
+          umma_bf16(tmem + (t & 1) * 128, smem_desc(q_addr + off, 16), smem_desc(k_addr + off, 16), idesc_qk, k > 0);
         }
-        umma_commit(bar_s);
+        umma_commit(bar_s + 8 * (t & 1));
+        umma_commit(bar_ke + 8 * slot);
       }
       __syncwarp();
-      // P of this tile (and with it: S read, O_t of the previous tile read)
-      ok = mbar_wait_bounded(bar_p, (t + 1) & 1);
-      if (!ok || flags[2]) break;
+      return true;
+    };
+    // Q is written by the softmax threads; their first arrival on bar_p (phase 0) announces it
+    bool ok = mbar_wait_bounded(bar_p, 0);
+    tc_fence_after();
+    ok = ok && issue_qk(0);
+    for (int t = 0; ok && t < n_tiles; ++t) {
+      // the next tile's scores are computed while the softmax threads work on this one
+      if (t + 1 < n_tiles) ok = issue_qk(t + 1);
+      if (!ok) break;
+      // P of this tile (and with it: S(t) read, O_t of the previous tile read)
+      const int slot = t % kStages;
+      ok = mbar_wait_bounded(bar_p, (t + 1) & 1) && mbar_wait_bounded(bar_vf + 8 * slot, (t / kStages) & 1);
+      if (!ok || flags[4]) break;
       tc_fence_after();
       if (lane == 0) {
-        // O_t = P . V : 8 steps of 16 keys; P panels hold keys 0-63 / 64-127, V advances 16 key rows a step
+        const uint32_t v_addr = sbase + kVOff + slot * kOperandBytes;
 #pragma unroll
-        for (int k = 0; k < 8; ++k) {
+        for (int k = 0; k < 8; ++k) {   // 8 steps of 16 keys; P panels hold keys 0-63 / 64-127
           const uint32_t a_off = (k >> 2) * kPanelBytes + (k & 3) * 32;
           const uint64_t vd = smem_desc(v_addr + k * 2048, kPanelBytes);
-          umma_bf16(tmem + 128, smem_desc(p_addr + a_off, 16), vd, idesc_pv, k > 0);
-          umma_bf16(tmem + 128, smem_desc(plo_addr + a_off, 16), vd, idesc_pv, 1);
+          umma_bf16(tmem + kOCol, smem_desc(p_addr + a_off, 16), vd, idesc_pv, k > 0);
+          umma_bf16(tmem + kOCol, smem_desc(plo_addr + a_off, 16), vd, idesc_pv, 1);
         }
-        umma_commit(bar_empty + 8 * slot);          // K and V of this slot are consumed
-        if (t == n_tiles - 1) umma_commit(bar_done);
+        umma_commit(bar_ve + 8 * slot);
+        umma_commit(bar_o);
       }
       __syncwarp();
     }
-    if (!ok && lane == 0) { raise_status(P.status, SBK_ST_WAIT_TIMEOUT); flags[2] = 1; }
+    if (!ok && lane == 0 && !flags[4]) { raise_status(P.status, SBK_ST_WAIT_TIMEOUT); flags[4] = 1; }
   } else {
-    // ====================== softmax / accumulate / epilogue: thread = row ======================
-    const int r = threadIdx.x;             // row of the MMA tile = TMEM lane
+    // ====================== softmax / accumulate / epilogue ======================
+    const int r = (warp & 3) * 32 + lane;  // row of the MMA tile = TMEM lane
+    const int half = warp >> 2;            // which 64 keys of a tile / which 64 dims of the output
     const int slot_h = r >> 4, ql = r & 15;
     const bool row_ok = slot_h < G && ql < nq_tile;
     const int p_row = p0 + ql;             // position of this row's query
     const int lo_row = P.window_left < 0 ? 0 : (p_row - P.window_left > 0 ? p_row - P.window_left : 0);
-    // ---- Q rows into the swizzled K-major panels ----
+    // ---- Q rows into the swizzled K-major panels (this thread: its 64-dim half) ----
     {
       const uint4* qp = reinterpret_cast<const uint4*>(
-          P.q + (int64_t)(qs + j * kBQ + ql) * P.q_tok_stride + (int64_t)(hk * G + slot_h) * kD);
+          P.q + (int64_t)(qs + j * kBQ + ql) * P.q_tok_stride + (int64_t)(hk * G + slot_h) * kD + half * 64);
 #pragma unroll
-      for (int c = 0; c < 16; ++c) {
+      for (int c = 0; c < 8; ++c) {
         const uint4 v = row_ok ? qp[c] : make_uint4(0, 0, 0, 0);
-        *reinterpret_cast<uint4*>(smem + kQOff + (c >> 3) * kPanelBytes + swz(r, c & 7)) = v;
+        *reinterpret_cast<uint4*>(smem + kQOff + half * kPanelBytes + swz(r, c)) = v;
       }
       fence_proxy_async_smem();
       mbar_arrive(bar_p);                  // phase 0 of bar_p: Q is in place
     }
-    float acc[kD];
+    float acc[64];
 #pragma unroll
-    for (int d = 0; d < kD; ++d) acc[d] = 0.f;
+    for (int d = 0; d < 64; ++d) acc[d] = 0.f;
     float m_run = -INFINITY, l_run = 0.f;
-    const uint32_t t_row = tmem + ((uint32_t)(warp * 32) << 16);
+    const uint32_t t_lane = tmem + ((uint32_t)((warp & 3) * 32) << 16);
     bool ok = true;
     for (int t = 0; t < n_tiles; ++t) {
-      ok = mbar_wait_bounded(bar_s, t & 1);
-      if (!ok || flags[2]) break;
+      ok = mbar_wait_bounded(bar_s + 8 * (t & 1), (t >> 1) & 1);
+      if (!ok || flags[4]) break;
       tc_fence_after();
-      // O_t of the previous tile is complete as well (the tensor core works in issue order)
-      if (t > 0) {
-#pragma unroll
-        for (int cb = 0; cb < 4; ++cb) {
-          float o[32];
-          tmem_ld32(t_row + 128 + cb * 32, o);
-#pragma unroll
-          for (int i = 0; i < 32; ++i) acc[cb * 32 + i] += o[i];
-          if (P.dbg && t == 1 && blockIdx.x == 0 && blockIdx.y == 0)
-            for (int i = 0; i < 32; ++i) P.dbg[16384 + r * 128 + cb * 32 + i] = o[i];
-        }
-      }
+      // ---- my 64 scores of this row ----
+      uint32_t sr[2][32];
+      tmem_ld32_issue(t_lane + (t & 1) * 128 + half * 64, sr[0]);
+      tmem_ld32_issue(t_lane + (t & 1) * 128 + half * 64 + 32, sr[1]);
       const bool meta = t < n_mt;
       const int tb = meta ? t * kTileKeys : (c_lo + (t - n_mt) * kTileChunks) * kChunk;   // first key of the tile
-      // columns this row may see: [v_lo, v_hi)
+      // columns (of my half) this row may see: [v_lo, v_hi)
       int v_lo, v_hi;
       if (meta) { v_lo = 0; v_hi = P.n_meta_chunks * kChunk - tb; }
       else { v_lo = lo_row - tb; v_hi = p_row + 1 - tb; }
+      v_lo -= half * 64; v_hi -= half * 64;
       v_lo = v_lo < 0 ? 0 : v_lo;
-      v_hi = v_hi > kTileKeys ? kTileKeys : v_hi;
-      const bool bad = flags[t % kStages] != 0;
-      if (bad) v_hi = 0;
+      v_hi = v_hi > 64 ? 64 : v_hi;
+      if (flags[t & 3]) v_hi = 0;
+      const bool full = v_lo == 0 && v_hi == 64;
+      tmem_ld_fence(sr[0]);
+      tmem_ld_fence(sr[1]);
+      float mx[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
+#pragma unroll
+      for (int i = 0; i < 64; ++i) {
+        const float v = __uint_as_float(sr[i >> 5][i & 31]);
+        if (full || (i >= v_lo && i < v_hi)) mx[i & 3] = fmaxf(mx[i & 3], v);
+      }
+      // The two halves of a row must agree on the offset m exactly, but m only has to be an upper
+      // bound of the row's scores, not the maximum itself: the partial maxima are exchanged rounded
+      // UP to bf16 (both sides use the rounded values), in a buffer per tile parity.
+      __nv_bfloat16* xm = reinterpret_cast<__nv_bfloat16*>(xch) + (t & 1) * 256;
+      const __nv_bfloat16 mine_b = __float2bfloat16_ru(fmaxf(fmaxf(mx[0], mx[1]), fmaxf(mx[2], mx[3])));
+      xm[half * 128 + r] = mine_b;
+      softmax_bar();
+      const float both = fmaxf(__bfloat162float(mine_b), __bfloat162float(xm[(half ^ 1) * 128 + r]));
+      const float m_new = fmaxf(m_run, both * P.scale_log2);
+      const float m_s = fmaxf(m_new, kNegBig);
+      const float alpha = fast_exp2(m_run - m_s);
+      m_run = m_new;
+      // ---- probabilities, in place of the scores ----
+      float ls[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+      for (int i = 0; i < 64; ++i) {
+        float pv = fast_exp2(__uint_as_float(sr[i >> 5][i & 31]) * P.scale_log2 - m_s);
+        if (!full && (i < v_lo || i >= v_hi)) pv = 0.f;
+        sr[i >> 5][i & 31] = __float_as_uint(pv);
+        ls[i & 3] += pv;
+      }
+      l_run = l_run * alpha + (ls[0] + ls[1]) + (ls[2] + ls[3]);
+      // ---- O_t of the previous tile: in once its GEMM is done; then everything is rescaled ----
+      if (t > 0) {
+        ok = mbar_wait_bounded(bar_o, (t - 1) & 1);
+        if (!ok || flags[4]) break;
+        tc_fence_after();
+        uint32_t orr[2][32];
+        tmem_ld32_issue(t_lane + kOCol + half * 64, orr[0]);
+        tmem_ld32_issue(t_lane + kOCol + half * 64 + 32, orr[1]);
+        tmem_ld_fence(orr[0]);
+        tmem_ld_fence(orr[1]);
+#pragma unroll
+        for (int i = 0; i < 64; ++i) acc[i] = (acc[i] + __uint_as_float(orr[i >> 5][i & 31])) * alpha;
+      }
       // The cache block that holds the newest key also holds slots nobody has written yet; their V
       // bits may be anything, and a zero probability times a NaN is a NaN. Clear those rows of the
       // tile (at most 15, in the chunk of the last key) before the second GEMM reads them.
       if (!meta && tb + kTileKeys > key_hi) {
+        if (!mbar_wait_bounded(bar_vf + 8 * (t % kStages), (t / kStages) & 1)) { ok = false; break; }
         const int row0 = key_hi - tb;
         const int row1 = ((key_hi + kChunk - 1) / kChunk) * kChunk - tb;
-        uint8_t* vbase = smem + kStageOff + (t % kStages) * kStageBytes + kOperandBytes;
-        for (int i = r; i < (row1 - row0) * 16; i += 128) {
+        uint8_t* vbase = smem + kVOff + (t % kStages) * kOperandBytes;
+        for (int i = threadIdx.x; i < (row1 - row0) * 16; i += kSoftmaxThreads) {
           const int row = row0 + (i >> 4), c = i & 15;
           *reinterpret_cast<uint4*>(vbase + (c >> 3) * kPanelBytes + row * 128 + ((c & 7) << 4)) = make_uint4(0, 0, 0, 0);
         }
       }
-      const bool full = v_lo == 0 && v_hi == kTileKeys;
-      // ---- pass 1: row maximum ----
-      float mx = -INFINITY;
+      // ---- P to shared memory as a bf16 head plus a bf16 remainder (two MMAs per step): with the
+      //      head alone the rounding of the probabilities shows in the output (mean relative error
+      //      against an fp32 softmax just over 1e-3). My 64 keys are one panel of each. ----
 #pragma unroll
-      for (int cb = 0; cb < 4; ++cb) {
-        float sv[32];
-        tmem_ld32(t_row + cb * 32, sv);
-        if (full) {
+      for (int c = 0; c < 8; ++c) {   // 8 chunks of 8 keys
+        uint32_t hi[4], lo[4];
 #pragma unroll
-          for (int i = 0; i < 32; ++i) mx = fmaxf(mx, sv[i]);
-        } else {
-#pragma unroll
-          for (int i = 0; i < 32; ++i) {
-            const int col = cb * 32 + i;
-            if (col >= v_lo && col < v_hi) mx = fmaxf(mx, sv[i]);
-          }
+        for (int e = 0; e < 4; ++e) {
+          const int i0 = c * 8 + 2 * e;
+          const float a = __uint_as_float(sr[i0 >> 5][i0 & 31]), b = __uint_as_float(sr[(i0 + 1) >> 5][(i0 + 1) & 31]);
+          const float ah = __bfloat162float(__float2bfloat16_rn(a)), bh = __bfloat162float(__float2bfloat16_rn(b));
+          hi[e] = pack_bf16x2(ah, bh);
+          lo[e] = pack_bf16x2(a - ah, b - bh);
         }
+        const uint32_t o = half * kPanelBytes + swz(r, c);
+        *reinterpret_cast<uint4*>(smem + kPOff + o) = make_uint4(hi[0], hi[1], hi[2], hi[3]);
+        *reinterpret_cast<uint4*>(smem + kPLoOff + o) = make_uint4(lo[0], lo[1], lo[2], lo[3]);
       }
-      if (P.dbg && t == 0 && blockIdx.x == 0 && blockIdx.y == 0) {
-#pragma unroll
-        for (int cb = 0; cb < 4; ++cb) {
-          float sv[32];
-          tmem_ld32(t_row + cb * 32, sv);
-          for (int i = 0; i < 32; ++i) P.dbg[r * 128 + cb * 32 + i] = sv[i];
-        }
-      }
-      const float m_new = fmaxf(m_run, mx * P.scale_log2);
-      const float m_s = fmaxf(m_new, kNegBig);
-      const float alpha = fast_exp2(m_run - m_s);
-      m_run = m_new;
-      l_run *= alpha;
-#pragma unroll
-      for (int d = 0; d < kD; ++d) acc[d] *= alpha;
-      // ---- pass 2: P = exp2(S * scale - m), bf16, into the swizzled panels ----
-      float l_add = 0.f;
-#pragma unroll
-      for (int cb = 0; cb < 4; ++cb) {
-        float sv[32];
-        tmem_ld32(t_row + cb * 32, sv);
-#pragma unroll
-        for (int i = 0; i < 32; ++i) {
-          const int col = cb * 32 + i;
-          float pv = fast_exp2(sv[i] * P.scale_log2 - m_s);
-          if (!full && (col < v_lo || col >= v_hi)) pv = 0.f;
-          sv[i] = pv;
-          l_add += pv;
-        }
-        // P goes to the second GEMM as a bf16 head plus a bf16 remainder (two MMAs per step): with
-        // the head alone the rounding of the probabilities shows in the output (mean relative
-        // error against an fp32 softmax just over 1e-3)
-#pragma unroll
-        for (int c = 0; c < 4; ++c) {   // 4 chunks of 8 keys
-          uint32_t hi[4], lo[4];
-#pragma unroll
-          for (int e = 0; e < 4; ++e) {
-            const float a = sv[c * 8 + 2 * e], b = sv[c * 8 + 2 * e + 1];
-            const float ah = __bfloat162float(__float2bfloat16_rn(a)), bh = __bfloat162float(__float2bfloat16_rn(b));
-            hi[e] = pack_bf16x2(ah, bh);
-            lo[e] = pack_bf16x2(a - ah, b - bh);
-          }
-          const int chunk = cb * 4 + c;   // 16 chunks of 8 keys: panel = chunk >> 3
-          const uint32_t o = (chunk >> 3) * kPanelBytes + swz(r, chunk & 7);
-          *reinterpret_cast<uint4*>(smem + kPOff + o) = make_uint4(hi[0], hi[1], hi[2], hi[3]);
-          *reinterpret_cast<uint4*>(smem + kPLoOff + o) = make_uint4(lo[0], lo[1], lo[2], lo[3]);
-        }
-      }
-      l_run += l_add;
       fence_proxy_async_smem();
       tc_fence_before();
       mbar_arrive(bar_p);                  // phase t + 1
     }
-    if (ok && !flags[2]) {
-      ok = mbar_wait_bounded(bar_done, 0);
+    if (ok && !flags[4]) {
+      ok = mbar_wait_bounded(bar_o, (n_tiles - 1) & 1);
       if (ok) {
         tc_fence_after();
+        uint32_t orr[2][32];
+        tmem_ld32_issue(t_lane + kOCol + half * 64, orr[0]);
+        tmem_ld32_issue(t_lane + kOCol + half * 64 + 32, orr[1]);
+        tmem_ld_fence(orr[0]);
+        tmem_ld_fence(orr[1]);
 #pragma unroll
-        for (int cb = 0; cb < 4; ++cb) {
-          float o[32];
-          tmem_ld32(t_row + 128 + cb * 32, o);
-#pragma unroll
-          for (int i = 0; i < 32; ++i) acc[cb * 32 + i] += o[i];
-          if (P.dbg && n_tiles == 1 && blockIdx.x == 0 && blockIdx.y == 0)
-            for (int i = 0; i < 32; ++i) P.dbg[16384 + r * 128 + cb * 32 + i] = o[i];
-        }
+        for (int i = 0; i < 64; ++i) acc[i] += __uint_as_float(orr[i >> 5][i & 31]);
+        // the two halves of a row hold partial sums of the probabilities
+        softmax_bar();                     // the last exchange of maxima has been read by everyone
+        xch[half * 128 + r] = l_run;
+        softmax_bar();
+        const float l_tot = l_run + xch[(half ^ 1) * 128 + r];
         if (row_ok) {
-          const float inv = l_run > 0.f ? 1.f / l_run : 0.f;
+          const float inv = l_tot > 0.f ? 1.f / l_tot : 0.f;
           uint4* op = reinterpret_cast<uint4*>(
-              P.out + (int64_t)(qs + j * kBQ + ql) * P.out_tok_stride + (int64_t)(hk * G + slot_h) * kD);
+              P.out + (int64_t)(qs + j * kBQ + ql) * P.out_tok_stride + (int64_t)(hk * G + slot_h) * kD + half * 64);
 #pragma unroll
-          for (int c = 0; c < 16; ++c) {
+          for (int c = 0; c < 8; ++c) {
             uint4 w;
             w.x = pack_bf16x2(acc[c * 8 + 0] * inv, acc[c * 8 + 1] * inv);
             w.y = pack_bf16x2(acc[c * 8 + 2] * inv, acc[c * 8 + 3] * inv);
@@ -419,16 +449,16 @@ swa_prefill_tc_kernel(const Params P, const __grid_constant__ CUtensorMap map_k,
         }
       }
     }
-    if (!ok && lane == 0) { raise_status(P.status, SBK_ST_WAIT_TIMEOUT); flags[2] = 1; }
+    if (!ok && lane == 0 && !flags[4]) { raise_status(P.status, SBK_ST_WAIT_TIMEOUT); flags[4] = 1; }
   }
 
   // ---- teardown: everyone meets here, then the allocating warp returns the TMEM columns ----
-  if (flags[2]) {
+  if (flags[4]) {
     for (int i = 0; i < 1000; ++i) __nanosleep(1000);   // let copies and MMAs in flight land
   }
   tc_fence_before();
   __syncthreads();
-  if (warp == 5) tmem_dealloc(tmem, kTmemCols);
+  if (warp == 9) tmem_dealloc(tmem, kTmemCols);
 }
 
 int launch(const Params& P, int kvh, const CUtensorMap& map_k, const CUtensorMap& map_v,
