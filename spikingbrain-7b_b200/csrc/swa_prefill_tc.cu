@@ -130,10 +130,20 @@ __host__ __device__ constexpr uint32_t instr_desc(int b_mn) {
 // byte offset of the 16-byte chunk `c` (0..7) of row `r` inside a [128 rows][128 B] swizzled panel
 __device__ __forceinline__ uint32_t swz(int r, int c) { return (uint32_t)(r * 128 + ((c ^ (r & 7)) << 4)); }
 
+// two probabilities -> packed bf16 heads and packed bf16 remainders (one conversion each)
+__device__ __forceinline__ void split_bf16x2(float a, float b, uint32_t& hi, uint32_t& lo) {
+  __nv_bfloat162 h = __floats2bfloat162_rn(a, b);   // a in the low half
+  hi = *reinterpret_cast<uint32_t*>(&h);
+  const float ah = __uint_as_float(hi << 16), bh = __uint_as_float(hi & 0xffff0000u);
+  __nv_bfloat162 l = __floats2bfloat162_rn(a - ah, b - bh);
+  lo = *reinterpret_cast<uint32_t*>(&l);
+}
+
 __device__ __forceinline__ void softmax_bar() {
   asm volatile("bar.sync 1, %0;" ::"n"(kSoftmaxThreads) : "memory");
 }
 
+// (registers are handed out to groups of four warps: ten warps count as twelve, hence 168 per thread)
 __global__ void __launch_bounds__(kThreads, 1)
 swa_prefill_tc_kernel(const Params P, const __grid_constant__ CUtensorMap map_k,
                       const __grid_constant__ CUtensorMap map_v, const __grid_constant__ CUtensorMap map_k2,
@@ -342,10 +352,13 @@ swa_prefill_tc_kernel(const Params P, const __grid_constant__ CUtensorMap map_k,
       tmem_ld_fence(sr[0]);
       tmem_ld_fence(sr[1]);
       float mx[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
+      if (full) {
 #pragma unroll
-      for (int i = 0; i < 64; ++i) {
-        const float v = __uint_as_float(sr[i >> 5][i & 31]);
-        if (full || (i >= v_lo && i < v_hi)) mx[i & 3] = fmaxf(mx[i & 3], v);
+        for (int i = 0; i < 64; ++i) mx[i & 3] = fmaxf(mx[i & 3], __uint_as_float(sr[i >> 5][i & 31]));
+      } else {
+#pragma unroll
+        for (int i = 0; i < 64; ++i)
+          if (i >= v_lo && i < v_hi) mx[i & 3] = fmaxf(mx[i & 3], __uint_as_float(sr[i >> 5][i & 31]));
       }
       // The two halves of a row must agree on the offset m exactly, but m only has to be an upper
       // bound of the row's scores, not the maximum itself: the partial maxima are exchanged rounded
@@ -361,26 +374,28 @@ swa_prefill_tc_kernel(const Params P, const __grid_constant__ CUtensorMap map_k,
       m_run = m_new;
       // ---- probabilities, in place of the scores ----
       float ls[4] = {0.f, 0.f, 0.f, 0.f};
+      if (full) {
 #pragma unroll
-      for (int i = 0; i < 64; ++i) {
-        float pv = fast_exp2(__uint_as_float(sr[i >> 5][i & 31]) * P.scale_log2 - m_s);
-        if (!full && (i < v_lo || i >= v_hi)) pv = 0.f;
-        sr[i >> 5][i & 31] = __float_as_uint(pv);
-        ls[i & 3] += pv;
+        for (int i = 0; i < 64; ++i) {
+          const float pv = fast_exp2(__uint_as_float(sr[i >> 5][i & 31]) * P.scale_log2 - m_s);
+          sr[i >> 5][i & 31] = __float_as_uint(pv);
+          ls[i & 3] += pv;
+        }
+      } else {
+#pragma unroll
+        for (int i = 0; i < 64; ++i) {
+          float pv = fast_exp2(__uint_as_float(sr[i >> 5][i & 31]) * P.scale_log2 - m_s);
+          if (i < v_lo || i >= v_hi) pv = 0.f;
+          sr[i >> 5][i & 31] = __float_as_uint(pv);
+          ls[i & 3] += pv;
+        }
       }
       l_run = l_run * alpha + (ls[0] + ls[1]) + (ls[2] + ls[3]);
-      // ---- O_t of the previous tile: in once its GEMM is done; then everything is rescaled ----
+      // ---- the previous tile's second GEMM must be done: it reads P, and O_t is picked up below ----
       if (t > 0) {
         ok = mbar_wait_bounded(bar_o, (t - 1) & 1);
         if (!ok || flags[4]) break;
         tc_fence_after();
-        uint32_t orr[2][32];
-        tmem_ld32_issue(t_lane + kOCol + half * 64, orr[0]);
-        tmem_ld32_issue(t_lane + kOCol + half * 64 + 32, orr[1]);
-        tmem_ld_fence(orr[0]);
-        tmem_ld_fence(orr[1]);
-#pragma unroll
-        for (int i = 0; i < 64; ++i) acc[i] = (acc[i] + __uint_as_float(orr[i >> 5][i & 31])) * alpha;
       }
       // The cache block that holds the newest key also holds slots nobody has written yet; their V
       // bits may be anything, and a zero probability times a NaN is a NaN. Clear those rows of the
@@ -404,16 +419,29 @@ swa_prefill_tc_kernel(const Params P, const __grid_constant__ CUtensorMap map_k,
 #pragma unroll
         for (int e = 0; e < 4; ++e) {
           const int i0 = c * 8 + 2 * e;
-          const float a = __uint_as_float(sr[i0 >> 5][i0 & 31]), b = __uint_as_float(sr[(i0 + 1) >> 5][(i0 + 1) & 31]);
-          const float ah = __bfloat162float(__float2bfloat16_rn(a)), bh = __bfloat162float(__float2bfloat16_rn(b));
-          hi[e] = pack_bf16x2(ah, bh);
-          lo[e] = pack_bf16x2(a - ah, b - bh);
+          split_bf16x2(__uint_as_float(sr[i0 >> 5][i0 & 31]), __uint_as_float(sr[(i0 + 1) >> 5][(i0 + 1) & 31]),
+                       hi[e], lo[e]);
         }
         const uint32_t o = half * kPanelBytes + swz(r, c);
         *reinterpret_cast<uint4*>(smem + kPOff + o) = make_uint4(hi[0], hi[1], hi[2], hi[3]);
         *reinterpret_cast<uint4*>(smem + kPLoOff + o) = make_uint4(lo[0], lo[1], lo[2], lo[3]);
       }
       fence_proxy_async_smem();
+      // ---- O_t of the previous tile; then everything is rescaled (the scores' registers are free now) ----
+      if (t > 0) {
+        uint32_t orr[2][32];
+        tmem_ld32_issue(t_lane + kOCol + half * 64, orr[0]);
+        tmem_ld32_issue(t_lane + kOCol + half * 64 + 32, orr[1]);
+        tmem_ld_fence(orr[0]);
+        tmem_ld_fence(orr[1]);
+        if (__all_sync(0xffffffffu, alpha == 1.f)) {   // the usual case once the maxima have settled
+#pragma unroll
+          for (int i = 0; i < 64; ++i) acc[i] += __uint_as_float(orr[i >> 5][i & 31]);
+        } else {
+#pragma unroll
+          for (int i = 0; i < 64; ++i) acc[i] = (acc[i] + __uint_as_float(orr[i >> 5][i & 31])) * alpha;
+        }
+      }
       tc_fence_before();
       mbar_arrive(bar_p);                  // phase t + 1
     }
