@@ -10,17 +10,17 @@
 //     softmax on S straight from TMEM; P -> bf16 head + bf16 remainder -> shared memory
 //     O_t[128 rows, 128 dims] = P . V       16 x tcgen05.mma, fresh accumulator in TMEM
 //     O += O_t (registers; rescaled by exp2(m_old - m_new) beforehand)
-// Roles (320 threads):
-//   warps 0-7  softmax / accumulate / epilogue. A TMEM lane (= row) can only be read by warps with
-//              the same index mod 4, so warps w and w + 4 share the rows 32 (w mod 4) ... + 31: the
-//              first takes keys 0-63 of a tile and dims 0-63 of the output, the second the other
-//              halves; they exchange their partial row maxima through shared memory once a tile.
-//   warp 8     TMA producer: walks the block table; a 128-key tile of K or V is 16 copies of 2 KiB
+// Roles (608 threads):
+//   warps 0-15 softmax / accumulate / epilogue. A TMEM lane (= row) can only be read by warps with
+//              the same index mod 4, so warps w, w + 4, w + 8, w + 12 share the rows 32 (w mod 4) ... + 31:
+//              each takes 32 keys of a tile and 32 dims of the output; they exchange their partial
+//              row maxima through shared memory once a tile.
+//   warps 16, 17  TMA producers of the K and of the V ring: walk the block table; a 128-key tile of K or V is 16 copies of 2 KiB
 //              (one per 16-token block piece and 64-dim half), landing as two [128 keys][128 B]
 //              panels with the 128-byte swizzle -- the canonical K-major layout for K in S = Q.K^T
 //              and at once the canonical MN-major layout for V in O = P.V. K and V have rings of
 //              their own (two slots each): a K slot is free as soon as its S is computed.
-//   warp 9     allocates TMEM and issues the MMAs (one thread). S is double-buffered in TMEM, so
+//   warp 18    allocates TMEM and issues the MMAs (one thread). S is double-buffered in TMEM, so
 //              Q.K^T of tile t+1 runs while the softmax threads work on tile t, and P.V of tile t
 //              runs while they compute the exponentials of tile t+1.
 // Hand-offs are mbarriers; the tensor core signals them through tcgen05.commit. Every wait is bounded.
@@ -49,8 +49,12 @@ constexpr int kVOff = kKOff + kStages * kOperandBytes;       // V ring
 constexpr int kBarOff = kVOff + kStages * kOperandBytes;     // 229376
 constexpr int kXchOff = kBarOff + 128;                       // 2 x 128 floats: partial row maxima / sums
 constexpr int kSmemBytes = kXchOff + 1024 + 64 + 1024;       // + TMEM slot and flags; + alignment slack
-constexpr int kSoftmaxThreads = 256;
-constexpr int kThreads = kSoftmaxThreads + 64;
+constexpr int kSplit = 4;                     // softmax threads per row
+constexpr int kCols = 128 / kSplit;           // keys of a tile / dims of the output per softmax thread
+constexpr int kSoftmaxWarps = 4 * kSplit;
+constexpr int kSoftmaxThreads = 32 * kSoftmaxWarps;
+constexpr int kThreads = kSoftmaxThreads + 96;   // + K producer, V producer, MMA issuer
+static_assert(kCols == 32, "a softmax thread reads its columns with one 32-column TMEM load");
 constexpr int kTmemCols = 512;                // S0: columns [0,128), S1: [128,256), O_t: [256,384)
 constexpr int kOCol = 256;
 constexpr float kNegBig = -1.0e30f;
@@ -127,6 +131,10 @@ __host__ __device__ constexpr uint32_t instr_desc(int b_mn) {
   return (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)b_mn << 16) | ((128u >> 3) << 17) | ((128u >> 4) << 24);
 }
 
+#define SBK_STAMP(who, idx)                                                              \
+  if (P.dbg && blockIdx.x == 0 && blockIdx.y == 0 && (who) && t < 60)                     \
+    reinterpret_cast<long long*>(P.dbg)[t * 8 + (idx)] = clock64();
+
 // byte offset of the 16-byte chunk `c` (0..7) of row `r` inside a [128 rows][128 B] swizzled panel
 __device__ __forceinline__ uint32_t swz(int r, int c) { return (uint32_t)(r * 128 + ((c ^ (r & 7)) << 4)); }
 
@@ -139,11 +147,11 @@ __device__ __forceinline__ void split_bf16x2(float a, float b, uint32_t& hi, uin
   lo = *reinterpret_cast<uint32_t*>(&l);
 }
 
-__device__ __forceinline__ void softmax_bar() {
-  asm volatile("bar.sync 1, %0;" ::"n"(kSoftmaxThreads) : "memory");
+// barrier among the kSplit warps that share the rows 32 q ... 32 q + 31 (named barriers 1..4)
+__device__ __forceinline__ void row_bar(int q) {
+  asm volatile("bar.sync %0, %1;" ::"r"(q + 1), "n"(32 * kSplit) : "memory");
 }
 
-// (registers are handed out to groups of four warps: ten warps count as twelve, hence 168 per thread)
 __global__ void __launch_bounds__(kThreads, 1)
 swa_prefill_tc_kernel(const Params P, const __grid_constant__ CUtensorMap map_k,
                       const __grid_constant__ CUtensorMap map_v, const __grid_constant__ CUtensorMap map_k2,
@@ -193,7 +201,7 @@ swa_prefill_tc_kernel(const Params P, const __grid_constant__ CUtensorMap map_k,
   // zero probability must not meet a NaN), and what a slot holds later is older, finite data
   for (int i = threadIdx.x; i < kStages * kOperandBytes / 16; i += kThreads)
     *reinterpret_cast<uint4*>(smem + kVOff + i * 16) = make_uint4(0, 0, 0, 0);
-  if (warp == 9) {
+  if (warp == kSoftmaxWarps + 2) {
     tmem_alloc(smem_u32(const_cast<uint32_t*>(tmem_slot)), kTmemCols);
     tmem_relinquish();
   }
@@ -203,8 +211,9 @@ swa_prefill_tc_kernel(const Params P, const __grid_constant__ CUtensorMap map_k,
   tc_fence_after();
   const uint32_t tmem = *tmem_slot;
 
-  if (warp == 8) {
-    // ================================= TMA producer =================================
+  if (warp == kSoftmaxWarps || warp == kSoftmaxWarps + 1) {
+    // ===== TMA producers: one warp per ring (K, V), so that a K tile never queues behind a V slot =====
+    const int kind = warp - kSoftmaxWarps;   // 0: K ring, 1: V ring
     const int32_t* table = P.block_tables + (int64_t)s * P.max_blocks;
     int64_t pb_lane = -1;
     int batch_c0 = 0;
@@ -220,10 +229,10 @@ swa_prefill_tc_kernel(const Params P, const __grid_constant__ CUtensorMap map_k,
         pb_lane = (c <= c_hi && lb < P.max_blocks) ? (int64_t)table[lb] : -1;
       }
       const int slot = t % kStages, use = t / kStages;
-      // lane -> one copy of 2 KiB: chunk (lane >> 2), 64-dim half ((lane >> 1) & 1), K or V (lane & 1)
-      const int i = lane >> 2, half = (lane >> 1) & 1, is_v = lane & 1;
+      // lane -> one copy of 2 KiB: chunk (lane >> 1), 64-dim half (lane & 1); lanes 16-31 idle
+      const int i = (lane >> 1) & 7, half = lane & 1;
       const int c = c0 + i;
-      const bool active = c <= c_end;
+      const bool active = lane < 16 && c <= c_end;
       int src_lane = c - batch_c0;
       src_lane = src_lane < 0 ? 0 : (src_lane > 31 ? 31 : src_lane);
       const int64_t pb_tab = __shfl_sync(0xffffffffu, pb_lane, src_lane);
@@ -232,29 +241,27 @@ swa_prefill_tc_kernel(const Params P, const __grid_constant__ CUtensorMap map_k,
       bad = __any_sync(0xffffffffu, bad);
       const int nvalid = c_end - c0 + 1 < kTileChunks ? c_end - c0 + 1 : kTileChunks;
       const int tin = meta ? 0 : (c * kChunk) % P.block_size;
-      const uint32_t dst = sbase + (is_v ? kVOff : kKOff) + slot * kOperandBytes + half * kPanelBytes + i * 2048;
-      const CUtensorMap* map = meta ? (is_v ? &map_v2 : &map_k2) : (is_v ? &map_v : &map_k);
-      for (int kind = 0; kind < 2 && ok; ++kind) {   // K first: the first GEMM of the tile needs only K
-        const uint32_t bar_e = (kind ? bar_ve : bar_ke) + 8 * slot, bar_f = (kind ? bar_vf : bar_kf) + 8 * slot;
-        if (use > 0 && !mbar_wait_bounded(bar_e, (use - 1) & 1)) ok = false;
-        if (flags[4]) ok = false;
-        if (!ok) break;
-        if (lane == 0) {
-          if (kind == 0) {
-            flags[t & 3] = bad ? 1 : 0;
-            if (bad) raise_status(P.status, SBK_ST_BAD_BLOCK);
-          }
-          mbar_arrive_expect_tx(bar_f, bad ? 0u : (uint32_t)nvalid * 2u * 2048u);
+      const uint32_t dst = sbase + (kind ? kVOff : kKOff) + slot * kOperandBytes + half * kPanelBytes + i * 2048;
+      const CUtensorMap* map = meta ? (kind ? &map_v2 : &map_k2) : (kind ? &map_v : &map_k);
+      const uint32_t bar_e = (kind ? bar_ve : bar_ke) + 8 * slot, bar_f = (kind ? bar_vf : bar_kf) + 8 * slot;
+      if (use > 0 && !mbar_wait_bounded(bar_e, (use - 1) & 1)) ok = false;
+      if (flags[4]) ok = false;
+      if (!ok) break;
+      if (lane == 0) {
+        if (kind == 0) {
+          flags[t & 3] = bad ? 1 : 0;
+          if (bad) raise_status(P.status, SBK_ST_BAD_BLOCK);
         }
-        __syncwarp();
-        if (!bad && active && is_v == kind) {
-          if (P.tile_copy) tma_load_4d(dst, map, 0, tin, hk * 2 + half, (int)pb, bar_f);
-          else tma_load_4d(dst, map, 0, hk * 2 + half, tin, (int)pb, bar_f);
-        }
+        mbar_arrive_expect_tx(bar_f, bad ? 0u : (uint32_t)nvalid * 2u * 2048u);
+      }
+      __syncwarp();
+      if (!bad && active) {
+        if (P.tile_copy) tma_load_4d(dst, map, 0, tin, hk * 2 + half, (int)pb, bar_f);
+        else tma_load_4d(dst, map, 0, hk * 2 + half, tin, (int)pb, bar_f);
       }
     }
     if (!ok && lane == 0 && !flags[4]) { raise_status(P.status, SBK_ST_WAIT_TIMEOUT); flags[4] = 1; }
-  } else if (warp == 9) {
+  } else if (warp == kSoftmaxWarps + 2) {
     // ================================= MMA issuer =================================
     const uint32_t idesc_qk = instr_desc(0), idesc_pv = instr_desc(1);
     const uint32_t q_addr = sbase + kQOff, p_addr = sbase + kPOff, plo_addr = sbase + kPLoOff;
@@ -284,11 +291,13 @@ swa_prefill_tc_kernel(const Params P, const __grid_constant__ CUtensorMap map_k,
       // the next tile's scores are computed while the softmax threads work on this one
       if (t + 1 < n_tiles) ok = issue_qk(t + 1);
       if (!ok) break;
+      SBK_STAMP(lane == 0, 7)
       // P of this tile (and with it: S(t) read, O_t of the previous tile read)
       const int slot = t % kStages;
       ok = mbar_wait_bounded(bar_p, (t + 1) & 1) && mbar_wait_bounded(bar_vf + 8 * slot, (t / kStages) & 1);
       if (!ok || flags[4]) break;
       tc_fence_after();
+      SBK_STAMP(lane == 0, 5)
       if (lane == 0) {
         const uint32_t v_addr = sbase + kVOff + slot * kOperandBytes;
 #pragma unroll
@@ -301,73 +310,78 @@ swa_prefill_tc_kernel(const Params P, const __grid_constant__ CUtensorMap map_k,
         umma_commit(bar_ve + 8 * slot);
         umma_commit(bar_o);
       }
+      SBK_STAMP(lane == 0, 6)
       __syncwarp();
     }
     if (!ok && lane == 0 && !flags[4]) { raise_status(P.status, SBK_ST_WAIT_TIMEOUT); flags[4] = 1; }
   } else {
     // ====================== softmax / accumulate / epilogue ======================
+    constexpr int kCh = kCols / 8;         // 16-byte chunks of bf16 per thread and row
     const int r = (warp & 3) * 32 + lane;  // row of the MMA tile = TMEM lane
-    const int half = warp >> 2;            // which 64 keys of a tile / which 64 dims of the output
+    const int part = warp >> 2;            // which kCols keys of a tile / which kCols dims of the output
+    const int panel = (part * kCols) >> 6, ch0 = ((part * kCols) & 63) >> 3;
     const int slot_h = r >> 4, ql = r & 15;
     const bool row_ok = slot_h < G && ql < nq_tile;
     const int p_row = p0 + ql;             // position of this row's query
     const int lo_row = P.window_left < 0 ? 0 : (p_row - P.window_left > 0 ? p_row - P.window_left : 0);
-    // ---- Q rows into the swizzled K-major panels (this thread: its 64-dim half) ----
+    // ---- Q rows into the swizzled K-major panels (this thread: its kCols dims) ----
     {
       const uint4* qp = reinterpret_cast<const uint4*>(
-          P.q + (int64_t)(qs + j * kBQ + ql) * P.q_tok_stride + (int64_t)(hk * G + slot_h) * kD + half * 64);
+          P.q + (int64_t)(qs + j * kBQ + ql) * P.q_tok_stride + (int64_t)(hk * G + slot_h) * kD + part * kCols);
 #pragma unroll
-      for (int c = 0; c < 8; ++c) {
+      for (int c = 0; c < kCh; ++c) {
         const uint4 v = row_ok ? qp[c] : make_uint4(0, 0, 0, 0);
-        *reinterpret_cast<uint4*>(smem + kQOff + half * kPanelBytes + swz(r, c)) = v;
+        *reinterpret_cast<uint4*>(smem + kQOff + panel * kPanelBytes + swz(r, ch0 + c)) = v;
       }
       fence_proxy_async_smem();
       mbar_arrive(bar_p);                  // phase 0 of bar_p: Q is in place
     }
-    float acc[64];
+    float acc[kCols];
 #pragma unroll
-    for (int d = 0; d < 64; ++d) acc[d] = 0.f;
+    for (int d = 0; d < kCols; ++d) acc[d] = 0.f;
     float m_run = -INFINITY, l_run = 0.f;
     const uint32_t t_lane = tmem + ((uint32_t)((warp & 3) * 32) << 16);
+    __nv_bfloat16* xm = reinterpret_cast<__nv_bfloat16*>(xch);   // [kSplit][128] partial row maxima
     bool ok = true;
     for (int t = 0; t < n_tiles; ++t) {
       ok = mbar_wait_bounded(bar_s + 8 * (t & 1), (t >> 1) & 1);
       if (!ok || flags[4]) break;
       tc_fence_after();
-      // ---- my 64 scores of this row ----
-      uint32_t sr[2][32];
-      tmem_ld32_issue(t_lane + (t & 1) * 128 + half * 64, sr[0]);
-      tmem_ld32_issue(t_lane + (t & 1) * 128 + half * 64 + 32, sr[1]);
+      SBK_STAMP(threadIdx.x == 0, 0)
+      SBK_STAMP(threadIdx.x == 511, 512 + 0)
+      // ---- my kCols scores of this row ----
+      uint32_t sr[32];
+      tmem_ld32_issue(t_lane + (t & 1) * 128 + part * kCols, sr);
       const bool meta = t < n_mt;
       const int tb = meta ? t * kTileKeys : (c_lo + (t - n_mt) * kTileChunks) * kChunk;   // first key of the tile
-      // columns (of my half) this row may see: [v_lo, v_hi)
+      // columns (of my part) this row may see: [v_lo, v_hi)
       int v_lo, v_hi;
       if (meta) { v_lo = 0; v_hi = P.n_meta_chunks * kChunk - tb; }
       else { v_lo = lo_row - tb; v_hi = p_row + 1 - tb; }
-      v_lo -= half * 64; v_hi -= half * 64;
+      v_lo -= part * kCols; v_hi -= part * kCols;
       v_lo = v_lo < 0 ? 0 : v_lo;
-      v_hi = v_hi > 64 ? 64 : v_hi;
+      v_hi = v_hi > kCols ? kCols : v_hi;
       if (flags[t & 3]) v_hi = 0;
-      const bool full = v_lo == 0 && v_hi == 64;
-      tmem_ld_fence(sr[0]);
-      tmem_ld_fence(sr[1]);
+      const bool full = v_lo == 0 && v_hi == kCols;
+      tmem_ld_fence(sr);
       float mx[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
       if (full) {
 #pragma unroll
-        for (int i = 0; i < 64; ++i) mx[i & 3] = fmaxf(mx[i & 3], __uint_as_float(sr[i >> 5][i & 31]));
+        for (int i = 0; i < kCols; ++i) mx[i & 3] = fmaxf(mx[i & 3], __uint_as_float(sr[i]));
       } else {
 #pragma unroll
-        for (int i = 0; i < 64; ++i)
-          if (i >= v_lo && i < v_hi) mx[i & 3] = fmaxf(mx[i & 3], __uint_as_float(sr[i >> 5][i & 31]));
+        for (int i = 0; i < kCols; ++i)
+          if (i >= v_lo && i < v_hi) mx[i & 3] = fmaxf(mx[i & 3], __uint_as_float(sr[i]));
       }
-      // The two halves of a row must agree on the offset m exactly, but m only has to be an upper
+      // The threads of a row must agree on the offset m exactly, but m only has to be an upper
       // bound of the row's scores, not the maximum itself: the partial maxima are exchanged rounded
-      // UP to bf16 (both sides use the rounded values), in a buffer per tile parity.
-      __nv_bfloat16* xm = reinterpret_cast<__nv_bfloat16*>(xch) + (t & 1) * 256;
-      const __nv_bfloat16 mine_b = __float2bfloat16_ru(fmaxf(fmaxf(mx[0], mx[1]), fmaxf(mx[2], mx[3])));
-      xm[half * 128 + r] = mine_b;
-      softmax_bar();
-      const float both = fmaxf(__bfloat162float(mine_b), __bfloat162float(xm[(half ^ 1) * 128 + r]));
+      // UP to bf16 (every side uses the rounded values).
+      row_bar(warp & 3);                   // everyone has read the previous tile's maxima
+      xm[part * 128 + r] = __float2bfloat16_ru(fmaxf(fmaxf(mx[0], mx[1]), fmaxf(mx[2], mx[3])));
+      row_bar(warp & 3);
+      float both = -INFINITY;
+#pragma unroll
+      for (int q2 = 0; q2 < kSplit; ++q2) both = fmaxf(both, __bfloat162float(xm[q2 * 128 + r]));
       const float m_new = fmaxf(m_run, both * P.scale_log2);
       const float m_s = fmaxf(m_new, kNegBig);
       const float alpha = fast_exp2(m_run - m_s);
@@ -376,27 +390,30 @@ swa_prefill_tc_kernel(const Params P, const __grid_constant__ CUtensorMap map_k,
       float ls[4] = {0.f, 0.f, 0.f, 0.f};
       if (full) {
 #pragma unroll
-        for (int i = 0; i < 64; ++i) {
-          const float pv = fast_exp2(__uint_as_float(sr[i >> 5][i & 31]) * P.scale_log2 - m_s);
-          sr[i >> 5][i & 31] = __float_as_uint(pv);
+        for (int i = 0; i < kCols; ++i) {
+          const float pv = fast_exp2(__uint_as_float(sr[i]) * P.scale_log2 - m_s);
+          sr[i] = __float_as_uint(pv);
           ls[i & 3] += pv;
         }
       } else {
 #pragma unroll
-        for (int i = 0; i < 64; ++i) {
-          float pv = fast_exp2(__uint_as_float(sr[i >> 5][i & 31]) * P.scale_log2 - m_s);
+        for (int i = 0; i < kCols; ++i) {
+          float pv = fast_exp2(__uint_as_float(sr[i]) * P.scale_log2 - m_s);
           if (i < v_lo || i >= v_hi) pv = 0.f;
-          sr[i >> 5][i & 31] = __float_as_uint(pv);
+          sr[i] = __float_as_uint(pv);
           ls[i & 3] += pv;
         }
       }
       l_run = l_run * alpha + (ls[0] + ls[1]) + (ls[2] + ls[3]);
+      SBK_STAMP(threadIdx.x == 0, 1)
+      SBK_STAMP(threadIdx.x == 511, 512 + 1)
       // ---- the previous tile's second GEMM must be done: it reads P, and O_t is picked up below ----
       if (t > 0) {
         ok = mbar_wait_bounded(bar_o, (t - 1) & 1);
         if (!ok || flags[4]) break;
         tc_fence_after();
       }
+      SBK_STAMP(threadIdx.x == 0, 2)
       // The cache block that holds the newest key also holds slots nobody has written yet; their V
       // bits may be anything, and a zero probability times a NaN is a NaN. Clear those rows of the
       // tile (at most 15, in the chunk of the last key) before the second GEMM reads them.
@@ -412,61 +429,59 @@ swa_prefill_tc_kernel(const Params P, const __grid_constant__ CUtensorMap map_k,
       }
       // ---- P to shared memory as a bf16 head plus a bf16 remainder (two MMAs per step): with the
       //      head alone the rounding of the probabilities shows in the output (mean relative error
-      //      against an fp32 softmax just over 1e-3). My 64 keys are one panel of each. ----
+      //      against an fp32 softmax just over 1e-3) ----
 #pragma unroll
-      for (int c = 0; c < 8; ++c) {   // 8 chunks of 8 keys
+      for (int c = 0; c < kCh; ++c) {   // chunks of 8 keys
         uint32_t hi[4], lo[4];
 #pragma unroll
-        for (int e = 0; e < 4; ++e) {
-          const int i0 = c * 8 + 2 * e;
-          split_bf16x2(__uint_as_float(sr[i0 >> 5][i0 & 31]), __uint_as_float(sr[(i0 + 1) >> 5][(i0 + 1) & 31]),
-                       hi[e], lo[e]);
-        }
-        const uint32_t o = half * kPanelBytes + swz(r, c);
+        for (int e = 0; e < 4; ++e)
+          split_bf16x2(__uint_as_float(sr[c * 8 + 2 * e]), __uint_as_float(sr[c * 8 + 2 * e + 1]), hi[e], lo[e]);
+        const uint32_t o = panel * kPanelBytes + swz(r, ch0 + c);
         *reinterpret_cast<uint4*>(smem + kPOff + o) = make_uint4(hi[0], hi[1], hi[2], hi[3]);
         *reinterpret_cast<uint4*>(smem + kPLoOff + o) = make_uint4(lo[0], lo[1], lo[2], lo[3]);
       }
       fence_proxy_async_smem();
+      SBK_STAMP(threadIdx.x == 0, 3)
       // ---- O_t of the previous tile; then everything is rescaled (the scores' registers are free now) ----
       if (t > 0) {
-        uint32_t orr[2][32];
-        tmem_ld32_issue(t_lane + kOCol + half * 64, orr[0]);
-        tmem_ld32_issue(t_lane + kOCol + half * 64 + 32, orr[1]);
-        tmem_ld_fence(orr[0]);
-        tmem_ld_fence(orr[1]);
+        uint32_t orr[32];
+        tmem_ld32_issue(t_lane + kOCol + part * kCols, orr);
+        tmem_ld_fence(orr);
         if (__all_sync(0xffffffffu, alpha == 1.f)) {   // the usual case once the maxima have settled
 #pragma unroll
-          for (int i = 0; i < 64; ++i) acc[i] += __uint_as_float(orr[i >> 5][i & 31]);
+          for (int i = 0; i < kCols; ++i) acc[i] += __uint_as_float(orr[i]);
         } else {
 #pragma unroll
-          for (int i = 0; i < 64; ++i) acc[i] = (acc[i] + __uint_as_float(orr[i >> 5][i & 31])) * alpha;
+          for (int i = 0; i < kCols; ++i) acc[i] = (acc[i] + __uint_as_float(orr[i])) * alpha;
         }
       }
       tc_fence_before();
+      SBK_STAMP(threadIdx.x == 0, 4)
+      SBK_STAMP(threadIdx.x == 511, 512 + 4)
       mbar_arrive(bar_p);                  // phase t + 1
     }
     if (ok && !flags[4]) {
       ok = mbar_wait_bounded(bar_o, (n_tiles - 1) & 1);
       if (ok) {
         tc_fence_after();
-        uint32_t orr[2][32];
-        tmem_ld32_issue(t_lane + kOCol + half * 64, orr[0]);
-        tmem_ld32_issue(t_lane + kOCol + half * 64 + 32, orr[1]);
-        tmem_ld_fence(orr[0]);
-        tmem_ld_fence(orr[1]);
+        uint32_t orr[32];
+        tmem_ld32_issue(t_lane + kOCol + part * kCols, orr);
+        tmem_ld_fence(orr);
 #pragma unroll
-        for (int i = 0; i < 64; ++i) acc[i] += __uint_as_float(orr[i >> 5][i & 31]);
-        // the two halves of a row hold partial sums of the probabilities
-        softmax_bar();                     // the last exchange of maxima has been read by everyone
-        xch[half * 128 + r] = l_run;
-        softmax_bar();
-        const float l_tot = l_run + xch[(half ^ 1) * 128 + r];
+        for (int i = 0; i < kCols; ++i) acc[i] += __uint_as_float(orr[i]);
+        // the threads of a row hold partial sums of the probabilities; the P panels are free now
+        float* xl = reinterpret_cast<float*>(smem + kPOff);      // [kSplit][128]
+        xl[part * 128 + r] = l_run;
+        row_bar(warp & 3);
+        float l_tot = 0.f;
+#pragma unroll
+        for (int q2 = 0; q2 < kSplit; ++q2) l_tot += xl[q2 * 128 + r];
         if (row_ok) {
           const float inv = l_tot > 0.f ? 1.f / l_tot : 0.f;
           uint4* op = reinterpret_cast<uint4*>(
-              P.out + (int64_t)(qs + j * kBQ + ql) * P.out_tok_stride + (int64_t)(hk * G + slot_h) * kD + half * 64);
+              P.out + (int64_t)(qs + j * kBQ + ql) * P.out_tok_stride + (int64_t)(hk * G + slot_h) * kD + part * kCols);
 #pragma unroll
-          for (int c = 0; c < 8; ++c) {
+          for (int c = 0; c < kCh; ++c) {
             uint4 w;
             w.x = pack_bf16x2(acc[c * 8 + 0] * inv, acc[c * 8 + 1] * inv);
             w.y = pack_bf16x2(acc[c * 8 + 2] * inv, acc[c * 8 + 3] * inv);
@@ -486,7 +501,7 @@ swa_prefill_tc_kernel(const Params P, const __grid_constant__ CUtensorMap map_k,
   }
   tc_fence_before();
   __syncthreads();
-  if (warp == 9) tmem_dealloc(tmem, kTmemCols);
+  if (warp == kSoftmaxWarps + 2) tmem_dealloc(tmem, kTmemCols);
 }
 
 int launch(const Params& P, int kvh, const CUtensorMap& map_k, const CUtensorMap& map_v,
