@@ -339,11 +339,11 @@ extern "C" int sbk_swa_prefill(const void* q, int64_t q_tok_stride, const void* 
     set_error("sbk_swa_prefill: grid too large");
     return SBK_E_ARG;
   }
-  // Two kernels serve this entry point: tcgen05 (tensor memory, 128-key tiles) and mma.sync.
-  // SBK_PREFILL_KERNEL = "tc" | "mma" picks one; the tcgen05 kernel moves q and out as 16-byte vectors.
+  // Two kernels serve this entry point: tcgen05 (tensor memory, 128-key tiles; the default) and
+  // mma.sync (SBK_PREFILL_KERNEL=mma, or when q / out cannot be moved as 16-byte vectors).
   const char* pick = getenv("SBK_PREFILL_KERNEL");
   const bool vec_ok = aligned16(q) && aligned16(out) && q_tok_stride % 8 == 0 && out_tok_stride % 8 == 0;
-  const bool use_tc = vec_ok && pick != nullptr && strcmp(pick, "tc") == 0;
+  const bool use_tc = vec_ok && !(pick != nullptr && strcmp(pick, "mma") == 0);
   if (use_tc) {
     CUtensorMap mk, mv, mk2, mv2;
     int tc_mode = 0;
@@ -361,8 +361,6 @@ extern "C" int sbk_swa_prefill(const void* q, int64_t q_tok_stride, const void* 
     T.block_size = block_size; T.window_left = window_left; T.scale_log2 = scale * kLog2e;
     T.out = (__nv_bfloat16*)out; T.out_tok_stride = out_tok_stride; T.status = status;
     T.n_meta_chunks = 0;
-    T.dbg = nullptr;
-    if (const char* d = getenv("SBK_PREFILL_DEBUG_PTR")) T.dbg = (float*)strtoull(d, nullptr, 0);
     if (num_meta > 0) {
       const int64_t mstride = (int64_t)16 * kvh * D * 2;
       if (!get_map(&mk2, MapKey{key2, kvh, num_meta / 16, 16, mstride, 1}, &tc_mode) ||

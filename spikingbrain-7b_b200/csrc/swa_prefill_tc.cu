@@ -131,10 +131,6 @@ __host__ __device__ constexpr uint32_t instr_desc(int b_mn) {
   return (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)b_mn << 16) | ((128u >> 3) << 17) | ((128u >> 4) << 24);
 }
 
-#define SBK_STAMP(who, idx)                                                              \
-  if (P.dbg && blockIdx.x == 0 && blockIdx.y == 0 && (who) && t < 60)                     \
-    reinterpret_cast<long long*>(P.dbg)[t * 8 + (idx)] = clock64();
-
 // byte offset of the 16-byte chunk `c` (0..7) of row `r` inside a [128 rows][128 B] swizzled panel
 __device__ __forceinline__ uint32_t swz(int r, int c) { return (uint32_t)(r * 128 + ((c ^ (r & 7)) << 4)); }
 
@@ -291,13 +287,11 @@ swa_prefill_tc_kernel(const Params P, const __grid_constant__ CUtensorMap map_k,
       // the next tile's scores are computed while the softmax threads work on this one
       if (t + 1 < n_tiles) ok = issue_qk(t + 1);
       if (!ok) break;
-      SBK_STAMP(lane == 0, 7)
       // P of this tile (and with it: S(t) read, O_t of the previous tile read)
       const int slot = t % kStages;
       ok = mbar_wait_bounded(bar_p, (t + 1) & 1) && mbar_wait_bounded(bar_vf + 8 * slot, (t / kStages) & 1);
       if (!ok || flags[4]) break;
       tc_fence_after();
-      SBK_STAMP(lane == 0, 5)
       if (lane == 0) {
         const uint32_t v_addr = sbase + kVOff + slot * kOperandBytes;
 #pragma unroll
@@ -310,7 +304,6 @@ swa_prefill_tc_kernel(const Params P, const __grid_constant__ CUtensorMap map_k,
         umma_commit(bar_ve + 8 * slot);
         umma_commit(bar_o);
       }
-      SBK_STAMP(lane == 0, 6)
       __syncwarp();
     }
     if (!ok && lane == 0 && !flags[4]) { raise_status(P.status, SBK_ST_WAIT_TIMEOUT); flags[4] = 1; }
@@ -347,8 +340,6 @@ swa_prefill_tc_kernel(const Params P, const __grid_constant__ CUtensorMap map_k,
       ok = mbar_wait_bounded(bar_s + 8 * (t & 1), (t >> 1) & 1);
       if (!ok || flags[4]) break;
       tc_fence_after();
-      SBK_STAMP(threadIdx.x == 0, 0)
-      SBK_STAMP(threadIdx.x == 511, 512 + 0)
       // ---- my kCols scores of this row ----
       uint32_t sr[32];
       tmem_ld32_issue(t_lane + (t & 1) * 128 + part * kCols, sr);
@@ -405,15 +396,12 @@ swa_prefill_tc_kernel(const Params P, const __grid_constant__ CUtensorMap map_k,
         }
       }
       l_run = l_run * alpha + (ls[0] + ls[1]) + (ls[2] + ls[3]);
-      SBK_STAMP(threadIdx.x == 0, 1)
-      SBK_STAMP(threadIdx.x == 511, 512 + 1)
       // ---- the previous tile's second GEMM must be done: it reads P, and O_t is picked up below ----
       if (t > 0) {
         ok = mbar_wait_bounded(bar_o, (t - 1) & 1);
         if (!ok || flags[4]) break;
         tc_fence_after();
       }
-      SBK_STAMP(threadIdx.x == 0, 2)
       // The cache block that holds the newest key also holds slots nobody has written yet; their V
       // bits may be anything, and a zero probability times a NaN is a NaN. Clear those rows of the
       // tile (at most 15, in the chunk of the last key) before the second GEMM reads them.
@@ -441,7 +429,6 @@ swa_prefill_tc_kernel(const Params P, const __grid_constant__ CUtensorMap map_k,
         *reinterpret_cast<uint4*>(smem + kPLoOff + o) = make_uint4(lo[0], lo[1], lo[2], lo[3]);
       }
       fence_proxy_async_smem();
-      SBK_STAMP(threadIdx.x == 0, 3)
       // ---- O_t of the previous tile; then everything is rescaled (the scores' registers are free now) ----
       if (t > 0) {
         uint32_t orr[32];
@@ -456,8 +443,6 @@ swa_prefill_tc_kernel(const Params P, const __grid_constant__ CUtensorMap map_k,
         }
       }
       tc_fence_before();
-      SBK_STAMP(threadIdx.x == 0, 4)
-      SBK_STAMP(threadIdx.x == 511, 512 + 4)
       mbar_arrive(bar_p);                  // phase t + 1
     }
     if (ok && !flags[4]) {

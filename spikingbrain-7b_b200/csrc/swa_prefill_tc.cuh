@@ -16,7 +16,6 @@ struct Params {
   __nv_bfloat16* out; int64_t out_tok_stride;
   int32_t* status; int tile_copy;
   int n_meta_chunks;   // 16-token chunks of always-visible sink keys, streamed ahead of the window
-  float* dbg;          // development aid: S, O_t of the first tile of CTA (0,0) are copied here when set
 };
 
 // Tensor maps with ONE 128-byte row (64 dims of one kv head) per copy: box_rows == 1.

@@ -295,7 +295,7 @@ def test_swa_decode_with_sink_tokens(ops, H, kvh, n_meta):
         _check_attn(out.cpu(), ref, lse.cpu(), lse_ref)
 
 
-def test_swa_prefill_with_sink_tokens(ops):
+def test_swa_prefill_with_sink_tokens(ops, prefill_kernel):
     D, H, kvh, bs, wl, n_meta = 128, 28, 4, 16, 63, 128
     ctx, new = [0, 90], [50, 33]
     total = [c + n for c, n in zip(ctx, new)]
@@ -354,24 +354,55 @@ def _prefill_case(ops, ctx, new, wl, H, kvh, bs, seed):
     assert worst <= ATTN_MAX_ABS and num / den <= ATTN_MEAN_REL, (worst, num / den)
 
 
+@pytest.fixture(params=["tc", "mma"])
+def prefill_kernel(request, monkeypatch):
+    """The prefill entry point has two kernels: tcgen05 (default) and mma.sync; the environment
+    variable is read at every call."""
+    monkeypatch.setenv("SBK_PREFILL_KERNEL", request.param)
+    return request.param
+
+
 @pytest.mark.parametrize("ctx,new", [([0], [1]), ([0], [16]), ([0], [17]), ([5], [40]), ([0, 100, 33], [70, 3, 129])])
-def test_swa_prefill_small_edges(ops, ctx, new):
+def test_swa_prefill_small_edges(ops, prefill_kernel, ctx, new):
     _prefill_case(ops, ctx, new, wl=63, H=28, kvh=4, bs=16, seed=60)
 
 
 @pytest.mark.parametrize("wl", [0, 15, 16, 255, 4096, -1])
-def test_swa_prefill_window_edges(ops, wl):
+def test_swa_prefill_window_edges(ops, prefill_kernel, wl):
     _prefill_case(ops, [300, 0, 1000], [200, 513, 64], wl=wl, H=28, kvh=4, bs=16, seed=61)
 
 
 @pytest.mark.parametrize("H,kvh,bs", [(7, 1, 16), (14, 2, 32), (32, 4, 64), (4, 4, 16), (16, 2, 128)])
-def test_swa_prefill_head_layouts_and_block_sizes(ops, H, kvh, bs):
+def test_swa_prefill_head_layouts_and_block_sizes(ops, prefill_kernel, H, kvh, bs):
     _prefill_case(ops, [700, 0], [300, 260], wl=511, H=H, kvh=kvh, bs=bs, seed=62)
 
 
-def test_swa_prefill_long_chunk_at_model_shapes(ops):
+def test_swa_prefill_long_chunk_at_model_shapes(ops, prefill_kernel):
     """One 2048-token chunk on top of 6000 cached tokens, window 4096, 28/4 heads."""
     _prefill_case(ops, [6000], [2048], wl=4096, H=28, kvh=4, bs=16, seed=63)
+
+
+def test_swa_prefill_unaligned_views_take_the_vector_free_kernel(ops):
+    """q and out as views whose rows start 4 bytes off a 16-byte boundary: the tcgen05 kernel moves
+    them as 16-byte vectors, so the entry point must fall back to the mma.sync kernel by itself."""
+    D, H, kvh, bs, wl = 128, 28, 4, 16, 63
+    ctx, new = [40], [50]
+    kv, table, nb = make_paged_kv([90], -1, kvh, D, bs, seed=64)
+    g = torch.Generator().manual_seed(65)
+    q = (torch.randn(50, H, D, generator=g) / math.sqrt(D)).bfloat16()
+    qbuf = torch.zeros(50 * H * D + 2, dtype=torch.bfloat16, device=DEV)
+    obuf = torch.zeros_like(qbuf)
+    qv, ov = qbuf[2:].view(50, H, D), obuf[2:].view(50, H, D)
+    qv.copy_(q)
+    assert qv.data_ptr() % 16 == 4
+    kv_d = kv.to(DEV)
+    st = _status()
+    ops.swa_prefill(qv, kv_d[0], kv_d[1], table.to(DEV), torch.tensor([0, 50], dtype=torch.int32, device=DEV),
+                    torch.tensor(ctx, dtype=torch.int32, device=DEV), 50, window_left=wl, out=ov, status=st)
+    assert st.item() == 0
+    for i in (0, 17, 49):
+        ref = ref_ops.swa_paged_decode_ref(q[i][None], kv[0], kv[1], table, [41 + i], wl, D ** -0.5)[0].bfloat16().float()
+        assert float((ov[i].float().cpu() - ref).abs().max()) <= ATTN_MAX_ABS
 
 
 # ------------------------------------------------------------------------------------ GLA
