@@ -40,23 +40,22 @@ constexpr int kTileKeys = 128;                // keys per MMA tile
 constexpr int kTileChunks = kTileKeys / kChunk;
 constexpr int kPanelBytes = 128 * 128;        // [128 rows][128 B]: 64 bf16 of every row
 constexpr int kOperandBytes = 2 * kPanelBytes;   // a [128 x 128] bf16 operand: two panels
-constexpr int kStages = 2;                    // slots of the K ring and of the V ring
+constexpr int kStages = 3;                    // slots of the K ring and of the V ring
 constexpr int kQOff = 0;
-constexpr int kPOff = kOperandBytes;             // P rounded to bf16
-constexpr int kPLoOff = 2 * kOperandBytes;        // what the rounding dropped, again as bf16
-constexpr int kKOff = 3 * kOperandBytes;                     // K ring
+constexpr int kKOff = kOperandBytes;                         // K ring
 constexpr int kVOff = kKOff + kStages * kOperandBytes;       // V ring
 constexpr int kBarOff = kVOff + kStages * kOperandBytes;     // 229376
-constexpr int kXchOff = kBarOff + 128;                       // 2 x 128 floats: partial row maxima / sums
-constexpr int kSmemBytes = kXchOff + 1024 + 64 + 1024;       // + TMEM slot and flags; + alignment slack
+constexpr int kXchOff = kBarOff + 128;                       // 4 x 128 floats: partial row maxima / sums
+constexpr int kSmemBytes = kXchOff + 2048 + 64 + 768;        // + TMEM slot and flags; + alignment slack
 constexpr int kSplit = 4;                     // softmax threads per row
 constexpr int kCols = 128 / kSplit;           // keys of a tile / dims of the output per softmax thread
 constexpr int kSoftmaxWarps = 4 * kSplit;
 constexpr int kSoftmaxThreads = 32 * kSoftmaxWarps;
 constexpr int kThreads = kSoftmaxThreads + 96;   // + K producer, V producer, MMA issuer
 static_assert(kCols == 32, "a softmax thread reads its columns with one 32-column TMEM load");
-constexpr int kTmemCols = 512;                // S0: columns [0,128), S1: [128,256), O_t: [256,384)
-constexpr int kOCol = 256;
+constexpr int kTmemCols = 512;                // S0: columns [0,128), S1: [128,256), O_t: [256,384),
+constexpr int kOCol = 256;                    // P as packed bf16 pairs: head [384,448), remainder [448,512)
+constexpr int kPCol = 384, kPLoCol = 448;
 constexpr float kNegBig = -1.0e30f;
 
 // ---- tcgen05 wrappers ---------------------------------------------------------------------
@@ -85,6 +84,18 @@ __device__ __forceinline__ void umma_bf16(uint32_t d_tmem, uint64_t a_desc, uint
       "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
       : "memory");
 }
+// the same with A read from tensor memory (128 lanes x 8 columns of packed 16-bit pairs per K = 16)
+__device__ __forceinline__ void umma_bf16_ts(uint32_t d_tmem, uint32_t a_tmem, uint64_t b_desc, uint32_t idesc,
+                                             uint32_t accumulate) {
+  asm volatile(
+      "{\n"
+      " .reg .pred p;\n"
+      " setp.ne.b32 p, %4, 0;\n"
+      " tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n"
+      "}\n" ::"r"(d_tmem),
+      "r"(a_tmem), "l"(b_desc), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
 // the mbarrier gets one arrival when every MMA issued so far by this thread has completed
 __device__ __forceinline__ void umma_commit(uint32_t bar) {
   asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
@@ -103,6 +114,17 @@ __device__ __forceinline__ void tmem_ld32_issue(uint32_t taddr, uint32_t (&r)[32
       : "r"(taddr)
       : "memory");
 }
+// 16 consecutive 32-bit columns of this thread's TMEM lane <- registers (asynchronous until tmem_st_wait)
+__device__ __forceinline__ void tmem_st16(uint32_t taddr, const uint32_t (&r)[16]) {
+  asm volatile(
+      "tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], "
+      "{%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16};" ::"r"(taddr),
+      "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]), "r"(r[8]), "r"(r[9]),
+      "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15])
+      : "memory");
+}
+__device__ __forceinline__ void tmem_st_wait() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
+
 // Waits for the loads issued so far and ties the registers to the wait, so that the compiler
 // cannot schedule a use of them ahead of it (the empty statements cost nothing at run time).
 __device__ __forceinline__ void tmem_ld_fence(uint32_t (&r)[32]) {
@@ -155,13 +177,17 @@ swa_prefill_tc_kernel(const Params P, const __grid_constant__ CUtensorMap map_k,
   extern __shared__ uint8_t smem_raw[];
   uint8_t* const smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
   const uint32_t sbase = smem_u32(smem);
+  if (sbase - smem_u32(smem_raw) > 768u) {   // the launch leaves room for this much padding only
+    if (threadIdx.x == 0) raise_status(P.status, SBK_ST_WAIT_TIMEOUT);
+    return;
+  }
   // barriers: K ring full/empty, V ring full/empty, S0/S1 ready, P ready, O_t ready
   const uint32_t bar_kf = sbase + kBarOff, bar_ke = bar_kf + 8 * kStages;
   const uint32_t bar_vf = bar_ke + 8 * kStages, bar_ve = bar_vf + 8 * kStages;
   const uint32_t bar_s = bar_ve + 8 * kStages, bar_p = bar_s + 16, bar_o = bar_p + 8;
   float* xch = reinterpret_cast<float*>(smem + kXchOff);                       // [2][128]
-  volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(smem + kXchOff + 1024);
-  volatile int* flags = reinterpret_cast<volatile int*>(smem + kXchOff + 1024 + 16);   // [0..3] tile t & 3 bad, [4] abort
+  volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(smem + kXchOff + 2048);
+  volatile int* flags = reinterpret_cast<volatile int*>(smem + kXchOff + 2048 + 16);   // [0..7] tile t & 7 bad, [8] abort
 
   const int s = blockIdx.x / P.tiles_per_seq;
   const int j = blockIdx.x - s * P.tiles_per_seq;
@@ -190,7 +216,7 @@ swa_prefill_tc_kernel(const Params P, const __grid_constant__ CUtensorMap map_k,
     }
     mbar_init(bar_p, kSoftmaxThreads);
     mbar_init(bar_o, 1);
-    for (int i = 0; i < 5; ++i) flags[i] = 0;
+    for (int i = 0; i < 9; ++i) flags[i] = 0;
     fence_mbar_init();
   }
   // V panels start finite: a tile may be filled only in part (its other keys are masked, and a
@@ -241,11 +267,11 @@ swa_prefill_tc_kernel(const Params P, const __grid_constant__ CUtensorMap map_k,
       const CUtensorMap* map = meta ? (kind ? &map_v2 : &map_k2) : (kind ? &map_v : &map_k);
       const uint32_t bar_e = (kind ? bar_ve : bar_ke) + 8 * slot, bar_f = (kind ? bar_vf : bar_kf) + 8 * slot;
       if (use > 0 && !mbar_wait_bounded(bar_e, (use - 1) & 1)) ok = false;
-      if (flags[4]) ok = false;
+      if (flags[8]) ok = false;
       if (!ok) break;
       if (lane == 0) {
         if (kind == 0) {
-          flags[t & 3] = bad ? 1 : 0;
+          flags[t & 7] = bad ? 1 : 0;
           if (bad) raise_status(P.status, SBK_ST_BAD_BLOCK);
         }
         mbar_arrive_expect_tx(bar_f, bad ? 0u : (uint32_t)nvalid * 2u * 2048u);
@@ -256,15 +282,15 @@ swa_prefill_tc_kernel(const Params P, const __grid_constant__ CUtensorMap map_k,
         else tma_load_4d(dst, map, 0, hk * 2 + half, tin, (int)pb, bar_f);
       }
     }
-    if (!ok && lane == 0 && !flags[4]) { raise_status(P.status, SBK_ST_WAIT_TIMEOUT); flags[4] = 1; }
+    if (!ok && lane == 0 && !flags[8]) { raise_status(P.status, SBK_ST_WAIT_TIMEOUT); flags[8] = 1; }
   } else if (warp == kSoftmaxWarps + 2) {
     // ================================= MMA issuer =================================
     const uint32_t idesc_qk = instr_desc(0), idesc_pv = instr_desc(1);
-    const uint32_t q_addr = sbase + kQOff, p_addr = sbase + kPOff, plo_addr = sbase + kPLoOff;
+    const uint32_t q_addr = sbase + kQOff;
     // S(t) = Q . K(t)^T into S buffer t & 1; frees the K slot
     auto issue_qk = [&](int t) -> bool {
       const int slot = t % kStages;
-      if (!mbar_wait_bounded(bar_kf + 8 * slot, (t / kStages) & 1) || flags[4]) return false;
+      if (!mbar_wait_bounded(bar_kf + 8 * slot, (t / kStages) & 1) || flags[8]) return false;
       tc_fence_after();
       if (lane == 0) {
         const uint32_t k_addr = sbase + kKOff + slot * kOperandBytes;
@@ -290,23 +316,22 @@ swa_prefill_tc_kernel(const Params P, const __grid_constant__ CUtensorMap map_k,
       // P of this tile (and with it: S(t) read, O_t of the previous tile read)
       const int slot = t % kStages;
       ok = mbar_wait_bounded(bar_p, (t + 1) & 1) && mbar_wait_bounded(bar_vf + 8 * slot, (t / kStages) & 1);
-      if (!ok || flags[4]) break;
+      if (!ok || flags[8]) break;
       tc_fence_after();
       if (lane == 0) {
         const uint32_t v_addr = sbase + kVOff + slot * kOperandBytes;
 #pragma unroll
-        for (int k = 0; k < 8; ++k) {   // 8 steps of 16 keys; P panels hold keys 0-63 / 64-127
-          const uint32_t a_off = (k >> 2) * kPanelBytes + (k & 3) * 32;
+        for (int k = 0; k < 8; ++k) {   // 8 steps of 16 keys: 8 TMEM columns of P (head, then remainder), 16 rows of V
           const uint64_t vd = smem_desc(v_addr + k * 2048, kPanelBytes);
-          umma_bf16(tmem + kOCol, smem_desc(p_addr + a_off, 16), vd, idesc_pv, k > 0);
-          umma_bf16(tmem + kOCol, smem_desc(plo_addr + a_off, 16), vd, idesc_pv, 1);
+          umma_bf16_ts(tmem + kOCol, tmem + kPCol + k * 8, vd, idesc_pv, k > 0);
+          umma_bf16_ts(tmem + kOCol, tmem + kPLoCol + k * 8, vd, idesc_pv, 1);
         }
         umma_commit(bar_ve + 8 * slot);
         umma_commit(bar_o);
       }
       __syncwarp();
     }
-    if (!ok && lane == 0 && !flags[4]) { raise_status(P.status, SBK_ST_WAIT_TIMEOUT); flags[4] = 1; }
+    if (!ok && lane == 0 && !flags[8]) { raise_status(P.status, SBK_ST_WAIT_TIMEOUT); flags[8] = 1; }
   } else {
     // ====================== softmax / accumulate / epilogue ======================
     constexpr int kCh = kCols / 8;         // 16-byte chunks of bf16 per thread and row
@@ -338,7 +363,7 @@ swa_prefill_tc_kernel(const Params P, const __grid_constant__ CUtensorMap map_k,
     bool ok = true;
     for (int t = 0; t < n_tiles; ++t) {
       ok = mbar_wait_bounded(bar_s + 8 * (t & 1), (t >> 1) & 1);
-      if (!ok || flags[4]) break;
+      if (!ok || flags[8]) break;
       tc_fence_after();
       // ---- my kCols scores of this row ----
       uint32_t sr[32];
@@ -352,7 +377,7 @@ swa_prefill_tc_kernel(const Params P, const __grid_constant__ CUtensorMap map_k,
       v_lo -= part * kCols; v_hi -= part * kCols;
       v_lo = v_lo < 0 ? 0 : v_lo;
       v_hi = v_hi > kCols ? kCols : v_hi;
-      if (flags[t & 3]) v_hi = 0;
+      if (flags[t & 7]) v_hi = 0;
       const bool full = v_lo == 0 && v_hi == kCols;
       tmem_ld_fence(sr);
       float mx[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
@@ -399,7 +424,7 @@ swa_prefill_tc_kernel(const Params P, const __grid_constant__ CUtensorMap map_k,
       // ---- the previous tile's second GEMM must be done: it reads P, and O_t is picked up below ----
       if (t > 0) {
         ok = mbar_wait_bounded(bar_o, (t - 1) & 1);
-        if (!ok || flags[4]) break;
+        if (!ok || flags[8]) break;
         tc_fence_after();
       }
       // The cache block that holds the newest key also holds slots nobody has written yet; their V
@@ -414,21 +439,20 @@ swa_prefill_tc_kernel(const Params P, const __grid_constant__ CUtensorMap map_k,
           const int row = row0 + (i >> 4), c = i & 15;
           *reinterpret_cast<uint4*>(vbase + (c >> 3) * kPanelBytes + row * 128 + ((c & 7) << 4)) = make_uint4(0, 0, 0, 0);
         }
+        fence_proxy_async_smem();
       }
-      // ---- P to shared memory as a bf16 head plus a bf16 remainder (two MMAs per step): with the
+      // ---- P to tensor memory, where the second GEMM reads its A operand: packed bf16 pairs (key 2c in
+      //      the low half of column c), as a bf16 head plus a bf16 remainder (two MMAs per step): with the
       //      head alone the rounding of the probabilities shows in the output (mean relative error
       //      against an fp32 softmax just over 1e-3) ----
+      {
+        uint32_t hi[16], lo[16];
 #pragma unroll
-      for (int c = 0; c < kCh; ++c) {   // chunks of 8 keys
-        uint32_t hi[4], lo[4];
-#pragma unroll
-        for (int e = 0; e < 4; ++e)
-          split_bf16x2(__uint_as_float(sr[c * 8 + 2 * e]), __uint_as_float(sr[c * 8 + 2 * e + 1]), hi[e], lo[e]);
-        const uint32_t o = panel * kPanelBytes + swz(r, ch0 + c);
-        *reinterpret_cast<uint4*>(smem + kPOff + o) = make_uint4(hi[0], hi[1], hi[2], hi[3]);
-        *reinterpret_cast<uint4*>(smem + kPLoOff + o) = make_uint4(lo[0], lo[1], lo[2], lo[3]);
+        for (int e = 0; e < 16; ++e)
+          split_bf16x2(__uint_as_float(sr[2 * e]), __uint_as_float(sr[2 * e + 1]), hi[e], lo[e]);
+        tmem_st16(t_lane + kPCol + part * (kCols / 2), hi);
+        tmem_st16(t_lane + kPLoCol + part * (kCols / 2), lo);
       }
-      fence_proxy_async_smem();
       // ---- O_t of the previous tile; then everything is rescaled (the scores' registers are free now) ----
       if (t > 0) {
         uint32_t orr[32];
@@ -442,10 +466,11 @@ swa_prefill_tc_kernel(const Params P, const __grid_constant__ CUtensorMap map_k,
           for (int i = 0; i < kCols; ++i) acc[i] = (acc[i] + __uint_as_float(orr[i])) * alpha;
         }
       }
+      tmem_st_wait();
       tc_fence_before();
       mbar_arrive(bar_p);                  // phase t + 1
     }
-    if (ok && !flags[4]) {
+    if (ok && !flags[8]) {
       ok = mbar_wait_bounded(bar_o, (n_tiles - 1) & 1);
       if (ok) {
         tc_fence_after();
@@ -454,8 +479,9 @@ swa_prefill_tc_kernel(const Params P, const __grid_constant__ CUtensorMap map_k,
         tmem_ld_fence(orr);
 #pragma unroll
         for (int i = 0; i < kCols; ++i) acc[i] += __uint_as_float(orr[i]);
-        // the threads of a row hold partial sums of the probabilities; the P panels are free now
-        float* xl = reinterpret_cast<float*>(smem + kPOff);      // [kSplit][128]
+        // the threads of a row hold partial sums of the probabilities
+        row_bar(warp & 3);                 // the last exchange of maxima has been read by everyone
+        float* xl = xch;                                         // [kSplit][128]
         xl[part * 128 + r] = l_run;
         row_bar(warp & 3);
         float l_tot = 0.f;
@@ -477,11 +503,11 @@ swa_prefill_tc_kernel(const Params P, const __grid_constant__ CUtensorMap map_k,
         }
       }
     }
-    if (!ok && lane == 0 && !flags[4]) { raise_status(P.status, SBK_ST_WAIT_TIMEOUT); flags[4] = 1; }
+    if (!ok && lane == 0 && !flags[8]) { raise_status(P.status, SBK_ST_WAIT_TIMEOUT); flags[8] = 1; }
   }
 
   // ---- teardown: everyone meets here, then the allocating warp returns the TMEM columns ----
-  if (flags[4]) {
+  if (flags[8]) {
     for (int i = 0; i < 1000; ++i) __nanosleep(1000);   // let copies and MMAs in flight land
   }
   tc_fence_before();
