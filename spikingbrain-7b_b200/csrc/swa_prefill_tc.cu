@@ -53,9 +53,8 @@ constexpr int kSoftmaxWarps = 4 * kSplit;
 constexpr int kSoftmaxThreads = 32 * kSoftmaxWarps;
 constexpr int kThreads = kSoftmaxThreads + 96;   // + K producer, V producer, MMA issuer
 static_assert(kCols == 32, "a softmax thread reads its columns with one 32-column TMEM load");
-constexpr int kTmemCols = 512;                // S0: columns [0,128), S1: [128,256), O_t: [256,384),
-constexpr int kOCol = 256;                    // P as packed bf16 pairs: head [384,448), remainder [448,512)
-constexpr int kPCol = 384, kPLoCol = 448;
+constexpr int kTmemCols = 512;                // S0 / P0: columns [0,128), S1 / P1: [128,256), O: [256,384)
+constexpr int kOCol = 256;
 constexpr float kNegBig = -1.0e30f;
 
 // ---- tcgen05 wrappers ---------------------------------------------------------------------
@@ -121,6 +120,17 @@ __device__ __forceinline__ void tmem_st16(uint32_t taddr, const uint32_t (&r)[16
       "{%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16};" ::"r"(taddr),
       "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]), "r"(r[8]), "r"(r[9]),
       "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15])
+      : "memory");
+}
+__device__ __forceinline__ void tmem_st32(uint32_t taddr, const uint32_t (&r)[32]) {
+  asm volatile(
+      "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], "
+      "{%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16, "
+      "%17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31, %32};" ::"r"(taddr),
+      "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]), "r"(r[8]), "r"(r[9]),
+      "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15]), "r"(r[16]), "r"(r[17]), "r"(r[18]),
+      "r"(r[19]), "r"(r[20]), "r"(r[21]), "r"(r[22]), "r"(r[23]), "r"(r[24]), "r"(r[25]), "r"(r[26]), "r"(r[27]),
+      "r"(r[28]), "r"(r[29]), "r"(r[30]), "r"(r[31])
       : "memory");
 }
 __device__ __forceinline__ void tmem_st_wait() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
@@ -323,8 +333,8 @@ swa_prefill_tc_kernel(const Params P, const __grid_constant__ CUtensorMap map_k,
 #pragma unroll
         for (int k = 0; k < 8; ++k) {   // 8 steps of 16 keys: 8 TMEM columns of P (head, then remainder), 16 rows of V
           const uint64_t vd = smem_desc(v_addr + k * 2048, kPanelBytes);
-          umma_bf16_ts(tmem + kOCol, tmem + kPCol + k * 8, vd, idesc_pv, k > 0);
-          umma_bf16_ts(tmem + kOCol, tmem + kPLoCol + k * 8, vd, idesc_pv, 1);
+          umma_bf16_ts(tmem + kOCol, tmem + (t & 1) * 128 + k * 8, vd, idesc_pv, (t > 0) || (k > 0));
+          umma_bf16_ts(tmem + kOCol, tmem + (t & 1) * 128 + 64 + k * 8, vd, idesc_pv, 1);
         }
         umma_commit(bar_ve + 8 * slot);
         umma_commit(bar_o);
@@ -354,9 +364,6 @@ swa_prefill_tc_kernel(const Params P, const __grid_constant__ CUtensorMap map_k,
       fence_proxy_async_smem();
       mbar_arrive(bar_p);                  // phase 0 of bar_p: Q is in place
     }
-    float acc[kCols];
-#pragma unroll
-    for (int d = 0; d < kCols; ++d) acc[d] = 0.f;
     float m_run = -INFINITY, l_run = 0.f;
     const uint32_t t_lane = tmem + ((uint32_t)((warp & 3) * 32) << 16);
     __nv_bfloat16* xm = reinterpret_cast<__nv_bfloat16*>(xch);   // [kSplit][128] partial row maxima
@@ -398,9 +405,14 @@ swa_prefill_tc_kernel(const Params P, const __grid_constant__ CUtensorMap map_k,
       float both = -INFINITY;
 #pragma unroll
       for (int q2 = 0; q2 < kSplit; ++q2) both = fmaxf(both, __bfloat162float(xm[q2 * 128 + r]));
-      const float m_new = fmaxf(m_run, both * P.scale_log2);
+      // The offset in use moves only when the row maximum has grown by more than 2^8 (the
+      // probabilities then stay below 256, far inside fp32 and bf16 range): O, which accumulates in
+      // tensor memory, has to be rescaled only then, which after the first tile is rare.
+      const float cand = fmaxf(m_run, both * P.scale_log2);
+      const bool move = cand > m_run + 8.f;   // also the first visible key of a row (m_run = -inf)
+      const float m_new = move ? cand : m_run;
       const float m_s = fmaxf(m_new, kNegBig);
-      const float alpha = fast_exp2(m_run - m_s);
+      const float alpha = move ? fast_exp2(m_run - m_s) : 1.f;
       m_run = m_new;
       // ---- probabilities, in place of the scores ----
       float ls[4] = {0.f, 0.f, 0.f, 0.f};
@@ -421,11 +433,17 @@ swa_prefill_tc_kernel(const Params P, const __grid_constant__ CUtensorMap map_k,
         }
       }
       l_run = l_run * alpha + (ls[0] + ls[1]) + (ls[2] + ls[3]);
-      // ---- the previous tile's second GEMM must be done: it reads P, and O_t is picked up below ----
-      if (t > 0) {
+      // ---- rescale O (my kCols dims of this row) where the offset moved; the GEMMs that wrote it must be done ----
+      if (__any_sync(0xffffffffu, t > 0 && alpha != 1.f)) {
         ok = mbar_wait_bounded(bar_o, (t - 1) & 1);
         if (!ok || flags[8]) break;
         tc_fence_after();
+        uint32_t orr[32];
+        tmem_ld32_issue(t_lane + kOCol + part * kCols, orr);
+        tmem_ld_fence(orr);
+#pragma unroll
+        for (int i = 0; i < kCols; ++i) orr[i] = __float_as_uint(__uint_as_float(orr[i]) * alpha);
+        tmem_st32(t_lane + kOCol + part * kCols, orr);
       }
       // The cache block that holds the newest key also holds slots nobody has written yet; their V
       // bits may be anything, and a zero probability times a NaN is a NaN. Clear those rows of the
@@ -446,25 +464,14 @@ swa_prefill_tc_kernel(const Params P, const __grid_constant__ CUtensorMap map_k,
       //      head alone the rounding of the probabilities shows in the output (mean relative error
       //      against an fp32 softmax just over 1e-3) ----
       {
+        // P takes the place of S in the same TMEM buffer (every thread of the row has its scores in
+        // registers since the exchange of the maxima): head in columns [0,64), remainder in [64,128)
         uint32_t hi[16], lo[16];
 #pragma unroll
         for (int e = 0; e < 16; ++e)
           split_bf16x2(__uint_as_float(sr[2 * e]), __uint_as_float(sr[2 * e + 1]), hi[e], lo[e]);
-        tmem_st16(t_lane + kPCol + part * (kCols / 2), hi);
-        tmem_st16(t_lane + kPLoCol + part * (kCols / 2), lo);
-      }
-      // ---- O_t of the previous tile; then everything is rescaled (the scores' registers are free now) ----
-      if (t > 0) {
-        uint32_t orr[32];
-        tmem_ld32_issue(t_lane + kOCol + part * kCols, orr);
-        tmem_ld_fence(orr);
-        if (__all_sync(0xffffffffu, alpha == 1.f)) {   // the usual case once the maxima have settled
-#pragma unroll
-          for (int i = 0; i < kCols; ++i) acc[i] += __uint_as_float(orr[i]);
-        } else {
-#pragma unroll
-          for (int i = 0; i < kCols; ++i) acc[i] = (acc[i] + __uint_as_float(orr[i])) * alpha;
-        }
+        tmem_st16(t_lane + (t & 1) * 128 + part * (kCols / 2), hi);
+        tmem_st16(t_lane + (t & 1) * 128 + 64 + part * (kCols / 2), lo);
       }
       tmem_st_wait();
       tc_fence_before();
@@ -477,8 +484,9 @@ swa_prefill_tc_kernel(const Params P, const __grid_constant__ CUtensorMap map_k,
         uint32_t orr[32];
         tmem_ld32_issue(t_lane + kOCol + part * kCols, orr);
         tmem_ld_fence(orr);
+        float acc[kCols];
 #pragma unroll
-        for (int i = 0; i < kCols; ++i) acc[i] += __uint_as_float(orr[i]);
+        for (int i = 0; i < kCols; ++i) acc[i] = __uint_as_float(orr[i]);
         // the threads of a row hold partial sums of the probabilities
         row_bar(warp & 3);                 // the last exchange of maxima has been read by everyone
         float* xl = xch;                                         // [kSplit][128]
