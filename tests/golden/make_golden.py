@@ -2,7 +2,7 @@
 
 Run it only in a container that holds the reference checkout (read-only):
 
-    python tests/golden/make_golden.py [/path/to/SpikingBrain-7B]
+    python tests/golden/make_golden.py /path/to/SpikingBrain-7B
 
 It executes, on the CPU,
   * hf_7B_model/cache.py `Cache.update` on deterministic K/V streams          -> cache_*.npz
@@ -31,7 +31,9 @@ import numpy as np
 import torch
 
 HERE = os.path.dirname(os.path.abspath(__file__))
-REF = sys.argv[1] if len(sys.argv) > 1 else "/root/reference"
+if len(sys.argv) < 2:
+    sys.exit("usage: python tests/golden/make_golden.py /path/to/SpikingBrain-7B")
+REF = sys.argv[1]
 
 
 def load_ref(rel_path, name):
