@@ -5,7 +5,9 @@
 //     state[slot[s]] <- S
 // One CTA of 256 threads per (sequence, head). The 64 KiB state tile lives in REGISTERS for the
 // whole run (thread = float4 of v columns x 16 k rows), so it crosses HBM twice per chunk instead
-// of twice per token; per token only the four 128-vectors q, k, g, v are read and o written.
+// of twice per token; per token only the four 128-vectors q, k, g, v are read and o written. The
+// work is fp32 arithmetic on the CUDA cores (the state and read-out must hold 1e-4 against an fp32
+// recurrence), so the count of operations per state element is what matters: see the round below.
 // Tokens are staged four at a time through shared memory; the read-out's sum over k rows is
 // finished across the 8 row groups once per four tokens. The same optional fused neighbours as
 // the single-token step (GlaFusion): ReLU on q/k, gate logits -> log-decay, per-head RMS norm.
@@ -53,7 +55,16 @@ gla_scan_kernel(const T* __restrict__ q, const T* __restrict__ k, const T* __res
   const int tid = threadIdx.x;
   const int c4 = tid % TPR, r0 = tid / TPR;
 
+  // Within a round of up to four tokens the decays are factored out of the state: with
+  // G_t[r] = g_1[r] + ... + g_t[r] (per key row r) and St = diag(exp(-G_t)) S_t,
+  //     St_t = St_(t-1) + (k_t exp(-G_t)) v_t^T ,   o_t = (q_t scale exp(G_t)) . St_t ,
+  // and the true state comes back at the end of the round as diag(exp(G_R)) St_R: two fused
+  // multiply-adds per state element and token instead of three operations. A row whose decay
+  // within a round is too strong for that (exp(-G) would leave fp32 range; gate logits far below
+  // -500) makes the whole CTA keep the plain recurrence for that round.
   __shared__ float s_q[kScanTokens][D], s_k[kScanTokens][D], s_d[kScanTokens][D];
+  __shared__ float s_end[D];        // what the row is multiplied by at the end of the round
+  __shared__ int s_plain[1];        // 1: this round runs the plain recurrence
   __shared__ float4 s_v[kScanTokens][TPR];
   __shared__ float4 s_o[kScanTokens][GROUPS][TPR];
   __shared__ float s_sq[2][8];
@@ -68,39 +79,106 @@ gla_scan_kernel(const T* __restrict__ q, const T* __restrict__ k, const T* __res
     for (int i = 0; i < RPT; ++i) S[i] = ld_stream_f4(tile + (int64_t)(r0 + i * GROUPS) * TPR + c4);
   }
 
+  // The inputs of a round are fetched into registers one round ahead (thread -> key row d = tid % D
+  // and the tokens tt = tid / D, tid / D + 256 / D, ...; every thread also takes the row's four gate
+  // values, to sum the log-decays itself), so that their latency hides behind the previous round.
+  constexpr int TSTEP = 256 / D;           // 2 for D = 128, 4 for D = 64
+  constexpr int TPT = kScanTokens / TSTEP; // tokens per thread and round
+  const int sd = tid % D, st0 = tid / D;
+  T pg[kScanTokens], pq[TPT], pk[TPT], pv[TPT];
+  auto prefetch = [&](int tb2) {
+#pragma unroll
+    for (int tt = 0; tt < kScanTokens; ++tt)
+      if (tb2 + tt < t1) pg[tt] = g[((int64_t)(tb2 + tt) * Hkv + hk) * D + sd];
+#pragma unroll
+    for (int u = 0; u < TPT; ++u) {
+      const int64_t tok = tb2 + st0 + u * TSTEP;
+      if (tok < t1) {
+        const int64_t kv_off = (tok * Hkv + hk) * D + sd;
+        pq[u] = q[(tok * H + h) * D + sd];
+        pk[u] = k[kv_off];
+        pv[u] = v[kv_off];
+      }
+    }
+  };
+  prefetch(t0);
+
   for (int tb = t0; tb < t1; tb += kScanTokens) {
     const int nt = t1 - tb < kScanTokens ? t1 - tb : kScanTokens;
-    // ---- stage q*scale, k, exp(g), v of up to four tokens ----
-    for (int idx = tid; idx < nt * D; idx += 256) {
-      const int tt = idx / D, d = idx - tt * D;
-      const int64_t tok = tb + tt;
-      float qv = scan_to_f32(q[(tok * H + h) * D + d]);
-      const int64_t kv_off = (tok * Hkv + hk) * D + d;
-      float kv = scan_to_f32(k[kv_off]);
-      if (fu.relu_qk) { qv = fmaxf(qv, 0.f); kv = fmaxf(kv, 0.f); }
-      s_q[tt][d] = qv * scale;
-      s_k[tt][d] = kv;
-      s_d[tt][d] = expf(gla_gate<T>(scan_to_f32(g[kv_off]), fu));
-      reinterpret_cast<float*>(&s_v[tt][0])[d] = scan_to_f32(v[kv_off]);
+    // ---- stage the round from the registers ----
+    {
+      float gl[kScanTokens];
+      float G = 0.f;
+#pragma unroll
+      for (int tt = 0; tt < kScanTokens; ++tt) {
+        gl[tt] = tt < nt ? gla_gate<T>(scan_to_f32(pg[tt]), fu) : 0.f;
+        G += gl[tt];
+      }
+      // exp(60) keeps every product well inside fp32 range (a NaN also lands on the plain side); the
+      // choice is made for the whole CTA, so that the common case runs without a branch per row
+      const bool plain = __syncthreads_or(!(G > -60.f)) != 0;
+      if (tid == 0) s_plain[0] = plain ? 1 : 0;
+      if (tid < D) s_end[sd] = plain ? 1.f : __expf(G);
+      float Gt = 0.f;
+#pragma unroll
+      for (int tt = 0; tt < kScanTokens; ++tt) {
+        Gt += gl[tt];
+        if (tt < nt && tt % TSTEP == st0) {
+          float qv = scan_to_f32(pq[tt / TSTEP]);
+          float kv = scan_to_f32(pk[tt / TSTEP]);
+          if (fu.relu_qk) { qv = fmaxf(qv, 0.f); kv = fmaxf(kv, 0.f); }
+          s_d[tt][sd] = __expf(gl[tt]);                                // used by plain rounds only
+          s_k[tt][sd] = plain ? kv : kv * __expf(-Gt);
+          s_q[tt][sd] = plain ? qv * scale : qv * scale * __expf(Gt);
+          reinterpret_cast<float*>(&s_v[tt][0])[sd] = scan_to_f32(pv[tt / TSTEP]);
+        }
+      }
     }
+    if (tb + kScanTokens < t1) prefetch(tb + kScanTokens);
     __syncthreads();
-    for (int tt = 0; tt < nt; ++tt) {
-      const float4 vv = s_v[tt][c4];
-      float4 o = make_float4(0.f, 0.f, 0.f, 0.f);
+    if (!s_plain[0]) {
+      for (int tt = 0; tt < nt; ++tt) {
+        const float4 vv = s_v[tt][c4];
+        float4 o = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+        for (int i = 0; i < RPT; ++i) {
+          const int r = r0 + i * GROUPS;
+          const float kk = s_k[tt][r], qq = s_q[tt][r];
+          S[i].x = fmaf(kk, vv.x, S[i].x);
+          S[i].y = fmaf(kk, vv.y, S[i].y);
+          S[i].z = fmaf(kk, vv.z, S[i].z);
+          S[i].w = fmaf(kk, vv.w, S[i].w);
+          o.x = fmaf(qq, S[i].x, o.x);
+          o.y = fmaf(qq, S[i].y, o.y);
+          o.z = fmaf(qq, S[i].z, o.z);
+          o.w = fmaf(qq, S[i].w, o.w);
+        }
+        s_o[tt][r0][c4] = o;
+      }
 #pragma unroll
       for (int i = 0; i < RPT; ++i) {
-        const int r = r0 + i * GROUPS;
-        const float d = s_d[tt][r], kk = s_k[tt][r], qq = s_q[tt][r];
-        S[i].x = fmaf(d, S[i].x, kk * vv.x);
-        S[i].y = fmaf(d, S[i].y, kk * vv.y);
-        S[i].z = fmaf(d, S[i].z, kk * vv.z);
-        S[i].w = fmaf(d, S[i].w, kk * vv.w);
-        o.x = fmaf(qq, S[i].x, o.x);
-        o.y = fmaf(qq, S[i].y, o.y);
-        o.z = fmaf(qq, S[i].z, o.z);
-        o.w = fmaf(qq, S[i].w, o.w);
+        const float e = s_end[r0 + i * GROUPS];
+        S[i].x *= e; S[i].y *= e; S[i].z *= e; S[i].w *= e;
       }
-      s_o[tt][r0][c4] = o;
+    } else {
+      for (int tt = 0; tt < nt; ++tt) {
+        const float4 vv = s_v[tt][c4];
+        float4 o = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+        for (int i = 0; i < RPT; ++i) {
+          const int r = r0 + i * GROUPS;
+          const float d = s_d[tt][r], kk = s_k[tt][r], qq = s_q[tt][r];
+          S[i].x = fmaf(d, S[i].x, kk * vv.x);
+          S[i].y = fmaf(d, S[i].y, kk * vv.y);
+          S[i].z = fmaf(d, S[i].z, kk * vv.z);
+          S[i].w = fmaf(d, S[i].w, kk * vv.w);
+          o.x = fmaf(qq, S[i].x, o.x);
+          o.y = fmaf(qq, S[i].y, o.y);
+          o.z = fmaf(qq, S[i].z, o.z);
+          o.w = fmaf(qq, S[i].w, o.w);
+        }
+        s_o[tt][r0][c4] = o;
+      }
     }
     __syncthreads();
     // ---- finish the read-out: sum the row groups, one output element per thread and trip ----
