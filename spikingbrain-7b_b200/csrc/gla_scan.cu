@@ -8,8 +8,8 @@
 // of twice per token; per token only the four 128-vectors q, k, g, v are read and o written. The
 // work is fp32 arithmetic on the CUDA cores (the state and read-out must hold 1e-4 against an fp32
 // recurrence), so the count of operations per state element is what matters: see the round below.
-// Tokens are staged four at a time through shared memory; the read-out's sum over k rows is
-// finished across the 8 row groups once per four tokens. The same optional fused neighbours as
+// Tokens are staged eight at a time through shared memory; the read-out's sum over k rows is
+// finished across the 8 row groups once per eight tokens. The same optional fused neighbours as
 // the single-token step (GlaFusion): ReLU on q/k, gate logits -> log-decay, per-head RMS norm.
 #include <math.h>
 
@@ -30,7 +30,7 @@ __device__ __forceinline__ float scan_from_f32<float>(float x) { return x; }
 template <>
 __device__ __forceinline__ __nv_bfloat16 scan_from_f32<__nv_bfloat16>(float x) { return __float2bfloat16_rn(x); }
 
-constexpr int kScanTokens = 4;   // tokens staged per round
+constexpr int kScanTokens = 8;   // tokens staged per round
 
 template <typename T, typename TO, int D>
 __global__ void __launch_bounds__(256)
@@ -55,14 +55,14 @@ gla_scan_kernel(const T* __restrict__ q, const T* __restrict__ k, const T* __res
   const int tid = threadIdx.x;
   const int c4 = tid % TPR, r0 = tid / TPR;
 
-  // Within a round of up to four tokens the decays are factored out of the state: with
+  // Within a round of up to eight tokens the decays are factored out of the state: with
   // G_t[r] = g_1[r] + ... + g_t[r] (per key row r) and St = diag(exp(-G_t)) S_t,
   //     St_t = St_(t-1) + (k_t exp(-G_t)) v_t^T ,   o_t = (q_t scale exp(G_t)) . St_t ,
   // and the true state comes back at the end of the round as diag(exp(G_R)) St_R: two fused
   // multiply-adds per state element and token instead of three operations. A row whose decay
   // within a round is too strong for that (exp(-G) would leave fp32 range; gate logits far below
   // -500) makes the whole CTA keep the plain recurrence for that round.
-  __shared__ float s_q[kScanTokens][D], s_k[kScanTokens][D], s_d[kScanTokens][D];
+  __shared__ float s_q[kScanTokens][D], s_k[kScanTokens][D];
   __shared__ float s_end[D];        // what the row is multiplied by at the end of the round
   __shared__ int s_plain[1];        // 1: this round runs the plain recurrence
   __shared__ float4 s_v[kScanTokens][TPR];
@@ -80,7 +80,7 @@ gla_scan_kernel(const T* __restrict__ q, const T* __restrict__ k, const T* __res
   }
 
   // The inputs of a round are fetched into registers one round ahead (thread -> key row d = tid % D
-  // and the tokens tt = tid / D, tid / D + 256 / D, ...; every thread also takes the row's four gate
+  // and the tokens tt = tid / D, tid / D + 256 / D, ...; every thread also takes the row's eight gate
   // values, to sum the log-decays itself), so that their latency hides behind the previous round.
   constexpr int TSTEP = 256 / D;           // 2 for D = 128, 4 for D = 64
   constexpr int TPT = kScanTokens / TSTEP; // tokens per thread and round
@@ -127,7 +127,6 @@ gla_scan_kernel(const T* __restrict__ q, const T* __restrict__ k, const T* __res
           float qv = scan_to_f32(pq[tt / TSTEP]);
           float kv = scan_to_f32(pk[tt / TSTEP]);
           if (fu.relu_qk) { qv = fmaxf(qv, 0.f); kv = fmaxf(kv, 0.f); }
-          s_d[tt][sd] = __expf(gl[tt]);                                // used by plain rounds only
           s_k[tt][sd] = plain ? kv : kv * __expf(-Gt);
           s_q[tt][sd] = plain ? qv * scale : qv * scale * __expf(Gt);
           reinterpret_cast<float*>(&s_v[tt][0])[sd] = scan_to_f32(pv[tt / TSTEP]);
@@ -167,7 +166,9 @@ gla_scan_kernel(const T* __restrict__ q, const T* __restrict__ k, const T* __res
 #pragma unroll
         for (int i = 0; i < RPT; ++i) {
           const int r = r0 + i * GROUPS;
-          const float d = s_d[tt][r], kk = s_k[tt][r], qq = s_q[tt][r];
+          // (rare path: the decay is recomputed from the gate instead of being staged)
+          const float d = expf(gla_gate<T>(scan_to_f32(g[((int64_t)(tb + tt) * Hkv + hk) * D + r]), fu));
+          const float kk = s_k[tt][r], qq = s_q[tt][r];
           S[i].x = fmaf(d, S[i].x, kk * vv.x);
           S[i].y = fmaf(d, S[i].y, kk * vv.y);
           S[i].z = fmaf(d, S[i].z, kk * vv.z);
