@@ -301,6 +301,26 @@ int sbk_swa_prefill(const void* q, int64_t q_tok_stride, const void* k_cache, co
                     int32_t* status, void* stream);
 
 /*
+ * The same attention over K/V that are NOT in a paged cache but passed as tensors: the prompt run
+ * of MetaAttentionImpl.forward without block tables (vllm_hymeta/attention/meta_attention.py:833-884:
+ * metatoken_flash_attn_varlen_func(q1=query, k1=key, v1=value, cu_seqlens_q, cu_seqlens_k, causal,
+ * window_size)), which is also what the engine's memory-profiling run executes.
+ *
+ *  key, value   [n_kv_tokens, kvh, D] bf16, `kv_tok_stride` elements between tokens (>= kvh*D: they
+ *               may be column slices of one projection output); 16-byte aligned
+ *  k_start_loc  [n_seqs+1] int32: sequence s owns keys k_start_loc[s] .. k_start_loc[s+1]-1; its last
+ *               query sees its last key (queries are aligned to the end of the keys, as flash-attn's
+ *               causal mask does when a sequence has more keys than queries)
+ *  q, out       as in sbk_swa_prefill, but 16-byte aligned with token strides multiples of 8 elements
+ *               (tcgen05 kernel only)
+ */
+int sbk_swa_prefill_dense(const void* q, int64_t q_tok_stride, const void* key, const void* value,
+                          int64_t kv_tok_stride, int64_t n_kv_tokens, const int32_t* query_start_loc,
+                          const int32_t* k_start_loc, int n_seqs, int max_query_len, int H, int kvh, int D,
+                          int window_left, float scale, void* out, int64_t out_tok_stride,
+                          const void* key2, const void* value2, int num_meta, int32_t* status, void* stream);
+
+/*
  * GLA scan over a run of tokens per sequence with state carry (prefill and chunked prefill):
  * for each sequence the state is read once, advanced token by token exactly as sbk_gla_step
  * would, and written back once. Stands in for the per-sequence loop of

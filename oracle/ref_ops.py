@@ -363,3 +363,40 @@ class StepPlannerRef:
                     self.ring.append(self.table[b][i])
                 self.table[b][i] = -1
             self.lens[b] = 0
+
+
+def swa_prefill_dense_ref(q: torch.Tensor, key: torch.Tensor, value: torch.Tensor, query_start_loc: List[int],
+                          k_start_loc: List[int], window_left: int, scale: float,
+                          key2: Optional[torch.Tensor] = None, value2: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """The prompt run without block tables (vllm_hymeta/attention/meta_attention.py:843-884:
+    varlen attention of q over the prompt's own key/value, causal, window (window_left, 0)), in
+    fp32: query i of a sequence with n_q queries and n_k keys sits at key position n_k - n_q + i
+    (flash-attn aligns the causal mask to the end of the keys) and sees keys
+    [position - window_left, position] plus the sink keys key2/value2 if given.
+    q [T, H, D]; key, value [Tk, kvh, D] -> [T, H, D] fp32."""
+    T, H, D = q.shape
+    kvh = key.shape[1]
+    out = torch.zeros(T, H, D)
+    for s in range(len(query_start_loc) - 1):
+        q0, q1 = query_start_loc[s], query_start_loc[s + 1]
+        k0, k1 = k_start_loc[s], k_start_loc[s + 1]
+        n_q, n_k = q1 - q0, k1 - k0
+        ks = repeat_kv(key[k0:k1].float().transpose(0, 1), H // kvh)       # [H, n_k, D]
+        vs = repeat_kv(value[k0:k1].float().transpose(0, 1), H // kvh)
+        sc = torch.einsum("ihd,hnd->hin", q[q0:q1].float(), ks) * scale       # [H, n_q, n_k]
+        pos = (n_k - n_q) + torch.arange(n_q)[:, None]
+        kp = torch.arange(n_k)[None, :]
+        ok = kp <= pos
+        if window_left >= 0:
+            ok &= kp >= pos - window_left
+        sc = sc.masked_fill(~ok[None], float("-inf"))
+        if key2 is not None:
+            k2 = repeat_kv(key2.float().transpose(0, 1), H // kvh)
+            v2 = repeat_kv(value2.float().transpose(0, 1), H // kvh)
+            s2 = torch.einsum("ihd,hnd->hin", q[q0:q1].float(), k2) * scale
+            p = torch.softmax(torch.cat([s2, sc], dim=-1), dim=-1)
+            o = torch.einsum("hin,hnd->ihd", p[..., :k2.shape[1]], v2) + torch.einsum("hin,hnd->ihd", p[..., k2.shape[1]:], vs)
+        else:
+            o = torch.einsum("hin,hnd->ihd", torch.softmax(sc, dim=-1), vs)
+        out[q0:q1] = o
+    return out

@@ -503,17 +503,28 @@ class MetaAttentionImpl:
         window_left = self.sliding_window[0]
 
         if prefill_meta := attn_metadata.prefill_metadata:
-            if (kv_cache.numel() == 0 or prefill_meta.block_tables is None
-                    or prefill_meta.block_tables.numel() == 0):
-                raise NotImplementedError(
-                    "prefill over K/V that is not reachable through block tables (profile run or "
-                    "un-chunked first prompt) has no kernel on this path; schedule prompts with "
-                    "chunked prefill so that their block tables are passed")
-            # windowed attention of the prompt tokens over the paged cache (their own K/V included:
-            # the append above has run), 16 queries and one kv group per CTA
             pq = prefill_query if prefill_query.stride()[1:] == (D, 1) else prefill_query.contiguous()
             po = out3[:num_prefill_tokens]
             tmp = po if po.stride()[1:] == (D, 1) else torch.empty_like(po, memory_format=torch.contiguous_format)
+            if (kv_cache.numel() == 0 or prefill_meta.block_tables is None
+                    or prefill_meta.block_tables.numel() == 0):
+                # prompt run without block tables (the un-chunked first prompt, the memory-profiling
+                # run): q and k are the prompt itself and have the same lengths (reference :843-884)
+                if key is None or value is None:
+                    raise ValueError("the prompt run without block tables attends over key/value; they are required")
+                n_kv = num_prefill_tokens
+                qsl = prefill_meta.query_start_loc.to(torch.int32).contiguous()
+                ksl = qsl if prefill_meta.seq_start_loc is None else prefill_meta.seq_start_loc.to(torch.int32).contiguous()
+                ops.swa_prefill_dense(pq, key.view(-1, self.num_kv_heads, D)[:n_kv],
+                                      value.view(-1, self.num_kv_heads, D)[:n_kv], qsl, ksl,
+                                      prefill_meta.max_query_len, window_left=window_left, scale=self.scale,
+                                      out=tmp, key2=key2, value2=value2, status=self._status)
+                if tmp is not po:
+                    po.copy_(tmp)
+                prefill_meta = None
+        if prefill_meta:
+            # windowed attention of the prompt tokens over the paged cache (their own K/V included:
+            # the append above has run), 16 queries and one kv group per CTA
             ops.swa_prefill(pq, kv_cache[0], kv_cache[1], prefill_meta.block_tables.contiguous(),
                             prefill_meta.query_start_loc.to(torch.int32).contiguous(),
                             prefill_meta.context_lens_tensor.to(torch.int32).contiguous(),

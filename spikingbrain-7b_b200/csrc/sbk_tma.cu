@@ -25,7 +25,7 @@ static EncodeTiledFn encode_fn() {
 static bool encode_map(CUtensorMap* m, const MapKey& k, bool tile_copy) {
   EncodeTiledFn fn = encode_fn();
   if (!fn) return false;
-  const cuuint64_t row_bytes = (cuuint64_t)k.kvh * 256;
+  const cuuint64_t row_bytes = k.tok_stride ? (cuuint64_t)k.tok_stride : (cuuint64_t)k.kvh * 256;
   cuuint64_t dim[4], stride[3];
   cuuint32_t box[4], estr[4] = {1, 1, 1, 1};
   dim[0] = 64; dim[3] = (cuuint64_t)k.num_blocks;

@@ -7,7 +7,9 @@
 
 namespace sbk {
 
-// A cache [num_blocks][block][kvh][128] bf16 seen as 64-element (128-byte) rows.
+// A cache [num_blocks][block][kvh][128] bf16 seen as 64-element (128-byte) rows. (A dense
+// [T][kvh][128] tensor, possibly a strided view of a wider row, is the same thing with one block of T
+// tokens and its own token stride; tokens past T read as zeros.)
 //   tile copies: dims (64, token in block, 128-byte row of a token, block) -- the token stride
 //                (kvh*256 B) comes BEFORE the row stride (128 B), so a box of (64, 16, box_rows, 1)
 //                lands in shared memory as [row][token][128 B];
@@ -16,10 +18,11 @@ namespace sbk {
 // Both use the 128-byte swizzle (16-byte chunk index XOR token & 7 for tiles on 1 KiB boundaries).
 struct MapKey {
   const void* base; int kvh; int64_t num_blocks; int block_size; int64_t block_stride;
-  int box_rows;   // 128-byte rows per tile copy: 2*kvh (all kv heads) or 2 (one kv head)
+  int box_rows;   // 128-byte rows per tile copy: 2*kvh (all kv heads), 2 (one kv head) or 1 (64 dims)
+  int64_t tok_stride = 0;   // bytes between tokens; 0: kvh*256 (rows of a block contiguous)
   bool operator==(const MapKey& o) const {
     return base == o.base && kvh == o.kvh && num_blocks == o.num_blocks && block_size == o.block_size &&
-           block_stride == o.block_stride && box_rows == o.box_rows;
+           block_stride == o.block_stride && box_rows == o.box_rows && tok_stride == o.tok_stride;
   }
 };
 

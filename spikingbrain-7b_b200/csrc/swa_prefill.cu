@@ -361,6 +361,7 @@ extern "C" int sbk_swa_prefill(const void* q, int64_t q_tok_stride, const void* 
     T.block_size = block_size; T.window_left = window_left; T.scale_log2 = scale * kLog2e;
     T.out = (__nv_bfloat16*)out; T.out_tok_stride = out_tok_stride; T.status = status;
     T.n_meta_chunks = 0;
+    T.k_start_loc = nullptr;
     if (num_meta > 0) {
       const int64_t mstride = (int64_t)16 * kvh * D * 2;
       if (!get_map(&mk2, MapKey{key2, kvh, num_meta / 16, 16, mstride, 1}, &tc_mode) ||
@@ -413,4 +414,74 @@ extern "C" int sbk_swa_prefill(const void* q, int64_t q_tok_stride, const void* 
   dim3 grid(n_seqs * tiles, kvh);
   swa_prefill_kernel<<<grid, (P.G + 1) * 32, kSmemBytes, (cudaStream_t)stream>>>(P, map_k, map_v, map_k2, map_v2);
   return check_launch("sbk_swa_prefill");
+}
+
+extern "C" int sbk_swa_prefill_dense(const void* q, int64_t q_tok_stride, const void* key, const void* value,
+                                     int64_t kv_tok_stride, int64_t n_kv_tokens, const int32_t* query_start_loc,
+                                     const int32_t* k_start_loc, int n_seqs, int max_query_len, int H, int kvh,
+                                     int D, int window_left, float scale, void* out, int64_t out_tok_stride,
+                                     const void* key2, const void* value2, int num_meta, int32_t* status,
+                                     void* stream) {
+  using namespace sbk;
+  using namespace sbk::prefill;
+  if (num_meta < 0 || num_meta % 16 != 0 || (num_meta > 0 && (!key2 || !value2 || !aligned16(key2) || !aligned16(value2)))) {
+    set_error("sbk_swa_prefill_dense: sink tokens need 16-byte aligned key2/value2 and a count that is a multiple of 16 (got %d)",
+              num_meta);
+    return SBK_E_ARG;
+  }
+  if (n_seqs < 0 || max_query_len < 0 || n_kv_tokens < 0 || H <= 0 || kvh <= 0 || H % kvh != 0) {
+    set_error("sbk_swa_prefill_dense: bad sizes n_seqs=%d H=%d kvh=%d", n_seqs, H, kvh);
+    return SBK_E_ARG;
+  }
+  if (D != kD || H / kvh > 8) {
+    set_error("sbk_swa_prefill_dense: unsupported shape D=%d H/kvh=%d (need D=128, at most 8 query heads per kv head)",
+              D, H / kvh);
+    return SBK_E_ARG;
+  }
+  if (n_seqs == 0 || max_query_len == 0) return SBK_OK;
+  if (!q || !key || !value || !query_start_loc || !k_start_loc || !out || n_kv_tokens == 0) {
+    set_error("sbk_swa_prefill_dense: null pointer or no key tokens");
+    return SBK_E_ARG;
+  }
+  if (!aligned16(q) || !aligned16(out) || q_tok_stride % 8 || out_tok_stride % 8 || !aligned16(key) ||
+      !aligned16(value) || kv_tok_stride % 8 || kv_tok_stride < (int64_t)kvh * D) {
+    set_error("sbk_swa_prefill_dense: q, out, key, value must be 16-byte aligned with token strides that are "
+              "multiples of 8 elements (key/value at least kvh*D)");
+    return SBK_E_ALIGN;
+  }
+  const int tiles = (max_query_len + kBQ - 1) / kBQ;
+  if ((int64_t)n_seqs * tiles > 2147483647LL || kvh > 65535) {
+    set_error("sbk_swa_prefill_dense: grid too large");
+    return SBK_E_ARG;
+  }
+  // the tensors as one block of n_kv_tokens tokens with their own token stride
+  CUtensorMap mk, mv, mk2, mv2;
+  int tc_mode = 0;
+  const int64_t bstride = n_kv_tokens * kv_tok_stride * 2;
+  if (n_kv_tokens > 2147483647LL ||
+      !get_map(&mk, MapKey{key, kvh, 1, (int)n_kv_tokens, bstride, 1, kv_tok_stride * 2}, &tc_mode) ||
+      !get_map(&mv, MapKey{value, kvh, 1, (int)n_kv_tokens, bstride, 1, kv_tok_stride * 2}, &tc_mode)) {
+    set_error("sbk_swa_prefill_dense: cuTensorMapEncodeTiled rejected the key/value geometry");
+    return SBK_E_ARG;
+  }
+  mk2 = mk; mv2 = mv;
+  prefill_tc::Params T;
+  T.q = (const __nv_bfloat16*)q; T.q_tok_stride = q_tok_stride;
+  T.block_tables = nullptr; T.max_blocks = 0;
+  T.query_start_loc = query_start_loc; T.context_lens = nullptr; T.k_start_loc = k_start_loc;
+  T.n_seqs = n_seqs; T.tiles_per_seq = tiles; T.H = H; T.G = H / kvh; T.num_blocks = 1;
+  T.block_size = 16; T.window_left = window_left; T.scale_log2 = scale * kLog2e;
+  T.out = (__nv_bfloat16*)out; T.out_tok_stride = out_tok_stride; T.status = status;
+  T.n_meta_chunks = 0;
+  if (num_meta > 0) {
+    const int64_t mstride = (int64_t)16 * kvh * D * 2;
+    if (!get_map(&mk2, MapKey{key2, kvh, num_meta / 16, 16, mstride, 1}, &tc_mode) ||
+        !get_map(&mv2, MapKey{value2, kvh, num_meta / 16, 16, mstride, 1}, &tc_mode)) {
+      set_error("sbk_swa_prefill_dense: cuTensorMapEncodeTiled rejected the sink-token tensors");
+      return SBK_E_ARG;
+    }
+    T.n_meta_chunks = num_meta / 16;
+  }
+  T.tile_copy = tc_mode;
+  return prefill_tc::launch(T, kvh, mk, mv, mk2, mv2, (cudaStream_t)stream);
 }

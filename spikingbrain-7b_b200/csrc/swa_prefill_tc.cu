@@ -206,7 +206,10 @@ swa_prefill_tc_kernel(const Params P, const __grid_constant__ CUtensorMap map_k,
   const int n_q = P.query_start_loc[s + 1] - qs;
   if (j * kBQ >= n_q) return;   // whole CTA, before anything is allocated
   const int nq_tile = n_q - j * kBQ < kBQ ? n_q - j * kBQ : kBQ;
-  const int p0 = P.context_lens[s] + j * kBQ;                 // position of the tile's first query
+  const bool dense = P.k_start_loc != nullptr;
+  const int k_start = dense ? P.k_start_loc[s] : 0;
+  const int ctx = dense ? (P.k_start_loc[s + 1] - k_start) - n_q : P.context_lens[s];
+  const int p0 = ctx + j * kBQ;                               // position of the tile's first query
   const int key_lo = P.window_left < 0 ? 0 : (p0 - P.window_left > 0 ? p0 - P.window_left : 0);
   const int key_hi = p0 + nq_tile;                            // exclusive
   const int c_lo = key_lo / kChunk, c_hi = (key_hi - 1) / kChunk;
@@ -246,7 +249,7 @@ swa_prefill_tc_kernel(const Params P, const __grid_constant__ CUtensorMap map_k,
   if (warp == kSoftmaxWarps || warp == kSoftmaxWarps + 1) {
     // ===== TMA producers: one warp per ring (K, V), so that a K tile never queues behind a V slot =====
     const int kind = warp - kSoftmaxWarps;   // 0: K ring, 1: V ring
-    const int32_t* table = P.block_tables + (int64_t)s * P.max_blocks;
+    const int32_t* table = dense ? nullptr : P.block_tables + (int64_t)s * P.max_blocks;
     int64_t pb_lane = -1;
     int batch_c0 = 0;
     bool ok = true;
@@ -258,7 +261,7 @@ swa_prefill_tc_kernel(const Params P, const __grid_constant__ CUtensorMap map_k,
         batch_c0 = c0;
         const int c = c0 + lane;
         const int lb = (c * kChunk) / P.block_size;
-        pb_lane = (c <= c_hi && lb < P.max_blocks) ? (int64_t)table[lb] : -1;
+        pb_lane = dense ? 0 : ((c <= c_hi && lb < P.max_blocks) ? (int64_t)table[lb] : -1);
       }
       const int slot = t % kStages, use = t / kStages;
       // lane -> one copy of 2 KiB: chunk (lane >> 1), 64-dim half (lane & 1); lanes 16-31 idle
@@ -269,10 +272,10 @@ swa_prefill_tc_kernel(const Params P, const __grid_constant__ CUtensorMap map_k,
       src_lane = src_lane < 0 ? 0 : (src_lane > 31 ? 31 : src_lane);
       const int64_t pb_tab = __shfl_sync(0xffffffffu, pb_lane, src_lane);
       const int64_t pb = meta ? (int64_t)c : pb_tab;           // the sink tensors are their own block table
-      bool bad = !meta && active && (pb < 0 || pb >= P.num_blocks);
+      bool bad = !meta && !dense && active && (pb < 0 || pb >= P.num_blocks);
       bad = __any_sync(0xffffffffu, bad);
       const int nvalid = c_end - c0 + 1 < kTileChunks ? c_end - c0 + 1 : kTileChunks;
-      const int tin = meta ? 0 : (c * kChunk) % P.block_size;
+      const int tin = meta ? 0 : (dense ? k_start + c * kChunk : (c * kChunk) % P.block_size);
       const uint32_t dst = sbase + (kind ? kVOff : kKOff) + slot * kOperandBytes + half * kPanelBytes + i * 2048;
       const CUtensorMap* map = meta ? (kind ? &map_v2 : &map_k2) : (kind ? &map_v : &map_k);
       const uint32_t bar_e = (kind ? bar_ve : bar_ke) + 8 * slot, bar_f = (kind ? bar_vf : bar_kf) + 8 * slot;

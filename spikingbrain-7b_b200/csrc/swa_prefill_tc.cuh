@@ -16,6 +16,9 @@ struct Params {
   __nv_bfloat16* out; int64_t out_tok_stride;
   int32_t* status; int tile_copy;
   int n_meta_chunks;   // 16-token chunks of always-visible sink keys, streamed ahead of the window
+  // dense mode: K/V are not in a paged cache but tensors [T, kvh, D] (the maps see them as one block of
+  // T tokens); sequence s owns keys k_start_loc[s] .. k_start_loc[s+1]-1 and its last query sees its last key
+  const int32_t* k_start_loc;   // NULL: paged mode
 };
 
 // Tensor maps with ONE 128-byte row (64 dims of one kv head) per copy: box_rows == 1.

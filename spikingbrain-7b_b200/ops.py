@@ -550,3 +550,48 @@ def release_rows(rows: torch.Tensor, seq_lens: torch.Tensor, block_tables: torch
     _abi.check("sbk_release_rows", rc)
     global LAUNCHES
     LAUNCHES += 1 if rows.numel() else 0
+
+
+def swa_prefill_dense(q: torch.Tensor, key: torch.Tensor, value: torch.Tensor, query_start_loc: torch.Tensor,
+                      k_start_loc: torch.Tensor, max_query_len: int, *, window_left: int,
+                      scale: Optional[float] = None, out: Optional[torch.Tensor] = None,
+                      key2: Optional[torch.Tensor] = None, value2: Optional[torch.Tensor] = None,
+                      status: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """Sliding-window causal attention of runs of query tokens over K/V given as tensors
+    (key/value [Tk, kvh, D] bf16, possibly strided views of a wider projection output) instead of
+    a paged cache: the prompt run without block tables. Sequence s owns query rows
+    query_start_loc[s]:query_start_loc[s+1] and key rows k_start_loc[s]:k_start_loc[s+1]; its last
+    query sees its last key."""
+    _need_cuda(q, key, value, query_start_loc, k_start_loc, out, status)
+    if q.dim() != 3 or key.dim() != 3 or key.shape != value.shape or q.shape[2] != key.shape[2]:
+        raise ValueError("q must be [T, H, D] and key/value equal-shaped [Tk, kvh, D]")
+    T, H, d = q.shape
+    Tk, kvh, _ = key.shape
+    if any(t.dtype != torch.bfloat16 for t in (q, key, value)):
+        raise ValueError("q, key, value must be bf16")
+    for t in (key, value):
+        if Tk and ((d > 1 and t.stride(2) != 1) or (kvh > 1 and t.stride(1) != d)):
+            raise ValueError("the heads of key/value must be contiguous")
+    if Tk > 1 and key.stride(0) != value.stride(0):
+        raise ValueError("key and value must share one token stride")
+    if T and q.stride()[1:] != (d, 1):
+        raise ValueError("the heads of q must be contiguous")
+    n_seqs = query_start_loc.numel() - 1
+    _i32(query_start_loc, "query_start_loc")
+    _i32(k_start_loc, "k_start_loc", n_seqs + 1)
+    if out is None:
+        out = torch.empty((T, H, d), dtype=torch.bfloat16, device=q.device)
+    elif out.shape != (T, H, d) or out.dtype != torch.bfloat16 or (T and out.stride()[1:] != (d, 1)):
+        raise ValueError("out must be bf16 [T, H, D] with contiguous heads")
+    if scale is None:
+        scale = d ** -0.5
+    n_meta = _check_meta(key2, value2, kvh, d)
+    rc = _abi.lib.sbk_swa_prefill_dense(
+        _ptr(q), q.stride(0) if T else H * d, _ptr(key), _ptr(value), key.stride(0) if Tk > 1 else kvh * d, Tk,
+        _ptr(query_start_loc), _ptr(k_start_loc), n_seqs, int(max_query_len), H, kvh, d, window_left,
+        float(scale), _ptr(out), out.stride(0) if T else H * d, _ptr(key2), _ptr(value2), n_meta, _ptr(status),
+        _stream())
+    _abi.check("sbk_swa_prefill_dense", rc)
+    global LAUNCHES
+    LAUNCHES += 1 if (T and n_seqs) else 0
+    return out

@@ -382,6 +382,37 @@ def test_swa_prefill_long_chunk_at_model_shapes(ops, prefill_kernel):
     _prefill_case(ops, [6000], [2048], wl=4096, H=28, kvh=4, bs=16, seed=63)
 
 
+@pytest.mark.parametrize("wl,n_meta", [(63, 0), (-1, 0), (300, 48), (0, 0)])
+def test_swa_prefill_dense_matches_oracle(ops, wl, n_meta):
+    """K/V as tensors instead of a paged cache: ragged sequences, more keys than queries in some
+    (the queries are the tail), keys and values as strided column slices, optional sink keys."""
+    H, kvh, D = 28, 4, 128
+    n_k = [300, 16, 1, 129, 77]
+    n_q = [300, 5, 1, 129, 20]
+    ksl, qsl = [0], [0]
+    for a, b in zip(n_k, n_q):
+        ksl.append(ksl[-1] + a); qsl.append(qsl[-1] + b)
+    g = torch.Generator().manual_seed(66)
+    q = (torch.randn(qsl[-1], H, D, generator=g) / math.sqrt(D)).bfloat16()
+    kvbuf = (torch.randn(ksl[-1], 2 * kvh * D + 64, generator=g) / math.sqrt(D)).bfloat16()
+    key = kvbuf[:, :kvh * D].view(-1, kvh, D)
+    value = kvbuf[:, kvh * D:2 * kvh * D].view(-1, kvh, D)
+    k2 = (torch.randn(n_meta, kvh, D, generator=g) / math.sqrt(D)).bfloat16() if n_meta else None
+    v2 = (torch.randn(n_meta, kvh, D, generator=g) / math.sqrt(D)).bfloat16() if n_meta else None
+    want = ref_ops.swa_prefill_dense_ref(q, key, value, qsl, ksl, wl, D ** -0.5, k2, v2).bfloat16().float()
+    kvd = kvbuf.to(DEV)
+    st = _status()
+    out = ops.swa_prefill_dense(q.to(DEV), kvd[:, :kvh * D].view(-1, kvh, D), kvd[:, kvh * D:2 * kvh * D].view(-1, kvh, D),
+                                torch.tensor(qsl, dtype=torch.int32, device=DEV),
+                                torch.tensor(ksl, dtype=torch.int32, device=DEV), max(n_q), window_left=wl,
+                                key2=None if k2 is None else k2.to(DEV), value2=None if v2 is None else v2.to(DEV),
+                                status=st)
+    assert st.item() == 0
+    o = out.float().cpu()
+    assert torch.isfinite(o).all()
+    assert float((o - want).abs().max()) <= ATTN_MAX_ABS and mean_rel(o, want) <= ATTN_MEAN_REL
+
+
 def test_swa_prefill_unaligned_views_take_the_vector_free_kernel(ops):
     """q and out as views whose rows start 4 bytes off a 16-byte boundary: the tcgen05 kernel moves
     them as 16-byte vectors, so the entry point must fall back to the mma.sync kernel by itself."""

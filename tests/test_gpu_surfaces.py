@@ -342,8 +342,57 @@ def test_backend_forward_unsupported_paths_raise(pkg):
                                block_tables=torch.zeros(1, 0, dtype=torch.int32, device=DEV), use_cuda_graph=False,
                                max_query_len=2, query_start_loc=torch.tensor([0, 2], dtype=torch.int32, device=DEV),
                                seq_start_loc=torch.tensor([0, 2], dtype=torch.int32, device=DEV))
-    with pytest.raises(NotImplementedError):       # a prompt whose K/V cannot be reached through tables
-        impl.forward(None, q, kx, kx, None, None, None, kv, pm, output=torch.empty_like(q))
+    # a prompt whose K/V cannot be reached through tables attends over the key/value tensors themselves
+    out = torch.empty_like(q)
+    impl.forward(None, q, kx, kx, None, None, None, kv, pm, output=out)
+    want = ref_ops.swa_prefill_dense_ref(q.view(2, 28, 128).cpu(), kx.view(2, 4, 128).cpu(), kx.view(2, 4, 128).cpu(),
+                                         [0, 2], [0, 2], impl.sliding_window[0], impl.scale)
+    assert float((out.view(2, 28, 128).float().cpu() - want).abs().max()) <= 2e-2
+
+
+def test_backend_prompt_run_without_block_tables(pkg):
+    """The un-chunked first prompt (and the profiling run, kv_cache.numel() == 0): q, k, v are column
+    slices of one projection output; attention over the prompt's own K/V, K/V also appended."""
+    from spikingbrain_7b_b200.backend import MetaAttentionBackend, MetaAttentionImpl, MetaAttentionMetadata
+    H, kvh, D, bs, sw = 28, 4, 128, 16, 129
+    lens = [200, 1, 77, 350]
+    T = sum(lens)
+    g = torch.Generator().manual_seed(80)
+    qkv = (torch.randn(T, (H + 2 * kvh) * D, generator=g) / math.sqrt(D)).bfloat16().to(DEV)
+    q, k, v = qkv[:, :H * D], qkv[:, H * D:(H + kvh) * D], qkv[:, (H + kvh) * D:]
+    qsl = [0]
+    for n in lens:
+        qsl.append(qsl[-1] + n)
+    nb = sum((n + bs - 1) // bs for n in lens) + 2
+    perm = torch.randperm(nb, generator=g).tolist()
+    slots, used = [], 0
+    for n in lens:
+        blocks = perm[used:used + (n + bs - 1) // bs]; used += len(blocks)
+        slots += [blocks[t // bs] * bs + t % bs for t in range(n)]
+    impl = MetaAttentionImpl(H, D, D ** -0.5, kvh, None, sw, "auto")
+    wl = impl.sliding_window[0]
+    want = ref_ops.swa_prefill_dense_ref(q.view(T, H, D).cpu(), k.reshape(T, kvh, D).cpu(), v.reshape(T, kvh, D).cpu(),
+                                         qsl, qsl, wl, D ** -0.5).bfloat16().float()
+    for kv in (torch.zeros(MetaAttentionBackend.get_kv_cache_shape(nb, bs, kvh, D), dtype=torch.bfloat16, device=DEV),
+               torch.empty(0, dtype=torch.bfloat16, device=DEV)):
+        md = MetaAttentionMetadata(num_prefills=len(lens), num_prefill_tokens=T, num_decode_tokens=0,
+                                   slot_mapping=torch.tensor(slots, device=DEV), seq_lens=lens,
+                                   seq_lens_tensor=torch.tensor(lens, dtype=torch.int32, device=DEV),
+                                   max_prefill_seq_len=max(lens), max_decode_seq_len=0,
+                                   context_lens_tensor=torch.zeros(len(lens), dtype=torch.int32, device=DEV),
+                                   block_tables=torch.zeros(len(lens), 0, dtype=torch.int32, device=DEV),
+                                   use_cuda_graph=False, max_query_len=max(lens),
+                                   query_start_loc=torch.tensor(qsl, dtype=torch.int32, device=DEV),
+                                   seq_start_loc=torch.tensor(qsl, dtype=torch.int32, device=DEV))
+        out = torch.empty(T, H * D, dtype=torch.bfloat16, device=DEV)
+        impl.forward(None, q, k, v, None, None, None, kv, md, output=out)
+        assert impl.status() == 0
+        o = out.view(T, H, D).float().cpu()
+        assert float((o - want).abs().max()) <= 2e-2 and mean_rel(o, want) <= 1e-3
+        if kv.numel():   # the prompt's K/V went into the cache as well
+            flat = kv.view(2, nb * bs, kvh, D)
+            assert torch.equal(flat[0, torch.tensor(slots, device=DEV)], k.reshape(T, kvh, D))
+            assert torch.equal(flat[1, torch.tensor(slots, device=DEV)], v.reshape(T, kvh, D))
 
 
 # ------------------------------------------------------- fused neighbours through the surfaces
