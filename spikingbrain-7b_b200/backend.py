@@ -535,7 +535,22 @@ class MetaAttentionImpl:
 
         if decode_meta := attn_metadata.decode_metadata:
             if decode_meta.max_decode_query_len is not None and decode_meta.max_decode_query_len > 1:
-                raise NotImplementedError("multi-token (varlen) decode has no kernel on this path")
+                # several query tokens per sequence (reference :924-953, varlen attention over the
+                # cache through the block tables): the prefill kernel, each sequence's queries being
+                # the tail of its seq_len tokens
+                if decode_meta.query_start_loc is None:
+                    raise ValueError("multi-token decode needs decode_metadata.query_start_loc")
+                dq = decode_query if decode_query.stride()[1:] == (D, 1) else decode_query.contiguous()
+                do = out3[num_prefill_tokens:]
+                dtmp = do if do.stride()[1:] == (D, 1) else torch.empty_like(do, memory_format=torch.contiguous_format)
+                dqsl = decode_meta.query_start_loc.to(torch.int32).contiguous()
+                ctx = (decode_meta.seq_lens_tensor.to(torch.int32) - (dqsl[1:] - dqsl[:-1])).contiguous()
+                ops.swa_prefill(dq, kv_cache[0], kv_cache[1], decode_meta.block_tables.contiguous(), dqsl, ctx,
+                                decode_meta.max_decode_query_len, window_left=window_left, scale=self.scale,
+                                out=dtmp, key2=key2, value2=value2, status=self._status)
+                if dtmp is not do:
+                    do.copy_(dtmp)
+                return output
             self._decode(decode_query, kv_cache, decode_meta.block_tables, decode_meta.seq_lens_tensor,
                          window_left, out3[num_prefill_tokens:], key2, value2)
         return output

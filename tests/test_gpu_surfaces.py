@@ -350,6 +350,55 @@ def test_backend_forward_unsupported_paths_raise(pkg):
     assert float((out.view(2, 28, 128).float().cpu() - want).abs().max()) <= 2e-2
 
 
+def test_backend_multi_token_decode_through_block_tables(pkg):
+    """max_decode_query_len > 1 (several new tokens per sequence, e.g. speculative decoding): every
+    query attends causally inside the window over the cache, its own K/V appended by the same call."""
+    from spikingbrain_7b_b200.backend import MetaAttentionBackend, MetaAttentionImpl, MetaAttentionMetadata
+    H, kvh, D, bs, sw = 28, 4, 128, 16, 65
+    ctx, new = [100, 7, 64], [3, 1, 5]
+    B, T = len(ctx), sum(new)
+    g = torch.Generator().manual_seed(81)
+    nb = 40
+    perm = torch.randperm(nb, generator=g).tolist()
+    tables = [perm[b * 10:(b + 1) * 10] for b in range(B)]
+    kv = torch.zeros(MetaAttentionBackend.get_kv_cache_shape(nb, bs, kvh, D), dtype=torch.bfloat16)
+    for b in range(B):
+        for t in range(ctx[b]):
+            kv[:, tables[b][t // bs], t % bs] = (torch.randn(2, kvh, D, generator=g) / math.sqrt(D)).bfloat16()
+    q = (torch.randn(T, H * D, generator=g) / math.sqrt(D)).bfloat16()
+    k = (torch.randn(T, kvh * D, generator=g) / math.sqrt(D)).bfloat16()
+    v = (torch.randn(T, kvh * D, generator=g) / math.sqrt(D)).bfloat16()
+    qsl, slots = [0], []
+    for b in range(B):
+        qsl.append(qsl[-1] + new[b])
+        slots += [tables[b][t // bs] * bs + t % bs for t in range(ctx[b], ctx[b] + new[b])]
+    lens = [c + n for c, n in zip(ctx, new)]
+    impl = MetaAttentionImpl(H, D, D ** -0.5, kvh, None, sw, "auto")
+    wl = impl.sliding_window[0]
+    md = MetaAttentionMetadata(num_prefills=0, num_prefill_tokens=0, num_decode_tokens=T,
+                               slot_mapping=torch.tensor(slots, device=DEV), seq_lens=lens,
+                               seq_lens_tensor=torch.tensor(lens, dtype=torch.int32, device=DEV),
+                               max_prefill_seq_len=0, max_decode_seq_len=max(lens), context_lens_tensor=None,
+                               block_tables=torch.tensor(tables, dtype=torch.int32, device=DEV), use_cuda_graph=False,
+                               max_query_len=max(new), max_decode_query_len=max(new),
+                               query_start_loc=torch.tensor(qsl, dtype=torch.int32, device=DEV),
+                               seq_start_loc=None)
+    kv_d = kv.to(DEV)
+    out = torch.empty(T, H * D, dtype=torch.bfloat16, device=DEV)
+    impl.forward(None, q.to(DEV), k.to(DEV), v.to(DEV), None, None, None, kv_d, md, output=out)
+    assert impl.status() == 0
+    ref_ops.paged_append(k.view(T, kvh, D), v.view(T, kvh, D), kv[0], kv[1], torch.tensor(slots))
+    assert torch.equal(kv_d.cpu(), kv)
+    table_t = torch.tensor(tables, dtype=torch.int32)
+    for b in range(B):
+        for i in range(new[b]):
+            pos = ctx[b] + i
+            ref = ref_ops.swa_paged_decode_ref(q[qsl[b] + i].view(1, H, D), kv[0], kv[1], table_t[b:b + 1], [pos + 1], wl,
+                                               D ** -0.5)[0].bfloat16().float()
+            got = out[qsl[b] + i].view(H, D).float().cpu()
+            assert float((got - ref).abs().max()) <= 2e-2, (b, i)
+
+
 def test_backend_prompt_run_without_block_tables(pkg):
     """The un-chunked first prompt (and the profiling run, kv_cache.numel() == 0): q, k, v are column
     slices of one projection output; attention over the prompt's own K/V, K/V also appended."""
