@@ -311,13 +311,16 @@ int sbk_swa_prefill(const void* q, int64_t q_tok_stride, const void* k_cache, co
  *  k_start_loc  [n_seqs+1] int32: sequence s owns keys k_start_loc[s] .. k_start_loc[s+1]-1; its last
  *               query sees its last key (queries are aligned to the end of the keys, as flash-attn's
  *               causal mask does when a sequence has more keys than queries)
+ *  causal       non-zero: as above. 0: every query sees every key of its sequence and the window is
+ *               ignored (the pass of the sink tokens' own queries over key2/value2,
+ *               fa_kernel_metatoken.py:262-276, which the reference runs with causal=False)
  *  q, out       as in sbk_swa_prefill, but 16-byte aligned with token strides multiples of 8 elements
  *               (tcgen05 kernel only)
  */
 int sbk_swa_prefill_dense(const void* q, int64_t q_tok_stride, const void* key, const void* value,
                           int64_t kv_tok_stride, int64_t n_kv_tokens, const int32_t* query_start_loc,
                           const int32_t* k_start_loc, int n_seqs, int max_query_len, int H, int kvh, int D,
-                          int window_left, float scale, void* out, int64_t out_tok_stride,
+                          int window_left, int causal, float scale, void* out, int64_t out_tok_stride,
                           const void* key2, const void* value2, int num_meta, int32_t* status, void* stream);
 
 /*

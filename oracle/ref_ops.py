@@ -367,12 +367,15 @@ class StepPlannerRef:
 
 def swa_prefill_dense_ref(q: torch.Tensor, key: torch.Tensor, value: torch.Tensor, query_start_loc: List[int],
                           k_start_loc: List[int], window_left: int, scale: float,
-                          key2: Optional[torch.Tensor] = None, value2: Optional[torch.Tensor] = None) -> torch.Tensor:
+                          key2: Optional[torch.Tensor] = None, value2: Optional[torch.Tensor] = None,
+                          causal: bool = True) -> torch.Tensor:
     """The prompt run without block tables (vllm_hymeta/attention/meta_attention.py:843-884:
     varlen attention of q over the prompt's own key/value, causal, window (window_left, 0)), in
     fp32: query i of a sequence with n_q queries and n_k keys sits at key position n_k - n_q + i
     (flash-attn aligns the causal mask to the end of the keys) and sees keys
-    [position - window_left, position] plus the sink keys key2/value2 if given.
+    [position - window_left, position] plus the sink keys key2/value2 if given. causal=False: every
+    query sees every key of its sequence (the pass of the sink tokens' own queries over key2/value2,
+    fa_kernel_metatoken.py:262-276).
     q [T, H, D]; key, value [Tk, kvh, D] -> [T, H, D] fp32."""
     T, H, D = q.shape
     kvh = key.shape[1]
@@ -386,9 +389,9 @@ def swa_prefill_dense_ref(q: torch.Tensor, key: torch.Tensor, value: torch.Tenso
         sc = torch.einsum("ihd,hnd->hin", q[q0:q1].float(), ks) * scale       # [H, n_q, n_k]
         pos = (n_k - n_q) + torch.arange(n_q)[:, None]
         kp = torch.arange(n_k)[None, :]
-        ok = kp <= pos
-        if window_left >= 0:
-            ok &= kp >= pos - window_left
+        ok = kp <= pos if causal else torch.ones(n_q, n_k, dtype=torch.bool)
+        if causal and window_left >= 0:
+            ok = ok & (kp >= pos - window_left)
         sc = sc.masked_fill(~ok[None], float("-inf"))
         if key2 is not None:
             k2 = repeat_kv(key2.float().transpose(0, 1), H // kvh)

@@ -60,7 +60,7 @@ SIGNATURES = {
         c_void_p]),
     "sbk_swa_prefill_dense": (c_int, [
         c_void_p, c_int64, c_void_p, c_void_p, c_int64, c_int64, c_void_p, c_void_p, c_int, c_int, c_int,
-        c_int, c_int, c_int, c_float, c_void_p, c_int64, c_void_p, c_void_p, c_int, c_void_p, c_void_p]),
+        c_int, c_int, c_int, c_int, c_float, c_void_p, c_int64, c_void_p, c_void_p, c_int, c_void_p, c_void_p]),
     "sbk_gla_step": (c_int, [
         c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int64, c_void_p, c_int, c_int,
         c_int, c_int, c_float, c_void_p, c_int, c_int, c_float, c_void_p, c_float, c_void_p,

@@ -462,10 +462,6 @@ class MetaAttentionImpl:
             assert (getattr(layer, "_k_scale_float", 1.0) == 1.0
                     and getattr(layer, "_v_scale_float", 1.0) == 1.0), (
                 "key/v_scale is only supported with an fp8 cache, which this path does not have")
-        if query2 is not None:
-            raise NotImplementedError(
-                "queries of the meta tokens themselves (the step that first computes them) have no kernel "
-                "on this path; pass their cached key2/value2 with query2=None")
         if (key2 is None) != (value2 is None):
             raise ValueError("key2 and value2 come together")
         if key2 is not None:
@@ -477,7 +473,28 @@ class MetaAttentionImpl:
         out3 = output.view(-1, H, D)
         if self._status is None or self._status.device != query.device:
             self._status = torch.zeros(1, dtype=torch.int32, device=query.device)
-
+        if query2 is not None:
+            # The step that first computes the meta (sink) tokens: their own queries attend over all of
+            # key2/value2, not causally (fa_kernel_metatoken.py:262-276), and their outputs come first
+            # in `output` (:279-280); everything else follows behind them.
+            if key2 is None:
+                raise ValueError("query2 needs key2/value2")
+            if attn_metadata.num_decode_tokens:
+                raise NotImplementedError("the meta tokens' own queries go with a prompt run, not with decode tokens "
+                                          "(the reference asserts the same)")
+            M = self.num_meta_tokens
+            q2 = query2.view(-1, H, D)
+            assert q2.shape[0] == M, "num_meta_tokens differs from query2"
+            if out3.shape[0] != query.shape[0] + M:
+                raise ValueError("with query2 the output holds num_meta_tokens rows ahead of the query tokens")
+            loc = torch.tensor([0, M], dtype=torch.int32, device=q2.device)
+            m_out = out3[:M]
+            m_tmp = m_out if m_out.stride()[1:] == (D, 1) else torch.empty_like(m_out, memory_format=torch.contiguous_format)
+            ops.swa_prefill_dense(q2 if q2.stride()[1:] == (D, 1) else q2.contiguous(), key2, value2, loc, loc, M,
+                                  window_left=-1, causal=False, scale=self.scale, out=m_tmp, status=self._status)
+            if m_tmp is not m_out:
+                m_out.copy_(m_tmp)
+            out3 = out3[M:]
         if (positions is None) != (cos_sin_cache is None):
             raise ValueError("positions and cos_sin_cache come together")
         if kv_cache.numel() > 0 and key is not None and value is not None:

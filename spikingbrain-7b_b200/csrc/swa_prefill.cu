@@ -362,6 +362,7 @@ extern "C" int sbk_swa_prefill(const void* q, int64_t q_tok_stride, const void* 
     T.out = (__nv_bfloat16*)out; T.out_tok_stride = out_tok_stride; T.status = status;
     T.n_meta_chunks = 0;
     T.k_start_loc = nullptr;
+    T.noncausal = 0;
     if (num_meta > 0) {
       const int64_t mstride = (int64_t)16 * kvh * D * 2;
       if (!get_map(&mk2, MapKey{key2, kvh, num_meta / 16, 16, mstride, 1}, &tc_mode) ||
@@ -419,9 +420,9 @@ extern "C" int sbk_swa_prefill(const void* q, int64_t q_tok_stride, const void* 
 extern "C" int sbk_swa_prefill_dense(const void* q, int64_t q_tok_stride, const void* key, const void* value,
                                      int64_t kv_tok_stride, int64_t n_kv_tokens, const int32_t* query_start_loc,
                                      const int32_t* k_start_loc, int n_seqs, int max_query_len, int H, int kvh,
-                                     int D, int window_left, float scale, void* out, int64_t out_tok_stride,
-                                     const void* key2, const void* value2, int num_meta, int32_t* status,
-                                     void* stream) {
+                                     int D, int window_left, int causal, float scale, void* out,
+                                     int64_t out_tok_stride, const void* key2, const void* value2, int num_meta,
+                                     int32_t* status, void* stream) {
   using namespace sbk;
   using namespace sbk::prefill;
   if (num_meta < 0 || num_meta % 16 != 0 || (num_meta > 0 && (!key2 || !value2 || !aligned16(key2) || !aligned16(value2)))) {
@@ -469,6 +470,7 @@ extern "C" int sbk_swa_prefill_dense(const void* q, int64_t q_tok_stride, const 
   T.q = (const __nv_bfloat16*)q; T.q_tok_stride = q_tok_stride;
   T.block_tables = nullptr; T.max_blocks = 0;
   T.query_start_loc = query_start_loc; T.context_lens = nullptr; T.k_start_loc = k_start_loc;
+  T.noncausal = causal ? 0 : 1;
   T.n_seqs = n_seqs; T.tiles_per_seq = tiles; T.H = H; T.G = H / kvh; T.num_blocks = 1;
   T.block_size = 16; T.window_left = window_left; T.scale_log2 = scale * kLog2e;
   T.out = (__nv_bfloat16*)out; T.out_tok_stride = out_tok_stride; T.status = status;

@@ -209,9 +209,10 @@ swa_prefill_tc_kernel(const Params P, const __grid_constant__ CUtensorMap map_k,
   const bool dense = P.k_start_loc != nullptr;
   const int k_start = dense ? P.k_start_loc[s] : 0;
   const int ctx = dense ? (P.k_start_loc[s + 1] - k_start) - n_q : P.context_lens[s];
-  const int p0 = ctx + j * kBQ;                               // position of the tile's first query
-  const int key_lo = P.window_left < 0 ? 0 : (p0 - P.window_left > 0 ? p0 - P.window_left : 0);
-  const int key_hi = p0 + nq_tile;                            // exclusive
+  const bool full_attn = dense && P.noncausal;                // every key of the sequence, no window
+  const int p0 = full_attn ? ctx + n_q - 1 : ctx + j * kBQ;   // position of the tile's first query
+  const int key_lo = (P.window_left < 0 || full_attn) ? 0 : (p0 - P.window_left > 0 ? p0 - P.window_left : 0);
+  const int key_hi = full_attn ? ctx + n_q : p0 + nq_tile;    // exclusive
   const int c_lo = key_lo / kChunk, c_hi = (key_hi - 1) / kChunk;
   const int n_chunks = c_hi - c_lo + 1;
   const int n_mt = (P.n_meta_chunks + kTileChunks - 1) / kTileChunks;   // sink-token tiles come first
@@ -353,8 +354,8 @@ swa_prefill_tc_kernel(const Params P, const __grid_constant__ CUtensorMap map_k,
     const int panel = (part * kCols) >> 6, ch0 = ((part * kCols) & 63) >> 3;
     const int slot_h = r >> 4, ql = r & 15;
     const bool row_ok = slot_h < G && ql < nq_tile;
-    const int p_row = p0 + ql;             // position of this row's query
-    const int lo_row = P.window_left < 0 ? 0 : (p_row - P.window_left > 0 ? p_row - P.window_left : 0);
+    const int p_row = full_attn ? p0 : p0 + ql;   // position of this row's query (its last visible key)
+    const int lo_row = (P.window_left < 0 || full_attn) ? 0 : (p_row - P.window_left > 0 ? p_row - P.window_left : 0);
     // ---- Q rows into the swizzled K-major panels (this thread: its kCols dims) ----
     {
       const uint4* qp = reinterpret_cast<const uint4*>(

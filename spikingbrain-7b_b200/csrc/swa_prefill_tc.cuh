@@ -19,6 +19,7 @@ struct Params {
   // dense mode: K/V are not in a paged cache but tensors [T, kvh, D] (the maps see them as one block of
   // T tokens); sequence s owns keys k_start_loc[s] .. k_start_loc[s+1]-1 and its last query sees its last key
   const int32_t* k_start_loc;   // NULL: paged mode
+  int noncausal;                // dense mode only: every query sees every key of its sequence
 };
 
 // Tensor maps with ONE 128-byte row (64 dims of one kv head) per copy: box_rows == 1.

@@ -553,7 +553,7 @@ def release_rows(rows: torch.Tensor, seq_lens: torch.Tensor, block_tables: torch
 
 
 def swa_prefill_dense(q: torch.Tensor, key: torch.Tensor, value: torch.Tensor, query_start_loc: torch.Tensor,
-                      k_start_loc: torch.Tensor, max_query_len: int, *, window_left: int,
+                      k_start_loc: torch.Tensor, max_query_len: int, *, window_left: int, causal: bool = True,
                       scale: Optional[float] = None, out: Optional[torch.Tensor] = None,
                       key2: Optional[torch.Tensor] = None, value2: Optional[torch.Tensor] = None,
                       status: Optional[torch.Tensor] = None) -> torch.Tensor:
@@ -561,7 +561,7 @@ def swa_prefill_dense(q: torch.Tensor, key: torch.Tensor, value: torch.Tensor, q
     (key/value [Tk, kvh, D] bf16, possibly strided views of a wider projection output) instead of
     a paged cache: the prompt run without block tables. Sequence s owns query rows
     query_start_loc[s]:query_start_loc[s+1] and key rows k_start_loc[s]:k_start_loc[s+1]; its last
-    query sees its last key."""
+    query sees its last key. ``causal=False``: every query sees every key of its sequence."""
     _need_cuda(q, key, value, query_start_loc, k_start_loc, out, status)
     if q.dim() != 3 or key.dim() != 3 or key.shape != value.shape or q.shape[2] != key.shape[2]:
         raise ValueError("q must be [T, H, D] and key/value equal-shaped [Tk, kvh, D]")
@@ -589,7 +589,7 @@ def swa_prefill_dense(q: torch.Tensor, key: torch.Tensor, value: torch.Tensor, q
     rc = _abi.lib.sbk_swa_prefill_dense(
         _ptr(q), q.stride(0) if T else H * d, _ptr(key), _ptr(value), key.stride(0) if Tk > 1 else kvh * d, Tk,
         _ptr(query_start_loc), _ptr(k_start_loc), n_seqs, int(max_query_len), H, kvh, d, window_left,
-        float(scale), _ptr(out), out.stride(0) if T else H * d, _ptr(key2), _ptr(value2), n_meta, _ptr(status),
+        int(causal), float(scale), _ptr(out), out.stride(0) if T else H * d, _ptr(key2), _ptr(value2), n_meta, _ptr(status),
         _stream())
     _abi.check("sbk_swa_prefill_dense", rc)
     global LAUNCHES

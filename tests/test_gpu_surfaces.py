@@ -330,10 +330,9 @@ def test_backend_forward_unsupported_paths_raise(pkg):
                       torch.tensor([[0], [1]], dtype=torch.int32, device=DEV))
     with pytest.raises(AssertionError):
         impl.forward(None, q, kx, kx, None, None, None, kv, md, output=None)
-    with pytest.raises(NotImplementedError):       # the meta tokens' own queries have no kernel here
-        impl.forward(None, q, kx, kx, q, None, None, kv, md, output=torch.empty_like(q))
-    with pytest.raises(AssertionError):            # num_meta_tokens (128) must match key2
-        impl.forward(None, q, kx, kx, None, kx, kx, kv, md, output=torch.empty_like(q))
+    impl2 = MetaAttentionImpl(28, 128, 1.0, 4, None, 65, "auto", num_meta_tokens=2)
+    with pytest.raises(NotImplementedError):       # the meta tokens' own queries do not go with decode tokens
+        impl2.forward(None, q, kx, kx, q, kx, kx, kv, md, output=torch.empty(4, 28, 128, dtype=torch.bfloat16, device=DEV))
     pm = MetaAttentionMetadata(num_prefills=1, num_prefill_tokens=2, num_decode_tokens=0,
                                slot_mapping=torch.tensor([-1, -1], device=DEV), seq_lens=[2],
                                seq_lens_tensor=torch.tensor([2], dtype=torch.int32, device=DEV),
@@ -397,6 +396,42 @@ def test_backend_multi_token_decode_through_block_tables(pkg):
                                                D ** -0.5)[0].bfloat16().float()
             got = out[qsl[b] + i].view(H, D).float().cpu()
             assert float((got - ref).abs().max()) <= 2e-2, (b, i)
+
+
+def test_backend_prompt_run_with_the_meta_tokens_own_queries(pkg):
+    """query2: the step that first computes the sink tokens. Their queries see all of key2/value2 (not
+    causally) and their outputs come first; the prompt's tokens see the sinks plus their causal window."""
+    from spikingbrain_7b_b200.backend import MetaAttentionImpl, MetaAttentionMetadata
+    H, kvh, D, sw, M = 14, 2, 128, 33, 32
+    lens = [50, 9]
+    T = sum(lens)
+    g = torch.Generator().manual_seed(82)
+    rn = lambda *s: (torch.randn(*s, generator=g) / math.sqrt(D)).bfloat16()
+    q, k, v = rn(T, H * D), rn(T, kvh * D), rn(T, kvh * D)
+    q2, k2, v2 = rn(M, H * D), rn(M, kvh * D), rn(M, kvh * D)
+    qsl = [0, 50, 59]
+    impl = MetaAttentionImpl(H, D, D ** -0.5, kvh, None, sw, "auto", num_meta_tokens=M)
+    wl = impl.sliding_window[0]
+    md = MetaAttentionMetadata(num_prefills=2, num_prefill_tokens=T, num_decode_tokens=0,
+                               slot_mapping=torch.full((T,), -1, device=DEV), seq_lens=lens,
+                               seq_lens_tensor=torch.tensor(lens, dtype=torch.int32, device=DEV),
+                               max_prefill_seq_len=max(lens), max_decode_seq_len=0,
+                               context_lens_tensor=torch.zeros(2, dtype=torch.int32, device=DEV),
+                               block_tables=torch.zeros(2, 0, dtype=torch.int32, device=DEV), use_cuda_graph=False,
+                               max_query_len=max(lens), query_start_loc=torch.tensor(qsl, dtype=torch.int32, device=DEV),
+                               seq_start_loc=torch.tensor(qsl, dtype=torch.int32, device=DEV))
+    out = torch.empty(M + T, H * D, dtype=torch.bfloat16, device=DEV)
+    impl.forward(None, q.to(DEV), k.to(DEV), v.to(DEV), q2.to(DEV), k2.to(DEV), v2.to(DEV),
+                 torch.empty(0, dtype=torch.bfloat16, device=DEV), md, output=out)
+    assert impl.status() == 0
+    k2r, v2r = k2.view(M, kvh, D), v2.view(M, kvh, D)
+    want_meta = ref_ops.swa_prefill_dense_ref(q2.view(M, H, D), k2r, v2r, [0, M], [0, M], -1, D ** -0.5, causal=False)
+    want_rest = ref_ops.swa_prefill_dense_ref(q.view(T, H, D), k.view(T, kvh, D), v.view(T, kvh, D), qsl, qsl, wl,
+                                              D ** -0.5, k2r, v2r)
+    got = out.view(M + T, H, D).float().cpu()
+    assert float((got[:M] - want_meta.bfloat16().float()).abs().max()) <= 2e-2
+    assert float((got[M:] - want_rest.bfloat16().float()).abs().max()) <= 2e-2
+    assert mean_rel(got[M:], want_rest.bfloat16().float()) <= 1e-3
 
 
 def test_backend_prompt_run_without_block_tables(pkg):
