@@ -29,7 +29,7 @@
 extern "C" {
 #endif
 
-#define SBK_ABI_VERSION 3
+#define SBK_ABI_VERSION 4
 
 /* element type codes */
 #define SBK_BF16 0
@@ -164,6 +164,59 @@ int sbk_swa_decode_static(const void* q, int64_t q_seq_stride, const void* k_cac
                           int64_t cache_block_stride_bytes, int window_left, float scale,
                           void* out, int out_dtype, int64_t out_seq_stride, float* lse_out,
                           int split_chunks, int max_pieces, int32_t* status, void* stream);
+
+/*
+ * Head-sharded decode with the all-gather of the head outputs fused into the kernel.
+ * The reference shards attention heads over tensor-parallel ranks and gathers the per-rank
+ * head outputs with a collective before the output projection
+ * (vllm_hymeta/model_for_7B/modeling_gla_swa.py:153-202, :228-231; gla_attention.py:126-145).
+ * Here every rank owns a gathered buffer [tokens, H_total, D] bf16 that its peers can store to:
+ * sbk_swa_decode_gather computes this rank's H heads exactly as sbk_swa_decode does, writes them
+ * into its own buffer (`out` = the address of its head slice, `out_seq_stride` = H_total * D)
+ * and stores each finished row into the same place of every peer's buffer (`peer_out[p]` = peer
+ * p's address of this rank's slice) with plain 16-byte stores through NVLink. The last CTA
+ * to finish then stores `flag_value` into `peer_flag[p]` (this rank's slot of peer p's flag
+ * array) with release semantics -- unless a wait inside the kernel ran out, in which case the
+ * flag stays and the peers' own wait reports the step. A rank sees the complete rows after
+ * sbk_peer_wait on its own flag array.
+ *  - flag values grow by one per step and are never reused; the caller alternates between two
+ *    gathered buffers so that a peer one step ahead does not store into rows still being read.
+ *  - `workspace` as for sbk_swa_decode; its first 16 bytes must be zero at the first call.
+ *  - No collective library call, no multicast object, no copy through a tensor map: peers are
+ *    reached by stores only.
+ *
+ * Peer memory: sbk_peer_alloc gives zeroed device memory of this process whose handle
+ * (sbk_peer_export, sbk_peer_handle_bytes() bytes, any byte transport between the processes)
+ * another process maps with sbk_peer_open; sbk_peer_close unmaps, sbk_peer_free releases.
+ * sbk_peer_wait(flags, n, self, value, flag_base, advance, timeout_ms): one launch on `stream`
+ * that returns once flags[p] >= value for every p != self, or after timeout_ms with
+ * SBK_ST_WAIT_TIMEOUT raised in `status` (the context stays usable). sbk_peer_signal stores
+ * `value` to n_peer flag addresses (a step in which this rank has no sequences).
+ *  - `flag_base` (device int32, may be null) makes the calls replayable from a CUDA graph: the
+ *    value stored / awaited is flag_value + *flag_base, read on the device, and sbk_peer_wait
+ *    adds `advance` to *flag_base once it is through (timed out or not). With flag_value 1 and
+ *    advance 1 on every rank each decode + wait pair is one step of a counter that lives on
+ *    the device; a graph must hold an even number of such pairs, because the pairs alternate
+ *    between the two gathered buffers and those addresses are fixed at capture.
+ */
+int sbk_swa_decode_gather(const void* q, int64_t q_seq_stride, const void* k_cache, const void* v_cache,
+                          const int32_t* block_tables, int max_blocks, const int32_t* seq_lens,
+                          int B, int H, int kvh, int D, int64_t num_blocks, int block_size,
+                          int64_t cache_block_stride_bytes, int window_left, float scale,
+                          void* out, int64_t out_seq_stride, void* workspace, size_t workspace_bytes,
+                          int split_chunks, int max_pieces, const void* key2, const void* value2,
+                          int num_meta, void* const* peer_out, int32_t* const* peer_flag, int n_peer,
+                          int32_t flag_value, const int32_t* flag_base, int32_t* status, void* stream);
+int sbk_peer_alloc(size_t bytes, void** ptr);
+int sbk_peer_free(void* ptr);
+int sbk_peer_handle_bytes(void);
+int sbk_peer_export(const void* ptr, void* handle, int handle_bytes);
+int sbk_peer_open(const void* handle, int handle_bytes, void** ptr);
+int sbk_peer_close(void* ptr);
+int sbk_peer_wait(const int32_t* flags, int n, int self, int32_t value, int32_t* flag_base,
+                  int32_t advance, int timeout_ms, int32_t* status, void* stream);
+int sbk_peer_signal(int32_t* const* peer_flag, int n_peer, int32_t value, const int32_t* flag_base,
+                    void* stream);
 
 /*
  * Rotary position embedding fused into the append: rotates the new tokens' query rows in place,

@@ -5,7 +5,7 @@ import of this module raises, and every caller above it fails with it.
 """
 import ctypes
 import os
-from ctypes import c_char_p, c_float, c_int, c_int64, c_size_t, c_void_p
+from ctypes import c_char_p, c_float, c_int, c_int32, c_int64, c_size_t, c_void_p
 
 PKG_DIR = os.path.dirname(os.path.abspath(__file__))
 # SBK_LIB_PATH points the binding at another build of the same sources (profiling variants)
@@ -15,7 +15,7 @@ SBK_BF16, SBK_F32 = 0, 1
 SBK_OK, SBK_E_ARG, SBK_E_ALIGN, SBK_E_WORKSPACE, SBK_E_LAUNCH = 0, -1, -2, -3, -4
 ST_BAD_SLOT, ST_BAD_BLOCK, ST_WAIT_TIMEOUT, ST_RETIRE_OVERFLOW, ST_BAD_POSITION = 1, 2, 4, 8, 16
 ST_OUT_OF_BLOCKS, ST_TABLE_FULL = 32, 64
-ABI_VERSION = 3
+ABI_VERSION = 4
 
 # name -> (restype, argtypes); must list every function include/sbk.h declares
 SIGNATURES = {
@@ -47,6 +47,18 @@ SIGNATURES = {
         c_void_p, c_int64, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_int,
         c_int, c_int64, c_int, c_int64, c_int, c_float, c_void_p, c_int, c_int64, c_void_p,
         c_int, c_int, c_void_p, c_void_p]),
+    "sbk_swa_decode_gather": (c_int, [
+        c_void_p, c_int64, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_int,
+        c_int, c_int64, c_int, c_int64, c_int, c_float, c_void_p, c_int64, c_void_p, c_size_t,
+        c_int, c_int, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_int, c_int32, c_void_p, c_void_p, c_void_p]),
+    "sbk_peer_alloc": (c_int, [c_size_t, c_void_p]),
+    "sbk_peer_free": (c_int, [c_void_p]),
+    "sbk_peer_handle_bytes": (c_int, []),
+    "sbk_peer_export": (c_int, [c_void_p, c_void_p, c_int]),
+    "sbk_peer_open": (c_int, [c_void_p, c_int, c_void_p]),
+    "sbk_peer_close": (c_int, [c_void_p]),
+    "sbk_peer_wait": (c_int, [c_void_p, c_int, c_int, c_int32, c_void_p, c_int32, c_int, c_void_p, c_void_p]),
+    "sbk_peer_signal": (c_int, [c_void_p, c_int, c_int32, c_void_p, c_void_p]),
     "sbk_rope_kv_append": (c_int, [
         c_void_p, c_int, c_int64, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p,
         c_void_p, c_int, c_int64, c_int, c_int, c_int, c_int, c_int64, c_int64, c_int, c_int64,

@@ -16,6 +16,10 @@ int check_launch(const char* what);
 
 inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
 
+// Other ranks of a head-sharded group that one kernel stores to (8 GPUs behind one switch).
+constexpr int kPeerTableSize = 7;
+struct Int32PtrTable { int32_t* p[kPeerTableSize]; };
+
 // -------------------------------------------------------------- device side
 __device__ __forceinline__ void raise_status(int32_t* status, int bit) {
   if (status != nullptr) atomicOr(status, bit);

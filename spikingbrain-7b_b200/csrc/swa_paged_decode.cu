@@ -45,6 +45,7 @@ constexpr int kD = 128;               // head dim
 constexpr int kConsumerWarps = 4;
 constexpr int kConsumers = kConsumerWarps * 32;
 constexpr int kThreads = kConsumers + 32;
+constexpr int kMaxPeers = kPeerTableSize;
 constexpr int kMaxSeqs = 1024;        // sequences per launch (prefix and length tables in shared memory)
 constexpr int kHeadStride = 132;      // floats per head row in the merge buffer (bank skew)
 constexpr int kMergeWarpBytes = 8 * kHeadStride * 4 + 64;
@@ -127,7 +128,30 @@ struct Params {
   int tile_copy;      // 1: one copy per tile (permuted-stride map), 0: one copy per 128-byte row
   int n_meta_chunks;  // 16-token chunks of always-visible sink keys (key2/value2), 0 = none
   int balanced;       // 1: equal runs of chunks per CTA; split_chunks is then the shortest run allowed
+  // Head-sharded use (kernel instantiated with PEER): every finished output row is also stored
+  // into the same place of each peer GPU's gathered buffer, and the last CTA to finish raises
+  // this rank's flag on every peer. ctrl[2] counts finished CTAs, ctrl[3] collects their aborts.
+  void* peer_out[kMaxPeers];        // peer p's address of this rank's (sequence 0, head 0) element
+  int32_t* peer_flag[kMaxPeers];    // this rank's slot in peer p's flag array
+  int n_peer; int32_t flag_value; int signal;
+  const int32_t* flag_base;         // device word added to flag_value when the flags are raised (may be null)
 };
+
+// Copies the finished output row of sequence b (this rank's H heads, contiguous) to every peer
+// with 16-byte stores. Called by the 128 consumer threads after a consumer_bar that follows the
+// row's last store, so the row is read back from this GPU's L2.
+template <typename TO>
+__device__ __forceinline__ void mirror_row(const Params& P, int b) {
+  const int n16 = (int)(P.H * kD * sizeof(TO) / 16);
+  const int64_t row = (int64_t)b * P.out_seq_stride;
+  const uint4* src = reinterpret_cast<const uint4*>(reinterpret_cast<const TO*>(P.out) + row);
+  for (int i = threadIdx.x; i < n16; i += kConsumers) {
+    const uint4 v = __ldcg(src + i);
+#pragma unroll
+    for (int p = 0; p < kMaxPeers; ++p)
+      if (p < P.n_peer) reinterpret_cast<uint4*>(reinterpret_cast<TO*>(P.peer_out[p]) + row)[i] = v;
+  }
+}
 
 // Folds the partials (m, l, O) of a split sequence into its output row; called by the 128
 // consumer threads of the CTA that completed the sequence's last piece. Thread = a float4 of dims
@@ -195,7 +219,7 @@ __device__ __forceinline__ void fold_pieces(const float* __restrict__ ws_o, cons
   }
 }
 
-template <int KVH, typename TO>
+template <int KVH, typename TO, bool PEER>
 __global__ void __launch_bounds__(kThreads, 2)
 swa_decode_kernel(const Params P, const __grid_constant__ CUtensorMap map_k,
                   const __grid_constant__ CUtensorMap map_v, const __grid_constant__ CUtensorMap map_k2,
@@ -631,6 +655,9 @@ swa_decode_kernel(const Params P, const __grid_constant__ CUtensorMap map_k,
           }
         }
       }
+      if constexpr (PEER) {
+        if (direct) consumer_bar();   // the row's stores came from all four warps
+      }
     } else {
       // several warps share a kv head (each took other tokens): merge through shared memory
       uint8_t* mbuf = smem + C::kRingBytes;
@@ -677,7 +704,10 @@ swa_decode_kernel(const Params P, const __grid_constant__ CUtensorMap map_k,
       }
       if (direct) consumer_bar();   // the merge buffer is free again only after every reader is done
     }
-    if (direct) continue;
+    if (direct) {
+      if constexpr (PEER) mirror_row<TO>(P, si.b);
+      continue;
+    }
 
     // ---- split sequence: whoever completes the last piece folds all of them ----
     __threadfence();
@@ -694,6 +724,35 @@ swa_decode_kernel(const Params P, const __grid_constant__ CUtensorMap map_k,
     if (!fold) continue;
     __threadfence();
     fold_pieces<TO>(P.ws_o, P.ws_ml, P.lse_out, P.H, P.max_pieces, P.out_seq_stride, si.b, si.n_pieces, out);
+    if constexpr (PEER) {
+      consumer_bar();
+      mirror_row<TO>(P, si.b);
+    }
+  }
+  if constexpr (PEER) {
+    // Every CTA: its peer stores are ordered before its count (fence at system scope, then the
+    // CTA's barrier, then one atomic). The CTA that counts last has therefore every row of this
+    // launch behind it; it raises this rank's flag on each peer, unless some CTA gave up on a
+    // wait -- the peers' own bounded wait then reports the step as failed on every rank.
+    __threadfence_system();
+    consumer_bar();
+    if (threadIdx.x == 0) {
+      if (misc[0]) atomicOr(&P.ctrl[3], 1);
+      __threadfence();
+      const int f = atomicAdd(&P.ctrl[2], 1);
+      if (f == (int)gridDim.x - 1) {
+        __threadfence_system();
+        const int failed = atomicExch(&P.ctrl[3], 0);
+        P.ctrl[2] = 0;
+        if (P.signal && !failed) {
+          const int32_t value = P.flag_value + (P.flag_base ? __ldcg(P.flag_base) : 0);
+#pragma unroll
+          for (int p = 0; p < kMaxPeers; ++p)
+            if (p < P.n_peer)
+              asm volatile("st.release.sys.global.s32 [%0], %1;" ::"l"(P.peer_flag[p]), "r"(value) : "memory");
+        }
+      }
+    }
   }
   // A wait that ran out may have left copies in flight: give them time to land before the
   // CTA retires (bounded; the result is already flagged invalid).
@@ -702,11 +761,11 @@ swa_decode_kernel(const Params P, const __grid_constant__ CUtensorMap map_k,
   }
 }
 
-template <int KVH, typename TO>
+template <int KVH, typename TO, bool PEER = false>
 int launch_swa(const Params& P0, int B_total, int n_ctas, const CUtensorMap& map_k, const CUtensorMap& map_v,
                const CUtensorMap& map_k2, const CUtensorMap& map_v2, cudaStream_t st) {
   using C = Cfg<KVH>;
-  auto kern = swa_decode_kernel<KVH, TO>;
+  auto kern = swa_decode_kernel<KVH, TO, PEER>;
   // The opt-in to large dynamic shared memory is per device; remember which devices have it.
   static bool configured[64] = {};
   int dev = 0;
@@ -731,6 +790,11 @@ int launch_swa(const Params& P0, int B_total, int n_ctas, const CUtensorMap& map
     P.out = (uint8_t*)P0.out + (int64_t)b0 * P0.out_seq_stride * sizeof(TO);
     if (P0.lse_out) P.lse_out = P0.lse_out + (int64_t)b0 * P0.H;
     P.done = P0.done + b0;
+    if constexpr (PEER) {
+      for (int p = 0; p < P0.n_peer; ++p)
+        P.peer_out[p] = (uint8_t*)P0.peer_out[p] + (int64_t)b0 * P0.out_seq_stride * sizeof(TO);
+      P.signal = b0 + kMaxSeqs >= B_total;   // launches of one stream finish in order: the last one tells the peers
+    }
     if (P0.ws_o) {
       P.ws_o = P0.ws_o + (int64_t)b0 * P0.max_pieces * P0.H * kD;
       P.ws_ml = P0.ws_ml + (int64_t)b0 * P0.max_pieces * P0.H * 2;
@@ -762,16 +826,20 @@ extern "C" size_t sbk_swa_workspace_bytes(int B, int H, int D, int max_pieces) {
   return n;
 }
 
-extern "C" int sbk_swa_decode(const void* q, int64_t q_seq_stride, const void* k_cache,
-                              const void* v_cache, const int32_t* block_tables, int max_blocks,
-                              const int32_t* seq_lens, int B, int H, int kvh, int D,
-                              int64_t num_blocks, int block_size, int64_t cache_block_stride_bytes,
-                              int window_left, float scale, void* out, int out_dtype,
-                              int64_t out_seq_stride, float* lse_out, void* workspace,
-                              size_t workspace_bytes, int split_chunks, int max_pieces,
-                              const void* key2, const void* value2, int num_meta,
-                              int32_t* status, void* stream) {
-  using namespace sbk;
+namespace sbk {
+struct PeerTargets {
+  void* const* out; int32_t* const* flag; int n; int32_t value; const int32_t* base;
+};
+
+static int swa_decode_impl(const void* q, int64_t q_seq_stride, const void* k_cache,
+                           const void* v_cache, const int32_t* block_tables, int max_blocks,
+                           const int32_t* seq_lens, int B, int H, int kvh, int D,
+                           int64_t num_blocks, int block_size, int64_t cache_block_stride_bytes,
+                           int window_left, float scale, void* out, int out_dtype,
+                           int64_t out_seq_stride, float* lse_out, void* workspace,
+                           size_t workspace_bytes, int split_chunks, int max_pieces,
+                           const void* key2, const void* value2, int num_meta,
+                           int32_t* status, void* stream, const PeerTargets* peers) {
   if (num_meta < 0 || num_meta % 16 != 0 || (num_meta > 0 && (!key2 || !value2 || !aligned16(key2) || !aligned16(value2)))) {
     set_error("sbk_swa_decode: sink tokens need 16-byte aligned key2/value2 and a count that is a multiple of 16 (got %d)",
               num_meta);
@@ -841,6 +909,12 @@ extern "C" int sbk_swa_decode(const void* q, int64_t q_seq_stride, const void* k
   }
   P.split_chunks = split_chunks; P.max_pieces = max_pieces; P.status = status;
   P.balanced = balanced;
+  P.n_peer = 0; P.flag_value = 0; P.signal = 0; P.flag_base = nullptr;
+  for (int p = 0; p < kMaxPeers; ++p) { P.peer_out[p] = nullptr; P.peer_flag[p] = nullptr; }
+  if (peers) {
+    for (int p = 0; p < peers->n; ++p) { P.peer_out[p] = peers->out[p]; P.peer_flag[p] = peers->flag[p]; }
+    P.n_peer = peers->n; P.flag_value = peers->value; P.flag_base = peers->base;
+  }
 
   static int sm_count[64] = {};
   int dev = 0;
@@ -880,8 +954,74 @@ extern "C" int sbk_swa_decode(const void* q, int64_t q_seq_stride, const void* k
     case 2: return launch_swa<2, TO>(P, B, n_ctas, map_k, map_v, map_k2, map_v2, st);  \
     default: return launch_swa<4, TO>(P, B, n_ctas, map_k, map_v, map_k2, map_v2, st); \
   }
+  if (peers) {
+    // gathered head outputs are bf16 (checked by the caller of this path)
+    switch (kvh) {
+      case 1: return launch_swa<1, __nv_bfloat16, true>(P, B, n_ctas, map_k, map_v, map_k2, map_v2, st);
+      case 2: return launch_swa<2, __nv_bfloat16, true>(P, B, n_ctas, map_k, map_v, map_k2, map_v2, st);
+      default: return launch_swa<4, __nv_bfloat16, true>(P, B, n_ctas, map_k, map_v, map_k2, map_v2, st);
+    }
+  }
   if (out_dtype == SBK_BF16) { SBK_SWA_KVH(__nv_bfloat16) } else { SBK_SWA_KVH(float) }
 #undef SBK_SWA_KVH
+}
+}  // namespace sbk
+
+extern "C" int sbk_swa_decode(const void* q, int64_t q_seq_stride, const void* k_cache,
+                              const void* v_cache, const int32_t* block_tables, int max_blocks,
+                              const int32_t* seq_lens, int B, int H, int kvh, int D,
+                              int64_t num_blocks, int block_size, int64_t cache_block_stride_bytes,
+                              int window_left, float scale, void* out, int out_dtype,
+                              int64_t out_seq_stride, float* lse_out, void* workspace,
+                              size_t workspace_bytes, int split_chunks, int max_pieces,
+                              const void* key2, const void* value2, int num_meta,
+                              int32_t* status, void* stream) {
+  return sbk::swa_decode_impl(q, q_seq_stride, k_cache, v_cache, block_tables, max_blocks, seq_lens, B, H, kvh,
+                              D, num_blocks, block_size, cache_block_stride_bytes, window_left, scale, out,
+                              out_dtype, out_seq_stride, lse_out, workspace, workspace_bytes, split_chunks,
+                              max_pieces, key2, value2, num_meta, status, stream, nullptr);
+}
+
+extern "C" int sbk_swa_decode_gather(const void* q, int64_t q_seq_stride, const void* k_cache,
+                                     const void* v_cache, const int32_t* block_tables, int max_blocks,
+                                     const int32_t* seq_lens, int B, int H, int kvh, int D,
+                                     int64_t num_blocks, int block_size, int64_t cache_block_stride_bytes,
+                                     int window_left, float scale, void* out, int64_t out_seq_stride,
+                                     void* workspace, size_t workspace_bytes, int split_chunks,
+                                     int max_pieces, const void* key2, const void* value2, int num_meta,
+                                     void* const* peer_out, int32_t* const* peer_flag, int n_peer,
+                                     int32_t flag_value, const int32_t* flag_base, int32_t* status,
+                                     void* stream) {
+  using namespace sbk;
+  if (n_peer < 0 || n_peer > kMaxPeers || (n_peer > 0 && (!peer_out || !peer_flag))) {
+    set_error("sbk_swa_decode_gather: n_peer=%d outside [0,%d] or null peer tables", n_peer, kMaxPeers);
+    return SBK_E_ARG;
+  }
+  if (B < 0) {
+    set_error("sbk_swa_decode_gather: bad size B=%d", B);
+    return SBK_E_ARG;
+  }
+  // rows travel as 16-byte vectors: H * D bf16 is a multiple of 16 bytes for D = 128, the bases
+  // and the row stride have to be as well
+  if (!aligned16(out) || (out_seq_stride * 2) % 16 != 0) {
+    set_error("sbk_swa_decode_gather: out and its row stride must be 16-byte multiples");
+    return SBK_E_ALIGN;
+  }
+  for (int p = 0; p < n_peer; ++p) {
+    if (!peer_out[p] || !peer_flag[p] || !aligned16(peer_out[p]) || (reinterpret_cast<uintptr_t>(peer_flag[p]) & 3u)) {
+      set_error("sbk_swa_decode_gather: peer %d: null or misaligned buffer / flag address", p);
+      return SBK_E_ALIGN;
+    }
+  }
+  if (B == 0 && n_peer > 0) {
+    // nothing to compute, but the peers still wait for this step's flag
+    return sbk_peer_signal(peer_flag, n_peer, flag_value, flag_base, stream);
+  }
+  PeerTargets pt{peer_out, peer_flag, n_peer, flag_value, flag_base};
+  return swa_decode_impl(q, q_seq_stride, k_cache, v_cache, block_tables, max_blocks, seq_lens, B, H, kvh, D,
+                         num_blocks, block_size, cache_block_stride_bytes, window_left, scale, out, SBK_BF16,
+                         out_seq_stride, nullptr, workspace, workspace_bytes, split_chunks, max_pieces, key2,
+                         value2, num_meta, status, stream, &pt);
 }
 
 // ---------------------------------------------------------------------------------------------

@@ -5,8 +5,9 @@ pointers and the current CUDA stream through the C ABI, and raises on a
 non-zero return code. Nothing here computes on the CPU and nothing falls back
 to PyTorch ops: without a CUDA device and libsbk.so these functions raise.
 """
-from typing import Optional, Tuple
+from typing import Optional, Sequence, Tuple
 
+import ctypes
 import os
 
 import torch
@@ -246,6 +247,24 @@ def swa_workspace(B: int, H: int, D: int, max_pieces: int, device) -> Optional[t
     return torch.zeros(n, dtype=torch.uint8, device=device) if n else None
 
 
+class PeerTargets:
+    """Where sbk_swa_decode_gather stores besides its own `out`: per peer the address of this
+    rank's head slice in the peer's gathered buffer and of this rank's slot in the peer's flag
+    array, and the value the flags take when the step's rows are complete."""
+
+    def __init__(self, out_addrs: Sequence[int], flag_addrs: Sequence[int], flag_value: int,
+                 flag_base: Optional[torch.Tensor] = None):
+        if len(out_addrs) != len(flag_addrs):
+            raise ValueError("one buffer address and one flag address per peer")
+        self.n = len(out_addrs)
+        self.out_table = (ctypes.c_void_p * max(self.n, 1))(*out_addrs)
+        self.flag_table = (ctypes.c_void_p * max(self.n, 1))(*flag_addrs)
+        self.flag_value = int(flag_value)
+        if flag_base is not None and (flag_base.dtype != torch.int32 or not flag_base.is_cuda):
+            raise ValueError("flag_base is an int32 word on the device")
+        self.flag_base = flag_base      # the flags take flag_value + flag_base[0], read on the device
+
+
 def swa_decode(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor,
                block_tables: torch.Tensor, seq_lens: torch.Tensor, *, window_left: int,
                scale: Optional[float] = None, out: Optional[torch.Tensor] = None,
@@ -253,12 +272,14 @@ def swa_decode(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor,
                workspace: Optional[torch.Tensor] = None, max_pieces: Optional[int] = None,
                split_chunks: Optional[int] = None, key2: Optional[torch.Tensor] = None,
                value2: Optional[torch.Tensor] = None,
-               status: Optional[torch.Tensor] = None) -> torch.Tensor:
+               status: Optional[torch.Tensor] = None, peers: Optional["PeerTargets"] = None) -> torch.Tensor:
     """Single-query sliding-window attention over the paged cache; q [B, H, D] bf16.
     ``split_chunks`` > 0: fixed pieces of that many 16-token chunks, drawn by the CTAs from a ticket
     counter; < 0: balanced mode (equal runs of chunks per CTA, runs no shorter than -split_chunks);
     default swa_auto_split.
-    ``key2`` / ``value2`` [n_meta, kvh, D]: sink tokens every query sees besides its window."""
+    ``key2`` / ``value2`` [n_meta, kvh, D]: sink tokens every query sees besides its window.
+    ``peers``: head-sharded use -- ``out`` is this rank's head slice of its gathered buffer, and the
+    kernel also stores every finished row to the peers and raises their flags (PeerTargets)."""
     _need_cuda(q, k_cache, v_cache, block_tables, seq_lens, out, lse, workspace, status)
     nb, bs, kvh, d, bstride = _cache_geometry(k_cache, v_cache)
     if q.dim() != 3 or q.shape[2] != d or q.dtype != torch.bfloat16 or k_cache.dtype != torch.bfloat16:
@@ -298,18 +319,30 @@ def swa_decode(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor,
         ev0 = torch.cuda.Event(enable_timing=True, external=True)
         ev1 = torch.cuda.Event(enable_timing=True, external=True)
         ev0.record()
-    rc = _abi.lib.sbk_swa_decode(
-        _ptr(q), q.stride(0) if B else H * d, _ptr(k_cache), _ptr(v_cache), _ptr(block_tables),
-        max_blocks, _ptr(seq_lens), B, H, kvh, d, nb, bs, bstride, window_left, float(scale),
-        _ptr(out), _DTYPE_CODE[out.dtype], out.stride(0) if B else H * d, _ptr(lse),
-        _ptr(workspace), workspace.numel() if workspace is not None else 0, split_chunks,
-        max_pieces, _ptr(key2), _ptr(value2), n_meta, _ptr(status), _stream())
-    _abi.check("sbk_swa_decode", rc)
+    if peers is not None:
+        if out.dtype != torch.bfloat16 or lse is not None:
+            raise ValueError("the gathered head outputs are bf16, without lse")
+        rc = _abi.lib.sbk_swa_decode_gather(
+            _ptr(q), q.stride(0) if B else H * d, _ptr(k_cache), _ptr(v_cache), _ptr(block_tables),
+            max_blocks, _ptr(seq_lens), B, H, kvh, d, nb, bs, bstride, window_left, float(scale),
+            _ptr(out), out.stride(0) if B else H * d, _ptr(workspace),
+            workspace.numel() if workspace is not None else 0, split_chunks, max_pieces, _ptr(key2),
+            _ptr(value2), n_meta, peers.out_table, peers.flag_table, peers.n, peers.flag_value,
+            _ptr(peers.flag_base), _ptr(status), _stream())
+        _abi.check("sbk_swa_decode_gather", rc)
+    else:
+        rc = _abi.lib.sbk_swa_decode(
+            _ptr(q), q.stride(0) if B else H * d, _ptr(k_cache), _ptr(v_cache), _ptr(block_tables),
+            max_blocks, _ptr(seq_lens), B, H, kvh, d, nb, bs, bstride, window_left, float(scale),
+            _ptr(out), _DTYPE_CODE[out.dtype], out.stride(0) if B else H * d, _ptr(lse),
+            _ptr(workspace), workspace.numel() if workspace is not None else 0, split_chunks,
+            max_pieces, _ptr(key2), _ptr(value2), n_meta, _ptr(status), _stream())
+        _abi.check("sbk_swa_decode", rc)
     if timing is not None:
         ev1.record()
         timing.append((ev0, ev1))
     global LAUNCHES
-    LAUNCHES += -(-B // 2048)
+    LAUNCHES += -(-B // 1024)
     return out
 
 

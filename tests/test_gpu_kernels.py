@@ -856,3 +856,134 @@ def test_plan_step_without_ring_is_advance_step(ops):
     assert lens.tolist() == [21, 16, 41] and st.item() == 0
     ops.plan_step(lens, tables, slots, block_size=bs, num_blocks=10, retire=False, status=st)   # row 1 needs a block
     assert st.item() == 32 and lens.tolist() == [21, 16, 41] and slots.tolist() == [-1] * 4
+
+
+# ------------------------------------------------------------------ fused all-gather of the head outputs
+def _emulated_gather(ops, lens, wl, H, kvh, tp, seed, split_chunks, step=1, base=None):
+    """Ranks of a head-sharded group run one after the other on this GPU, each with buffers of its
+    own: rank r computes its head slice and stores it to every other rank's buffer. No kernel
+    waits for another (the waits are enqueued after every writer has finished)."""
+    from spikingbrain_7b_b200.head_shard import shard_heads
+    D, bs = 128, 16
+    B = len(lens)
+    kv, table, nb = make_paged_kv(lens, wl, kvh, D, bs, seed=seed)
+    g = torch.Generator().manual_seed(seed + 100)
+    q = (torch.randn(B, H, D, generator=g) / math.sqrt(D)).bfloat16()
+    ref = ref_ops.swa_paged_decode_ref(q, kv[0], kv[1], table, lens, wl, D ** -0.5)
+    bufs = [torch.full((B, H, D), float("nan"), dtype=torch.bfloat16, device=DEV) for _ in range(tp)]
+    flags = [torch.zeros(tp, dtype=torch.int32, device=DEV) for _ in range(tp)]
+    st = _status()
+    lens_d = torch.tensor(lens, dtype=torch.int32, device=DEV)
+    table_d = table.to(DEV)
+    plain = []
+    for r in range(tp):
+        qh, kh = shard_heads(H, kvh, tp, r)
+        kv_l = kv[:, :, :, kh.start:kh.stop].contiguous().to(DEV)
+        q_l = q[:, qh.start:qh.stop].contiguous().to(DEV)
+        others = [p for p in range(tp) if p != r]
+        slice_bytes = len(qh) * D * 2
+        peers = ops.PeerTargets([bufs[p].data_ptr() + r * slice_bytes for p in others],
+                                [flags[p].data_ptr() + 4 * r for p in others], step, base)
+        ops.swa_decode(q_l, kv_l[0], kv_l[1], table_d, lens_d, window_left=wl, out=bufs[r][:, qh.start:qh.stop],
+                       peers=peers, split_chunks=split_chunks, status=st)
+        plain.append(ops.swa_decode(q_l, kv_l[0], kv_l[1], table_d, lens_d, window_left=wl,
+                                    split_chunks=split_chunks, status=st))
+    torch.cuda.synchronize()
+    return bufs, flags, torch.cat(plain, dim=1), ref, st
+
+
+@pytest.mark.parametrize("tp,H,kvh,split_chunks", [(2, 28, 4, -8), (4, 28, 4, -2), (2, 28, 4, 32), (1, 14, 2, -8),
+                                                   (4, 32, 8, -4), (7, 28, 28, -8)])
+def test_swa_decode_gather_fills_every_ranks_buffer(ops, tp, H, kvh, split_chunks):
+    """sbk_swa_decode_gather: every rank's buffer ends up with all heads, bit-identical to the plain
+    kernel's output (the rows are copied, not recomputed), flags raised to the step value; whole and
+    split sequences, empty ones, kv-head layouts of 1, 2 and 4 per rank."""
+    lens = [4100, 513, 40, 2000, 0, 1, 16, 8193, 333]
+    bufs, flags, plain, ref, st = _emulated_gather(ops, lens, 4096, H, kvh, tp, seed=60 + tp, split_chunks=split_chunks,
+                                                  step=5)
+    assert st.item() == 0
+    for r in range(tp):
+        assert torch.equal(bufs[r], plain)                      # NaN prefill: every element was written
+        want = [5] * tp
+        want[r] = 0                                             # nobody raises a rank's own slot
+        assert flags[r].tolist() == want
+    a = plain.float().cpu()
+    tgt = ref.bfloat16().float()
+    assert float((a - tgt).abs().max()) <= ATTN_MAX_ABS and mean_rel(a, tgt) <= ATTN_MEAN_REL
+
+
+def test_swa_decode_gather_many_sequences_two_launches(ops):
+    """More sequences than one launch takes: the peers' rows of the later launch land at the right
+    offset and only the last launch raises the flags."""
+    g = torch.Generator().manual_seed(70)
+    lens = torch.randint(0, 90, (1100,), generator=g).tolist()
+    bufs, flags, plain, ref, st = _emulated_gather(ops, lens, 63, 14, 2, 2, seed=71, split_chunks=-8, step=3)
+    assert st.item() == 0
+    assert torch.equal(bufs[0], plain) and torch.equal(bufs[1], plain)
+    assert flags[0].tolist() == [0, 3] and flags[1].tolist() == [3, 0]
+
+
+def test_swa_decode_gather_flag_value_relative_to_device_counter(ops):
+    """The flag value is flag_value + a word read on the device at the end of the kernel."""
+    base = torch.tensor([40], dtype=torch.int32, device=DEV)
+    bufs, flags, plain, ref, st = _emulated_gather(ops, [700, 3, 64], 255, 14, 2, 2, seed=72, split_chunks=-8, step=2,
+                                                  base=base)
+    assert st.item() == 0 and torch.equal(bufs[0], plain) and torch.equal(bufs[1], plain)
+    assert flags[0].tolist() == [0, 42] and flags[1].tolist() == [42, 0] and base.item() == 40
+
+
+def test_peer_wait_passes_and_times_out_cleanly(ops):
+    """sbk_peer_wait returns at once when every peer's flag has reached the value, and after its
+    time limit otherwise: status bit raised, kernel returned, context still usable."""
+    from spikingbrain_7b_b200 import _abi
+    flags = torch.tensor([7, 0, 9, 7], dtype=torch.int32, device=DEV)      # rank 1 is the reader
+    st = _status()
+    stream = torch.cuda.current_stream().cuda_stream
+    _abi.check("sbk_peer_wait", _abi.lib.sbk_peer_wait(flags.data_ptr(), 4, 1, 7, None, 0, 50, st.data_ptr(), stream))
+    torch.cuda.synchronize()
+    assert st.item() == 0
+    base = torch.tensor([4], dtype=torch.int32, device=DEV)                # value relative to a device word
+    _abi.check("sbk_peer_wait", _abi.lib.sbk_peer_wait(flags.data_ptr(), 4, 1, 3, base.data_ptr(), 2, 50,
+                                                       st.data_ptr(), stream))
+    torch.cuda.synchronize()
+    assert st.item() == 0 and base.item() == 6
+    ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    ev0.record()
+    _abi.check("sbk_peer_wait", _abi.lib.sbk_peer_wait(flags.data_ptr(), 4, 1, 2, base.data_ptr(), 1, 50,
+                                                       st.data_ptr(), stream))
+    ev1.record()
+    torch.cuda.synchronize()
+    assert st.item() == _abi.ST_WAIT_TIMEOUT and base.item() == 7          # the counter moves on regardless
+    assert 40.0 <= ev0.elapsed_time(ev1) <= 1000.0
+    assert int((flags + 1).sum().item()) == 27                              # the context still works
+    with pytest.raises(_abi.SbkError):
+        _abi.check("sbk_peer_wait", _abi.lib.sbk_peer_wait(flags.data_ptr(), 4, 1, 8, None, 0, 0, st.data_ptr(), stream))
+
+
+def test_peer_memory_alloc_export_and_signal(ops):
+    """Peer-visible memory: zeroed on allocation, exportable as a handle of the advertised size;
+    sbk_peer_signal raises flags inside it."""
+    import ctypes
+    from spikingbrain_7b_b200 import _abi
+    from spikingbrain_7b_b200.head_shard import _DeviceBytes
+    lib = _abi.lib
+    base = ctypes.c_void_p()
+    _abi.check("sbk_peer_alloc", lib.sbk_peer_alloc(4096, ctypes.byref(base)))
+    try:
+        hb = lib.sbk_peer_handle_bytes()
+        assert hb == 64
+        handle = ctypes.create_string_buffer(hb)
+        _abi.check("sbk_peer_export", lib.sbk_peer_export(base.value, handle, hb))
+        assert any(handle.raw)
+        with pytest.raises(_abi.SbkError):
+            _abi.check("sbk_peer_export", lib.sbk_peer_export(base.value, handle, hb - 1))
+        t = torch.as_tensor(_DeviceBytes(base.value, 4096), device=DEV)
+        assert t.data_ptr() == base.value and not t.any()
+        flags = t[:16].view(torch.int32)
+        table = (ctypes.c_void_p * 2)(base.value + 4, base.value + 12)
+        _abi.check("sbk_peer_signal", lib.sbk_peer_signal(table, 2, 11, None, torch.cuda.current_stream().cuda_stream))
+        torch.cuda.synchronize()
+        assert flags.tolist() == [0, 11, 0, 11]
+        del t, flags
+    finally:
+        _abi.check("sbk_peer_free", lib.sbk_peer_free(base.value))

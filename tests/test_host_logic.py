@@ -24,7 +24,7 @@ def test_library_exports_every_declared_symbol(sb):
         assert hasattr(lib, name), f"{name} declared in include/sbk.h but not exported"
     from spikingbrain_7b_b200 import _abi
     assert set(_abi.SIGNATURES) == declared
-    assert _abi.lib.sbk_abi_version() == _abi.ABI_VERSION == 3
+    assert _abi.lib.sbk_abi_version() == _abi.ABI_VERSION == 4
 
 
 def test_host_side_argument_errors_need_no_gpu(sb):

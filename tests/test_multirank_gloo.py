@@ -107,3 +107,45 @@ def test_head_shard_rules_follow_the_reference():
         shard_heads(28, 4, 8, 0)          # 28 query heads do not split eight ways: the reference rejects it too
     with pytest.raises(ValueError):
         shard_heads(24, 4, 6, 0)
+
+
+def test_fused_gather_layout_and_peer_addresses():
+    """Host side of the fused all-gather: where a writer's head slice and flag land in each peer's
+    allocation. A model of the stores (every rank writes its slice to every allocation) must fill
+    each gathered row exactly once, in rank order, and touch nothing else."""
+    import numpy as np
+    import pytest
+    from spikingbrain_7b_b200.head_shard import gather_layout, peer_addresses
+    T, H, D, tp = 5, 28, 128, 4
+    lay = gather_layout(T, H, D, tp)
+    assert lay["row_bytes"] == H * D * 2 and lay["slice_bytes"] == 7 * D * 2
+    assert lay["buffer_offsets"][1] % 256 == 0 and lay["flag_offset"] == 2 * lay["buffer_bytes"]
+    assert lay["total_bytes"] >= lay["flag_offset"] + 4 * tp
+    mem = [np.zeros(lay["total_bytes"], dtype=np.uint8) for _ in range(tp)]    # rank p's allocation
+    bases = [1 << 20, 3 << 20, 7 << 20, 9 << 20]                                # as mapped by the writer
+    for parity in (0, 1):
+        for m in mem:
+            m[:] = 0
+        for r in range(tp):
+            outs, flags = peer_addresses(lay, bases, r, parity)
+            assert len(outs) == len(flags) == tp - 1
+            others = [p for p in range(tp) if p != r]
+            # own slice in the own allocation, as the kernel's `out` would address it
+            own = lay["buffer_offsets"][parity] + r * lay["slice_bytes"]
+            targets = [(r, own)] + [(p, a - bases[p]) for p, a in zip(others, outs)]
+            for p, off in targets:
+                for t in range(T):
+                    o = off + t * lay["row_bytes"]
+                    assert not mem[p][o:o + lay["slice_bytes"]].any()             # nobody wrote here before
+                    mem[p][o:o + lay["slice_bytes"]] = r + 1
+            for p, a in zip(others, flags):
+                assert a - bases[p] == lay["flag_offset"] + 4 * r
+        for m in mem:
+            buf = m[lay["buffer_offsets"][parity]:][:T * lay["row_bytes"]].reshape(T, tp, lay["slice_bytes"])
+            assert all((buf[:, r] == r + 1).all() for r in range(tp))
+            other = m[lay["buffer_offsets"][1 - parity]:][:T * lay["row_bytes"]]
+            assert not other.any()
+    with pytest.raises(ValueError):
+        gather_layout(T, 28, 128, 8)
+    with pytest.raises(ValueError):
+        gather_layout(T, 32, 128, 16)
