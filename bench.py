@@ -55,6 +55,9 @@ def parse_args():
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--no-graph", action="store_true", help="launch every kernel from the host instead of replaying a CUDA graph")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--head-shard", action="store_true",
+                    help="instead of the headline run: the churn workload (1024 sequences, Zipf lengths) with attention "
+                         "heads split over the ranks, sliding-window decode + gather of the head outputs per layer")
     return ap.parse_args()
 
 
@@ -601,9 +604,121 @@ def run_reference(args):
     }))
 
 
+def run_head_shard(args):
+    """Continuous-batching churn shapes, head-sharded: every rank holds all sequences but only its kv
+    heads, decodes its query heads and needs every rank's head outputs afterwards. Times one
+    sliding-window layer three ways, on the device, max over ranks: the local kernel alone, kernel +
+    NCCL all-gather (+ the copy into head order), and the kernel that stores its rows to the peers
+    itself followed by the flag wait (replayed from a CUDA graph, as a serving loop would)."""
+    import numpy as np
+    import torch
+    import torch.distributed as dist
+    local = int(os.environ.get("LOCAL_RANK", 0))
+    torch.cuda.set_device(local)
+    device = torch.device("cuda", local)
+    rank, world = dist_setup("nccl", device)
+    if world < 2:
+        raise SystemExit("--head-shard needs at least two ranks (torch.distributed.run, one rank per GPU)")
+    from spikingbrain_7b_b200 import ops
+    from spikingbrain_7b_b200.head_shard import FusedHeadGather, all_gather_heads, shard_heads
+    qh, kh = shard_heads(H, KVH, world, rank)
+    Hl, kvl = len(qh), len(kh)
+    B = 1024
+    lens_np = np.clip(np.random.default_rng(0).zipf(1.2, size=B), 128, 65536).astype(np.int64)
+    nblk = (lens_np + BLOCK - 1) // BLOCK
+    first = np.maximum(0, lens_np - 1 - WINDOW_LEFT) // BLOCK
+    live = nblk - first
+    nb = int(live.sum())
+    g = torch.Generator().manual_seed(1)
+    perm = torch.randperm(nb, generator=g).to(torch.int32)          # a fragmented pool: blocks in random order
+    table = torch.full((B, int(nblk.max())), -1, dtype=torch.int32)
+    o = 0
+    for b in range(B):
+        table[b, first[b]:nblk[b]] = perm[o:o + live[b]]
+        o += int(live[b])
+    table = table.to(device)
+    lens = torch.from_numpy(lens_np.astype(np.int32)).to(device)
+    n_pools = 3                                                     # layers rotate over pools larger than L2 together
+    pools = [torch.randn(2, nb, BLOCK, kvl, D, device=device, dtype=torch.bfloat16) / math.sqrt(D) for _ in range(n_pools)]
+    q = (torch.randn(B, Hl, D, device=device) / math.sqrt(D)).bfloat16()
+    visible_bytes = float(np.minimum(lens_np, WINDOW_LEFT + 1).sum()) * kvl * D * 2 * 2
+    vis = min(table.shape[1] * BLOCK, WINDOW_LEFT + 1)
+    split = ops.swa_auto_split(B, vis, device)
+    mp = ops.swa_max_pieces(vis, split, B, device)
+    ws = ops.swa_workspace(B, Hl, D, mp, device)
+    fg = FusedHeadGather(B, H, D, device=device, timeout_ms=5000)
+    out_l = torch.empty(B, Hl, D, dtype=torch.bfloat16, device=device)
+    out_g = torch.empty(B, H, D, dtype=torch.bfloat16, device=device)
+    kw = dict(window_left=WINDOW_LEFT, workspace=ws, max_pieces=mp, split_chunks=split)
+
+    def local_only(i):
+        ops.swa_decode(q, pools[i % n_pools][0], pools[i % n_pools][1], table, lens, out=out_l, **kw)
+
+    def with_nccl(i):
+        local_only(i)
+        all_gather_heads(out_l, out=out_g)
+
+    def fused(i):
+        return fg.decode(q, pools[i % n_pools][0], pools[i % n_pools][1], table, lens, **kw)
+
+    # parity of the two gathers before anything is timed
+    with_nccl(0)
+    got = fused(0).clone()
+    torch.cuda.synchronize()
+    if not torch.equal(got, out_g) or fg.status.item() != 0:
+        raise SystemExit(f"rank {rank}: fused gather differs from the collective (status {fg.status.item()})")
+    fused(1)                                                        # an even number of calls before the capture
+    n_graph = 2 * n_pools
+    side = torch.cuda.Stream(device=device)
+    side.wait_stream(torch.cuda.current_stream())
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.stream(side), torch.cuda.graph(graph, stream=side):
+        for i in range(n_graph):
+            fused(i)
+    torch.cuda.current_stream().wait_stream(side)
+
+    def timed(fn, per_call):
+        for i in range(max(args.warmup, 3)):
+            fn(i)
+        dist.barrier(); torch.cuda.synchronize()
+        e0 = torch.cuda.Event(enable_timing=True); e1 = torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for i in range(args.steps):
+            fn(i)
+        e1.record()
+        dist.barrier(); torch.cuda.synchronize()
+        return max_over_ranks(e0.elapsed_time(e1) / args.steps / per_call, device) * 1e3      # microseconds
+
+    t_local = timed(local_only, 1)
+    t_nccl = timed(with_nccl, 1)
+    t_fused_eager = timed(fused, 1)
+    if fg.calls & 1:
+        fused(0)               # the graph begins on the first buffer: keep consecutive steps on different ones
+    t_fused = timed(lambda i: graph.replay(), n_graph)
+    status = fg.status.item()
+    fg.close()
+    if rank == 0:
+        print(json.dumps({
+            "metric": "head_sharded_swa_layer_time", "unit": "us", "higher_is_better": False, "n_gpus": world,
+            "steps": args.steps, "warmup": max(args.warmup, 3), "dtype": "bf16", "data": "synthetic",
+            "local_kernel_us": round(t_local, 2), "kernel_plus_nccl_all_gather_us": round(t_nccl, 2),
+            "fused_gather_graph_us": round(t_fused, 2), "fused_gather_eager_us": round(t_fused_eager, 2),
+            "local_kernel_gbs": round(visible_bytes / t_local / 1e3, 1), "status": status,
+            "gathered_bytes_per_rank": B * H * D * 2,
+            "config": {"workload": f"churn shapes: {B} sequences, ctx Zipf(1.2) clipped to [128, 65536], window_left "
+                                   f"{WINDOW_LEFT}, block {BLOCK}, {H}/{KVH} heads split {world} ways "
+                                   f"({Hl} q / {kvl} kv heads per GPU), head_dim {D}; inputs larger than L2 "
+                                   f"({n_pools} pools of {visible_bytes / 1e6:.0f} MB visible each in rotation)",
+                       "parallelism": f"tp{world}"}}))
+    dist.barrier()
+    dist.destroy_process_group()
+
+
 if __name__ == "__main__":
     a = parse_args()
-    if a.impl == "reference":
+    if a.head_shard:
+        run_head_shard(a)
+    elif a.impl == "reference":
         run_reference(a)
     else:
         run_b200(a)
