@@ -207,6 +207,16 @@ int sbk_swa_decode_gather(const void* q, int64_t q_seq_stride, const void* k_cac
                           int split_chunks, int max_pieces, const void* key2, const void* value2,
                           int num_meta, void* const* peer_out, int32_t* const* peer_flag, int n_peer,
                           int32_t flag_value, const int32_t* flag_base, int32_t* status, void* stream);
+/* The GLA step of a head-sharded layer with the same delivery: arguments as sbk_gla_step (bf16 in
+ * and out), `out` = this rank's head slice of its gathered buffer with `out_seq_stride` elements
+ * between sequences, `counter` = one zeroed int32 on the device (left at zero by every call). */
+int sbk_gla_step_gather(const void* q, const void* k, const void* v, const void* g,
+                        float* state, int64_t num_slots, const int64_t* slot_idx, int B, int H,
+                        int Hkv, int D, float scale, void* out, int64_t out_seq_stride,
+                        int fuse_flags, float gate_normalizer, const void* norm_weight,
+                        float norm_eps, int32_t* counter, void* const* peer_out,
+                        int32_t* const* peer_flag, int n_peer, int32_t flag_value,
+                        const int32_t* flag_base, int32_t* status, void* stream);
 int sbk_peer_alloc(size_t bytes, void** ptr);
 int sbk_peer_free(void* ptr);
 int sbk_peer_handle_bytes(void);

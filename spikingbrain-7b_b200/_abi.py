@@ -51,6 +51,10 @@ SIGNATURES = {
         c_void_p, c_int64, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_int,
         c_int, c_int64, c_int, c_int64, c_int, c_float, c_void_p, c_int64, c_void_p, c_size_t,
         c_int, c_int, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_int, c_int32, c_void_p, c_void_p, c_void_p]),
+    "sbk_gla_step_gather": (c_int, [
+        c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_void_p, c_int, c_int, c_int, c_int,
+        c_float, c_void_p, c_int64, c_int, c_float, c_void_p, c_float, c_void_p, c_void_p, c_void_p, c_int,
+        c_int32, c_void_p, c_void_p, c_void_p]),
     "sbk_peer_alloc": (c_int, [c_size_t, c_void_p]),
     "sbk_peer_free": (c_int, [c_void_p]),
     "sbk_peer_handle_bytes": (c_int, []),

@@ -146,6 +146,7 @@ class FusedHeadGather:
         # captured CUDA graph replays them unchanged.
         self.base = torch.zeros(1, dtype=torch.int32, device=self.device)
         self.calls = 0
+        self._counter = torch.zeros(1, dtype=torch.int32, device=self.device)
         from .ops import PeerTargets
         self._targets = []
         for parity in (0, 1):
@@ -174,6 +175,22 @@ class FusedHeadGather:
         gathered = self.buffers[parity][:B]
         ops.swa_decode(q_local, k_cache, v_cache, block_tables, seq_lens, window_left=window_left,
                        out=self.local_slice(gathered), peers=self._targets[parity], status=self.status, **kw)
+        self.wait()
+        return gathered
+
+    def gla_step(self, q_local: torch.Tensor, k: torch.Tensor, v: torch.Tensor, g: torch.Tensor,
+                 state: torch.Tensor, slot_idx: Optional[torch.Tensor] = None, **kw) -> torch.Tensor:
+        """The GLA layer's counterpart of `decode`: q_local [B, H/tp, D], k/v/g [B, kv heads of this
+        rank, D], state [slots, H/tp, D, D]; returns [B, H, D] with every rank's head outputs."""
+        from . import ops
+        B = q_local.shape[0]
+        if B > self.max_tokens or q_local.shape[1] != self.Hl:
+            raise ValueError(f"q_local must be [<= {self.max_tokens}, {self.Hl}, {self.D}]")
+        parity = self.calls & 1
+        self.calls += 1
+        gathered = self.buffers[parity][:B]
+        ops.gla_step(q_local, k, v, g, state, slot_idx, out=self.local_slice(gathered), peers=self._targets[parity],
+                     peer_counter=self._counter, status=self.status, **kw)
         self.wait()
         return gathered
 

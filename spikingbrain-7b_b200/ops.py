@@ -370,14 +370,18 @@ def gla_step(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, g: torch.Tensor,
              out_dtype: Optional[torch.dtype] = None, relu_qk: bool = False,
              gate_logit_normalizer: Optional[float] = None,
              norm_weight: Optional[torch.Tensor] = None, norm_eps: float = 1e-5,
-             status: Optional[torch.Tensor] = None) -> torch.Tensor:
+             status: Optional[torch.Tensor] = None, peers: Optional["PeerTargets"] = None,
+             peer_counter: Optional[torch.Tensor] = None) -> torch.Tensor:
     """In-place GLA state step on ``state`` [slots, H, D, D] fp32; q [B, H, D], k/v/g [B, Hkv, D].
 
     Fused neighbours of the reference layer (all off by default): ``relu_qk`` applies the feature
     map to q and k; ``gate_logit_normalizer`` makes ``g`` gate logits, turned into
     ``logsigmoid(g) / normalizer`` in the kernel; ``norm_weight`` [D] applies the per-head RMS norm
-    (g_norm) to the read-out."""
-    _need_cuda(q, k, v, g, state, slot_idx, out, status, norm_weight)
+    (g_norm) to the read-out.
+    ``peers`` (head-sharded use, bf16): ``out`` is this rank's head slice of its gathered buffer
+    (rows may be strided); the kernel stores the rows to the peers too and raises their flags;
+    ``peer_counter`` is one zeroed int32 kept for these calls."""
+    _need_cuda(q, k, v, g, state, slot_idx, out, status, norm_weight, peer_counter)
     flags, gnorm = _gla_fusion_args(q, D=q.shape[-1], relu_qk=relu_qk,
                                     gate_logit_normalizer=gate_logit_normalizer, norm_weight=norm_weight)
     if q.dim() != 3 or k.dim() != 3:
@@ -396,18 +400,33 @@ def gla_step(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, g: torch.Tensor,
         raise ValueError("slot_idx must be contiguous int64 [B]")
     if slot_idx is None and state.shape[0] < B:
         raise ValueError("state has fewer slots than sequences")
+    if scale is None:
+        scale = D ** -0.5
+    global LAUNCHES
+    if peers is not None:
+        if q.dtype != torch.bfloat16 or out is None or out.dtype != torch.bfloat16:
+            raise ValueError("the gathered GLA step takes bf16 inputs and a bf16 out slice")
+        if out.shape != (B, H, D) or (B and out.stride()[1:] != (D, 1)):
+            raise ValueError("out must be [B, H, D] with contiguous heads")
+        if peer_counter is None or peer_counter.dtype != torch.int32:
+            raise ValueError("peer_counter: one zeroed int32 on the device")
+        rc = _abi.lib.sbk_gla_step_gather(
+            _ptr(q), _ptr(k), _ptr(v), _ptr(g), _ptr(state), state.shape[0], _ptr(slot_idx), B, H, Hkv, D,
+            float(scale), _ptr(out), out.stride(0) if B else H * D, flags, gnorm, _ptr(norm_weight),
+            float(norm_eps), _ptr(peer_counter), peers.out_table, peers.flag_table, peers.n, peers.flag_value,
+            _ptr(peers.flag_base), _ptr(status), _stream())
+        _abi.check("sbk_gla_step_gather", rc)
+        LAUNCHES += 1
+        return out
     if out is None:
         out = torch.empty((B, H, D), dtype=out_dtype or q.dtype, device=q.device)
     elif out.shape != (B, H, D) or not out.is_contiguous() or out.dtype not in _DTYPE_CODE:
         raise ValueError("out must be contiguous [B, H, D] bf16 or fp32")
-    if scale is None:
-        scale = D ** -0.5
     rc = _abi.lib.sbk_gla_step(
         _ptr(q), _ptr(k), _ptr(v), _ptr(g), _DTYPE_CODE[q.dtype], _ptr(state), state.shape[0],
         _ptr(slot_idx), B, H, Hkv, D, float(scale), _ptr(out), _DTYPE_CODE[out.dtype],
         flags, gnorm, _ptr(norm_weight), float(norm_eps), _ptr(status), _stream())
     _abi.check("sbk_gla_step", rc)
-    global LAUNCHES
     LAUNCHES += 1 if B else 0
     return out
 

@@ -987,3 +987,49 @@ def test_peer_memory_alloc_export_and_signal(ops):
         del t, flags
     finally:
         _abi.check("sbk_peer_free", lib.sbk_peer_free(base.value))
+
+
+@pytest.mark.parametrize("tp,fused", [(2, False), (4, True), (1, True)])
+def test_gla_step_gather_fills_every_ranks_buffer(ops, tp, fused):
+    """sbk_gla_step_gather with the ranks emulated one after the other on this GPU: each rank's
+    state slice and head outputs equal the plain kernel's bit for bit, every buffer holds all heads,
+    padded sequences (slot -1) leave their rows alone, flags carry the step value."""
+    from spikingbrain_7b_b200.head_shard import shard_heads
+    B, H, Hkv, D, step = 6, 28, 4, 128, 9
+    g = torch.Generator().manual_seed(80 + tp)
+    q = torch.randn(B, H, D, generator=g).bfloat16()
+    k = torch.randn(B, Hkv, D, generator=g).bfloat16()
+    v = torch.randn(B, Hkv, D, generator=g).bfloat16()
+    gl = (3 * torch.randn(B, Hkv, D, generator=g)).bfloat16()
+    w = (1 + 0.3 * torch.randn(D, generator=g)).bfloat16().to(DEV)
+    state = torch.randn(B + 2, H, D, D, generator=g)
+    slot = torch.tensor([3, 0, -1, 7, 5, 1], dtype=torch.int64, device=DEV)
+    kw = dict(relu_qk=True, gate_logit_normalizer=16.0, norm_weight=w, norm_eps=1e-5) if fused else {}
+    if not fused:
+        gl = (torch.nn.functional.logsigmoid(gl.float()) / 16).bfloat16()
+    bufs = [torch.full((B, H, D), 7.0, dtype=torch.bfloat16, device=DEV) for _ in range(tp)]
+    flags = [torch.zeros(tp, dtype=torch.int32, device=DEV) for _ in range(tp)]
+    counter = torch.zeros(1, dtype=torch.int32, device=DEV)
+    st = _status()
+    plain = torch.full((B, H, D), 7.0, dtype=torch.bfloat16, device=DEV)
+    for r in range(tp):
+        qh, kh = shard_heads(H, Hkv, tp, r)
+        args = [t[:, hs.start:hs.stop].contiguous().to(DEV) for t, hs in ((q, qh), (k, kh), (v, kh), (gl, kh))]
+        s_gather = state[:, qh.start:qh.stop].contiguous().to(DEV)
+        s_plain = s_gather.clone()
+        others = [p for p in range(tp) if p != r]
+        peers = ops.PeerTargets([bufs[p].data_ptr() + r * len(qh) * D * 2 for p in others],
+                                [flags[p].data_ptr() + 4 * r for p in others], step)
+        ops.gla_step(*args, s_gather, slot, out=bufs[r][:, qh.start:qh.stop], peers=peers, peer_counter=counter,
+                     status=st, **kw)
+        o = ops.gla_step(*args, s_plain, slot, out_dtype=torch.bfloat16, status=st, **kw)
+        live = slot >= 0
+        plain[:, qh.start:qh.stop][live] = o[live]
+        torch.cuda.synchronize()
+        assert torch.equal(s_gather, s_plain) and counter.item() == 0
+    assert st.item() == 0
+    for r in range(tp):
+        assert torch.equal(bufs[r], plain)
+        want = [step] * tp
+        want[r] = 0
+        assert flags[r].tolist() == want

@@ -124,6 +124,24 @@ FUSED_WORKER = textwrap.dedent("""
         ref = ref_ops.swa_paged_decode_ref(q, kv[0], kv[1], table, lens, wl, D ** -0.5).bfloat16().float()
         a = got.float().cpu()
         assert float((a - ref).abs().max()) <= 2e-2 and mean_rel(a, ref) <= 1e-3
+    # the GLA layer's head outputs the same way (odd number of calls so far or not: the buffers alternate)
+    gq = torch.randn(B, H, D, generator=g).bfloat16()
+    gk, gv = torch.randn(B, KVH, D, generator=g).bfloat16(), torch.randn(B, KVH, D, generator=g).bfloat16()
+    gg = (3 * torch.randn(B, KVH, D, generator=g)).bfloat16()
+    gw = (1 + 0.3 * torch.randn(D, generator=g)).bfloat16().to(dev)
+    gstate = torch.randn(B, H, D, D, generator=g)
+    fused_kw = dict(relu_qk=True, gate_logit_normalizer=16.0, norm_weight=gw, norm_eps=1e-5)
+    loc = [t[:, hs.start:hs.stop].contiguous().to(dev) for t, hs in ((gq, qh), (gk, kh), (gv, kh), (gg, kh))]
+    s_a = gstate[:, qh.start:qh.stop].contiguous().to(dev)
+    s_b = s_a.clone()
+    for step in range(3):
+        og = fg.gla_step(*loc, s_a, **fused_kw).clone()
+        o_nccl_g = all_gather_heads(ops.gla_step(*loc, s_b, out_dtype=torch.bfloat16, **fused_kw))
+        torch.cuda.synchronize()
+        assert fg.status.item() == 0
+        assert torch.equal(og, o_nccl_g) and torch.equal(s_a, s_b)
+    if fg.calls & 1:
+        fg.decode(q_l, kv_l[0], kv_l[1], table_d, lens_d, window_left=wl)
     # device time of the two ways to get [B, H, D] on every rank (CUDA events, a few repeats)
     def timed(fn, n=20):
         for _ in range(3):
