@@ -191,13 +191,17 @@ swa_prefill_tc_kernel(const Params P, const __grid_constant__ CUtensorMap map_k,
     if (threadIdx.x == 0) raise_status(P.status, SBK_ST_WAIT_TIMEOUT);
     return;
   }
-  // barriers: K ring full/empty, V ring full/empty, S0/S1 ready, P ready, O_t ready
+  // barriers: K ring full/empty, V ring full/empty; S ready, P ready and O ready, each one per S
+  // buffer (tile t uses the barriers t & 1, phase t >> 1: with two barriers taking turns no waiter
+  // can be two phases away from the phase it waits for, whatever the timing of the other side);
+  // Q staged
   const uint32_t bar_kf = sbase + kBarOff, bar_ke = bar_kf + 8 * kStages;
   const uint32_t bar_vf = bar_ke + 8 * kStages, bar_ve = bar_vf + 8 * kStages;
-  const uint32_t bar_s = bar_ve + 8 * kStages, bar_p = bar_s + 16, bar_o = bar_p + 8;
+  const uint32_t bar_s = bar_ve + 8 * kStages, bar_p = bar_s + 16;
+  const uint32_t bar_q = sbase + kXchOff + 2048 + 8, bar_o = bar_q + 8;   // between the TMEM slot and the flags
   float* xch = reinterpret_cast<float*>(smem + kXchOff);                       // [2][128]
   volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(smem + kXchOff + 2048);
-  volatile int* flags = reinterpret_cast<volatile int*>(smem + kXchOff + 2048 + 16);   // [0..7] tile t & 7 bad, [8] abort
+  volatile uint8_t* flags = smem + kXchOff + 2048 + 32;   // [0..7] tile t & 7 bad, [8] abort
 
   const int s = blockIdx.x / P.tiles_per_seq;
   const int j = blockIdx.x - s * P.tiles_per_seq;
@@ -226,10 +230,13 @@ swa_prefill_tc_kernel(const Params P, const __grid_constant__ CUtensorMap map_k,
       mbar_init(bar_ke + 8 * i, 1);
       mbar_init(bar_vf + 8 * i, 1);
       mbar_init(bar_ve + 8 * i, 1);
-      mbar_init(bar_s + 8 * i, 1);
     }
-    mbar_init(bar_p, kSoftmaxThreads);
-    mbar_init(bar_o, 1);
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(bar_s + 8 * i, 1);
+      mbar_init(bar_p + 8 * i, kSoftmaxThreads);
+      mbar_init(bar_o + 8 * i, 1);
+    }
+    mbar_init(bar_q, kSoftmaxThreads);
     for (int i = 0; i < 9; ++i) flags[i] = 0;
     fence_mbar_init();
   }
@@ -319,8 +326,8 @@ swa_prefill_tc_kernel(const Params P, const __grid_constant__ CUtensorMap map_k,
       __syncwarp();
       return true;
     };
-    // Q is written by the softmax threads; their first arrival on bar_p (phase 0) announces it
-    bool ok = mbar_wait_bounded(bar_p, 0);
+    // Q is written by the softmax threads
+    bool ok = mbar_wait_bounded(bar_q, 0);
     tc_fence_after();
     ok = ok && issue_qk(0);
     for (int t = 0; ok && t < n_tiles; ++t) {
@@ -329,7 +336,7 @@ swa_prefill_tc_kernel(const Params P, const __grid_constant__ CUtensorMap map_k,
       if (!ok) break;
       // P of this tile (and with it: S(t) read, O_t of the previous tile read)
       const int slot = t % kStages;
-      ok = mbar_wait_bounded(bar_p, (t + 1) & 1) && mbar_wait_bounded(bar_vf + 8 * slot, (t / kStages) & 1);
+      ok = mbar_wait_bounded(bar_p + 8 * (t & 1), (t >> 1) & 1) && mbar_wait_bounded(bar_vf + 8 * slot, (t / kStages) & 1);
       if (!ok || flags[8]) break;
       tc_fence_after();
       if (lane == 0) {
@@ -341,7 +348,7 @@ swa_prefill_tc_kernel(const Params P, const __grid_constant__ CUtensorMap map_k,
           umma_bf16_ts(tmem + kOCol, tmem + (t & 1) * 128 + 64 + k * 8, vd, idesc_pv, 1);
         }
         umma_commit(bar_ve + 8 * slot);
-        umma_commit(bar_o);
+        umma_commit(bar_o + 8 * (t & 1));
       }
       __syncwarp();
     }
@@ -366,7 +373,7 @@ swa_prefill_tc_kernel(const Params P, const __grid_constant__ CUtensorMap map_k,
         *reinterpret_cast<uint4*>(smem + kQOff + panel * kPanelBytes + swz(r, ch0 + c)) = v;
       }
       fence_proxy_async_smem();
-      mbar_arrive(bar_p);                  // phase 0 of bar_p: Q is in place
+      mbar_arrive(bar_q);                  // Q is in place
     }
     float m_run = -INFINITY, l_run = 0.f;
     const uint32_t t_lane = tmem + ((uint32_t)((warp & 3) * 32) << 16);
@@ -439,7 +446,7 @@ swa_prefill_tc_kernel(const Params P, const __grid_constant__ CUtensorMap map_k,
       l_run = l_run * alpha + (ls[0] + ls[1]) + (ls[2] + ls[3]);
       // ---- rescale O (my kCols dims of this row) where the offset moved; the GEMMs that wrote it must be done ----
       if (__any_sync(0xffffffffu, t > 0 && alpha != 1.f)) {
-        ok = mbar_wait_bounded(bar_o, (t - 1) & 1);
+        ok = mbar_wait_bounded(bar_o + 8 * ((t - 1) & 1), ((t - 1) >> 1) & 1);
         if (!ok || flags[8]) break;
         tc_fence_after();
         uint32_t orr[32];
@@ -479,10 +486,10 @@ swa_prefill_tc_kernel(const Params P, const __grid_constant__ CUtensorMap map_k,
       }
       tmem_st_wait();
       tc_fence_before();
-      mbar_arrive(bar_p);                  // phase t + 1
+      mbar_arrive(bar_p + 8 * (t & 1));    // tile t
     }
     if (ok && !flags[8]) {
-      ok = mbar_wait_bounded(bar_o, (n_tiles - 1) & 1);
+      ok = mbar_wait_bounded(bar_o + 8 * ((n_tiles - 1) & 1), ((n_tiles - 1) >> 1) & 1);
       if (ok) {
         tc_fence_after();
         uint32_t orr[32];
