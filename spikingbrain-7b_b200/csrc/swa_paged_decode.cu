@@ -77,8 +77,13 @@ __device__ __forceinline__ Plan make_plan(int L, int window_left, int split_chun
 }
 
 struct StageInfo {   // written by the producer before it arms the stage's barrier
-  int b, piece, n_pieces, tok_base, lo, hi, flags, pad;
+  int b, piece, n_pieces, tok_base, lo, hi, flags;
+  int next_b;        // on an item's first stage: the sequence this CTA will take next, or -1
 };
+
+__device__ __forceinline__ void prefetch_l1(const void* p) {
+  asm volatile("prefetch.global.L1 [%0];" ::"l"(p));
+}
 
 template <int KVH>
 struct Cfg {
@@ -88,10 +93,14 @@ struct Cfg {
   static constexpr int kTileBytes = kChunk * kRows128 * 128;   // one sub-chunk of K or of V
   static constexpr int kVOffset = kSub * kTileBytes;           // = 16 KiB: K tiles, then V tiles
   static constexpr int kStageBytes = 2 * kVOffset;             // = 32 KiB
-  static constexpr int kStages = KVH == 4 ? 3 : 2;
+  static constexpr int kStages = 3;
   static constexpr int kRingBytes = kStages * kStageBytes;
+  // warps that share a kv head (kSub > 1) merge their partial results at the end of an item in the
+  // stage they have just consumed, before handing it back: no buffer of its own, so the ring has
+  // three stages for every head layout
   static constexpr int kMergeBytes = kSub > 1 ? kConsumerWarps * kMergeWarpBytes : 0;
-  static constexpr int kInfoOff = kRingBytes + kMergeBytes;
+  static_assert(kMergeBytes <= kStageBytes, "the merge scratch lives inside one stage");
+  static constexpr int kInfoOff = kRingBytes;
   static constexpr int kPreOff = kInfoOff + kStages * (int)sizeof(StageInfo);
   static constexpr int kLensOff = kPreOff + (kMaxSeqs + 4) * 4;
   static constexpr int kBarOff = kLensOff + kMaxSeqs * 4;
@@ -252,42 +261,56 @@ swa_decode_kernel(const Params P, const __grid_constant__ CUtensorMap map_k,
   __syncthreads();
   // ---- number of pieces of every sequence, as an exclusive prefix: item w belongs to the
   //      sequence b with pre[b] <= w < pre[b+1] ----
+  //      One round whatever the batch: a thread takes a run of consecutive sequences (all its
+  //      loads in flight at once), the block scans the per-thread sums, and every thread writes the
+  //      prefixes of its own run. (A round per kThreads sequences cost a load latency and two
+  //      block barriers each, in every CTA: about 10 us ahead of the first copy at 1024 sequences.)
   {
-    int running = 0;
-    for (int base = 0; base < P.B; base += kThreads) {
-      const int b = base + threadIdx.x;
-      const int Lb = b < P.B ? P.seq_lens[b] : 0;
-      if (b < P.B) lens_s[b] = Lb;
-      int incl = 0;
-      if (b < P.B) {
+    constexpr int kRun = (kMaxSeqs + kThreads - 1) / kThreads;
+    const int run_len = (P.B + kThreads - 1) / kThreads;      // <= kRun
+    const int b_lo = threadIdx.x * run_len;
+    int cnt[kRun];
+    int sum = 0, mx = 0;
+#pragma unroll
+    for (int i = 0; i < kRun; ++i) {
+      const int b = b_lo + i;
+      int c = 0;
+      if (i < run_len && b < P.B) {
+        const int Lb = P.seq_lens[b];
+        lens_s[b] = Lb;
         const Plan pl = make_plan(Lb, P.window_left, P.split_chunks, P.max_pieces);
         // balanced mode counts chunks (sink chunks included; an empty sequence keeps one, so that
         // somebody writes its zero output), ticket mode counts pieces
-        incl = P.balanced ? (Lb > 0 ? P.n_meta_chunks + pl.n_chunks : 1) : pl.n_pieces;
+        c = P.balanced ? (Lb > 0 ? P.n_meta_chunks + pl.n_chunks : 1) : pl.n_pieces;
       }
-      if (P.balanced) {
-        int mx = incl;
+      cnt[i] = c;
+      sum += c;
+      mx = max(mx, c);
+    }
+    if (P.balanced) {
 #pragma unroll
-        for (int off = 16; off > 0; off >>= 1) mx = max(mx, __shfl_xor_sync(0xffffffffu, mx, off));
-        if (lane == 0) atomicMax(const_cast<int*>(&misc[7]), mx);
-      }
+      for (int off = 16; off > 0; off >>= 1) mx = max(mx, __shfl_xor_sync(0xffffffffu, mx, off));
+      if (lane == 0) atomicMax(const_cast<int*>(&misc[7]), mx);
+    }
+    int incl = sum;
 #pragma unroll
-      for (int off = 1; off < 32; off <<= 1) {
-        const int t = __shfl_up_sync(0xffffffffu, incl, off);
-        if (lane >= off) incl += t;
-      }
-      __syncthreads();
-      if (lane == 31) misc[2 + warp] = incl;
-      __syncthreads();
-      int warp_off = 0, tile = 0;
+    for (int off = 1; off < 32; off <<= 1) {
+      const int t = __shfl_up_sync(0xffffffffu, incl, off);
+      if (lane >= off) incl += t;
+    }
+    if (lane == 31) misc[2 + warp] = incl;
+    __syncthreads();
+    int run = incl - sum;
 #pragma unroll
-      for (int w2 = 0; w2 < kThreads / 32; ++w2) {
-        const int t = misc[2 + w2];
-        if (w2 < warp) warp_off += t;
-        tile += t;
+    for (int w2 = 0; w2 < kThreads / 32; ++w2)
+      if (w2 < warp) run += misc[2 + w2];
+#pragma unroll
+    for (int i = 0; i < kRun; ++i) {
+      const int b = b_lo + i;
+      if (i < run_len && b < P.B) {
+        run += cnt[i];
+        pre[b + 1] = run;
       }
-      if (b < P.B) pre[b + 1] = running + warp_off + incl;
-      running += tile;
     }
     __syncthreads();
   }
@@ -301,7 +324,16 @@ swa_decode_kernel(const Params P, const __grid_constant__ CUtensorMap map_k,
     // Streams one item: sink chunks [meta_a, meta_b) of the [n_meta, kvh, D] tensors, as stages of
     // their own, then window chunks [cb, cb + n) of sequence b (n == 0 with no sink chunk still
     // sends one empty stage, so that an empty sequence gets its zero output written).
-    auto stream_item = [&](int b, int piece, int n_pieces, int meta_a, int meta_b, int cb, int n) {
+    // `next_b`: the sequence whose item follows on this CTA (-1: none or unknown). Its block-table
+    // entries are asked for now, and the consumers ask for its q row, so that neither side meets
+    // a trip to L2 at the start of the next item: with short sequences those trips are most of an
+    // item's time.
+    auto stream_item = [&](int b, int piece, int n_pieces, int meta_a, int meta_b, int cb, int n, int next_b) {
+      if (next_b >= 0 && lane < 2) {
+        const Plan np = make_plan(lens_s[next_b], P.window_left, P.split_chunks, P.max_pieces);
+        const int lb = (np.c_first * kChunk) / P.block_size + lane * 32;
+        if (lb < P.max_blocks) prefetch_l1(P.block_tables + (int64_t)next_b * P.max_blocks + lb);
+      }
       const int L = lens_s[b];
       const int t0 = first_visible(L, 1, P.window_left);
       const int n_ms = (meta_b - meta_a + C::kSub - 1) / C::kSub;
@@ -367,7 +399,7 @@ swa_decode_kernel(const Params P, const __grid_constant__ CUtensorMap map_k,
         if (lane == 0) {
           StageInfo si;
           si.b = b; si.piece = piece; si.n_pieces = n_pieces; si.tok_base = tok_base;
-          si.lo = lo; si.hi = hi; si.pad = 0;
+          si.lo = lo; si.hi = hi; si.next_b = next_b;
           si.flags = (jj == -n_ms ? kFlagFirst : 0) | (jj == nst - 1 ? kFlagLast : 0) | (bad ? kFlagBad : 0);
           info[s] = si;
           if (bad) raise_status(P.status, SBK_ST_BAD_BLOCK);
@@ -408,7 +440,8 @@ swa_decode_kernel(const Params P, const __grid_constant__ CUtensorMap map_k,
         for (int b = (int)blockIdx.x; b < P.B && !aborted; b += n_cta) {
           const int L = lens_s[b];
           const Plan plan = make_plan(L, P.window_left, P.split_chunks, P.max_pieces);
-          stream_item(b, 0, 1, 0, L > 0 ? P.n_meta_chunks : 0, plan.c_first, plan.n_chunks);
+          stream_item(b, 0, 1, 0, L > 0 ? P.n_meta_chunks : 0, plan.c_first, plan.n_chunks,
+                      b + n_cta < P.B ? b + n_cta : -1);
         }
       } else if (g0 < total) {
         int lo_b = 0, hi_b = P.B;   // largest b with pre[b] <= g0
@@ -427,7 +460,7 @@ swa_decode_kernel(const Params P, const __grid_constant__ CUtensorMap map_k,
           const int ma = va < nm ? va : nm, mb = vb < nm ? vb : nm;
           const int wa = (va > nm ? va : nm) - nm, wb = (vb > nm ? vb : nm) - nm;
           stream_item(b, (int)blockIdx.x - first_run, n_pieces, ma, mb, plan.c_first + wa,
-                      L > 0 ? wb - wa : 0);
+                      L > 0 ? wb - wa : 0, (b + 1 < P.B && pre[b + 1] < g1) ? b + 1 : -1);
         }
       }
     } else {
@@ -451,7 +484,7 @@ swa_decode_kernel(const Params P, const __grid_constant__ CUtensorMap map_k,
         if (n > plan.chunks_per_piece) n = plan.chunks_per_piece;
         if (n < 0) n = 0;
         // sink keys are visible to every query: the first piece of a sequence streams them
-        stream_item(b, piece, plan.n_pieces, 0, (piece == 0 && L > 0) ? P.n_meta_chunks : 0, cb, n);
+        stream_item(b, piece, plan.n_pieces, 0, (piece == 0 && L > 0) ? P.n_meta_chunks : 0, cb, n, -1);
       }
     }
     if (!aborted) {
@@ -526,6 +559,12 @@ swa_decode_kernel(const Params P, const __grid_constant__ CUtensorMap map_k,
 #pragma unroll
       for (int mt = 0; mt < kD / 16; ++mt) { acc[mt][0] = acc[mt][1] = acc[mt][2] = acc[mt][3] = 0.f; }
       m0 = m1 = -INFINITY; l0 = l1 = 0.f;
+      // the q rows of this warp's heads in the next item: G * 256 bytes, one line per lane
+      if (si.next_b >= 0) {
+        const uint8_t* nq = reinterpret_cast<const uint8_t*>(P.q + (int64_t)si.next_b * P.q_seq_stride + (int64_t)hk * G * kD);
+        const int off = lane * 128 < G * kD * 2 ? lane * 128 : G * kD * 2 - 1;
+        if (lane <= 2 * G) prefetch_l1(nq + off);
+      }
     }
 
     const int tb = si.tok_base + sub * kChunk;            // my 16 tokens: [tb, tb+16)
@@ -614,7 +653,10 @@ swa_decode_kernel(const Params P, const __grid_constant__ CUtensorMap map_k,
       if (ragged) fence_proxy_async_smem();   // my zero fill precedes the next tensor copy into these rows
     }
     __syncwarp();
-    if (lane == 0) mbar_arrive(bar_empty + 8 * s);
+    // the last stage of an item doubles as the merge scratch when warps share a kv head: it goes
+    // back to the producer after the merge
+    const bool keep_stage = C::kSub > 1 && (si.flags & kFlagLast);
+    if (lane == 0 && !keep_stage) mbar_arrive(bar_empty + 8 * s);
     if (!(si.flags & kFlagLast)) continue;
 
     // ================= end of an item: write its partial or the output =================
@@ -660,9 +702,10 @@ swa_decode_kernel(const Params P, const __grid_constant__ CUtensorMap map_k,
       }
     } else {
       // several warps share a kv head (each took other tokens): merge through shared memory
-      uint8_t* mbuf = smem + C::kRingBytes;
+      uint8_t* mbuf = smem + s * C::kStageBytes;
       float* wo = reinterpret_cast<float*>(mbuf + warp * kMergeWarpBytes);
       float* wml = wo + 8 * kHeadStride;
+      consumer_bar();   // every warp is done reading this stage's K and V
 #pragma unroll
       for (int mt = 0; mt < kD / 16; ++mt) {
         const int d = mt * 16 + gq;
@@ -702,7 +745,11 @@ swa_decode_kernel(const Params P, const __grid_constant__ CUtensorMap map_k,
           if (d == 0) { P.ws_ml[(pbase + h) * 2] = M; P.ws_ml[(pbase + h) * 2 + 1] = Ls; }
         }
       }
-      if (direct) consumer_bar();   // the merge buffer is free again only after every reader is done
+      // every reader of the scratch is done; these generic writes precede the tensor copies that
+      // will refill the stage
+      fence_proxy_async_smem();
+      consumer_bar();
+      if (lane == 0) mbar_arrive(bar_empty + 8 * s);
     }
     if (direct) {
       if constexpr (PEER) mirror_row<TO>(P, si.b);
