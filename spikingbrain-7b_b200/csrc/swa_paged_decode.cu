@@ -35,6 +35,8 @@
 //   the CTA that completes the last piece of a sequence (a counter per sequence) folds them
 //   and writes the output, so there is no second kernel. A single piece writes `out` directly.
 // HBM-bound: min(seq_len, window_left+1) * kvh*128*2*2 bytes read per sequence.
+#include <stdlib.h>
+
 #include "sbk_common.cuh"
 #include "sbk_tma.cuh"
 
@@ -46,6 +48,10 @@ constexpr int kConsumerWarps = 4;
 constexpr int kConsumers = kConsumerWarps * 32;
 constexpr int kThreads = kConsumers + 32;
 constexpr int kMaxPeers = kPeerTableSize;
+// Balanced mode charges every sequence this many chunks on top of its own. Measured on 1024 sequences
+// with Zipf(1.2) lengths: 0 -> 8 takes the launch from 215 to 176 us with 2 kv heads per GPU, from
+// 119 to 96 us with one, from 334 to 328 us with four; 4 and 16 are within a few percent of 8.
+constexpr int kItemCostChunks = 8;
 constexpr int kMaxSeqs = 1024;        // sequences per launch (prefix and length tables in shared memory)
 constexpr int kHeadStride = 132;      // floats per head row in the merge buffer (bank skew)
 constexpr int kMergeWarpBytes = 8 * kHeadStride * 4 + 64;
@@ -137,6 +143,7 @@ struct Params {
   int tile_copy;      // 1: one copy per tile (permuted-stride map), 0: one copy per 128-byte row
   int n_meta_chunks;  // 16-token chunks of always-visible sink keys (key2/value2), 0 = none
   int balanced;       // 1: equal runs of chunks per CTA; split_chunks is then the shortest run allowed
+  int item_cost;      // balanced mode: what starting and finishing a sequence costs a CTA, in chunks (< 0: default)
   // Head-sharded use (kernel instantiated with PEER): every finished output row is also stored
   // into the same place of each peer GPU's gathered buffer, and the last CTA to finish raises
   // this rank's flag on every peer. ctrl[2] counts finished CTAs, ctrl[3] collects their aborts.
@@ -259,6 +266,7 @@ swa_decode_kernel(const Params P, const __grid_constant__ CUtensorMap map_k,
     fence_mbar_init();
   }
   __syncthreads();
+  const int item_cost = !P.balanced ? 0 : (P.item_cost >= 0 ? P.item_cost : kItemCostChunks);
   // ---- number of pieces of every sequence, as an exclusive prefix: item w belongs to the
   //      sequence b with pre[b] <= w < pre[b+1] ----
   //      One round whatever the batch: a thread takes a run of consecutive sequences (all its
@@ -282,10 +290,15 @@ swa_decode_kernel(const Params P, const __grid_constant__ CUtensorMap map_k,
         // balanced mode counts chunks (sink chunks included; an empty sequence keeps one, so that
         // somebody writes its zero output), ticket mode counts pieces
         c = P.balanced ? (Lb > 0 ? P.n_meta_chunks + pl.n_chunks : 1) : pl.n_pieces;
+        mx = max(mx, c);
+        // Balanced runs are equal in cost, not in chunks: a sequence also costs its CTA a fixed
+        // time (first loads, merge of the warps' partials, output), counted as `item_cost` slots
+        // after its chunks that no run streams. Without them a CTA handed thirty short sequences
+        // finishes long after one handed a single long sequence of the same number of chunks.
+        if (P.balanced) c += item_cost;
       }
       cnt[i] = c;
       sum += c;
-      mx = max(mx, c);
     }
     if (P.balanced) {
 #pragma unroll
@@ -435,7 +448,8 @@ swa_decode_kernel(const Params P, const __grid_constant__ CUtensorMap map_k,
       // fastest as whole sequences (no partials to write and fold): sequence b goes to CTA
       // b mod n_cta. The kernel is bound by HBM, not by the busiest CTA, as long as enough CTAs
       // keep copies in flight.
-      const bool whole = 2 * P.B >= n_cta && (int64_t)misc[7] * P.B <= (int64_t)total + total / 8;
+      const int64_t total_chunks = (int64_t)total - (int64_t)item_cost * P.B;
+      const bool whole = 2 * P.B >= n_cta && (int64_t)misc[7] * P.B <= total_chunks + total_chunks / 8;
       if (whole) {
         for (int b = (int)blockIdx.x; b < P.B && !aborted; b += n_cta) {
           const int L = lens_s[b];
@@ -453,10 +467,13 @@ swa_decode_kernel(const Params P, const __grid_constant__ CUtensorMap map_k,
           const int L = lens_s[b];
           const Plan plan = make_plan(L, P.window_left, P.split_chunks, P.max_pieces);
           const int nm = L > 0 ? P.n_meta_chunks : 0;
+          const int cr = L > 0 ? nm + plan.n_chunks : 1;       // the sequence's chunks; its cost slots follow them
           const int va = (int)(g0 > pre[b] ? g0 - pre[b] : 0);
-          const int vb = (int)((g1 < pre[b + 1] ? g1 : pre[b + 1]) - pre[b]);
+          if (va >= cr) continue;                               // only cost slots of b fall into this run
+          int vb = (int)((g1 < pre[b + 1] ? g1 : pre[b + 1]) - pre[b]);
+          if (vb > cr) vb = cr;
           const int first_run = pre[b] / per;
-          const int n_pieces = (pre[b + 1] - 1) / per - first_run + 1;
+          const int n_pieces = (pre[b] + cr - 1) / per - first_run + 1;
           const int ma = va < nm ? va : nm, mb = vb < nm ? vb : nm;
           const int wa = (va > nm ? va : nm) - nm, wb = (vb > nm ? vb : nm) - nm;
           stream_item(b, (int)blockIdx.x - first_run, n_pieces, ma, mb, plan.c_first + wa,
@@ -956,6 +973,13 @@ static int swa_decode_impl(const void* q, int64_t q_seq_stride, const void* k_ca
   }
   P.split_chunks = split_chunks; P.max_pieces = max_pieces; P.status = status;
   P.balanced = balanced;
+  {
+    static const int env_cost = [] {
+      const char* e = getenv("SBK_SWA_ITEM_COST");   // tuning aid: chunks charged per sequence in balanced mode
+      return e ? atoi(e) : -1;
+    }();
+    P.item_cost = env_cost;
+  }
   P.n_peer = 0; P.flag_value = 0; P.signal = 0; P.flag_base = nullptr;
   for (int p = 0; p < kMaxPeers; ++p) { P.peer_out[p] = nullptr; P.peer_flag[p] = nullptr; }
   if (peers) {
