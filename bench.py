@@ -37,9 +37,9 @@ N_SWA, N_GLA = 14, 14
 NOMINAL_HBM_GBS = 8000.0
 FALLBACK_HBM_GBS = 6650.0
 # DRAM bytes moved per algorithmic byte by the sliding-window decode kernel, from the ncu capture
-# summarised in profiles/swa_decode_kernel_b256_ctx8192.md (2.1584 GB read + 4.9 MB written for
+# summarised in profiles/swa_decode_kernel_b256_ctx8192.md (2.1582 GB read + 6.5 MB written for
 # 2.1481 GB of visible K/V: no re-reads). Traffic grows in proportion to the tokens read.
-SWA_TRAFFIC_PER_ALGORITHMIC_BYTE = (2.158386e9 + 4.914944e6) / (256 * 4097 * 2048)
+SWA_TRAFFIC_PER_ALGORITHMIC_BYTE = (2.158249e9 + 6.497536e6) / (256 * 4097 * 2048)
 
 
 def parse_args():
