@@ -695,6 +695,35 @@ def run_head_shard(args):
     if fg.calls & 1:
         fused(0)               # the graph begins on the first buffer: keep consecutive steps on different ones
     t_fused = timed(lambda i: graph.replay(), n_graph)
+
+    # ---- the GLA layer of the same step: state [B, H/tp, D, D] fp32 per rank, two copies in rotation ----
+    gq = torch.relu(torch.randn(B, Hl, D, device=device) / math.sqrt(D)).bfloat16()
+    gk = torch.relu(torch.randn(B, kvl, D, device=device) / math.sqrt(D)).bfloat16()
+    gv = (torch.randn(B, kvl, D, device=device) / math.sqrt(D)).bfloat16()
+    gg = (torch.nn.functional.logsigmoid(torch.randn(B, kvl, D, device=device)) / 16).bfloat16()
+    states = [torch.randn(B, Hl, D, D, device=device) * 0.01 for _ in range(2)]
+    gla_bytes = 2.0 * B * Hl * D * D * 4
+
+    def gla_local(i):
+        ops.gla_step(gq, gk, gv, gg, states[i & 1], out=out_l)
+
+    def gla_nccl(i):
+        gla_local(i)
+        all_gather_heads(out_l, out=out_g)
+
+    def gla_fused(i):
+        return fg.gla_step(gq, gk, gv, gg, states[i & 1])
+
+    gla_fused(0); gla_fused(1)
+    side.wait_stream(torch.cuda.current_stream())
+    gla_graph = torch.cuda.CUDAGraph()
+    with torch.cuda.stream(side), torch.cuda.graph(gla_graph, stream=side):
+        for i in range(4):
+            gla_fused(i)
+    torch.cuda.current_stream().wait_stream(side)
+    t_gla_local = timed(gla_local, 1)
+    t_gla_nccl = timed(gla_nccl, 1)
+    t_gla_fused = timed(lambda i: gla_graph.replay(), 4)
     status = fg.status.item()
     fg.close()
     if rank == 0:
@@ -704,6 +733,9 @@ def run_head_shard(args):
             "local_kernel_us": round(t_local, 2), "kernel_plus_nccl_all_gather_us": round(t_nccl, 2),
             "fused_gather_graph_us": round(t_fused, 2), "fused_gather_eager_us": round(t_fused_eager, 2),
             "local_kernel_gbs": round(visible_bytes / t_local / 1e3, 1), "status": status,
+            "gla_local_kernel_us": round(t_gla_local, 2), "gla_kernel_plus_nccl_all_gather_us": round(t_gla_nccl, 2),
+            "gla_fused_gather_graph_us": round(t_gla_fused, 2),
+            "gla_local_kernel_gbs": round(gla_bytes / t_gla_local / 1e3, 1),
             "gathered_bytes_per_rank": B * H * D * 2,
             "config": {"workload": f"churn shapes: {B} sequences, ctx Zipf(1.2) clipped to [128, 65536], window_left "
                                    f"{WINDOW_LEFT}, block {BLOCK}, {H}/{KVH} heads split {world} ways "

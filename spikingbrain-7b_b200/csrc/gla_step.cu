@@ -45,11 +45,13 @@ struct GlaPeer {
 };
 
 __device__ __forceinline__ void gla_peer_tail(const GlaPeer& pp) {
-  // peer stores -> fence (system) -> the CTA's barrier -> one count; whoever counts last has all
-  // rows of the launch behind it
-  __threadfence_system();
+  // peer stores -> the CTA's barrier -> ONE thread's fence at system scope (cumulative: it covers
+  // what the barrier ordered before it) -> one count; whoever counts last has all rows of the launch
+  // behind it. A system fence in every thread would wait out each thread's 64 KB of state stores
+  // and doubled the kernel's time.
   __syncthreads();
   if (threadIdx.x == 0) {
+    __threadfence();   // release at GPU scope towards the CTA that counts last; its system fence carries it on
     const int total = (int)(gridDim.x * gridDim.y);
     const int f = atomicAdd(pp.counter, 1);
     if (f == total - 1) {

@@ -794,15 +794,15 @@ swa_decode_kernel(const Params P, const __grid_constant__ CUtensorMap map_k,
     }
   }
   if constexpr (PEER) {
-    // Every CTA: its peer stores are ordered before its count (fence at system scope, then the
-    // CTA's barrier, then one atomic). The CTA that counts last has therefore every row of this
-    // launch behind it; it raises this rank's flag on each peer, unless some CTA gave up on a
-    // wait -- the peers' own bounded wait then reports the step as failed on every rank.
-    __threadfence_system();
+    // Every CTA: its peer stores are ordered before its count (the consumers' barrier, then one
+    // thread's fence at system scope, which is cumulative over what the barrier ordered before it,
+    // then one atomic). The CTA that counts last has therefore every row of this launch behind
+    // it; it raises this rank's flag on each peer, unless some CTA gave up on a wait -- the
+    // peers' own bounded wait then reports the step as failed on every rank.
     consumer_bar();
     if (threadIdx.x == 0) {
       if (misc[0]) atomicOr(&P.ctrl[3], 1);
-      __threadfence();
+      __threadfence_system();
       const int f = atomicAdd(&P.ctrl[2], 1);
       if (f == (int)gridDim.x - 1) {
         __threadfence_system();
