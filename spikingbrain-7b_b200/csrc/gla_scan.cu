@@ -32,8 +32,31 @@ __device__ __forceinline__ __nv_bfloat16 scan_from_f32<__nv_bfloat16>(float x) {
 
 constexpr int kScanTokens = 8;   // tokens staged per round
 
+// Two fp32 values in one 64-bit register, for the packed fp32 instructions of sm_100
+// (fma.rn.f32x2 / mul.rn.f32x2: two IEEE operations per instruction, same results as the scalar
+// ones). The scan is bound by instructions issued per token, not by the FMA units.
+typedef unsigned long long f32x2;
+__device__ __forceinline__ f32x2 pack2(float lo, float hi) {
+  f32x2 r;
+  asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(lo), "f"(hi));
+  return r;
+}
+__device__ __forceinline__ void unpack2(f32x2 p, float& lo, float& hi) {
+  asm("mov.b64 {%0, %1}, %2;" : "=f"(lo), "=f"(hi) : "l"(p));
+}
+__device__ __forceinline__ f32x2 ffma2(f32x2 a, f32x2 b, f32x2 c) {
+  f32x2 d;
+  asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(d) : "l"(a), "l"(b), "l"(c));
+  return d;
+}
+__device__ __forceinline__ f32x2 fmul2(f32x2 a, f32x2 b) {
+  f32x2 d;
+  asm("mul.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b));
+  return d;
+}
+
 template <typename T, typename TO, int D>
-__global__ void __launch_bounds__(256)
+__global__ void __launch_bounds__(256, 2)
 gla_scan_kernel(const T* __restrict__ q, const T* __restrict__ k, const T* __restrict__ v,
                 const T* __restrict__ g, const int32_t* __restrict__ query_start_loc,
                 float* __restrict__ state, int64_t num_slots, const int64_t* __restrict__ slot_idx,
@@ -42,6 +65,8 @@ gla_scan_kernel(const T* __restrict__ q, const T* __restrict__ k, const T* __res
   constexpr int TPR = D / 4;          // threads per state row
   constexpr int GROUPS = 256 / TPR;   // row groups
   constexpr int RPT = D / GROUPS;     // rows per thread
+  constexpr int PPT = RPT / 2;        // ... held as pairs of adjacent rows: 2 (r0 + i GROUPS), + 1
+  static_assert(RPT % 2 == 0, "rows are paired");
   const int h = blockIdx.x;
   const int s = blockIdx.y;
   const int t0 = query_start_loc[s], t1 = query_start_loc[s + 1];
@@ -62,21 +87,31 @@ gla_scan_kernel(const T* __restrict__ q, const T* __restrict__ k, const T* __res
   // multiply-adds per state element and token instead of three operations. A row whose decay
   // within a round is too strong for that (exp(-G) would leave fp32 range; gate logits far below
   // -500) makes the whole CTA keep the plain recurrence for that round.
-  __shared__ float s_q[kScanTokens][D], s_k[kScanTokens][D];
-  __shared__ float s_end[D];        // what the row is multiplied by at the end of the round
+  __shared__ __align__(16) float s_q[kScanTokens][D];   // read two rows at a time (64-bit loads)
+  __shared__ __align__(16) float s_k[kScanTokens][D];
+  __shared__ __align__(16) float s_end[D];        // what the row is multiplied by at the end of the round
   __shared__ int s_plain[1];        // 1: this round runs the plain recurrence
   __shared__ float4 s_v[kScanTokens][TPR];
   __shared__ float4 s_o[kScanTokens][GROUPS][TPR];
   __shared__ float s_sq[2][8];
 
   float4* tile = reinterpret_cast<float4*>(state + ((slot * H + h) * (int64_t)D) * D);
-  float4 S[RPT];
+  // SP[i][c] = (S[row, col c], S[row + 1, col c]) for row = 2 (r0 + i GROUPS) and the thread's four
+  // columns: the two rows of a pair go through one packed FMA, their k (and q) values come as one
+  // 64-bit shared-memory load
+  f32x2 SP[PPT][4];
   if (reset && reset[s]) {
 #pragma unroll
-    for (int i = 0; i < RPT; ++i) S[i] = make_float4(0.f, 0.f, 0.f, 0.f);
+    for (int i = 0; i < PPT; ++i) SP[i][0] = SP[i][1] = SP[i][2] = SP[i][3] = 0ull;
   } else {
 #pragma unroll
-    for (int i = 0; i < RPT; ++i) S[i] = ld_stream_f4(tile + (int64_t)(r0 + i * GROUPS) * TPR + c4);
+    for (int i = 0; i < PPT; ++i) {
+      const int r = 2 * (r0 + i * GROUPS);
+      const float4 a = ld_stream_f4(tile + (int64_t)r * TPR + c4);
+      const float4 b = ld_stream_f4(tile + (int64_t)(r + 1) * TPR + c4);
+      SP[i][0] = pack2(a.x, b.x); SP[i][1] = pack2(a.y, b.y);
+      SP[i][2] = pack2(a.z, b.z); SP[i][3] = pack2(a.w, b.w);
+    }
   }
 
   // The inputs of a round are fetched into registers one round ahead (thread -> key row d = tid % D
@@ -138,47 +173,61 @@ gla_scan_kernel(const T* __restrict__ q, const T* __restrict__ k, const T* __res
     if (!s_plain[0]) {
       for (int tt = 0; tt < nt; ++tt) {
         const float4 vv = s_v[tt][c4];
-        float4 o = make_float4(0.f, 0.f, 0.f, 0.f);
+        const f32x2 v0 = pack2(vv.x, vv.x), v1 = pack2(vv.y, vv.y), v2 = pack2(vv.z, vv.z), v3 = pack2(vv.w, vv.w);
+        f32x2 o0 = 0ull, o1 = 0ull, o2 = 0ull, o3 = 0ull;   // per column: (sum over even rows, sum over odd rows)
 #pragma unroll
-        for (int i = 0; i < RPT; ++i) {
-          const int r = r0 + i * GROUPS;
-          const float kk = s_k[tt][r], qq = s_q[tt][r];
-          S[i].x = fmaf(kk, vv.x, S[i].x);
-          S[i].y = fmaf(kk, vv.y, S[i].y);
-          S[i].z = fmaf(kk, vv.z, S[i].z);
-          S[i].w = fmaf(kk, vv.w, S[i].w);
-          o.x = fmaf(qq, S[i].x, o.x);
-          o.y = fmaf(qq, S[i].y, o.y);
-          o.z = fmaf(qq, S[i].z, o.z);
-          o.w = fmaf(qq, S[i].w, o.w);
+        for (int i = 0; i < PPT; ++i) {
+          const int r = 2 * (r0 + i * GROUPS);
+          const f32x2 kk = *reinterpret_cast<const f32x2*>(&s_k[tt][r]);
+          const f32x2 qq = *reinterpret_cast<const f32x2*>(&s_q[tt][r]);
+          SP[i][0] = ffma2(kk, v0, SP[i][0]);
+          SP[i][1] = ffma2(kk, v1, SP[i][1]);
+          SP[i][2] = ffma2(kk, v2, SP[i][2]);
+          SP[i][3] = ffma2(kk, v3, SP[i][3]);
+          o0 = ffma2(qq, SP[i][0], o0);
+          o1 = ffma2(qq, SP[i][1], o1);
+          o2 = ffma2(qq, SP[i][2], o2);
+          o3 = ffma2(qq, SP[i][3], o3);
         }
+        float4 o;
+        float lo, hi;
+        unpack2(o0, lo, hi); o.x = lo + hi;
+        unpack2(o1, lo, hi); o.y = lo + hi;
+        unpack2(o2, lo, hi); o.z = lo + hi;
+        unpack2(o3, lo, hi); o.w = lo + hi;
         s_o[tt][r0][c4] = o;
       }
 #pragma unroll
-      for (int i = 0; i < RPT; ++i) {
-        const float e = s_end[r0 + i * GROUPS];
-        S[i].x *= e; S[i].y *= e; S[i].z *= e; S[i].w *= e;
+      for (int i = 0; i < PPT; ++i) {
+        const f32x2 e = *reinterpret_cast<const f32x2*>(&s_end[2 * (r0 + i * GROUPS)]);
+        SP[i][0] = fmul2(SP[i][0], e); SP[i][1] = fmul2(SP[i][1], e);
+        SP[i][2] = fmul2(SP[i][2], e); SP[i][3] = fmul2(SP[i][3], e);
       }
     } else {
+      // (rare path: the decay is recomputed from the gate instead of being staged; scalar arithmetic)
       for (int tt = 0; tt < nt; ++tt) {
         const float4 vv = s_v[tt][c4];
-        float4 o = make_float4(0.f, 0.f, 0.f, 0.f);
+        const float vc[4] = {vv.x, vv.y, vv.z, vv.w};
+        float oc[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
-        for (int i = 0; i < RPT; ++i) {
-          const int r = r0 + i * GROUPS;
-          // (rare path: the decay is recomputed from the gate instead of being staged)
-          const float d = expf(gla_gate<T>(scan_to_f32(g[((int64_t)(tb + tt) * Hkv + hk) * D + r]), fu));
-          const float kk = s_k[tt][r], qq = s_q[tt][r];
-          S[i].x = fmaf(d, S[i].x, kk * vv.x);
-          S[i].y = fmaf(d, S[i].y, kk * vv.y);
-          S[i].z = fmaf(d, S[i].z, kk * vv.z);
-          S[i].w = fmaf(d, S[i].w, kk * vv.w);
-          o.x = fmaf(qq, S[i].x, o.x);
-          o.y = fmaf(qq, S[i].y, o.y);
-          o.z = fmaf(qq, S[i].z, o.z);
-          o.w = fmaf(qq, S[i].w, o.w);
+        for (int i = 0; i < PPT; ++i) {
+#pragma unroll
+          for (int hf = 0; hf < 2; ++hf) {
+            const int r = 2 * (r0 + i * GROUPS) + hf;
+            const float d = expf(gla_gate<T>(scan_to_f32(g[((int64_t)(tb + tt) * Hkv + hk) * D + r]), fu));
+            const float kk = s_k[tt][r], qq = s_q[tt][r];
+#pragma unroll
+            for (int c = 0; c < 4; ++c) {
+              float lo, hi;
+              unpack2(SP[i][c], lo, hi);
+              float& x = hf ? hi : lo;
+              x = fmaf(d, x, kk * vc[c]);
+              oc[c] = fmaf(qq, x, oc[c]);
+              SP[i][c] = pack2(lo, hi);
+            }
+          }
         }
-        s_o[tt][r0][c4] = o;
+        s_o[tt][r0][c4] = make_float4(oc[0], oc[1], oc[2], oc[3]);
       }
     }
     __syncthreads();
@@ -215,7 +264,14 @@ gla_scan_kernel(const T* __restrict__ q, const T* __restrict__ k, const T* __res
     // reads of s_o above before the next writes to s_o
   }
 #pragma unroll
-  for (int i = 0; i < RPT; ++i) st_stream_f4(tile + (int64_t)(r0 + i * GROUPS) * TPR + c4, S[i]);
+  for (int i = 0; i < PPT; ++i) {
+    const int r = 2 * (r0 + i * GROUPS);
+    float4 a, b;
+    unpack2(SP[i][0], a.x, b.x); unpack2(SP[i][1], a.y, b.y);
+    unpack2(SP[i][2], a.z, b.z); unpack2(SP[i][3], a.w, b.w);
+    st_stream_f4(tile + (int64_t)r * TPR + c4, a);
+    st_stream_f4(tile + (int64_t)(r + 1) * TPR + c4, b);
+  }
 }
 
 }  // namespace sbk
