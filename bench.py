@@ -58,6 +58,9 @@ def parse_args():
     ap.add_argument("--head-shard", action="store_true",
                     help="instead of the headline run: the churn workload (1024 sequences, Zipf lengths) with attention "
                          "heads split over the ranks, sliding-window decode + gather of the head outputs per layer")
+    ap.add_argument("--tp", type=int, default=0,
+                    help="--head-shard: head shards per group (default: all ranks); the ranks form world/tp "
+                         "sequence groups, e.g. 8 GPUs as 4 head shards x 2 groups")
     return ap.parse_args()
 
 
@@ -620,11 +623,17 @@ def run_head_shard(args):
     if world < 2:
         raise SystemExit("--head-shard needs at least two ranks (torch.distributed.run, one rank per GPU)")
     from spikingbrain_7b_b200 import ops
-    from spikingbrain_7b_b200.head_shard import FusedHeadGather, all_gather_heads, shard_heads
-    qh, kh = shard_heads(H, KVH, world, rank)
+    from spikingbrain_7b_b200.head_shard import FusedHeadGather, all_gather_heads, make_hybrid_layout, shard_heads
+    # head shards inside a group, sequences across groups (28 heads do not split 8 ways: 8 GPUs run
+    # as 4 head shards x 2 sequence groups)
+    lay = make_hybrid_layout(args.tp or world)
+    tp = lay.tp_size
+    qh, kh = shard_heads(H, KVH, tp, lay.tp_rank)
     Hl, kvl = len(qh), len(kh)
-    B = 1024
-    lens_np = np.clip(np.random.default_rng(0).zipf(1.2, size=B), 128, 65536).astype(np.int64)
+    all_lens = np.clip(np.random.default_rng(0).zipf(1.2, size=1024), 128, 65536).astype(np.int64)
+    mine = lay.my_sequences(len(all_lens))
+    lens_np = all_lens[mine.start:mine.stop]
+    B = len(lens_np)
     nblk = (lens_np + BLOCK - 1) // BLOCK
     first = np.maximum(0, lens_np - 1 - WINDOW_LEFT) // BLOCK
     live = nblk - first
@@ -646,7 +655,7 @@ def run_head_shard(args):
     split = ops.swa_auto_split(B, vis, device)
     mp = ops.swa_max_pieces(vis, split, B, device)
     ws = ops.swa_workspace(B, Hl, D, mp, device)
-    fg = FusedHeadGather(B, H, D, device=device, timeout_ms=5000)
+    fg = FusedHeadGather(B, H, D, group=lay.tp_group, device=device, timeout_ms=5000)
     out_l = torch.empty(B, Hl, D, dtype=torch.bfloat16, device=device)
     out_g = torch.empty(B, H, D, dtype=torch.bfloat16, device=device)
     kw = dict(window_left=WINDOW_LEFT, workspace=ws, max_pieces=mp, split_chunks=split)
@@ -656,16 +665,17 @@ def run_head_shard(args):
 
     def with_nccl(i):
         local_only(i)
-        all_gather_heads(out_l, out=out_g)
+        all_gather_heads(out_l, group=lay.tp_group, out=out_g)
 
     def fused(i):
         return fg.decode(q, pools[i % n_pools][0], pools[i % n_pools][1], table, lens, **kw)
 
     # parity of the two gathers before anything is timed
-    with_nccl(0)
+    local_only(0)
+    want = all_gather_heads(out_l, group=lay.tp_group, out=out_g).clone()      # (a group of one returns its input)
     got = fused(0).clone()
     torch.cuda.synchronize()
-    if not torch.equal(got, out_g) or fg.status.item() != 0:
+    if not torch.equal(got, want) or fg.status.item() != 0:
         raise SystemExit(f"rank {rank}: fused gather differs from the collective (status {fg.status.item()})")
     fused(1)                                                        # an even number of calls before the capture
     n_graph = 2 * n_pools
@@ -709,7 +719,7 @@ def run_head_shard(args):
 
     def gla_nccl(i):
         gla_local(i)
-        all_gather_heads(out_l, out=out_g)
+        all_gather_heads(out_l, group=lay.tp_group, out=out_g)
 
     def gla_fused(i):
         return fg.gla_step(gq, gk, gv, gg, states[i & 1])
@@ -736,12 +746,13 @@ def run_head_shard(args):
             "gla_local_kernel_us": round(t_gla_local, 2), "gla_kernel_plus_nccl_all_gather_us": round(t_gla_nccl, 2),
             "gla_fused_gather_graph_us": round(t_gla_fused, 2),
             "gla_local_kernel_gbs": round(gla_bytes / t_gla_local / 1e3, 1),
-            "gathered_bytes_per_rank": B * H * D * 2,
-            "config": {"workload": f"churn shapes: {B} sequences, ctx Zipf(1.2) clipped to [128, 65536], window_left "
-                                   f"{WINDOW_LEFT}, block {BLOCK}, {H}/{KVH} heads split {world} ways "
-                                   f"({Hl} q / {kvl} kv heads per GPU), head_dim {D}; inputs larger than L2 "
-                                   f"({n_pools} pools of {visible_bytes / 1e6:.0f} MB visible each in rotation)",
-                       "parallelism": f"tp{world}"}}))
+            "gathered_bytes_per_rank": B * H * D * 2, "whole_job_sequences_per_layer_s": round(
+                len(all_lens) / (max(t_fused, 1e-9) * 1e-6)),
+            "config": {"workload": f"churn shapes: {len(all_lens)} sequences ({B} per sequence group), ctx Zipf(1.2) "
+                                   f"clipped to [128, 65536], window_left {WINDOW_LEFT}, block {BLOCK}, {H}/{KVH} heads "
+                                   f"split {tp} ways ({Hl} q / {kvl} kv heads per GPU), head_dim {D}; inputs larger "
+                                   f"than L2 ({n_pools} pools of {visible_bytes / 1e6:.0f} MB visible each in rotation)",
+                       "parallelism": f"tp{tp} x {lay.n_seq_groups} sequence groups"}}))
     dist.barrier()
     dist.destroy_process_group()
 

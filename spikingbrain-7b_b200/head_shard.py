@@ -33,6 +33,47 @@ def shard_heads(num_heads: int, num_kv_heads: int, tp_size: int, tp_rank: int) -
     return range(tp_rank * hq, (tp_rank + 1) * hq), kv
 
 
+class HybridLayout:
+    """Ranks of one node as `n_seq_groups` groups of `tp_size` head shards: rank = group * tp_size +
+    tp_rank. Heads are split inside a group (one gather per attention layer, among its tp_size
+    ranks only), sequences across groups (no traffic between groups). This is how 8 GPUs run the
+    28-head model: 28 heads do not split 8 ways (the reference asserts against it,
+    vllm_hymeta/model_for_7B/gla_attention.py:128), 4 head shards x 2 sequence groups do."""
+
+    def __init__(self, tp_size: int, world_size: int, rank: int, tp_group: Optional[dist.ProcessGroup]):
+        self.tp_size, self.world_size, self.rank = tp_size, world_size, rank
+        self.n_seq_groups = world_size // tp_size
+        self.seq_group = rank // tp_size
+        self.tp_rank = rank % tp_size
+        self.tp_group = tp_group
+
+    def my_sequences(self, n_sequences: int) -> range:
+        """Contiguous share of `n_sequences` owned by this rank's sequence group."""
+        return split_sequences(n_sequences, self.n_seq_groups, self.seq_group)
+
+
+def split_sequences(n_sequences: int, n_groups: int, group: int) -> range:
+    """Group g of n takes sequences [g * ceil-balanced share): sizes differ by at most one."""
+    base, extra = divmod(n_sequences, n_groups)
+    start = group * base + min(group, extra)
+    return range(start, start + base + (1 if group < extra else 0))
+
+
+def make_hybrid_layout(tp_size: int) -> HybridLayout:
+    """Collective over the default process group: every rank must call it. Creates one process
+    group per head-shard group and returns this rank's view."""
+    world, rank = dist.get_world_size(), dist.get_rank()
+    if tp_size < 1 or world % tp_size != 0:
+        raise ValueError(f"{world} ranks do not form groups of {tp_size} head shards")
+    mine = None
+    for g in range(world // tp_size):
+        ranks = list(range(g * tp_size, (g + 1) * tp_size))
+        grp = dist.new_group(ranks)          # every rank takes part in every creation
+        if rank in ranks:
+            mine = grp
+    return HybridLayout(tp_size, world, rank, mine)
+
+
 def all_gather_heads(local: torch.Tensor, group: Optional[dist.ProcessGroup] = None,
                      out: Optional[torch.Tensor] = None) -> torch.Tensor:
     """local [T, Hl, D] (this rank's heads) -> [T, tp*Hl, D] with rank r's heads at [r*Hl, (r+1)*Hl).

@@ -149,3 +149,53 @@ def test_fused_gather_layout_and_peer_addresses():
         gather_layout(T, 28, 128, 8)
     with pytest.raises(ValueError):
         gather_layout(T, 32, 128, 16)
+
+
+HYBRID_WORKER = textwrap.dedent("""
+    import os, sys, json
+    sys.path.insert(0, {root!r})
+    import torch
+    import torch.distributed as dist
+    from spikingbrain_7b_b200.head_shard import all_gather_heads, make_hybrid_layout, shard_heads
+
+    dist.init_process_group("gloo")
+    rank, world = dist.get_rank(), dist.get_world_size()
+    lay = make_hybrid_layout(2)                     # 4 ranks = 2 sequence groups x 2 head shards
+    assert (lay.n_seq_groups, lay.seq_group, lay.tp_rank) == (2, rank // 2, rank % 2)
+    seqs = lay.my_sequences(7)
+    assert list(seqs) == ([0, 1, 2, 3] if lay.seq_group == 0 else [4, 5, 6])
+    # the group's sequences, all 8 heads; a rank computes its 4 heads and gathers inside its group only
+    full = torch.arange(7 * 8 * 4, dtype=torch.float32).view(7, 8, 4)[seqs.start:seqs.stop]
+    qh, kvh = shard_heads(8, 2, lay.tp_size, lay.tp_rank)
+    got = all_gather_heads(full[:, qh.start:qh.stop].contiguous(), group=lay.tp_group)
+    assert torch.equal(got, full)
+    dist.barrier()
+    if rank == 0:
+        print(json.dumps({{"ok": True}}))
+    dist.destroy_process_group()
+""")
+
+
+def test_hybrid_layout_four_gloo_ranks(sb, tmp_path):
+    """Head shards inside a group, sequences across groups: the gather stays inside the group."""
+    script = tmp_path / "hybrid_worker.py"
+    script.write_text(HYBRID_WORKER.format(root=ROOT))
+    port = _free_port()
+    procs = []
+    for rank in range(4):
+        env = dict(os.environ, RANK=str(rank), LOCAL_RANK=str(rank), WORLD_SIZE="4", MASTER_ADDR="127.0.0.1",
+                   MASTER_PORT=str(port))
+        procs.append(subprocess.Popen([sys.executable, str(script)], env=env, stdout=subprocess.PIPE,
+                                      stderr=subprocess.PIPE, text=True))
+    outs = [p.communicate(timeout=240) for p in procs]
+    for p, (out, err) in zip(procs, outs):
+        assert p.returncode == 0, err[-2000:]
+    assert '"ok": true' in outs[0][0]
+
+
+def test_split_sequences_covers_without_overlap():
+    from spikingbrain_7b_b200.head_shard import split_sequences
+    for n, g in ((1024, 2), (7, 3), (2, 4), (0, 2)):
+        parts = [split_sequences(n, g, i) for i in range(g)]
+        assert [x for p in parts for x in p] == list(range(n))
+        assert max(len(p) for p in parts) - min(len(p) for p in parts) <= 1
