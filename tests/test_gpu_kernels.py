@@ -533,6 +533,29 @@ def test_gla_scan_matches_oracle_on_ragged_runs(ops, dtype, H, Hkv, D):
     assert torch.equal(state_d[untouched].cpu(), state[untouched])
 
 
+def test_gla_scan_long_runs_at_model_shapes(ops):
+    """Eight sequences of 512 tokens at the model's shapes (28/4 heads, head dim 128, bf16 inputs) with a
+    carried-in state: 64 rounds of eight tokens per (sequence, head) against the token-by-token oracle."""
+    H, Hkv, D, n_seqs, n = 28, 4, 128, 8, 512
+    T = n_seqs * n
+    qsl = [i * n for i in range(n_seqs + 1)]
+    g = torch.Generator().manual_seed(33)
+    q = torch.relu(torch.randn(T, H, D, generator=g) / math.sqrt(D)).bfloat16()
+    k = torch.relu(torch.randn(T, Hkv, D, generator=g) / math.sqrt(D)).bfloat16()
+    v = (torch.randn(T, Hkv, D, generator=g) / math.sqrt(D)).bfloat16()
+    gk = (torch.nn.functional.logsigmoid(torch.randn(T, Hkv, D, generator=g)) / 16).bfloat16()
+    state = torch.randn(n_seqs, H, D, D, generator=g) * 0.1
+    ref_state = state.clone()
+    ref = ref_ops.gla_scan_ref(q, k, v, gk, ref_state, qsl)
+    state_d = state.to(DEV)
+    st = _status()
+    out = ops.gla_scan(q.to(DEV), k.to(DEV), v.to(DEV), gk.to(DEV), state_d,
+                       torch.tensor(qsl, dtype=torch.int32, device=DEV), out_dtype=torch.float32, status=st)
+    assert st.item() == 0
+    assert rel_err(out.cpu(), ref) <= GLA_REL
+    assert rel_err(state_d.cpu(), ref_state) <= GLA_REL
+
+
 def test_gla_scan_equals_chained_steps_and_chunking_is_invisible(ops):
     """One scan over 48 tokens == three scans over 16 == 48 single-token steps of sbk_gla_step."""
     B, T, H, Hkv, D = 2, 48, 28, 4, 128
