@@ -57,7 +57,8 @@ swa_prefill_kernel(const Params P, const __grid_constant__ CUtensorMap map_k,
   volatile int* flags = reinterpret_cast<volatile int*>(smem + kFlagOff);   // [0..2] stage bad, [3] abort
 
   const int s = blockIdx.x / P.tiles_per_seq;
-  const int j = blockIdx.x - s * P.tiles_per_seq;
+  // later query tiles see more keys: they are launched first, so the long items do not start last
+  const int j = P.tiles_per_seq - 1 - (int)(blockIdx.x - s * P.tiles_per_seq);
   const int hk = blockIdx.y;
   const int qs = P.query_start_loc[s];
   const int n_q = P.query_start_loc[s + 1] - qs;

@@ -204,7 +204,8 @@ swa_prefill_tc_kernel(const Params P, const __grid_constant__ CUtensorMap map_k,
   volatile uint8_t* flags = smem + kXchOff + 2048 + 32;   // [0..7] tile t & 7 bad, [8] abort
 
   const int s = blockIdx.x / P.tiles_per_seq;
-  const int j = blockIdx.x - s * P.tiles_per_seq;
+  // later query tiles see more keys: they are launched first, so the long items do not start last
+  const int j = P.tiles_per_seq - 1 - (int)(blockIdx.x - s * P.tiles_per_seq);
   const int hk = blockIdx.y;
   const int qs = P.query_start_loc[s];
   const int n_q = P.query_start_loc[s + 1] - qs;
