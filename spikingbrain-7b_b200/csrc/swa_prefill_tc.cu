@@ -166,6 +166,34 @@ __host__ __device__ constexpr uint32_t instr_desc(int b_mn) {
 // byte offset of the 16-byte chunk `c` (0..7) of row `r` inside a [128 rows][128 B] swizzled panel
 __device__ __forceinline__ uint32_t swz(int r, int c) { return (uint32_t)(r * 128 + ((c ^ (r & 7)) << 4)); }
 
+
+// packed fp32 pairs and the three-input maximum of sm_100: the softmax side of this kernel is bound
+// by instructions issued, and these halve the count of the multiply-adds, sums and maxima
+typedef unsigned long long f32x2;
+__device__ __forceinline__ f32x2 pack2(float lo, float hi) {
+  f32x2 r;
+  asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(lo), "f"(hi));
+  return r;
+}
+__device__ __forceinline__ void unpack2(f32x2 p, float& lo, float& hi) {
+  asm("mov.b64 {%0, %1}, %2;" : "=f"(lo), "=f"(hi) : "l"(p));
+}
+__device__ __forceinline__ f32x2 ffma2(f32x2 a, f32x2 b, f32x2 c) {
+  f32x2 d;
+  asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(d) : "l"(a), "l"(b), "l"(c));
+  return d;
+}
+__device__ __forceinline__ f32x2 fadd2(f32x2 a, f32x2 b) {
+  f32x2 d;
+  asm("add.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b));
+  return d;
+}
+__device__ __forceinline__ float fmax3(float a, float b, float c) {
+  float d;
+  asm("max.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(a), "f"(b), "f"(c));
+  return d;
+}
+
 // two probabilities -> packed bf16 heads and packed bf16 remainders (one conversion each)
 __device__ __forceinline__ void split_bf16x2(float a, float b, uint32_t& hi, uint32_t& lo) {
   __nv_bfloat162 h = __floats2bfloat162_rn(a, b);   // a in the low half
@@ -402,7 +430,8 @@ swa_prefill_tc_kernel(const Params P, const __grid_constant__ CUtensorMap map_k,
       float mx[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
       if (full) {
 #pragma unroll
-        for (int i = 0; i < kCols; ++i) mx[i & 3] = fmaxf(mx[i & 3], __uint_as_float(sr[i]));
+        for (int i = 0; i < kCols; i += 2)
+          mx[(i >> 1) & 3] = fmax3(mx[(i >> 1) & 3], __uint_as_float(sr[i]), __uint_as_float(sr[i + 1]));
       } else {
 #pragma unroll
         for (int i = 0; i < kCols; ++i)
@@ -429,12 +458,21 @@ swa_prefill_tc_kernel(const Params P, const __grid_constant__ CUtensorMap map_k,
       // ---- probabilities, in place of the scores ----
       float ls[4] = {0.f, 0.f, 0.f, 0.f};
       if (full) {
+        const f32x2 sc2 = pack2(P.scale_log2, P.scale_log2), nm2 = pack2(-m_s, -m_s);
+        f32x2 la = 0ull, lb = 0ull;
 #pragma unroll
-        for (int i = 0; i < kCols; ++i) {
-          const float pv = fast_exp2(__uint_as_float(sr[i]) * P.scale_log2 - m_s);
-          sr[i] = __float_as_uint(pv);
-          ls[i & 3] += pv;
+        for (int i = 0; i < kCols; i += 4) {
+          float x0, x1, x2, x3;
+          unpack2(ffma2(pack2(__uint_as_float(sr[i]), __uint_as_float(sr[i + 1])), sc2, nm2), x0, x1);
+          unpack2(ffma2(pack2(__uint_as_float(sr[i + 2]), __uint_as_float(sr[i + 3])), sc2, nm2), x2, x3);
+          const float p0 = fast_exp2(x0), p1 = fast_exp2(x1), p2 = fast_exp2(x2), p3 = fast_exp2(x3);
+          sr[i] = __float_as_uint(p0); sr[i + 1] = __float_as_uint(p1);
+          sr[i + 2] = __float_as_uint(p2); sr[i + 3] = __float_as_uint(p3);
+          la = fadd2(la, pack2(p0, p1));
+          lb = fadd2(lb, pack2(p2, p3));
         }
+        unpack2(la, ls[0], ls[1]);
+        unpack2(lb, ls[2], ls[3]);
       } else {
 #pragma unroll
         for (int i = 0; i < kCols; ++i) {
