@@ -244,6 +244,20 @@ class FusedHeadGather:
         self._abi.check("sbk_peer_wait", rc)
         ops.LAUNCHES += 1
 
+    def resync(self) -> None:
+        """After a step that some rank did not take part in (its peers saw SBK_ST_WAIT_TIMEOUT): bring
+        every rank's step counter, flags and buffer turn back to the start. Collective over the group;
+        call it on every rank, between steps."""
+        torch.cuda.synchronize(self.device)
+        dist.barrier(group=self.group)          # nobody is storing into a peer any more
+        self.flags.zero_()
+        self.base.zero_()
+        self.status.zero_()
+        self._counter.zero_()
+        self.calls = 0
+        torch.cuda.synchronize(self.device)
+        dist.barrier(group=self.group)          # every rank starts from zero before the next stores arrive
+
     def close(self) -> None:
         if self._closed:
             return

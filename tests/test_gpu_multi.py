@@ -186,7 +186,7 @@ FUSED_WORKER = textwrap.dedent("""
 """)
 
 
-def _run_two_ranks(script_text, tmp_path, name):
+def _run_two_ranks(script_text, tmp_path, name, extra_env=None):
     script = tmp_path / name
     script.write_text(script_text)
     with socket.socket() as s:
@@ -196,6 +196,7 @@ def _run_two_ranks(script_text, tmp_path, name):
     for rank in range(2):
         env = dict(os.environ, RANK=str(rank), LOCAL_RANK=str(rank), WORLD_SIZE="2", MASTER_ADDR="127.0.0.1",
                    MASTER_PORT=str(port))
+        env.update(extra_env or {})
         procs.append(subprocess.Popen([sys.executable, str(script)], env=env, stdout=subprocess.PIPE,
                                       stderr=subprocess.PIPE, text=True))
     outs = [p.communicate(timeout=600) for p in procs]
@@ -212,3 +213,66 @@ def test_fused_head_gather_two_ranks(sb, tmp_path):
     outs = _run_two_ranks(FUSED_WORKER.format(root=ROOT), tmp_path, "fused_worker.py")
     assert '"ok": true' in outs[0][0]
     print(outs[0][0].strip().splitlines()[-1])
+
+
+MISSED_STEP_WORKER = textwrap.dedent("""
+    import os, sys, math, json, datetime, time
+    sys.path.insert(0, {root!r})
+    import torch
+    import torch.distributed as dist
+    from tests.helpers import make_paged_kv
+    from spikingbrain_7b_b200 import _abi, ops
+    from spikingbrain_7b_b200.head_shard import FusedHeadGather, all_gather_heads, shard_heads
+
+    rank, world = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"])
+    torch.cuda.set_device(rank)
+    dev = torch.device("cuda", rank)
+    dist.init_process_group("nccl", device_id=dev, timeout=datetime.timedelta(seconds=90))
+    H, KVH, D, bs, wl = 28, 4, 128, 16, 255
+    lens = [300, 17, 64]
+    B = len(lens)
+    kv, table, nb = make_paged_kv(lens, wl, KVH, D, bs, seed=54)
+    qh, kh = shard_heads(H, KVH, world, rank)
+    kv_l = kv[:, :, :, kh.start:kh.stop].contiguous().to(dev)
+    lens_d = torch.tensor(lens, dtype=torch.int32, device=dev)
+    table_d = table.to(dev)
+    g = torch.Generator().manual_seed(55)
+    q = (torch.randn(B, H, D, generator=g) / math.sqrt(D)).bfloat16()
+    q_l = q[:, qh.start:qh.stop].contiguous().to(dev)
+    want = all_gather_heads(ops.swa_decode(q_l, kv_l[0], kv_l[1], table_d, lens_d, window_left=wl)).clone()
+    fg = FusedHeadGather(8, H, D, device=dev, timeout_ms=300)
+    def step():
+        o = fg.decode(q_l, kv_l[0], kv_l[1], table_d, lens_d, window_left=wl).clone()
+        torch.cuda.synchronize()
+        return o
+    assert torch.equal(step(), want) and fg.status.item() == 0
+    dist.barrier()
+    # rank 1 sits the next step out (between steps, nothing of its own in flight): rank 0's wait runs
+    # out after 300 ms, says so in the status word and returns; the context stays usable
+    if rank == 0:
+        t0 = time.time()
+        step()
+        assert fg.status.item() == _abi.ST_WAIT_TIMEOUT
+        assert 0.25 <= time.time() - t0 <= 10.0
+        assert int((lens_d + 1).sum().item()) == sum(lens) + B
+    fg.resync()                                  # both ranks: counters, flags and buffer turn back to the start
+    assert fg.status.item() == 0
+    for _ in range(3):
+        assert torch.equal(step(), want) and fg.status.item() == 0
+    fg.close()
+    dist.barrier()
+    if rank == 0:
+        print(json.dumps({{"ok": True}}))
+    dist.destroy_process_group()
+""")
+
+
+def test_fused_head_gather_missed_step_is_reported_and_recovered(sb, tmp_path):
+    """A peer that does not take a step: the bounded flag wait reports it (no hang, no fault), and after a
+    host-side resync the gather works again."""
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs two GPUs")
+    # in-switch reduction off in the collective library for a test in which a rank falls out of step
+    outs = _run_two_ranks(MISSED_STEP_WORKER.format(root=ROOT), tmp_path, "missed_step_worker.py",
+                          extra_env={"NCCL_NVLS_ENABLE": "0"})
+    assert '"ok": true' in outs[0][0]
