@@ -126,6 +126,27 @@ __device__ __forceinline__ void store_out<__nv_bfloat16>(__nv_bfloat16* p, float
   *p = __float2bfloat16_rn(x);
 }
 
+// four consecutive outputs: one vector store where the address allows it
+__device__ __forceinline__ void store_out4(float* p, float a, float b, float c, float d) {
+  if ((reinterpret_cast<uintptr_t>(p) & 15u) == 0) {
+    *reinterpret_cast<float4*>(p) = make_float4(a, b, c, d);
+  } else {
+    p[0] = a; p[1] = b; p[2] = c; p[3] = d;
+  }
+}
+__device__ __forceinline__ void store_out4(__nv_bfloat16* p, float a, float b, float c, float d) {
+  if ((reinterpret_cast<uintptr_t>(p) & 7u) == 0) {
+    __nv_bfloat162 lo = __floats2bfloat162_rn(a, b), hi = __floats2bfloat162_rn(c, d);
+    uint2 w;
+    w.x = *reinterpret_cast<uint32_t*>(&lo);
+    w.y = *reinterpret_cast<uint32_t*>(&hi);
+    *reinterpret_cast<uint2*>(p) = w;
+  } else {
+    p[0] = __float2bfloat16_rn(a); p[1] = __float2bfloat16_rn(b);
+    p[2] = __float2bfloat16_rn(c); p[3] = __float2bfloat16_rn(d);
+  }
+}
+
 __device__ __forceinline__ void consumer_bar() {
   asm volatile("bar.sync 1, %0;" ::"n"(kConsumers) : "memory");
 }
@@ -736,30 +757,36 @@ swa_decode_kernel(const Params P, const __grid_constant__ CUtensorMap map_k,
         wml[8 + 2 * tq] = ls0; wml[8 + 2 * tq + 1] = ls1;
       }
       consumer_bar();
-      const int d = threadIdx.x;   // 128 consumer threads <-> 128 dims
-      for (int h = 0; h < P.H; ++h) {
+      // heads go round the four warps, a lane takes four dims of a head (one 128-bit read per
+      // partial): at most H / 4 trips, two in flight, instead of H dependent ones
+      const int d4 = lane * 4;
+#pragma unroll 2
+      for (int h = warp; h < P.H; h += kConsumerWarps) {
         const int kvhd = h / G, nq = h - kvhd * G;
         float M = -INFINITY;
 #pragma unroll
         for (int sw = 0; sw < C::kSub; ++sw)
           M = fmaxf(M, reinterpret_cast<const float*>(mbuf + (kvhd + KVH * sw) * kMergeWarpBytes)[8 * kHeadStride + nq]);
         const float Ms = fmaxf(M, kNegBig);
-        float Ls = 0.f, O = 0.f;
+        float Ls = 0.f;
+        float4 O = make_float4(0.f, 0.f, 0.f, 0.f);
 #pragma unroll
         for (int sw = 0; sw < C::kSub; ++sw) {
           const float* po = reinterpret_cast<const float*>(mbuf + (kvhd + KVH * sw) * kMergeWarpBytes);
           const float wgt = fast_exp2(po[8 * kHeadStride + nq] - Ms);
           Ls += po[8 * kHeadStride + 8 + nq] * wgt;
-          O += po[nq * kHeadStride + d] * wgt;
+          const float4 o = *reinterpret_cast<const float4*>(po + nq * kHeadStride + d4);
+          O.x += o.x * wgt; O.y += o.y * wgt; O.z += o.z * wgt; O.w += o.w * wgt;
         }
         if (direct) {
           const float inv = Ls > 0.f ? 1.f / Ls : 0.f;
-          store_out<TO>(out + (int64_t)si.b * P.out_seq_stride + (int64_t)h * kD + d, O * inv);
-          if (P.lse_out && d == 0)
+          TO* op = out + (int64_t)si.b * P.out_seq_stride + (int64_t)h * kD + d4;
+          store_out4(op, O.x * inv, O.y * inv, O.z * inv, O.w * inv);
+          if (P.lse_out && lane == 0)
             P.lse_out[(int64_t)si.b * P.H + h] = Ls > 0.f ? (M + log2f(Ls)) * kLn2 : -INFINITY;
         } else {
-          P.ws_o[(pbase + h) * kD + d] = O;
-          if (d == 0) { P.ws_ml[(pbase + h) * 2] = M; P.ws_ml[(pbase + h) * 2 + 1] = Ls; }
+          *reinterpret_cast<float4*>(P.ws_o + (pbase + h) * kD + d4) = O;
+          if (lane == 0) { P.ws_ml[(pbase + h) * 2] = M; P.ws_ml[(pbase + h) * 2 + 1] = Ls; }
         }
       }
       // every reader of the scratch is done; these generic writes precede the tensor copies that
