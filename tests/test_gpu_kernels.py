@@ -1056,3 +1056,33 @@ def test_gla_step_gather_fills_every_ranks_buffer(ops, tp, fused):
         want = [step] * tp
         want[r] = 0
         assert flags[r].tolist() == want
+
+
+@pytest.mark.parametrize("H,kvh", [(7, 1), (14, 2)])
+@pytest.mark.parametrize("out_dtype", [torch.bfloat16, torch.float32])
+def test_swa_decode_output_rows_need_no_alignment(ops, H, kvh, out_dtype):
+    """Head layouts whose warps share a kv head write four outputs at a time where the address
+    allows it; an output tensor that starts one element into its storage takes the scalar stores."""
+    D, bs, wl = 128, 16, 255
+    lens = [300, 17, 64, 0, 1000]
+    B = len(lens)
+    kv, table, nb = make_paged_kv(lens, wl, kvh, D, bs, seed=90)
+    g = torch.Generator().manual_seed(91)
+    q = (torch.randn(B, H, D, generator=g) / math.sqrt(D)).bfloat16()
+    ref = ref_ops.swa_paged_decode_ref(q, kv[0], kv[1], table, lens, wl, D ** -0.5)
+    kv_d = kv.to(DEV)
+    lens_d = torch.tensor(lens, dtype=torch.int32, device=DEV)
+    outs = []
+    for off in (0, 1):
+        store = torch.full((B * H * D + 8,), float("nan"), dtype=out_dtype, device=DEV)
+        out = store[off:off + B * H * D].view(B, H, D)
+        st = _status()
+        ops.swa_decode(q.to(DEV), kv_d[0], kv_d[1], table.to(DEV), lens_d, window_left=wl, out=out, status=st)
+        torch.cuda.synchronize()
+        assert st.item() == 0 and torch.isfinite(out.float()).all()
+        assert torch.isnan(store[:off].float()).all() and torch.isnan(store[off + B * H * D:].float()).all()
+        outs.append(out.clone())
+    assert torch.equal(outs[0], outs[1])
+    a = outs[0].float().cpu()
+    tgt = ref.to(out_dtype).float()
+    assert float((a - tgt).abs().max()) <= ATTN_MAX_ABS and mean_rel(a, tgt) <= ATTN_MEAN_REL
