@@ -171,7 +171,8 @@ gla_scan_kernel(const T* __restrict__ q, const T* __restrict__ k, const T* __res
     if (tb + kScanTokens < t1) prefetch(tb + kScanTokens);
     __syncthreads();
     if (!s_plain[0]) {
-      for (int tt = 0; tt < nt; ++tt) {
+      // one token of the round: the state update and the read-out of this thread's rows and columns
+      auto token = [&](int tt) {
         const float4 vv = s_v[tt][c4];
         const f32x2 v0 = pack2(vv.x, vv.x), v1 = pack2(vv.y, vv.y), v2 = pack2(vv.z, vv.z), v3 = pack2(vv.w, vv.w);
         f32x2 o0 = 0ull, o1 = 0ull, o2 = 0ull, o3 = 0ull;   // per column: (sum over even rows, sum over odd rows)
@@ -196,6 +197,13 @@ gla_scan_kernel(const T* __restrict__ q, const T* __restrict__ k, const T* __res
         unpack2(o2, lo, hi); o.z = lo + hi;
         unpack2(o3, lo, hi); o.w = lo + hi;
         s_o[tt][r0][c4] = o;
+      };
+      if (nt == kScanTokens) {
+        // a full round, unrolled: the loads of the next token overlap the arithmetic of this one
+#pragma unroll
+        for (int tt = 0; tt < kScanTokens; ++tt) token(tt);
+      } else {
+        for (int tt = 0; tt < nt; ++tt) token(tt);
       }
 #pragma unroll
       for (int i = 0; i < PPT; ++i) {
