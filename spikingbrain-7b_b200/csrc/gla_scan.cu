@@ -30,6 +30,27 @@ __device__ __forceinline__ float scan_from_f32<float>(float x) { return x; }
 template <>
 __device__ __forceinline__ __nv_bfloat16 scan_from_f32<__nv_bfloat16>(float x) { return __float2bfloat16_rn(x); }
 
+// four consecutive outputs: one vector store where the address allows it
+__device__ __forceinline__ void scan_store4(float* p, float4 a) {
+  if ((reinterpret_cast<uintptr_t>(p) & 15u) == 0) {
+    *reinterpret_cast<float4*>(p) = a;
+  } else {
+    p[0] = a.x; p[1] = a.y; p[2] = a.z; p[3] = a.w;
+  }
+}
+__device__ __forceinline__ void scan_store4(__nv_bfloat16* p, float4 a) {
+  if ((reinterpret_cast<uintptr_t>(p) & 7u) == 0) {
+    __nv_bfloat162 lo = __floats2bfloat162_rn(a.x, a.y), hi = __floats2bfloat162_rn(a.z, a.w);
+    uint2 w;
+    w.x = *reinterpret_cast<uint32_t*>(&lo);
+    w.y = *reinterpret_cast<uint32_t*>(&hi);
+    *reinterpret_cast<uint2*>(p) = w;
+  } else {
+    p[0] = __float2bfloat16_rn(a.x); p[1] = __float2bfloat16_rn(a.y);
+    p[2] = __float2bfloat16_rn(a.z); p[3] = __float2bfloat16_rn(a.w);
+  }
+}
+
 constexpr int kScanTokens = 8;   // tokens staged per round
 
 // Two fp32 values in one 64-bit register, for the packed fp32 instructions of sm_100
@@ -93,7 +114,6 @@ gla_scan_kernel(const T* __restrict__ q, const T* __restrict__ k, const T* __res
   __shared__ int s_plain[1];        // 1: this round runs the plain recurrence
   __shared__ float4 s_v[kScanTokens][TPR];
   __shared__ float4 s_o[kScanTokens][GROUPS][TPR];
-  __shared__ float s_sq[2][8];
 
   float4* tile = reinterpret_cast<float4*>(state + ((slot * H + h) * (int64_t)D) * D);
   // SP[i][c] = (S[row, col c], S[row + 1, col c]) for row = 2 (r0 + i GROUPS) and the thread's four
@@ -239,34 +259,36 @@ gla_scan_kernel(const T* __restrict__ q, const T* __restrict__ k, const T* __res
       }
     }
     __syncthreads();
-    // ---- finish the read-out: sum the row groups, one output element per thread and trip ----
-    // (nt * D is a multiple of 32, so a warp is valid or idle as a whole; a token's D outputs
-    // sit in D/32 consecutive warps of one trip)
-    for (int base = 0, trip = 0; base < nt * D; base += 256, ++trip) {
+    // ---- finish the read-out: sum the row groups; a thread takes four outputs of one token ----
+    // (a token's D outputs sit in TPR consecutive lanes: one warp for D = 128, half a warp for
+    // D = 64, so the sum of squares of the fused norm is a shuffle reduction, no barrier)
+    for (int base = 0; base < nt * TPR; base += 256) {
       const int idx = base + tid;
-      const bool valid = idx < nt * D;
-      const int tt = valid ? idx / D : 0, d = valid ? idx - tt * D : 0;
-      float acc = 0.f;
+      const bool valid = idx < nt * TPR;
+      const int tt = valid ? idx / TPR : 0, c = valid ? idx - tt * TPR : 0;
+      float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
       if (valid) {
-        const float* so = reinterpret_cast<const float*>(&s_o[tt][0][0]);
 #pragma unroll
-        for (int gi = 0; gi < GROUPS; ++gi) acc += so[gi * D + d];
+        for (int gi = 0; gi < GROUPS; ++gi) {
+          const float4 p = s_o[tt][gi][c];
+          acc.x += p.x; acc.y += p.y; acc.z += p.z; acc.w += p.w;
+        }
       }
       if (fu.norm_weight != nullptr) {
-        float sq = acc * acc;
+        float sq = acc.x * acc.x + acc.y * acc.y + acc.z * acc.z + acc.w * acc.w;
 #pragma unroll
-        for (int off = 16; off > 0; off >>= 1) sq += __shfl_xor_sync(0xffffffffu, sq, off);
-        if ((tid & 31) == 0) s_sq[trip & 1][tid >> 5] = sq;
-        __syncthreads();
-        constexpr int WPT = D / 32;
-        const int w0 = ((tid >> 5) / WPT) * WPT;
-        float tot = 0.f;
-#pragma unroll
-        for (int w = 0; w < WPT; ++w) tot += s_sq[trip & 1][w0 + w];
-        acc = acc * rsqrtf(tot / D + fu.norm_eps) *
-              scan_to_f32(reinterpret_cast<const T*>(fu.norm_weight)[d]);
+        for (int off = TPR / 2; off > 0; off >>= 1) sq += __shfl_xor_sync(0xffffffffu, sq, off);
+        const float rs = rsqrtf(sq / D + fu.norm_eps);
+        const T* w = reinterpret_cast<const T*>(fu.norm_weight) + 4 * c;
+        acc.x = acc.x * rs * scan_to_f32(w[0]);
+        acc.y = acc.y * rs * scan_to_f32(w[1]);
+        acc.z = acc.z * rs * scan_to_f32(w[2]);
+        acc.w = acc.w * rs * scan_to_f32(w[3]);
       }
-      if (valid) out[((int64_t)(tb + tt) * H + h) * D + d] = scan_from_f32<TO>(acc);
+      if (valid) {
+        TO* op = out + ((int64_t)(tb + tt) * H + h) * D + 4 * c;
+        scan_store4(op, acc);
+      }
     }
     // the next round's staging only touches s_q/s_k/s_d/s_v, and its first barrier orders the
     // reads of s_o above before the next writes to s_o
