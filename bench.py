@@ -36,9 +36,10 @@ H, KVH, D, WINDOW_LEFT, BLOCK = 28, 4, 128, 4096, 16
 N_SWA, N_GLA = 14, 14
 NOMINAL_HBM_GBS = 8000.0
 FALLBACK_HBM_GBS = 6650.0
-# DRAM bytes moved per algorithmic byte by the sliding-window decode kernel, from the ncu capture
-# summarised in profiles/swa_decode_kernel_b256_ctx8192.md (2.1582 GB read + 6.5 MB written for
-# 2.1481 GB of visible K/V: no re-reads). Traffic grows in proportion to the tokens read.
+# DRAM bytes moved per algorithmic byte by the sliding-window decode kernel: a constant taken from
+# one ncu capture of one launch at this batch and context (dram__bytes_read.sum 2.1582 GB +
+# dram__bytes_write.sum 6.5 MB for 2.1481 GB of visible K/V: no re-reads), not measured in this
+# run. Traffic grows in proportion to the tokens read.
 SWA_TRAFFIC_PER_ALGORITHMIC_BYTE = (2.158249e9 + 6.497536e6) / (256 * 4097 * 2048)
 
 
@@ -118,7 +119,7 @@ def use_all_host_threads():
     return torch.get_num_threads()
 
 
-def cpu_baseline(args, sample_seqs=8, repeats=3):
+def cpu_baseline(args, sample_seqs=8, repeats=5):
     cores = use_all_host_threads()
     t = cpu_reference_step_seconds(sample_seqs, args.ctx + 1, repeats)
     per_seq_layerpair = t / sample_seqs
@@ -181,6 +182,56 @@ class ClockSampler:
                 "samples": len(sm)}
 
 
+# ------------------------------------------------------------------------ instrumentation
+class Instrument:
+    """The benchmark's own bookkeeping around the library calls it goes through (the library
+    carries none): `launches` counts the kernels launched through spikingbrain_7b_b200.ops, and
+    while `timing` is a list every swa_decode call appends a (start, end) pair of CUDA events
+    recorded on the launching stream around its kernel. Installed by wrapping the functions of
+    the ops module once per process."""
+    _installed = None
+
+    def __init__(self, ops, abi):
+        import torch
+        self.launches = 0
+        self.timing = None
+        count = {
+            "kv_append": lambda a, kw: 1, "rope_kv_append": lambda a, kw: 1, "kv_gather": lambda a, kw: 1,
+            "swa_decode": lambda a, kw: -(-a[0].shape[0] // 1024), "gla_step": lambda a, kw: 1,
+            "swa_prefill": lambda a, kw: 1, "swa_prefill_dense": lambda a, kw: 1, "plan_step": lambda a, kw: 1,
+            "release_rows": lambda a, kw: 1,
+            # chunk-parallel form: local scan + carry + scan proper
+            "gla_scan": lambda a, kw: 3 if kw.get("workspace") is not None and abi.lib.sbk_gla_scan_workspace_bytes(
+                a[5].numel() - 1, int(kw.get("max_query_len", 0)), a[0].shape[1], a[0].shape[2]) else 1,
+        }
+        for name, n_of in count.items():
+            inner = getattr(ops, name)
+
+            def wrapped(*a, _inner=inner, _n=n_of, _name=name, **kw):
+                timing = self.timing if _name == "swa_decode" else None
+                if timing is not None:
+                    # external: inside a stream capture these become event-record nodes of the
+                    # graph, so the pair times the launch of the latest replay
+                    ev0 = torch.cuda.Event(enable_timing=True, external=True)
+                    ev1 = torch.cuda.Event(enable_timing=True, external=True)
+                    ev0.record()
+                out = _inner(*a, **kw)
+                if timing is not None:
+                    ev1.record()
+                    timing.append((ev0, ev1))
+                self.launches += _n(a, kw)
+                return out
+
+            setattr(ops, name, wrapped)
+
+    @classmethod
+    def install(cls):
+        if cls._installed is None:
+            from spikingbrain_7b_b200 import _abi, ops
+            cls._installed = cls(ops, _abi)
+        return cls._installed
+
+
 # -------------------------------------------------------------------------- the engine
 class DecodeEngine:
     """Holds the per-layer caches of one GPU and runs decode steps through the reference-facing
@@ -197,6 +248,7 @@ class DecodeEngine:
         from spikingbrain_7b_b200.block_pool import DeviceStepPlanner
         from spikingbrain_7b_b200.gla_slots import GLACacheManager, my_fused_recurrent_gla
         self.torch, self.np, self.ops = torch, np, ops
+        self.instr = Instrument.install()
         self.Meta = MetaAttentionMetadata
         self.gla_fn = my_fused_recurrent_gla
         self.device = device
@@ -274,10 +326,10 @@ class DecodeEngine:
                 j = i & 1
                 # three of the sliding-window launches carry timing events (first, middle, last layer):
                 # an event node between two kernels costs the overlap of their tail and head
-                ops.SWA_TIMING = timing if i in (0, self.n_swa // 2, self.n_swa - 1) else None
+                self.instr.timing = timing if i in (0, self.n_swa // 2, self.n_swa - 1) else None
                 self.impls[i].forward(None, self.q[j], self.k[j], self.v[j], None, None, None, self.kv[i],
                                       meta, output=self.out)
-                ops.SWA_TIMING = None
+                self.instr.timing = None
 
     def step(self, e2e=False):
         """One decode step: the planner launch and the layers' kernels -- replayed from a captured
@@ -308,7 +360,6 @@ class DecodeEngine:
         side = torch.cuda.Stream(device=self.device)
         side.wait_stream(torch.cuda.current_stream())
         g = torch.cuda.CUDAGraph()
-        launches0 = ops.LAUNCHES
         with torch.cuda.stream(side):
             if e2e:
                 self._e2e_setup()
@@ -321,11 +372,11 @@ class DecodeEngine:
                 self.graph_e2e = g
             else:
                 self.enqueue_layers(meta)
-                launches0 = ops.LAUNCHES
+                launches0 = self.instr.launches
                 self.swa_events = []
                 with torch.cuda.graph(g, stream=side):
                     self.enqueue_layers(meta, timing=self.swa_events)
-                self.launches_per_step = ops.LAUNCHES - launches0
+                self.launches_per_step = self.instr.launches - launches0
                 self.graph = g
         torch.cuda.current_stream().wait_stream(side)
         torch.cuda.synchronize()
@@ -497,14 +548,14 @@ def run_b200(args):
     for _ in range(max(args.warmup, 3)):
         eng.step()
     if args.no_graph:
-        launches0 = ops.LAUNCHES
+        launches0 = eng.instr.launches
         timing = []
         _orig = eng.enqueue_layers
         eng.enqueue_layers = lambda meta, timing=timing: _orig(meta, timing=timing)
         total_ms = timed(args.steps, e2e=False)
         torch.cuda.synchronize()
         swa_ms.extend(a.elapsed_time(b) for a, b in timing)
-        launches = ops.LAUNCHES - launches0
+        launches = eng.instr.launches - launches0
         eng.enqueue_layers = _orig
     else:
         eng.capture()
@@ -529,7 +580,15 @@ def run_b200(args):
                    "h2d_bytes_per_step": eng.h2d_bytes // args.steps,
                    "d2h_bytes_per_step": eng.d2h_bytes // args.steps, "ms_per_step": e2e_ms}
 
-    status = sum(impl.status() for impl in eng.impls)
+    # every status word of the run: the layers' kernels and the planner (a step the planner refuses
+    # -- out of blocks, table full -- fills the slot mapping with -1 and appends nothing, so a run
+    # that saw one has not timed the workload)
+    status = 0
+    for impl in eng.impls:
+        status |= impl.status()
+    status |= int(eng.plan.status.item())
+    if status != 0:
+        raise SystemExit(f"rank {rank}: device status {status} after the timed steps; the run is void")
     if rank != 0:
         if world > 1:
             dist.destroy_process_group()
@@ -567,8 +626,8 @@ def run_b200(args):
                      "algorithmic_bytes_per_launch": swa_layer_bytes, "avg_launch_ms": swa_avg_ms,
                      "launches_timed": len(swa_ms),
                      "traffic": int(swa_layer_bytes * SWA_TRAFFIC_PER_ALGORITHMIC_BYTE),
-                     "traffic_source": "ncu dram__bytes_read.sum + dram__bytes_write.sum of one launch of the same "
-                                       "batch and context (profiles/swa_decode_kernel_b256_ctx8192.md), scaled by tokens"},
+                     "traffic_source": "constant from an ncu capture (dram__bytes_read.sum + dram__bytes_write.sum of "
+                                       "one launch at this batch and context), scaled by tokens; not measured in this run"},
         "e2e": e2e_obj, "gpu_launches": launches, "clocks": clocks, "device_status": status,
     }
     if not args.no_cpu_baseline:

@@ -29,7 +29,7 @@
 extern "C" {
 #endif
 
-#define SBK_ABI_VERSION 4
+#define SBK_ABI_VERSION 5
 
 /* element type codes */
 #define SBK_BF16 0
@@ -114,17 +114,26 @@ int sbk_kv_gather(const void* k_cache, const void* v_cache, const int32_t* block
  *  out          [B, H, D] of `out_dtype` (SBK_BF16 or SBK_F32), `out_seq_stride` elements
  *  lse_out      [B, H] float natural-log-sum-exp of the scaled scores, or NULL
  *  workspace    at least sbk_swa_workspace_bytes(B,H,D,max_pieces) bytes, 16-byte aligned. It
- *               begins with the work-ticket counter and one completion counter per sequence
- *               (16 + 4*roundup(B,4) bytes): these must be ZERO before the first call with a
+ *               begins with the work-ticket counters and one completion counter per sequence
+ *               (32 + 4*roundup(B,4) bytes): these must be ZERO before the first call with a
  *               given buffer and B, and every call that ends without SBK_ST_WAIT_TIMEOUT leaves
- *               them zero. Split-K partials follow. Calls that overlap on the GPU need
- *               separate workspaces.
+ *               them zero. A call in which a wait ran out leaves them where they stood and
+ *               MARKS the workspace: every later call given it raises SBK_ST_WAIT_TIMEOUT again
+ *               and computes nothing, so the fault cannot turn into silently wrong rows; zero
+ *               those leading bytes (or the whole buffer) to use it again. Split-K partials
+ *               follow. Calls that overlap on the GPU need separate workspaces.
  *  key2,value2  [num_meta, kvh, D] bf16 contiguous "meta" (sink) tokens that every query sees on top of
  *               its window -- the second attention pass over k2/v2 and the log-sum-exp merge of
  *               fa_kernel_metatoken.py:124-194, done here as extra leading tiles of the same
  *               softmax; num_meta a multiple of 16, 0 (with NULLs) for none
- *  split_chunks target number of 16-token chunks per split (<=0: library default)
- *  max_pieces   upper bound on splits per sequence (grid.x); >= 1
+ *  split_chunks how a sequence is split over CTAs.  > 0: fixed pieces of that many 16-token
+ *               chunks, handed to the CTAs through a ticket counter.  < 0: balanced mode -- the
+ *               chunks of the whole batch are cut into one equal run per CTA, and -split_chunks
+ *               is the shortest run allowed (with max_pieces == 1 this degrades to whole
+ *               sequences).  0: fixed pieces of 32 chunks. The Python wrapper's default is -8.
+ *  max_pieces   upper bound on the pieces of one sequence (sizes the workspace); >= 1
+ *  item_cost    balanced mode only: what starting and finishing a sequence is charged, in chunks,
+ *               when the runs are made equal in cost (< 0: the library's tuned value, 8)
  * Supported: D == 128, H % kvh == 0, H/kvh <= 8, kvh in {1,2,4}, block_size % 16 == 0.
  */
 size_t sbk_swa_workspace_bytes(int B, int H, int D, int max_pieces);
@@ -138,24 +147,27 @@ int sbk_swa_decode(const void* q, int64_t q_seq_stride, const void* k_cache, con
                    int64_t cache_block_stride_bytes, int window_left, float scale,
                    void* out, int out_dtype, int64_t out_seq_stride, float* lse_out,
                    void* workspace, size_t workspace_bytes, int split_chunks, int max_pieces,
-                   const void* key2, const void* value2, int num_meta,
+                   int item_cost, const void* key2, const void* value2, int num_meta,
                    int32_t* status, void* stream);
 
 /*
  * sbk_swa_decode for callers that cannot allocate device memory -- a server that gave all free
  * HBM to its KV pool at start-up, a loop that forbids allocator calls once running, a binding
- * with no tensor library behind it. No counterpart in the reference. Same arguments as
- * sbk_swa_decode without `workspace`: the scratch is a fixed array of
- * sbk_swa_static_scratch_bytes() (16 MiB) inside the library, resident on every GPU that loads
- * the library until the process ends.
+ * with no tensor library behind it. No counterpart in the reference. The arguments of
+ * sbk_swa_decode without `workspace`, `item_cost` (library value) and the sink tokens
+ * key2/value2/num_meta (not served here: use sbk_swa_decode for layers that have them): the
+ * scratch is a fixed array of sbk_swa_static_scratch_bytes() (16 MiB) inside the library,
+ * resident on every GPU that loads the library until the process ends.
  *  - sbk_swa_workspace_bytes(B, H, D, max_pieces) must not exceed that size, else
  *    SBK_E_WORKSPACE is returned and nothing is launched (with one piece per sequence any B up
  *    to about four million fits; with 9 pieces and 28 heads B up to 128).
  *  - The first call on a device looks the array's device address up; make that call before
  *    starting a stream capture. The call itself performs no allocation of any kind.
  *  - All calls share the one array: two calls whose kernels can overlap on the GPU (different
- *    streams, no dependency) race on it. Calls on one stream are safe; the counters are
- *    cleared on `stream` at the start of every call.
+ *    streams, no dependency) race on it. Calls on one stream are safe; the counters (and the
+ *    mark a timed-out call leaves) are cleared on `stream` at the start of every call.
+ *  - The per-device address table behind the first-call look-up is not locked: make the first
+ *    call on a device from one thread.
  */
 size_t sbk_swa_static_scratch_bytes(void);
 int sbk_swa_decode_static(const void* q, int64_t q_seq_stride, const void* k_cache, const void* v_cache,
@@ -181,7 +193,7 @@ int sbk_swa_decode_static(const void* q, int64_t q_seq_stride, const void* k_cac
  * sbk_peer_wait on its own flag array.
  *  - flag values grow by one per step and are never reused; the caller alternates between two
  *    gathered buffers so that a peer one step ahead does not store into rows still being read.
- *  - `workspace` as for sbk_swa_decode; its first 16 bytes must be zero at the first call.
+ *  - `workspace`, `split_chunks`, `max_pieces`, `item_cost` as for sbk_swa_decode.
  *  - No collective library call, no multicast object, no copy through a tensor map: peers are
  *    reached by stores only.
  *
@@ -204,8 +216,8 @@ int sbk_swa_decode_gather(const void* q, int64_t q_seq_stride, const void* k_cac
                           int B, int H, int kvh, int D, int64_t num_blocks, int block_size,
                           int64_t cache_block_stride_bytes, int window_left, float scale,
                           void* out, int64_t out_seq_stride, void* workspace, size_t workspace_bytes,
-                          int split_chunks, int max_pieces, const void* key2, const void* value2,
-                          int num_meta, void* const* peer_out, int32_t* const* peer_flag, int n_peer,
+                          int split_chunks, int max_pieces, int item_cost, const void* key2,
+                          const void* value2, int num_meta, void* const* peer_out, int32_t* const* peer_flag, int n_peer,
                           int32_t flag_value, const int32_t* flag_base, int32_t* status, void* stream);
 /* The GLA step of a head-sharded layer with the same delivery: arguments as sbk_gla_step (bf16 in
  * and out), `out` = this rank's head slice of its gathered buffer with `out_seq_stride` elements
@@ -290,7 +302,8 @@ int sbk_rope_kv_append(void* query, int H, int64_t q_token_stride_bytes, void* k
  *
  * sbk_pool_init: ring <- 0..num_blocks-1, counters reset; seq_lens <- 0 and block_tables <- -1
  * when given. sbk_release_rows: rows [n_rows] int32 name finished sequences; their live blocks go
- * back on the ring, their entries become -1 and their lengths 0.
+ * back on the ring, their entries become -1 and their lengths 0. A row named more than once is
+ * released once.
  */
 int sbk_pool_init(int32_t* ring, uint64_t* ctrl, int num_blocks, int32_t* seq_lens,
                   int32_t* block_tables, int max_blocks, int B, void* stream);
@@ -353,14 +366,21 @@ int sbk_gla_step(const void* q, const void* k, const void* v, const void* g, int
  *  out          [T, H, D] bf16, `out_tok_stride` elements between tokens
  *  key2,value2,num_meta  sink tokens as in sbk_swa_decode (the k2/v2 pass of
  *               fa_kernel_metatoken.py:198-280), or NULL, NULL, 0
+ *  kernel       SBK_PREFILL_AUTO: the tcgen05 kernel (tensor memory, 128-key tiles) when q and out
+ *               are 16-byte aligned with token strides that are multiples of 8 elements, else the
+ *               mma.sync kernel; SBK_PREFILL_TCGEN05 / SBK_PREFILL_MMA_SYNC force one (the former
+ *               returns SBK_E_ALIGN when q / out do not meet its rule)
  * Supported: D == 128, H % kvh == 0, H/kvh <= 8, block_size % 16 == 0.
  */
+#define SBK_PREFILL_AUTO 0
+#define SBK_PREFILL_TCGEN05 1
+#define SBK_PREFILL_MMA_SYNC 2
 int sbk_swa_prefill(const void* q, int64_t q_tok_stride, const void* k_cache, const void* v_cache,
                     const int32_t* block_tables, int max_blocks, const int32_t* query_start_loc,
                     const int32_t* context_lens, int n_seqs, int max_query_len, int H, int kvh, int D,
                     int64_t num_blocks, int block_size, int64_t cache_block_stride_bytes,
                     int window_left, float scale, void* out, int64_t out_tok_stride,
-                    const void* key2, const void* value2, int num_meta,
+                    const void* key2, const void* value2, int num_meta, int kernel,
                     int32_t* status, void* stream);
 
 /*
@@ -402,12 +422,27 @@ int sbk_swa_prefill_dense(const void* q, int64_t q_tok_stride, const void* key, 
  *               modeling_gla_swa.py:391-414) instead of reading the slot
  *  out          [T, H, D] of out_dtype
  *  fuse_flags, gate_normalizer, norm_weight, norm_eps   as in sbk_gla_step
+ *  max_query_len, workspace, workspace_bytes
+ *               the chunk-parallel form, which the reference reaches through chunk_gla /
+ *               fused_chunk_gla spreading one sequence over the GPU: given the longest run of the
+ *               call (host value) and sbk_gla_scan_workspace_bytes(n_seqs, max_query_len, H, D)
+ *               bytes of 16-byte aligned scratch (contents irrelevant before, meaningless after),
+ *               a call whose (sequence, head) chains would fill less than half of the GPU cuts
+ *               every run into sub-chunks: a local scan of each from a zero state, a carry of the
+ *               states from sub-chunk to sub-chunk, and the scan proper of every sub-chunk from its
+ *               true incoming state -- three launches. The sum is the same in another association:
+ *               state and outputs agree with the one-chain scan to fp32 rounding, not bit for
+ *               bit. workspace NULL or max_query_len <= 0: one chain per (sequence, head), whose
+ *               result does not depend on how the tokens were cut into calls. The size query
+ *               returns 0 when the call would not be cut (nothing to allocate).
  */
+size_t sbk_gla_scan_workspace_bytes(int n_seqs, int max_query_len, int H, int D);
 int sbk_gla_scan(const void* q, const void* k, const void* v, const void* g, int in_dtype,
                  const int32_t* query_start_loc, int n_seqs, float* state, int64_t num_slots,
                  const int64_t* slot_idx, const uint8_t* reset, int H, int Hkv, int D, float scale,
                  void* out, int out_dtype, int fuse_flags, float gate_normalizer,
-                 const void* norm_weight, float norm_eps, int32_t* status, void* stream);
+                 const void* norm_weight, float norm_eps, int max_query_len, void* workspace,
+                 size_t workspace_bytes, int32_t* status, void* stream);
 
 #ifdef __cplusplus
 }

@@ -8,14 +8,14 @@ import os
 from ctypes import c_char_p, c_float, c_int, c_int32, c_int64, c_size_t, c_void_p
 
 PKG_DIR = os.path.dirname(os.path.abspath(__file__))
-# SBK_LIB_PATH points the binding at another build of the same sources (profiling variants)
-LIB_PATH = os.environ.get("SBK_LIB_PATH") or os.path.join(PKG_DIR, "libsbk.so")
+LIB_PATH = os.path.join(PKG_DIR, "libsbk.so")
 
 SBK_BF16, SBK_F32 = 0, 1
+PREFILL_AUTO, PREFILL_TCGEN05, PREFILL_MMA_SYNC = 0, 1, 2
 SBK_OK, SBK_E_ARG, SBK_E_ALIGN, SBK_E_WORKSPACE, SBK_E_LAUNCH = 0, -1, -2, -3, -4
 ST_BAD_SLOT, ST_BAD_BLOCK, ST_WAIT_TIMEOUT, ST_RETIRE_OVERFLOW, ST_BAD_POSITION = 1, 2, 4, 8, 16
 ST_OUT_OF_BLOCKS, ST_TABLE_FULL = 32, 64
-ABI_VERSION = 4
+ABI_VERSION = 5
 
 # name -> (restype, argtypes); must list every function include/sbk.h declares
 SIGNATURES = {
@@ -33,15 +33,16 @@ SIGNATURES = {
     "sbk_swa_decode": (c_int, [
         c_void_p, c_int64, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_int,
         c_int, c_int64, c_int, c_int64, c_int, c_float, c_void_p, c_int, c_int64, c_void_p,
-        c_void_p, c_size_t, c_int, c_int, c_void_p, c_void_p, c_int, c_void_p, c_void_p]),
+        c_void_p, c_size_t, c_int, c_int, c_int, c_void_p, c_void_p, c_int, c_void_p, c_void_p]),
     "sbk_swa_prefill": (c_int, [
         c_void_p, c_int64, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_int, c_int,
         c_int, c_int, c_int, c_int64, c_int, c_int64, c_int, c_float, c_void_p, c_int64, c_void_p,
-        c_void_p, c_int, c_void_p, c_void_p]),
+        c_void_p, c_int, c_int, c_void_p, c_void_p]),
+    "sbk_gla_scan_workspace_bytes": (c_size_t, [c_int, c_int, c_int, c_int]),
     "sbk_gla_scan": (c_int, [
         c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int, c_void_p, c_int64, c_void_p,
         c_void_p, c_int, c_int, c_int, c_float, c_void_p, c_int, c_int, c_float, c_void_p, c_float,
-        c_void_p, c_void_p]),
+        c_int, c_void_p, c_size_t, c_void_p, c_void_p]),
     "sbk_swa_static_scratch_bytes": (c_size_t, []),
     "sbk_swa_decode_static": (c_int, [
         c_void_p, c_int64, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_int,
@@ -50,7 +51,8 @@ SIGNATURES = {
     "sbk_swa_decode_gather": (c_int, [
         c_void_p, c_int64, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_int,
         c_int, c_int64, c_int, c_int64, c_int, c_float, c_void_p, c_int64, c_void_p, c_size_t,
-        c_int, c_int, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_int, c_int32, c_void_p, c_void_p, c_void_p]),
+        c_int, c_int, c_int, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_int, c_int32, c_void_p, c_void_p,
+        c_void_p]),
     "sbk_gla_step_gather": (c_int, [
         c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_void_p, c_int, c_int, c_int, c_int,
         c_float, c_void_p, c_int64, c_int, c_float, c_void_p, c_float, c_void_p, c_void_p, c_void_p, c_int,

@@ -7,16 +7,19 @@ helper types the reference leans on (`AttentionType`, `PAD_SLOT_ID`, the slot-ma
 helpers) are restated here from their documented behaviour.
 
 What runs where
-  cache write         -> sbk_kv_append   (reference: reshape_and_cache_flash, :790-799)
+  cache write         -> sbk_kv_append / sbk_rope_kv_append (reference: reshape_and_cache_flash, :790-799)
   one-token decode    -> sbk_swa_decode  (reference: flash-attn fwd_kvcache, :955-981)
   prefill with tables -> sbk_swa_prefill (reference: flash-attn varlen forward with block
-                         tables, :900-919): 16 query tokens x one kv group per CTA
+                         tables, :900-919): 16 query tokens x one kv group per CTA, tcgen05
+  prompt run without block tables (the un-chunked first prompt, the memory-profiling run)
+                      -> sbk_swa_prefill_dense over key/value as passed (reference :843-884)
+  multi-token decode  -> sbk_swa_prefill, the queries being the tail of each sequence (:924-953)
   meta tokens         -> key2/value2 are streamed as extra always-visible leading tiles of the same
                          softmax (reference: second flash-attn pass + LSE merge,
-                         fa_kernel_metatoken.py:124-194); query2 is not supported
-  prefill without block tables (the profile run / un-paged prompt), multi-token
-  "varlen" decode, query2, fp8 KV, ALiBi, soft-cap, encoder and cross attention
-                                         -> NotImplementedError, never a fallback.
+                         fa_kernel_metatoken.py:124-194); the meta tokens' own queries (query2) run
+                         non-causally over key2/value2 through sbk_swa_prefill_dense (:262-280)
+  fp8 KV, ALiBi, soft-cap, encoder and cross attention, head sizes the kernels are not built for
+                      -> NotImplementedError, never a fallback.
 """
 from collections import defaultdict
 from dataclasses import dataclass
@@ -439,8 +442,13 @@ class MetaAttentionImpl:
         return ws
 
     def status(self) -> int:
-        """Device-side status bits accumulated by this layer's kernels (synchronises)."""
-        return 0 if self._status is None else int(self._status.item())
+        """Device-side status bits accumulated by this layer's kernels (synchronises). After
+        SBK_ST_WAIT_TIMEOUT the decode workspaces are stale (the kernel marks them and every later
+        call would report the timeout again): they are dropped here, the next call gets fresh ones."""
+        bits = 0 if self._status is None else int(self._status.item())
+        if bits & 4:
+            self._workspace.clear()
+        return bits
 
     def forward(self, layer, query: torch.Tensor, key: torch.Tensor, value: torch.Tensor,
                 query2: Optional[torch.Tensor], key2: Optional[torch.Tensor],

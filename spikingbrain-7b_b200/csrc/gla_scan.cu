@@ -11,6 +11,19 @@
 // Tokens are staged eight at a time through shared memory; the read-out's sum over k rows is
 // finished across the 8 row groups once per eight tokens. The same optional fused neighbours as
 // the single-token step (GlaFusion): ReLU on q/k, gate logits -> log-decay, per-head RMS norm.
+//
+// Chunk-parallel form (a few long sequences, e.g. one 8192-token prompt chunk per GPU, which as
+// one chain per (sequence, head) would occupy 28 of 296 CTA slots): a run is cut into sub-chunks
+// of `sub_len` tokens that different CTAs own.
+//   pass 1  (kScanLocal)  every sub-chunk but a sequence's last one is scanned WITHOUT read-out
+//           (one multiply-add per state element and token instead of two): sub-chunk 0 from the
+//           sequence's true incoming state, the others from zero. It leaves its end state L_j and
+//           the product of its decays per key row, P_j = exp(sum_t g_t), in the workspace.
+//   carry   S_in(1) = L_0;  S_in(j+1) = diag(P_j) S_in(j) + L_j  -- element-wise, in place over L_j.
+//   pass 2  (kScanFull)   every sub-chunk is scanned with read-out from its true incoming state;
+//           the last one writes the sequence's state back.
+// The recurrence is linear in the state, so this is the same sum in another association: results
+// agree with the one-chain scan to fp32 rounding (a few 1e-7 relative), not bit for bit.
 #include <math.h>
 
 #include "sbk_common.cuh"
@@ -76,27 +89,43 @@ __device__ __forceinline__ f32x2 fmul2(f32x2 a, f32x2 b) {
   return d;
 }
 
-template <typename T, typename TO, int D>
+enum : int { kScanFull = 0, kScanLocal = 1 };
+
+// Where the sub-chunks of the chunk-parallel form keep their states: tiles [n_seqs][n_sub-1][H][D*D]
+// then decay products [n_seqs][n_sub-1][H][D]; n_sub == 1: one chain per (sequence, head), unused.
+struct ScanSplit {
+  float* tiles; float* decays; int n_sub; int sub_len;
+};
+
+template <typename T, typename TO, int D, int MODE>
 __global__ void __launch_bounds__(256, 2)
 gla_scan_kernel(const T* __restrict__ q, const T* __restrict__ k, const T* __restrict__ v,
                 const T* __restrict__ g, const int32_t* __restrict__ query_start_loc,
                 float* __restrict__ state, int64_t num_slots, const int64_t* __restrict__ slot_idx,
                 const uint8_t* __restrict__ reset, int H, int Hkv, float scale, TO* __restrict__ out,
-                int32_t* status, const GlaFusion fu) {
+                int32_t* status, const GlaFusion fu, const ScanSplit sp) {
   constexpr int TPR = D / 4;          // threads per state row
   constexpr int GROUPS = 256 / TPR;   // row groups
   constexpr int RPT = D / GROUPS;     // rows per thread
   constexpr int PPT = RPT / 2;        // ... held as pairs of adjacent rows: 2 (r0 + i GROUPS), + 1
   static_assert(RPT % 2 == 0, "rows are paired");
   const int h = blockIdx.x;
-  const int s = blockIdx.y;
-  const int t0 = query_start_loc[s], t1 = query_start_loc[s + 1];
+  const int s = blockIdx.y / sp.n_sub;
+  const int sub = blockIdx.y - s * sp.n_sub;       // sub-chunk of the run (0 when runs are not cut)
+  const int run0 = query_start_loc[s], run1 = query_start_loc[s + 1];
   const int64_t slot = slot_idx ? slot_idx[s] : (int64_t)s;
-  if (slot < 0 || t1 <= t0) return;
+  if (slot < 0 || run1 <= run0) return;
   if (slot >= num_slots) {
-    if (threadIdx.x == 0) raise_status(status, SBK_ST_BAD_SLOT);
+    if (threadIdx.x == 0 && sub == 0 && MODE == kScanFull) raise_status(status, SBK_ST_BAD_SLOT);
     return;
   }
+  const int t0 = sp.n_sub > 1 ? run0 + sub * sp.sub_len : run0;
+  const int t1 = sp.n_sub > 1 && t0 + sp.sub_len < run1 ? t0 + sp.sub_len : run1;
+  if (t0 >= run1) return;                           // the run is shorter than this sub-chunk's start
+  const bool last_sub = t1 == run1;
+  if (MODE == kScanLocal && last_sub) return;       // nobody needs the local state of the last sub-chunk
+  // tile of this (sequence, sub-chunk, head) in the workspace, and the one before it
+  const int64_t ws_idx = ((int64_t)s * (sp.n_sub - 1) + sub) * H + h;
   const int hk = h / (H / Hkv);
   const int tid = threadIdx.x;
   const int c4 = tid % TPR, r0 = tid / TPR;
@@ -116,19 +145,23 @@ gla_scan_kernel(const T* __restrict__ q, const T* __restrict__ k, const T* __res
   __shared__ float4 s_o[kScanTokens][GROUPS][TPR];
 
   float4* tile = reinterpret_cast<float4*>(state + ((slot * H + h) * (int64_t)D) * D);
+  // incoming state: the slot (or zero on reset) for the head of the run; for a later sub-chunk the
+  // carried state the pass before left in the workspace (full scan) or zero (local scan)
+  const float4* tile_in = sub == 0 ? tile : reinterpret_cast<const float4*>(sp.tiles + (ws_idx - H) * (int64_t)D * D);
+  const bool from_zero = sub == 0 ? (reset && reset[s]) : MODE == kScanLocal;
   // SP[i][c] = (S[row, col c], S[row + 1, col c]) for row = 2 (r0 + i GROUPS) and the thread's four
   // columns: the two rows of a pair go through one packed FMA, their k (and q) values come as one
   // 64-bit shared-memory load
   f32x2 SP[PPT][4];
-  if (reset && reset[s]) {
+  if (from_zero) {
 #pragma unroll
     for (int i = 0; i < PPT; ++i) SP[i][0] = SP[i][1] = SP[i][2] = SP[i][3] = 0ull;
   } else {
 #pragma unroll
     for (int i = 0; i < PPT; ++i) {
       const int r = 2 * (r0 + i * GROUPS);
-      const float4 a = ld_stream_f4(tile + (int64_t)r * TPR + c4);
-      const float4 b = ld_stream_f4(tile + (int64_t)(r + 1) * TPR + c4);
+      const float4 a = ld_stream_f4(tile_in + (int64_t)r * TPR + c4);
+      const float4 b = ld_stream_f4(tile_in + (int64_t)(r + 1) * TPR + c4);
       SP[i][0] = pack2(a.x, b.x); SP[i][1] = pack2(a.y, b.y);
       SP[i][2] = pack2(a.z, b.z); SP[i][3] = pack2(a.w, b.w);
     }
@@ -150,13 +183,14 @@ gla_scan_kernel(const T* __restrict__ q, const T* __restrict__ k, const T* __res
       const int64_t tok = tb2 + st0 + u * TSTEP;
       if (tok < t1) {
         const int64_t kv_off = (tok * Hkv + hk) * D + sd;
-        pq[u] = q[(tok * H + h) * D + sd];
+        if (MODE == kScanFull) pq[u] = q[(tok * H + h) * D + sd];
         pk[u] = k[kv_off];
         pv[u] = v[kv_off];
       }
     }
   };
   prefetch(t0);
+  float g_run = 0.f;   // local scan: sum of this key row's log-decays over the sub-chunk (threads < D)
 
   for (int tb = t0; tb < t1; tb += kScanTokens) {
     const int nt = t1 - tb < kScanTokens ? t1 - tb : kScanTokens;
@@ -174,16 +208,20 @@ gla_scan_kernel(const T* __restrict__ q, const T* __restrict__ k, const T* __res
       const bool plain = __syncthreads_or(!(G > -60.f)) != 0;
       if (tid == 0) s_plain[0] = plain ? 1 : 0;
       if (tid < D) s_end[sd] = plain ? 1.f : __expf(G);
+      if (MODE == kScanLocal) g_run += G;
       float Gt = 0.f;
 #pragma unroll
       for (int tt = 0; tt < kScanTokens; ++tt) {
         Gt += gl[tt];
         if (tt < nt && tt % TSTEP == st0) {
-          float qv = scan_to_f32(pq[tt / TSTEP]);
           float kv = scan_to_f32(pk[tt / TSTEP]);
-          if (fu.relu_qk) { qv = fmaxf(qv, 0.f); kv = fmaxf(kv, 0.f); }
+          if (fu.relu_qk) kv = fmaxf(kv, 0.f);
           s_k[tt][sd] = plain ? kv : kv * __expf(-Gt);
-          s_q[tt][sd] = plain ? qv * scale : qv * scale * __expf(Gt);
+          if (MODE == kScanFull) {
+            float qv = scan_to_f32(pq[tt / TSTEP]);
+            if (fu.relu_qk) qv = fmaxf(qv, 0.f);
+            s_q[tt][sd] = plain ? qv * scale : qv * scale * __expf(Gt);
+          }
           reinterpret_cast<float*>(&s_v[tt][0])[sd] = scan_to_f32(pv[tt / TSTEP]);
         }
       }
@@ -200,16 +238,19 @@ gla_scan_kernel(const T* __restrict__ q, const T* __restrict__ k, const T* __res
         for (int i = 0; i < PPT; ++i) {
           const int r = 2 * (r0 + i * GROUPS);
           const f32x2 kk = *reinterpret_cast<const f32x2*>(&s_k[tt][r]);
-          const f32x2 qq = *reinterpret_cast<const f32x2*>(&s_q[tt][r]);
           SP[i][0] = ffma2(kk, v0, SP[i][0]);
           SP[i][1] = ffma2(kk, v1, SP[i][1]);
           SP[i][2] = ffma2(kk, v2, SP[i][2]);
           SP[i][3] = ffma2(kk, v3, SP[i][3]);
-          o0 = ffma2(qq, SP[i][0], o0);
-          o1 = ffma2(qq, SP[i][1], o1);
-          o2 = ffma2(qq, SP[i][2], o2);
-          o3 = ffma2(qq, SP[i][3], o3);
+          if (MODE == kScanFull) {
+            const f32x2 qq = *reinterpret_cast<const f32x2*>(&s_q[tt][r]);
+            o0 = ffma2(qq, SP[i][0], o0);
+            o1 = ffma2(qq, SP[i][1], o1);
+            o2 = ffma2(qq, SP[i][2], o2);
+            o3 = ffma2(qq, SP[i][3], o3);
+          }
         }
+        if (MODE == kScanLocal) return;
         float4 o;
         float lo, hi;
         unpack2(o0, lo, hi); o.x = lo + hi;
@@ -243,7 +284,7 @@ gla_scan_kernel(const T* __restrict__ q, const T* __restrict__ k, const T* __res
           for (int hf = 0; hf < 2; ++hf) {
             const int r = 2 * (r0 + i * GROUPS) + hf;
             const float d = expf(gla_gate<T>(scan_to_f32(g[((int64_t)(tb + tt) * Hkv + hk) * D + r]), fu));
-            const float kk = s_k[tt][r], qq = s_q[tt][r];
+            const float kk = s_k[tt][r], qq = MODE == kScanFull ? s_q[tt][r] : 0.f;
 #pragma unroll
             for (int c = 0; c < 4; ++c) {
               float lo, hi;
@@ -255,14 +296,15 @@ gla_scan_kernel(const T* __restrict__ q, const T* __restrict__ k, const T* __res
             }
           }
         }
-        s_o[tt][r0][c4] = make_float4(oc[0], oc[1], oc[2], oc[3]);
+        if (MODE == kScanFull) s_o[tt][r0][c4] = make_float4(oc[0], oc[1], oc[2], oc[3]);
       }
     }
     __syncthreads();
     // ---- finish the read-out: sum the row groups; a thread takes four outputs of one token ----
     // (a token's D outputs sit in TPR consecutive lanes: one warp for D = 128, half a warp for
     // D = 64, so the sum of squares of the fused norm is a shuffle reduction, no barrier)
-    for (int base = 0; base < nt * TPR; base += 256) {
+    // (a local scan has no read-out; the barrier above guards its staging buffers)
+    for (int base = 0; MODE == kScanFull && base < nt * TPR; base += 256) {
       const int idx = base + tid;
       const bool valid = idx < nt * TPR;
       const int tt = valid ? idx / TPR : 0, c = valid ? idx - tt * TPR : 0;
@@ -293,24 +335,92 @@ gla_scan_kernel(const T* __restrict__ q, const T* __restrict__ k, const T* __res
     // the next round's staging only touches s_q/s_k/s_d/s_v, and its first barrier orders the
     // reads of s_o above before the next writes to s_o
   }
+  // the end state goes to the slot (end of the run), to the workspace (local scan), or nowhere (a
+  // full scan of an inner sub-chunk: the carried states are already in the workspace)
+  float4* tile_out = tile;
+  if (MODE == kScanLocal) {
+    tile_out = reinterpret_cast<float4*>(sp.tiles + ws_idx * (int64_t)D * D);
+    if (tid < D) sp.decays[ws_idx * D + sd] = expf(g_run);
+  } else if (!last_sub) {
+    return;
+  }
 #pragma unroll
   for (int i = 0; i < PPT; ++i) {
     const int r = 2 * (r0 + i * GROUPS);
     float4 a, b;
     unpack2(SP[i][0], a.x, b.x); unpack2(SP[i][1], a.y, b.y);
     unpack2(SP[i][2], a.z, b.z); unpack2(SP[i][3], a.w, b.w);
-    st_stream_f4(tile + (int64_t)r * TPR + c4, a);
-    st_stream_f4(tile + (int64_t)(r + 1) * TPR + c4, b);
+    st_stream_f4(tile_out + (int64_t)r * TPR + c4, a);
+    st_stream_f4(tile_out + (int64_t)(r + 1) * TPR + c4, b);
   }
 }
 
+// The carry between the two passes: for every (sequence, head), S_in(1) = L_0 stays where it is and
+// S_in(j+1) = diag(P_j) S_in(j) + L_j replaces L_j for j = 1 .. n_sub-2, in order. Element-wise: a CTA
+// takes D*D/kCarrySplit elements of a tile, a thread one float4 of them per trip.
+constexpr int kCarrySplit = 8;
+template <int D>
+__global__ void __launch_bounds__(256)
+gla_scan_carry_kernel(const int32_t* __restrict__ query_start_loc, const int64_t* __restrict__ slot_idx,
+                      int64_t num_slots, int H, const ScanSplit sp) {
+  const int h = blockIdx.x / kCarrySplit, part = blockIdx.x % kCarrySplit;
+  const int s = blockIdx.y;
+  const int n_tok = query_start_loc[s + 1] - query_start_loc[s];
+  const int64_t slot = slot_idx ? slot_idx[s] : (int64_t)s;
+  if (slot < 0 || slot >= num_slots || n_tok <= 0) return;
+  const int n_used = (n_tok + sp.sub_len - 1) / sp.sub_len;   // sub-chunks this run really has
+  constexpr int kPer = D * D / 4 / kCarrySplit;               // float4s per CTA
+  for (int e = threadIdx.x; e < kPer; e += 256) {
+    const int e4 = part * kPer + e;
+    const int row = e4 / (D / 4);
+    const int64_t base = ((int64_t)s * (sp.n_sub - 1)) * H + h;
+    float4 S = reinterpret_cast<const float4*>(sp.tiles + base * (int64_t)D * D)[e4];
+    for (int j = 1; j + 1 < n_used; ++j) {
+      const int64_t idx = base + (int64_t)j * H;
+      float4* lp = reinterpret_cast<float4*>(sp.tiles + idx * (int64_t)D * D) + e4;
+      const float4 L = *lp;
+      const float pj = sp.decays[idx * D + row];
+      S.x = fmaf(pj, S.x, L.x); S.y = fmaf(pj, S.y, L.y);
+      S.z = fmaf(pj, S.z, L.z); S.w = fmaf(pj, S.w, L.w);
+      *lp = S;
+    }
+  }
+}
+
+// How a call is cut into sub-chunks: only when the (sequence, head) chains would leave at least
+// half of the machine's CTA slots (two per SM, 148 SMs) empty, into as many sub-chunks as fill
+// them, none shorter than 256 tokens (a sub-chunk costs a state tile in and out on top of its
+// tokens). Returns n_sub (1: do not cut) and sets *sub_len (a multiple of the staging round).
+static int scan_split_plan(int n_seqs, int max_query_len, int H, int* sub_len) {
+  constexpr int kSlots = 2 * 148;
+  *sub_len = max_query_len;
+  const int64_t chains = (int64_t)n_seqs * H;
+  if (chains <= 0 || max_query_len < 512 || 2 * chains > kSlots) return 1;
+  int n_sub = (int)(kSlots / chains);
+  if (n_sub > max_query_len / 256) n_sub = max_query_len / 256;
+  if (n_sub > 64) n_sub = 64;
+  if (n_sub < 2) return 1;
+  int len = (max_query_len + n_sub - 1) / n_sub;
+  len = (len + kScanTokens - 1) / kScanTokens * kScanTokens;
+  *sub_len = len;
+  return (max_query_len + len - 1) / len;
+}
+
 }  // namespace sbk
+
+extern "C" size_t sbk_gla_scan_workspace_bytes(int n_seqs, int max_query_len, int H, int D) {
+  int sub_len = 0;
+  const int n_sub = sbk::scan_split_plan(n_seqs, max_query_len, H, &sub_len);
+  if (n_sub < 2 || D <= 0) return 0;
+  return (size_t)n_seqs * (n_sub - 1) * H * ((size_t)D * D + D) * sizeof(float);
+}
 
 extern "C" int sbk_gla_scan(const void* q, const void* k, const void* v, const void* g, int in_dtype,
                             const int32_t* query_start_loc, int n_seqs, float* state,
                             int64_t num_slots, const int64_t* slot_idx, const uint8_t* reset, int H,
                             int Hkv, int D, float scale, void* out, int out_dtype, int fuse_flags,
                             float gate_normalizer, const void* norm_weight, float norm_eps,
+                            int max_query_len, void* workspace, size_t workspace_bytes,
                             int32_t* status, void* stream) {
   using namespace sbk;
   GlaFusion fu;
@@ -340,13 +450,49 @@ extern "C" int sbk_gla_scan(const void* q, const void* k, const void* v, const v
     set_error("sbk_gla_scan: n_seqs=%d exceeds 65535", n_seqs);
     return SBK_E_ARG;
   }
-  dim3 grid(H, n_seqs);
+  // One chain per (sequence, head), or -- given a workspace and the longest run -- the
+  // chunk-parallel form when the chains alone would leave most of the GPU idle.
+  ScanSplit sp{nullptr, nullptr, 1, 0};
+  if (workspace != nullptr && max_query_len > 0) {
+    int sub_len = 0;
+    const int n_sub = scan_split_plan(n_seqs, max_query_len, H, &sub_len);
+    if (n_sub > 1) {
+      const size_t need = sbk_gla_scan_workspace_bytes(n_seqs, max_query_len, H, D);
+      if (workspace_bytes < need) {
+        set_error("sbk_gla_scan: workspace of %zu bytes given, %zu needed (sbk_gla_scan_workspace_bytes)",
+                  workspace_bytes, need);
+        return SBK_E_WORKSPACE;
+      }
+      if (!aligned16(workspace)) {
+        set_error("sbk_gla_scan: workspace must be 16-byte aligned");
+        return SBK_E_ALIGN;
+      }
+      sp.tiles = (float*)workspace;
+      sp.decays = sp.tiles + (size_t)n_seqs * (n_sub - 1) * H * D * D;
+      sp.n_sub = n_sub;
+      sp.sub_len = sub_len;
+    }
+  }
+  if ((int64_t)n_seqs * sp.n_sub > 65535) {
+    set_error("sbk_gla_scan: n_seqs=%d x %d sub-chunks exceeds 65535", n_seqs, sp.n_sub);
+    return SBK_E_ARG;
+  }
+  dim3 grid(H, n_seqs * sp.n_sub);
   cudaStream_t st = (cudaStream_t)stream;
-#define SBK_SCAN_LAUNCH(T, TO, DD)                                                              \
-  gla_scan_kernel<T, TO, DD><<<grid, 256, 0, st>>>((const T*)q, (const T*)k, (const T*)v,       \
-                                                   (const T*)g, query_start_loc, state,         \
-                                                   num_slots, slot_idx, reset, H, Hkv, scale,   \
-                                                   (TO*)out, status, fu)
+#define SBK_SCAN_LAUNCH(T, TO, DD)                                                                      \
+  do {                                                                                                  \
+    if (sp.n_sub > 1) {                                                                                 \
+      gla_scan_kernel<T, TO, DD, kScanLocal><<<grid, 256, 0, st>>>(                                     \
+          (const T*)q, (const T*)k, (const T*)v, (const T*)g, query_start_loc, state, num_slots,        \
+          slot_idx, reset, H, Hkv, scale, (TO*)out, status, fu, sp);                                    \
+      if (sp.n_sub > 2)                                                                                 \
+        gla_scan_carry_kernel<DD><<<dim3(H * kCarrySplit, n_seqs), 256, 0, st>>>(query_start_loc,       \
+                                                                                 slot_idx, num_slots, H, sp); \
+    }                                                                                                   \
+    gla_scan_kernel<T, TO, DD, kScanFull><<<grid, 256, 0, st>>>(                                        \
+        (const T*)q, (const T*)k, (const T*)v, (const T*)g, query_start_loc, state, num_slots,          \
+        slot_idx, reset, H, Hkv, scale, (TO*)out, status, fu, sp);                                      \
+  } while (0)
 #define SBK_SCAN_D(T, TO)                     \
   do {                                        \
     if (D == 128) SBK_SCAN_LAUNCH(T, TO, 128); \

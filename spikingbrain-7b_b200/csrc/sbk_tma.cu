@@ -48,27 +48,41 @@ static int g_copy_mode = -1;
 int copy_mode() { return g_copy_mode; }
 
 // A map holds nothing but the address and the dimensions, so a cached one stays valid as long
-// as the geometry does.
-bool get_map(CUtensorMap* out, const MapKey& key, int* tile_copy) {
-  static std::mutex mu;
+// as the geometry does. The cache is keyed by the geometry and the form (tile / row copies).
+static bool cached_map(CUtensorMap* out, const MapKey& key, bool tile_copy) {
   constexpr int kSlots = 128;
   static MapKey keys[kSlots];
+  static bool forms[kSlots];
   static CUtensorMap maps[kSlots];
   static int used = 0, next = 0;
-  std::lock_guard<std::mutex> lock(mu);
-  if (g_copy_mode < 0) {
-    CUtensorMap probe;
-    g_copy_mode = encode_map(&probe, key, true) ? 1 : 0;
-  }
-  *tile_copy = g_copy_mode;
   for (int i = 0; i < used; ++i)
-    if (keys[i] == key) { *out = maps[i]; return true; }
+    if (forms[i] == tile_copy && keys[i] == key) { *out = maps[i]; return true; }
   CUtensorMap m;
-  if (!encode_map(&m, key, g_copy_mode == 1)) return false;
+  if (!encode_map(&m, key, tile_copy)) return false;
   const int slot = used < kSlots ? used++ : (next++ % kSlots);
-  keys[slot] = key; maps[slot] = m;
+  keys[slot] = key; forms[slot] = tile_copy; maps[slot] = m;
   *out = m;
   return true;
+}
+
+bool get_maps(CUtensorMap* out, const MapKey* keys, int n, int* tile_copy) {
+  static std::mutex mu;
+  std::lock_guard<std::mutex> lock(mu);
+  if (g_copy_mode < 0) {
+    // Whether this driver takes the permuted strides is asked once, with a fixed geometry (one
+    // block of 16 tokens x 4 kv heads, rows contiguous) at the first caller's base address: the
+    // answer must not depend on what that caller happens to pass.
+    CUtensorMap probe;
+    g_copy_mode = encode_map(&probe, MapKey{keys[0].base, 4, 1, 16, 16 * 4 * 256, 8}, true) ? 1 : 0;
+  }
+  // Every map of one launch has the same form. A geometry the tile form cannot express (a token
+  // stride or block stride the encoder rejects there) falls back to row copies for this call only.
+  for (int form = g_copy_mode; form >= 0; --form) {
+    bool ok = true;
+    for (int i = 0; i < n && ok; ++i) ok = cached_map(&out[i], keys[i], form == 1);
+    if (ok) { *tile_copy = form; return true; }
+  }
+  return false;
 }
 
 }  // namespace sbk

@@ -26,9 +26,11 @@ struct MapKey {
   }
 };
 
-// Encoded map for `key` from a small process-wide cache. *tile_copy tells which of the two forms
-// this driver accepts (the permuted-stride form is probed once per process).
-bool get_map(CUtensorMap* out, const MapKey& key, int* tile_copy);
+// Encoded maps for the `n` geometries of one launch, from a small process-wide cache, all in one
+// form: *tile_copy = 1 for tile copies (the permuted-stride form, when the driver takes it --
+// asked once per process with a fixed geometry -- and every key can be expressed in it), else 0
+// for row copies. False when some key cannot be encoded in either form.
+bool get_maps(CUtensorMap* out, const MapKey* keys, int n, int* tile_copy);
 int copy_mode();   // -1 unknown, 1 tile copies, 0 row copies
 
 // 4-D tensor copy global -> shared (TMA), completion in bytes on an mbarrier

@@ -258,7 +258,9 @@ __global__ void pool_init_kernel(int32_t* ring, unsigned long long* ctrl, int nu
 // Finished sequences give their blocks back: rows[i] names a table row; its live blocks (a
 // contiguous run ending at the block of its last token) are pushed on the ring in logical
 // order, its entries become -1 and its length 0. One CTA, pushes placed by a prefix sum in the
-// order of `rows`, so the ring contents are deterministic.
+// order of `rows`, so the ring contents are deterministic. A row named more than once is released
+// once, at its first mention (a repeat would otherwise count its blocks twice and hand the same
+// physical block to two sequences later on): every entry is checked against the ones before it.
 __global__ void __launch_bounds__(kPlanThreads)
 release_rows_kernel(const int32_t* __restrict__ rows, int n_rows, int32_t* seq_lens,
                     int32_t* block_tables, int max_blocks, int B, int block_size, int32_t* ring,
@@ -277,6 +279,11 @@ release_rows_kernel(const int32_t* __restrict__ rows, int n_rows, int32_t* seq_l
     first = j + 1;
     return last - j;
   };
+  auto repeated = [&](int i, int b) {
+    for (int j = 0; j < i; ++j)
+      if (rows[j] == b) return true;
+    return false;
+  };
   int v[3] = {0, 0, 0};
   for (int i = i_begin; i < i_end; ++i) {
     const int b = rows[i];
@@ -284,6 +291,7 @@ release_rows_kernel(const int32_t* __restrict__ rows, int n_rows, int32_t* seq_l
       raise_status(status, SBK_ST_BAD_SLOT);
       continue;
     }
+    if (repeated(i, b)) continue;
     int first;
     v[0] += live_run(b, first);
   }
@@ -293,7 +301,7 @@ release_rows_kernel(const int32_t* __restrict__ rows, int n_rows, int32_t* seq_l
   unsigned long long at = tail + (unsigned long long)v[0];
   for (int i = i_begin; i < i_end; ++i) {
     const int b = rows[i];
-    if (b < 0 || b >= B) continue;
+    if (b < 0 || b >= B || repeated(i, b)) continue;
     int first;
     const int cnt = live_run(b, first);
     int32_t* row = block_tables + (int64_t)b * max_blocks;

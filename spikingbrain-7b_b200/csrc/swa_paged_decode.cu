@@ -35,8 +35,6 @@
 //   the CTA that completes the last piece of a sequence (a counter per sequence) folds them
 //   and writes the output, so there is no second kernel. A single piece writes `out` directly.
 // HBM-bound: min(seq_len, window_left+1) * kvh*128*2*2 bytes read per sequence.
-#include <stdlib.h>
-
 #include "sbk_common.cuh"
 #include "sbk_tma.cuh"
 
@@ -111,7 +109,7 @@ struct Cfg {
   static constexpr int kLensOff = kPreOff + (kMaxSeqs + 4) * 4;
   static constexpr int kBarOff = kLensOff + kMaxSeqs * 4;
   static constexpr int kMiscOff = kBarOff + 2 * kStages * 8;
-  static constexpr int kSmemBytes = kMiscOff + 32 + 1024;      // + slack to align the ring to 1 KiB
+  static constexpr int kSmemBytes = kMiscOff + 48 + 1024;      // + slack to align the ring to 1 KiB
   static_assert(kConsumerWarps % KVH == 0, "warps must split evenly over kv heads");
   static_assert(kVOffset == 16384, "a stage holds 16 KiB of K and 16 KiB of V");
   static_assert(kSmemBytes <= 115200, "two CTAs must fit one SM");
@@ -158,7 +156,8 @@ struct Params {
   const int32_t* seq_lens; int B; int H; int64_t num_blocks;
   int block_size; int64_t block_stride; int window_left; float scale_log2;
   void* out; int64_t out_seq_stride; float* lse_out;
-  int32_t* ctrl;      // [0] next ticket, [1] CTAs that ran out of tickets
+  int32_t* ctrl;      // [0] next ticket, [1] CTAs that ran out of tickets, [2] CTAs through and [3] aborts
+                      // (gather), [4] set for good by a CTA whose wait ran out: the counters are then stale
   int32_t* done;      // [B] pieces finished per sequence
   float* ws_o; float* ws_ml; int split_chunks; int max_pieces; int32_t* status;
   int tile_copy;      // 1: one copy per tile (permuted-stride map), 0: one copy per 128-byte row
@@ -271,7 +270,8 @@ swa_decode_kernel(const Params P, const __grid_constant__ CUtensorMap map_k,
   int* lens_s = reinterpret_cast<int*>(smem + C::kLensOff);
   const uint32_t bar_full = ring + C::kBarOff;
   const uint32_t bar_empty = bar_full + C::kStages * 8;
-  volatile int* misc = reinterpret_cast<volatile int*>(smem + C::kMiscOff);  // [0] abort, [1] fold flag, [2..6] scan
+  // [0] abort, [1] fold flag, [2..6] scan, [7] longest sequence in chunks, [8] workspace marked stale
+  volatile int* misc = reinterpret_cast<volatile int*>(smem + C::kMiscOff);
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
   const int G = P.H / KVH;
@@ -283,10 +283,19 @@ swa_decode_kernel(const Params P, const __grid_constant__ CUtensorMap map_k,
     }
     misc[0] = 0;
     misc[7] = 0;
+    misc[8] = __ldcg(P.ctrl + 4);
     pre[0] = 0;
     fence_mbar_init();
   }
   __syncthreads();
+  // An earlier launch on this workspace gave up on a wait: its ticket and completion counters
+  // were left where they stood, so nothing computed with them can be trusted. Say so again and
+  // compute nothing (in the gathering form the flags stay down and the peers' wait reports the
+  // step) until the caller has zeroed the head of the workspace.
+  if (misc[8]) {
+    if (threadIdx.x == 0) raise_status(P.status, SBK_ST_WAIT_TIMEOUT);
+    return;
+  }
   const int item_cost = !P.balanced ? 0 : (P.item_cost >= 0 ? P.item_cost : kItemCostChunks);
   // ---- number of pieces of every sequence, as an exclusive prefix: item w belongs to the
   //      sequence b with pre[b] <= w < pre[b+1] ----
@@ -390,7 +399,7 @@ swa_decode_kernel(const Params P, const __grid_constant__ CUtensorMap map_k,
         const int s = it % C::kStages;
         const int use = it / C::kStages;
         if (use > 0 && !mbar_wait_bounded(bar_empty + 8 * s, (use - 1) & 1)) {
-          if (lane == 0) { raise_status(P.status, SBK_ST_WAIT_TIMEOUT); misc[0] = 1; }
+          if (lane == 0) { raise_status(P.status, SBK_ST_WAIT_TIMEOUT); P.ctrl[4] = 1; misc[0] = 1; }
           aborted = true;
           return;
         }
@@ -538,6 +547,7 @@ swa_decode_kernel(const Params P, const __grid_constant__ CUtensorMap map_k,
         }
       } else if (lane == 0) {
         raise_status(P.status, SBK_ST_WAIT_TIMEOUT);
+        P.ctrl[4] = 1;
         misc[0] = 1;
       }
       // the CTA that draws the last losing ticket rewinds the counters for the next launch
@@ -575,7 +585,7 @@ swa_decode_kernel(const Params P, const __grid_constant__ CUtensorMap map_k,
   for (int it = 0;; ++it) {
     const int s = it % C::kStages;
     if (!mbar_wait_bounded(bar_full + 8 * s, (it / C::kStages) & 1)) {
-      if (lane == 0) { raise_status(P.status, SBK_ST_WAIT_TIMEOUT); misc[0] = 1; }
+      if (lane == 0) { raise_status(P.status, SBK_ST_WAIT_TIMEOUT); P.ctrl[4] = 1; misc[0] = 1; }
       break;
     }
     const StageInfo si = info[s];
@@ -609,11 +619,7 @@ swa_decode_kernel(const Params P, const __grid_constant__ CUtensorMap map_k,
     const int vlo = si.lo > tb ? si.lo : tb;
     const int vhi = si.hi < tb + kChunk ? si.hi : tb + kChunk;
     const bool ragged = vlo > tb || vhi < tb + kChunk;
-#ifdef SBK_SWA_SKIP_MATH
-    if (false) {
-#else
     if (!(si.flags & kFlagBad) && vhi > vlo) {
-#endif
       if (ragged) {
         // A tile always brings 16 token rows; those outside the visible range may hold anything.
         // Their V must be finite (a zero probability times a NaN would poison the accumulator):
@@ -825,7 +831,9 @@ swa_decode_kernel(const Params P, const __grid_constant__ CUtensorMap map_k,
     // thread's fence at system scope, which is cumulative over what the barrier ordered before it,
     // then one atomic). The CTA that counts last has therefore every row of this launch behind
     // it; it raises this rank's flag on each peer, unless some CTA gave up on a wait -- the
-    // peers' own bounded wait then reports the step as failed on every rank.
+    // peers' own bounded wait then reports the step as failed on every rank. (A batch of more than
+    // kMaxSeqs sequences is several launches of which the last one signals: a CTA that gives up in
+    // an earlier one also marks the workspace, ctrl[4], so the later ones compute and signal nothing.)
     consumer_bar();
     if (threadIdx.x == 0) {
       if (misc[0]) atomicOr(&P.ctrl[3], 1);
@@ -904,7 +912,7 @@ int launch_swa(const Params& P0, int B_total, int n_ctas, const CUtensorMap& map
   return SBK_OK;
 }
 
-static size_t ctrl_bytes(int B) { return 16 + (size_t)((B + 3) / 4 * 4) * 4; }
+static size_t ctrl_bytes(int B) { return 32 + (size_t)((B + 3) / 4 * 4) * 4; }
 
 }  // namespace sbk
 
@@ -928,7 +936,7 @@ static int swa_decode_impl(const void* q, int64_t q_seq_stride, const void* k_ca
                            int64_t num_blocks, int block_size, int64_t cache_block_stride_bytes,
                            int window_left, float scale, void* out, int out_dtype,
                            int64_t out_seq_stride, float* lse_out, void* workspace,
-                           size_t workspace_bytes, int split_chunks, int max_pieces,
+                           size_t workspace_bytes, int split_chunks, int max_pieces, int item_cost,
                            const void* key2, const void* value2, int num_meta,
                            int32_t* status, void* stream, const PeerTargets* peers) {
   if (num_meta < 0 || num_meta % 16 != 0 || (num_meta > 0 && (!key2 || !value2 || !aligned16(key2) || !aligned16(value2)))) {
@@ -992,7 +1000,7 @@ static int swa_decode_impl(const void* q, int64_t q_seq_stride, const void* k_ca
   P.B = B; P.H = H; P.num_blocks = num_blocks; P.block_size = block_size;
   P.block_stride = cache_block_stride_bytes; P.window_left = window_left;
   P.scale_log2 = scale * kLog2e; P.out = out; P.out_seq_stride = out_seq_stride; P.lse_out = lse_out;
-  P.ctrl = (int32_t*)workspace; P.done = P.ctrl + 4;
+  P.ctrl = (int32_t*)workspace; P.done = P.ctrl + 8;
   P.ws_o = nullptr; P.ws_ml = nullptr;
   if (max_pieces > 1) {
     P.ws_o = (float*)((uint8_t*)workspace + ctrl_bytes(B));
@@ -1000,13 +1008,7 @@ static int swa_decode_impl(const void* q, int64_t q_seq_stride, const void* k_ca
   }
   P.split_chunks = split_chunks; P.max_pieces = max_pieces; P.status = status;
   P.balanced = balanced;
-  {
-    static const int env_cost = [] {
-      const char* e = getenv("SBK_SWA_ITEM_COST");   // tuning aid: chunks charged per sequence in balanced mode
-      return e ? atoi(e) : -1;
-    }();
-    P.item_cost = env_cost;
-  }
+  P.item_cost = item_cost;
   P.n_peer = 0; P.flag_value = 0; P.signal = 0; P.flag_base = nullptr;
   for (int p = 0; p < kMaxPeers; ++p) { P.peer_out[p] = nullptr; P.peer_flag[p] = nullptr; }
   if (peers) {
@@ -1024,27 +1026,23 @@ static int swa_decode_impl(const void* q, int64_t q_seq_stride, const void* k_ca
     if (dev >= 0 && dev < 64) sm_count[dev] = sms;
   }
   const int n_ctas = 2 * sms;
-  CUtensorMap map_k, map_v;
+  // the sink tensors [num_meta, kvh, D] read as a cache of num_meta/16 blocks of 16 tokens
+  const int64_t mstride = (int64_t)16 * kvh * D * 2;
+  const MapKey keys[4] = {MapKey{k_cache, kvh, num_blocks, block_size, cache_block_stride_bytes, 2 * kvh},
+                          MapKey{v_cache, kvh, num_blocks, block_size, cache_block_stride_bytes, 2 * kvh},
+                          MapKey{key2, kvh, num_meta / 16, 16, mstride, 2 * kvh},
+                          MapKey{value2, kvh, num_meta / 16, 16, mstride, 2 * kvh}};
+  CUtensorMap maps[4];
   int tile_copy = 0;
-  if (!get_map(&map_k, MapKey{k_cache, kvh, num_blocks, block_size, cache_block_stride_bytes, 2 * kvh}, &tile_copy) ||
-      !get_map(&map_v, MapKey{v_cache, kvh, num_blocks, block_size, cache_block_stride_bytes, 2 * kvh}, &tile_copy)) {
-    set_error("sbk_swa_decode: cuTensorMapEncodeTiled rejected the cache geometry (blocks=%lld block=%d kvh=%d)",
-              (long long)num_blocks, block_size, kvh);
+  if (!get_maps(maps, keys, num_meta > 0 ? 4 : 2, &tile_copy)) {
+    set_error("sbk_swa_decode: cuTensorMapEncodeTiled rejected the cache geometry (blocks=%lld block=%d kvh=%d) "
+              "or the sink-token tensors", (long long)num_blocks, block_size, kvh);
     return SBK_E_ARG;
   }
+  const CUtensorMap &map_k = maps[0], &map_v = maps[1];
+  const CUtensorMap &map_k2 = num_meta > 0 ? maps[2] : maps[0], &map_v2 = num_meta > 0 ? maps[3] : maps[1];
   P.tile_copy = tile_copy;
-  CUtensorMap map_k2 = map_k, map_v2 = map_v;
-  P.n_meta_chunks = 0;
-  if (num_meta > 0) {
-    // the sink tensors [num_meta, kvh, D] read as a cache of num_meta/16 blocks of 16 tokens
-    const int64_t mstride = (int64_t)16 * kvh * D * 2;
-    if (!get_map(&map_k2, MapKey{key2, kvh, num_meta / 16, 16, mstride, 2 * kvh}, &tile_copy) ||
-        !get_map(&map_v2, MapKey{value2, kvh, num_meta / 16, 16, mstride, 2 * kvh}, &tile_copy)) {
-      set_error("sbk_swa_decode: cuTensorMapEncodeTiled rejected the sink-token tensors");
-      return SBK_E_ARG;
-    }
-    P.n_meta_chunks = num_meta / 16;
-  }
+  P.n_meta_chunks = num_meta / 16;
   cudaStream_t st = (cudaStream_t)stream;
 #define SBK_SWA_KVH(TO)                                                            \
   switch (kvh) {                                                                   \
@@ -1071,13 +1069,13 @@ extern "C" int sbk_swa_decode(const void* q, int64_t q_seq_stride, const void* k
                               int64_t num_blocks, int block_size, int64_t cache_block_stride_bytes,
                               int window_left, float scale, void* out, int out_dtype,
                               int64_t out_seq_stride, float* lse_out, void* workspace,
-                              size_t workspace_bytes, int split_chunks, int max_pieces,
+                              size_t workspace_bytes, int split_chunks, int max_pieces, int item_cost,
                               const void* key2, const void* value2, int num_meta,
                               int32_t* status, void* stream) {
   return sbk::swa_decode_impl(q, q_seq_stride, k_cache, v_cache, block_tables, max_blocks, seq_lens, B, H, kvh,
                               D, num_blocks, block_size, cache_block_stride_bytes, window_left, scale, out,
                               out_dtype, out_seq_stride, lse_out, workspace, workspace_bytes, split_chunks,
-                              max_pieces, key2, value2, num_meta, status, stream, nullptr);
+                              max_pieces, item_cost, key2, value2, num_meta, status, stream, nullptr);
 }
 
 extern "C" int sbk_swa_decode_gather(const void* q, int64_t q_seq_stride, const void* k_cache,
@@ -1086,7 +1084,7 @@ extern "C" int sbk_swa_decode_gather(const void* q, int64_t q_seq_stride, const 
                                      int64_t num_blocks, int block_size, int64_t cache_block_stride_bytes,
                                      int window_left, float scale, void* out, int64_t out_seq_stride,
                                      void* workspace, size_t workspace_bytes, int split_chunks,
-                                     int max_pieces, const void* key2, const void* value2, int num_meta,
+                                     int max_pieces, int item_cost, const void* key2, const void* value2, int num_meta,
                                      void* const* peer_out, int32_t* const* peer_flag, int n_peer,
                                      int32_t flag_value, const int32_t* flag_base, int32_t* status,
                                      void* stream) {
@@ -1118,8 +1116,8 @@ extern "C" int sbk_swa_decode_gather(const void* q, int64_t q_seq_stride, const 
   PeerTargets pt{peer_out, peer_flag, n_peer, flag_value, flag_base};
   return swa_decode_impl(q, q_seq_stride, k_cache, v_cache, block_tables, max_blocks, seq_lens, B, H, kvh, D,
                          num_blocks, block_size, cache_block_stride_bytes, window_left, scale, out, SBK_BF16,
-                         out_seq_stride, nullptr, workspace, workspace_bytes, split_chunks, max_pieces, key2,
-                         value2, num_meta, status, stream, &pt);
+                         out_seq_stride, nullptr, workspace, workspace_bytes, split_chunks, max_pieces, item_cost,
+                         key2, value2, num_meta, status, stream, &pt);
 }
 
 // ---------------------------------------------------------------------------------------------
@@ -1186,6 +1184,6 @@ extern "C" int sbk_swa_decode_static(const void* q, int64_t q_seq_stride, const 
   }
   return sbk_swa_decode(q, q_seq_stride, k_cache, v_cache, block_tables, max_blocks, seq_lens, B, H, kvh, D,
                         num_blocks, block_size, cache_block_stride_bytes, window_left, scale, out, out_dtype,
-                        out_seq_stride, lse_out, scratch, kStaticScratchBytes, split_chunks, max_pieces, nullptr,
+                        out_seq_stride, lse_out, scratch, kStaticScratchBytes, split_chunks, max_pieces, -1, nullptr,
                         nullptr, 0, status, stream);
 }

@@ -11,8 +11,6 @@
 // rows, O += P V with P as bf16 head + bf16 remainder (32 mma.sync), fp32 accumulation.
 // The new tokens' K/V must already be in the cache (the append runs first).
 #include "sbk_common.cuh"
-#include <stdlib.h>
-#include <string.h>
 
 #include "sbk_tma.cuh"
 #include "swa_prefill_tc.cuh"
@@ -302,10 +300,14 @@ extern "C" int sbk_swa_prefill(const void* q, int64_t q_tok_stride, const void* 
                                const int32_t* context_lens, int n_seqs, int max_query_len, int H, int kvh,
                                int D, int64_t num_blocks, int block_size, int64_t cache_block_stride_bytes,
                                int window_left, float scale, void* out, int64_t out_tok_stride,
-                               const void* key2, const void* value2, int num_meta,
+                               const void* key2, const void* value2, int num_meta, int kernel,
                                int32_t* status, void* stream) {
   using namespace sbk;
   using namespace sbk::prefill;
+  if (kernel != SBK_PREFILL_AUTO && kernel != SBK_PREFILL_TCGEN05 && kernel != SBK_PREFILL_MMA_SYNC) {
+    set_error("sbk_swa_prefill: kernel=%d is none of SBK_PREFILL_AUTO / _TCGEN05 / _MMA_SYNC", kernel);
+    return SBK_E_ARG;
+  }
   if (num_meta < 0 || num_meta % 16 != 0 || (num_meta > 0 && (!key2 || !value2 || !aligned16(key2) || !aligned16(value2)))) {
     set_error("sbk_swa_prefill: sink tokens need 16-byte aligned key2/value2 and a count that is a multiple of 16 (got %d)",
               num_meta);
@@ -340,20 +342,29 @@ extern "C" int sbk_swa_prefill(const void* q, int64_t q_tok_stride, const void* 
     set_error("sbk_swa_prefill: grid too large");
     return SBK_E_ARG;
   }
-  // Two kernels serve this entry point: tcgen05 (tensor memory, 128-key tiles; the default) and
-  // mma.sync (SBK_PREFILL_KERNEL=mma, or when q / out cannot be moved as 16-byte vectors).
-  const char* pick = getenv("SBK_PREFILL_KERNEL");
+  // Two kernels serve this entry point: tcgen05 (tensor memory, 128-key tiles; what `kernel` AUTO
+  // picks) and mma.sync (on request, or under AUTO when q / out cannot be moved as 16-byte vectors).
   const bool vec_ok = aligned16(q) && aligned16(out) && q_tok_stride % 8 == 0 && out_tok_stride % 8 == 0;
-  const bool use_tc = vec_ok && !(pick != nullptr && strcmp(pick, "mma") == 0);
+  if (kernel == SBK_PREFILL_TCGEN05 && !vec_ok) {
+    set_error("sbk_swa_prefill: the tcgen05 kernel needs q and out 16-byte aligned with token strides that are "
+              "multiples of 8 elements");
+    return SBK_E_ALIGN;
+  }
+  const bool use_tc = vec_ok && kernel != SBK_PREFILL_MMA_SYNC;
+  const int64_t mstride = (int64_t)16 * kvh * D * 2;   // the sink tensors as blocks of 16 tokens
   if (use_tc) {
-    CUtensorMap mk, mv, mk2, mv2;
+    const MapKey keys[4] = {MapKey{k_cache, kvh, num_blocks, block_size, cache_block_stride_bytes, 1},
+                            MapKey{v_cache, kvh, num_blocks, block_size, cache_block_stride_bytes, 1},
+                            MapKey{key2, kvh, num_meta / 16, 16, mstride, 1},
+                            MapKey{value2, kvh, num_meta / 16, 16, mstride, 1}};
+    CUtensorMap maps[4];
     int tc_mode = 0;
-    if (!get_map(&mk, MapKey{k_cache, kvh, num_blocks, block_size, cache_block_stride_bytes, 1}, &tc_mode) ||
-        !get_map(&mv, MapKey{v_cache, kvh, num_blocks, block_size, cache_block_stride_bytes, 1}, &tc_mode)) {
-      set_error("sbk_swa_prefill: cuTensorMapEncodeTiled rejected the cache geometry");
+    if (!get_maps(maps, keys, num_meta > 0 ? 4 : 2, &tc_mode)) {
+      set_error("sbk_swa_prefill: cuTensorMapEncodeTiled rejected the cache geometry or the sink-token tensors");
       return SBK_E_ARG;
     }
-    mk2 = mk; mv2 = mv;
+    const CUtensorMap &mk = maps[0], &mv = maps[1];
+    const CUtensorMap &mk2 = num_meta > 0 ? maps[2] : maps[0], &mv2 = num_meta > 0 ? maps[3] : maps[1];
     prefill_tc::Params T;
     T.q = (const __nv_bfloat16*)q; T.q_tok_stride = q_tok_stride;
     T.block_tables = block_tables; T.max_blocks = max_blocks;
@@ -361,28 +372,24 @@ extern "C" int sbk_swa_prefill(const void* q, int64_t q_tok_stride, const void* 
     T.n_seqs = n_seqs; T.tiles_per_seq = tiles; T.H = H; T.G = H / kvh; T.num_blocks = num_blocks;
     T.block_size = block_size; T.window_left = window_left; T.scale_log2 = scale * kLog2e;
     T.out = (__nv_bfloat16*)out; T.out_tok_stride = out_tok_stride; T.status = status;
-    T.n_meta_chunks = 0;
+    T.n_meta_chunks = num_meta / 16;
     T.k_start_loc = nullptr;
     T.noncausal = 0;
-    if (num_meta > 0) {
-      const int64_t mstride = (int64_t)16 * kvh * D * 2;
-      if (!get_map(&mk2, MapKey{key2, kvh, num_meta / 16, 16, mstride, 1}, &tc_mode) ||
-          !get_map(&mv2, MapKey{value2, kvh, num_meta / 16, 16, mstride, 1}, &tc_mode)) {
-        set_error("sbk_swa_prefill: cuTensorMapEncodeTiled rejected the sink-token tensors");
-        return SBK_E_ARG;
-      }
-      T.n_meta_chunks = num_meta / 16;
-    }
     T.tile_copy = tc_mode;
     return prefill_tc::launch(T, kvh, mk, mv, mk2, mv2, (cudaStream_t)stream);
   }
-  CUtensorMap map_k, map_v;
+  const MapKey keys[4] = {MapKey{k_cache, kvh, num_blocks, block_size, cache_block_stride_bytes, 2},
+                          MapKey{v_cache, kvh, num_blocks, block_size, cache_block_stride_bytes, 2},
+                          MapKey{key2, kvh, num_meta / 16, 16, mstride, 2},
+                          MapKey{value2, kvh, num_meta / 16, 16, mstride, 2}};
+  CUtensorMap maps[4];
   int tile_copy = 0;
-  if (!get_map(&map_k, MapKey{k_cache, kvh, num_blocks, block_size, cache_block_stride_bytes, 2}, &tile_copy) ||
-      !get_map(&map_v, MapKey{v_cache, kvh, num_blocks, block_size, cache_block_stride_bytes, 2}, &tile_copy)) {
-    set_error("sbk_swa_prefill: cuTensorMapEncodeTiled rejected the cache geometry");
+  if (!get_maps(maps, keys, num_meta > 0 ? 4 : 2, &tile_copy)) {
+    set_error("sbk_swa_prefill: cuTensorMapEncodeTiled rejected the cache geometry or the sink-token tensors");
     return SBK_E_ARG;
   }
+  const CUtensorMap &map_k = maps[0], &map_v = maps[1];
+  const CUtensorMap &map_k2 = num_meta > 0 ? maps[2] : maps[0], &map_v2 = num_meta > 0 ? maps[3] : maps[1];
   static bool configured[64] = {};
   int dev = 0;
   cudaGetDevice(&dev);
@@ -401,17 +408,7 @@ extern "C" int sbk_swa_prefill(const void* q, int64_t q_tok_stride, const void* 
   P.n_seqs = n_seqs; P.tiles_per_seq = tiles; P.H = H; P.G = H / kvh; P.num_blocks = num_blocks;
   P.block_size = block_size; P.window_left = window_left; P.scale_log2 = scale * kLog2e;
   P.out = (__nv_bfloat16*)out; P.out_tok_stride = out_tok_stride; P.status = status;
-  CUtensorMap map_k2 = map_k, map_v2 = map_v;
-  P.n_meta_chunks = 0;
-  if (num_meta > 0) {
-    const int64_t mstride = (int64_t)16 * kvh * D * 2;
-    if (!get_map(&map_k2, MapKey{key2, kvh, num_meta / 16, 16, mstride, 2}, &tile_copy) ||
-        !get_map(&map_v2, MapKey{value2, kvh, num_meta / 16, 16, mstride, 2}, &tile_copy)) {
-      set_error("sbk_swa_prefill: cuTensorMapEncodeTiled rejected the sink-token tensors");
-      return SBK_E_ARG;
-    }
-    P.n_meta_chunks = num_meta / 16;
-  }
+  P.n_meta_chunks = num_meta / 16;
   P.tile_copy = tile_copy;
   dim3 grid(n_seqs * tiles, kvh);
   swa_prefill_kernel<<<grid, (P.G + 1) * 32, kSmemBytes, (cudaStream_t)stream>>>(P, map_k, map_v, map_k2, map_v2);
@@ -457,16 +454,21 @@ extern "C" int sbk_swa_prefill_dense(const void* q, int64_t q_tok_stride, const 
     return SBK_E_ARG;
   }
   // the tensors as one block of n_kv_tokens tokens with their own token stride
-  CUtensorMap mk, mv, mk2, mv2;
-  int tc_mode = 0;
   const int64_t bstride = n_kv_tokens * kv_tok_stride * 2;
-  if (n_kv_tokens > 2147483647LL ||
-      !get_map(&mk, MapKey{key, kvh, 1, (int)n_kv_tokens, bstride, 1, kv_tok_stride * 2}, &tc_mode) ||
-      !get_map(&mv, MapKey{value, kvh, 1, (int)n_kv_tokens, bstride, 1, kv_tok_stride * 2}, &tc_mode)) {
-    set_error("sbk_swa_prefill_dense: cuTensorMapEncodeTiled rejected the key/value geometry");
+  const int64_t mstride = (int64_t)16 * kvh * D * 2;
+  const int kv_tokens32 = n_kv_tokens > 2147483647LL ? 0 : (int)n_kv_tokens;
+  const MapKey keys[4] = {MapKey{key, kvh, 1, kv_tokens32, bstride, 1, kv_tok_stride * 2},
+                          MapKey{value, kvh, 1, kv_tokens32, bstride, 1, kv_tok_stride * 2},
+                          MapKey{key2, kvh, num_meta / 16, 16, mstride, 1},
+                          MapKey{value2, kvh, num_meta / 16, 16, mstride, 1}};
+  CUtensorMap maps[4];
+  int tc_mode = 0;
+  if (kv_tokens32 == 0 || !get_maps(maps, keys, num_meta > 0 ? 4 : 2, &tc_mode)) {
+    set_error("sbk_swa_prefill_dense: cuTensorMapEncodeTiled rejected the key/value geometry or the sink-token tensors");
     return SBK_E_ARG;
   }
-  mk2 = mk; mv2 = mv;
+  const CUtensorMap &mk = maps[0], &mv = maps[1];
+  const CUtensorMap &mk2 = num_meta > 0 ? maps[2] : maps[0], &mv2 = num_meta > 0 ? maps[3] : maps[1];
   prefill_tc::Params T;
   T.q = (const __nv_bfloat16*)q; T.q_tok_stride = q_tok_stride;
   T.block_tables = nullptr; T.max_blocks = 0;
@@ -475,16 +477,7 @@ extern "C" int sbk_swa_prefill_dense(const void* q, int64_t q_tok_stride, const 
   T.n_seqs = n_seqs; T.tiles_per_seq = tiles; T.H = H; T.G = H / kvh; T.num_blocks = 1;
   T.block_size = 16; T.window_left = window_left; T.scale_log2 = scale * kLog2e;
   T.out = (__nv_bfloat16*)out; T.out_tok_stride = out_tok_stride; T.status = status;
-  T.n_meta_chunks = 0;
-  if (num_meta > 0) {
-    const int64_t mstride = (int64_t)16 * kvh * D * 2;
-    if (!get_map(&mk2, MapKey{key2, kvh, num_meta / 16, 16, mstride, 1}, &tc_mode) ||
-        !get_map(&mv2, MapKey{value2, kvh, num_meta / 16, 16, mstride, 1}, &tc_mode)) {
-      set_error("sbk_swa_prefill_dense: cuTensorMapEncodeTiled rejected the sink-token tensors");
-      return SBK_E_ARG;
-    }
-    T.n_meta_chunks = num_meta / 16;
-  }
+  T.n_meta_chunks = num_meta / 16;
   T.tile_copy = tc_mode;
   return prefill_tc::launch(T, kvh, mk, mv, mk2, mv2, (cudaStream_t)stream);
 }

@@ -139,7 +139,8 @@ def gla_decode_layer(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, gk: torc
 def gla_prefill_scan(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, g: torch.Tensor,
                      kv_caches: torch.Tensor, slot_idx: torch.Tensor, query_start_loc: torch.Tensor,
                      context_lens: Optional[torch.Tensor] = None, scale: Optional[float] = None,
-                     status: Optional[torch.Tensor] = None, **fused) -> torch.Tensor:
+                     status: Optional[torch.Tensor] = None, max_query_len: int = 0,
+                     workspace: Optional[torch.Tensor] = None, **fused) -> torch.Tensor:
     """The prefill half of GatedLinearAttention._prefill_and_mix_infer
     (vllm_hymeta/model_for_7B/gla_attention.py:179-211) in one launch for all prompt sequences:
     q [T, H, D], k/v/g [T, H or Hkv, D] are the prompt tokens of `len(slot_idx)` sequences laid
@@ -147,12 +148,18 @@ def gla_prefill_scan(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, g: torch
     outputs [T, H, D] returned. A sequence whose `context_lens` entry is 0 is a new prompt and
     starts from a zero state whatever its slot holds (the reference zeroes such slots beforehand,
     modeling_gla_swa.py:391-414, and treats NaN-filled slots as empty, gla_attention.py:196-198).
-    ``fused``: relu_qk, gate_logit_normalizer, norm_weight, norm_eps of ops.gla_scan."""
+    ``fused``: relu_qk, gate_logit_normalizer, norm_weight, norm_eps of ops.gla_scan.
+    ``max_query_len`` (the metadata's host-side longest prompt run): when given, a call with few
+    long runs spreads each run over several CTAs, the counterpart of the reference's chunk-parallel
+    chunk_gla / fused_chunk_gla; ``workspace`` (ops.gla_scan_workspace) is allocated here if
+    omitted."""
     reset = None
     if context_lens is not None:
         reset = (context_lens == 0).to(torch.uint8)
     if slot_idx.dtype != torch.int64:
         slot_idx = slot_idx.to(torch.int64)
+    if max_query_len > 0 and workspace is None:
+        workspace = ops.gla_scan_workspace(slot_idx.numel(), max_query_len, q.shape[1], q.shape[2], q.device)
     return ops.gla_scan(q.contiguous(), k.contiguous(), v.contiguous(), g.contiguous(), kv_caches,
                         query_start_loc.to(torch.int32), slot_idx, reset, scale=scale, status=status,
-                        **fused)
+                        max_query_len=max_query_len, workspace=workspace, **fused)

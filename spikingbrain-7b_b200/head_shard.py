@@ -242,7 +242,6 @@ class FusedHeadGather:
         rc = self._abi.lib.sbk_peer_wait(self.flags.data_ptr(), self.tp, self.rank, 1, self.base.data_ptr(), 1,
                                          self.timeout_ms, self.status.data_ptr(), ops._stream())
         self._abi.check("sbk_peer_wait", rc)
-        ops.LAUNCHES += 1
 
     def resync(self) -> None:
         """After a step that some rank did not take part in (its peers saw SBK_ST_WAIT_TIMEOUT): bring

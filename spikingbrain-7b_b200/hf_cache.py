@@ -42,6 +42,7 @@ class _PagedWindow:
         self.bs = block_size
         self.n_cached = 0  # tokens the reference class would hold now
         self.L = 0         # length the planner holds for every row (relative to the table's column 0)
+        self._scratch: Dict[int, Tuple[torch.Tensor, int, int]] = {}   # query heads -> decode workspace
         self._alloc(capacity_tokens)
 
     def _alloc(self, capacity_tokens: int) -> None:
@@ -58,6 +59,7 @@ class _PagedWindow:
         self._n_new = torch.zeros(self.B, dtype=torch.int32, device=self.device)
         self.L = 0
         self._first_live = 0   # table columns the planner has retired so far (the same for every row)
+        self._scratch.clear()  # sized by the table width
 
     # The logical block index of a sequence only ever grows; before it would run off the table
     # the live blocks are moved back to column 0 (positions are relative, nothing else changes).
@@ -143,8 +145,18 @@ class _PagedWindow:
                              window_left=self.n_cached - 1, status=self.status)
 
     def decode(self, q: torch.Tensor, scale: Optional[float], out=None) -> torch.Tensor:
+        # one zero-initialised workspace per head count, sized for the fixed batch and the widest
+        # window the table can hold: no allocation and no memset per step
+        H = q.shape[1]
+        if H not in self._scratch:
+            vis = self.max_blocks * self.bs if self.window is None else min(self.max_blocks * self.bs, self.window)
+            split = ops.swa_auto_split(self.B, vis, self.device)
+            pieces = ops.swa_max_pieces(vis, split, self.B, self.device)
+            self._scratch[H] = (ops.swa_workspace(self.B, H, self.D, pieces, self.device), split, pieces)
+        ws, split, pieces = self._scratch[H]
         return ops.swa_decode(q, self.kv[0], self.kv[1], self.table_d, self.lens_d,
-                              window_left=self.n_cached - 1, scale=scale, out=out, status=self.status)
+                              window_left=self.n_cached - 1, scale=scale, out=out, workspace=ws,
+                              split_chunks=split, max_pieces=pieces, status=self.status)
 
 
 class _LayerState(dict):
@@ -258,6 +270,25 @@ class Cache(transformers.cache_utils.Cache):
                                                 conv_state=d.get("conv_state")))
         return cache
 
+    def status(self) -> int:
+        """The device-side status bits (SBK_ST_*) raised so far by the planner and the kernels of every
+        paged layer, OR-ed together; 0 = nothing to report. One device synchronisation. A non-zero
+        word means some step did not do what was asked: e.g. SBK_ST_OUT_OF_BLOCKS / SBK_ST_TABLE_FULL
+        from the planner, after which that step's tokens were NOT appended. After SBK_ST_WAIT_TIMEOUT
+        the decode workspaces are stale; they are dropped here so that the next step gets fresh ones."""
+        words = [s.paged.status for s in self.states if s.paged is not None]
+        if not words:
+            return 0
+        acc = words[0].clone()
+        for w in words[1:]:
+            acc |= w
+        bits = int(acc.item())
+        if bits & 4:   # SBK_ST_WAIT_TIMEOUT
+            for s in self.states:
+                if s.paged is not None:
+                    s.paged._scratch.clear()
+        return bits
+
     # ------------------------------------------------------------------ fast paths
     def update_rotary(self, q: Optional[torch.Tensor], k: torch.Tensor, v: torch.Tensor,
                       position_ids: torch.Tensor, cos_sin_cache: torch.Tensor, layer_idx: int,
@@ -319,6 +350,8 @@ class Cache(transformers.cache_utils.Cache):
         if S is None:
             S = torch.zeros(B, H, D, D, dtype=torch.float32, device=q.device)
         qsl = torch.arange(B + 1, dtype=torch.int32, device=q.device) * T
-        o = ops.gla_scan(tm(q), tm(k), tm(v), tm(g), S, qsl, scale=scale, **fused)
+        # few long runs are spread over the GPU (chunk-parallel form), as the reference's chunk_gla is
+        ws = ops.gla_scan_workspace(B, T, H, D, q.device)
+        o = ops.gla_scan(tm(q), tm(k), tm(v), tm(g), S, qsl, scale=scale, max_query_len=T, workspace=ws, **fused)
         self.update(recurrent_state=S, layer_idx=layer_idx, offset=T)
         return o.view(B, T, H, D).transpose(1, 2)

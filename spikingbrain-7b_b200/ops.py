@@ -8,7 +8,6 @@ to PyTorch ops: without a CUDA device and libsbk.so these functions raise.
 from typing import Optional, Sequence, Tuple
 
 import ctypes
-import os
 
 import torch
 
@@ -17,12 +16,6 @@ from ._abi import SBK_BF16, SBK_F32
 
 _DTYPE_CODE = {torch.bfloat16: SBK_BF16, torch.float32: SBK_F32}
 DEFAULT_SPLIT_CHUNKS = 32  # 16-token chunks per split of a sequence (512 tokens)
-
-# Instrumentation for benchmarks. LAUNCHES counts the kernels this module has launched.
-# When SWA_TIMING is a list, every swa_decode call appends a (start, end) pair of CUDA
-# events recorded on the launching stream around its kernels.
-LAUNCHES = 0
-SWA_TIMING = None
 
 
 def _ptr(t: Optional[torch.Tensor]) -> Optional[int]:
@@ -106,8 +99,6 @@ def kv_append(key: torch.Tensor, value: torch.Tensor, k_cache: torch.Tensor, v_c
         tok_stride, nb, bs, bstride, _ptr(block_tables), max_blocks, _ptr(seq_lens),
         _ptr(query_start_loc), B, window_left, _ptr(retired_out), max_ret, _ptr(status), _stream())
     _abi.check("sbk_kv_append", rc)
-    global LAUNCHES
-    LAUNCHES += 1 if (T or B) else 0
 
 
 def build_cos_sin_cache(rot_dim: int, max_position: int, base: float = 10000.0,
@@ -161,8 +152,6 @@ def rope_kv_append(query: Optional[torch.Tensor], key: torch.Tensor, value: torc
         _ptr(seq_lens), _ptr(query_start_loc), B, window_left, _ptr(retired_out), max_ret, _ptr(status),
         _stream())
     _abi.check("sbk_rope_kv_append", rc)
-    global LAUNCHES
-    LAUNCHES += 1 if (T or B) else 0
 
 
 def kv_gather(k_cache: torch.Tensor, v_cache: torch.Tensor, block_tables: torch.Tensor,
@@ -183,8 +172,6 @@ def kv_gather(k_cache: torch.Tensor, v_cache: torch.Tensor, block_tables: torch.
         k_cache.element_size(), nb, bs, bstride, window_left, _ptr(k_out), _ptr(v_out), n_out,
         _ptr(status), _stream())
     _abi.check("sbk_kv_gather", rc)
-    global LAUNCHES
-    LAUNCHES += 1 if (B and n_out) else 0
     return k_out, v_out
 
 
@@ -210,10 +197,8 @@ def swa_auto_split(B: int, max_visible_tokens: int, device) -> int:
     """The default ``split_chunks`` of swa_decode: negative = balanced mode, in which the kernel
     cuts the batch's chunks (of 16 tokens) into one equal run per CTA (two CTAs per SM) whatever
     the spread of lengths; the magnitude is the shortest run it may cut (8 chunks = 128 tokens =
-    256 KiB of K and V at 4 kv heads, below which the per-item cost outweighs the balance).
-    The environment variable SBK_SWA_SPLIT_CHUNKS overrides it (tuning, A/B measurements)."""
-    env = os.environ.get("SBK_SWA_SPLIT_CHUNKS")
-    return int(env) if env else -8
+    256 KiB of K and V at 4 kv heads, below which the per-item cost outweighs the balance)."""
+    return -8
 
 
 def _n_ctas(device) -> int:
@@ -270,13 +255,14 @@ def swa_decode(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor,
                scale: Optional[float] = None, out: Optional[torch.Tensor] = None,
                out_dtype: Optional[torch.dtype] = None, lse: Optional[torch.Tensor] = None,
                workspace: Optional[torch.Tensor] = None, max_pieces: Optional[int] = None,
-               split_chunks: Optional[int] = None, key2: Optional[torch.Tensor] = None,
-               value2: Optional[torch.Tensor] = None,
+               split_chunks: Optional[int] = None, item_cost: int = -1,
+               key2: Optional[torch.Tensor] = None, value2: Optional[torch.Tensor] = None,
                status: Optional[torch.Tensor] = None, peers: Optional["PeerTargets"] = None) -> torch.Tensor:
     """Single-query sliding-window attention over the paged cache; q [B, H, D] bf16.
     ``split_chunks`` > 0: fixed pieces of that many 16-token chunks, drawn by the CTAs from a ticket
     counter; < 0: balanced mode (equal runs of chunks per CTA, runs no shorter than -split_chunks);
-    default swa_auto_split.
+    default swa_auto_split. ``item_cost``: balanced mode's charge per sequence in chunks (-1: the
+    library's tuned value).
     ``key2`` / ``value2`` [n_meta, kvh, D]: sink tokens every query sees besides its window.
     ``peers``: head-sharded use -- ``out`` is this rank's head slice of its gathered buffer, and the
     kernel also stores every finished row to the peers and raises their flags (PeerTargets)."""
@@ -312,13 +298,6 @@ def swa_decode(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor,
     if scale is None:
         scale = d ** -0.5
     n_meta = _check_meta(key2, value2, kvh, d)
-    timing = SWA_TIMING
-    if timing is not None:
-        # external: inside a stream capture these become event-record nodes of the graph, so
-        # the pair times the launch of the latest replay
-        ev0 = torch.cuda.Event(enable_timing=True, external=True)
-        ev1 = torch.cuda.Event(enable_timing=True, external=True)
-        ev0.record()
     if peers is not None:
         if out.dtype != torch.bfloat16 or lse is not None:
             raise ValueError("the gathered head outputs are bf16, without lse")
@@ -326,8 +305,8 @@ def swa_decode(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor,
             _ptr(q), q.stride(0) if B else H * d, _ptr(k_cache), _ptr(v_cache), _ptr(block_tables),
             max_blocks, _ptr(seq_lens), B, H, kvh, d, nb, bs, bstride, window_left, float(scale),
             _ptr(out), out.stride(0) if B else H * d, _ptr(workspace),
-            workspace.numel() if workspace is not None else 0, split_chunks, max_pieces, _ptr(key2),
-            _ptr(value2), n_meta, peers.out_table, peers.flag_table, peers.n, peers.flag_value,
+            workspace.numel() if workspace is not None else 0, split_chunks, max_pieces, int(item_cost),
+            _ptr(key2), _ptr(value2), n_meta, peers.out_table, peers.flag_table, peers.n, peers.flag_value,
             _ptr(peers.flag_base), _ptr(status), _stream())
         _abi.check("sbk_swa_decode_gather", rc)
     else:
@@ -336,13 +315,8 @@ def swa_decode(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor,
             max_blocks, _ptr(seq_lens), B, H, kvh, d, nb, bs, bstride, window_left, float(scale),
             _ptr(out), _DTYPE_CODE[out.dtype], out.stride(0) if B else H * d, _ptr(lse),
             _ptr(workspace), workspace.numel() if workspace is not None else 0, split_chunks,
-            max_pieces, _ptr(key2), _ptr(value2), n_meta, _ptr(status), _stream())
+            max_pieces, int(item_cost), _ptr(key2), _ptr(value2), n_meta, _ptr(status), _stream())
         _abi.check("sbk_swa_decode", rc)
-    if timing is not None:
-        ev1.record()
-        timing.append((ev0, ev1))
-    global LAUNCHES
-    LAUNCHES += -(-B // 1024)
     return out
 
 
@@ -402,7 +376,6 @@ def gla_step(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, g: torch.Tensor,
         raise ValueError("state has fewer slots than sequences")
     if scale is None:
         scale = D ** -0.5
-    global LAUNCHES
     if peers is not None:
         if q.dtype != torch.bfloat16 or out is None or out.dtype != torch.bfloat16:
             raise ValueError("the gathered GLA step takes bf16 inputs and a bf16 out slice")
@@ -416,7 +389,6 @@ def gla_step(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, g: torch.Tensor,
             float(norm_eps), _ptr(peer_counter), peers.out_table, peers.flag_table, peers.n, peers.flag_value,
             _ptr(peers.flag_base), _ptr(status), _stream())
         _abi.check("sbk_gla_step_gather", rc)
-        LAUNCHES += 1
         return out
     if out is None:
         out = torch.empty((B, H, D), dtype=out_dtype or q.dtype, device=q.device)
@@ -427,7 +399,6 @@ def gla_step(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, g: torch.Tensor,
         _ptr(slot_idx), B, H, Hkv, D, float(scale), _ptr(out), _DTYPE_CODE[out.dtype],
         flags, gnorm, _ptr(norm_weight), float(norm_eps), _ptr(status), _stream())
     _abi.check("sbk_gla_step", rc)
-    LAUNCHES += 1 if B else 0
     return out
 
 
@@ -437,12 +408,16 @@ def gla_scan(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, g: torch.Tensor,
              out: Optional[torch.Tensor] = None, out_dtype: Optional[torch.dtype] = None,
              relu_qk: bool = False, gate_logit_normalizer: Optional[float] = None,
              norm_weight: Optional[torch.Tensor] = None, norm_eps: float = 1e-5,
+             max_query_len: int = 0, workspace: Optional[torch.Tensor] = None,
              status: Optional[torch.Tensor] = None) -> torch.Tensor:
     """GLA over runs of tokens with state carry. q [T, H, D], k/v/g [T, Hkv, D] token-major;
     sequence s owns rows query_start_loc[s]:query_start_loc[s+1]; ``state`` [slots, H, D, D] fp32 is
     advanced in place; ``reset`` [n_seqs] uint8/bool marks sequences that start from zero. The
-    fused neighbours (``relu_qk``, ``gate_logit_normalizer``, ``norm_weight``) are those of gla_step."""
-    _need_cuda(q, k, v, g, state, query_start_loc, slot_idx, reset, out, status, norm_weight)
+    fused neighbours (``relu_qk``, ``gate_logit_normalizer``, ``norm_weight``) are those of gla_step.
+    ``max_query_len`` (the longest run, a host value) with ``workspace`` (gla_scan_workspace) lets a
+    call with few long runs spread every run over several CTAs (chunk-parallel form; results agree
+    with the one-chain scan to fp32 rounding instead of bit for bit)."""
+    _need_cuda(q, k, v, g, state, query_start_loc, slot_idx, reset, out, status, norm_weight, workspace)
     flags, gnorm = _gla_fusion_args(q, D=q.shape[-1], relu_qk=relu_qk,
                                     gate_logit_normalizer=gate_logit_normalizer, norm_weight=norm_weight)
     if q.dim() != 3 or k.dim() != 3:
@@ -478,22 +453,33 @@ def gla_scan(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, g: torch.Tensor,
     rc = _abi.lib.sbk_gla_scan(
         _ptr(q), _ptr(k), _ptr(v), _ptr(g), _DTYPE_CODE[q.dtype], _ptr(query_start_loc), n_seqs,
         _ptr(state), state.shape[0], _ptr(slot_idx), _ptr(reset), H, Hkv, D, float(scale), _ptr(out),
-        _DTYPE_CODE[out.dtype], flags, gnorm, _ptr(norm_weight), float(norm_eps), _ptr(status),
-        _stream())
+        _DTYPE_CODE[out.dtype], flags, gnorm, _ptr(norm_weight), float(norm_eps),
+        int(max_query_len) if workspace is not None else 0, _ptr(workspace),
+        workspace.numel() * workspace.element_size() if workspace is not None else 0, _ptr(status), _stream())
     _abi.check("sbk_gla_scan", rc)
-    global LAUNCHES
-    LAUNCHES += 1 if n_seqs else 0
     return out
+
+
+def gla_scan_workspace(n_seqs: int, max_query_len: int, H: int, D: int, device) -> Optional[torch.Tensor]:
+    """Scratch for the chunk-parallel form of gla_scan, or None when a call of this shape runs as
+    one chain per (sequence, head) anyway. Contents need no initialisation."""
+    n = _abi.lib.sbk_gla_scan_workspace_bytes(n_seqs, max_query_len, H, D)
+    return torch.empty(n, dtype=torch.uint8, device=device) if n else None
+
+
+PREFILL_KERNELS = {"auto": _abi.PREFILL_AUTO, "tcgen05": _abi.PREFILL_TCGEN05, "mma_sync": _abi.PREFILL_MMA_SYNC}
 
 
 def swa_prefill(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, block_tables: torch.Tensor,
                 query_start_loc: torch.Tensor, context_lens: torch.Tensor, max_query_len: int, *,
                 window_left: int, scale: Optional[float] = None, out: Optional[torch.Tensor] = None,
                 key2: Optional[torch.Tensor] = None, value2: Optional[torch.Tensor] = None,
-                status: Optional[torch.Tensor] = None) -> torch.Tensor:
+                kernel: str = "auto", status: Optional[torch.Tensor] = None) -> torch.Tensor:
     """Sliding-window attention of runs of query tokens (q [T, H, D] bf16, token-major) over the
     paged cache, the runs' own K/V already appended. Sequence s owns rows
-    query_start_loc[s]:query_start_loc[s+1] and had context_lens[s] tokens cached before."""
+    query_start_loc[s]:query_start_loc[s+1] and had context_lens[s] tokens cached before.
+    ``kernel``: "auto" (tcgen05 where q / out allow 16-byte vectors, else mma.sync), "tcgen05",
+    "mma_sync"."""
     _need_cuda(q, k_cache, v_cache, block_tables, query_start_loc, context_lens, out, status)
     nb, bs, kvh, d, bstride = _cache_geometry(k_cache, v_cache)
     if q.dim() != 3 or q.shape[2] != d or q.dtype != torch.bfloat16 or k_cache.dtype != torch.bfloat16:
@@ -515,10 +501,9 @@ def swa_prefill(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, b
         _ptr(q), q.stride(0) if T else H * d, _ptr(k_cache), _ptr(v_cache), _ptr(block_tables),
         block_tables.shape[1], _ptr(query_start_loc), _ptr(context_lens), n_seqs, int(max_query_len), H,
         kvh, d, nb, bs, bstride, window_left, float(scale), _ptr(out), out.stride(0) if T else H * d,
-        _ptr(key2), _ptr(value2), _check_meta(key2, value2, kvh, d), _ptr(status), _stream())
+        _ptr(key2), _ptr(value2), _check_meta(key2, value2, kvh, d), PREFILL_KERNELS[kernel], _ptr(status),
+        _stream())
     _abi.check("sbk_swa_prefill", rc)
-    global LAUNCHES
-    LAUNCHES += 1 if (n_seqs and max_query_len) else 0
     return out
 
 
@@ -583,8 +568,6 @@ def plan_step(seq_lens: torch.Tensor, block_tables: torch.Tensor, slot_mapping: 
                                 _ptr(slot_mapping), _ptr(positions), _ptr(context_lens),
                                 _ptr(query_start_loc), T, _ptr(status), _stream())
     _abi.check("sbk_plan_step", rc)
-    global LAUNCHES
-    LAUNCHES += 1
 
 
 def release_rows(rows: torch.Tensor, seq_lens: torch.Tensor, block_tables: torch.Tensor, *,
@@ -600,8 +583,6 @@ def release_rows(rows: torch.Tensor, seq_lens: torch.Tensor, block_tables: torch
     rc = _abi.lib.sbk_release_rows(_ptr(rows), rows.numel(), _ptr(seq_lens), _ptr(block_tables), max_blocks,
                                    B, block_size, _ptr(ring), _ptr(ctrl), num_blocks, _ptr(status), _stream())
     _abi.check("sbk_release_rows", rc)
-    global LAUNCHES
-    LAUNCHES += 1 if rows.numel() else 0
 
 
 def swa_prefill_dense(q: torch.Tensor, key: torch.Tensor, value: torch.Tensor, query_start_loc: torch.Tensor,
@@ -644,6 +625,4 @@ def swa_prefill_dense(q: torch.Tensor, key: torch.Tensor, value: torch.Tensor, q
         int(causal), float(scale), _ptr(out), out.stride(0) if T else H * d, _ptr(key2), _ptr(value2), n_meta, _ptr(status),
         _stream())
     _abi.check("sbk_swa_prefill_dense", rc)
-    global LAUNCHES
-    LAUNCHES += 1 if (T and n_seqs) else 0
     return out

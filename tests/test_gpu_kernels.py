@@ -272,6 +272,110 @@ def test_swa_decode_config2_shapes(ops):
     _check_attn(out, ref, lse, lse_ref)
 
 
+def _big_paged_case(lens, wl, H, kvh, bs, seed):
+    """A large paged pool built on the device (every visible block of every sequence, random block
+    order, -1 for blocks before the window) -> (q, kv, table, lens tensor) on the GPU."""
+    D = 128
+    g = torch.Generator().manual_seed(seed)
+    B = len(lens)
+    first = [max(0, L - 1 - wl) // bs if wl >= 0 else 0 for L in lens]
+    last = [(L - 1) // bs for L in lens]
+    n_live = [l - f + 1 for f, l in zip(first, last)]
+    nb = sum(n_live) + 5
+    perm = torch.randperm(nb, generator=g).to(torch.int32)
+    table = torch.full((B, max(last) + 1), -1, dtype=torch.int32)
+    o = 0
+    for b in range(B):
+        table[b, first[b]:last[b] + 1] = perm[o:o + n_live[b]]
+        o += n_live[b]
+    torch.manual_seed(seed)
+    kv = (torch.randn(2, nb, bs, kvh, D, device=DEV, dtype=torch.bfloat16) / math.sqrt(D))
+    q = (torch.randn(B, H, D, device=DEV) / math.sqrt(D)).bfloat16()
+    return q, kv, table.to(DEV), torch.tensor(lens, dtype=torch.int32, device=DEV)
+
+
+def test_swa_decode_benchmarked_geometry_b256_ctx8192(ops):
+    """The shape the decode benchmark times: 256 sequences at 8192 tokens, window_left 4096 (4097 visible
+    keys), block 16, 28/4 heads, default split -- the whole-sequence partition with one CTA per
+    sequence. Every output row against the oracle."""
+    H, kvh, bs, wl, D = 28, 4, 16, 4096, 128
+    lens = [8192] * 256
+    q, kv, table, lens_d = _big_paged_case(lens, wl, H, kvh, bs, seed=40)
+    st = _status()
+    lse = torch.empty(len(lens), H, dtype=torch.float32, device=DEV)
+    out = ops.swa_decode(q, kv[0], kv[1], table, lens_d, window_left=wl, lse=lse, status=st)
+    torch.cuda.synchronize()
+    assert st.item() == 0
+    kv_c = kv.cpu()
+    ref, lse_ref = ref_ops.swa_paged_decode_ref(q.cpu(), kv_c[0], kv_c[1], table.cpu(), lens, wl, D ** -0.5,
+                                                return_lse=True)
+    _check_attn(out.cpu(), ref, lse.cpu(), lse_ref)
+
+
+def test_swa_decode_churn_lengths_b1024_default_split(ops):
+    """The churn workload's batch: 1024 sequences (the most one launch takes), lengths
+    clip(zipf(1.2), 128, 65536) drawn with numpy's default_rng(0), window_left 4096, default split
+    (the balanced partition: equal runs of chunks per CTA across sequence boundaries)."""
+    import numpy as np
+    H, kvh, bs, wl, D = 28, 4, 16, 4096, 128
+    lens = np.clip(np.random.default_rng(0).zipf(1.2, size=1024), 128, 65536).astype(int).tolist()
+    q, kv, table, lens_d = _big_paged_case(lens, wl, H, kvh, bs, seed=41)
+    st = _status()
+    lse = torch.empty(len(lens), H, dtype=torch.float32, device=DEV)
+    out = ops.swa_decode(q, kv[0], kv[1], table, lens_d, window_left=wl, lse=lse, status=st)
+    torch.cuda.synchronize()
+    assert st.item() == 0
+    kv_c = kv.cpu()
+    ref, lse_ref = ref_ops.swa_paged_decode_ref(q.cpu(), kv_c[0], kv_c[1], table.cpu(), lens, wl, D ** -0.5,
+                                                return_lse=True)
+    _check_attn(out.cpu(), ref, lse.cpu(), lse_ref)
+
+
+def test_swa_decode_more_sequences_than_one_launch_default_split(ops):
+    """1500 short sequences: two launches (1024 + 476) sharing one workspace, balanced partition."""
+    g = torch.Generator().manual_seed(42)
+    lens = torch.randint(1, 400, (1500,), generator=g).tolist()
+    out, ref, lse, lse_ref = _run_attn(ops, lens, wl=255, H=28, kvh=4, bs=16, seed=43, split_chunks=None)
+    _check_attn(out, ref, lse, lse_ref)
+
+
+@pytest.mark.parametrize("split", [-8, 4])
+def test_swa_decode_marked_workspace_reports_instead_of_computing(ops, split):
+    """A call in which a wait ran out leaves its counters where they stood and marks the workspace
+    (word 4 of its head). A later call given that workspace must not fold stale partials into
+    rows it reports as good: it raises SBK_ST_WAIT_TIMEOUT again and writes nothing. Once the head
+    is zeroed the workspace serves again. The mark is planted by hand here (no wait is made to
+    run out), together with stale counters."""
+    from spikingbrain_7b_b200 import _abi
+    H, kvh, bs, wl, D = 28, 4, 16, 1023, 128
+    lens = [1500, 17, 1024, 1025, 300, 64]
+    kv, table, nb = make_paged_kv(lens, wl, kvh, D, bs, seed=44)
+    q = (torch.randn(len(lens), H, D, generator=torch.Generator().manual_seed(45)) / math.sqrt(D)).bfloat16()
+    ref = ref_ops.swa_paged_decode_ref(q, kv[0], kv[1], table, lens, wl, D ** -0.5)
+    pieces = 9
+    ws = ops.swa_workspace(len(lens), H, D, pieces, DEV)
+    head = ws[:32 + 4 * 8].view(torch.int32)
+    head[0] = 3          # a ticket counter that was never rewound
+    head[4] = 1          # the mark
+    head[8:14] = 2       # completion counters of sequences that were half done
+    kv_d = kv.to(DEV)
+    args = (q.to(DEV), kv_d[0], kv_d[1], table.to(DEV), torch.tensor(lens, dtype=torch.int32, device=DEV))
+    st = _status()
+    out = torch.full((len(lens), H, D), 7.0, dtype=torch.bfloat16, device=DEV)
+    ops.swa_decode(*args, window_left=wl, out=out, workspace=ws, max_pieces=pieces, split_chunks=split, status=st)
+    torch.cuda.synchronize()
+    assert st.item() == _abi.ST_WAIT_TIMEOUT
+    assert bool((out == 7.0).all()), "a marked workspace must not produce rows"
+    ws[:head.numel() * 4].zero_()
+    st.zero_()
+    ops.swa_decode(*args, window_left=wl, out=out, workspace=ws, max_pieces=pieces, split_chunks=split, status=st)
+    torch.cuda.synchronize()
+    assert st.item() == 0
+    tgt = ref.bfloat16().float()
+    assert float((out.float().cpu() - tgt).abs().max()) <= ATTN_MAX_ABS and mean_rel(out.float().cpu(), tgt) <= ATTN_MEAN_REL
+    assert not head.any(), "a clean call leaves the head of the workspace at zero"
+
+
 @pytest.mark.parametrize("H,kvh,n_meta", [(28, 4, 128), (7, 1, 16), (14, 2, 48)])
 def test_swa_decode_with_sink_tokens(ops, H, kvh, n_meta):
     """Meta (sink) tokens every query sees besides its window: one softmax over both."""
@@ -308,7 +412,7 @@ def test_swa_prefill_with_sink_tokens(ops, prefill_kernel):
     st = _status()
     out = ops.swa_prefill(q.to(DEV), kv_d[0], kv_d[1], table.to(DEV), torch.tensor([0, 50, 83], dtype=torch.int32, device=DEV),
                           torch.tensor(ctx, dtype=torch.int32, device=DEV), 50, window_left=wl, key2=k2.to(DEV),
-                          value2=v2.to(DEV), status=st).float().cpu()
+                          value2=v2.to(DEV), kernel=prefill_kernel, status=st).float().cpu()
     assert st.item() == 0
     row = 0
     for s in range(2):
@@ -320,7 +424,7 @@ def test_swa_prefill_with_sink_tokens(ops, prefill_kernel):
 
 
 # --------------------------------------------------------------------- prefill attention
-def _prefill_case(ops, ctx, new, wl, H, kvh, bs, seed):
+def _prefill_case(ops, ctx, new, wl, H, kvh, bs, seed, kernel="auto"):
     """Sequences with `ctx[s]` cached tokens get `new[s]` more: append, then windowed attention of
     the new tokens; the oracle treats every new token as a one-token decode at its position."""
     D = 128
@@ -336,7 +440,7 @@ def _prefill_case(ops, ctx, new, wl, H, kvh, bs, seed):
     st = _status()
     kv_d = kv.to(DEV)
     out = ops.swa_prefill(q.to(DEV), kv_d[0], kv_d[1], table.to(DEV), torch.tensor(qsl, dtype=torch.int32, device=DEV),
-                          torch.tensor(ctx, dtype=torch.int32, device=DEV), max(new), window_left=wl, status=st)
+                          torch.tensor(ctx, dtype=torch.int32, device=DEV), max(new), window_left=wl, kernel=kernel, status=st)
     torch.cuda.synchronize()
     assert st.item() == 0
     o = out.float().cpu()
@@ -354,32 +458,31 @@ def _prefill_case(ops, ctx, new, wl, H, kvh, bs, seed):
     assert worst <= ATTN_MAX_ABS and num / den <= ATTN_MEAN_REL, (worst, num / den)
 
 
-@pytest.fixture(params=["tc", "mma"])
-def prefill_kernel(request, monkeypatch):
-    """The prefill entry point has two kernels: tcgen05 (default) and mma.sync; the environment
-    variable is read at every call."""
-    monkeypatch.setenv("SBK_PREFILL_KERNEL", request.param)
+@pytest.fixture(params=["tcgen05", "mma_sync"])
+def prefill_kernel(request):
+    """The prefill entry point has two kernels, chosen by its `kernel` argument: tcgen05 (what "auto"
+    takes for aligned q / out) and mma.sync."""
     return request.param
 
 
 @pytest.mark.parametrize("ctx,new", [([0], [1]), ([0], [16]), ([0], [17]), ([5], [40]), ([0, 100, 33], [70, 3, 129])])
 def test_swa_prefill_small_edges(ops, prefill_kernel, ctx, new):
-    _prefill_case(ops, ctx, new, wl=63, H=28, kvh=4, bs=16, seed=60)
+    _prefill_case(ops, ctx, new, wl=63, H=28, kvh=4, bs=16, seed=60, kernel=prefill_kernel)
 
 
 @pytest.mark.parametrize("wl", [0, 15, 16, 255, 4096, -1])
 def test_swa_prefill_window_edges(ops, prefill_kernel, wl):
-    _prefill_case(ops, [300, 0, 1000], [200, 513, 64], wl=wl, H=28, kvh=4, bs=16, seed=61)
+    _prefill_case(ops, [300, 0, 1000], [200, 513, 64], wl=wl, H=28, kvh=4, bs=16, seed=61, kernel=prefill_kernel)
 
 
 @pytest.mark.parametrize("H,kvh,bs", [(7, 1, 16), (14, 2, 32), (32, 4, 64), (4, 4, 16), (16, 2, 128)])
 def test_swa_prefill_head_layouts_and_block_sizes(ops, prefill_kernel, H, kvh, bs):
-    _prefill_case(ops, [700, 0], [300, 260], wl=511, H=H, kvh=kvh, bs=bs, seed=62)
+    _prefill_case(ops, [700, 0], [300, 260], wl=511, H=H, kvh=kvh, bs=bs, seed=62, kernel=prefill_kernel)
 
 
 def test_swa_prefill_long_chunk_at_model_shapes(ops, prefill_kernel):
     """One 2048-token chunk on top of 6000 cached tokens, window 4096, 28/4 heads."""
-    _prefill_case(ops, [6000], [2048], wl=4096, H=28, kvh=4, bs=16, seed=63)
+    _prefill_case(ops, [6000], [2048], wl=4096, H=28, kvh=4, bs=16, seed=63, kernel=prefill_kernel)
 
 
 @pytest.mark.parametrize("wl,n_meta", [(63, 0), (-1, 0), (300, 48), (0, 0)])
@@ -581,6 +684,102 @@ def test_gla_scan_equals_chained_steps_and_chunking_is_invisible(ops):
     o_all = o_all.view(B, T, H, D)
     assert torch.equal(torch.cat(o_chunks, 1), o_all) and torch.equal(s_chunks, s_all)      # same arithmetic, same bits
     assert rel_err(torch.stack(o_steps, 1), o_all) <= 1e-6 and rel_err(s_steps, s_all) <= 1e-6
+
+
+def _scan_inputs(T, H, Hkv, D, seed, dtype=torch.bfloat16, strong_decay=False):
+    g = torch.Generator().manual_seed(seed)
+    q = torch.relu(torch.randn(T, H, D, generator=g) / math.sqrt(D)).to(dtype)
+    k = torch.relu(torch.randn(T, Hkv, D, generator=g) / math.sqrt(D)).to(dtype)
+    v = (torch.randn(T, Hkv, D, generator=g) / math.sqrt(D)).to(dtype)
+    gk = torch.nn.functional.logsigmoid(torch.randn(T, Hkv, D, generator=g)) / (0.05 if strong_decay else 16)
+    return q, k, v, gk.to(dtype)
+
+
+@pytest.mark.parametrize("runs,H,Hkv,D,carry_in", [([8192], 28, 4, 128, True), ([8192], 28, 4, 128, False),
+                                                   ([3000, 700, 2049], 28, 4, 128, True), ([4096], 8, 2, 64, True),
+                                                   ([1537, 1024], 7, 1, 128, True)])
+def test_gla_scan_chunk_parallel_matches_one_chain_and_oracle(ops, runs, H, Hkv, D, carry_in):
+    """Few long runs: given the longest run and a workspace the scan cuts every run into sub-chunks
+    owned by different CTAs (local scans, carry, scan proper). The recurrence is linear in the
+    state, so the result is the one-chain scan's in another association: outputs and final states
+    within 1e-5 of it (tolerance, not bit equality), and within the 1e-4 bar of the token-by-token
+    oracle on two sampled heads."""
+    n_seqs = len(runs)
+    qsl = [0]
+    for n in runs:
+        qsl.append(qsl[-1] + n)
+    T = qsl[-1]
+    q, k, v, gk = _scan_inputs(T, H, Hkv, D, seed=35)
+    g = torch.Generator().manual_seed(36)
+    state = torch.randn(n_seqs + 1, H, D, D, generator=g) * 0.1
+    slot_idx = torch.arange(n_seqs, 0, -1, dtype=torch.int64)             # slots n_seqs .. 1; slot 0 stays untouched
+    reset = [not carry_in] + [False] * (n_seqs - 1)
+    ws = ops.gla_scan_workspace(n_seqs, max(runs), H, D, DEV)
+    assert ws is not None, "this shape is meant to be cut"
+    dev = lambda t: t.to(DEV)
+    qsl_d = torch.tensor(qsl, dtype=torch.int32, device=DEV)
+    reset_d = torch.tensor(reset, device=DEV)
+    s_one, s_par = dev(state), dev(state)
+    st = _status()
+    o_one = ops.gla_scan(dev(q), dev(k), dev(v), dev(gk), s_one, qsl_d, dev(slot_idx), reset_d,
+                         out_dtype=torch.float32, status=st)
+    ws.fill_(0xFF)                                                        # the scratch needs no initialisation (NaNs)
+    o_par = ops.gla_scan(dev(q), dev(k), dev(v), dev(gk), s_par, qsl_d, dev(slot_idx), reset_d,
+                         out_dtype=torch.float32, max_query_len=max(runs), workspace=ws, status=st)
+    torch.cuda.synchronize()
+    assert st.item() == 0
+    assert torch.isfinite(o_par).all() and torch.isfinite(s_par).all()
+    assert rel_err(o_par, o_one) <= 1e-5 and rel_err(s_par, s_one) <= 1e-5
+    assert torch.equal(s_par[0].cpu(), state[0])
+    G = H // Hkv
+    for h in sorted({1 % H, H - 2}):
+        hk = h // G
+        ref_state = state[:, h:h + 1].clone()
+        ref = ref_ops.gla_scan_ref(q[:, h:h + 1], k[:, hk:hk + 1], v[:, hk:hk + 1], gk[:, hk:hk + 1], ref_state, qsl,
+                                   slot_idx.tolist(), reset)
+        assert rel_err(o_par[:, h:h + 1].cpu(), ref) <= GLA_REL
+        assert rel_err(s_par[:, h:h + 1].cpu(), ref_state) <= GLA_REL
+
+
+def test_gla_scan_chunk_parallel_strong_decay_and_fused_neighbours(ops):
+    """The chunk-parallel form with gates strong enough that a sub-chunk's decay product underflows
+    to zero (the carried state then contributes nothing, as in the one-chain scan), and with the
+    fused neighbours (ReLU on q/k, gate logits, per-head RMS norm) switched on."""
+    H, Hkv, D, T = 28, 4, 128, 4096
+    q, k, v, gk = _scan_inputs(T, H, Hkv, D, seed=37, strong_decay=True)
+    qsl_d = torch.tensor([0, T], dtype=torch.int32, device=DEV)
+    ws = ops.gla_scan_workspace(1, T, H, D, DEV)
+    dev = lambda t: t.to(DEV)
+    g = torch.Generator().manual_seed(38)
+    state = torch.randn(1, H, D, D, generator=g)
+    s_one, s_par = dev(state), dev(state)
+    o_one = ops.gla_scan(dev(q), dev(k), dev(v), dev(gk), s_one, qsl_d, out_dtype=torch.float32)
+    o_par = ops.gla_scan(dev(q), dev(k), dev(v), dev(gk), s_par, qsl_d, out_dtype=torch.float32, max_query_len=T,
+                         workspace=ws)
+    assert torch.isfinite(o_par).all()
+    assert rel_err(o_par, o_one) <= 1e-5 and rel_err(s_par, s_one) <= 1e-5
+    # fused: un-prepared projections in, normalised read-out out
+    qp = (torch.randn(T, H, D, generator=g)).bfloat16()
+    kp = (torch.randn(T, Hkv, D, generator=g)).bfloat16()
+    logits = (3 * torch.randn(T, Hkv, D, generator=g)).bfloat16()
+    w = (1 + 0.3 * torch.randn(D, generator=g)).bfloat16().to(DEV)
+    kw = dict(relu_qk=True, gate_logit_normalizer=16.0, norm_weight=w, norm_eps=1e-5, out_dtype=torch.float32)
+    s_one, s_par = dev(state), dev(state)
+    o_one = ops.gla_scan(dev(qp), dev(kp), dev(v), dev(logits), s_one, qsl_d, **kw)
+    o_par = ops.gla_scan(dev(qp), dev(kp), dev(v), dev(logits), s_par, qsl_d, max_query_len=T, workspace=ws, **kw)
+    assert rel_err(o_par, o_one) <= 1e-5 and rel_err(s_par, s_one) <= 1e-5
+
+
+def test_gla_scan_workspace_too_small_is_refused(ops):
+    from spikingbrain_7b_b200 import _abi
+    H, Hkv, D, T = 28, 4, 128, 2048
+    q, k, v, gk = (t.to(DEV) for t in _scan_inputs(T, H, Hkv, D, seed=39))
+    state = torch.zeros(1, H, D, D, device=DEV)
+    small = torch.empty(1024, dtype=torch.uint8, device=DEV)
+    with pytest.raises(_abi.SbkError) as e:
+        ops.gla_scan(q, k, v, gk, state, torch.tensor([0, T], dtype=torch.int32, device=DEV), max_query_len=T,
+                     workspace=small)
+    assert e.value.code == _abi.SBK_E_WORKSPACE
 
 
 # ------------------------------------------------------------- rotary embedding in the append
@@ -846,6 +1045,29 @@ def test_plan_step_churn_with_releases_and_chunked_prompts(ops):
         assert dev.context_lens.tolist() == want["context_lens"]
     snap = _same_state(dev, ref)
     assert snap["status"] == 0 and snap["steps"] == 60
+
+
+def test_release_rows_names_a_row_twice_releases_it_once(ops):
+    """A repeated entry in the list of finished rows must not count the row's blocks twice (the ring's
+    tail would run ahead of what was pushed and a block would later be handed to two sequences): the
+    device state equals the CPU model's, in which the second mention finds an empty row."""
+    B, bs, wl, max_blocks = 6, 16, -1, 12
+    dev, ref = _planner_pair(B * 12, bs, B, max_blocks, wl, T=B * 64)
+    n_new = [40, 17, 64, 1, 33, 50]
+    assert ref.plan(n_new, T=B * 64) is not None
+    dev.plan(torch.tensor(n_new, dtype=torch.int32, device=DEV))
+    rows = [2, 4, 2, 0, 4, 2]
+    ref.release(rows)
+    dev.release(torch.tensor(rows, dtype=torch.int32, device=DEV))
+    snap = _same_state(dev, ref)
+    assert snap["status"] == 0
+    assert len(snap["free"]) == len(set(snap["free"])), "a block id sits in the ring twice"
+    # the pool still serves: re-admit the released rows and compare every slot
+    n_new = [16, 0, 70, 0, 5, 0]
+    want = ref.plan(n_new, T=B * 64)
+    dev.plan(torch.tensor(n_new, dtype=torch.int32, device=DEV))
+    assert dev.slot_mapping.tolist() == want["slot_mapping"]
+    _same_state(dev, ref)
 
 
 def test_plan_step_refuses_cleanly_when_the_ring_is_empty_or_a_row_is_full(ops):

@@ -1,6 +1,9 @@
-"""GPU, two ranks over NCCL: the head-sharded decode step. Each rank holds half of the kv heads
-(its slice of the paged K/V pool) and half of the query heads (its slice of the GLA state), runs the
-same kernels on its slice, and the head outputs are all-gathered. Skipped on a box with one GPU."""
+"""GPU, several ranks (one process per GPU): the head-sharded decode step. Each rank holds its share
+of the kv heads (its slice of the paged K/V pool) and of the query heads (its slice of the GLA state),
+runs the same kernels on its slice, and the head outputs are gathered on every rank -- by NCCL, or by
+the kernels themselves through peer stores. Two ranks split 28/4 heads as 14/2, four ranks as 7/1
+(the split the churn configuration names); eight GPUs run as 4 head shards x 2 sequence groups.
+Every test is skipped on a box with fewer GPUs than it needs."""
 import os
 import socket
 import subprocess
@@ -66,23 +69,31 @@ WORKER = textwrap.dedent("""
 """)
 
 
-def test_head_sharded_decode_two_ranks_nccl(sb, tmp_path):
-    if torch.cuda.device_count() < 2:
-        pytest.skip("needs two GPUs")
-    script = tmp_path / "worker.py"
-    script.write_text(WORKER.format(root=ROOT))
+def _run_ranks(n_ranks, script_text, tmp_path, name, extra_env=None):
+    """One child process per rank on GPUs 0 .. n_ranks-1; every one must exit 0."""
+    if torch.cuda.device_count() < n_ranks:
+        pytest.skip(f"needs {n_ranks} GPUs")
+    script = tmp_path / name
+    script.write_text(script_text)
     with socket.socket() as s:
         s.bind(("127.0.0.1", 0))
         port = s.getsockname()[1]
     procs = []
-    for rank in range(2):
-        env = dict(os.environ, RANK=str(rank), LOCAL_RANK=str(rank), WORLD_SIZE="2", MASTER_ADDR="127.0.0.1",
-                   MASTER_PORT=str(port))
+    for rank in range(n_ranks):
+        env = dict(os.environ, RANK=str(rank), LOCAL_RANK=str(rank), WORLD_SIZE=str(n_ranks),
+                   MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+        env.update(extra_env or {})
         procs.append(subprocess.Popen([sys.executable, str(script)], env=env, stdout=subprocess.PIPE,
                                       stderr=subprocess.PIPE, text=True))
     outs = [p.communicate(timeout=600) for p in procs]
     for p, (out, err) in zip(procs, outs):
         assert p.returncode == 0, err[-3000:]
+    return outs
+
+
+@pytest.mark.parametrize("n_ranks", [2, 4])
+def test_head_sharded_decode_nccl(sb, tmp_path, n_ranks):
+    outs = _run_ranks(n_ranks, WORKER.format(root=ROOT), tmp_path, "worker.py")
     assert '"ok": true' in outs[0][0]
 
 
@@ -186,33 +197,92 @@ FUSED_WORKER = textwrap.dedent("""
 """)
 
 
-def _run_two_ranks(script_text, tmp_path, name, extra_env=None):
-    script = tmp_path / name
-    script.write_text(script_text)
-    with socket.socket() as s:
-        s.bind(("127.0.0.1", 0))
-        port = s.getsockname()[1]
-    procs = []
-    for rank in range(2):
-        env = dict(os.environ, RANK=str(rank), LOCAL_RANK=str(rank), WORLD_SIZE="2", MASTER_ADDR="127.0.0.1",
-                   MASTER_PORT=str(port))
-        env.update(extra_env or {})
-        procs.append(subprocess.Popen([sys.executable, str(script)], env=env, stdout=subprocess.PIPE,
-                                      stderr=subprocess.PIPE, text=True))
-    outs = [p.communicate(timeout=600) for p in procs]
-    for p, (out, err) in zip(procs, outs):
-        assert p.returncode == 0, err[-3000:]
-    return outs
-
-
-def test_fused_head_gather_two_ranks(sb, tmp_path):
-    """Two processes, two GPUs: the decode kernel stores each rank's head slice into the other
-    rank's buffer through NVLink and raises its flag; the result equals the collective's bit for bit."""
-    if torch.cuda.device_count() < 2:
-        pytest.skip("needs two GPUs")
-    outs = _run_two_ranks(FUSED_WORKER.format(root=ROOT), tmp_path, "fused_worker.py")
+@pytest.mark.parametrize("n_ranks", [2, 4])
+def test_fused_head_gather(sb, tmp_path, n_ranks):
+    """One process per GPU: the decode kernel (and the GLA step) stores each rank's head slice into
+    every other rank's buffer through NVLink and raises its flag there; the result equals the
+    collective's bit for bit and the oracle within the attention / GLA bars. Four ranks: 7 query
+    heads and 1 kv head per rank, three peers per rank."""
+    outs = _run_ranks(n_ranks, FUSED_WORKER.format(root=ROOT), tmp_path, "fused_worker.py")
     assert '"ok": true' in outs[0][0]
     print(outs[0][0].strip().splitlines()[-1])
+
+
+HYBRID_WORKER = textwrap.dedent("""
+    import os, sys, math, json, datetime
+    sys.path.insert(0, {root!r})
+    import torch
+    import torch.distributed as dist
+    from oracle import ref_ops
+    from tests.helpers import make_paged_kv, mean_rel, rel_err
+    from spikingbrain_7b_b200 import ops
+    from spikingbrain_7b_b200.head_shard import FusedHeadGather, all_gather_heads, make_hybrid_layout, shard_heads
+
+    rank, world = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"])
+    tp = {tp}
+    torch.cuda.set_device(rank)
+    dev = torch.device("cuda", rank)
+    dist.init_process_group("nccl", device_id=dev, timeout=datetime.timedelta(seconds=90))
+    lay = make_hybrid_layout(tp)
+    assert lay.n_seq_groups == world // tp and lay.tp_rank == rank % tp and lay.seq_group == rank // tp
+    H, KVH, D, bs, wl = 28, 4, 128, 16, 1023
+    all_lens = [1500, 17, 1024, 1025, 300, 64, 0, 5000, 33, 2048, 700]
+    kv, table, nb = make_paged_kv(all_lens, wl, KVH, D, bs, seed=56)          # the same global problem everywhere
+    mine = lay.my_sequences(len(all_lens))                                   # this group's sequences ...
+    qh, kh = shard_heads(H, KVH, tp, lay.tp_rank)                            # ... and this rank's heads
+    lens = all_lens[mine.start:mine.stop]
+    B = len(lens)
+    kv_l = kv[:, :, :, kh.start:kh.stop].contiguous().to(dev)
+    table_d = table[mine.start:mine.stop].contiguous().to(dev)
+    lens_d = torch.tensor(lens, dtype=torch.int32, device=dev)
+    fg = FusedHeadGather(16, H, D, group=lay.tp_group, device=dev, timeout_ms=5000)
+    g = torch.Generator().manual_seed(57)
+    for step in range(4):
+        q = (torch.randn(len(all_lens), H, D, generator=g) / math.sqrt(D)).bfloat16()
+        q_l = q[mine.start:mine.stop, qh.start:qh.stop].contiguous().to(dev)
+        got = fg.decode(q_l, kv_l[0], kv_l[1], table_d, lens_d, window_left=wl).clone()
+        want = all_gather_heads(ops.swa_decode(q_l, kv_l[0], kv_l[1], table_d, lens_d, window_left=wl),
+                                group=lay.tp_group)
+        torch.cuda.synchronize()
+        assert fg.status.item() == 0, fg.status.item()
+        assert got.shape == (B, H, D) and torch.equal(got, want)             # gathered inside the group only
+        ref = ref_ops.swa_paged_decode_ref(q[mine.start:mine.stop], kv[0], kv[1], table[mine.start:mine.stop], lens,
+                                           wl, D ** -0.5).bfloat16().float()
+        a = got.float().cpu()
+        assert float((a - ref).abs().max()) <= 2e-2 and mean_rel(a, ref) <= 1e-3
+    gq = torch.relu(torch.randn(len(all_lens), H, D, generator=g) / math.sqrt(D)).bfloat16()
+    gk = torch.relu(torch.randn(len(all_lens), KVH, D, generator=g) / math.sqrt(D)).bfloat16()
+    gv = (torch.randn(len(all_lens), KVH, D, generator=g) / math.sqrt(D)).bfloat16()
+    gg = (torch.nn.functional.logsigmoid(torch.randn(len(all_lens), KVH, D, generator=g)) / 16).bfloat16()
+    gstate = torch.randn(len(all_lens), H, D, D, generator=g)
+    sl = lambda t, hs: t[mine.start:mine.stop, hs.start:hs.stop].contiguous().to(dev)
+    s_l = sl(gstate, qh)
+    og = fg.gla_step(sl(gq, qh), sl(gk, kh), sl(gv, kh), sl(gg, kh), s_l).clone()
+    torch.cuda.synchronize()
+    assert fg.status.item() == 0
+    ref_state = gstate[mine.start:mine.stop].clone()
+    gref = ref_ops.gla_step_ref(gq[mine.start:mine.stop], gk[mine.start:mine.stop], gv[mine.start:mine.stop],
+                                gg[mine.start:mine.stop], ref_state)
+    assert float((og.float().cpu() - gref.bfloat16().float()).abs().max()) <= 2e-2 * float(gref.abs().max())
+    assert rel_err(s_l.cpu(), ref_state[:, qh.start:qh.stop]) <= 1e-4
+    if fg.calls & 1:
+        fg.gla_step(sl(gq, qh), sl(gk, kh), sl(gv, kh), sl(gg, kh), s_l)
+    fg.close()
+    dist.barrier()
+    if rank == 0:
+        print(json.dumps({{"ok": True, "groups": lay.n_seq_groups, "tp": tp}}))
+    dist.destroy_process_group()
+""")
+
+
+@pytest.mark.parametrize("n_ranks,tp", [(4, 2), (8, 4)])
+def test_hybrid_layout_head_shards_times_sequence_groups(sb, tmp_path, n_ranks, tp):
+    """n_ranks GPUs as n_ranks/tp sequence groups of tp head shards (eight GPUs: 4 x 2, because 28
+    heads do not split eight ways): every group decodes its own sequences, the fused gather and the
+    collective run inside a group only, and each rank ends up with all 28 heads of its group's
+    sequences -- bit-equal between the two gathers and within the bars of the oracle."""
+    outs = _run_ranks(n_ranks, HYBRID_WORKER.format(root=ROOT, tp=tp), tmp_path, "hybrid_worker.py")
+    assert '"ok": true' in outs[0][0]
 
 
 MISSED_STEP_WORKER = textwrap.dedent("""
@@ -247,9 +317,9 @@ MISSED_STEP_WORKER = textwrap.dedent("""
         return o
     assert torch.equal(step(), want) and fg.status.item() == 0
     dist.barrier()
-    # rank 1 sits the next step out (between steps, nothing of its own in flight): rank 0's wait runs
-    # out after 300 ms, says so in the status word and returns; the context stays usable
-    if rank == 0:
+    # the last rank sits the next step out (between steps, nothing of its own in flight): the others'
+    # wait runs out after 300 ms, says so in the status word and returns; the context stays usable
+    if rank != world - 1:
         t0 = time.time()
         step()
         assert fg.status.item() == _abi.ST_WAIT_TIMEOUT
@@ -267,12 +337,11 @@ MISSED_STEP_WORKER = textwrap.dedent("""
 """)
 
 
-def test_fused_head_gather_missed_step_is_reported_and_recovered(sb, tmp_path):
-    """A peer that does not take a step: the bounded flag wait reports it (no hang, no fault), and after a
-    host-side resync the gather works again."""
-    if torch.cuda.device_count() < 2:
-        pytest.skip("needs two GPUs")
+@pytest.mark.parametrize("n_ranks", [2, 4])
+def test_fused_head_gather_missed_step_is_reported_and_recovered(sb, tmp_path, n_ranks):
+    """A peer that does not take a step (the last rank sits it out): the bounded flag wait of every
+    other rank reports it (no hang, no fault), and after a host-side resync the gather works again."""
     # in-switch reduction off in the collective library for a test in which a rank falls out of step
-    outs = _run_two_ranks(MISSED_STEP_WORKER.format(root=ROOT), tmp_path, "missed_step_worker.py",
-                          extra_env={"NCCL_NVLS_ENABLE": "0"})
+    outs = _run_ranks(n_ranks, MISSED_STEP_WORKER.format(root=ROOT), tmp_path, "missed_step_worker.py",
+                      extra_env={"NCCL_NVLS_ENABLE": "0"})
     assert '"ok": true' in outs[0][0]

@@ -24,7 +24,63 @@ def test_library_exports_every_declared_symbol(sb):
         assert hasattr(lib, name), f"{name} declared in include/sbk.h but not exported"
     from spikingbrain_7b_b200 import _abi
     assert set(_abi.SIGNATURES) == declared
-    assert _abi.lib.sbk_abi_version() == _abi.ABI_VERSION == 4
+    assert _abi.lib.sbk_abi_version() == _abi.ABI_VERSION == 5
+    assert int(re.search(r"#define SBK_ABI_VERSION (\d+)", header).group(1)) == _abi.ABI_VERSION
+
+
+def _header_prototypes():
+    """name -> (return class, [argument class]) of every function include/sbk.h declares; a class is
+    'ptr', 'float', 'i32', 'i64' or 'size'."""
+    text = open(os.path.join(ROOT, "include", "sbk.h")).read()
+    text = re.sub(r"/\*.*?\*/", " ", text, flags=re.S)
+    text = "\n".join(l for l in text.splitlines() if not l.lstrip().startswith("#"))
+
+    def cls(decl):
+        decl = decl.strip()
+        if "*" in decl:
+            return "ptr"
+        base = re.sub(r"\b(const|unsigned)\b", "", decl).split()
+        ty = base[0] if base else decl
+        return {"float": "float", "int": "i32", "int32_t": "i32", "int64_t": "i64", "size_t": "size",
+                "void": "void"}[ty]
+
+    protos = {}
+    for ret, name, args in re.findall(r"([A-Za-z_0-9\s\*]+?)\b(sbk_[a-z_0-9]+)\s*\(([^)]*)\)\s*;", text):
+        args = args.strip()
+        arg_list = [] if args in ("", "void") else [cls(a) for a in args.split(",")]
+        protos[name] = (cls(ret), arg_list)
+    return protos
+
+
+def test_binding_signatures_match_the_header(sb):
+    """Every prototype of include/sbk.h against _abi.SIGNATURES: same argument count, and pointer /
+    float / 32-bit / 64-bit / size class of every argument and of the return value, so the header,
+    the ctypes binding and the stub in INTEGRATION.md (generated from the binding) cannot drift."""
+    from ctypes import c_char_p, c_float, c_int, c_int32, c_int64, c_size_t, c_void_p
+    from spikingbrain_7b_b200 import _abi
+    to_cls = {c_void_p: "ptr", c_char_p: "ptr", c_float: "float", c_int: "i32", c_int32: "i32", c_int64: "i64",
+              c_size_t: "size"}
+    protos = _header_prototypes()
+    assert set(protos) == set(_abi.SIGNATURES)
+    for name, (restype, argtypes) in _abi.SIGNATURES.items():
+        h_ret, h_args = protos[name]
+        assert to_cls[restype] == h_ret, f"{name}: return type"
+        assert len(argtypes) == len(h_args), f"{name}: {len(argtypes)} bound arguments, {len(h_args)} declared"
+        for i, (a, b) in enumerate(zip(argtypes, h_args)):
+            assert to_cls[a] == b, f"{name}: argument {i} bound as {to_cls[a]}, declared {b}"
+
+
+def test_integration_doc_stub_is_the_current_binding(sb):
+    """The sample ctypes stub in INTEGRATION.md lists sbk_gla_step's arguments: they must be the
+    header's, in number and order."""
+    text = open(os.path.join(ROOT, "include", "sbk.h")).read()
+    m = re.search(r"int sbk_gla_step\(([^;]*)\);", text)
+    names = [a.strip().split()[-1].lstrip("*") for a in m.group(1).replace("\n", " ").split(",")]
+    doc = open(os.path.join(ROOT, "INTEGRATION.md")).read()
+    stub = re.search(r"sbk_gla_step\.argtypes = \[(.*?)\]", doc, flags=re.S)
+    assert stub is not None, "INTEGRATION.md lost its sbk_gla_step stub"
+    doc_names = re.findall(r"#\s*([A-Za-z_0-9]+)", stub.group(1))
+    assert doc_names == names, (doc_names, names)
 
 
 def test_host_side_argument_errors_need_no_gpu(sb):
@@ -34,12 +90,12 @@ def test_host_side_argument_errors_need_no_gpu(sb):
     rc = lib.sbk_gla_step(None, None, None, None, 0, None, 4, None, 2, 28, 4, 96, 1.0, None, 0, 0, 0.0, None, 0.0, None, None)
     assert rc == _abi.SBK_E_ARG and b"D=96" in lib.sbk_last_error()
     rc = lib.sbk_swa_decode(None, 0, None, None, None, 4, None, 2, 36, 4, 128, 8, 16, 0, 63, 1.0, None, 0, 0,
-                            None, None, 0, 0, 1, None, None, 0, None, None)
+                            None, None, 0, 0, 1, -1, None, None, 0, None, None)
     assert rc == _abi.SBK_E_ARG and b"unsupported shape" in lib.sbk_last_error()
     rc = lib.sbk_swa_decode(None, 0, None, None, None, 4, None, 2, 28, 4, 128, 8, 24, 0, 63, 1.0, None, 0, 0,
-                            None, None, 0, 0, 1, None, None, 0, None, None)
+                            None, None, 0, 0, 1, -1, None, None, 0, None, None)
     rc2 = lib.sbk_swa_decode(None, 0, None, None, None, 4, None, 2, 28, 4, 128, 8, 16, 0, 63, 1.0, None, 0, 0,
-                             None, None, 0, 0, 1, None, None, 100, None, None)
+                             None, None, 0, 0, 1, -1, None, None, 100, None, None)
     assert rc2 == _abi.SBK_E_ARG            # 100 sink tokens: not a multiple of 16, and no tensors
     assert rc == _abi.SBK_E_ARG and b"multiple of 16" in lib.sbk_last_error()
     assert lib.sbk_kv_append(None, None, None, None, None, 3, 4, 128, 2, 1024, 8, 16, 16384, None, 0, None,
@@ -47,6 +103,13 @@ def test_host_side_argument_errors_need_no_gpu(sb):
     # empty work is a successful no-op
     assert lib.sbk_gla_step(None, None, None, None, 0, None, 0, None, 0, 28, 4, 128, 1.0, None, 0, 0, 0.0, None, 0.0, None, None) == 0
     assert lib.sbk_swa_workspace_bytes(256, 28, 128, 9) >= 256 * 9 * 28 * 130 * 4
+    # the chunk-parallel GLA scan: cut only when the (sequence, head) chains leave the GPU mostly idle
+    assert lib.sbk_gla_scan_workspace_bytes(8, 8192, 28, 128) == 0          # 224 chains: not cut
+    assert lib.sbk_gla_scan_workspace_bytes(1, 256, 28, 128) == 0           # too short to cut
+    assert lib.sbk_gla_scan_workspace_bytes(1, 8192, 28, 128) == 9 * 28 * (128 * 128 + 128) * 4   # 10 sub-chunks
+    rc = lib.sbk_swa_prefill(None, 0, None, None, None, 4, None, None, 1, 16, 28, 4, 128, 8, 16, 0, 63, 1.0, None, 0,
+                             None, None, 0, 7, None, None)
+    assert rc == _abi.SBK_E_ARG and b"kernel=7" in lib.sbk_last_error()
     with pytest.raises(RuntimeError):
         from spikingbrain_7b_b200 import ops
         ops.gla_step(torch.zeros(1, 2, 64), torch.zeros(1, 2, 64), torch.zeros(1, 2, 64),

@@ -6,6 +6,9 @@ free HBM on its KV pool at start-up, or a control loop that bans allocator calls
 For them the decode scratch sits in a fixed array inside the library. The array is shared by
 every call and remembers what the previous call wrote, so the check runs twice in a row on
 different inputs: the second call must not be disturbed by what the first one left behind.
+With fixed pieces the order in which a sequence's partials are folded does not depend on timing,
+so the two entry points must agree bit for bit (a tolerance here could hide a stale partial); the
+CPU oracle is the second, independent comparison, within the bars of the other attention tests.
 Collected last on purpose (file name), so a run that stops at the first failure has already
 been through every other test.
 """
@@ -39,10 +42,12 @@ def _call(lib, static, q, kv, table, lens, out, lse, H, kvh, D, bs, wl, split, m
     tail = (split, max_pieces, status.data_ptr(), stream)
     if static:
         return lib.sbk_swa_decode_static(*head, *tail)
-    return lib.sbk_swa_decode(*head, ws.data_ptr(), ws.numel(), split, max_pieces, None, None, 0, status.data_ptr(), stream)
+    return lib.sbk_swa_decode(*head, ws.data_ptr(), ws.numel(), split, max_pieces, -1, None, None, 0,
+                              status.data_ptr(), stream)
 
 
 def test_static_scratch_entry_point_matches_workspace_entry_point_twice(sb):
+    from oracle import ref_ops
     from spikingbrain_7b_b200 import _abi
     lib = _abi.lib
     assert torch.cuda.is_available()
@@ -64,11 +69,14 @@ def test_static_scratch_entry_point_matches_workspace_entry_point_twice(sb):
         assert rc == 0, lib.sbk_last_error()
         torch.cuda.synchronize()
         assert status.item() == 0
-        a, b = out_new.float(), out_ref.float()
-        assert torch.isfinite(a).all(), f"round {round_no}"
-        assert float((a - b).abs().max()) <= MAX_ABS, f"round {round_no}"
-        assert float((a - b).abs().sum() / b.abs().sum()) <= MEAN_REL, f"round {round_no}"
-        assert float((lse_new - lse_ref).abs().max()) <= 1e-3, f"round {round_no}"
+        assert torch.isfinite(out_new.float()).all(), f"round {round_no}"
+        assert torch.equal(out_new, out_ref), f"round {round_no}: the two entry points differ"
+        assert torch.equal(lse_new, lse_ref), f"round {round_no}: the two entry points differ in lse"
+        want = ref_ops.swa_paged_decode_ref(q.cpu(), kv[0].cpu(), kv[1].cpu(), table.cpu(), lens, wl,
+                                            D ** -0.5).bfloat16().float()
+        a = out_new.float().cpu()
+        assert float((a - want).abs().max()) <= MAX_ABS, f"round {round_no}"
+        assert float((a - want).abs().sum() / want.abs().sum()) <= MEAN_REL, f"round {round_no}"
 
 
 def test_static_scratch_entry_point_rejects_what_does_not_fit(sb):
