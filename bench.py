@@ -16,6 +16,18 @@ N GPUs: every rank owns its own 256 sequences (sequence sharding, no collective)
 
 Prints ONE JSON line (rank 0). `--impl reference` times the CPU oracle (the PyTorch
 restatement of the reference path) on the host cores instead.
+
+The default run is the configuration the metric is quoted on (batch 256 at 8192 tokens). The other
+configurations of the path have lines of their own (never the headline):
+    --config 2     single-step op test: one sliding-window + one GLA layer, batch 64, contexts
+                   uniform in [1024, 32768]
+    --config 4     long-context eviction: per GPU one 131072-token prompt prefilled in 8192-token
+                   chunks through the block tables (append + windowed attention + GLA scan), then
+                   512 decode steps, on the device-resident planner
+    --head-shard   churn shapes (1024 sequences, Zipf lengths) with the heads split over the ranks
+`--full-step` adds to the default line the same step with the model's dense callers around the
+path (projections, MLP, norms, logits: plain PyTorch on random bf16 weights of the 7B shapes), as
+`full_step`, so that the cache-path tokens/s is not read as a model throughput.
 """
 import argparse
 import json
@@ -49,7 +61,8 @@ def parse_args():
     ap.add_argument("--steps", type=int, default=50)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
-    ap.add_argument("--batch", type=int, default=256, help="sequences per GPU")
+    ap.add_argument("--batch", type=int, default=None,
+                    help="sequences per GPU (default: 256; --config 2: 64; --config 4: 1)")
     ap.add_argument("--ctx", type=int, default=8192, help="context length of every sequence")
     ap.add_argument("--swa-layers", type=int, default=N_SWA)
     ap.add_argument("--gla-layers", type=int, default=N_GLA)
@@ -59,19 +72,41 @@ def parse_args():
     ap.add_argument("--head-shard", action="store_true",
                     help="instead of the headline run: the churn workload (1024 sequences, Zipf lengths) with attention "
                          "heads split over the ranks, sliding-window decode + gather of the head outputs per layer")
+    ap.add_argument("--config", type=int, default=3, choices=[2, 3, 4],
+                    help="which configuration of the path to run (3 = the headline; 2 and 4 print lines of their own)")
+    ap.add_argument("--full-step", action="store_true",
+                    help="also time the decode step with the model's dense callers (plain PyTorch) around the path")
+    ap.add_argument("--prompt", type=int, default=131072, help="--config 4: prompt tokens per sequence")
+    ap.add_argument("--chunk", type=int, default=8192, help="--config 4: prefill chunk")
+    ap.add_argument("--decode-steps", type=int, default=512, help="--config 4: decode steps after the prompt")
     ap.add_argument("--tp", type=int, default=0,
                     help="--head-shard: head shards per group (default: all ranks); the ranks form world/tp "
                          "sequence groups, e.g. 8 GPUs as 4 head shards x 2 groups")
-    return ap.parse_args()
+    args = ap.parse_args()
+    if args.batch is None:
+        args.batch = {2: 64, 3: 256, 4: 1}[args.config]
+    if args.config == 2:
+        args.swa_layers = args.gla_layers = 1
+    return args
 
 
 # ------------------------------------------------------------------------- bytes model
-def cache_bytes_per_step(batch, ctx_after, n_swa, n_gla):
-    """Algorithmic cache bytes of one decode step (K/V read + appended, GLA state read+written)."""
-    vis = min(ctx_after, WINDOW_LEFT + 1)
-    swa = batch * (vis * 2 * KVH * D * 2 + 2 * KVH * D * 2)
+def cache_bytes_per_step(lens_after, n_swa, n_gla):
+    """Algorithmic cache bytes of one decode step (K/V read + appended, GLA state read+written) for
+    sequences of the given lengths (after the step's token)."""
+    batch = len(lens_after)
+    vis = sum(min(int(L), WINDOW_LEFT + 1) for L in lens_after)
+    swa = vis * 2 * KVH * D * 2 + batch * 2 * KVH * D * 2
     gla = batch * 2 * H * D * D * 4
     return n_swa * swa + n_gla * gla, swa, gla
+
+
+def config_lens(args):
+    """Context length of every sequence of a rank at the start of the run."""
+    import numpy as np
+    if args.config == 2:      # uniform in [1024, 32768], seed 0
+        return np.random.default_rng(0).integers(1024, 32769, size=args.batch).astype(np.int64)
+    return np.full(args.batch, args.ctx, dtype=np.int64)
 
 
 # ------------------------------------------------------------------- CPU oracle timing
@@ -254,23 +289,27 @@ class DecodeEngine:
         self.device = device
         self.B = B = args.batch
         self.n_swa, self.n_gla = args.swa_layers, args.gla_layers
-        total_steps = args.steps * 2 + args.warmup * 2 + 8
-        max_len = args.ctx + total_steps + 1
+        lens = config_lens(args)
+        self.lens0 = lens
+        total_steps = args.steps * 3 + args.warmup * 3 + 16
+        max_len = int(lens.max()) + total_steps + 1
         self.max_blocks = (max_len + BLOCK - 1) // BLOCK + 1
-        live = (WINDOW_LEFT + 1) // BLOCK + 3
-        n_blocks = B * live + 64
+        # sequences arrive with their context: only the window's blocks are resident, handed out
+        # in a random order; the rest of the pool (three spare blocks per sequence) is the free ring
+        first_live = np.maximum(0, lens - WINDOW_LEFT) // BLOCK
+        last = (lens + BLOCK - 1) // BLOCK
+        n_live = last - first_live
+        n_blocks = int(n_live.sum()) + 3 * B + 64
         self.plan = DeviceStepPlanner(n_blocks, BLOCK, WINDOW_LEFT, B, self.max_blocks, device)
-        # sequences arrive with `ctx` tokens of context: only the window's blocks are resident,
-        # handed out in a random order; the rest of the pool is the free ring
         g = np.random.default_rng(1234 + (device.index or 0))
         order = g.permutation(n_blocks).astype(np.int32)
-        first_live = max(0, args.ctx - WINDOW_LEFT) // BLOCK
-        last = (args.ctx + BLOCK - 1) // BLOCK
         table = np.full((B, self.max_blocks), -1, dtype=np.int32)
-        used = B * (last - first_live)
-        table[:, first_live:last] = order[:used].reshape(B, last - first_live)
-        self.plan.load_state(np.full(B, args.ctx, dtype=np.int32), table, order[used:])
-        self.ctx0, self.steps_done = args.ctx, 0
+        used = 0
+        for b in range(B):
+            table[b, first_live[b]:last[b]] = order[used:used + n_live[b]]
+            used += int(n_live[b])
+        self.plan.load_state(lens.astype(np.int32), table, order[used:])
+        self.ctx0, self.steps_done = int(lens.max()), 0
         self.table_d, self.lens_d, self.slots_d = self.plan.block_tables, self.plan.seq_lens, self.plan.slot_mapping
         self.kv = []
         for _ in range(self.n_swa):
@@ -293,7 +332,7 @@ class DecodeEngine:
         self.gg = (torch.nn.functional.logsigmoid(torch.randn(B, KVH, 1, D, device=device)) / 16).bfloat16()
         self.out = torch.empty(B, H, D, dtype=torch.bfloat16, device=device)
         self.gla_out = torch.empty(B, H, D, dtype=torch.bfloat16, device=device)
-        self.graph = self.graph_e2e = self._e2e = None
+        self.graph = self.graph_e2e = self._e2e = self.graph_full = self._full = None
         self.swa_events = []
         self.launches_per_step = 0
         # pinned host staging for the end-to-end mode
@@ -380,6 +419,101 @@ class DecodeEngine:
                 self.graph = g
         torch.cuda.current_stream().wait_stream(side)
         torch.cuda.synchronize()
+
+    # ---------------------------------------------------- the step with the model's dense callers
+    HIDDEN, INTER, VOCAB = 3584, 18944, 152064
+
+    def _full_setup(self):
+        """Random bf16 weights of the 7B shapes (hidden 3584, MLP 18944, 28 layers alternating GLA /
+        sliding-window attention, vocabulary 152064): the callers of the cache path, as plain PyTorch."""
+        torch = self.torch
+        if self._full is not None:
+            return self._full
+        dev, hid, inter = self.device, self.HIDDEN, self.INTER
+        kvd = KVH * D
+
+        def w(o, i):
+            return torch.empty(o, i, device=dev, dtype=torch.bfloat16).normal_(0.0, i ** -0.5)
+
+        ones = lambda n: torch.ones(n, device=dev, dtype=torch.bfloat16)
+        f = type("Full", (), {})()
+        f.gla, f.swa = [], []
+        mlp = lambda: dict(n2=ones(hid), gate_up=w(2 * inter, hid), down=w(hid, inter))
+        for _ in range(self.n_gla):
+            f.gla.append(dict(n1=ones(hid), qkv=w(hid + 2 * kvd, hid), gk0=w(16, hid), gk1=w(kvd, 16), gate=w(hid, hid),
+                              o=w(hid, hid), g_norm=ones(D), **mlp()))
+        for _ in range(self.n_swa):
+            f.swa.append(dict(n1=ones(hid), qkv=w(hid + 2 * kvd, hid), o=w(hid, hid), **mlp()))
+        f.final_norm, f.lm_head = ones(hid), w(self.VOCAB, hid)
+        f.x0 = torch.randn(self.B, hid, device=dev).bfloat16()
+        f.tokens = torch.zeros(self.B, dtype=torch.int64, device=dev)
+        f.attn_out = torch.empty(self.B, H, D, dtype=torch.bfloat16, device=dev)
+        f.cos_sin = self.ops.build_cos_sin_cache(D, self.max_blocks * BLOCK, 1e6, torch.bfloat16, dev)
+        n_params = sum(t.numel() for lay in f.gla + f.swa for t in lay.values()) + f.lm_head.numel()
+        f.weight_bytes = 2 * n_params
+        self._full = f
+        return f
+
+    def enqueue_full(self, meta):
+        """One decode step of the whole stack on the current stream: norms, projections, the cache path
+        (GLA step with its fused neighbours; rotary + append + sliding-window decode), output
+        projections, MLPs and the logits' argmax. The dense parts are torch ops (cuBLAS)."""
+        from spikingbrain_7b_b200.gla_slots import gla_decode_layer
+        torch, f = self.torch, self._full_setup()
+        F = torch.nn.functional
+        hid, inter, kvd, B = self.HIDDEN, self.INTER, KVH * D, self.B
+        self.plan.plan()
+        h = f.x0
+
+        def mlp(h, lay):
+            r = F.rms_norm(h, (hid,), lay["n2"], 1e-6)
+            gu = r @ lay["gate_up"].t()
+            return h + (F.silu(gu[:, :inter]) * gu[:, inter:]) @ lay["down"].t()
+
+        for i in range(max(self.n_swa, self.n_gla)):
+            if i < self.n_gla:
+                lay = f.gla[i]
+                r = F.rms_norm(h, (hid,), lay["n1"], 1e-6)
+                qkv = r @ lay["qkv"].t()
+                q = qkv[:, :hid].reshape(B, H, D)
+                k = qkv[:, hid:hid + kvd].reshape(B, KVH, D)
+                v = qkv[:, hid + kvd:].reshape(B, KVH, D)
+                gk = ((r @ lay["gk0"].t()) @ lay["gk1"].t()).view(B, KVH, D)
+                o = gla_decode_layer(q, k, v, gk, self.gla.cache[i], self.slot_idx, lay["g_norm"])
+                o = o.view(B, hid) * F.silu(r @ lay["gate"].t())
+                h = mlp(h + o @ lay["o"].t(), lay)
+            if i < self.n_swa:
+                lay = f.swa[i]
+                r = F.rms_norm(h, (hid,), lay["n1"], 1e-6)
+                qkv = r @ lay["qkv"].t()
+                q = qkv[:, :hid].view(B, H, D)
+                k = qkv[:, hid:hid + kvd].view(B, KVH, D)
+                v = qkv[:, hid + kvd:].view(B, KVH, D)
+                self.impls[i].forward(None, q, k, v, None, None, None, self.kv[i], meta, output=f.attn_out,
+                                      positions=self.plan.positions, cos_sin_cache=f.cos_sin)
+                h = mlp(h + f.attn_out.view(B, hid) @ lay["o"].t(), lay)
+        logits = F.rms_norm(h, (hid,), f.final_norm, 1e-6) @ f.lm_head.t()
+        f.tokens.copy_(logits.argmax(-1))
+
+    def capture_full(self):
+        torch = self.torch
+        meta = self._metadata()
+        side = torch.cuda.Stream(device=self.device)
+        side.wait_stream(torch.cuda.current_stream())
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.stream(side):
+            self.enqueue_full(meta)          # warm-up: cuBLAS workspaces, kernel attributes
+            self.enqueue_full(meta)
+            with torch.cuda.graph(g, stream=side):
+                self.enqueue_full(meta)
+        torch.cuda.current_stream().wait_stream(side)
+        torch.cuda.synchronize()
+        self.steps_done += 3
+        self.graph_full = g
+
+    def step_full(self):
+        self.steps_done += 1
+        self.graph_full.replay()
 
     # ------------------------------------------------------------------- end-to-end step
     def _e2e_setup(self):
@@ -483,6 +617,15 @@ def max_over_ranks(value, device):
     return float(t.item())
 
 
+def workload_name(args):
+    shapes = f"window_left {WINDOW_LEFT}, block {BLOCK}, 28/4 heads, head_dim 128"
+    if args.config == 2:
+        return (f"single-step op test: {args.swa_layers} sliding-window + {args.gla_layers} GLA layer, batch {args.batch} "
+                f"per GPU, ctx uniform in [1024, 32768] (numpy default_rng(0)), {shapes}")
+    return (f"7B-shaped decode step, cache path of {args.swa_layers} sliding-window + {args.gla_layers} GLA layers, "
+            f"batch {args.batch} per GPU, ctx {args.ctx}, {shapes}")
+
+
 def job_tokens_per_s(batch_per_rank, world, ms_per_step):
     """Whole-job throughput: every rank decodes one token for each of its sequences per step."""
     return batch_per_rank * world / (ms_per_step * 1e-3)
@@ -580,6 +723,27 @@ def run_b200(args):
                    "h2d_bytes_per_step": eng.h2d_bytes // args.steps,
                    "d2h_bytes_per_step": eng.d2h_bytes // args.steps, "ms_per_step": e2e_ms}
 
+    # ---- the same step with the model's dense callers around the path (plain PyTorch) ----
+    full_obj = None
+    if args.full_step:
+        eng.capture_full()
+        for _ in range(3):
+            eng.step_full()
+        barrier()
+        e0 = torch.cuda.Event(enable_timing=True); e1 = torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(args.steps):
+            eng.step_full()
+        e1.record()
+        torch.cuda.synchronize()
+        full_ms = max_over_ranks(e0.elapsed_time(e1), device) / args.steps
+        full_obj = {"tokens_per_s": job_tokens_per_s(args.batch, world, full_ms), "ms_per_step": full_ms,
+                    "cache_path_share_of_step": ms_per_step / full_ms, "weight_bytes_per_gpu": eng._full.weight_bytes,
+                    "what": "the decode step with RMSNorm, QKV / gate / low-rank gate / output projections, SwiGLU MLP "
+                            "and logits + argmax as torch ops on random bf16 weights of the 7B shapes (hidden 3584, "
+                            "MLP 18944, vocabulary 152064), the cache path through the fused forms (rotary in the append; "
+                            "ReLU, gate and g_norm in the GLA step); CUDA graph replay"}
+
     # every status word of the run: the layers' kernels and the planner (a step the planner refuses
     # -- out of blocks, table full -- fills the slot mapping with -1 and appends nothing, so a run
     # that saw one has not timed the workload)
@@ -599,8 +763,8 @@ def run_b200(args):
         peak, peak_src = float(json.load(open(peaks_path))["hbm_gbs"]), "measured (MEASURED_PEAKS.json hbm_gbs)"
     else:
         peak, peak_src = FALLBACK_HBM_GBS, "fallback"
-    ctx_after = args.ctx + max(args.warmup, 3) + args.steps // 2
-    step_bytes, swa_layer_bytes, gla_layer_bytes = cache_bytes_per_step(args.batch, ctx_after, args.swa_layers, args.gla_layers)
+    lens_mid = eng.lens0 + max(args.warmup, 3) + args.steps // 2
+    step_bytes, swa_layer_bytes, gla_layer_bytes = cache_bytes_per_step(lens_mid, args.swa_layers, args.gla_layers)
     swa_avg_ms = statistics.mean(swa_ms) if swa_ms else None
     achieved = swa_layer_bytes / (swa_avg_ms * 1e-3) / 1e9 if swa_avg_ms else None
     line = {
@@ -609,12 +773,10 @@ def run_b200(args):
         "n_gpus": world, "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": ms_per_step,
         "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16 K/V, f32 GLA state",
         "data": "synthetic",
-        "config": {"workload": f"7B-shaped decode step, cache path of {args.swa_layers} sliding-window + "
-                               f"{args.gla_layers} GLA layers, batch {args.batch} per GPU, ctx {args.ctx}, "
-                               f"window_left {WINDOW_LEFT}, block {BLOCK}, 28/4 heads, head_dim 128",
+        "config": {"workload": workload_name(args),
                    "parallelism": f"sequence-sharded x{world}, no collective",
                    "launch": "host launches" if args.no_graph else "CUDA graph replay of the step (planner launch + layer kernels); no host metadata work",
-                   "l2": "working set (KV pools + GLA state, tens of GB) far exceeds the 126 MB L2; no flush needed"},
+                   "l2": f"the step streams {step_bytes / 1e6:.0f} MB of K/V and GLA state, more than the 126 MB L2; no flush needed"},
         "cache_gbs": world * step_bytes / (ms_per_step * 1e-3) / 1e9,
         "cache_gbs_per_gpu": step_bytes / (ms_per_step * 1e-3) / 1e9,
         "cache_frac_of_8tbs": step_bytes / (ms_per_step * 1e-3) / 1e9 / NOMINAL_HBM_GBS,
@@ -630,9 +792,274 @@ def run_b200(args):
                                        "one launch at this batch and context), scaled by tokens; not measured in this run"},
         "e2e": e2e_obj, "gpu_launches": launches, "clocks": clocks, "device_status": status,
     }
+    if args.config == 2:
+        line["gla_step_bytes_per_launch"] = gla_layer_bytes
+    if full_obj is not None:
+        line["full_step"] = full_obj
     if not args.no_cpu_baseline:
         line["cpu_baseline"] = cpu_baseline(args)
     print(json.dumps(line))
+    if world > 1:
+        dist.destroy_process_group()
+
+
+def run_longctx(args):
+    """Long-context eviction: every rank owns `batch` sequences (default one). A prompt of `--prompt`
+    tokens goes through the path in chunks of `--chunk`: one planner launch per chunk (retire the blocks
+    no token of the chunk can see, allocate the chunk's blocks, slots, lengths -- on the device), then per
+    layer the GLA scan with state carry (chunk-parallel when the sequences are few) and, through
+    MetaAttentionImpl.forward with prefill metadata, the append and the windowed attention over the block
+    tables. Then `--decode-steps` one-token steps replayed from a CUDA graph. Sequence-sharded: no
+    collective. Prints its own JSON line."""
+    import numpy as np
+    import torch
+    import torch.distributed as dist
+    local = int(os.environ.get("LOCAL_RANK", 0))
+    torch.cuda.set_device(local)
+    device = torch.device("cuda", local)
+    rank, world = dist_setup("nccl", device)
+    from spikingbrain_7b_b200 import ops
+    from spikingbrain_7b_b200.backend import MetaAttentionImpl, MetaAttentionMetadata
+    from spikingbrain_7b_b200.block_pool import DeviceStepPlanner
+    from spikingbrain_7b_b200.gla_slots import GLACacheManager, gla_prefill_scan, my_fused_recurrent_gla
+    instr = Instrument.install()
+    S, prompt, chunk, dsteps = args.batch, args.prompt, args.chunk, args.decode_steps
+    n_swa, n_gla = args.swa_layers, args.gla_layers
+    if prompt % chunk:
+        raise SystemExit("--prompt must be a multiple of --chunk")
+    T = S * chunk
+    max_blocks = (prompt + dsteps) // BLOCK + 2
+    per_seq = (WINDOW_LEFT + chunk) // BLOCK + 4       # the window, the chunk in flight, partial blocks at the ends
+    n_blocks = S * per_seq + 16
+    plan = DeviceStepPlanner(n_blocks, BLOCK, WINDOW_LEFT, S, max_blocks, device, max_tokens=T)
+    kv = [torch.zeros(2, n_blocks, BLOCK, KVH, D, dtype=torch.bfloat16, device=device) for _ in range(n_swa)]
+    gla = GLACacheManager(torch.float32, (max(n_gla, 1), S, H, D, D), device=device)
+    _, slot_idx = gla.current_run_tensors({f"r{i}": [0] for i in range(S)})
+    impls = [MetaAttentionImpl(H, D, D ** -0.5, KVH, None, WINDOW_LEFT + 1, "auto") for _ in range(n_swa)]
+    rn = lambda *s: (torch.randn(*s, device=device) / math.sqrt(D)).bfloat16()
+    q, k, v = rn(T, H, D), rn(T, KVH, D), rn(T, KVH, D)
+    gq, gk, gv = torch.relu(rn(T, H, D)), torch.relu(rn(T, KVH, D)), rn(T, KVH, D)
+    gg = (torch.nn.functional.logsigmoid(torch.randn(T, KVH, D, device=device)) / 16).bfloat16()
+    out, gout = torch.empty(T, H, D, dtype=torch.bfloat16, device=device), torch.empty(T, H, D, dtype=torch.bfloat16, device=device)
+    n_new = torch.full((S,), chunk, dtype=torch.int32, device=device)
+    scan_ws = ops.gla_scan_workspace(S, chunk, H, D, device)
+    gla_status = torch.zeros(1, dtype=torch.int32, device=device)
+    pin = lambda t: t.cpu().pin_memory()
+    host_in = [pin(t) for t in (q, k, v, gq, gk, gv, gg)]
+    host_out = torch.empty(out.shape, dtype=out.dtype).pin_memory()
+    h2d = d2h = 0
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    def prefill_chunk(pos, e2e, trim=True):
+        nonlocal h2d, d2h
+        plan.plan(n_new)
+        meta = MetaAttentionMetadata(
+            num_prefills=S, num_prefill_tokens=T, num_decode_tokens=0, slot_mapping=plan.slot_mapping,
+            seq_lens=[pos + chunk] * S, seq_lens_tensor=plan.seq_lens, max_prefill_seq_len=pos + chunk,
+            max_decode_seq_len=0, context_lens_tensor=plan.context_lens, block_tables=plan.block_tables,
+            use_cuda_graph=False, max_query_len=chunk, query_start_loc=plan.query_start_loc)
+        for i in range(max(n_swa, n_gla)):
+            if i < n_gla:
+                if e2e:
+                    for dst, src in zip((gq, gk, gv, gg), host_in[3:]):
+                        dst.copy_(src, non_blocking=True); h2d += src.numel() * 2
+                gla_prefill_scan(gq, gk, gv, gg, gla.cache[i], slot_idx, plan.query_start_loc, plan.context_lens,
+                                 status=gla_status, max_query_len=chunk, workspace=scan_ws, out=gout)
+                if e2e:
+                    host_out.copy_(gout, non_blocking=True); d2h += gout.numel() * 2
+            if i < n_swa:
+                if e2e:
+                    for dst, src in zip((q, k, v), host_in[:3]):
+                        dst.copy_(src, non_blocking=True); h2d += src.numel() * 2
+                impls[i].forward(None, q, k, v, None, None, None, kv[i], meta, output=out)
+                if e2e:
+                    host_out.copy_(out, non_blocking=True); d2h += out.numel() * 2
+        if trim:
+            plan.trim()  # the chunk's look-back window goes back to the ring at once
+
+    def reset_state():
+        ops.pool_init(plan.ring, plan.ctrl, plan.seq_lens, plan.block_tables)
+        gla.cache.zero_()
+
+    def prefill(e2e, trim_last=True):
+        barrier()
+        e0 = torch.cuda.Event(enable_timing=True); e1 = torch.cuda.Event(enable_timing=True)
+        t0 = time.perf_counter()
+        e0.record()
+        n_chunks = prompt // chunk
+        for c in range(n_chunks):
+            prefill_chunk(c * chunk, e2e, trim=trim_last or c + 1 < n_chunks)
+        e1.record()
+        torch.cuda.synchronize()
+        ms = max(e0.elapsed_time(e1), (time.perf_counter() - t0) * 1e3 if e2e else 0.0)
+        return max_over_ranks(ms, device)
+
+    # decode step: the same tensors' first S rows are the step's one token per sequence
+    q1, k1, v1 = q[:S].contiguous(), k[:S].contiguous(), v[:S].contiguous()
+    g1 = [t[:S].reshape(S, t.shape[1], 1, D).contiguous() for t in (gq, gk, gv, gg)]
+    out1, gout1 = torch.empty(S, H, D, dtype=torch.bfloat16, device=device), torch.empty(S, H, D, dtype=torch.bfloat16, device=device)
+    h1 = [pin(t) for t in (q1, k1, v1, *g1)]
+    h_out1 = torch.empty(out1.shape, dtype=out1.dtype).pin_memory()
+
+    def enqueue_decode(e2e):
+        nonlocal h2d, d2h
+        plan.plan()
+        meta = MetaAttentionMetadata(
+            num_prefills=0, num_prefill_tokens=0, num_decode_tokens=S, slot_mapping=plan.slot_mapping[:S], seq_lens=None,
+            seq_lens_tensor=plan.seq_lens, max_prefill_seq_len=0, max_decode_seq_len=prompt + dsteps,
+            context_lens_tensor=None, block_tables=plan.block_tables, use_cuda_graph=False, max_query_len=1,
+            max_decode_query_len=1)
+        for i in range(max(n_swa, n_gla)):
+            if i < n_gla:
+                if e2e:
+                    for dst, src in zip(g1, h1[3:]):
+                        dst.copy_(src, non_blocking=True); h2d += src.numel() * 2
+                my_fused_recurrent_gla(*g1, kv_caches=gla.cache[i], slot_idx=slot_idx, out=gout1)
+                if e2e:
+                    h_out1.copy_(gout1, non_blocking=True); d2h += gout1.numel() * 2
+            if i < n_swa:
+                if e2e:
+                    for dst, src in zip((q1, k1, v1), h1[:3]):
+                        dst.copy_(src, non_blocking=True); h2d += src.numel() * 2
+                impls[i].forward(None, q1, k1, v1, None, None, None, kv[i], meta, output=out1)
+                if e2e:
+                    h_out1.copy_(out1, non_blocking=True); d2h += out1.numel() * 2
+
+    def capture_decode(e2e):
+        side = torch.cuda.Stream(device=device)
+        side.wait_stream(torch.cuda.current_stream())
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.stream(side):
+            enqueue_decode(e2e)
+            with torch.cuda.graph(g, stream=side):
+                enqueue_decode(e2e)
+        torch.cuda.current_stream().wait_stream(side)
+        torch.cuda.synchronize()
+        return g
+
+    def decode(graph, n, sync_each):
+        barrier()
+        e0 = torch.cuda.Event(enable_timing=True); e1 = torch.cuda.Event(enable_timing=True)
+        t0 = time.perf_counter()
+        e0.record()
+        for _ in range(n):
+            graph.replay()
+            if sync_each:
+                torch.cuda.current_stream().synchronize()     # the caller holds the step's outputs on the host
+        e1.record()
+        torch.cuda.synchronize()
+        ms = max(e0.elapsed_time(e1), (time.perf_counter() - t0) * 1e3 if sync_each else 0.0)
+        return max_over_ranks(ms, device)
+
+    sampler = ClockSampler(local)
+    # ---- warm-up: two chunks (kernel attributes, tensor maps, allocator), then start over ----
+    for c in range(2):
+        prefill_chunk(c * chunk, False)
+    reset_state()
+    if rank == 0:
+        sampler.start()
+    launches0 = instr.launches
+    prefill_ms = prefill(False, trim_last=False)     # (the last chunk's trim follows the probe below)
+    launches_prefill = instr.launches - launches0 + 1
+    # ---- the last chunk's kernels once more, alone, on the state the prefill left (that chunk's look-back
+    #      window has not been trimmed yet: every block its queries can see is still resident) ----
+    def timed(fn, n=5):
+        fn()
+        torch.cuda.synchronize()
+        e0 = torch.cuda.Event(enable_timing=True); e1 = torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(n):
+            fn()
+        e1.record()
+        torch.cuda.synchronize()
+        return max_over_ranks(e0.elapsed_time(e1) / n, device)
+
+    qsl = (torch.arange(S + 1, dtype=torch.int32, device=device) * chunk)
+    ctx_t = plan.seq_lens - chunk       # as if the last `chunk` tokens of every sequence were this call's
+    probe_status = torch.zeros(1, dtype=torch.int32, device=device)
+    attn_ms = timed(lambda: ops.swa_prefill(q, kv[0][0], kv[0][1], plan.block_tables, qsl, ctx_t.contiguous(), chunk,
+                                            window_left=WINDOW_LEFT, out=out, status=probe_status)) if n_swa else None
+    scan_ms = timed(lambda: ops.gla_scan(gq, gk, gv, gg, gla.cache[0], qsl, slot_idx, out=gout, max_query_len=chunk,
+                                         workspace=scan_ws)) if n_gla else None
+    chain_ms = timed(lambda: ops.gla_scan(gq, gk, gv, gg, gla.cache[0], qsl, slot_idx, out=gout)) if n_gla else None
+    attn_flops = 4.0 * D * H * S * sum(min(prompt - chunk + i, WINDOW_LEFT) + 1 for i in range(chunk))
+
+    plan.trim()
+    snap = plan.snapshot()
+    resident = [sum(1 for e in row if e >= 0) for row in snap["table"]]
+    peak_resident_prefill = (n_blocks - snap["min_free"]) / S
+    g_dec = capture_decode(False)          # (two steps of the 512 go into the warm-up and the capture)
+    launches0 = instr.launches
+    enqueue_decode(False)
+    launches_per_decode_step = instr.launches - launches0
+    for _ in range(max(args.warmup, 3)):
+        g_dec.replay()
+    n_dec = max(1, dsteps - 3 - max(args.warmup, 3))
+    decode_ms = decode(g_dec, n_dec, False)
+    clocks = sampler.stop() if rank == 0 else None
+    snap_d = plan.snapshot()
+    resident_d = max(sum(1 for e in row if e >= 0) for row in snap_d["table"])
+
+    # ---- end to end: the layers' inputs come from pinned host memory and their outputs go back, per layer ----
+    e2e_obj = None
+    if not args.no_e2e:
+        reset_state()
+        h2d = d2h = 0
+        e2e_prefill_ms = prefill(True)
+        g_e2e = capture_decode(True)
+        per_step_in, per_step_out = h2d, d2h
+        h2d = d2h = 0
+        enqueue_decode(True)
+        torch.cuda.synchronize()
+        per_step_in, per_step_out = h2d, d2h
+        e2e_decode_ms = decode(g_e2e, n_dec, True)
+        e2e_obj = {"value": S * world * n_dec / (e2e_decode_ms * 1e-3), "unit": "tokens/s",
+                   "h2d_bytes_per_step": per_step_in, "d2h_bytes_per_step": per_step_out,
+                   "ms_per_step": e2e_decode_ms / n_dec,
+                   "prefill_tokens_per_s": S * world * prompt / (e2e_prefill_ms * 1e-3),
+                   "prefill_h2d_bytes_per_chunk": sum(t.numel() * 2 for t in host_in[3:]) * n_gla + sum(t.numel() * 2 for t in host_in[:3]) * n_swa,
+                   "prefill_d2h_bytes_per_chunk": out.numel() * 2 * (n_gla + n_swa)}
+    status = int(plan.status.item()) | int(gla_status.item()) | int(probe_status.item())
+    for impl in impls:
+        status |= impl.status()
+    if status != 0:
+        raise SystemExit(f"rank {rank}: device status {status}; the run is void")
+    if rank != 0:
+        if world > 1:
+            dist.destroy_process_group()
+        return
+    peaks_path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    tf_peak = float(json.load(open(peaks_path))["bf16_tflops_sustained"]) if os.path.exists(peaks_path) else 1400.0
+    attn_tflops = attn_flops / (attn_ms * 1e-3) / 1e12 if attn_ms else None
+    ms_per_step = decode_ms / n_dec
+    print(json.dumps({
+        "metric": "decode tokens/s and cache HBM GB/s (% of 8 TB/s)", "value": S * world * n_dec / (decode_ms * 1e-3),
+        "unit": "tokens/s", "n_gpus": world, "steps": n_dec, "warmup": max(args.warmup, 3), "ms_per_step": ms_per_step,
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16 K/V, f32 GLA state",
+        "data": "synthetic",
+        "config": {"workload": f"long-context eviction: {S} sequence(s) per GPU, prompt {prompt} in chunks of {chunk} "
+                               f"through the block tables, then {dsteps} decode steps; cache path of {n_swa} sliding-window + "
+                               f"{n_gla} GLA layers, window_left {WINDOW_LEFT}, block {BLOCK}, 28/4 heads, head_dim 128",
+                   "parallelism": f"sequence-sharded x{world}, no collective",
+                   "launch": "prefill: host launches, one planner launch per chunk; decode: CUDA graph replay",
+                   "l2": "decode at one sequence per GPU is launch-bound (its window, 8 MB per layer, fits L2); the prefill "
+                         "kernels are compute-bound"},
+        "prefill_tokens_per_s": S * world * prompt / (prefill_ms * 1e-3), "prefill_ms": prefill_ms,
+        "prefill_ms_per_chunk": prefill_ms / (prompt // chunk),
+        "prefill_attention": {"ms_per_chunk_layer_at_full_window": attn_ms, "useful_tflops": attn_tflops,
+                              "frac_of_bf16_sustained": attn_tflops / tf_peak if attn_tflops else None,
+                              "peak_tflops": tf_peak},
+        "gla_scan": {"ms_per_chunk_layer": scan_ms, "one_chain_per_head_ms": chain_ms,
+                     "form": "chunk-parallel" if scan_ws is not None else "one chain per (sequence, head)"},
+        "resident_blocks_per_seq": {"after_prefill": max(resident), "peak_during_prefill": peak_resident_prefill,
+                                    "after_decode": resident_d, "window_bound": WINDOW_LEFT // BLOCK + 2,
+                                    "whole_history_would_need": (prompt + dsteps) // BLOCK + 1},
+        "e2e": e2e_obj, "gpu_launches": launches_prefill + launches_per_decode_step * n_dec,
+        "clocks": clocks, "device_status": status}))
     if world > 1:
         dist.destroy_process_group()
 
@@ -657,10 +1084,7 @@ def run_reference(args):
         "unit": "tokens/s", "n_gpus": args.gpus, "steps": args.steps, "warmup": max(args.warmup, 1),
         "ms_per_step": step_s * 1e3, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
         "dtype": "bf16 K/V, f32 GLA state", "data": "synthetic",
-        "config": {"workload": f"7B-shaped decode step, cache path of {args.swa_layers} sliding-window + "
-                               f"{args.gla_layers} GLA layers, batch {args.batch} per GPU, ctx {args.ctx}, "
-                               f"window_left {WINDOW_LEFT}, block {BLOCK}, 28/4 heads, head_dim 128",
-                   "parallelism": "host cores of rank 0"},
+        "config": {"workload": workload_name(args), "parallelism": "host cores of rank 0"},
         "cpu_baseline": {"value": value, "unit": "tokens/s", "cores": cores, "kind": "port", "sample": sample},
         "e2e": {"value": value, "unit": "tokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
     }))
@@ -822,5 +1246,7 @@ if __name__ == "__main__":
         run_head_shard(a)
     elif a.impl == "reference":
         run_reference(a)
+    elif a.config == 4:
+        run_longctx(a)
     else:
         run_b200(a)

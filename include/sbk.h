@@ -286,7 +286,10 @@ int sbk_rope_kv_append(void* query, int H, int64_t q_token_stride_bytes, void* k
  * manager behind it - and what MetaAttentionMetadata.advance_step (:338-409) does on the device
  * for multi-step decode. For every row b with n_new[b] > 0 (n_new NULL: one token per row):
  *   - blocks wholly before max(0, seq_lens[b] - window_left) are retired: pushed on the ring,
- *     their table entries set to -1 (retire != 0; window_left -1 retires nothing);
+ *     their table entries set to -1 (retire != 0; window_left -1 retires nothing). retire == 2
+ *     ("trim") also visits the rows WITHOUT new tokens and retires what their next token will not
+ *     see: after a prompt chunk its look-back window (up to a chunk's worth of blocks beyond the
+ *     window) is given back at once instead of at the row's next step;
  *   - missing table entries of the logical blocks the new tokens fall in are filled from the ring
  *     (retirement first, so blocks freed by this step can be reused by it);
  *   - slot_mapping [T] int64 and positions [T] int64 (or NULL) get one entry per new token,

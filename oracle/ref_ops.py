@@ -306,21 +306,24 @@ class StepPlannerRef:
         self.table = [[-1] * max_blocks for _ in range(B)]
         self.min_free = num_blocks
 
-    def plan(self, n_new: Optional[List[int]] = None, T: Optional[int] = None, retire: bool = True):
+    def plan(self, n_new: Optional[List[int]] = None, T: Optional[int] = None, retire: bool = True,
+             trim: bool = False):
+        """``trim``: rows without new tokens give back what their next token will not see."""
         n_new = [1] * self.B if n_new is None else [max(0, int(n)) for n in n_new]
         total = sum(n_new)
         T = total if T is None else T
         pushes, need = [], 0
         for b, n in enumerate(n_new):
-            if n == 0:
+            if n == 0 and not (trim and retire):
                 continue
             L = self.lens[b]
-            lb0, lb1 = L // self.bs, (L + n - 1) // self.bs
-            if lb1 >= self.max_blocks or total > T:
-                return None
-            need += sum(1 for lb in range(lb0, lb1 + 1) if self.table[b][lb] < 0)
+            if n > 0:
+                lb0, lb1 = L // self.bs, (L + n - 1) // self.bs
+                if lb1 >= self.max_blocks or total > T:
+                    return None
+                need += sum(1 for lb in range(lb0, lb1 + 1) if self.table[b][lb] < 0)
             if retire:
-                first_live = first_visible(L + n, n, self.wl) // self.bs
+                first_live = min(first_visible(L + n, n, self.wl) // self.bs, self.max_blocks)
                 j = first_live - 1
                 while j >= 0 and self.table[b][j] >= 0:
                     j -= 1

@@ -280,6 +280,21 @@ class DeviceStepPlanner:
                             ctrl=self.ctrl, positions=self.positions, context_lens=self.context_lens,
                             query_start_loc=self.query_start_loc, status=self.status)
 
+    def trim(self) -> None:
+        """Give back, for every row, the blocks its next token will not see. A planner launch with no
+        new tokens: after a prompt chunk the rows still hold the chunk's look-back window (the first
+        token of the chunk saw window_left tokens behind it); this returns the resident set to the
+        window at once, so the blocks can serve other sequences before the row's next step."""
+        import torch
+        if not hasattr(self, "_zeros"):
+            self._zeros = torch.zeros(self.max_seqs, dtype=torch.int32, device=self.seq_lens.device)
+        self._ops.plan_step(self.seq_lens, self.block_tables, self.slot_mapping,
+                            block_size=self.block_size, num_blocks=self.num_blocks,
+                            window_left=self.window_left, retire=True, trim=True, n_new=self._zeros,
+                            ring=self.ring, ctrl=self.ctrl, positions=self.positions,
+                            context_lens=self.context_lens, query_start_loc=self.query_start_loc,
+                            status=self.status)
+
     def release(self, rows) -> None:
         """rows: device int32 tensor of finished table rows; their blocks return to the ring."""
         self._ops.release_rows(rows, self.seq_lens, self.block_tables, block_size=self.block_size,

@@ -96,18 +96,23 @@ __device__ __forceinline__ RowPlan plan_row(const PlanParams& p, int b) {
   r.first_live = r.lb0 = 0;
   r.lb1 = -1;
   r.overflow = false;
-  if (r.n == 0) return r;
+  // a row without new tokens is left alone, except in trim mode (retire == 2), where it gives up
+  // what its NEXT token will not see: blocks wholly before seq_len - window_left
+  if (r.n == 0 && p.retire != 2) return r;
   const int32_t* row = p.block_tables + (int64_t)b * p.max_blocks;
-  r.lb0 = r.L / p.block_size;
-  r.lb1 = (r.L + r.n - 1) / p.block_size;
-  if (r.lb1 >= p.max_blocks) {
-    r.overflow = true;
-    return r;
+  if (r.n > 0) {
+    r.lb0 = r.L / p.block_size;
+    r.lb1 = (r.L + r.n - 1) / p.block_size;
+    if (r.lb1 >= p.max_blocks) {
+      r.overflow = true;
+      return r;
+    }
+    for (int lb = r.lb0; lb <= r.lb1; ++lb) r.need += row[lb] < 0;
   }
-  for (int lb = r.lb0; lb <= r.lb1; ++lb) r.need += row[lb] < 0;
   if (p.retire) {
     const int t0 = first_visible(r.L + r.n, r.n, p.window_left);
     r.first_live = t0 / p.block_size;   // <= lb0, so never one of the blocks counted above
+    if (r.first_live > p.max_blocks) r.first_live = p.max_blocks;
     for (int j = r.first_live - 1; j >= 0 && row[j] >= 0; --j) ++r.nret;
   }
   return r;
@@ -343,6 +348,10 @@ extern "C" int sbk_plan_step(const int32_t* n_new, int32_t* seq_lens, int32_t* b
     set_error("sbk_plan_step: negative or zero dimension");
     return SBK_E_ARG;
   }
+  if (retire < 0 || retire > 2) {
+    set_error("sbk_plan_step: retire=%d is none of 0 (keep), 1 (retire), 2 (retire and trim idle rows)", retire);
+    return SBK_E_ARG;
+  }
   if (B == 0 && T == 0) return SBK_OK;
   if ((B > 0 && (!seq_lens || !block_tables)) || (T > 0 && !slot_mapping)) {
     set_error("sbk_plan_step: null pointer");
@@ -368,7 +377,7 @@ extern "C" int sbk_plan_step(const int32_t* n_new, int32_t* seq_lens, int32_t* b
   p.B = B;
   p.block_size = block_size;
   p.window_left = window_left;
-  p.retire = retire != 0;
+  p.retire = retire;
   p.ring = ring;
   p.ctrl = reinterpret_cast<unsigned long long*>(ctrl);
   p.num_blocks = num_blocks;

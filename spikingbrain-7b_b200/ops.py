@@ -536,14 +536,15 @@ def pool_init(ring: torch.Tensor, ctrl: torch.Tensor, seq_lens: Optional[torch.T
 
 
 def plan_step(seq_lens: torch.Tensor, block_tables: torch.Tensor, slot_mapping: torch.Tensor, *,
-              block_size: int, num_blocks: int, window_left: int = -1, retire: bool = True,
+              block_size: int, num_blocks: int, window_left: int = -1, retire: bool = True, trim: bool = False,
               n_new: Optional[torch.Tensor] = None, ring: Optional[torch.Tensor] = None,
               ctrl: Optional[torch.Tensor] = None, positions: Optional[torch.Tensor] = None,
               context_lens: Optional[torch.Tensor] = None, query_start_loc: Optional[torch.Tensor] = None,
               status: Optional[torch.Tensor] = None) -> None:
     """One launch that retires out-of-window blocks, allocates the blocks of the new tokens from
     the ring, writes slot_mapping / positions / context_lens / query_start_loc and advances
-    seq_lens, all on device-resident state (see sbk_plan_step in include/sbk.h)."""
+    seq_lens, all on device-resident state (see sbk_plan_step in include/sbk.h). ``trim``: rows
+    without new tokens also give back the blocks their next token will not see."""
     _need_cuda(seq_lens, block_tables, slot_mapping, n_new, ring, ctrl, positions, context_lens,
                query_start_loc, status)
     B, max_blocks = block_tables.shape
@@ -564,7 +565,7 @@ def plan_step(seq_lens: torch.Tensor, block_tables: torch.Tensor, slot_mapping: 
     if n_new is not None and query_start_loc is None:
         raise ValueError("n_new needs a query_start_loc buffer")
     rc = _abi.lib.sbk_plan_step(_ptr(n_new), _ptr(seq_lens), _ptr(block_tables), max_blocks, B, block_size,
-                                window_left, int(retire), _ptr(ring), _ptr(ctrl), num_blocks,
+                                window_left, 2 if (trim and retire) else int(retire), _ptr(ring), _ptr(ctrl), num_blocks,
                                 _ptr(slot_mapping), _ptr(positions), _ptr(context_lens),
                                 _ptr(query_start_loc), T, _ptr(status), _stream())
     _abi.check("sbk_plan_step", rc)

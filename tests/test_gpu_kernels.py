@@ -1047,6 +1047,29 @@ def test_plan_step_churn_with_releases_and_chunked_prompts(ops):
     assert snap["status"] == 0 and snap["steps"] == 60
 
 
+def test_plan_step_trim_gives_back_a_chunks_look_back_window(ops):
+    """After a prompt chunk a row still holds the blocks the chunk's first token looked back on; a
+    trim launch (no new tokens) returns every row to what its next token will see. Device state,
+    ring order included, equals the CPU model after every launch."""
+    B, bs, wl, max_blocks = 3, 16, 63, 64
+    dev, ref = _planner_pair(B * 20, bs, B, max_blocks, wl, T=B * 128)
+    T = B * 128
+    for n_new in ([128, 40, 0], [128, 128, 7], [1, 0, 100]):
+        want = ref.plan(n_new, T=T)
+        assert want is not None
+        dev.plan(torch.tensor(n_new, dtype=torch.int32, device=DEV))
+        assert dev.slot_mapping.tolist() == want["slot_mapping"]
+        _same_state(dev, ref)
+        held = [sum(1 for e in row if e >= 0) for row in ref.table]
+        assert ref.plan([0] * B, T=T, trim=True) is not None
+        dev.trim()
+        snap = _same_state(dev, ref)
+        after = [sum(1 for e in row if e >= 0) for row in snap["table"]]
+        assert all(a <= wl // bs + 2 for a in after), after
+        assert sum(after) <= sum(held)
+    assert snap["status"] == 0
+
+
 def test_release_rows_names_a_row_twice_releases_it_once(ops):
     """A repeated entry in the list of finished rows must not count the row's blocks twice (the ring's
     tail would run ahead of what was pushed and a block would later be handed to two sequences): the

@@ -101,6 +101,115 @@ def test_long_context_chunked_prefill_then_decode_with_eviction(sb):
     assert mgr.pool.num_free + int((mgr.table >= 0).sum()) == nb
 
 
+def test_long_context_at_full_scale_on_the_device_planner(sb):
+    """The long-context configuration at its stated lengths, scaled in layers (one sliding-window and
+    one GLA layer), on the planner that lives on the GPU: a 131072-token prompt in 16 chunks of 8192
+    through MetaAttentionImpl.forward (append + windowed attention over the block tables) and the
+    chunk-parallel GLA scan, then 512 one-token steps. Checked: the resident blocks return to the
+    window after every chunk (trim) and every step, the peak is the window plus the chunk in flight,
+    retired block ids come back, sampled query rows follow the dense-history oracle, and the GLA
+    state after the whole prompt equals a single token-by-token scan on two sampled heads."""
+    from spikingbrain_7b_b200 import ops
+    from spikingbrain_7b_b200.backend import MetaAttentionImpl, MetaAttentionMetadata
+    from spikingbrain_7b_b200.block_pool import DeviceStepPlanner
+    from spikingbrain_7b_b200.gla_slots import GLACacheManager, gla_prefill_scan, my_fused_recurrent_gla
+    from tests.helpers import rel_err
+    prompt, chunk, steps, wl = 131072, 8192, 512, 4096
+    impl = MetaAttentionImpl(H, D, D ** -0.5, KVH, None, wl + 1, "auto")
+    assert impl.sliding_window[0] == wl
+    max_blocks = (prompt + steps) // BS + 2
+    n_blocks = (wl + chunk) // BS + 4 + 16          # the whole history would need 8224 blocks
+    plan = DeviceStepPlanner(n_blocks, BS, wl, 1, max_blocks, DEV, max_tokens=chunk)
+    kv_d = torch.zeros(2, n_blocks, BS, KVH, D, dtype=torch.bfloat16, device=DEV)
+    gla = GLACacheManager(torch.float32, (1, 1, H, D, D), device=DEV)
+    _, slot_idx = gla.current_run_tensors({"r0": [0]})
+    scan_ws = ops.gla_scan_workspace(1, chunk, H, D, DEV)
+    assert scan_ws is not None
+    Ttot = prompt + steps
+    k_hist = torch.empty(Ttot, KVH, D, dtype=torch.bfloat16)
+    v_hist = torch.empty(Ttot, KVH, D, dtype=torch.bfloat16)
+    heads = (2, 25)                                   # GLA heads followed on the CPU (kv heads 0 and 3)
+    g_hist = {h: [torch.empty(prompt, 1, D, dtype=torch.bfloat16) for _ in range(4)] for h in heads}
+    n_new = torch.full((1,), chunk, dtype=torch.int32, device=DEV)
+    gla_status = torch.zeros(1, dtype=torch.int32, device=DEV)
+    seen_blocks, reused, peak = set(), 0, 0
+    mk = lambda n, h, seed: (torch.randn(n, h, D, device=DEV, generator=torch.Generator(DEV).manual_seed(seed)) / math.sqrt(D)).bfloat16()
+
+    def check_rows(out, q_rows, positions):
+        for o, qr, p in zip(out, q_rows, positions):
+            tgt = _dense_ref(qr, k_hist, v_hist, p, wl).bfloat16().float()
+            assert float((o - tgt).abs().max()) <= 2e-2 and mean_rel(o, tgt) <= 1e-3, f"position {p}"
+
+    def account():
+        nonlocal reused, peak
+        row = plan.block_tables[0].tolist()
+        live = {e for e in row if e >= 0}
+        return live
+
+    for c in range(prompt // chunk):                                     # ---- chunked prefill
+        pos = c * chunk
+        q, k, v = mk(chunk, H, 100 + c), mk(chunk, KVH, 200 + c), mk(chunk, KVH, 300 + c)
+        gq, gk, gv = torch.relu(mk(chunk, H, 400 + c)), torch.relu(mk(chunk, KVH, 500 + c)), mk(chunk, KVH, 600 + c)
+        gg = (torch.nn.functional.logsigmoid(math.sqrt(D) * mk(chunk, KVH, 700 + c).float()) / 16).bfloat16()
+        k_hist[pos:pos + chunk], v_hist[pos:pos + chunk] = k.cpu(), v.cpu()
+        for h in heads:
+            for dst, src, hh in zip(g_hist[h], (gq, gk, gv, gg), (h, h // 7, h // 7, h // 7)):
+                dst[pos:pos + chunk] = src[:, hh:hh + 1].cpu()
+        before = account()
+        plan.plan(n_new)
+        live = account()
+        reused += len((live - before) & seen_blocks)
+        seen_blocks |= live
+        peak = max(peak, len(live))
+        md = MetaAttentionMetadata(
+            num_prefills=1, num_prefill_tokens=chunk, num_decode_tokens=0, slot_mapping=plan.slot_mapping,
+            seq_lens=[pos + chunk], seq_lens_tensor=plan.seq_lens, max_prefill_seq_len=pos + chunk, max_decode_seq_len=0,
+            context_lens_tensor=plan.context_lens, block_tables=plan.block_tables, use_cuda_graph=False,
+            max_query_len=chunk, query_start_loc=plan.query_start_loc)
+        out = torch.empty(chunk, H, D, dtype=torch.bfloat16, device=DEV)
+        impl.forward(None, q, k, v, None, None, None, kv_d, md, output=out)
+        gla_prefill_scan(gq, gk, gv, gg, gla.cache[0], slot_idx, plan.query_start_loc, plan.context_lens,
+                         status=gla_status, max_query_len=chunk, workspace=scan_ws)
+        sample = [0, 1, 15, 16, 4095, 4096, 4097, chunk - 1]
+        check_rows(out[sample].float().cpu(), q[sample].cpu(), [pos + i for i in sample])
+        plan.trim()
+        assert len(account()) <= wl // BS + 2, f"chunk {c}: {len(account())} blocks resident after the chunk"
+    assert peak <= (wl + chunk) // BS + 3
+    assert plan.seq_lens.tolist() == [prompt]
+    # the GLA state after 131072 tokens in 16 x 10 sub-chunks against one token-by-token scan
+    state = gla.cache[0][int(slot_idx[0])].cpu()
+    for h in heads:
+        ref_state = torch.zeros(1, 1, D, D)
+        ref_ops.gla_scan_ref(*g_hist[h], ref_state, [0, prompt])
+        assert rel_err(state[h], ref_state[0, 0]) <= 1e-4, f"GLA head {h}"
+
+    gq1 = [t.view(1, t.shape[1], 1, D) for t in (torch.relu(mk(1, H, 800)), torch.relu(mk(1, KVH, 801)), mk(1, KVH, 802))]
+    gg1 = (torch.nn.functional.logsigmoid(torch.randn(1, KVH, 1, D, device=DEV)) / 16).bfloat16()
+    for step in range(steps):                                            # ---- decode
+        pos = prompt + step
+        q, k, v = mk(1, H, 1000 + step), mk(1, KVH, 2000 + step), mk(1, KVH, 3000 + step)
+        k_hist[pos], v_hist[pos] = k[0].cpu(), v[0].cpu()
+        before = account()
+        plan.plan()
+        live = account()
+        reused += len((live - before) & seen_blocks)
+        seen_blocks |= live
+        assert len(live) <= wl // BS + 2
+        md = MetaAttentionMetadata(
+            num_prefills=0, num_prefill_tokens=0, num_decode_tokens=1, slot_mapping=plan.slot_mapping[:1], seq_lens=None,
+            seq_lens_tensor=plan.seq_lens, max_prefill_seq_len=0, max_decode_seq_len=pos + 1, context_lens_tensor=None,
+            block_tables=plan.block_tables, use_cuda_graph=False, max_query_len=1, max_decode_query_len=1)
+        out = torch.empty(1, H, D, dtype=torch.bfloat16, device=DEV)
+        impl.forward(None, q, k, v, None, None, None, kv_d, md, output=out)
+        my_fused_recurrent_gla(*gq1, gg1, kv_caches=gla.cache[0], slot_idx=slot_idx, status=gla_status)
+        if step % 37 == 0 or step == steps - 1:
+            check_rows(out.float().cpu(), q.cpu(), [pos])
+    assert reused > 0, "retired blocks must come back through the ring"
+    assert impl.status() == 0 and plan.status.item() == 0 and gla_status.item() == 0
+    snap = plan.snapshot()
+    assert len(snap["free"]) + sum(1 for e in snap["table"][0] if e >= 0) == n_blocks      # nothing leaked
+
+
 def test_gla_state_carried_across_chunks_equals_single_scan(sb):
     """A prompt pushed through the GLA slot cache in chunks (token steps on the device, new
     slots handed out by the manager) leaves the state a single sequential scan leaves."""

@@ -89,11 +89,12 @@ def test_reference_arm_runs_on_rank_zero_only(monkeypatch, capsys):
 def test_cache_byte_model_matches_the_shapes():
     sys.path.insert(0, ROOT)
     import bench
-    total, swa, gla = bench.cache_bytes_per_step(256, 8193, 14, 14)
+    total, swa, gla = bench.cache_bytes_per_step([8193] * 256, 14, 14)
     assert swa == 256 * (4097 * 2048 + 2048)            # window of K/V read + one token appended
     assert gla == 256 * 2 * 28 * 128 * 128 * 4          # state read + written
     assert total == 14 * (swa + gla) == 43232788480
-    assert bench.cache_bytes_per_step(2, 100, 1, 0)[0] == 2 * (100 * 2048 + 2048)
+    assert bench.cache_bytes_per_step([100, 100], 1, 0)[0] == 2 * (100 * 2048 + 2048)
+    assert bench.cache_bytes_per_step([100, 9000], 1, 0)[1] == (100 + 4097) * 2048 + 2 * 2048      # ragged batch
 
 
 def test_head_shard_rules_follow_the_reference():
