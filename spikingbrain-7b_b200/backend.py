@@ -92,7 +92,10 @@ class MetaAttentionBackend:
 
     @staticmethod
     def get_supported_head_sizes() -> List[int]:
-        return [32, 64, 96, 128, 160, 192, 224, 256]
+        """The reference lists 32 ... 256 in steps of 32 (meta_attention.py:57-59, what flash-attn
+        takes); the kernels here are built for the head size of the 7B model only, and the list says
+        so instead of advertising sizes whose construction would then fail."""
+        return [128]
 
     @staticmethod
     def get_name() -> str:
@@ -426,8 +429,6 @@ class MetaAttentionImpl:
         if self.head_size not in support_head_sizes:
             raise ValueError(f"Head size {head_size} is not supported by MetaAttention. "
                              f"Supported head sizes are {support_head_sizes}.")
-        if self.head_size != 128:
-            raise NotImplementedError("the sliding-window decode kernel is built for head size 128")
         self.attn_type = attn_type
         self._status: Optional[torch.Tensor] = None
         self._workspace: Dict[Any, Optional[torch.Tensor]] = {}

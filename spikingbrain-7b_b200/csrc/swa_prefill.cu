@@ -342,6 +342,7 @@ extern "C" int sbk_swa_prefill(const void* q, int64_t q_tok_stride, const void* 
     set_error("sbk_swa_prefill: grid too large");
     return SBK_E_ARG;
   }
+  const int bq_tc = prefill_tc::queries_per_tile(H / kvh);
   // Two kernels serve this entry point: tcgen05 (tensor memory, 128-key tiles; what `kernel` AUTO
   // picks) and mma.sync (on request, or under AUTO when q / out cannot be moved as 16-byte vectors).
   const bool vec_ok = aligned16(q) && aligned16(out) && q_tok_stride % 8 == 0 && out_tok_stride % 8 == 0;
@@ -369,7 +370,8 @@ extern "C" int sbk_swa_prefill(const void* q, int64_t q_tok_stride, const void* 
     T.q = (const __nv_bfloat16*)q; T.q_tok_stride = q_tok_stride;
     T.block_tables = block_tables; T.max_blocks = max_blocks;
     T.query_start_loc = query_start_loc; T.context_lens = context_lens;
-    T.n_seqs = n_seqs; T.tiles_per_seq = tiles; T.H = H; T.G = H / kvh; T.num_blocks = num_blocks;
+    T.n_seqs = n_seqs; T.bq = bq_tc; T.tiles_per_seq = (max_query_len + bq_tc - 1) / bq_tc; T.H = H; T.G = H / kvh;
+    T.num_blocks = num_blocks;
     T.block_size = block_size; T.window_left = window_left; T.scale_log2 = scale * kLog2e;
     T.out = (__nv_bfloat16*)out; T.out_tok_stride = out_tok_stride; T.status = status;
     T.n_meta_chunks = num_meta / 16;
@@ -448,7 +450,8 @@ extern "C" int sbk_swa_prefill_dense(const void* q, int64_t q_tok_stride, const 
               "multiples of 8 elements (key/value at least kvh*D)");
     return SBK_E_ALIGN;
   }
-  const int tiles = (max_query_len + kBQ - 1) / kBQ;
+  const int bq_tc = prefill_tc::queries_per_tile(H / kvh);
+  const int tiles = (max_query_len + bq_tc - 1) / bq_tc;
   if ((int64_t)n_seqs * tiles > 2147483647LL || kvh > 65535) {
     set_error("sbk_swa_prefill_dense: grid too large");
     return SBK_E_ARG;
@@ -474,7 +477,7 @@ extern "C" int sbk_swa_prefill_dense(const void* q, int64_t q_tok_stride, const 
   T.block_tables = nullptr; T.max_blocks = 0;
   T.query_start_loc = query_start_loc; T.context_lens = nullptr; T.k_start_loc = k_start_loc;
   T.noncausal = causal ? 0 : 1;
-  T.n_seqs = n_seqs; T.tiles_per_seq = tiles; T.H = H; T.G = H / kvh; T.num_blocks = 1;
+  T.n_seqs = n_seqs; T.bq = bq_tc; T.tiles_per_seq = tiles; T.H = H; T.G = H / kvh; T.num_blocks = 1;
   T.block_size = 16; T.window_left = window_left; T.scale_log2 = scale * kLog2e;
   T.out = (__nv_bfloat16*)out; T.out_tok_stride = out_tok_stride; T.status = status;
   T.n_meta_chunks = num_meta / 16;

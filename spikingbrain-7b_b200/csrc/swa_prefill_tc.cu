@@ -2,10 +2,11 @@
 // tensor cores: tcgen05.mma with both GEMMs' accumulators in tensor memory (TMEM), operands staged
 // in shared memory by TMA tensor copies.
 //
-// A CTA owns 16 consecutive query tokens of one sequence and one kv head. The (up to 8) query
-// heads of that kv group times the 16 queries form the 128 rows of an MMA tile
-// (row = head slot * 16 + query; head slots past the group size are zero rows), so one K/V tile in
-// shared memory serves all of them. Keys are taken 128 at a time:
+// A CTA owns 128 / G consecutive query tokens of one sequence and one kv head, G being the query
+// heads per kv head: those queries times the G heads form the 128 rows of an MMA tile
+// (row = query * G + head; 18 queries x 7 heads fill 126 of the 128 rows, where 16 queries x 8 head
+// slots with one slot empty would fill 112), so one K/V tile in shared memory serves all of them.
+// Keys are taken 128 at a time:
 //     S[128 rows, 128 keys]  = Q . K^T      8 x tcgen05.mma (M128 N128 K16), accumulator in TMEM
 //     softmax on S straight from TMEM; P -> bf16 head + bf16 remainder -> shared memory
 //     O_t[128 rows, 128 dims] = P . V       16 x tcgen05.mma, fresh accumulator in TMEM
@@ -35,7 +36,6 @@ namespace prefill_tc {
 
 constexpr int kD = 128;
 constexpr int kChunk = 16;                    // keys per cache-block piece
-constexpr int kBQ = 16;                       // queries per CTA
 constexpr int kTileKeys = 128;                // keys per MMA tile
 constexpr int kTileChunks = kTileKeys / kChunk;
 constexpr int kPanelBytes = 128 * 128;        // [128 rows][128 B]: 64 bf16 of every row
@@ -237,6 +237,7 @@ swa_prefill_tc_kernel(const Params P, const __grid_constant__ CUtensorMap map_k,
   const int hk = blockIdx.y;
   const int qs = P.query_start_loc[s];
   const int n_q = P.query_start_loc[s + 1] - qs;
+  const int kBQ = P.bq;         // queries per CTA
   if (j * kBQ >= n_q) return;   // whole CTA, before anything is allocated
   const int nq_tile = n_q - j * kBQ < kBQ ? n_q - j * kBQ : kBQ;
   const bool dense = P.k_start_loc != nullptr;
@@ -388,8 +389,8 @@ swa_prefill_tc_kernel(const Params P, const __grid_constant__ CUtensorMap map_k,
     const int r = (warp & 3) * 32 + lane;  // row of the MMA tile = TMEM lane
     const int part = warp >> 2;            // which kCols keys of a tile / which kCols dims of the output
     const int panel = (part * kCols) >> 6, ch0 = ((part * kCols) & 63) >> 3;
-    const int slot_h = r >> 4, ql = r & 15;
-    const bool row_ok = slot_h < G && ql < nq_tile;
+    const int ql = r / G, slot_h = r - ql * G;   // rows past bq * G land on ql == bq: never a query of the tile
+    const bool row_ok = ql < nq_tile;
     const int p_row = full_attn ? p0 : p0 + ql;   // position of this row's query (its last visible key)
     const int lo_row = (P.window_left < 0 || full_attn) ? 0 : (p_row - P.window_left > 0 ? p_row - P.window_left : 0);
     // ---- Q rows into the swizzled K-major panels (this thread: its kCols dims) ----

@@ -12,6 +12,7 @@ struct Params {
   const int32_t* block_tables; int max_blocks;
   const int32_t* query_start_loc; const int32_t* context_lens;
   int n_seqs; int tiles_per_seq; int H; int G; int64_t num_blocks; int block_size;
+  int bq;              // query tokens per CTA: 128 / G (the 128 rows of a tile are bq queries x G heads)
   int window_left; float scale_log2;
   __nv_bfloat16* out; int64_t out_tok_stride;
   int32_t* status; int tile_copy;
@@ -23,6 +24,7 @@ struct Params {
 };
 
 // Tensor maps with ONE 128-byte row (64 dims of one kv head) per copy: box_rows == 1.
+inline int queries_per_tile(int G) { return 128 / G; }
 int launch(const Params& P, int kvh, const CUtensorMap& map_k, const CUtensorMap& map_v,
            const CUtensorMap& map_k2, const CUtensorMap& map_v2, cudaStream_t stream);
 

@@ -191,7 +191,7 @@ def test_backend_static_surface():
                                                MetaAttentionMetadataBuilder)
     assert MetaAttentionBackend.get_name() == "META_FLASH_ATTN"
     assert MetaAttentionBackend.accept_output_buffer is True
-    assert MetaAttentionBackend.get_supported_head_sizes() == [32, 64, 96, 128, 160, 192, 224, 256]
+    assert MetaAttentionBackend.get_supported_head_sizes() == [128]      # what the kernels are built for
     assert MetaAttentionBackend.get_kv_cache_shape(10, 16, 4, 128) == (2, 10, 16, 4, 128)
     with pytest.raises(ValueError):
         MetaAttentionBackend.get_kv_cache_shape(10, 8, 4, 128)
