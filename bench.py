@@ -235,9 +235,7 @@ class Instrument:
             "swa_decode": lambda a, kw: -(-a[0].shape[0] // 1024), "gla_step": lambda a, kw: 1,
             "swa_prefill": lambda a, kw: 1, "swa_prefill_dense": lambda a, kw: 1, "plan_step": lambda a, kw: 1,
             "release_rows": lambda a, kw: 1,
-            # chunk-parallel form: local scan + carry + scan proper
-            "gla_scan": lambda a, kw: 3 if kw.get("workspace") is not None and abi.lib.sbk_gla_scan_workspace_bytes(
-                a[5].numel() - 1, int(kw.get("max_query_len", 0)), a[0].shape[1], a[0].shape[2]) else 1,
+            "gla_scan": self._scan_launches,
         }
         for name, n_of in count.items():
             inner = getattr(ops, name)
@@ -258,6 +256,20 @@ class Instrument:
                 return out
 
             setattr(ops, name, wrapped)
+
+    def _scan_launches(self, a, kw):
+        """Kernels one gla_scan call launches: one chain per (sequence, head); the tensor-core form plus the
+        token-by-token kernel that finishes what it left; or local scans + carry + scan proper."""
+        import torch
+        from spikingbrain_7b_b200 import _abi
+        mql = int(kw.get("max_query_len", 0))
+        if kw.get("workspace") is None or mql <= 0:
+            return 1
+        n_seqs, H, D = a[5].numel() - 1, a[0].shape[1], a[0].shape[2]
+        hand_over = (n_seqs * H * 4 + 255) // 256 * 256 if mql >= 256 else 0
+        if hand_over and a[0].dtype == torch.bfloat16 and D == 128:
+            return 2
+        return 3 if _abi.lib.sbk_gla_scan_workspace_bytes(n_seqs, mql, H, D) > hand_over else 1
 
     @classmethod
     def install(cls):
@@ -723,6 +735,24 @@ def run_b200(args):
                    "h2d_bytes_per_step": eng.h2d_bytes // args.steps,
                    "d2h_bytes_per_step": eng.d2h_bytes // args.steps, "ms_per_step": e2e_ms}
 
+    # ---- the decode kernel alone: back-to-back launches over two copies of one layer's pool in turn
+    #      (together larger than L2), no event nodes between graph kernels, nothing else running ----
+    alone_ms = None
+    if eng.n_swa:
+        pools = [eng.kv[0], eng.kv[0].clone()]
+        call = lambda i: eng.impls[0]._decode(eng.q[0], pools[i & 1], eng.table_d, eng.lens_d, WINDOW_LEFT, eng.out)
+        for i in range(4):
+            call(i)
+        barrier()
+        e0 = torch.cuda.Event(enable_timing=True); e1 = torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for i in range(20):
+            call(i)
+        e1.record()
+        torch.cuda.synchronize()
+        alone_ms = max_over_ranks(e0.elapsed_time(e1) / 20, device)
+        del pools
+
     # ---- the same step with the model's dense callers around the path (plain PyTorch) ----
     full_obj = None
     if args.full_step:
@@ -787,6 +817,12 @@ def run_b200(args):
                      "frac_of_8tbs": achieved / NOMINAL_HBM_GBS if achieved else None,
                      "algorithmic_bytes_per_launch": swa_layer_bytes, "avg_launch_ms": swa_avg_ms,
                      "launches_timed": len(swa_ms),
+                     "alone": {"avg_launch_ms": alone_ms,
+                               "achieved": swa_layer_bytes / (alone_ms * 1e-3) / 1e9 if alone_ms else None,
+                               "frac": swa_layer_bytes / (alone_ms * 1e-3) / 1e9 / peak if alone_ms else None,
+                               "how": "20 back-to-back launches over two copies of one layer's pool in turn, nothing "
+                                      "else on the GPU (inside the step a launch shares HBM with the write-back of the "
+                                      "GLA kernel before it, and its timing events are graph nodes of their own)"},
                      "traffic": int(swa_layer_bytes * SWA_TRAFFIC_PER_ALGORITHMIC_BYTE),
                      "traffic_source": "constant from an ncu capture (dram__bytes_read.sum + dram__bytes_write.sum of "
                                        "one launch at this batch and context), scaled by tokens; not measured in this run"},

@@ -26,6 +26,7 @@
 // agree with the one-chain scan to fp32 rounding (a few 1e-7 relative), not bit for bit.
 #include <math.h>
 
+#include "gla_scan_tc.cuh"
 #include "sbk_common.cuh"
 
 namespace sbk {
@@ -95,6 +96,9 @@ enum : int { kScanFull = 0, kScanLocal = 1 };
 // then decay products [n_seqs][n_sub-1][H][D]; n_sub == 1: one chain per (sequence, head), unused.
 struct ScanSplit {
   float* tiles; float* decays; int n_sub; int sub_len;
+  // [n_seqs * H] or NULL: the token each (sequence, head) chain starts from when another kernel has
+  // already taken the run that far (and left the state in the slot); only with n_sub == 1
+  const int32_t* resume;
 };
 
 template <typename T, typename TO, int D, int MODE>
@@ -119,7 +123,11 @@ gla_scan_kernel(const T* __restrict__ q, const T* __restrict__ k, const T* __res
     if (threadIdx.x == 0 && sub == 0 && MODE == kScanFull) raise_status(status, SBK_ST_BAD_SLOT);
     return;
   }
-  const int t0 = sp.n_sub > 1 ? run0 + sub * sp.sub_len : run0;
+  int t0 = sp.n_sub > 1 ? run0 + sub * sp.sub_len : run0;
+  if (sp.resume != nullptr) {
+    const int done = sp.resume[(int64_t)s * H + h];
+    if (done > t0) t0 = done;
+  }
   const int t1 = sp.n_sub > 1 && t0 + sp.sub_len < run1 ? t0 + sp.sub_len : run1;
   if (t0 >= run1) return;                           // the run is shorter than this sub-chunk's start
   const bool last_sub = t1 == run1;
@@ -148,7 +156,7 @@ gla_scan_kernel(const T* __restrict__ q, const T* __restrict__ k, const T* __res
   // incoming state: the slot (or zero on reset) for the head of the run; for a later sub-chunk the
   // carried state the pass before left in the workspace (full scan) or zero (local scan)
   const float4* tile_in = sub == 0 ? tile : reinterpret_cast<const float4*>(sp.tiles + (ws_idx - H) * (int64_t)D * D);
-  const bool from_zero = sub == 0 ? (reset && reset[s]) : MODE == kScanLocal;
+  const bool from_zero = sub == 0 ? (reset && reset[s] && t0 == run0) : MODE == kScanLocal;
   // SP[i][c] = (S[row, col c], S[row + 1, col c]) for row = 2 (r0 + i GROUPS) and the thread's four
   // columns: the two rows of a pair go through one packed FMA, their k (and q) values come as one
   // 64-bit shared-memory load
@@ -391,6 +399,11 @@ gla_scan_carry_kernel(const int32_t* __restrict__ query_start_loc, const int64_t
 // half of the machine's CTA slots (two per SM, 148 SMs) empty, into as many sub-chunks as fill
 // them, none shorter than 256 tokens (a sub-chunk costs a state tile in and out on top of its
 // tokens). Returns n_sub (1: do not cut) and sets *sub_len (a multiple of the staging round).
+static size_t resume_bytes(int n_seqs, int max_query_len, int H) {
+  if (max_query_len < gla_tc::kMinRun) return 0;
+  return ((size_t)n_seqs * H * sizeof(int32_t) + 255) / 256 * 256;
+}
+
 static int scan_split_plan(int n_seqs, int max_query_len, int H, int* sub_len) {
   constexpr int kSlots = 2 * 148;
   *sub_len = max_query_len;
@@ -409,10 +422,13 @@ static int scan_split_plan(int n_seqs, int max_query_len, int H, int* sub_len) {
 }  // namespace sbk
 
 extern "C" size_t sbk_gla_scan_workspace_bytes(int n_seqs, int max_query_len, int H, int D) {
+  if (n_seqs <= 0 || H <= 0 || D <= 0) return 0;
   int sub_len = 0;
   const int n_sub = sbk::scan_split_plan(n_seqs, max_query_len, H, &sub_len);
-  if (n_sub < 2 || D <= 0) return 0;
-  return (size_t)n_seqs * (n_sub - 1) * H * ((size_t)D * D + D) * sizeof(float);
+  // the hand-over positions of the tensor-core form come first, the sub-chunk states after them
+  size_t n = sbk::resume_bytes(n_seqs, max_query_len, H);
+  if (n_sub >= 2) n += (size_t)n_seqs * (n_sub - 1) * H * ((size_t)D * D + D) * sizeof(float);
+  return n;
 }
 
 extern "C" int sbk_gla_scan(const void* q, const void* k, const void* v, const void* g, int in_dtype,
@@ -452,25 +468,41 @@ extern "C" int sbk_gla_scan(const void* q, const void* k, const void* v, const v
   }
   // One chain per (sequence, head), or -- given a workspace and the longest run -- the
   // chunk-parallel form when the chains alone would leave most of the GPU idle.
-  ScanSplit sp{nullptr, nullptr, 1, 0};
+  ScanSplit sp{nullptr, nullptr, 1, 0, nullptr};
+  cudaStream_t st = (cudaStream_t)stream;
   if (workspace != nullptr && max_query_len > 0) {
-    int sub_len = 0;
-    const int n_sub = scan_split_plan(n_seqs, max_query_len, H, &sub_len);
-    if (n_sub > 1) {
-      const size_t need = sbk_gla_scan_workspace_bytes(n_seqs, max_query_len, H, D);
-      if (workspace_bytes < need) {
-        set_error("sbk_gla_scan: workspace of %zu bytes given, %zu needed (sbk_gla_scan_workspace_bytes)",
-                  workspace_bytes, need);
-        return SBK_E_WORKSPACE;
+    const size_t need = sbk_gla_scan_workspace_bytes(n_seqs, max_query_len, H, D);
+    if (workspace_bytes < need) {
+      set_error("sbk_gla_scan: workspace of %zu bytes given, %zu needed (sbk_gla_scan_workspace_bytes)",
+                workspace_bytes, need);
+      return SBK_E_WORKSPACE;
+    }
+    if (need > 0 && !aligned16(workspace)) {
+      set_error("sbk_gla_scan: workspace must be 16-byte aligned");
+      return SBK_E_ALIGN;
+    }
+    const size_t rb = resume_bytes(n_seqs, max_query_len, H);
+    if (rb > 0 && in_dtype == SBK_BF16 && D == 128 && aligned16(q) && aligned16(k) && aligned16(v) && aligned16(g) &&
+        aligned16(out)) {
+      // Long runs of bf16 tokens at head dim 128: the chunked form on the tensor cores takes every run as
+      // far as its gates allow; the token-by-token kernel below finishes what it left (normally nothing).
+      gla_tc::Params T;
+      T.q = (const __nv_bfloat16*)q; T.k = (const __nv_bfloat16*)k; T.v = (const __nv_bfloat16*)v;
+      T.g = (const __nv_bfloat16*)g; T.query_start_loc = query_start_loc; T.state = state; T.num_slots = num_slots;
+      T.slot_idx = slot_idx; T.reset = reset; T.H = H; T.Hkv = Hkv; T.scale = scale; T.out = out;
+      T.out_f32 = out_dtype == SBK_F32; T.status = status; T.fu = fu; T.resume = (int32_t*)workspace;
+      const int rc = gla_tc::launch(T, n_seqs, st);
+      if (rc != SBK_OK) return rc;
+      sp.resume = (const int32_t*)workspace;
+    } else {
+      int sub_len = 0;
+      const int n_sub = scan_split_plan(n_seqs, max_query_len, H, &sub_len);
+      if (n_sub > 1) {
+        sp.tiles = (float*)((uint8_t*)workspace + rb);
+        sp.decays = sp.tiles + (size_t)n_seqs * (n_sub - 1) * H * D * D;
+        sp.n_sub = n_sub;
+        sp.sub_len = sub_len;
       }
-      if (!aligned16(workspace)) {
-        set_error("sbk_gla_scan: workspace must be 16-byte aligned");
-        return SBK_E_ALIGN;
-      }
-      sp.tiles = (float*)workspace;
-      sp.decays = sp.tiles + (size_t)n_seqs * (n_sub - 1) * H * D * D;
-      sp.n_sub = n_sub;
-      sp.sub_len = sub_len;
     }
   }
   if ((int64_t)n_seqs * sp.n_sub > 65535) {
@@ -478,7 +510,6 @@ extern "C" int sbk_gla_scan(const void* q, const void* k, const void* v, const v
     return SBK_E_ARG;
   }
   dim3 grid(H, n_seqs * sp.n_sub);
-  cudaStream_t st = (cudaStream_t)stream;
 #define SBK_SCAN_LAUNCH(T, TO, DD)                                                                      \
   do {                                                                                                  \
     if (sp.n_sub > 1) {                                                                                 \

@@ -695,27 +695,32 @@ def _scan_inputs(T, H, Hkv, D, seed, dtype=torch.bfloat16, strong_decay=False):
     return q, k, v, gk.to(dtype)
 
 
-@pytest.mark.parametrize("runs,H,Hkv,D,carry_in", [([8192], 28, 4, 128, True), ([8192], 28, 4, 128, False),
-                                                   ([3000, 700, 2049], 28, 4, 128, True), ([4096], 8, 2, 64, True),
-                                                   ([1537, 1024], 7, 1, 128, True)])
-def test_gla_scan_chunk_parallel_matches_one_chain_and_oracle(ops, runs, H, Hkv, D, carry_in):
-    """Few long runs: given the longest run and a workspace the scan cuts every run into sub-chunks
-    owned by different CTAs (local scans, carry, scan proper). The recurrence is linear in the
-    state, so the result is the one-chain scan's in another association: outputs and final states
-    within 1e-5 of it (tolerance, not bit equality), and within the 1e-4 bar of the token-by-token
-    oracle on two sampled heads."""
+@pytest.mark.parametrize("runs,H,Hkv,D,carry_in,dtype", [
+    ([8192], 28, 4, 128, True, torch.bfloat16), ([8192], 28, 4, 128, False, torch.bfloat16),
+    ([3000, 700, 2049], 28, 4, 128, True, torch.bfloat16), ([1537, 1024], 7, 1, 128, True, torch.bfloat16),
+    ([130, 4000, 1, 257], 14, 2, 128, True, torch.bfloat16),
+    ([8192], 28, 4, 128, True, torch.float32), ([4096], 8, 2, 64, True, torch.bfloat16),
+    ([2049, 3000], 7, 7, 128, False, torch.float32)])
+def test_gla_scan_long_runs_chunked_forms_match_one_chain_and_oracle(ops, runs, H, Hkv, D, carry_in, dtype):
+    """Long runs: given the longest run and a workspace the scan leaves the one-chain, token-by-token
+    form. bf16 tokens at head dim 128 go through the chunked form on the tensor cores (128-token
+    chunks, split-bf16 operands); other inputs, when the runs are few, are cut into sub-chunks owned by
+    different CTAs (local scans, carry, scan proper). Either way the recurrence is linear in the state
+    and the result is the one-chain scan's in another association: outputs and final states within 1e-5
+    of it (tolerance, not bit equality), and within the 1e-4 bar of the token-by-token oracle on two
+    sampled heads."""
     n_seqs = len(runs)
     qsl = [0]
     for n in runs:
         qsl.append(qsl[-1] + n)
     T = qsl[-1]
-    q, k, v, gk = _scan_inputs(T, H, Hkv, D, seed=35)
+    q, k, v, gk = _scan_inputs(T, H, Hkv, D, seed=35, dtype=dtype)
     g = torch.Generator().manual_seed(36)
     state = torch.randn(n_seqs + 1, H, D, D, generator=g) * 0.1
     slot_idx = torch.arange(n_seqs, 0, -1, dtype=torch.int64)             # slots n_seqs .. 1; slot 0 stays untouched
     reset = [not carry_in] + [False] * (n_seqs - 1)
     ws = ops.gla_scan_workspace(n_seqs, max(runs), H, D, DEV)
-    assert ws is not None, "this shape is meant to be cut"
+    assert ws is not None, "this shape is meant to leave the one-chain form"
     dev = lambda t: t.to(DEV)
     qsl_d = torch.tensor(qsl, dtype=torch.int32, device=DEV)
     reset_d = torch.tensor(reset, device=DEV)
@@ -741,10 +746,41 @@ def test_gla_scan_chunk_parallel_matches_one_chain_and_oracle(ops, runs, H, Hkv,
         assert rel_err(s_par[:, h:h + 1].cpu(), ref_state) <= GLA_REL
 
 
+def test_gla_scan_hand_over_in_the_middle_of_a_run(ops):
+    """Gates that turn strong half way through a run: the tensor-core form takes the chunks whose
+    summed log-decay stays inside its range and stops at the first one that does not; the
+    token-by-token kernel picks the run up at that token with the state the first one left in the
+    slot. The seam must not show."""
+    H, Hkv, D, T = 28, 4, 128, 3000
+    q, k, v, gk = _scan_inputs(T, H, Hkv, D, seed=46)
+    _, _, _, strong = _scan_inputs(T, H, Hkv, D, seed=47, strong_decay=True)
+    gk[1300:2000] = strong[1300:2000]                 # chunks 10..15 of 128 tokens are out of range
+    qsl = [0, T]
+    qsl_d = torch.tensor(qsl, dtype=torch.int32, device=DEV)
+    ws = ops.gla_scan_workspace(1, T, H, D, DEV)
+    dev = lambda t: t.to(DEV)
+    state = torch.randn(1, H, D, D, generator=torch.Generator().manual_seed(48)) * 0.1
+    s_one, s_tc = dev(state), dev(state)
+    st = _status()
+    o_one = ops.gla_scan(dev(q), dev(k), dev(v), dev(gk), s_one, qsl_d, out_dtype=torch.float32, status=st)
+    o_tc = ops.gla_scan(dev(q), dev(k), dev(v), dev(gk), s_tc, qsl_d, out_dtype=torch.float32, max_query_len=T,
+                        workspace=ws, status=st)
+    assert st.item() == 0
+    assert ws[:4 * H].view(torch.int32).tolist() == [1280] * H     # every head stopped ahead of the 11th chunk
+    assert torch.isfinite(o_tc).all()
+    assert rel_err(o_tc, o_one) <= 1e-5 and rel_err(s_tc, s_one) <= 1e-5
+    # bf16 outputs: the same values rounded once
+    s_b = dev(state)
+    o_b = ops.gla_scan(dev(q), dev(k), dev(v), dev(gk), s_b, qsl_d, out_dtype=torch.bfloat16, max_query_len=T, workspace=ws)
+    assert float((o_b.float() - o_one).abs().max()) <= 2.0 ** -8 * float(o_one.abs().max())
+    assert torch.equal(s_b, s_tc)
+
+
 def test_gla_scan_chunk_parallel_strong_decay_and_fused_neighbours(ops):
-    """The chunk-parallel form with gates strong enough that a sub-chunk's decay product underflows
-    to zero (the carried state then contributes nothing, as in the one-chain scan), and with the
-    fused neighbours (ReLU on q/k, gate logits, per-head RMS norm) switched on."""
+    """The chunked forms with gates strong enough that a sub-chunk's decay product underflows to zero
+    (the carried state then contributes nothing, as in the one-chain scan; the tensor-core form hands
+    such runs over whole), and with the fused neighbours (ReLU on q/k, gate logits, per-head RMS norm)
+    switched on."""
     H, Hkv, D, T = 28, 4, 128, 4096
     q, k, v, gk = _scan_inputs(T, H, Hkv, D, seed=37, strong_decay=True)
     qsl_d = torch.tensor([0, T], dtype=torch.int32, device=DEV)

@@ -103,10 +103,12 @@ def test_host_side_argument_errors_need_no_gpu(sb):
     # empty work is a successful no-op
     assert lib.sbk_gla_step(None, None, None, None, 0, None, 0, None, 0, 28, 4, 128, 1.0, None, 0, 0, 0.0, None, 0.0, None, None) == 0
     assert lib.sbk_swa_workspace_bytes(256, 28, 128, 9) >= 256 * 9 * 28 * 130 * 4
-    # the chunk-parallel GLA scan: cut only when the (sequence, head) chains leave the GPU mostly idle
-    assert lib.sbk_gla_scan_workspace_bytes(8, 8192, 28, 128) == 0          # 224 chains: not cut
-    assert lib.sbk_gla_scan_workspace_bytes(1, 256, 28, 128) == 0           # too short to cut
-    assert lib.sbk_gla_scan_workspace_bytes(1, 8192, 28, 128) == 9 * 28 * (128 * 128 + 128) * 4   # 10 sub-chunks
+    # GLA scan scratch: the hand-over positions of the tensor-core form (one int32 per sequence and head,
+    # rounded to 256 bytes, for runs of 256 tokens or more) and, when the (sequence, head) chains would leave
+    # the GPU mostly idle, the sub-chunk states of the chunk-parallel form
+    assert lib.sbk_gla_scan_workspace_bytes(8, 8192, 28, 128) == 1024       # 224 chains: not cut
+    assert lib.sbk_gla_scan_workspace_bytes(1, 255, 28, 128) == 0           # short runs: one chain, token by token
+    assert lib.sbk_gla_scan_workspace_bytes(1, 8192, 28, 128) == 256 + 9 * 28 * (128 * 128 + 128) * 4   # 10 sub-chunks
     rc = lib.sbk_swa_prefill(None, 0, None, None, None, 4, None, None, 1, 16, 28, 4, 128, 8, 16, 0, 63, 1.0, None, 0,
                              None, None, 0, 7, None, None)
     assert rc == _abi.SBK_E_ARG and b"kernel=7" in lib.sbk_last_error()
