@@ -49,6 +49,7 @@ constexpr float kMaxDecay = 80.f;              // |G_C| beyond this: the chunk g
 // scratch that lives in the V operand's bytes while V itself is not there
 constexpr int kPartOff = kV;                   // [32][128] f32: per token group, the sum of its four gates
 constexpr int kXchOff = kV + 16384;            // [4][128] f32: partial sums of squares of the fused norm
+constexpr int kStageOff = kQH;                 // output rows of a chunk on their way out: 128 x (512 + 16) bytes at most
 
 __device__ __forceinline__ void workers_bar() { asm volatile("bar.sync 1, %0;" ::"n"(kWorkers) : "memory"); }
 // the four warps that share the TMEM lanes (rows) 32 q ... 32 q + 31
@@ -57,6 +58,11 @@ __device__ __forceinline__ void row_bar(int q) { asm volatile("bar.sync %0, 128;
 __device__ __forceinline__ float bf_lo(uint32_t w) { return __uint_as_float(w << 16); }
 __device__ __forceinline__ float bf_hi(uint32_t w) { return __uint_as_float(w & 0xffff0000u); }
 
+// FUSED: the element-wise neighbours (ReLU on q/k, gate logits -> log-decay, per-head RMS norm) are
+// compiled in. The plain instantiation has no run-time branches inside its unrolled loops, which
+// lets the compiler keep the global loads of a chunk ahead of their uses (0.76 -> 0.62 ms on one
+// 8192-token run).
+template <bool FUSED>
 __global__ void __launch_bounds__(kThreads, 1) gla_scan_tc_kernel(const Params P) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* const smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
@@ -223,28 +229,48 @@ __global__ void __launch_bounds__(kThreads, 1) gla_scan_tc_kernel(const Params P
       const uint32_t ph = c & 1;
       const int tb = run0 + c * kC;
       const int nt = run1 - tb < kC ? run1 - tb : kC;
+      bulk_wait_read<0>();   // (the threads that sent the previous chunk's rows off: the staging bytes are free)
       // ============ prepare: cumulative gates, Qs / Ks split, V ============
       float cum[4][8];
       {
         float run[8];
 #pragma unroll
         for (int j = 0; j < 8; ++j) run[j] = 0.f;
+        // (all four loads are issued before the first is used: one trip to L2, not four)
+        uint4 gw4[4];
 #pragma unroll
         for (int i = 0; i < 4; ++i) {
           const int tl = tg * 4 + i;
-          uint4 gw = make_uint4(0, 0, 0, 0);
-          if (tl < nt) gw = *reinterpret_cast<const uint4*>(P.g + ((int64_t)(tb + tl) * P.Hkv + hk) * kD + d0);
-          const uint32_t w[4] = {gw.x, gw.y, gw.z, gw.w};
+          const int tc = tl < nt ? tl : 0;   // a row that exists; its value is dropped below
+          gw4[i] = *reinterpret_cast<const uint4*>(P.g + ((int64_t)(tb + tc) * P.Hkv + hk) * kD + d0);
+        }
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          const int tl = tg * 4 + i;
+          const uint32_t w[4] = {gw4[i].x, gw4[i].y, gw4[i].z, gw4[i].w};
 #pragma unroll
           for (int e = 0; e < 4; ++e) {
-            const float g0 = tl < nt ? gla_gate<__nv_bfloat16>(bf_lo(w[e]), P.fu) : 0.f;
-            const float g1 = tl < nt ? gla_gate<__nv_bfloat16>(bf_hi(w[e]), P.fu) : 0.f;
+            const float g0 = tl < nt ? (FUSED ? gla_gate<__nv_bfloat16>(bf_lo(w[e]), P.fu) : bf_lo(w[e])) : 0.f;
+            const float g1 = tl < nt ? (FUSED ? gla_gate<__nv_bfloat16>(bf_hi(w[e]), P.fu) : bf_hi(w[e])) : 0.f;
             run[2 * e] += g0; run[2 * e + 1] += g1;
             cum[i][2 * e] = run[2 * e]; cum[i][2 * e + 1] = run[2 * e + 1];
           }
         }
         *reinterpret_cast<float4*>(part_s + tg * kD + d0) = make_float4(run[0], run[1], run[2], run[3]);
         *reinterpret_cast<float4*>(part_s + tg * kD + d0 + 4) = make_float4(run[4], run[5], run[6], run[7]);
+      }
+      // the next chunk's rows on their way into L2 meanwhile (its loads then meet L2, not HBM, latency):
+      // one request per 128-byte line
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        const int tn = tb + kC + tg * 4 + i;
+        if (tn < run1 && (dg & 7) == 0) {
+          const int64_t kv_n = ((int64_t)tn * P.Hkv + hk) * kD + d0;
+          asm volatile("prefetch.global.L2 [%0];" ::"l"(P.g + kv_n));
+          asm volatile("prefetch.global.L2 [%0];" ::"l"(P.k + kv_n));
+          asm volatile("prefetch.global.L2 [%0];" ::"l"(P.v + kv_n));
+          asm volatile("prefetch.global.L2 [%0];" ::"l"(P.q + ((int64_t)tn * P.H + h) * kD + d0));
+        }
       }
       workers_bar();
       if (tid < kD) {   // one thread per key dim: exclusive prefix over the 32 token groups
@@ -270,22 +296,31 @@ __global__ void __launch_bounds__(kThreads, 1) gla_scan_tc_kernel(const Params P
       workers_bar();   // the scratch is read; V may land on it (and flags[2] is read by everyone)
       if (stop) break;
 #pragma unroll
-      for (int i = 0; i < 4; ++i) {
+      for (int i2 = 0; i2 < 4; i2 += 2) {
+      // (two tokens' loads are issued together: two trips to L2 per chunk instead of four)
+      uint4 qw2[2], kw2[2], vw2[2];
+#pragma unroll
+      for (int u = 0; u < 2; ++u) {
+        const int tl = tg * 4 + i2 + u;
+        const int tc = tl < nt ? tl : 0;
+        const int64_t kv_off = ((int64_t)(tb + tc) * P.Hkv + hk) * kD + d0;
+        qw2[u] = *reinterpret_cast<const uint4*>(P.q + ((int64_t)(tb + tc) * P.H + h) * kD + d0);
+        kw2[u] = *reinterpret_cast<const uint4*>(P.k + kv_off);
+        vw2[u] = *reinterpret_cast<const uint4*>(P.v + kv_off);
+      }
+#pragma unroll
+      for (int u = 0; u < 2; ++u) {
+        const int i = i2 + u;
         const int tl = tg * 4 + i;
-        uint4 qw = make_uint4(0, 0, 0, 0), kw = qw, vw = qw;
-        if (tl < nt) {
-          const int64_t kv_off = ((int64_t)(tb + tl) * P.Hkv + hk) * kD + d0;
-          qw = *reinterpret_cast<const uint4*>(P.q + ((int64_t)(tb + tl) * P.H + h) * kD + d0);
-          kw = *reinterpret_cast<const uint4*>(P.k + kv_off);
-          vw = *reinterpret_cast<const uint4*>(P.v + kv_off);
-        }
+        uint4 qw = qw2[u], kw = kw2[u], vw = vw2[u];
+        if (tl >= nt) qw = kw = vw = make_uint4(0, 0, 0, 0);
         const uint32_t qx[4] = {qw.x, qw.y, qw.z, qw.w}, kx[4] = {kw.x, kw.y, kw.z, kw.w};
         uint32_t qh[4], ql[4], kh[4], kl[4];
 #pragma unroll
         for (int e = 0; e < 4; ++e) {
           const float G0 = (base[2 * e] + cum[i][2 * e]) * kLog2e, G1 = (base[2 * e + 1] + cum[i][2 * e + 1]) * kLog2e;
           float q0 = bf_lo(qx[e]), q1 = bf_hi(qx[e]), k0 = bf_lo(kx[e]), k1 = bf_hi(kx[e]);
-          if (P.fu.relu_qk) { q0 = fmaxf(q0, 0.f); q1 = fmaxf(q1, 0.f); k0 = fmaxf(k0, 0.f); k1 = fmaxf(k1, 0.f); }
+          if (FUSED && P.fu.relu_qk) { q0 = fmaxf(q0, 0.f); q1 = fmaxf(q1, 0.f); k0 = fmaxf(k0, 0.f); k1 = fmaxf(k1, 0.f); }
           split_bf16x2(q0 * P.scale * fast_exp2(G0), q1 * P.scale * fast_exp2(G1), qh[e], ql[e]);
           split_bf16x2(k0 * fast_exp2(-G0), k1 * fast_exp2(-G1), kh[e], kl[e]);
         }
@@ -295,6 +330,7 @@ __global__ void __launch_bounds__(kThreads, 1) gla_scan_tc_kernel(const Params P
         *reinterpret_cast<uint4*>(smem + kKH + o) = make_uint4(kh[0], kh[1], kh[2], kh[3]);
         *reinterpret_cast<uint4*>(smem + kKL + o) = make_uint4(kl[0], kl[1], kl[2], kl[3]);
         *reinterpret_cast<uint4*>(smem + kV + o) = vw;
+      }
       }
       fence_proxy_async_smem();   // these generic writes (and the state operands) precede the MMAs' reads
       tc_fence_before();
@@ -350,7 +386,7 @@ __global__ void __launch_bounds__(kThreads, 1) gla_scan_tc_kernel(const Params P
         tmem_ld32_issue(t_lane + kOCol + part * 32, orr);
         tmem_ld_fence(orr);
         float rs = 1.f;
-        if (P.fu.norm_weight != nullptr) {   // the layer's per-head RMS norm on the fp32 read-out
+        if (FUSED && P.fu.norm_weight != nullptr) {   // the layer's per-head RMS norm on the fp32 read-out
           float sq = 0.f;
 #pragma unroll
           for (int i = 0; i < 32; ++i) sq = fmaf(__uint_as_float(orr[i]), __uint_as_float(orr[i]), sq);
@@ -363,30 +399,43 @@ __global__ void __launch_bounds__(kThreads, 1) gla_scan_tc_kernel(const Params P
           for (int i = 0; i < 32; ++i)
             orr[i] = __float_as_uint(__uint_as_float(orr[i]) * rs * __bfloat162float(w[i]));
         }
-        if (r < nt) {
-          const int64_t o_off = ((int64_t)(tb + r) * P.H + h) * kD + part * 32;
-          if (P.out_f32) {
-            float4* op = reinterpret_cast<float4*>(reinterpret_cast<float*>(P.out) + o_off);
+        // A thread holds 64 (or 128) bytes of a token's row, and the 32 lanes of a warp hold 32 different
+        // rows: stored from here they would be 32 separate sectors per instruction, and the loads of the
+        // next chunk would queue behind them. The rows are put together in shared memory (in the
+        // operands' bytes, free now: every MMA of the chunk is done; rows 16 bytes apart from a multiple
+        // of 128, so the lanes do not collide) and leave as one bulk copy per row.
+        const int row_bytes = P.out_f32 ? kD * 4 : kD * 2;
+        uint8_t* const srow = smem + kStageOff + r * (row_bytes + 16);
+        if (P.out_f32) {
+          float4* op = reinterpret_cast<float4*>(srow + part * 128);
 #pragma unroll
-            for (int c4 = 0; c4 < 8; ++c4)
-              op[c4] = make_float4(__uint_as_float(orr[4 * c4]), __uint_as_float(orr[4 * c4 + 1]),
-                                   __uint_as_float(orr[4 * c4 + 2]), __uint_as_float(orr[4 * c4 + 3]));
-          } else {
-            uint4* op = reinterpret_cast<uint4*>(reinterpret_cast<__nv_bfloat16*>(P.out) + o_off);
+          for (int c4 = 0; c4 < 8; ++c4)
+            op[c4] = make_float4(__uint_as_float(orr[4 * c4]), __uint_as_float(orr[4 * c4 + 1]),
+                                 __uint_as_float(orr[4 * c4 + 2]), __uint_as_float(orr[4 * c4 + 3]));
+        } else {
+          uint4* op = reinterpret_cast<uint4*>(srow + part * 64);
 #pragma unroll
-            for (int c4 = 0; c4 < 4; ++c4) {
-              uint4 w4;
-              w4.x = pack_bf16x2(__uint_as_float(orr[8 * c4]), __uint_as_float(orr[8 * c4 + 1]));
-              w4.y = pack_bf16x2(__uint_as_float(orr[8 * c4 + 2]), __uint_as_float(orr[8 * c4 + 3]));
-              w4.z = pack_bf16x2(__uint_as_float(orr[8 * c4 + 4]), __uint_as_float(orr[8 * c4 + 5]));
-              w4.w = pack_bf16x2(__uint_as_float(orr[8 * c4 + 6]), __uint_as_float(orr[8 * c4 + 7]));
-              op[c4] = w4;
-            }
+          for (int c4 = 0; c4 < 4; ++c4) {
+            uint4 w4;
+            w4.x = pack_bf16x2(__uint_as_float(orr[8 * c4]), __uint_as_float(orr[8 * c4 + 1]));
+            w4.y = pack_bf16x2(__uint_as_float(orr[8 * c4 + 2]), __uint_as_float(orr[8 * c4 + 3]));
+            w4.z = pack_bf16x2(__uint_as_float(orr[8 * c4 + 4]), __uint_as_float(orr[8 * c4 + 5]));
+            w4.w = pack_bf16x2(__uint_as_float(orr[8 * c4 + 6]), __uint_as_float(orr[8 * c4 + 7]));
+            op[c4] = w4;
           }
         }
+        fence_proxy_async_smem();
+        workers_bar();
+        if (part == 0 && r < nt) {
+          uint8_t* dst = reinterpret_cast<uint8_t*>(P.out) + (((int64_t)(tb + r) * P.H + h) * kD) * (P.out_f32 ? 4 : 2);
+          bulk_s2g(dst, smem_u32(srow), (uint32_t)row_bytes);
+          bulk_commit();
+        }
       }
-      // (the next chunk's first barrier orders these reads of the exchange buffer before its scratch writes)
+      // (the next chunk's first barrier orders the reads of the exchange buffer before its scratch
+      // writes; the copies out of the staging rows are waited for at the top of the loop)
     }
+    bulk_wait_all<0>();   // the last rows have left shared memory and are written
     if (!ok) {
       if (lane == 0 && !flags[0]) { raise_status(P.status, SBK_ST_WAIT_TIMEOUT); flags[0] = 1; }
       if (tid == 0) *my_resume = run1;   // the status word says the result is void; nobody resumes it
@@ -422,7 +471,9 @@ int launch(const Params& P, int n_seqs, cudaStream_t stream) {
   int dev = 0;
   cudaGetDevice(&dev);
   if (dev < 0 || dev >= 64 || !configured[dev]) {
-    cudaError_t e = cudaFuncSetAttribute(gla_scan_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes);
+    cudaError_t e = cudaFuncSetAttribute(gla_scan_tc_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes);
+    if (e == cudaSuccess)
+      e = cudaFuncSetAttribute(gla_scan_tc_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes);
     if (e != cudaSuccess) {
       set_error("sbk_gla_scan: cannot opt in to %d bytes of shared memory: %s", kSmemBytes, cudaGetErrorString(e));
       return SBK_E_LAUNCH;
@@ -430,7 +481,10 @@ int launch(const Params& P, int n_seqs, cudaStream_t stream) {
     if (dev >= 0 && dev < 64) configured[dev] = true;
   }
   dim3 grid(P.H, n_seqs);
-  gla_scan_tc_kernel<<<grid, kThreads, kSmemBytes, stream>>>(P);
+  if (P.fu.relu_qk || P.fu.gate_logits || P.fu.norm_weight != nullptr)
+    gla_scan_tc_kernel<true><<<grid, kThreads, kSmemBytes, stream>>>(P);
+  else
+    gla_scan_tc_kernel<false><<<grid, kThreads, kSmemBytes, stream>>>(P);
   return check_launch("sbk_gla_scan");
 }
 
