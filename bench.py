@@ -266,8 +266,16 @@ class Instrument:
         if kw.get("workspace") is None or mql <= 0:
             return 1
         n_seqs, H, D = a[5].numel() - 1, a[0].shape[1], a[0].shape[2]
-        hand_over = (n_seqs * H * 4 + 255) // 256 * 256 if mql >= 256 else 0
+        hand_over = (2 * n_seqs * H * 4 + 255) // 256 * 256 if mql >= 256 else 0
         if hand_over and a[0].dtype == torch.bfloat16 and D == 128:
+            # tensor-core form + the token-by-token kernel behind it; with few chains: local pass, carry
+            # (three pieces or more) and full pass
+            chains, n_chunks = n_seqs * H, -(-mql // 128)
+            if 2 * chains <= 148 and n_chunks >= 4:
+                per = max(2, -(-n_chunks // (148 // chains)))
+                n_sub = -(-n_chunks // per)
+                if n_sub >= 2:
+                    return 3 + (1 if n_sub > 2 else 0)
             return 2
         return 3 if _abi.lib.sbk_gla_scan_workspace_bytes(n_seqs, mql, H, D) > hand_over else 1
 

@@ -399,9 +399,28 @@ gla_scan_carry_kernel(const int32_t* __restrict__ query_start_loc, const int64_t
 // half of the machine's CTA slots (two per SM, 148 SMs) empty, into as many sub-chunks as fill
 // them, none shorter than 256 tokens (a sub-chunk costs a state tile in and out on top of its
 // tokens). Returns n_sub (1: do not cut) and sets *sub_len (a multiple of the staging round).
+// Head of the workspace for the tensor-core form: per (sequence, head) the hand-over position, then
+// the flag "a piece of this run cannot be taken" of the chunk-parallel use.
 static size_t resume_bytes(int n_seqs, int max_query_len, int H) {
   if (max_query_len < gla_tc::kMinRun) return 0;
-  return ((size_t)n_seqs * H * sizeof(int32_t) + 255) / 256 * 256;
+  return ((size_t)2 * n_seqs * H * sizeof(int32_t) + 255) / 256 * 256;
+}
+
+// How the tensor-core form cuts its runs: one CTA per SM (its operands fill the shared memory), so
+// 148 slots; only when the chains fill at most half of them, and into pieces of at least two chunks.
+static int tc_split_plan(int n_seqs, int max_query_len, int H, int* sub_chunks) {
+  constexpr int kSlots = 148;
+  const int n_chunks = (max_query_len + gla_tc::kChunkTokens - 1) / gla_tc::kChunkTokens;
+  *sub_chunks = n_chunks;
+  const int64_t chains = (int64_t)n_seqs * H;
+  if (chains <= 0 || n_chunks < 4 || 2 * chains > kSlots) return 1;
+  int n_sub = (int)(kSlots / chains);
+  int per = (n_chunks + n_sub - 1) / n_sub;
+  if (per < 2) per = 2;
+  n_sub = (n_chunks + per - 1) / per;
+  if (n_sub < 2) return 1;
+  *sub_chunks = per;
+  return n_sub;
 }
 
 static int scan_split_plan(int n_seqs, int max_query_len, int H, int* sub_len) {
@@ -427,7 +446,10 @@ extern "C" size_t sbk_gla_scan_workspace_bytes(int n_seqs, int max_query_len, in
   const int n_sub = sbk::scan_split_plan(n_seqs, max_query_len, H, &sub_len);
   // the hand-over positions of the tensor-core form come first, the sub-chunk states after them
   size_t n = sbk::resume_bytes(n_seqs, max_query_len, H);
-  if (n_sub >= 2) n += (size_t)n_seqs * (n_sub - 1) * H * ((size_t)D * D + D) * sizeof(float);
+  int per = 0;
+  const int n_sub_tc = n > 0 ? sbk::tc_split_plan(n_seqs, max_query_len, H, &per) : 1;
+  const int most = n_sub > n_sub_tc ? n_sub : n_sub_tc;     // whichever form the call takes
+  if (most >= 2) n += (size_t)n_seqs * (most - 1) * H * ((size_t)D * D + D) * sizeof(float);
   return n;
 }
 
@@ -491,7 +513,29 @@ extern "C" int sbk_gla_scan(const void* q, const void* k, const void* v, const v
       T.g = (const __nv_bfloat16*)g; T.query_start_loc = query_start_loc; T.state = state; T.num_slots = num_slots;
       T.slot_idx = slot_idx; T.reset = reset; T.H = H; T.Hkv = Hkv; T.scale = scale; T.out = out;
       T.out_f32 = out_dtype == SBK_F32; T.status = status; T.fu = fu; T.resume = (int32_t*)workspace;
-      const int rc = gla_tc::launch(T, n_seqs, st);
+      T.tiles = nullptr; T.decays = nullptr; T.n_sub = 1; T.sub_chunks = 0; T.bail = nullptr;
+      int per = 0;
+      const int n_sub_tc = tc_split_plan(n_seqs, max_query_len, H, &per);
+      if (n_sub_tc > 1 && D == 128) {
+        // few long runs: every run in pieces that different CTAs own -- local pass, carry, full pass
+        T.n_sub = n_sub_tc; T.sub_chunks = per;
+        T.bail = T.resume + (size_t)n_seqs * H;
+        T.tiles = (float*)((uint8_t*)workspace + rb);
+        T.decays = T.tiles + (size_t)n_seqs * (n_sub_tc - 1) * H * D * D;
+        if (cudaMemsetAsync(T.bail, 0, (size_t)n_seqs * H * sizeof(int32_t), st) != cudaSuccess) {
+          set_error("sbk_gla_scan: clearing the workspace head failed");
+          return SBK_E_LAUNCH;
+        }
+        int rc = gla_tc::launch(T, n_seqs, true, st);
+        if (rc != SBK_OK) return rc;
+        if (n_sub_tc > 2) {
+          const ScanSplit cs{T.tiles, T.decays, n_sub_tc, per * gla_tc::kChunkTokens, nullptr};
+          gla_scan_carry_kernel<128><<<dim3(H * kCarrySplit, n_seqs), 256, 0, st>>>(query_start_loc, slot_idx, num_slots, H, cs);
+          rc = check_launch("sbk_gla_scan");
+          if (rc != SBK_OK) return rc;
+        }
+      }
+      const int rc = gla_tc::launch(T, n_seqs, false, st);
       if (rc != SBK_OK) return rc;
       sp.resume = (const int32_t*)workspace;
     } else {

@@ -62,27 +62,46 @@ __device__ __forceinline__ float bf_hi(uint32_t w) { return __uint_as_float(w & 
 // compiled in. The plain instantiation has no run-time branches inside its unrolled loops, which
 // lets the compiler keep the global loads of a chunk ahead of their uses (0.76 -> 0.62 ms on one
 // 8192-token run).
-template <bool FUSED>
+// LOCAL: the first pass of the chunk-parallel form: no queries, no read-out (of the five products
+// only S += Ks^T . V), the end state and the product of the decays go to the workspace.
+template <bool FUSED, bool LOCAL>
 __global__ void __launch_bounds__(kThreads, 1) gla_scan_tc_kernel(const Params P) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* const smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
   const uint32_t sbase = smem_u32(smem);
-  const int h = blockIdx.x, s = blockIdx.y;
+  const int h = blockIdx.x;
+  const int s = blockIdx.y / P.n_sub, sub = blockIdx.y - s * P.n_sub;   // sub: this CTA's piece of the run
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int run0 = P.query_start_loc[s], run1 = P.query_start_loc[s + 1];
   const int64_t slot = P.slot_idx ? P.slot_idx[s] : (int64_t)s;
   int32_t* const my_resume = P.resume + (int64_t)s * P.H + h;
   if (slot < 0 || run1 <= run0 || slot >= P.num_slots) {   // whole CTA, before anything is allocated
-    if (tid == 0) {
+    if (tid == 0 && sub == 0 && !LOCAL) {
       *my_resume = run1;
       if (slot >= P.num_slots) raise_status(P.status, SBK_ST_BAD_SLOT);
     }
     return;
   }
-  if (sbase - smem_u32(smem_raw) > 1023u) {   // the launch leaves room for this much padding only
-    if (tid == 0) { raise_status(P.status, SBK_ST_WAIT_TIMEOUT); *my_resume = run1; }
+  const int n_chunks = (run1 - run0 + kC - 1) / kC;                       // of the run
+  const int c_lo = P.n_sub > 1 ? sub * P.sub_chunks : 0;                  // of this CTA: [c_lo, c_hi)
+  const int c_hi = P.n_sub > 1 && c_lo + P.sub_chunks < n_chunks ? c_lo + P.sub_chunks : n_chunks;
+  const bool is_last = c_hi == n_chunks;
+  if (c_lo >= n_chunks) return;          // the run is shorter than this piece's start
+  if (LOCAL && is_last) return;          // nobody needs the local state of a run's last piece
+  int32_t* const my_bail = P.bail ? P.bail + (int64_t)s * P.H + h : nullptr;
+  if (!LOCAL && my_bail != nullptr && *my_bail != 0) {   // the local pass met a chunk it does not take
+    if (is_last && tid == 0) *my_resume = run0;          // the whole run goes to the other kernel
     return;
   }
+  if (sbase - smem_u32(smem_raw) > 1023u) {   // the launch leaves room for this much padding only
+    if (tid == 0) {
+      raise_status(P.status, SBK_ST_WAIT_TIMEOUT);
+      if (is_last && !LOCAL) *my_resume = run1;
+    }
+    return;
+  }
+  // tile of this (sequence, piece, head) in the workspace; the piece before it is H tiles back
+  const int64_t ws_idx = ((int64_t)s * (P.n_sub - 1) + sub) * P.H + h;
   float* const egc = reinterpret_cast<float*>(smem + kMiscOff);                 // exp(G_C) per key dim
   const uint32_t bar_prep = sbase + kMiscOff + 512, bar_a = bar_prep + 8, bar_p = bar_a + 8;
   const uint32_t bar_s = bar_p + 8, bar_o = bar_s + 8;
@@ -106,18 +125,32 @@ __global__ void __launch_bounds__(kThreads, 1) gla_scan_tc_kernel(const Params P
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem = *tmem_slot;
-  const int n_chunks = (run1 - run0 + kC - 1) / kC;
   const int hk = h / (P.H / P.Hkv);
 
   if (warp == kWorkers / 32) {
     // ================================= MMA issuer =================================
     const uint32_t id_kk = instr_desc(0, 0), id_kmn = instr_desc(1, 0), id_mnmn = instr_desc(1, 1);
     bool ok = true;
-    for (int c = 0; ok && c < n_chunks; ++c) {
-      const uint32_t ph = c & 1;
+    for (int c = c_lo; ok && c < c_hi; ++c) {
+      const uint32_t ph = (c - c_lo) & 1;
       ok = mbar_wait_bounded(bar_prep, ph);
       if (!ok || flags[0] || flags[1]) break;
       tc_fence_after();
+      if (LOCAL) {
+        if (lane == 0) {
+#pragma unroll
+          for (int pr = 0; pr < 2; ++pr) {
+            const uint32_t ka = sbase + (pr ? kKL : kKH);
+#pragma unroll
+            for (int k = 0; k < 8; ++k)
+              umma_bf16(tmem + kSCol, smem_desc(ka + k * 2048, kPanelBytes), smem_desc(sbase + kV + k * 2048, kPanelBytes),
+                        id_mnmn, 1);
+          }
+          umma_commit(bar_s);
+        }
+        __syncwarp();
+        continue;
+      }
       if (lane == 0) {
         // A = Qs . Ks^T : both K-major, 8 steps of 16 dims (4 per 64-dim panel)
 #pragma unroll
@@ -196,8 +229,8 @@ __global__ void __launch_bounds__(kThreads, 1) gla_scan_tc_kernel(const Params P
         *reinterpret_cast<uint4*>(smem + kSL + o) = make_uint4(lo[0], lo[1], lo[2], lo[3]);
       }
     };
-    auto store_state_global = [&](const uint32_t (&x)[32]) {
-      float4* dst = reinterpret_cast<float4*>(tile + (int64_t)r * kD + part * 32);
+    auto store_state_global = [&](const uint32_t (&x)[32], float* to) {
+      float4* dst = reinterpret_cast<float4*>(to + (int64_t)r * kD + part * 32);
 #pragma unroll
       for (int c = 0; c < 8; ++c)
         st_stream_f4(dst + c, make_float4(__uint_as_float(x[4 * c]), __uint_as_float(x[4 * c + 1]),
@@ -207,11 +240,15 @@ __global__ void __launch_bounds__(kThreads, 1) gla_scan_tc_kernel(const Params P
     // ---- incoming state: the slot (or zero) -> tensor memory and the split operands ----
     {
       uint32_t sv[32];
-      if (P.reset && P.reset[s]) {
+      // the run's slot (or zero) for its first piece; for a later piece the carried state of the pass
+      // before (full pass) or zero (local pass)
+      const bool from_zero = sub == 0 ? (P.reset && P.reset[s]) : LOCAL;
+      const float* src_tile = sub == 0 ? tile : P.tiles + (ws_idx - P.H) * (int64_t)kD * kD;
+      if (from_zero) {
 #pragma unroll
         for (int i = 0; i < 32; ++i) sv[i] = 0u;
       } else {
-        const float4* src = reinterpret_cast<const float4*>(tile + (int64_t)r * kD + part * 32);
+        const float4* src = reinterpret_cast<const float4*>(src_tile + (int64_t)r * kD + part * 32);
 #pragma unroll
         for (int c = 0; c < 8; ++c) {
           const float4 x = ld_stream_f4(src + c);
@@ -224,9 +261,10 @@ __global__ void __launch_bounds__(kThreads, 1) gla_scan_tc_kernel(const Params P
       tmem_st_wait();
     }
 
-    int c = 0;
-    for (; c < n_chunks; ++c) {
-      const uint32_t ph = c & 1;
+    float g_piece = 0.f;   // local pass, threads < 128: log-decay of key dim `tid` summed over the piece
+    int c = c_lo;
+    for (; c < c_hi; ++c) {
+      const uint32_t ph = (c - c_lo) & 1;
       const int tb = run0 + c * kC;
       const int nt = run1 - tb < kC ? run1 - tb : kC;
       bulk_wait_read<0>();   // (the threads that sent the previous chunk's rows off: the staging bytes are free)
@@ -282,6 +320,7 @@ __global__ void __launch_bounds__(kThreads, 1) gla_scan_tc_kernel(const Params P
           acc += x;
         }
         egc[tid] = fast_exp2(acc * kLog2e);
+        g_piece += acc;
         if (!(acc >= -kMaxDecay && acc <= 0.f)) flags[2] = 1;   // too strong a decay (or not a decay, or NaN)
       }
       workers_bar();
@@ -304,7 +343,8 @@ __global__ void __launch_bounds__(kThreads, 1) gla_scan_tc_kernel(const Params P
         const int tl = tg * 4 + i2 + u;
         const int tc = tl < nt ? tl : 0;
         const int64_t kv_off = ((int64_t)(tb + tc) * P.Hkv + hk) * kD + d0;
-        qw2[u] = *reinterpret_cast<const uint4*>(P.q + ((int64_t)(tb + tc) * P.H + h) * kD + d0);
+        if (!LOCAL) qw2[u] = *reinterpret_cast<const uint4*>(P.q + ((int64_t)(tb + tc) * P.H + h) * kD + d0);
+        else qw2[u] = make_uint4(0, 0, 0, 0);
         kw2[u] = *reinterpret_cast<const uint4*>(P.k + kv_off);
         vw2[u] = *reinterpret_cast<const uint4*>(P.v + kv_off);
       }
@@ -321,12 +361,14 @@ __global__ void __launch_bounds__(kThreads, 1) gla_scan_tc_kernel(const Params P
           const float G0 = (base[2 * e] + cum[i][2 * e]) * kLog2e, G1 = (base[2 * e + 1] + cum[i][2 * e + 1]) * kLog2e;
           float q0 = bf_lo(qx[e]), q1 = bf_hi(qx[e]), k0 = bf_lo(kx[e]), k1 = bf_hi(kx[e]);
           if (FUSED && P.fu.relu_qk) { q0 = fmaxf(q0, 0.f); q1 = fmaxf(q1, 0.f); k0 = fmaxf(k0, 0.f); k1 = fmaxf(k1, 0.f); }
-          split_bf16x2(q0 * P.scale * fast_exp2(G0), q1 * P.scale * fast_exp2(G1), qh[e], ql[e]);
+          if (!LOCAL) split_bf16x2(q0 * P.scale * fast_exp2(G0), q1 * P.scale * fast_exp2(G1), qh[e], ql[e]);
           split_bf16x2(k0 * fast_exp2(-G0), k1 * fast_exp2(-G1), kh[e], kl[e]);
         }
         const uint32_t o = p_off + swz(tl, dg & 7);
-        *reinterpret_cast<uint4*>(smem + kQH + o) = make_uint4(qh[0], qh[1], qh[2], qh[3]);
-        *reinterpret_cast<uint4*>(smem + kQL + o) = make_uint4(ql[0], ql[1], ql[2], ql[3]);
+        if (!LOCAL) {
+          *reinterpret_cast<uint4*>(smem + kQH + o) = make_uint4(qh[0], qh[1], qh[2], qh[3]);
+          *reinterpret_cast<uint4*>(smem + kQL + o) = make_uint4(ql[0], ql[1], ql[2], ql[3]);
+        }
         *reinterpret_cast<uint4*>(smem + kKH + o) = make_uint4(kh[0], kh[1], kh[2], kh[3]);
         *reinterpret_cast<uint4*>(smem + kKL + o) = make_uint4(kl[0], kl[1], kl[2], kl[3]);
         *reinterpret_cast<uint4*>(smem + kV + o) = vw;
@@ -337,6 +379,7 @@ __global__ void __launch_bounds__(kThreads, 1) gla_scan_tc_kernel(const Params P
       mbar_arrive(bar_prep);
 
       // ============ A: keep s <= t, split, back into tensor memory ============
+      if (!LOCAL) {
       ok = mbar_wait_bounded(bar_a, ph);
       if (!ok || flags[0]) break;
       tc_fence_after();
@@ -359,6 +402,7 @@ __global__ void __launch_bounds__(kThreads, 1) gla_scan_tc_kernel(const Params P
       }
       tc_fence_before();
       mbar_arrive(bar_p);
+      }
 
       // ============ state: S_out = diag(exp G_C) (S_in + Ks^T V) ============
       ok = mbar_wait_bounded(bar_s, ph);
@@ -373,11 +417,15 @@ __global__ void __launch_bounds__(kThreads, 1) gla_scan_tc_kernel(const Params P
         for (int i = 0; i < 32; ++i) sr[i] = __float_as_uint(__uint_as_float(sr[i]) * e);
         tmem_st32(t_lane + kSCol + part * 32, sr);
         store_state_split(sr);
-        if (c + 1 == n_chunks) store_state_global(sr);
+        if (c + 1 == c_hi) {   // end of this CTA's piece: the run's slot, or the workspace (local pass)
+          if (LOCAL) store_state_global(sr, P.tiles + ws_idx * (int64_t)kD * kD);
+          else if (is_last) store_state_global(sr, tile);
+        }
         tmem_st_wait();
       }
 
       // ============ outputs of the chunk ============
+      if (LOCAL) continue;
       ok = mbar_wait_bounded(bar_o, ph);
       if (!ok || flags[0]) break;
       tc_fence_after();
@@ -438,21 +486,34 @@ __global__ void __launch_bounds__(kThreads, 1) gla_scan_tc_kernel(const Params P
     bulk_wait_all<0>();   // the last rows have left shared memory and are written
     if (!ok) {
       if (lane == 0 && !flags[0]) { raise_status(P.status, SBK_ST_WAIT_TIMEOUT); flags[0] = 1; }
-      if (tid == 0) *my_resume = run1;   // the status word says the result is void; nobody resumes it
-    } else if (c < n_chunks) {
-      // Stopped ahead of chunk c: hand the run over. The state as of its first token goes back to the
-      // slot (nothing to store if not a single chunk ran: the other kernel starts from the slot or
-      // from zero by itself); the MMA warp is let out of its wait.
-      if (c > 0) {
-        uint32_t sr[32];
-        tmem_ld32_issue(t_lane + kSCol + part * 32, sr);
-        tmem_ld_fence(sr);
-        store_state_global(sr);
+      if (tid == 0 && is_last && !LOCAL) *my_resume = run1;   // the status word says the result is void; nobody resumes it
+    } else if (c < c_hi) {
+      // Stopped ahead of chunk c; the MMA warp is let out of its wait.
+      if (LOCAL) {
+        // a piece of the run cannot be taken: the full pass leaves the whole run to the other kernel
+        if (tid == 0) atomicExch(my_bail, 1);
+      } else if (is_last) {
+        // Hand the rest of the run over. The state as of chunk c's first token goes back to the slot
+        // (nothing to store if the run has not been touched at all: the other kernel then starts from
+        // the slot, or from zero, by itself).
+        if (c > c_lo || sub > 0) {
+          uint32_t sr[32];
+          tmem_ld32_issue(t_lane + kSCol + part * 32, sr);
+          tmem_ld_fence(sr);
+          store_state_global(sr, tile);
+        }
+        if (tid == 0) *my_resume = run0 + c * kC;
+      } else if (tid == 0) {
+        // an inner piece the local pass went through without complaint: cannot happen (same gates,
+        // same arithmetic); if it does, the run's result is void and the status word says so
+        raise_status(P.status, SBK_ST_WAIT_TIMEOUT);
       }
-      if (tid == 0) { *my_resume = run0 + c * kC; flags[1] = 1; }
+      if (tid == 0) flags[1] = 1;
       __threadfence_block();
       mbar_arrive(bar_prep);
-    } else if (tid == 0) {
+    } else if (LOCAL) {
+      if (tid < kD) P.decays[ws_idx * kD + tid] = expf(g_piece);
+    } else if (tid == 0 && is_last) {
       *my_resume = run1;
     }
   }
@@ -466,25 +527,35 @@ __global__ void __launch_bounds__(kThreads, 1) gla_scan_tc_kernel(const Params P
   if (warp == kWorkers / 32) tmem_dealloc(tmem, kTmemCols);
 }
 
-int launch(const Params& P, int n_seqs, cudaStream_t stream) {
+template <bool FUSED, bool LOCAL>
+static cudaError_t opt_in() {
+  return cudaFuncSetAttribute(gla_scan_tc_kernel<FUSED, LOCAL>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes);
+}
+
+int launch(const Params& P, int n_seqs, bool local, cudaStream_t stream) {
   static bool configured[64] = {};
   int dev = 0;
   cudaGetDevice(&dev);
   if (dev < 0 || dev >= 64 || !configured[dev]) {
-    cudaError_t e = cudaFuncSetAttribute(gla_scan_tc_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes);
-    if (e == cudaSuccess)
-      e = cudaFuncSetAttribute(gla_scan_tc_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes);
+    cudaError_t e = opt_in<false, false>();
+    if (e == cudaSuccess) e = opt_in<true, false>();
+    if (e == cudaSuccess) e = opt_in<false, true>();
+    if (e == cudaSuccess) e = opt_in<true, true>();
     if (e != cudaSuccess) {
       set_error("sbk_gla_scan: cannot opt in to %d bytes of shared memory: %s", kSmemBytes, cudaGetErrorString(e));
       return SBK_E_LAUNCH;
     }
     if (dev >= 0 && dev < 64) configured[dev] = true;
   }
-  dim3 grid(P.H, n_seqs);
-  if (P.fu.relu_qk || P.fu.gate_logits || P.fu.norm_weight != nullptr)
-    gla_scan_tc_kernel<true><<<grid, kThreads, kSmemBytes, stream>>>(P);
-  else
-    gla_scan_tc_kernel<false><<<grid, kThreads, kSmemBytes, stream>>>(P);
+  dim3 grid(P.H, n_seqs * P.n_sub);
+  const bool fused = P.fu.relu_qk || P.fu.gate_logits || P.fu.norm_weight != nullptr;
+  if (local) {
+    if (fused) gla_scan_tc_kernel<true, true><<<grid, kThreads, kSmemBytes, stream>>>(P);
+    else gla_scan_tc_kernel<false, true><<<grid, kThreads, kSmemBytes, stream>>>(P);
+  } else {
+    if (fused) gla_scan_tc_kernel<true, false><<<grid, kThreads, kSmemBytes, stream>>>(P);
+    else gla_scan_tc_kernel<false, false><<<grid, kThreads, kSmemBytes, stream>>>(P);
+  }
   return check_launch("sbk_gla_scan");
 }
 

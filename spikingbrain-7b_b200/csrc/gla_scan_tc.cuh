@@ -18,11 +18,20 @@ struct Params {
   // went all the way). A chunk whose decay is too strong for the factored form stops the chain; the
   // token-by-token kernel picks the run up from there.
   int32_t* resume;
+  // Chunk-parallel use (n_sub > 1): a run is cut into n_sub pieces of sub_chunks 128-token chunks that
+  // different CTAs own. The local pass (launch(..., local = true)) scans every piece but a run's last
+  // without read-out, piece 0 from the run's incoming state and the others from zero, and leaves
+  // the end states in `tiles` [n_seqs][n_sub-1][H][D*D] and the products of the decays in `decays`
+  // [n_seqs][n_sub-1][H][D]; after the carry between them the full pass starts every piece from
+  // its true incoming state. `bail` [n_seqs * H], zeroed by the caller: set by the local pass when a
+  // piece met a chunk it does not take; the full pass then leaves the whole run to the other kernel.
+  float* tiles; float* decays; int n_sub; int sub_chunks; int32_t* bail;
 };
 
 constexpr int kMinRun = 256;   // shortest longest-run for which the entry point takes this kernel
+constexpr int kChunkTokens = 128;
 
-int launch(const Params& P, int n_seqs, cudaStream_t stream);
+int launch(const Params& P, int n_seqs, bool local, cudaStream_t stream);
 
 }  // namespace gla_tc
 }  // namespace sbk

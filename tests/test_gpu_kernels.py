@@ -746,32 +746,40 @@ def test_gla_scan_long_runs_chunked_forms_match_one_chain_and_oracle(ops, runs, 
         assert rel_err(s_par[:, h:h + 1].cpu(), ref_state) <= GLA_REL
 
 
-def test_gla_scan_hand_over_in_the_middle_of_a_run(ops):
+@pytest.mark.parametrize("n_seqs", [3, 1])
+def test_gla_scan_hand_over_in_the_middle_of_a_run(ops, n_seqs):
     """Gates that turn strong half way through a run: the tensor-core form takes the chunks whose
     summed log-decay stays inside its range and stops at the first one that does not; the
     token-by-token kernel picks the run up at that token with the state the first one left in the
-    slot. The seam must not show."""
-    H, Hkv, D, T = 28, 4, 128, 3000
+    slot. The seam must not show. With a single sequence the runs are cut into pieces owned by
+    different CTAs, a piece in the middle meets the strong gates, and the whole run is handed over."""
+    H, Hkv, D, T1 = 28, 4, 128, 3000
+    T = n_seqs * T1
     q, k, v, gk = _scan_inputs(T, H, Hkv, D, seed=46)
     _, _, _, strong = _scan_inputs(T, H, Hkv, D, seed=47, strong_decay=True)
-    gk[1300:2000] = strong[1300:2000]                 # chunks 10..15 of 128 tokens are out of range
-    qsl = [0, T]
+    for s in range(n_seqs):
+        gk[s * T1 + 1300:s * T1 + 2000] = strong[s * T1 + 1300:s * T1 + 2000]     # chunks 10..15 are out of range
+    qsl = [s * T1 for s in range(n_seqs + 1)]
     qsl_d = torch.tensor(qsl, dtype=torch.int32, device=DEV)
-    ws = ops.gla_scan_workspace(1, T, H, D, DEV)
+    ws = ops.gla_scan_workspace(n_seqs, T1, H, D, DEV)
     dev = lambda t: t.to(DEV)
-    state = torch.randn(1, H, D, D, generator=torch.Generator().manual_seed(48)) * 0.1
+    state = torch.randn(n_seqs, H, D, D, generator=torch.Generator().manual_seed(48)) * 0.1
     s_one, s_tc = dev(state), dev(state)
     st = _status()
     o_one = ops.gla_scan(dev(q), dev(k), dev(v), dev(gk), s_one, qsl_d, out_dtype=torch.float32, status=st)
-    o_tc = ops.gla_scan(dev(q), dev(k), dev(v), dev(gk), s_tc, qsl_d, out_dtype=torch.float32, max_query_len=T,
+    o_tc = ops.gla_scan(dev(q), dev(k), dev(v), dev(gk), s_tc, qsl_d, out_dtype=torch.float32, max_query_len=T1,
                         workspace=ws, status=st)
     assert st.item() == 0
-    assert ws[:4 * H].view(torch.int32).tolist() == [1280] * H     # every head stopped ahead of the 11th chunk
+    stops = ws[:4 * H * n_seqs].view(torch.int32).view(n_seqs, H).tolist()
+    if n_seqs == 1:
+        assert stops == [[0] * H]                                  # cut into pieces: the run is handed over whole
+    else:
+        assert stops == [[s * T1 + 1280] * H for s in range(n_seqs)]   # every head stopped ahead of its 11th chunk
     assert torch.isfinite(o_tc).all()
     assert rel_err(o_tc, o_one) <= 1e-5 and rel_err(s_tc, s_one) <= 1e-5
     # bf16 outputs: the same values rounded once
     s_b = dev(state)
-    o_b = ops.gla_scan(dev(q), dev(k), dev(v), dev(gk), s_b, qsl_d, out_dtype=torch.bfloat16, max_query_len=T, workspace=ws)
+    o_b = ops.gla_scan(dev(q), dev(k), dev(v), dev(gk), s_b, qsl_d, out_dtype=torch.bfloat16, max_query_len=T1, workspace=ws)
     assert float((o_b.float() - o_one).abs().max()) <= 2.0 ** -8 * float(o_one.abs().max())
     assert torch.equal(s_b, s_tc)
 

@@ -106,7 +106,7 @@ def test_host_side_argument_errors_need_no_gpu(sb):
     # GLA scan scratch: the hand-over positions of the tensor-core form (one int32 per sequence and head,
     # rounded to 256 bytes, for runs of 256 tokens or more) and, when the (sequence, head) chains would leave
     # the GPU mostly idle, the sub-chunk states of the chunk-parallel form
-    assert lib.sbk_gla_scan_workspace_bytes(8, 8192, 28, 128) == 1024       # 224 chains: not cut
+    assert lib.sbk_gla_scan_workspace_bytes(8, 8192, 28, 128) == 1792       # 224 chains: not cut; 2 x 224 int32
     assert lib.sbk_gla_scan_workspace_bytes(1, 255, 28, 128) == 0           # short runs: one chain, token by token
     assert lib.sbk_gla_scan_workspace_bytes(1, 8192, 28, 128) == 256 + 9 * 28 * (128 * 128 + 128) * 4   # 10 sub-chunks
     rc = lib.sbk_swa_prefill(None, 0, None, None, None, 4, None, None, 1, 16, 28, 4, 128, 8, 16, 0, 63, 1.0, None, 0,
