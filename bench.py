@@ -1098,7 +1098,11 @@ def run_longctx(args):
                               "frac_of_bf16_sustained": attn_tflops / tf_peak if attn_tflops else None,
                               "peak_tflops": tf_peak},
         "gla_scan": {"ms_per_chunk_layer": scan_ms, "one_chain_per_head_ms": chain_ms,
-                     "form": "chunk-parallel" if scan_ws is not None else "one chain per (sequence, head)"},
+                     "form": {1: "CUDA cores, one chain per (sequence, head)",
+                              2: "tensor cores (tcgen05), one chain per (sequence, head)",
+                              3: "tensor cores (tcgen05), runs in two pieces: local pass + full pass",
+                              4: "tensor cores (tcgen05), chunk-parallel: local pass, carry, full pass"}[
+                         instr._scan_launches((gq, gk, gv, gg, None, qsl), {"workspace": scan_ws, "max_query_len": chunk})]},
         "resident_blocks_per_seq": {"after_prefill": max(resident), "peak_during_prefill": peak_resident_prefill,
                                     "after_decode": resident_d, "window_bound": WINDOW_LEFT // BLOCK + 2,
                                     "whole_history_would_need": (prompt + dsteps) // BLOCK + 1},
