@@ -58,14 +58,18 @@ __device__ __forceinline__ void row_bar(int q) { asm volatile("bar.sync %0, 128;
 __device__ __forceinline__ float bf_lo(uint32_t w) { return __uint_as_float(w << 16); }
 __device__ __forceinline__ float bf_hi(uint32_t w) { return __uint_as_float(w & 0xffff0000u); }
 
-// FUSED: the element-wise neighbours (ReLU on q/k, gate logits -> log-decay, per-head RMS norm) are
-// compiled in. The plain instantiation has no run-time branches inside its unrolled loops, which
-// lets the compiler keep the global loads of a chunk ahead of their uses (0.76 -> 0.62 ms on one
-// 8192-token run).
+// F: which element-wise neighbours are compiled in -- bit 0 ReLU on q/k, bit 1 gate logits ->
+// log-decay, bit 2 per-head RMS norm; -1: whatever the call's flags say, decided at run time.
+// Instantiated for 0 (plain), 7 (the reference layer's three) and -1 (any other mix): without
+// run-time branches inside its unrolled loops the compiler keeps the global loads of a chunk ahead
+// of their uses (0.76 -> 0.62 ms on one 8192-token run for the plain one).
 // LOCAL: the first pass of the chunk-parallel form: no queries, no read-out (of the five products
 // only S += Ks^T . V), the end state and the product of the decays go to the workspace.
-template <bool FUSED, bool LOCAL>
+template <int F, bool LOCAL>
 __global__ void __launch_bounds__(kThreads, 1) gla_scan_tc_kernel(const Params P) {
+  const bool f_relu = F < 0 ? P.fu.relu_qk != 0 : (F & 1) != 0;
+  const bool f_gate = F < 0 ? P.fu.gate_logits != 0 : (F & 2) != 0;
+  const bool f_norm = F < 0 ? P.fu.norm_weight != nullptr : (F & 4) != 0;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* const smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
   const uint32_t sbase = smem_u32(smem);
@@ -288,8 +292,8 @@ __global__ void __launch_bounds__(kThreads, 1) gla_scan_tc_kernel(const Params P
           const uint32_t w[4] = {gw4[i].x, gw4[i].y, gw4[i].z, gw4[i].w};
 #pragma unroll
           for (int e = 0; e < 4; ++e) {
-            const float g0 = tl < nt ? (FUSED ? gla_gate<__nv_bfloat16>(bf_lo(w[e]), P.fu) : bf_lo(w[e])) : 0.f;
-            const float g1 = tl < nt ? (FUSED ? gla_gate<__nv_bfloat16>(bf_hi(w[e]), P.fu) : bf_hi(w[e])) : 0.f;
+            const float g0 = tl < nt ? (f_gate ? gla_gate_logit<__nv_bfloat16>(bf_lo(w[e]), P.fu.gate_normalizer) : bf_lo(w[e])) : 0.f;
+            const float g1 = tl < nt ? (f_gate ? gla_gate_logit<__nv_bfloat16>(bf_hi(w[e]), P.fu.gate_normalizer) : bf_hi(w[e])) : 0.f;
             run[2 * e] += g0; run[2 * e + 1] += g1;
             cum[i][2 * e] = run[2 * e]; cum[i][2 * e + 1] = run[2 * e + 1];
           }
@@ -297,6 +301,22 @@ __global__ void __launch_bounds__(kThreads, 1) gla_scan_tc_kernel(const Params P
         *reinterpret_cast<float4*>(part_s + tg * kD + d0) = make_float4(run[0], run[1], run[2], run[3]);
         *reinterpret_cast<float4*>(part_s + tg * kD + d0 + 4) = make_float4(run[4], run[5], run[6], run[7]);
       }
+      // q, k, v of this thread's first two tokens are asked for now and arrive under the scan below;
+      // those of the other two when the first two are worked on
+      auto load_pair = [&](int i2, uint4 (&q2)[2], uint4 (&k2)[2], uint4 (&v2)[2]) {
+#pragma unroll
+        for (int u = 0; u < 2; ++u) {
+          const int tl = tg * 4 + i2 + u;
+          const int tc = tl < nt ? tl : 0;   // a row that exists; its values are dropped where they are used
+          const int64_t kv_off = ((int64_t)(tb + tc) * P.Hkv + hk) * kD + d0;
+          if (!LOCAL) q2[u] = *reinterpret_cast<const uint4*>(P.q + ((int64_t)(tb + tc) * P.H + h) * kD + d0);
+          else q2[u] = make_uint4(0, 0, 0, 0);
+          k2[u] = *reinterpret_cast<const uint4*>(P.k + kv_off);
+          v2[u] = *reinterpret_cast<const uint4*>(P.v + kv_off);
+        }
+      };
+      uint4 qa[2], ka[2], va[2];
+      load_pair(0, qa, ka, va);
       // the next chunk's rows on their way into L2 meanwhile (its loads then meet L2, not HBM, latency):
       // one request per 128-byte line
 #pragma unroll
@@ -334,25 +354,15 @@ __global__ void __launch_bounds__(kThreads, 1) gla_scan_tc_kernel(const Params P
       }
       workers_bar();   // the scratch is read; V may land on it (and flags[2] is read by everyone)
       if (stop) break;
+      uint4 qb[2], kb[2], vb[2];
+      load_pair(2, qb, kb, vb);
 #pragma unroll
       for (int i2 = 0; i2 < 4; i2 += 2) {
-      // (two tokens' loads are issued together: two trips to L2 per chunk instead of four)
-      uint4 qw2[2], kw2[2], vw2[2];
-#pragma unroll
-      for (int u = 0; u < 2; ++u) {
-        const int tl = tg * 4 + i2 + u;
-        const int tc = tl < nt ? tl : 0;
-        const int64_t kv_off = ((int64_t)(tb + tc) * P.Hkv + hk) * kD + d0;
-        if (!LOCAL) qw2[u] = *reinterpret_cast<const uint4*>(P.q + ((int64_t)(tb + tc) * P.H + h) * kD + d0);
-        else qw2[u] = make_uint4(0, 0, 0, 0);
-        kw2[u] = *reinterpret_cast<const uint4*>(P.k + kv_off);
-        vw2[u] = *reinterpret_cast<const uint4*>(P.v + kv_off);
-      }
 #pragma unroll
       for (int u = 0; u < 2; ++u) {
         const int i = i2 + u;
         const int tl = tg * 4 + i;
-        uint4 qw = qw2[u], kw = kw2[u], vw = vw2[u];
+        uint4 qw = i2 ? qb[u] : qa[u], kw = i2 ? kb[u] : ka[u], vw = i2 ? vb[u] : va[u];
         if (tl >= nt) qw = kw = vw = make_uint4(0, 0, 0, 0);
         const uint32_t qx[4] = {qw.x, qw.y, qw.z, qw.w}, kx[4] = {kw.x, kw.y, kw.z, kw.w};
         uint32_t qh[4], ql[4], kh[4], kl[4];
@@ -360,7 +370,7 @@ __global__ void __launch_bounds__(kThreads, 1) gla_scan_tc_kernel(const Params P
         for (int e = 0; e < 4; ++e) {
           const float G0 = (base[2 * e] + cum[i][2 * e]) * kLog2e, G1 = (base[2 * e + 1] + cum[i][2 * e + 1]) * kLog2e;
           float q0 = bf_lo(qx[e]), q1 = bf_hi(qx[e]), k0 = bf_lo(kx[e]), k1 = bf_hi(kx[e]);
-          if (FUSED && P.fu.relu_qk) { q0 = fmaxf(q0, 0.f); q1 = fmaxf(q1, 0.f); k0 = fmaxf(k0, 0.f); k1 = fmaxf(k1, 0.f); }
+          if (f_relu) { q0 = fmaxf(q0, 0.f); q1 = fmaxf(q1, 0.f); k0 = fmaxf(k0, 0.f); k1 = fmaxf(k1, 0.f); }
           if (!LOCAL) split_bf16x2(q0 * P.scale * fast_exp2(G0), q1 * P.scale * fast_exp2(G1), qh[e], ql[e]);
           split_bf16x2(k0 * fast_exp2(-G0), k1 * fast_exp2(-G1), kh[e], kl[e]);
         }
@@ -434,7 +444,7 @@ __global__ void __launch_bounds__(kThreads, 1) gla_scan_tc_kernel(const Params P
         tmem_ld32_issue(t_lane + kOCol + part * 32, orr);
         tmem_ld_fence(orr);
         float rs = 1.f;
-        if (FUSED && P.fu.norm_weight != nullptr) {   // the layer's per-head RMS norm on the fp32 read-out
+        if (f_norm) {   // the layer's per-head RMS norm on the fp32 read-out
           float sq = 0.f;
 #pragma unroll
           for (int i = 0; i < 32; ++i) sq = fmaf(__uint_as_float(orr[i]), __uint_as_float(orr[i]), sq);
@@ -527,9 +537,9 @@ __global__ void __launch_bounds__(kThreads, 1) gla_scan_tc_kernel(const Params P
   if (warp == kWorkers / 32) tmem_dealloc(tmem, kTmemCols);
 }
 
-template <bool FUSED, bool LOCAL>
+template <int F, bool LOCAL>
 static cudaError_t opt_in() {
-  return cudaFuncSetAttribute(gla_scan_tc_kernel<FUSED, LOCAL>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes);
+  return cudaFuncSetAttribute(gla_scan_tc_kernel<F, LOCAL>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes);
 }
 
 int launch(const Params& P, int n_seqs, bool local, cudaStream_t stream) {
@@ -537,10 +547,12 @@ int launch(const Params& P, int n_seqs, bool local, cudaStream_t stream) {
   int dev = 0;
   cudaGetDevice(&dev);
   if (dev < 0 || dev >= 64 || !configured[dev]) {
-    cudaError_t e = opt_in<false, false>();
-    if (e == cudaSuccess) e = opt_in<true, false>();
-    if (e == cudaSuccess) e = opt_in<false, true>();
-    if (e == cudaSuccess) e = opt_in<true, true>();
+    cudaError_t e = opt_in<0, false>();
+    if (e == cudaSuccess) e = opt_in<7, false>();
+    if (e == cudaSuccess) e = opt_in<-1, false>();
+    if (e == cudaSuccess) e = opt_in<0, true>();
+    if (e == cudaSuccess) e = opt_in<7, true>();
+    if (e == cudaSuccess) e = opt_in<-1, true>();
     if (e != cudaSuccess) {
       set_error("sbk_gla_scan: cannot opt in to %d bytes of shared memory: %s", kSmemBytes, cudaGetErrorString(e));
       return SBK_E_LAUNCH;
@@ -548,14 +560,16 @@ int launch(const Params& P, int n_seqs, bool local, cudaStream_t stream) {
     if (dev >= 0 && dev < 64) configured[dev] = true;
   }
   dim3 grid(P.H, n_seqs * P.n_sub);
-  const bool fused = P.fu.relu_qk || P.fu.gate_logits || P.fu.norm_weight != nullptr;
-  if (local) {
-    if (fused) gla_scan_tc_kernel<true, true><<<grid, kThreads, kSmemBytes, stream>>>(P);
-    else gla_scan_tc_kernel<false, true><<<grid, kThreads, kSmemBytes, stream>>>(P);
-  } else {
-    if (fused) gla_scan_tc_kernel<true, false><<<grid, kThreads, kSmemBytes, stream>>>(P);
-    else gla_scan_tc_kernel<false, false><<<grid, kThreads, kSmemBytes, stream>>>(P);
-  }
+  const int mix = (P.fu.relu_qk ? 1 : 0) | (P.fu.gate_logits ? 2 : 0) | (P.fu.norm_weight != nullptr ? 4 : 0);
+#define SBK_TC_LAUNCH(FF)                                                                        \
+  do {                                                                                           \
+    if (local) gla_scan_tc_kernel<FF, true><<<grid, kThreads, kSmemBytes, stream>>>(P);          \
+    else gla_scan_tc_kernel<FF, false><<<grid, kThreads, kSmemBytes, stream>>>(P);               \
+  } while (0)
+  if (mix == 0) SBK_TC_LAUNCH(0);
+  else if (mix == 7) SBK_TC_LAUNCH(7);
+  else SBK_TC_LAUNCH(-1);
+#undef SBK_TC_LAUNCH
   return check_launch("sbk_gla_scan");
 }
 

@@ -160,13 +160,16 @@ bool make_gla_fusion(GlaFusion* fu, const char* who, int flags, float gate_norma
 // the input type before the division, which is what the reference's `F.logsigmoid(gk) / 16` on a
 // bf16 tensor produces.
 template <typename T>
-__device__ __forceinline__ float gla_gate(float x, const GlaFusion& fu) {
-  if (!fu.gate_logits) return x;
+__device__ __forceinline__ float gla_gate_logit(float x, float gate_normalizer) {
   float ls = fminf(x, 0.f) - log1pf(expf(-fabsf(x)));
   if (sizeof(T) == 2) ls = __bfloat162float(__float2bfloat16_rn(ls));
-  float gq = ls / fu.gate_normalizer;
+  float gq = ls / gate_normalizer;
   if (sizeof(T) == 2) gq = __bfloat162float(__float2bfloat16_rn(gq));
   return gq;
+}
+template <typename T>
+__device__ __forceinline__ float gla_gate(float x, const GlaFusion& fu) {
+  return fu.gate_logits ? gla_gate_logit<T>(x, fu.gate_normalizer) : x;
 }
 
 // first token a decode query at position seq_len-1 can still see
