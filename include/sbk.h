@@ -435,9 +435,17 @@ int sbk_swa_prefill_dense(const void* q, int64_t q_tok_stride, const void* key, 
  *               states from sub-chunk to sub-chunk, and the scan proper of every sub-chunk from its
  *               true incoming state -- three launches. The sum is the same in another association:
  *               state and outputs agree with the one-chain scan to fp32 rounding, not bit for
- *               bit. workspace NULL or max_query_len <= 0: one chain per (sequence, head), whose
- *               result does not depend on how the tokens were cut into calls. The size query
- *               returns 0 when the call would not be cut (nothing to allocate).
+ *               bit. With bf16 tokens at D = 128, 16-byte aligned q/k/v/g/out and a longest run of
+ *               at least 256 tokens the call takes the chunked form on the tensor cores instead
+ *               (tcgen05, 128-token chunks, every fp32 operand as a bf16 head plus a bf16
+ *               remainder; few long runs are cut into pieces as above): same agreement with the
+ *               one-chain scan (1e-5 of the largest output). A chunk whose summed log-decay leaves
+ *               the range of that form (|sum| > 80 on some key dim) ends it for that (sequence,
+ *               head); the token-by-token kernel finishes the run from there in the same call.
+ *               max_query_len only plans the cut: a run longer than stated is still scanned
+ *               correctly (its last piece takes the rest). workspace NULL or max_query_len <= 0:
+ *               one chain per (sequence, head), whose result does not depend on how the tokens
+ *               were cut into calls. The size query returns 0 when the call needs no scratch.
  */
 size_t sbk_gla_scan_workspace_bytes(int n_seqs, int max_query_len, int H, int D);
 int sbk_gla_scan(const void* q, const void* k, const void* v, const void* g, int in_dtype,

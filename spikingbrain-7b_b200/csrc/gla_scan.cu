@@ -128,7 +128,8 @@ gla_scan_kernel(const T* __restrict__ q, const T* __restrict__ k, const T* __res
     const int done = sp.resume[(int64_t)s * H + h];
     if (done > t0) t0 = done;
   }
-  const int t1 = sp.n_sub > 1 && t0 + sp.sub_len < run1 ? t0 + sp.sub_len : run1;
+  // a run longer than the caller said: its last sub-chunk takes the rest
+  const int t1 = sub + 1 < sp.n_sub && t0 + sp.sub_len < run1 ? t0 + sp.sub_len : run1;
   if (t0 >= run1) return;                           // the run is shorter than this sub-chunk's start
   const bool last_sub = t1 == run1;
   if (MODE == kScanLocal && last_sub) return;       // nobody needs the local state of the last sub-chunk
@@ -376,7 +377,8 @@ gla_scan_carry_kernel(const int32_t* __restrict__ query_start_loc, const int64_t
   const int n_tok = query_start_loc[s + 1] - query_start_loc[s];
   const int64_t slot = slot_idx ? slot_idx[s] : (int64_t)s;
   if (slot < 0 || slot >= num_slots || n_tok <= 0) return;
-  const int n_used = (n_tok + sp.sub_len - 1) / sp.sub_len;   // sub-chunks this run really has
+  int n_used = (n_tok + sp.sub_len - 1) / sp.sub_len;         // sub-chunks this run really has
+  n_used = n_used < sp.n_sub ? n_used : sp.n_sub;
   constexpr int kPer = D * D / 4 / kCarrySplit;               // float4s per CTA
   for (int e = threadIdx.x; e < kPer; e += 256) {
     const int e4 = part * kPer + e;

@@ -88,7 +88,8 @@ __global__ void __launch_bounds__(kThreads, 1) gla_scan_tc_kernel(const Params P
   }
   const int n_chunks = (run1 - run0 + kC - 1) / kC;                       // of the run
   const int c_lo = P.n_sub > 1 ? sub * P.sub_chunks : 0;                  // of this CTA: [c_lo, c_hi)
-  const int c_hi = P.n_sub > 1 && c_lo + P.sub_chunks < n_chunks ? c_lo + P.sub_chunks : n_chunks;
+  // a run longer than the caller said: its last piece takes the rest
+  const int c_hi = sub + 1 < P.n_sub && c_lo + P.sub_chunks < n_chunks ? c_lo + P.sub_chunks : n_chunks;
   const bool is_last = c_hi == n_chunks;
   if (c_lo >= n_chunks) return;          // the run is shorter than this piece's start
   if (LOCAL && is_last) return;          // nobody needs the local state of a run's last piece
@@ -301,22 +302,6 @@ __global__ void __launch_bounds__(kThreads, 1) gla_scan_tc_kernel(const Params P
         *reinterpret_cast<float4*>(part_s + tg * kD + d0) = make_float4(run[0], run[1], run[2], run[3]);
         *reinterpret_cast<float4*>(part_s + tg * kD + d0 + 4) = make_float4(run[4], run[5], run[6], run[7]);
       }
-      // q, k, v of this thread's first two tokens are asked for now and arrive under the scan below;
-      // those of the other two when the first two are worked on
-      auto load_pair = [&](int i2, uint4 (&q2)[2], uint4 (&k2)[2], uint4 (&v2)[2]) {
-#pragma unroll
-        for (int u = 0; u < 2; ++u) {
-          const int tl = tg * 4 + i2 + u;
-          const int tc = tl < nt ? tl : 0;   // a row that exists; its values are dropped where they are used
-          const int64_t kv_off = ((int64_t)(tb + tc) * P.Hkv + hk) * kD + d0;
-          if (!LOCAL) q2[u] = *reinterpret_cast<const uint4*>(P.q + ((int64_t)(tb + tc) * P.H + h) * kD + d0);
-          else q2[u] = make_uint4(0, 0, 0, 0);
-          k2[u] = *reinterpret_cast<const uint4*>(P.k + kv_off);
-          v2[u] = *reinterpret_cast<const uint4*>(P.v + kv_off);
-        }
-      };
-      uint4 qa[2], ka[2], va[2];
-      load_pair(0, qa, ka, va);
       // the next chunk's rows on their way into L2 meanwhile (its loads then meet L2, not HBM, latency):
       // one request per 128-byte line
 #pragma unroll
@@ -354,15 +339,25 @@ __global__ void __launch_bounds__(kThreads, 1) gla_scan_tc_kernel(const Params P
       }
       workers_bar();   // the scratch is read; V may land on it (and flags[2] is read by everyone)
       if (stop) break;
-      uint4 qb[2], kb[2], vb[2];
-      load_pair(2, qb, kb, vb);
 #pragma unroll
       for (int i2 = 0; i2 < 4; i2 += 2) {
+      // (two tokens' loads are issued together: two trips to L2 per chunk instead of four)
+      uint4 qw2[2], kw2[2], vw2[2];
+#pragma unroll
+      for (int u = 0; u < 2; ++u) {
+        const int tl = tg * 4 + i2 + u;
+        const int tc = tl < nt ? tl : 0;
+        const int64_t kv_off = ((int64_t)(tb + tc) * P.Hkv + hk) * kD + d0;
+        if (!LOCAL) qw2[u] = *reinterpret_cast<const uint4*>(P.q + ((int64_t)(tb + tc) * P.H + h) * kD + d0);
+        else qw2[u] = make_uint4(0, 0, 0, 0);
+        kw2[u] = *reinterpret_cast<const uint4*>(P.k + kv_off);
+        vw2[u] = *reinterpret_cast<const uint4*>(P.v + kv_off);
+      }
 #pragma unroll
       for (int u = 0; u < 2; ++u) {
         const int i = i2 + u;
         const int tl = tg * 4 + i;
-        uint4 qw = i2 ? qb[u] : qa[u], kw = i2 ? kb[u] : ka[u], vw = i2 ? vb[u] : va[u];
+        uint4 qw = qw2[u], kw = kw2[u], vw = vw2[u];
         if (tl >= nt) qw = kw = vw = make_uint4(0, 0, 0, 0);
         const uint32_t qx[4] = {qw.x, qw.y, qw.z, qw.w}, kx[4] = {kw.x, kw.y, kw.z, kw.w};
         uint32_t qh[4], ql[4], kh[4], kl[4];

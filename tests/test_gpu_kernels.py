@@ -814,6 +814,30 @@ def test_gla_scan_chunk_parallel_strong_decay_and_fused_neighbours(ops):
     assert rel_err(o_par, o_one) <= 1e-5 and rel_err(s_par, s_one) <= 1e-5
 
 
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float32])
+def test_gla_scan_run_longer_than_the_caller_said(ops, dtype):
+    """`max_query_len` only plans the cut: a run longer than stated (here 4096 tokens against a stated
+    1024 and 2048) still comes out right, its last piece taking the rest, and nothing is written past the
+    workspace sized for the stated length."""
+    H, Hkv, D, T = 28, 4, 128, 4096
+    q, k, v, gk = _scan_inputs(T, H, Hkv, D, seed=52, dtype=dtype)
+    qsl_d = torch.tensor([0, T], dtype=torch.int32, device=DEV)
+    dev = lambda t: t.to(DEV)
+    state = torch.randn(1, H, D, D, generator=torch.Generator().manual_seed(53)) * 0.1
+    s_one = dev(state)
+    o_one = ops.gla_scan(dev(q), dev(k), dev(v), dev(gk), s_one, qsl_d, out_dtype=torch.float32)
+    for stated in (1024, 2048):
+        ws = ops.gla_scan_workspace(1, stated, H, D, DEV)
+        guard = torch.full((ws.numel() + 4096,), 0x5A, dtype=torch.uint8, device=DEV)
+        inner = guard[:ws.numel()]
+        s_par, st = dev(state), _status()
+        o_par = ops.gla_scan(dev(q), dev(k), dev(v), dev(gk), s_par, qsl_d, out_dtype=torch.float32,
+                             max_query_len=stated, workspace=inner, status=st)
+        assert st.item() == 0
+        assert rel_err(o_par, o_one) <= 1e-5 and rel_err(s_par, s_one) <= 1e-5
+        assert bool((guard[ws.numel():] == 0x5A).all())
+
+
 def test_gla_scan_workspace_too_small_is_refused(ops):
     from spikingbrain_7b_b200 import _abi
     H, Hkv, D, T = 28, 4, 128, 2048
