@@ -315,6 +315,7 @@ swa_prefill_tc_kernel(const Params P, const __grid_constant__ CUtensorMap map_k,
       m_run = m_new;
       // ---- probabilities, in place of the scores ----
       float ls[4] = {0.f, 0.f, 0.f, 0.f};
+      uint32_t hi[16], lo[16];
       if (full) {
         const f32x2 sc2 = pack2(P.scale_log2, P.scale_log2), nm2 = pack2(-m_s, -m_s);
         f32x2 la = 0ull, lb = 0ull;
@@ -324,10 +325,12 @@ swa_prefill_tc_kernel(const Params P, const __grid_constant__ CUtensorMap map_k,
           unpack2(ffma2(pack2(__uint_as_float(sr[i]), __uint_as_float(sr[i + 1])), sc2, nm2), x0, x1);
           unpack2(ffma2(pack2(__uint_as_float(sr[i + 2]), __uint_as_float(sr[i + 3])), sc2, nm2), x2, x3);
           const float p0 = fast_exp2(x0), p1 = fast_exp2(x1), p2 = fast_exp2(x2), p3 = fast_exp2(x3);
-          sr[i] = __float_as_uint(p0); sr[i + 1] = __float_as_uint(p1);
-          sr[i + 2] = __float_as_uint(p2); sr[i + 3] = __float_as_uint(p3);
           la = fadd2(la, pack2(p0, p1));
           lb = fadd2(lb, pack2(p2, p3));
+          // split here, among the exponentials: the special-function unit paces those, and the
+          // conversions fill the issue slots it leaves
+          split_bf16x2(p0, p1, hi[i >> 1], lo[i >> 1]);
+          split_bf16x2(p2, p3, hi[(i >> 1) + 1], lo[(i >> 1) + 1]);
         }
         unpack2(la, ls[0], ls[1]);
         unpack2(lb, ls[2], ls[3]);
@@ -339,6 +342,9 @@ swa_prefill_tc_kernel(const Params P, const __grid_constant__ CUtensorMap map_k,
           sr[i] = __float_as_uint(pv);
           ls[i & 3] += pv;
         }
+#pragma unroll
+        for (int e = 0; e < 16; ++e)
+          split_bf16x2(__uint_as_float(sr[2 * e]), __uint_as_float(sr[2 * e + 1]), hi[e], lo[e]);
       }
       l_run = l_run * alpha + (ls[0] + ls[1]) + (ls[2] + ls[3]);
       // ---- rescale O (my kCols dims of this row) where the offset moved; the GEMMs that wrote it must be done ----
@@ -374,10 +380,6 @@ swa_prefill_tc_kernel(const Params P, const __grid_constant__ CUtensorMap map_k,
       {
         // P takes the place of S in the same TMEM buffer (every thread of the row has its scores in
         // registers since the exchange of the maxima): head in columns [0,64), remainder in [64,128)
-        uint32_t hi[16], lo[16];
-#pragma unroll
-        for (int e = 0; e < 16; ++e)
-          split_bf16x2(__uint_as_float(sr[2 * e]), __uint_as_float(sr[2 * e + 1]), hi[e], lo[e]);
         tmem_st16(t_lane + (t & 1) * 128 + part * (kCols / 2), hi);
         tmem_st16(t_lane + (t & 1) * 128 + 64 + part * (kCols / 2), lo);
       }
