@@ -369,15 +369,19 @@ int sbk_gla_step(const void* q, const void* k, const void* v, const void* g, int
  *  out          [T, H, D] bf16, `out_tok_stride` elements between tokens
  *  key2,value2,num_meta  sink tokens as in sbk_swa_decode (the k2/v2 pass of
  *               fa_kernel_metatoken.py:198-280), or NULL, NULL, 0
- *  kernel       SBK_PREFILL_AUTO: the tcgen05 kernel (tensor memory, 128-key tiles) when q and out
- *               are 16-byte aligned with token strides that are multiples of 8 elements, else the
- *               mma.sync kernel; SBK_PREFILL_TCGEN05 / SBK_PREFILL_MMA_SYNC force one (the former
- *               returns SBK_E_ALIGN when q / out do not meet its rule)
+ *  kernel       SBK_PREFILL_AUTO: a tcgen05 kernel (tensor memory, 128-key tiles) when q and out
+ *               are 16-byte aligned with token strides that are multiples of 8 elements -- two
+ *               query tiles per CTA taking turns when max_query_len exceeds one tile's 128 / (H/kvh)
+ *               queries, one tile per CTA otherwise -- else the mma.sync kernel;
+ *               SBK_PREFILL_TCGEN05 (one tile) / SBK_PREFILL_TCGEN05_PAIR (two tiles) /
+ *               SBK_PREFILL_MMA_SYNC force one (the tcgen05 ones return SBK_E_ALIGN when q / out
+ *               do not meet their rule). All three compute the same function.
  * Supported: D == 128, H % kvh == 0, H/kvh <= 8, block_size % 16 == 0.
  */
 #define SBK_PREFILL_AUTO 0
 #define SBK_PREFILL_TCGEN05 1
 #define SBK_PREFILL_MMA_SYNC 2
+#define SBK_PREFILL_TCGEN05_PAIR 3
 int sbk_swa_prefill(const void* q, int64_t q_tok_stride, const void* k_cache, const void* v_cache,
                     const int32_t* block_tables, int max_blocks, const int32_t* query_start_loc,
                     const int32_t* context_lens, int n_seqs, int max_query_len, int H, int kvh, int D,

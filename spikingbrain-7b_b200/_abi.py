@@ -11,7 +11,7 @@ PKG_DIR = os.path.dirname(os.path.abspath(__file__))
 LIB_PATH = os.path.join(PKG_DIR, "libsbk.so")
 
 SBK_BF16, SBK_F32 = 0, 1
-PREFILL_AUTO, PREFILL_TCGEN05, PREFILL_MMA_SYNC = 0, 1, 2
+PREFILL_AUTO, PREFILL_TCGEN05, PREFILL_MMA_SYNC, PREFILL_TCGEN05_PAIR = 0, 1, 2, 3
 SBK_OK, SBK_E_ARG, SBK_E_ALIGN, SBK_E_WORKSPACE, SBK_E_LAUNCH = 0, -1, -2, -3, -4
 ST_BAD_SLOT, ST_BAD_BLOCK, ST_WAIT_TIMEOUT, ST_RETIRE_OVERFLOW, ST_BAD_POSITION = 1, 2, 4, 8, 16
 ST_OUT_OF_BLOCKS, ST_TABLE_FULL = 32, 64

@@ -7,7 +7,7 @@ import sys
 PKG_DIR = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(PKG_DIR, "csrc")
 LIB_PATH = os.path.join(PKG_DIR, "libsbk.so")
-SOURCES = ["sbk_abi.cu", "sbk_tma.cu", "kv_append.cu", "rope_kv_append.cu", "step_plan.cu", "gla_step.cu", "gla_scan.cu", "gla_scan_tc.cu", "swa_paged_decode.cu", "peer.cu", "swa_prefill.cu", "swa_prefill_tc.cu"]
+SOURCES = ["sbk_abi.cu", "sbk_tma.cu", "kv_append.cu", "rope_kv_append.cu", "step_plan.cu", "gla_step.cu", "gla_scan.cu", "gla_scan_tc.cu", "swa_paged_decode.cu", "peer.cu", "swa_prefill.cu", "swa_prefill_tc.cu", "swa_prefill_tc2.cu"]
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
     "-Xcompiler", "-fPIC", "-shared",

@@ -304,8 +304,9 @@ extern "C" int sbk_swa_prefill(const void* q, int64_t q_tok_stride, const void* 
                                int32_t* status, void* stream) {
   using namespace sbk;
   using namespace sbk::prefill;
-  if (kernel != SBK_PREFILL_AUTO && kernel != SBK_PREFILL_TCGEN05 && kernel != SBK_PREFILL_MMA_SYNC) {
-    set_error("sbk_swa_prefill: kernel=%d is none of SBK_PREFILL_AUTO / _TCGEN05 / _MMA_SYNC", kernel);
+  if (kernel != SBK_PREFILL_AUTO && kernel != SBK_PREFILL_TCGEN05 && kernel != SBK_PREFILL_MMA_SYNC &&
+      kernel != SBK_PREFILL_TCGEN05_PAIR) {
+    set_error("sbk_swa_prefill: kernel=%d is none of SBK_PREFILL_AUTO / _TCGEN05 / _MMA_SYNC / _TCGEN05_PAIR", kernel);
     return SBK_E_ARG;
   }
   if (num_meta < 0 || num_meta % 16 != 0 || (num_meta > 0 && (!key2 || !value2 || !aligned16(key2) || !aligned16(value2)))) {
@@ -343,10 +344,12 @@ extern "C" int sbk_swa_prefill(const void* q, int64_t q_tok_stride, const void* 
     return SBK_E_ARG;
   }
   const int bq_tc = prefill_tc::queries_per_tile(H / kvh);
-  // Two kernels serve this entry point: tcgen05 (tensor memory, 128-key tiles; what `kernel` AUTO
-  // picks) and mma.sync (on request, or under AUTO when q / out cannot be moved as 16-byte vectors).
+  // Three kernels serve this entry point: tcgen05 with two query tiles per CTA taking turns (what
+  // `kernel` AUTO picks when a run has more queries than one tile), tcgen05 with one tile per CTA
+  // (AUTO for shorter runs), and mma.sync (on request, or under AUTO when q / out cannot be moved
+  // as 16-byte vectors).
   const bool vec_ok = aligned16(q) && aligned16(out) && q_tok_stride % 8 == 0 && out_tok_stride % 8 == 0;
-  if (kernel == SBK_PREFILL_TCGEN05 && !vec_ok) {
+  if ((kernel == SBK_PREFILL_TCGEN05 || kernel == SBK_PREFILL_TCGEN05_PAIR) && !vec_ok) {
     set_error("sbk_swa_prefill: the tcgen05 kernel needs q and out 16-byte aligned with token strides that are "
               "multiples of 8 elements");
     return SBK_E_ALIGN;
@@ -370,7 +373,9 @@ extern "C" int sbk_swa_prefill(const void* q, int64_t q_tok_stride, const void* 
     T.q = (const __nv_bfloat16*)q; T.q_tok_stride = q_tok_stride;
     T.block_tables = block_tables; T.max_blocks = max_blocks;
     T.query_start_loc = query_start_loc; T.context_lens = context_lens;
-    T.n_seqs = n_seqs; T.bq = bq_tc; T.tiles_per_seq = (max_query_len + bq_tc - 1) / bq_tc; T.H = H; T.G = H / kvh;
+    const bool pair = kernel == SBK_PREFILL_TCGEN05_PAIR || (kernel == SBK_PREFILL_AUTO && max_query_len > bq_tc);
+    const int per_cta = pair ? 2 * bq_tc : bq_tc;
+    T.n_seqs = n_seqs; T.bq = bq_tc; T.tiles_per_seq = (max_query_len + per_cta - 1) / per_cta; T.H = H; T.G = H / kvh;
     T.num_blocks = num_blocks;
     T.block_size = block_size; T.window_left = window_left; T.scale_log2 = scale * kLog2e;
     T.out = (__nv_bfloat16*)out; T.out_tok_stride = out_tok_stride; T.status = status;
@@ -378,6 +383,7 @@ extern "C" int sbk_swa_prefill(const void* q, int64_t q_tok_stride, const void* 
     T.k_start_loc = nullptr;
     T.noncausal = 0;
     T.tile_copy = tc_mode;
+    if (pair) return prefill_tc2::launch(T, kvh, mk, mv, mk2, mv2, (cudaStream_t)stream);
     return prefill_tc::launch(T, kvh, mk, mv, mk2, mv2, (cudaStream_t)stream);
   }
   const MapKey keys[4] = {MapKey{k_cache, kvh, num_blocks, block_size, cache_block_stride_bytes, 2},
@@ -477,10 +483,12 @@ extern "C" int sbk_swa_prefill_dense(const void* q, int64_t q_tok_stride, const 
   T.block_tables = nullptr; T.max_blocks = 0;
   T.query_start_loc = query_start_loc; T.context_lens = nullptr; T.k_start_loc = k_start_loc;
   T.noncausal = causal ? 0 : 1;
-  T.n_seqs = n_seqs; T.bq = bq_tc; T.tiles_per_seq = tiles; T.H = H; T.G = H / kvh; T.num_blocks = 1;
+  const bool pair = max_query_len > bq_tc;     // as under SBK_PREFILL_AUTO in the paged entry point
+  T.n_seqs = n_seqs; T.bq = bq_tc; T.tiles_per_seq = pair ? (tiles + 1) / 2 : tiles; T.H = H; T.G = H / kvh; T.num_blocks = 1;
   T.block_size = 16; T.window_left = window_left; T.scale_log2 = scale * kLog2e;
   T.out = (__nv_bfloat16*)out; T.out_tok_stride = out_tok_stride; T.status = status;
   T.n_meta_chunks = num_meta / 16;
   T.tile_copy = tc_mode;
+  if (pair) return prefill_tc2::launch(T, kvh, mk, mv, mk2, mv2, (cudaStream_t)stream);
   return prefill_tc::launch(T, kvh, mk, mv, mk2, mv2, (cudaStream_t)stream);
 }

@@ -29,4 +29,10 @@ int launch(const Params& P, int kvh, const CUtensorMap& map_k, const CUtensorMap
            const CUtensorMap& map_k2, const CUtensorMap& map_v2, cudaStream_t stream);
 
 }  // namespace prefill_tc
+
+// the same work with two query tiles per CTA taking turns (tiles_per_seq counts pairs of tiles)
+namespace prefill_tc2 {
+int launch(const prefill_tc::Params& P, int kvh, const CUtensorMap& map_k, const CUtensorMap& map_v,
+           const CUtensorMap& map_k2, const CUtensorMap& map_v2, cudaStream_t stream);
+}  // namespace prefill_tc2
 }  // namespace sbk

@@ -467,7 +467,8 @@ def gla_scan_workspace(n_seqs: int, max_query_len: int, H: int, D: int, device) 
     return torch.empty(n, dtype=torch.uint8, device=device) if n else None
 
 
-PREFILL_KERNELS = {"auto": _abi.PREFILL_AUTO, "tcgen05": _abi.PREFILL_TCGEN05, "mma_sync": _abi.PREFILL_MMA_SYNC}
+PREFILL_KERNELS = {"auto": _abi.PREFILL_AUTO, "tcgen05": _abi.PREFILL_TCGEN05, "mma_sync": _abi.PREFILL_MMA_SYNC,
+                   "tcgen05_pair": _abi.PREFILL_TCGEN05_PAIR}
 
 
 def swa_prefill(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, block_tables: torch.Tensor,

@@ -458,10 +458,11 @@ def _prefill_case(ops, ctx, new, wl, H, kvh, bs, seed, kernel="auto"):
     assert worst <= ATTN_MAX_ABS and num / den <= ATTN_MEAN_REL, (worst, num / den)
 
 
-@pytest.fixture(params=["tcgen05", "mma_sync"])
+@pytest.fixture(params=["tcgen05", "tcgen05_pair", "mma_sync"])
 def prefill_kernel(request):
-    """The prefill entry point has two kernels, chosen by its `kernel` argument: tcgen05 (what "auto"
-    takes for aligned q / out) and mma.sync."""
+    """The prefill entry point has three kernels, chosen by its `kernel` argument: tcgen05 with one
+    query tile per CTA, tcgen05 with two tiles taking turns (between them what "auto" takes for aligned
+    q / out) and mma.sync."""
     return request.param
 
 
