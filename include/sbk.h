@@ -50,6 +50,8 @@ extern "C" {
 #define SBK_ST_BAD_POSITION 16   /* a position outside the cos/sin table (token left untouched) */
 #define SBK_ST_OUT_OF_BLOCKS 32  /* sbk_plan_step: the ring of free blocks cannot serve the step */
 #define SBK_ST_TABLE_FULL 64     /* sbk_plan_step: a table row or slot_mapping is too short for the step */
+#define SBK_ST_VALUE_RANGE 128   /* sbk_swa_prefill, two-tile tcgen05 kernel: a V value of magnitude 2^16 or more
+                                    (or inf / NaN) met its fp16 second GEMM; SBK_PREFILL_TCGEN05 serves such a cache */
 
 int sbk_abi_version(void);
 const char* sbk_last_error(void);

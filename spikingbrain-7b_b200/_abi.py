@@ -14,7 +14,7 @@ SBK_BF16, SBK_F32 = 0, 1
 PREFILL_AUTO, PREFILL_TCGEN05, PREFILL_MMA_SYNC, PREFILL_TCGEN05_PAIR = 0, 1, 2, 3
 SBK_OK, SBK_E_ARG, SBK_E_ALIGN, SBK_E_WORKSPACE, SBK_E_LAUNCH = 0, -1, -2, -3, -4
 ST_BAD_SLOT, ST_BAD_BLOCK, ST_WAIT_TIMEOUT, ST_RETIRE_OVERFLOW, ST_BAD_POSITION = 1, 2, 4, 8, 16
-ST_OUT_OF_BLOCKS, ST_TABLE_FULL = 32, 64
+ST_OUT_OF_BLOCKS, ST_TABLE_FULL, ST_VALUE_RANGE = 32, 64, 128
 ABI_VERSION = 5
 
 # name -> (restype, argtypes); must list every function include/sbk.h declares

@@ -139,6 +139,22 @@ __host__ __device__ constexpr uint32_t instr_desc(int b_mn, int a_mn = 0) {
          ((128u >> 4) << 24);
 }
 
+// the same with both operands fp16
+__host__ __device__ constexpr uint32_t instr_desc_f16(int b_mn, int a_mn = 0) {
+  return (1u << 4) | ((uint32_t)a_mn << 15) | ((uint32_t)b_mn << 16) | ((128u >> 3) << 17) | ((128u >> 4) << 24);
+}
+
+// two floats -> packed fp16 pair, `lo` in the low half (round to nearest even)
+__device__ __forceinline__ uint32_t pack_f16x2(float lo, float hi) {
+  uint32_t r;
+  asm("cvt.rn.f16x2.f32 %0, %1, %2;" : "=r"(r) : "f"(hi), "f"(lo));
+  return r;
+}
+// packed bf16 pair -> packed fp16 pair, element by element (exact inside fp16's normal range)
+__device__ __forceinline__ uint32_t bf16x2_to_f16x2(uint32_t w) {
+  return pack_f16x2(__uint_as_float(w << 16), __uint_as_float(w & 0xffff0000u));
+}
+
 // byte offset of the 16-byte chunk `c` (0..7) of row `r` inside a [128 rows][128 B] swizzled panel
 __device__ __forceinline__ uint32_t swz(int r, int c) { return (uint32_t)(r * 128 + ((c ^ (r & 7)) << 4)); }
 
