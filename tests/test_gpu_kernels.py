@@ -486,6 +486,79 @@ def test_swa_prefill_long_chunk_at_model_shapes(ops, prefill_kernel):
     _prefill_case(ops, [6000], [2048], wl=4096, H=28, kvh=4, bs=16, seed=63, kernel=prefill_kernel)
 
 
+def _set_token(kv, table, s, i, bs, k=None, v=None):
+    pb = int(table[s, i // bs])
+    if k is not None:
+        kv[0, pb, i % bs] = k
+    if v is not None:
+        kv[1, pb, i % bs] = v
+
+
+def test_swa_prefill_scores_that_keep_growing_move_the_offset(ops, prefill_kernel):
+    """Keys whose scores rise by about 13 (log2 units) per 128-key tile: the softmax offset, which the
+    tcgen05 kernels move only when a row's maximum outgrows it by 2^8, moves on every tile, and the
+    output accumulated so far is rescaled in tensor memory each time. (Random keys never do this after
+    a row's first tile.)"""
+    D, H, kvh, bs, wl = 128, 28, 4, 16, 1023
+    ctx, new = [900], [400]
+    kv, table, nb = make_paged_kv([1300], -1, kvh, D, bs, seed=81)
+    g = torch.Generator().manual_seed(82)
+    u = torch.randn(D, generator=g)
+    u = u / u.norm()
+    for i in range(1300):
+        k = (0.07 * i * math.sqrt(D) / 8) * u + 0.05 * torch.randn(kvh, D, generator=g)
+        _set_token(kv, table, 0, i, bs, k=k.bfloat16())
+    q = (8 * u + 0.3 * torch.randn(400, H, D, generator=g)).bfloat16()
+    st = _status()
+    kv_d = kv.to(DEV)
+    out = ops.swa_prefill(q.to(DEV), kv_d[0], kv_d[1], table.to(DEV), torch.tensor([0, 400], dtype=torch.int32, device=DEV),
+                          torch.tensor(ctx, dtype=torch.int32, device=DEV), 400, window_left=wl, kernel=prefill_kernel,
+                          status=st).float().cpu()
+    assert st.item() == 0 and torch.isfinite(out).all()
+    num = den = worst = 0.0
+    for i in (0, 1, 17, 18, 35, 36, 127, 200, 399):
+        ref = ref_ops.swa_paged_decode_ref(q[i][None], kv[0], kv[1], table[0:1], [900 + i + 1], wl, D ** -0.5)[0]
+        d = (out[i] - ref.bfloat16().float()).abs()
+        worst = max(worst, float(d.max())); num += float(d.sum()); den += float(ref.abs().sum())
+    assert worst <= ATTN_MAX_ABS and num / den <= ATTN_MEAN_REL, (worst, num / den)
+
+
+def test_swa_prefill_value_range_of_the_two_tile_kernel(ops):
+    """The two-tile tcgen05 kernel multiplies P and V in fp16. Values up to fp16's largest magnitude
+    go through it unharmed; one beyond raises SBK_ST_VALUE_RANGE there, and the one-tile kernel (bf16
+    throughout) serves the same cache with status 0."""
+    from spikingbrain_7b_b200 import _abi
+    D, H, kvh, bs, wl = 128, 28, 4, 16, 255
+    kv, table, nb = make_paged_kv([500], -1, kvh, D, bs, seed=83)
+    g = torch.Generator().manual_seed(84)
+    q = (torch.randn(200, H, D, generator=g) / math.sqrt(D)).bfloat16()
+    big = (torch.randn(kvh, D, generator=g) * 2.0e4).clamp(-6.0e4, 6.0e4).bfloat16()     # inside fp16 range
+    _set_token(kv, table, 0, 350, bs, v=big)
+    args = lambda kvt: (q.to(DEV), kvt[0], kvt[1], table.to(DEV), torch.tensor([0, 200], dtype=torch.int32, device=DEV),
+                        torch.tensor([300], dtype=torch.int32, device=DEV), 200)
+
+    def check(out):
+        for i in (0, 49, 50, 51, 120, 199):
+            ref = ref_ops.swa_paged_decode_ref(q[i][None], kv[0], kv[1], table[0:1], [300 + i + 1], wl, D ** -0.5)[0]
+            ref = ref.bfloat16().float()
+            assert mean_rel(out[i], ref) <= ATTN_MEAN_REL and float((out[i] - ref).abs().max()) <= 2.0 ** -7 * float(ref.abs().max())
+
+    st = _status()
+    out = ops.swa_prefill(*args(kv.to(DEV)), window_left=wl, kernel="tcgen05_pair", status=st).float().cpu()
+    assert st.item() == 0
+    check(out)
+    over = torch.zeros(kvh, D)
+    over[1, 5] = 1.0e5
+    _set_token(kv, table, 0, 360, bs, v=over.bfloat16())
+    st = _status()
+    ops.swa_prefill(*args(kv.to(DEV)), window_left=wl, kernel="tcgen05_pair", status=st)
+    assert st.item() == _abi.ST_VALUE_RANGE
+    st = _status()
+    out = ops.swa_prefill(*args(kv.to(DEV)), window_left=wl, kernel="tcgen05", status=st).float().cpu()
+    assert st.item() == 0
+    check(out)
+
+
 @pytest.mark.parametrize("wl,n_meta", [(63, 0), (-1, 0), (300, 48), (0, 0)])
 def test_swa_prefill_dense_matches_oracle(ops, wl, n_meta):
     """K/V as tensors instead of a paged cache: ragged sequences, more keys than queries in some
