@@ -268,7 +268,7 @@ swa_prefill_pair_kernel(const Params P, const __grid_constant__ CUtensorMap map_
     //       conversion is element by element), then the rows past the newest key are cleared =====
     const int ct = threadIdx.x - 32 * (kSoftmaxWarps + 3);     // 0 .. 32 * kConvWarps - 1
     bool ok = true;
-    uint32_t big = 0;                                          // an exponent beyond fp16's was seen
+    uint32_t top = 0;                                          // largest magnitude seen (bf16 bits, per half)
     for (int t = 0; t < n_tiles; ++t) {
       const int slot = t % kStagesV;
       ok = mbar_wait_bounded(bar_vf + 8 * slot, (t / kStagesV) & 1);
@@ -294,8 +294,7 @@ swa_prefill_pair_kernel(const Params P, const __grid_constant__ CUtensorMap map_
           uint32_t x[4] = {w.x, w.y, w.z, w.w};
 #pragma unroll
           for (int e = 0; e < 4; ++e) {
-            // bf16 exponent field of 0x8F or more: magnitude of 2^16 or more (or inf / NaN)
-            big |= ((x[e] & 0x7f80u) >= 0x4780u) | ((x[e] & 0x7f800000u) >= 0x47800000u);
+            top = __vmaxu2(top, x[e] & 0x7fff7fffu);
             x[e] = bf16x2_to_f16x2(x[e]);
           }
           *ptr = make_uint4(x[0], x[1], x[2], x[3]);
@@ -312,7 +311,9 @@ swa_prefill_pair_kernel(const Params P, const __grid_constant__ CUtensorMap map_
       __syncwarp();
       if (lane == 0) mbar_arrive(bar_vc + 8 * slot);
     }
-    if (__any_sync(0xffffffffu, big != 0) && lane == 0) raise_status(P.status, SBK_ST_VALUE_RANGE);
+    // bf16 bits of 0x4780 or more: a magnitude of 2^16 or more (or inf / NaN), which fp16 does not hold
+    if (__any_sync(0xffffffffu, (top & 0xffffu) >= 0x4780u || (top >> 16) >= 0x4780u) && lane == 0)
+      raise_status(P.status, SBK_ST_VALUE_RANGE);
     if (!ok && lane == 0 && !flags[8]) { raise_status(P.status, SBK_ST_WAIT_TIMEOUT); flags[8] = 1; }
   } else {
     // ====================== softmax / epilogue: one thread per row ======================
