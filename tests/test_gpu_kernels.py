@@ -523,6 +523,31 @@ def test_swa_prefill_scores_that_keep_growing_move_the_offset(ops, prefill_kerne
     assert worst <= ATTN_MAX_ABS and num / den <= ATTN_MEAN_REL, (worst, num / den)
 
 
+def test_swa_prefill_bad_block_is_reported_and_contained(ops, prefill_kernel):
+    """A block-table entry outside the pool inside one sequence's window: the kernels raise
+    SBK_ST_BAD_BLOCK, skip the keys of that tile (nothing is read through the bad id), keep every output
+    finite, and the other sequence's rows are untouched by it."""
+    from spikingbrain_7b_b200 import _abi
+    D, H, kvh, bs, wl = 128, 28, 4, 16, 511
+    ctx, new = [600, 300], [200, 150]
+    kv, table, nb = make_paged_kv([800, 450], -1, kvh, D, bs, seed=85)
+    g = torch.Generator().manual_seed(86)
+    q = (torch.randn(350, H, D, generator=g) / math.sqrt(D)).bfloat16()
+    bad = table.clone()
+    bad[0, 500 // bs] = nb + 3                       # inside the window of every new token of sequence 0
+    st = _status()
+    kv_d = kv.to(DEV)
+    out = ops.swa_prefill(q.to(DEV), kv_d[0], kv_d[1], bad.to(DEV), torch.tensor([0, 200, 350], dtype=torch.int32, device=DEV),
+                          torch.tensor(ctx, dtype=torch.int32, device=DEV), 200, window_left=wl, kernel=prefill_kernel,
+                          status=st).float().cpu()
+    assert st.item() == _abi.ST_BAD_BLOCK
+    assert torch.isfinite(out).all()
+    for i in (0, 17, 18, 36, 149):
+        ref = ref_ops.swa_paged_decode_ref(q[200 + i][None], kv[0], kv[1], table[1:2], [300 + i + 1], wl, D ** -0.5)[0]
+        ref = ref.bfloat16().float()
+        assert float((out[200 + i] - ref).abs().max()) <= ATTN_MAX_ABS and mean_rel(out[200 + i], ref) <= ATTN_MEAN_REL
+
+
 def test_swa_prefill_value_range_of_the_two_tile_kernel(ops):
     """The two-tile tcgen05 kernel multiplies P and V in fp16. Values up to fp16's largest magnitude
     go through it unharmed; one beyond raises SBK_ST_VALUE_RANGE there, and the one-tile kernel (bf16
