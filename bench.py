@@ -872,7 +872,7 @@ def run_longctx(args):
     if prompt % chunk:
         raise SystemExit("--prompt must be a multiple of --chunk")
     T = S * chunk
-    max_blocks = (prompt + dsteps) // BLOCK + 2
+    max_blocks = (max(prompt, 2 * chunk) + dsteps) // BLOCK + 2      # (the warm-up below runs two chunks whatever the prompt)
     per_seq = (WINDOW_LEFT + chunk) // BLOCK + 4       # the window, the chunk in flight, partial blocks at the ends
     n_blocks = S * per_seq + 16
     plan = DeviceStepPlanner(n_blocks, BLOCK, WINDOW_LEFT, S, max_blocks, device, max_tokens=T)
