@@ -19,9 +19,9 @@
 // (exact for magnitudes in [2^-14, 65504]; smaller ones lose bits no output shows; a larger one
 // raises SBK_ST_VALUE_RANGE, its row of the output is not finite, and the one-tile kernel serves
 // such a cache). Both tiles read the converted V.
-// Roles (480 threads): warps 0-3 softmax / epilogue of tile A, warps 4-7 of tile B, warp 8 TMA
+// Roles (512 threads): warps 0-3 softmax / epilogue of tile A, warps 4-7 of tile B, warp 8 TMA
 // producer of the K ring, warp 9 of the V ring, warp 10 allocates tensor memory and issues the MMAs,
-// warps 11-14 convert V.
+// warps 11-15 convert V.
 // Every wait is bounded. Masks, sink tiles, dense and non-causal modes as in the one-tile kernel.
 #include "sbk_common.cuh"
 #include "sbk_tma.cuh"
@@ -46,7 +46,7 @@ constexpr int kVOff = kKOff + kStagesK * kOperandBytes;
 constexpr int kBarOff = kVOff + kStagesV * kOperandBytes;    // 229376
 constexpr int kSmemBytes = kBarOff + 256 + 1024;             // barriers, TMEM slot, flags; + alignment slack
 constexpr int kSoftmaxWarps = 8;
-constexpr int kConvWarps = 4;
+constexpr int kConvWarps = 5;   // (2: 5.09 ms, 4: 4.42, 5: 4.37, 6 and its spills: 4.65 on 8 x 8192 tokens)
 constexpr int kThreads = 32 * (kSoftmaxWarps + 3 + kConvWarps);
 constexpr int kTmemCols = 512;
 constexpr int kOCol = 256;
