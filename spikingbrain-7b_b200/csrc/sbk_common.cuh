@@ -68,6 +68,8 @@ __device__ __forceinline__ void fence_mbar_init() {
 __device__ __forceinline__ void fence_proxy_async_smem() {
   asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
 }
+// generic-proxy accesses (any state space) before, async-proxy accesses after
+__device__ __forceinline__ void fence_proxy_async_all() { asm volatile("fence.proxy.async;" ::: "memory"); }
 
 // ---- bulk async copies (TMA engine, untiled form) ---------------------------
 // global -> shared, completion counted in bytes on an mbarrier. Both addresses

@@ -57,7 +57,7 @@ constexpr float kLog2e = 1.4426950408889634f;
 constexpr float kLn2 = 0.6931471805599453f;
 constexpr float kNegBig = -1.0e30f;
 
-enum : int { kFlagFirst = 1, kFlagLast = 2, kFlagBad = 4, kFlagEnd = 8 };
+enum : int { kFlagFirst = 1, kFlagLast = 2, kFlagBad = 4, kFlagEnd = 8, kFlagFinal = 16 };   // Final: the CTA's last item
 
 struct Plan {
   int t0, c_first, n_chunks, n_pieces, chunks_per_piece;
@@ -109,7 +109,8 @@ struct Cfg {
   static constexpr int kLensOff = kPreOff + (kMaxSeqs + 4) * 4;
   static constexpr int kBarOff = kLensOff + kMaxSeqs * 4;
   static constexpr int kMiscOff = kBarOff + 2 * kStages * 8;
-  static constexpr int kSmemBytes = kMiscOff + 48 + 1024;      // + slack to align the ring to 1 KiB
+  static constexpr int kFoldBarOff = kMiscOff + 48;            // barrier of the fold's bulk copies
+  static constexpr int kSmemBytes = kFoldBarOff + 16 + 1024;   // + slack to align the ring to 1 KiB
   static_assert(kConsumerWarps % KVH == 0, "warps must split evenly over kv heads");
   static_assert(kVOffset == 16384, "a stage holds 16 KiB of K and 16 KiB of V");
   static_assert(kSmemBytes <= 115200, "two CTAs must fit one SM");
@@ -255,6 +256,55 @@ __device__ __forceinline__ void fold_pieces(const float* __restrict__ ws_o, cons
   }
 }
 
+// The same fold out of shared memory: `land` holds the O partials of the n_pieces pieces, [piece][H][D]
+// floats, then their (m, l) pairs, [piece][H][2]. `write` false: a dry run on whatever the memory
+// holds, for the sake of the instruction cache (this code runs once per CTA, at the very end of
+// the kernel, and fetching it cold costs more than running it).
+template <typename TO>
+__device__ __noinline__ void fold_landed(const float* land, float* lse_out, int H, int64_t out_seq_stride,
+                                      int b, int n_pieces, TO* out, bool write) {
+  const int d4 = threadIdx.x & 31;
+  const int w = threadIdx.x >> 5;
+  const float2* const ml = reinterpret_cast<const float2*>(land + (int64_t)n_pieces * H * kD);
+  constexpr int kU = 8;   // pieces whose loads are in flight together (the loops below are short chains otherwise)
+  for (int h = w; h < H; h += kConsumerWarps) {
+    float M = -INFINITY;
+    for (int i0 = 0; i0 < n_pieces; i0 += kU) {
+      float2 v[kU];
+#pragma unroll
+      for (int u = 0; u < kU; ++u) v[u] = ml[(i0 + u < n_pieces ? i0 + u : i0) * H + h];
+#pragma unroll
+      for (int u = 0; u < kU; ++u) M = fmaxf(M, v[u].x);
+    }
+    const float Ms = fmaxf(M, kNegBig);
+    float Ls = 0.f;
+    float4 O = make_float4(0.f, 0.f, 0.f, 0.f);
+    for (int i0 = 0; i0 < n_pieces; i0 += kU) {
+      float2 v[kU];
+      float4 o[kU];
+#pragma unroll
+      for (int u = 0; u < kU; ++u) {
+        const int i = i0 + u < n_pieces ? i0 + u : i0;
+        v[u] = ml[i * H + h];
+        o[u] = *reinterpret_cast<const float4*>(land + ((int64_t)i * H + h) * kD + d4 * 4);
+      }
+#pragma unroll
+      for (int u = 0; u < kU; ++u) {
+        const float wgt = i0 + u < n_pieces ? fast_exp2(v[u].x - Ms) : 0.f;
+        Ls += v[u].y * wgt;
+        O.x += o[u].x * wgt; O.y += o[u].y * wgt; O.z += o[u].z * wgt; O.w += o[u].w * wgt;
+      }
+    }
+    const float inv = Ls > 0.f ? 1.f / Ls : 0.f;
+    if (write) {
+      TO* op = out + (int64_t)b * out_seq_stride + (int64_t)h * kD + d4 * 4;
+      store_out4(op, O.x * inv, O.y * inv, O.z * inv, O.w * inv);
+      if (lse_out && d4 == 0)
+        lse_out[(int64_t)b * H + h] = Ls > 0.f ? (M + log2f(Ls)) * kLn2 : -INFINITY;
+    }
+  }
+}
+
 template <int KVH, typename TO, bool PEER>
 __global__ void __launch_bounds__(kThreads, 2)
 swa_decode_kernel(const Params P, const __grid_constant__ CUtensorMap map_k,
@@ -270,6 +320,7 @@ swa_decode_kernel(const Params P, const __grid_constant__ CUtensorMap map_k,
   int* lens_s = reinterpret_cast<int*>(smem + C::kLensOff);
   const uint32_t bar_full = ring + C::kBarOff;
   const uint32_t bar_empty = bar_full + C::kStages * 8;
+  const uint32_t bar_fold = ring + C::kFoldBarOff;
   // [0] abort, [1] fold flag, [2..6] scan, [7] longest sequence in chunks, [8] workspace marked stale
   volatile int* misc = reinterpret_cast<volatile int*>(smem + C::kMiscOff);
   const int warp = threadIdx.x >> 5;
@@ -281,6 +332,7 @@ swa_decode_kernel(const Params P, const __grid_constant__ CUtensorMap map_k,
       mbar_init(bar_full + 8 * s, 1);
       mbar_init(bar_empty + 8 * s, kConsumerWarps);
     }
+    mbar_init(bar_fold, 1);
     misc[0] = 0;
     misc[7] = 0;
     misc[8] = __ldcg(P.ctrl + 4);
@@ -371,7 +423,8 @@ swa_decode_kernel(const Params P, const __grid_constant__ CUtensorMap map_k,
     // entries are asked for now, and the consumers ask for its q row, so that neither side meets
     // a trip to L2 at the start of the next item: with short sequences those trips are most of an
     // item's time.
-    auto stream_item = [&](int b, int piece, int n_pieces, int meta_a, int meta_b, int cb, int n, int next_b) {
+    auto stream_item = [&](int b, int piece, int n_pieces, int meta_a, int meta_b, int cb, int n, int next_b,
+                           bool final_item = false) {
       if (next_b >= 0 && lane < 2) {
         const Plan np = make_plan(lens_s[next_b], P.window_left, P.split_chunks, P.max_pieces);
         const int lb = (np.c_first * kChunk) / P.block_size + lane * 32;
@@ -443,7 +496,8 @@ swa_decode_kernel(const Params P, const __grid_constant__ CUtensorMap map_k,
           StageInfo si;
           si.b = b; si.piece = piece; si.n_pieces = n_pieces; si.tok_base = tok_base;
           si.lo = lo; si.hi = hi; si.next_b = next_b;
-          si.flags = (jj == -n_ms ? kFlagFirst : 0) | (jj == nst - 1 ? kFlagLast : 0) | (bad ? kFlagBad : 0);
+          si.flags = (jj == -n_ms ? kFlagFirst : 0) | (jj == nst - 1 ? kFlagLast : 0) | (bad ? kFlagBad : 0) |
+                     (final_item && jj == nst - 1 ? kFlagFinal : 0);
           info[s] = si;
           if (bad) raise_status(P.status, SBK_ST_BAD_BLOCK);
           mbar_arrive_expect_tx(bar_full + 8 * s, bad ? 0u : (uint32_t)n_sub * 2u * C::kTileBytes);
@@ -506,8 +560,9 @@ swa_decode_kernel(const Params P, const __grid_constant__ CUtensorMap map_k,
           const int n_pieces = (pre[b] + cr - 1) / per - first_run + 1;
           const int ma = va < nm ? va : nm, mb = vb < nm ? vb : nm;
           const int wa = (va > nm ? va : nm) - nm, wb = (vb > nm ? vb : nm) - nm;
+          const int nb = (b + 1 < P.B && pre[b + 1] < g1) ? b + 1 : -1;
           stream_item(b, (int)blockIdx.x - first_run, n_pieces, ma, mb, plan.c_first + wa,
-                      L > 0 ? wb - wa : 0, (b + 1 < P.B && pre[b + 1] < g1) ? b + 1 : -1);
+                      L > 0 ? wb - wa : 0, nb, nb < 0);
         }
       }
     } else {
@@ -582,6 +637,9 @@ swa_decode_kernel(const Params P, const __grid_constant__ CUtensorMap map_k,
 #define SBK_K_ADDR(i) (stage + k_lane_off + ((i) >> 2) * 2048 + ((((((i) & 3) << 1) + cj_k) ^ xk) << 4))
 #define SBK_V_ADDR(i) (stage + v_lane_off + ((i) >> 2) * 2048 + ((((((i) & 3) << 1) + cj_v) ^ xv) << 4))
 
+  // the fold's code, once, while the first copies are on their way (two pieces of whatever the ring holds)
+  if (P.balanced && P.max_pieces > 1)
+    fold_landed<TO>(reinterpret_cast<const float*>(smem), nullptr, P.H, 0, 0, 2, out, false);
   for (int it = 0;; ++it) {
     const int s = it % C::kStages;
     if (!mbar_wait_bounded(bar_full + 8 * s, (it / C::kStages) & 1)) {
@@ -820,7 +878,34 @@ swa_decode_kernel(const Params P, const __grid_constant__ CUtensorMap map_k,
     consumer_bar();   // misc[1] may be rewritten by the next item only after everyone has read it
     if (!fold) continue;
     __threadfence();
-    fold_pieces<TO>(P.ws_o, P.ws_ml, P.lse_out, P.H, P.max_pieces, P.out_seq_stride, si.b, si.n_pieces, out);
+    // After its last item a CTA's ring is idle (only the end marker follows, which carries no data, and
+    // every warp is past the barriers above): the partials of all pieces land there by bulk copies
+    // issued together and are combined out of shared memory by code that has been run once already
+    // (see the warm-up in front of the loop). In balanced mode this sits at the very end of the
+    // kernel on every CTA at once.
+    const uint32_t o_bytes = (uint32_t)P.H * kD * 4u, ml_bytes = (uint32_t)P.H * 8u;
+    const float* const src_o = P.ws_o + (int64_t)si.b * P.max_pieces * P.H * kD;
+    const float* const src_ml = P.ws_ml + (int64_t)si.b * P.max_pieces * P.H * 2;
+    const bool land = (si.flags & kFlagFinal) && (ml_bytes & 15u) == 0 &&
+                      (uint32_t)si.n_pieces * (o_bytes + ml_bytes) <= (uint32_t)C::kRingBytes &&
+                      ((reinterpret_cast<uintptr_t>(src_o) | reinterpret_cast<uintptr_t>(src_ml)) & 15) == 0;
+    if (land) {
+      if (threadIdx.x == 0) {
+        fence_proxy_async_all();   // the partials were written through the generic proxy (by other CTAs)
+        mbar_arrive_expect_tx(bar_fold, (uint32_t)si.n_pieces * (o_bytes + ml_bytes));
+        for (int i = 0; i < si.n_pieces; ++i) {
+          bulk_g2s(ring + i * o_bytes, src_o + (int64_t)i * P.H * kD, o_bytes, bar_fold);
+          bulk_g2s(ring + si.n_pieces * o_bytes + i * ml_bytes, src_ml + (int64_t)i * P.H * 2, ml_bytes, bar_fold);
+        }
+      }
+      if (!mbar_wait_bounded(bar_fold, 0)) {
+        if (lane == 0) { raise_status(P.status, SBK_ST_WAIT_TIMEOUT); P.ctrl[4] = 1; misc[0] = 1; }
+        break;
+      }
+      fold_landed<TO>(reinterpret_cast<const float*>(smem), P.lse_out, P.H, P.out_seq_stride, si.b, si.n_pieces, out, true);
+    } else {
+      fold_pieces<TO>(P.ws_o, P.ws_ml, P.lse_out, P.H, P.max_pieces, P.out_seq_stride, si.b, si.n_pieces, out);
+    }
     if constexpr (PEER) {
       consumer_bar();
       mirror_row<TO>(P, si.b);
