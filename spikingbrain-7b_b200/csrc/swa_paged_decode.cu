@@ -110,7 +110,8 @@ struct Cfg {
   static constexpr int kBarOff = kLensOff + kMaxSeqs * 4;
   static constexpr int kMiscOff = kBarOff + 2 * kStages * 8;
   static constexpr int kFoldBarOff = kMiscOff + 48;            // barrier of the fold's bulk copies
-  static constexpr int kSmemBytes = kFoldBarOff + 16 + 1024;   // + slack to align the ring to 1 KiB
+  static constexpr int kFoldOff = kFoldBarOff + 16;            // scratch of the shared fold: 4 x 32 x 6 floats
+  static constexpr int kSmemBytes = kFoldOff + 3072 + 1024;    // + slack to align the ring to 1 KiB
   static_assert(kConsumerWarps % KVH == 0, "warps must split evenly over kv heads");
   static_assert(kVOffset == 16384, "a stage holds 16 KiB of K and 16 KiB of V");
   static_assert(kSmemBytes <= 115200, "two CTAs must fit one SM");
@@ -301,6 +302,88 @@ __device__ __noinline__ void fold_landed(const float* land, float* lse_out, int 
       store_out4(op, O.x * inv, O.y * inv, O.z * inv, O.w * inv);
       if (lse_out && d4 == 0)
         lse_out[(int64_t)b * H + h] = Ls > 0.f ? (M + log2f(Ls)) * kLn2 : -INFINITY;
+    }
+  }
+}
+
+// The fold of a split sequence shared out over the CTAs that hold its pieces (balanced mode): every
+// piece but the sequence's last is the last item of its CTA, which then has nothing else to do,
+// so those n_pieces - 1 CTAs wait for all pieces to be counted and fold the heads between them,
+// participant p the heads p, p + (n_pieces - 1), ... -- about one head each at one sequence per
+// launch, where a single CTA folding 33 pieces of 28 heads took 18 us of a 30 us kernel. Within a
+// CTA the four warps take every fourth piece of a head (a lane one float4 of dims, a warp's loads
+// issued together: one trip to L2), leave their (m, l, O) in `scratch` (shared memory, 4 x 32 x 6
+// floats) and warp 0 combines them and writes the head's output. `write` false: a dry run without
+// loads from the workspace or stores, for the sake of the instruction cache (this code runs once
+// per CTA, at the very end of the kernel, and fetching it cold costs more than running it).
+template <typename TO>
+__device__ __noinline__ void fold_heads(const float* __restrict__ ws_o, const float* __restrict__ ws_ml, float* scratch,
+                                     float* lse_out, int H, int max_pieces, int64_t out_seq_stride, int b,
+                                     int n_pieces, int part, int n_part, TO* out, bool write) {
+  constexpr int kB = 8;                                   // pieces of a warp whose loads are in flight together
+  const int lane = threadIdx.x & 31;
+  const int w = threadIdx.x >> 5;
+  const int64_t seq_base = (int64_t)b * max_pieces * H;
+  for (int h = part; h < H; h += n_part) {
+    float M = -INFINITY, Ls = 0.f;
+    float4 O = make_float4(0.f, 0.f, 0.f, 0.f);
+    for (int i0 = w; i0 < n_pieces; i0 += kB * kConsumerWarps) {
+      float2 ml[kB];
+      float4 o[kB];
+#pragma unroll
+      for (int u = 0; u < kB; ++u) {
+        const int i = i0 + u * kConsumerWarps;
+        const int64_t pi = seq_base + (int64_t)(i < n_pieces ? i : i0) * H + h;   // a piece that exists; dropped below
+        if (write) {
+          ml[u] = __ldcg(reinterpret_cast<const float2*>(ws_ml + pi * 2));
+          o[u] = __ldcg(reinterpret_cast<const float4*>(ws_o + pi * kD) + lane);
+        } else {
+          ml[u] = make_float2(scratch[u], scratch[u + 1]);
+          o[u] = make_float4(scratch[u], scratch[u + 1], scratch[u + 2], scratch[u + 3]);
+        }
+        if (i >= n_pieces) { ml[u].x = -INFINITY; ml[u].y = 0.f; }
+      }
+      float Mn = M;
+#pragma unroll
+      for (int u = 0; u < kB; ++u) Mn = fmaxf(Mn, ml[u].x);
+      const float Ms = fmaxf(Mn, kNegBig);
+      const float resc = fast_exp2(M - Ms);
+      Ls *= resc; O.x *= resc; O.y *= resc; O.z *= resc; O.w *= resc;
+#pragma unroll
+      for (int u = 0; u < kB; ++u) {
+        const float wgt = fast_exp2(ml[u].x - Ms);
+        Ls += ml[u].y * wgt;
+        O.x += o[u].x * wgt; O.y += o[u].y * wgt; O.z += o[u].z * wgt; O.w += o[u].w * wgt;
+      }
+      M = Mn;
+    }
+    consumer_bar();                                       // the scratch of the head before has been read
+    if (write) {
+      float* sp = scratch + (w * 32 + lane) * 6;
+      sp[0] = M; sp[1] = Ls; sp[2] = O.x; sp[3] = O.y; sp[4] = O.z; sp[5] = O.w;
+    }
+    consumer_bar();
+    if (w == 0) {
+      float Mt = -INFINITY;
+#pragma unroll
+      for (int q = 0; q < kConsumerWarps; ++q) Mt = fmaxf(Mt, scratch[(q * 32 + lane) * 6]);
+      const float Ms = fmaxf(Mt, kNegBig);
+      float Lt = 0.f;
+      float4 Ot = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+      for (int q = 0; q < kConsumerWarps; ++q) {
+        const float* sq = scratch + (q * 32 + lane) * 6;
+        const float wgt = fast_exp2(sq[0] - Ms);
+        Lt += sq[1] * wgt;
+        Ot.x += sq[2] * wgt; Ot.y += sq[3] * wgt; Ot.z += sq[4] * wgt; Ot.w += sq[5] * wgt;
+      }
+      if (write) {
+        const float inv = Lt > 0.f ? 1.f / Lt : 0.f;
+        TO* op = out + (int64_t)b * out_seq_stride + (int64_t)h * kD + lane * 4;
+        store_out4(op, Ot.x * inv, Ot.y * inv, Ot.z * inv, Ot.w * inv);
+        if (lse_out && lane == 0)
+          lse_out[(int64_t)b * H + h] = Lt > 0.f ? (Mt + log2f(Lt)) * kLn2 : -INFINITY;
+      }
     }
   }
 }
@@ -638,8 +721,10 @@ swa_decode_kernel(const Params P, const __grid_constant__ CUtensorMap map_k,
 #define SBK_V_ADDR(i) (stage + v_lane_off + ((i) >> 2) * 2048 + ((((((i) & 3) << 1) + cj_v) ^ xv) << 4))
 
   // the fold's code, once, while the first copies are on their way (two pieces of whatever the ring holds)
-  if (P.balanced && P.max_pieces > 1)
+  if (P.max_pieces > 1) {
     fold_landed<TO>(reinterpret_cast<const float*>(smem), nullptr, P.H, 0, 0, 2, out, false);
+    fold_heads<TO>(nullptr, nullptr, reinterpret_cast<float*>(smem + C::kFoldOff), nullptr, 1, 1, 0, 0, 4, 0, 1, out, false);
+  }
   for (int it = 0;; ++it) {
     const int s = it % C::kStages;
     if (!mbar_wait_bounded(bar_full + 8 * s, (it / C::kStages) & 1)) {
@@ -864,9 +949,49 @@ swa_decode_kernel(const Params P, const __grid_constant__ CUtensorMap map_k,
       continue;
     }
 
-    // ---- split sequence: whoever completes the last piece folds all of them ----
+    // ---- split sequence ----
     __threadfence();
     consumer_bar();
+    // Many pieces (at most two heads per piece): the fold goes head by head (fold_heads), and in
+    // balanced mode it is shared out. A piece that is not the sequence's last one ends its CTA's
+    // run (the sequence goes on in the next CTA's), so its CTA has nothing left to do: it counts
+    // its piece, waits until all pieces are counted and folds its share of the heads. The CTA of
+    // the last piece only counts. A second count by every participant tells the last one to
+    // finish to put the counter back to zero for the next launch. (The grid is a cooperative
+    // launch: every CTA is resident, so the wait ends.)
+    const bool by_heads = 2 * (si.n_pieces - 1) >= P.H;     // the same answer for every piece of the sequence
+    if (!PEER && P.balanced && by_heads) {
+      const bool takes_part = si.piece < si.n_pieces - 1;
+      if (threadIdx.x == 0) {
+        atomicAdd(&P.done[si.b], 1);
+        int ok = 1;
+        if (takes_part) {
+          ok = 0;
+          for (uint32_t i = 0; i < (1u << 21); ++i) {
+            if (*reinterpret_cast<volatile int32_t*>(&P.done[si.b]) >= si.n_pieces) { ok = 1; break; }
+            __nanosleep(200);   // (polls of many CTAs on one counter get in the way of the counting)
+          }
+        }
+        misc[1] = ok;
+      }
+      consumer_bar();
+      const int ok = misc[1];
+      consumer_bar();   // misc[1] may be rewritten by the next item only after everyone has read it
+      if (!takes_part) continue;
+      if (!ok) {
+        if (lane == 0) { raise_status(P.status, SBK_ST_WAIT_TIMEOUT); P.ctrl[4] = 1; misc[0] = 1; }
+        break;
+      }
+      __threadfence();
+      fold_heads<TO>(P.ws_o, P.ws_ml, reinterpret_cast<float*>(smem + C::kFoldOff), P.lse_out, P.H, P.max_pieces,
+                     P.out_seq_stride, si.b, si.n_pieces, si.piece, si.n_pieces - 1, out, true);
+      if (threadIdx.x == 0) {
+        const int prev = atomicAdd(&P.done[si.b], 1);
+        if (prev == 2 * si.n_pieces - 2) P.done[si.b] = 0;   // ready for the next launch
+      }
+      continue;
+    }
+    // ---- otherwise whoever completes the last piece folds all of them ----
     if (threadIdx.x == 0) {
       const int prev = atomicAdd(&P.done[si.b], 1);
       const int last = prev == si.n_pieces - 1;
@@ -886,7 +1011,7 @@ swa_decode_kernel(const Params P, const __grid_constant__ CUtensorMap map_k,
     const uint32_t o_bytes = (uint32_t)P.H * kD * 4u, ml_bytes = (uint32_t)P.H * 8u;
     const float* const src_o = P.ws_o + (int64_t)si.b * P.max_pieces * P.H * kD;
     const float* const src_ml = P.ws_ml + (int64_t)si.b * P.max_pieces * P.H * 2;
-    const bool land = (si.flags & kFlagFinal) && (ml_bytes & 15u) == 0 &&
+    const bool land = !by_heads && (si.flags & kFlagFinal) && (ml_bytes & 15u) == 0 &&
                       (uint32_t)si.n_pieces * (o_bytes + ml_bytes) <= (uint32_t)C::kRingBytes &&
                       ((reinterpret_cast<uintptr_t>(src_o) | reinterpret_cast<uintptr_t>(src_ml)) & 15) == 0;
     if (land) {
@@ -903,6 +1028,10 @@ swa_decode_kernel(const Params P, const __grid_constant__ CUtensorMap map_k,
         break;
       }
       fold_landed<TO>(reinterpret_cast<const float*>(smem), P.lse_out, P.H, P.out_seq_stride, si.b, si.n_pieces, out, true);
+    } else if (by_heads) {
+      // (ticket mode and the gathering form with many pieces: head by head, the shared form's arithmetic)
+      fold_heads<TO>(P.ws_o, P.ws_ml, reinterpret_cast<float*>(smem + C::kFoldOff), P.lse_out, P.H, P.max_pieces,
+                     P.out_seq_stride, si.b, si.n_pieces, 0, 1, out, true);
     } else {
       fold_pieces<TO>(P.ws_o, P.ws_ml, P.lse_out, P.H, P.max_pieces, P.out_seq_stride, si.b, si.n_pieces, out);
     }
@@ -990,7 +1119,20 @@ int launch_swa(const Params& P0, int B_total, int n_ctas, const CUtensorMap& map
     // runs); idle CTAs would otherwise be left to the block scheduler's placement, and an SM
     // whose two CTAs are both idle streams nothing.
     if (P0.balanced && 2 * P.B >= n_ctas && P.B < n_ctas) grid = P.B;
-    kern<<<grid, kThreads, C::kSmemBytes, st>>>(P, map_k, map_v, map_k2, map_v2);
+    if (P0.balanced && !PEER) {
+      // In balanced mode the CTAs of a sequence cut into many pieces wait for one another at the end
+      // (the shared fold): the grid is launched as a cooperative one, which the driver runs only
+      // with every CTA resident -- whatever else shares the GPU -- or not at all.
+      void* args[] = {(void*)&P, (void*)&map_k, (void*)&map_v, (void*)&map_k2, (void*)&map_v2};
+      const cudaError_t e = cudaLaunchCooperativeKernel((const void*)kern, dim3(grid), dim3(kThreads), args,
+                                                        (size_t)C::kSmemBytes, st);
+      if (e != cudaSuccess) {
+        set_error("sbk_swa_decode: cooperative launch of %d CTAs failed: %s", grid, cudaGetErrorString(e));
+        return SBK_E_LAUNCH;
+      }
+    } else {
+      kern<<<grid, kThreads, C::kSmemBytes, st>>>(P, map_k, map_v, map_k2, map_v2);
+    }
     int rc = check_launch("sbk_swa_decode");
     if (rc != SBK_OK) return rc;
   }
