@@ -133,6 +133,10 @@ int sbk_kv_gather(const void* k_cache, const void* v_cache, const int32_t* block
  *               chunks of the whole batch are cut into one equal run per CTA, and -split_chunks
  *               is the shortest run allowed (with max_pieces == 1 this degrades to whole
  *               sequences).  0: fixed pieces of 32 chunks. The Python wrapper's default is -8.
+ *               A balanced-mode launch is a cooperative launch (the CTAs that hold the pieces of a
+ *               sequence cut into many pieces wait for one another to share its fold): the grid of
+ *               two CTAs per SM must be resident at once, which the driver guarantees or refuses
+ *               (SBK_E_LAUNCH); it can be captured into a CUDA graph like any launch.
  *  max_pieces   upper bound on the pieces of one sequence (sizes the workspace); >= 1
  *  item_cost    balanced mode only: what starting and finishing a sequence is charged, in chunks,
  *               when the runs are made equal in cost (< 0: the library's tuned value, 8)
