@@ -218,6 +218,41 @@ def test_swa_decode_balanced_runs(ops, split_chunks, max_pieces):
     _check_attn(out, ref, lse, lse_ref)
 
 
+@pytest.mark.parametrize("lens,H,kvh", [([8193], 28, 4), ([8193, 5000, 4097], 28, 4), ([8193], 7, 1), ([6000, 8193], 14, 2)])
+def test_swa_decode_few_long_sequences_share_their_fold(ops, lens, H, kvh):
+    """Few sequences per launch are cut into many pieces (33 at one sequence); their fold goes head by
+    head and is shared out over the CTAs that hold the pieces, which wait for one another (cooperative
+    launch). Against the oracle, launch after launch on one workspace (the piece counters must come
+    back to zero), with the log-sum-exp, and against the ticket mode's result."""
+    D, bs, wl = 128, 16, 4096
+    kv, table, nb = make_paged_kv(lens, wl, kvh, D, bs, seed=91)
+    g = torch.Generator().manual_seed(92)
+    q = (torch.randn(len(lens), H, D, generator=g) / math.sqrt(D)).bfloat16()
+    ref, lse_ref = ref_ops.swa_paged_decode_ref(q, kv[0], kv[1], table, lens, wl, D ** -0.5, return_lse=True)
+    kv_d, q_d, table_d = kv.to(DEV), q.to(DEV), table.to(DEV)
+    lens_d = torch.tensor(lens, dtype=torch.int32, device=DEV)
+    v = min(table.shape[1] * bs, wl + 1)
+    split = ops.swa_auto_split(len(lens), v, torch.device(DEV))
+    mp = ops.swa_max_pieces(v, split)
+    assert split < 0 and 2 * (mp - 1) >= H          # balanced, and enough pieces for the head-by-head form
+    ws = ops.swa_workspace(len(lens), H, D, mp, DEV)
+    st = _status()
+    outs = []
+    for _ in range(4):
+        lse = torch.empty(len(lens), H, dtype=torch.float32, device=DEV)
+        outs.append(ops.swa_decode(q_d, kv_d[0], kv_d[1], table_d, lens_d, window_left=wl, lse=lse, workspace=ws,
+                                   max_pieces=mp, split_chunks=split, status=st))
+        torch.cuda.synchronize()
+        assert st.item() == 0
+        _check_attn(outs[-1].cpu(), ref, lse.cpu(), lse_ref)
+        assert torch.equal(outs[-1], outs[0])
+    head = ws[:32 + 4 * ((len(lens) + 3) // 4 * 4)].view(torch.int32)
+    assert not head.any()                            # tickets, counters and the stale mark are back at zero
+    ticket = ops.swa_decode(q_d, kv_d[0], kv_d[1], table_d, lens_d, window_left=wl, split_chunks=8, max_pieces=mp, status=st)
+    assert st.item() == 0
+    assert float((ticket.float() - outs[0].float()).abs().max()) <= 2.0 ** -7 * float(outs[0].float().abs().max())
+
+
 @pytest.mark.parametrize("H,kvh", [(7, 1), (14, 2), (28, 4)])
 def test_swa_decode_balanced_head_layouts_and_many_sequences(ops, H, kvh):
     """More sequences than CTAs, lengths from 0 to a few windows, every kv-head layout (stages of
