@@ -31,9 +31,12 @@
 //   a bf16 remainder (two MMAs), which keeps the rounding of the probabilities below the
 //   bf16 rounding of the output.
 // Split-K
-//   A sequence with several pieces writes un-normalised partials (m, l, O) to the workspace;
-//   the CTA that completes the last piece of a sequence (a counter per sequence) folds them
-//   and writes the output, so there is no second kernel. A single piece writes `out` directly.
+//   A sequence with several pieces writes un-normalised partials (m, l, O) to the workspace and
+//   counts them (a counter per sequence); there is no second kernel. Few pieces: the CTA that
+//   counts last folds them (out of its idle ring when the piece was its last item, else through
+//   registers). Many pieces (at most two heads per piece): head by head, and in balanced mode
+//   shared out over the CTAs that hold the pieces, which wait for one another -- balanced-mode
+//   launches are cooperative launches. A single piece writes `out` directly.
 // HBM-bound: min(seq_len, window_left+1) * kvh*128*2*2 bytes read per sequence.
 #include "sbk_common.cuh"
 #include "sbk_tma.cuh"
